@@ -1,0 +1,569 @@
+// Prefill NVFP4 linear for sm_100a: BF16 -> NVFP4 activation quantiser and a
+// warp-specialised tcgen05 block-scaled GEMM (kind::mxf4nvf4, scale_vec::4X) with
+// TMA-fed shared-memory stages and the accumulator in tensor memory.
+//
+// D[token][feature] = g_w * g_a * sum_terms sum_k A_term[token][k] * W[feature][k]
+//   A operand: quantised activations, 128 token rows per tile (UMMA M = 128)
+//   B operand: weights, up to 256 feature rows per tile (UMMA N = 128 or 256)
+//   both K-major, packed two E2M1 codes per byte, 128-byte swizzled rows of 256 k
+//   block scales: 512-byte atoms (128 rows x 4 scales) copied smem -> TMEM by tcgen05.cp
+//
+// One persistent CTA per SM, 192 threads: warp 0 issues TMA, warp 1 owns tensor memory
+// and issues the MMAs, warps 2..5 drain the accumulator (tcgen05.ld), scale, round to
+// BF16 and store. Every mbarrier wait is bounded: a wait that runs out records a code in
+// the plan's status word, raises a CTA-wide abort flag, and all roles fall through to the
+// common exit where tensor memory is released.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "nvfp4_internal.h"
+#include "nvfp4_layout.cuh"
+
+namespace augur_sm100 {
+namespace {
+
+static_assert(sizeof(augur_cuda_nvfp4_sm100_act_quant_args_v1) == 56, "act_quant ABI");
+static_assert(sizeof(augur_cuda_nvfp4_sm100_gemm_args_v1) == 80, "gemm ABI");
+
+constexpr uint32_t kTileM = 128;          // tokens per tile
+constexpr uint32_t kTileN = 256;          // features per tile (128 for a ragged last tile)
+constexpr uint32_t kBlockK = 256;         // k per shared-memory stage = one 128-byte swizzled row
+constexpr uint32_t kStages = 4;
+constexpr uint32_t kBytesA = kTileM * 128;            // 16 KB
+constexpr uint32_t kBytesB = kTileN * 128;            // 32 KB
+constexpr uint32_t kBytesSfA = 4 * kSfAtomBytes;      // 2 KB: 4 atoms (k) of one 128-row block
+constexpr uint32_t kBytesSfB = 8 * kSfAtomBytes;      // 4 KB: 2 row blocks x 4 atoms
+constexpr uint32_t kStageBytes = kBytesA + kBytesB + kBytesSfA + kBytesSfB;  // 55296
+constexpr uint32_t kGemmSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr uint32_t kGemmThreads = 192;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kTmemAcc = 0;          // 256 accumulator columns
+constexpr uint32_t kTmemSfA = 256;        // 2 x 16 columns (k-block parity)
+constexpr uint32_t kTmemSfB = 320;        // 2 x 32 columns
+constexpr uint32_t kWaitLimit = 20u * 1000u * 1000u;
+
+constexpr uint32_t kErrProducerWait = 0x101, kErrMmaWaitFull = 0x102, kErrMmaWaitTmem = 0x103,
+                   kErrEpilogueWait = 0x104;
+
+// ---- PTX wrappers ---------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+// Bounded wait. Returns false (after raising the abort flag) if the phase never completes
+// or if another role already aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                          uint32_t* status_word, uint32_t code) {
+    for (uint32_t spin = 0; spin < kWaitLimit; ++spin) {
+        if (mbar_test(bar, parity)) return true;
+        if ((spin & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicCAS(status_word, 0u, code);
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t x, uint32_t y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_copy_sf(uint32_t tmem, uint64_t desc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                       uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %6, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n}"
+        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tc_load32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptors (64-bit): start address >> 4 in bits [0,14), leading
+// byte offset >> 4 in [16,30), stride byte offset >> 4 in [32,46), descriptor version 1 in
+// [46,48), swizzle mode in [61,64) (0 = none, 2 = 128-byte).
+// K-major 128-byte-swizzled operand tile: rows are 128 bytes apart, 8-row groups 1024 bytes.
+__device__ __forceinline__ uint64_t operand_desc(uint32_t smem_addr) {
+    return static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) |
+           (uint64_t(1) << 46) | (uint64_t(2) << 61);
+}
+// Scale-factor atom for tcgen05.cp 32x128b: 32 rows of 16 bytes, 8-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t sf_desc(uint32_t smem_addr) {
+    return static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4) | (uint64_t(128 >> 4) << 32) | (uint64_t(1) << 46);
+}
+// Instruction descriptor, block-scaled: A/B format E2M1 (1) at bits [7,10) / [10,13), both
+// K-major, N >> 3 at [17,23), scale format UE4M3 (0) at bit 23, M >> 4 at [24,29), K = 64.
+__device__ __forceinline__ uint32_t instr_desc(uint32_t n) {
+    return (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((kTileM >> 4) << 24);
+}
+
+struct GemmParams {
+    const uint8_t* weight_sf;      // scale region of the weight tensor
+    const uint8_t* act_sf;         // scale region of term 0; terms are `act_term_stride` bytes apart
+    uint64_t act_term_stride;
+    __nv_bfloat16* out;
+    uint32_t* status_word;
+    uint32_t rows, cols, tokens, terms;
+    float scale;                   // g_w * g_a
+};
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant__ CUtensorMap map_weight,
+            const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    // 128-byte swizzled tiles need 1024-byte alignment.
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+    // bars[0..S) full, [S..2S) empty, [2S] tmem_full, [2S+1] tmem_empty; then tmem base + abort flag
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 2);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + kStages);
+    const uint32_t bar_tmem_full = smem_u32(bars + 2 * kStages), bar_tmem_empty = smem_u32(bars + 2 * kStages + 1);
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < kStages; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        mbar_init(bar_tmem_full, 1);
+        mbar_init(bar_tmem_empty, 4);   // one arrival per epilogue warp
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const uint32_t m_tiles = p.tokens / kTileM;
+    const uint32_t n_tiles = (p.rows + kTileN - 1) / kTileN;
+    const uint32_t total_tiles = m_tiles * n_tiles;
+    const uint32_t k_blocks = (p.cols + kBlockK - 1) / kBlockK;
+    const uint32_t steps = k_blocks * p.terms;              // pipeline steps per tile
+    const uint64_t sf_atoms_per_row_block = p.cols / 64;    // atoms along k
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- TMA producer ----------------
+        uint32_t stage = 0, phase = 0;
+        bool alive = true;
+        for (uint32_t tile = blockIdx.x; alive && tile < total_tiles; tile += gridDim.x) {
+            const uint32_t m_tile = tile % m_tiles, n_tile = tile / m_tiles;
+            const uint32_t n_rows = min(kTileN, p.rows - n_tile * kTileN);
+            for (uint32_t step = 0; step < steps; ++step) {
+                const uint32_t kb = step / p.terms, term = step % p.terms;
+                const uint32_t k_valid = min(kBlockK, p.cols - kb * kBlockK);   // multiple of 64
+                const uint32_t sf_bytes = k_valid / 64 * kSfAtomBytes;
+                if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status_word, kErrProducerWait)) {
+                    alive = false;
+                    break;
+                }
+                uint8_t* base = smem + stage * kStageBytes;
+                const uint32_t full = bar_full + 8 * stage;
+                const uint32_t row_blocks_b = n_rows / 128;
+                mbar_expect_tx(full, kBytesA + n_rows * 128 + sf_bytes * (1 + row_blocks_b));
+                tma_load_2d(smem_u32(base), &map_act, kb * 128, term * p.tokens + m_tile * kTileM, full);
+                tma_load_2d(smem_u32(base + kBytesA), &map_weight, kb * 128, n_tile * kTileN, full);
+                if (n_rows > 128) {
+                    tma_load_2d(smem_u32(base + kBytesA + 128 * 128), &map_weight, kb * 128, n_tile * kTileN + 128, full);
+                }
+                const uint8_t* sfa = p.act_sf + term * p.act_term_stride +
+                                     (static_cast<uint64_t>(m_tile) * sf_atoms_per_row_block + kb * 4) * kSfAtomBytes;
+                bulk_load(smem_u32(base + kBytesA + kBytesB), sfa, sf_bytes, full);
+                for (uint32_t rb = 0; rb < row_blocks_b; ++rb) {
+                    const uint8_t* sfb = p.weight_sf +
+                        ((static_cast<uint64_t>(n_tile) * 2 + rb) * sf_atoms_per_row_block + kb * 4) * kSfAtomBytes;
+                    bulk_load(smem_u32(base + kBytesA + kBytesB + kBytesSfA + rb * kBytesSfA), sfb, sf_bytes, full);
+                }
+                if (++stage == kStages) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- MMA issuer ----------------
+        uint32_t stage = 0, phase = 0, tmem_phase = 0, sf_buffer = 0;
+        bool alive = true;
+        for (uint32_t tile = blockIdx.x; alive && tile < total_tiles; tile += gridDim.x) {
+            const uint32_t n_tile = tile / m_tiles;
+            const uint32_t n_rows = min(kTileN, p.rows - n_tile * kTileN);
+            const uint32_t idesc = instr_desc(n_rows);
+            // the epilogue must have drained the previous tile's accumulator
+            if (!mbar_wait(bar_tmem_empty, tmem_phase ^ 1, abort_flag, p.status_word, kErrMmaWaitTmem)) break;
+            tc_fence_after();
+            for (uint32_t step = 0; step < steps; ++step) {
+                const uint32_t kb = step / p.terms;
+                const uint32_t k_valid = min(kBlockK, p.cols - kb * kBlockK);
+                if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status_word, kErrMmaWaitFull)) {
+                    alive = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t base = smem_u32(smem + stage * kStageBytes);
+                const uint32_t sfa_smem = base + kBytesA + kBytesB, sfb_smem = sfa_smem + kBytesSfA;
+                const uint32_t tmem_sfa = tmem_base + kTmemSfA + sf_buffer * 16;
+                const uint32_t tmem_sfb = tmem_base + kTmemSfB + sf_buffer * 32;
+                const uint64_t a_desc = operand_desc(base), b_desc = operand_desc(base + kBytesA);
+                for (uint32_t k = 0; k < k_valid / 64; ++k) {
+                    tc_copy_sf(tmem_sfa + 4 * k, sf_desc(sfa_smem + k * kSfAtomBytes));
+                    tc_copy_sf(tmem_sfb + 8 * k, sf_desc(sfb_smem + k * kSfAtomBytes));
+                    if (n_rows > 128) tc_copy_sf(tmem_sfb + 8 * k + 4, sf_desc(sfb_smem + kBytesSfA + k * kSfAtomBytes));
+                    // each MMA consumes 64 k = 32 bytes of every row: advance the start address by 32 >> 4
+                    tc_mma(tmem_base + kTmemAcc, a_desc + 2 * k, b_desc + 2 * k, idesc, tmem_sfa + 4 * k,
+                           tmem_sfb + 8 * k, (step | k) ? 1u : 0u);
+                }
+                tc_commit(bar_empty + 8 * stage);   // frees the stage when these MMAs have read it
+                sf_buffer ^= 1;
+                if (++stage == kStages) { stage = 0; phase ^= 1; }
+            }
+            if (alive) tc_commit(bar_tmem_full);      // accumulator complete
+            tmem_phase ^= 1;
+        }
+    } else if (warp >= 2) {
+        // ---------------- epilogue: TMEM -> registers -> BF16 -> global ----------------
+        const uint32_t quadrant = warp & 3;          // TMEM lanes this warp may read: 32*quadrant..+31
+        uint32_t tmem_phase = 0;
+        for (uint32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            const uint32_t m_tile = tile % m_tiles, n_tile = tile / m_tiles;
+            const uint32_t n_rows = min(kTileN, p.rows - n_tile * kTileN);
+            if (!mbar_wait(bar_tmem_full, tmem_phase, abort_flag, p.status_word, kErrEpilogueWait)) break;
+            tc_fence_after();
+            const uint32_t token = m_tile * kTileM + quadrant * 32 + lane;
+            __nv_bfloat16* out_row = p.out + static_cast<uint64_t>(token) * p.rows + n_tile * kTileN;
+            for (uint32_t c = 0; c < n_rows; c += 32) {
+                uint32_t v[32];
+                tc_load32(tmem_base + kTmemAcc + ((quadrant * 32) << 16) + c, v);
+                tc_wait_ld();
+                uint32_t packed[16];
+#pragma unroll
+                for (uint32_t i = 0; i < 16; ++i) {
+                    const __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(v[2 * i]) * p.scale,
+                                                                      __uint_as_float(v[2 * i + 1]) * p.scale);
+                    packed[i] = *reinterpret_cast<const uint32_t*>(&pair);
+                }
+                uint4* dst = reinterpret_cast<uint4*>(out_row + c);
+#pragma unroll
+                for (uint32_t i = 0; i < 4; ++i) {
+                    dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tmem_empty);
+            tmem_phase ^= 1;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ---- activation quantiser ------------------------------------------------------------------
+// Smallest positive E4M3 code whose value is >= d (d > 0), 126 if none.
+__device__ __forceinline__ uint32_t e4m3_ceil_code(float d) {
+    if (d > 448.0f) return 126;
+    if (d <= 0x1p-6f) {                          // subnormal range: multiples of 2^-9, and 2^-6 itself
+        const float steps = d * 512.0f;          // exact
+        uint32_t m = static_cast<uint32_t>(ceilf(steps));
+        return m < 1 ? 1 : m;                     // m == 8 is code 8 = 2^-6
+    }
+    const uint32_t bits = __float_as_uint(d);
+    uint32_t exponent = (bits >> 23) - 127 + 7;  // E4M3 biased exponent, >= 1 here
+    uint32_t mantissa = (bits >> 20) & 7;
+    if (bits & 0xfffffu) ++mantissa;             // round up
+    if (mantissa == 8) { mantissa = 0; ++exponent; }
+    return exponent * 8 + mantissa;
+}
+
+__device__ __forceinline__ float e4m3_positive_value(uint32_t code) {
+    const uint32_t exponent = code >> 3, mantissa = code & 7;
+    return exponent == 0 ? static_cast<float>(mantissa) * 0x1p-9f
+                         : __uint_as_float(((exponent + 120) << 23) | (mantissa << 20));
+}
+
+// Nearest E2M1 level; a tie goes to the smaller magnitude; zero is always code 0.
+__device__ __forceinline__ uint32_t e2m1_nearest(float v, float* level) {
+    const float a = fabsf(v);
+    uint32_t m;
+    float l;
+    if (a <= 0.25f) { m = 0; l = 0.0f; }
+    else if (a <= 0.75f) { m = 1; l = 0.5f; }
+    else if (a <= 1.25f) { m = 2; l = 1.0f; }
+    else if (a <= 1.75f) { m = 3; l = 1.5f; }
+    else if (a <= 2.5f) { m = 4; l = 2.0f; }
+    else if (a <= 3.5f) { m = 5; l = 3.0f; }
+    else if (a <= 5.0f) { m = 6; l = 4.0f; }
+    else { m = 7; l = 6.0f; }
+    const bool negative = v < 0.0f && m != 0;
+    *level = negative ? -l : l;
+    return negative ? (m | 8u) : m;
+}
+
+// One thread per (token, 16-element group). Destination: the code planes of all terms
+// stacked ([terms][tokens][cols/2], one TMA tensor of terms*tokens rows), then the scale
+// regions of all terms.
+__global__ void act_quant_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ destination, uint32_t tokens,
+                                 uint32_t cols, uint32_t terms, float global_scale) {
+    const uint32_t groups = cols / 16;
+    const uint64_t index = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (index >= static_cast<uint64_t>(tokens) * groups) return;
+    const uint32_t token = static_cast<uint32_t>(index / groups), group = static_cast<uint32_t>(index % groups);
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<uint64_t>(token) * cols + group * 16);
+    const uint4 lo = __ldg(src), hi = __ldg(src + 1);
+    const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+    float residual[16];
+#pragma unroll
+    for (uint32_t i = 0; i < 8; ++i) {
+        residual[2 * i] = __uint_as_float(words[i] << 16);
+        residual[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000u);
+    }
+    const uint64_t code_bytes = tcgen05_codes_bytes(tokens, cols), scale_bytes = tcgen05_scale_bytes(tokens, cols);
+    for (uint32_t term = 0; term < terms; ++term) {
+        float maximum = 0.0f;
+#pragma unroll
+        for (uint32_t i = 0; i < 16; ++i) maximum = fmaxf(maximum, fabsf(residual[i]));
+        const float desired = __fdiv_rn(maximum, __fmul_rn(6.0f, global_scale));
+        uint32_t scale_code = 0;
+        float scale = 0.0f;
+        if (desired > 0.0f) {
+            scale_code = e4m3_ceil_code(desired);
+            scale = e4m3_positive_value(scale_code);
+        }
+        const float divisor = __fmul_rn(scale, global_scale);
+        uint32_t packed[2] = {0, 0};
+#pragma unroll
+        for (uint32_t i = 0; i < 16; ++i) {
+            float normalized = divisor == 0.0f ? 0.0f : __fdiv_rn(residual[i], divisor);
+            normalized = fminf(fmaxf(normalized, -6.0f), 6.0f);
+            float level;
+            const uint32_t code = e2m1_nearest(normalized, &level);
+            packed[i >> 3] |= code << (4 * (i & 7));
+            residual[i] = __fsub_rn(residual[i], __fmul_rn(level, divisor));
+        }
+        *reinterpret_cast<uint2*>(destination + term * code_bytes + static_cast<uint64_t>(token) * (cols / 2) + group * 8) =
+            make_uint2(packed[0], packed[1]);
+        destination[terms * code_bytes + term * scale_bytes + tcgen05_scale_offset(token, group, cols)] =
+            static_cast<uint8_t>(scale_code);
+    }
+}
+
+// ---- tensor maps --------------------------------------------------------------------------------
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_entry() {
+    static EncodeTiled cached = [] {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult query = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &query) != cudaSuccess ||
+            query != cudaDriverEntryPointSuccess) {
+            cudaGetLastError();
+            fn = nullptr;
+        }
+        return reinterpret_cast<EncodeTiled>(fn);
+    }();
+    return cached;
+}
+
+// Packed codes as a 2-D byte tensor [rows][cols/2]; boxes of 128 rows x 128 bytes, 128-byte swizzle.
+// A host-side computation: no allocation and no device access.
+bool make_code_map(CUtensorMap* map, uint64_t address, uint64_t rows, uint32_t cols) {
+    const EncodeTiled encode = encode_entry();
+    if (!encode) return false;
+    const cuuint64_t dims[2] = {cols / 2, rows};
+    const cuuint64_t strides[1] = {cols / 2};
+    const cuuint32_t box[2] = {128, 128};
+    const cuuint32_t element_strides[2] = {1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, reinterpret_cast<void*>(address), dims, strides, box,
+                  element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// ---- validation ------------------------------------------------------------------------------------
+bool act_shape_ok(uint32_t tokens, uint32_t cols, uint32_t terms) {
+    return tokens && cols && tokens % kTileM == 0 && cols % 64 == 0 && terms >= 1 && terms <= 3 &&
+           static_cast<uint64_t>(tokens) * cols <= UINT32_MAX;
+}
+
+bool check_act_quant(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_act_quant_args_v1* a, bool full,
+                     augur_cuda_result_v1* failure) {
+    *failure = invalid();
+    if (!header_ok(d, s, a)) {
+        if (a && s && d >= 0 && s->ordinal == d && a->abi_version != AUGUR_CUDA_ABI_VERSION_V1) {
+            *failure = make_result(AUGUR_CUDA_STATUS_ABI_VERSION_MISMATCH);
+        }
+        return false;
+    }
+    if (!act_shape_ok(a->tokens, a->cols, a->terms) || !std::isfinite(a->global_scale) || a->global_scale <= 0.0f) {
+        return false;
+    }
+    if (a->input_len_bytes != static_cast<uint64_t>(a->tokens) * a->cols * 2 ||
+        a->destination_len_bytes != a->terms * tcgen05_extent_bytes(a->tokens, a->cols)) {
+        return false;
+    }
+    const Range r[2] = {{a->input_bf16, a->input_len_bytes, 16}, {a->destination, a->destination_len_bytes, 256}};
+    if (!all_disjoint(r, 2)) return false;
+    return !full || inspect_device_ranges(d, r, 2, failure);
+}
+
+bool check_gemm(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* plan,
+                const augur_cuda_nvfp4_sm100_gemm_args_v1* a, bool full, augur_cuda_result_v1* failure) {
+    *failure = invalid();
+    if (!header_ok(d, s, a)) {
+        if (a && s && d >= 0 && s->ordinal == d && a->abi_version != AUGUR_CUDA_ABI_VERSION_V1) {
+            *failure = make_result(AUGUR_CUDA_STATUS_ABI_VERSION_MISMATCH);
+        }
+        return false;
+    }
+    if (!plan_ok(plan, d, s) || !act_shape_ok(a->tokens, a->cols, a->activation_terms)) return false;
+    if (!a->rows || a->rows % 128 != 0 || static_cast<uint64_t>(a->rows) * a->cols > UINT32_MAX) return false;
+    if (!scale_ok(a->weight_global_scale) || !std::isfinite(a->activation_global_scale) ||
+        a->activation_global_scale <= 0.0f) {
+        return false;
+    }
+    if (a->weight_len_bytes != tcgen05_extent_bytes(a->rows, a->cols) ||
+        a->activation_len_bytes != a->activation_terms * tcgen05_extent_bytes(a->tokens, a->cols) ||
+        a->output_len_bytes != static_cast<uint64_t>(a->tokens) * a->rows * 2) {
+        return false;
+    }
+    const Range r[4] = {{a->weight, a->weight_len_bytes, 256},
+                        {a->activation, a->activation_len_bytes, 256},
+                        {a->output_bf16, a->output_len_bytes, 16},
+                        plan_scratch_range(plan)};
+    if (!all_disjoint(r, 4)) return false;
+    return !full || inspect_device_ranges(d, r, 3, failure);
+}
+
+}  // namespace
+
+cudaError_t gemm_configure_device() {
+    return cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
+}
+
+}  // namespace augur_sm100
+
+using namespace augur_sm100;
+
+extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_scratch_extent_host_v1(
+    uint32_t rows, uint32_t cols, uint32_t tokens, uint32_t activation_terms, uint64_t* out_bytes) {
+    if (!out_bytes || !rows || rows % 128 != 0 || !act_shape_ok(tokens, cols, activation_terms)) return invalid();
+    // The GEMM itself needs no scratch; a caller that lets the plan stage the quantised
+    // activations needs this much.
+    *out_bytes = activation_terms * tcgen05_extent_bytes(tokens, cols);
+    return ok();
+}
+
+extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_act_quant_preflight_v1(
+    int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_act_quant_args_v1* a) {
+    augur_cuda_result_v1 failure;
+    return check_act_quant(d, s, a, true, &failure) ? ok() : failure;
+}
+
+extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_act_quant_prevalidated_submit_v1(
+    int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_act_quant_args_v1* a) {
+    augur_cuda_result_v1 failure;
+    if (!check_act_quant(d, s, a, false, &failure)) return failure;
+    if (consume_injected_fault()) return make_result(AUGUR_CUDA_STATUS_DIAGNOSTIC_FAULT_INJECTED);
+    const cudaError_t e = cudaSetDevice(d);
+    if (e != cudaSuccess) return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE, e);
+    const uint64_t groups = static_cast<uint64_t>(a->tokens) * (a->cols / 16);
+    // Padding scale bytes of the destination are never read for tokens % 128 == 0.
+    act_quant_kernel<<<static_cast<uint32_t>((groups + 255) / 256), 256, 0, s->stream>>>(
+        reinterpret_cast<const uint16_t*>(a->input_bf16), reinterpret_cast<uint8_t*>(a->destination), a->tokens,
+        a->cols, a->terms, a->global_scale);
+    count_launch();
+    return submitted();
+}
+
+extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_bf16_preflight_v1(
+    int32_t d, augur_cuda_stream_t s, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_gemm_args_v1* a) {
+    augur_cuda_result_v1 failure;
+    if (!check_gemm(d, s, plan, a, true, &failure)) return failure;
+    CUtensorMap probe;
+    return make_code_map(&probe, a->weight, a->rows, a->cols) ? ok() : make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE);
+}
+
+extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_bf16_prevalidated_submit_v1(
+    int32_t d, augur_cuda_stream_t s, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_gemm_args_v1* a) {
+    augur_cuda_result_v1 failure;
+    if (!check_gemm(d, s, plan, a, false, &failure)) return failure;
+    if (consume_injected_fault()) return make_result(AUGUR_CUDA_STATUS_DIAGNOSTIC_FAULT_INJECTED);
+    const cudaError_t e = cudaSetDevice(d);
+    if (e != cudaSuccess) return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE, e);
+    // Tensor maps are encoded on the host into kernel parameter space: no allocation, no driver query.
+    // The activation map spans the stacked code planes of all terms (terms * tokens rows).
+    CUtensorMap map_act, map_weight;
+    if (!make_code_map(&map_weight, a->weight, a->rows, a->cols) ||
+        !make_code_map(&map_act, a->activation, static_cast<uint64_t>(a->activation_terms) * a->tokens, a->cols)) {
+        return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE);
+    }
+    GemmParams p{};
+    p.weight_sf = reinterpret_cast<const uint8_t*>(a->weight) + tcgen05_codes_bytes(a->rows, a->cols);
+    p.act_sf = reinterpret_cast<const uint8_t*>(a->activation) + a->activation_terms * tcgen05_codes_bytes(a->tokens, a->cols);
+    p.act_term_stride = tcgen05_scale_bytes(a->tokens, a->cols);
+    p.out = reinterpret_cast<__nv_bfloat16*>(a->output_bf16);
+    p.status_word = plan->status_word;
+    p.rows = a->rows; p.cols = a->cols; p.tokens = a->tokens; p.terms = a->activation_terms;
+    p.scale = a->weight_global_scale * a->activation_global_scale;
+    const uint32_t m_tiles = a->tokens / kTileM, n_tiles = (a->rows + kTileN - 1) / kTileN;
+    uint32_t grid = m_tiles * n_tiles;
+    if (grid > plan->sm_count) grid = plan->sm_count;
+    gemm_kernel<<<grid, kGemmThreads, kGemmSmemBytes, s->stream>>>(map_act, map_weight, p);
+    count_launch();
+    return submitted();
+}

@@ -1,0 +1,395 @@
+"""Host-side owners and checked bindings over the C ABI, for Python callers.
+
+The classes mirror the reference's safe wrappers in crates/augur-backend:
+owners of device resources (``cuda_runtime.rs``: OwnedCudaStream / OwnedCudaBuffer),
+an uploaded-and-repacked weight (``cuda_qwen35_qpn.rs:97-131``,
+``OwnedCudaQwen35QpnWeightV1::upload_checkpoint_nvfp4``), a retained projection
+that is preflighted once and then only submitted
+(``cuda_qwen35_prefill_cublas/qpn.rs:60-105``) and the FFN program
+(``qpn.rs:391-492``, ``CudaQwen35QpnFfnProgramV1``). torch is used for device
+memory and stream plumbing only; every computation goes through the C ABI.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import byref, c_uint32, c_uint64, c_void_p
+
+import numpy as np
+import torch
+
+from . import abi
+
+
+class CudaRuntimeError(RuntimeError):
+    """A non-OK ``augur_cuda_result_v1`` (crates/augur-backend/src/cuda_runtime.rs CudaRuntimeError)."""
+
+    def __init__(self, where: str, status: int, raw: int):
+        super().__init__(f"{where}: status {status}, cuda {raw}")
+        self.where, self.status, self.raw = where, status, raw
+
+
+def _check(where: str, result: abi.Result) -> None:
+    if result.status != abi.STATUS_OK:
+        raise CudaRuntimeError(where, result.status, result.raw_cuda_status)
+
+
+def _ptr(t: torch.Tensor) -> int:
+    return t.data_ptr()
+
+
+def _nbytes(t: torch.Tensor) -> int:
+    return t.numel() * t.element_size()
+
+
+class Stream:
+    """An ABI stream handle wrapping a torch CUDA stream (the current one by default)."""
+
+    def __init__(self, device: int | None = None, torch_stream: torch.cuda.Stream | None = None):
+        self.ordinal = torch.cuda.current_device() if device is None else int(device)
+        self.torch_stream = torch_stream or torch.cuda.current_stream(self.ordinal)
+        self.handle = c_void_p()
+        _check("stream_adopt", abi.lib().augur_cuda_nvfp4_sm100_stream_adopt_v1(
+            self.ordinal, c_void_p(self.torch_stream.cuda_stream), byref(self.handle)))
+
+    def synchronize(self) -> None:
+        _check("stream_synchronize", abi.lib().augur_cuda_nvfp4_sm100_stream_synchronize_v1(self.handle))
+
+    def close(self) -> None:
+        if self.handle:
+            abi.lib().augur_cuda_nvfp4_sm100_stream_destroy_v1(self.handle)
+            self.handle = c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Plan:
+    """Stream-owned scratch (split-K partials, arrival counters, activation staging)."""
+
+    def __init__(self, stream: Stream, scratch_bytes: int):
+        self.stream = stream
+        self.handle = c_void_p()
+        _check("plan_create", abi.lib().augur_cuda_nvfp4_sm100_plan_create_v1(
+            stream.ordinal, stream.handle, c_uint64(scratch_bytes), byref(self.handle)))
+
+    def snapshot(self) -> abi.PlanSnapshot:
+        snap = abi.header(abi.PlanSnapshot)
+        _check("plan_describe", abi.lib().augur_cuda_nvfp4_sm100_plan_describe_v1(self.handle, byref(snap)))
+        return snap
+
+    def device_status(self) -> int:
+        word = c_uint32()
+        _check("plan_device_status", abi.lib().augur_cuda_nvfp4_sm100_plan_device_status_v1(self.handle, byref(word)))
+        return int(word.value)
+
+    def close(self) -> None:
+        if self.handle:
+            abi.lib().augur_cuda_nvfp4_sm100_plan_destroy_v1(self.handle)
+            self.handle = c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def gemv_scratch_bytes(rows: int, cols: int, tokens: int = 8) -> int:
+    out = c_uint64()
+    _check("gemv_scratch_extent", abi.lib().augur_cuda_nvfp4_sm100_gemv_scratch_extent_host_v1(
+        rows, cols, tokens, byref(out)))
+    return int(out.value)
+
+
+def repack_extent(layout: int, rows: int, cols: int) -> int:
+    out = c_uint64()
+    _check("repack_extent", abi.lib().augur_cuda_nvfp4_sm100_repack_extent_host_v1(layout, rows, cols, byref(out)))
+    return int(out.value)
+
+
+def _u8p(a: np.ndarray | None):
+    if a is None:
+        return ctypes.cast(None, abi._U8P)
+    return a.ctypes.data_as(abi._U8P)
+
+
+def repack_host(layout: int, rows: int, cols: int, codes, scales, codes_b=None, scales_b=None) -> np.ndarray:
+    """Host-memory repack (same permutation as the device kernel)."""
+    codes = np.ascontiguousarray(codes, dtype=np.uint8)
+    scales = np.ascontiguousarray(scales, dtype=np.uint8)
+    if codes_b is not None:
+        codes_b = np.ascontiguousarray(codes_b, dtype=np.uint8)
+        scales_b = np.ascontiguousarray(scales_b, dtype=np.uint8)
+    out = np.zeros(repack_extent(layout, rows, cols), dtype=np.uint8)
+    _check("repack_host", abi.lib().augur_cuda_nvfp4_sm100_repack_host_v1(
+        layout, rows, cols, _u8p(codes), _u8p(scales), _u8p(codes_b), _u8p(scales_b), _u8p(out), c_uint64(out.size)))
+    return out
+
+
+def unpack_host(layout: int, rows: int, cols: int, packed: np.ndarray):
+    packed = np.ascontiguousarray(packed, dtype=np.uint8)
+    pair = layout == abi.LAYOUT_STREAM_PAIR
+    codes = np.zeros((rows, cols // 2), dtype=np.uint8)
+    scales = np.zeros((rows, cols // 16), dtype=np.uint8)
+    codes_b = np.zeros_like(codes) if pair else None
+    scales_b = np.zeros_like(scales) if pair else None
+    _check("unpack_host", abi.lib().augur_cuda_nvfp4_sm100_unpack_host_v1(
+        layout, rows, cols, _u8p(packed), c_uint64(packed.size), _u8p(codes), _u8p(scales), _u8p(codes_b), _u8p(scales_b)))
+    return (codes, scales, codes_b, scales_b) if pair else (codes, scales)
+
+
+class Nvfp4Sm100Weight:
+    """A weight uploaded to the device and repacked into one hot layout.
+
+    Mirrors ``OwnedCudaQwen35QpnWeightV1::upload_checkpoint_nvfp4``
+    (crates/augur-backend/src/cuda_qwen35_qpn.rs:97-131): host-side checks
+    (shape, extents, block scales < 127, global scale in [2^-32, 24]), upload of
+    the compact planes, repack preflight + submit on the device, synchronise.
+    """
+
+    def __init__(self, stream: Stream, layout: int, rows: int, cols: int, packed: torch.Tensor,
+                 global_scale: float, global_scale_b: float = 0.0):
+        self.stream, self.layout, self.rows, self.cols = stream, layout, rows, cols
+        self.packed, self.global_scale, self.global_scale_b = packed, float(global_scale), float(global_scale_b)
+
+    @staticmethod
+    def checked_checkpoint(rows: int, cols: int, codes: np.ndarray, scales: np.ndarray, global_scale: float):
+        if codes.size != rows * cols // 2 or scales.size != rows * cols // 16:
+            raise ValueError("plane extent mismatch")
+        if int(scales.max(initial=0)) >= 127:
+            raise ValueError("negative or NaN block scale")
+        if not (np.isfinite(global_scale) and 2.0 ** -32 <= global_scale <= 24.0):
+            raise ValueError("global scale out of range")
+
+    @classmethod
+    def upload_checkpoint_nvfp4(cls, stream: Stream, layout: int, rows: int, cols: int, codes, scales,
+                                global_scale: float, codes_b=None, scales_b=None, global_scale_b: float = 0.0):
+        device = torch.device("cuda", stream.ordinal)
+        planes = []
+        for c, s, g in ((codes, scales, global_scale), (codes_b, scales_b, global_scale_b)):
+            if c is None:
+                planes += [None, None]
+                continue
+            c = np.ascontiguousarray(c, dtype=np.uint8)
+            s = np.ascontiguousarray(s, dtype=np.uint8)
+            cls.checked_checkpoint(rows, cols, c, s, g)
+            planes += [torch.from_numpy(c).to(device), torch.from_numpy(s).to(device)]
+        return cls.repack_device_planes(stream, layout, rows, cols, planes[0], planes[1], global_scale,
+                                        planes[2], planes[3], global_scale_b)
+
+    @classmethod
+    def repack_device_planes(cls, stream: Stream, layout: int, rows: int, cols: int, codes: torch.Tensor,
+                             scales: torch.Tensor, global_scale: float, codes_b: torch.Tensor | None = None,
+                             scales_b: torch.Tensor | None = None, global_scale_b: float = 0.0):
+        """Repack compact planes that already live on the device (preflight + submit + synchronise)."""
+        destination = torch.empty(repack_extent(layout, rows, cols), dtype=torch.uint8, device=codes.device)
+        args = abi.header(abi.RepackArgs)
+        args.codes, args.codes_len_bytes = _ptr(codes), _nbytes(codes)
+        args.scales, args.scales_len_bytes = _ptr(scales), _nbytes(scales)
+        if codes_b is not None:
+            args.codes_b, args.codes_b_len_bytes = _ptr(codes_b), _nbytes(codes_b)
+            args.scales_b, args.scales_b_len_bytes = _ptr(scales_b), _nbytes(scales_b)
+        args.destination, args.destination_len_bytes = _ptr(destination), _nbytes(destination)
+        args.rows, args.cols, args.layout = rows, cols, layout
+        lib = abi.lib()
+        _check("repack_preflight", lib.augur_cuda_nvfp4_sm100_repack_preflight_v1(stream.ordinal, stream.handle, byref(args)))
+        _check("repack_submit", lib.augur_cuda_nvfp4_sm100_repack_prevalidated_submit_v1(stream.ordinal, stream.handle, byref(args)))
+        stream.synchronize()
+        return cls(stream, layout, rows, cols, destination, global_scale, global_scale_b)
+
+    def dequant_f32(self) -> torch.Tensor:
+        """Bit-exact f32 values of the repacked tensor ([rows, cols]; pair: [2, rows, cols])."""
+        pair = self.layout == abi.LAYOUT_STREAM_PAIR
+        shape = (2, self.rows, self.cols) if pair else (self.rows, self.cols)
+        out = torch.empty(shape, dtype=torch.float32, device=self.packed.device)
+        args = abi.header(abi.DequantArgs)
+        args.weight, args.weight_len_bytes = _ptr(self.packed), _nbytes(self.packed)
+        args.output_f32, args.output_len_bytes = _ptr(out), _nbytes(out)
+        args.rows, args.cols, args.layout = self.rows, self.cols, self.layout
+        args.global_scale, args.global_scale_b = self.global_scale, self.global_scale_b
+        lib = abi.lib()
+        s = self.stream
+        _check("dequant_preflight", lib.augur_cuda_nvfp4_sm100_dequant_f32_preflight_v1(s.ordinal, s.handle, byref(args)))
+        _check("dequant_submit", lib.augur_cuda_nvfp4_sm100_dequant_f32_prevalidated_submit_v1(s.ordinal, s.handle, byref(args)))
+        return out
+
+
+def dequant_compact_f32(stream: Stream, codes: torch.Tensor, scales: torch.Tensor, rows: int, cols: int,
+                        global_scale: float) -> torch.Tensor:
+    out = torch.empty((rows, cols), dtype=torch.float32, device=codes.device)
+    args = abi.header(abi.DequantArgs)
+    args.weight, args.weight_len_bytes = _ptr(codes), _nbytes(codes)
+    args.scales, args.scales_len_bytes = _ptr(scales), _nbytes(scales)
+    args.output_f32, args.output_len_bytes = _ptr(out), _nbytes(out)
+    args.rows, args.cols, args.layout, args.global_scale = rows, cols, abi.LAYOUT_COMPACT, global_scale
+    lib = abi.lib()
+    _check("dequant_preflight", lib.augur_cuda_nvfp4_sm100_dequant_f32_preflight_v1(stream.ordinal, stream.handle, byref(args)))
+    _check("dequant_submit", lib.augur_cuda_nvfp4_sm100_dequant_f32_prevalidated_submit_v1(stream.ordinal, stream.handle, byref(args)))
+    return out
+
+
+def gemv_args(weight: Nvfp4Sm100Weight, x: torch.Tensor, out: torch.Tensor, epilogue: int) -> abi.GemvArgs:
+    args = abi.header(abi.GemvArgs)
+    args.weight, args.weight_len_bytes = _ptr(weight.packed), _nbytes(weight.packed)
+    args.input_bf16, args.input_len_bytes = _ptr(x), _nbytes(x)
+    args.output, args.output_len_bytes = _ptr(out), _nbytes(out)
+    args.rows, args.cols, args.tokens, args.epilogue = weight.rows, weight.cols, x.shape[0], epilogue
+    args.global_scale, args.global_scale_b = weight.global_scale, weight.global_scale_b
+    return args
+
+
+class Nvfp4Sm100Projection:
+    """A retained small-token projection: preflight once at bind, submit many times.
+
+    Mirrors ``CudaQwen35QpnRetainedProjectionV1`` (qpn.rs:60-105, 202-224): the
+    binding keeps the plan, stream, weight, input and output alive, is immutable
+    after preflight, and ``submit_for_plan`` only enqueues.
+    """
+
+    def __init__(self, plan: Plan, weight: Nvfp4Sm100Weight, x: torch.Tensor, out: torch.Tensor, epilogue: int):
+        self.plan, self.weight, self.x, self.out = plan, weight, x, out
+        self.args = gemv_args(weight, x, out, epilogue)
+
+    @classmethod
+    def bind(cls, plan: Plan, weight: Nvfp4Sm100Weight, x: torch.Tensor, out: torch.Tensor | None = None,
+             epilogue: int | None = None):
+        if epilogue is None:
+            epilogue = abi.EPILOGUE_SWIGLU_BF16 if weight.layout == abi.LAYOUT_STREAM_PAIR else abi.EPILOGUE_LINEAR_BF16
+        if out is None:
+            dtype = torch.float32 if epilogue == abi.EPILOGUE_LINEAR_F32 else torch.bfloat16
+            out = torch.empty((x.shape[0], weight.rows), dtype=dtype, device=x.device)
+        self = cls(plan, weight, x, out, epilogue)
+        s = plan.stream
+        _check("gemv_preflight", abi.lib().augur_cuda_nvfp4_sm100_gemv_bf16_preflight_v1(
+            s.ordinal, s.handle, plan.handle, byref(self.args)))
+        return self
+
+    def submit_for_plan(self) -> None:
+        s = self.plan.stream
+        _check("gemv_submit", abi.lib().augur_cuda_nvfp4_sm100_gemv_bf16_prevalidated_submit_v1(
+            s.ordinal, s.handle, self.plan.handle, byref(self.args)))
+
+
+class Nvfp4Sm100FfnProgram:
+    """gate|up + SwiGLU, then down, as one validated program.
+
+    Mirrors ``CudaQwen35QpnFfnProgramV1::bind / submit_for_plan`` (qpn.rs:391-492).
+    """
+
+    def __init__(self, plan: Plan, gate_up: Nvfp4Sm100Weight, down: Nvfp4Sm100Weight, x: torch.Tensor,
+                 intermediate: torch.Tensor, out: torch.Tensor, down_epilogue: int):
+        self.plan, self.gate_up, self.down = plan, gate_up, down
+        self.x, self.intermediate, self.out = x, intermediate, out
+        self.args = abi.header(abi.MlpArgs)
+        self.args.gate_up = gemv_args(gate_up, x, intermediate, abi.EPILOGUE_SWIGLU_BF16)
+        self.args.down = gemv_args(down, intermediate, out, down_epilogue)
+
+    @classmethod
+    def bind(cls, plan: Plan, gate_up: Nvfp4Sm100Weight, down: Nvfp4Sm100Weight, x: torch.Tensor,
+             out: torch.Tensor | None = None, down_epilogue: int = abi.EPILOGUE_LINEAR_BF16):
+        tokens = x.shape[0]
+        intermediate = torch.empty((tokens, gate_up.rows), dtype=torch.bfloat16, device=x.device)
+        if out is None:
+            dtype = torch.float32 if down_epilogue == abi.EPILOGUE_LINEAR_F32 else torch.bfloat16
+            out = torch.empty((tokens, down.rows), dtype=dtype, device=x.device)
+        self = cls(plan, gate_up, down, x, intermediate, out, down_epilogue)
+        s = plan.stream
+        _check("mlp_preflight", abi.lib().augur_cuda_nvfp4_sm100_mlp_preflight_v1(
+            s.ordinal, s.handle, plan.handle, byref(self.args)))
+        return self
+
+    def submit_for_plan(self) -> None:
+        s = self.plan.stream
+        _check("mlp_submit", abi.lib().augur_cuda_nvfp4_sm100_mlp_prevalidated_submit_v1(
+            s.ordinal, s.handle, self.plan.handle, byref(self.args)))
+
+
+def mlp_scratch_bytes(hidden: int, intermediate: int, tokens: int = 8) -> int:
+    """Plan scratch for an FFN program: the two members use separate halves."""
+    need = max(gemv_scratch_bytes(intermediate, hidden, tokens), gemv_scratch_bytes(hidden, intermediate, tokens))
+    return 2 * (need + 256)
+
+
+def allocation_snapshot() -> tuple[int, int]:
+    a, f = c_uint64(), c_uint64()
+    abi.lib().augur_cuda_nvfp4_sm100_allocation_snapshot_v1(byref(a), byref(f))
+    return int(a.value), int(f.value)
+
+
+def launch_count() -> int:
+    return int(abi.lib().augur_cuda_nvfp4_sm100_launch_count_v1())
+
+
+def default_activation_global_scale(absmax: float = 448.0 * 6.0) -> float:
+    """Per-tensor activation scale so that `absmax` maps to the top of the E4M3 x E2M1 range."""
+    return float(np.float32(absmax) / np.float32(448.0 * 6.0))
+
+
+class Nvfp4Sm100PrefillLinear:
+    """Prefill projection: BF16 activations -> NVFP4 residual terms -> tcgen05 block-scaled GEMM.
+
+    Mirrors the wide-token branch of the retained projection
+    (crates/augur-cuda-sys/native/augur_qwen35_qpn_prefill.cuh:53-88: stage the
+    activations, then one tensor-core GEMM) with both members validated at bind time.
+    """
+
+    def __init__(self, plan: Plan, weight: Nvfp4Sm100Weight, x: torch.Tensor, out: torch.Tensor, terms: int,
+                 activation_global_scale: float):
+        assert weight.layout == abi.LAYOUT_TCGEN05
+        self.plan, self.weight, self.x, self.out, self.terms = plan, weight, x, out, terms
+        tokens, cols = x.shape
+        self.staged = torch.empty(terms * repack_extent(abi.LAYOUT_TCGEN05, tokens, cols), dtype=torch.uint8,
+                                  device=x.device)
+        q = abi.header(abi.ActQuantArgs)
+        q.input_bf16, q.input_len_bytes = _ptr(x), _nbytes(x)
+        q.destination, q.destination_len_bytes = _ptr(self.staged), _nbytes(self.staged)
+        q.tokens, q.cols, q.terms, q.global_scale = tokens, cols, terms, activation_global_scale
+        g = abi.header(abi.GemmArgs)
+        g.weight, g.weight_len_bytes = _ptr(weight.packed), _nbytes(weight.packed)
+        g.activation, g.activation_len_bytes = _ptr(self.staged), _nbytes(self.staged)
+        g.output_bf16, g.output_len_bytes = _ptr(out), _nbytes(out)
+        g.rows, g.cols, g.tokens, g.activation_terms = weight.rows, cols, tokens, terms
+        g.weight_global_scale, g.activation_global_scale = weight.global_scale, activation_global_scale
+        self.quant_args, self.gemm_args = q, g
+
+    @classmethod
+    def bind(cls, plan: Plan, weight: Nvfp4Sm100Weight, x: torch.Tensor, out: torch.Tensor | None = None,
+             terms: int = 1, activation_global_scale: float = 2.0 ** -8):
+        if out is None:
+            out = torch.empty((x.shape[0], weight.rows), dtype=torch.bfloat16, device=x.device)
+        self = cls(plan, weight, x, out, terms, activation_global_scale)
+        s, lib = plan.stream, abi.lib()
+        _check("act_quant_preflight", lib.augur_cuda_nvfp4_sm100_act_quant_preflight_v1(s.ordinal, s.handle, byref(self.quant_args)))
+        _check("gemm_preflight", lib.augur_cuda_nvfp4_sm100_gemm_bf16_preflight_v1(s.ordinal, s.handle, plan.handle, byref(self.gemm_args)))
+        return self
+
+    def submit_quant(self) -> None:
+        s = self.plan.stream
+        _check("act_quant_submit", abi.lib().augur_cuda_nvfp4_sm100_act_quant_prevalidated_submit_v1(
+            s.ordinal, s.handle, byref(self.quant_args)))
+
+    def submit_gemm(self) -> None:
+        s = self.plan.stream
+        _check("gemm_submit", abi.lib().augur_cuda_nvfp4_sm100_gemm_bf16_prevalidated_submit_v1(
+            s.ordinal, s.handle, self.plan.handle, byref(self.gemm_args)))
+
+    def submit_for_plan(self) -> None:
+        self.submit_quant()
+        self.submit_gemm()
+
+    def staged_planes(self):
+        """Quantised activations back on the host: (codes [terms, tokens, cols/2], scales [terms, tokens, cols/16])."""
+        tokens, cols = self.x.shape
+        raw = self.staged.cpu().numpy()
+        code_bytes = tokens * cols // 2
+        sf_bytes = repack_extent(abi.LAYOUT_TCGEN05, tokens, cols) - code_bytes
+        codes = raw[: self.terms * code_bytes].reshape(self.terms, tokens, cols // 2).copy()
+        scales = np.zeros((self.terms, tokens, cols // 16), dtype=np.uint8)
+        for term in range(self.terms):
+            packed = np.concatenate([codes[term].reshape(-1),
+                                     raw[self.terms * code_bytes + term * sf_bytes: self.terms * code_bytes + (term + 1) * sf_bytes]])
+            _, scales[term] = unpack_host(abi.LAYOUT_TCGEN05, tokens, cols, packed)
+        return codes, scales

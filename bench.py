@@ -1,0 +1,346 @@
+#!/usr/bin/env python
+"""Benchmark of the NVFP4 quantized-linear hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W            # this library (sm_100a kernels)
+    python bench.py --impl reference --gpus N --steps K ...  # the reference's CPU path, timed on host cores
+
+Workload (BASELINE config 1): the 27B-class NVFP4 MLP block at the fixed 8-row
+verify batch — gate|up 5120 -> 2x17408 fused with SiLU(gate)*up, then down
+17408 -> 5120 — with synthetic weights of the benchmark's value distributions.
+One step streams LAYERS distinct layers (2.4 GB of weights at N=1, far more than
+L2), so every weight byte of a step comes from HBM. With N > 1 the block is
+tensor-parallel: column-parallel gate|up, row-parallel down, one NCCL all-reduce
+of the 8 x 5120 BF16 output per layer.
+
+Prints one JSON line (rank 0). `value` is whole-job GB/s of algorithmic bytes
+with inputs resident in HBM; `e2e` is the same through the public host API with
+the activations copied from pinned host memory and the result read back every step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+HIDDEN, INTER, TOKENS, LAYERS = 5120, 17408, 8, 16
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def layer_bytes() -> int:
+    """Algorithmic bytes of one MLP layer: every weight byte once + the input + the output (whole job)."""
+    weights = 3 * HIDDEN * INTER * 9 // 16          # 0.5 B code + 1/16 B scale per element
+    return weights + 2 * TOKENS * HIDDEN * 2
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as handle:
+            data = json.load(handle)
+        return float(data["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append([field.strip() for field in line.split(",")])
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm, sm_max, reasons = [], [], set()
+        for row in self.rows:
+            if len(row) < 9:
+                continue
+            try:
+                sm.append(float(row[1]))
+                sm_max.append(float(row[2]))
+            except ValueError:
+                continue
+            for name, field in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), row[5:9]):
+                if field.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(sm_max) if sm_max else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------
+# reference arm: the CPU path (C restatement of the reference's Rust, all host threads)
+# ---------------------------------------------------------------------------------------------
+def cpu_layer_seconds(threads: int, repeats: int):
+    """Times `repeats` passes of one full MLP layer (M=8) through the CPU oracle."""
+    import oracle
+    from augur_v100_b200 import synth
+    gate = synth.make_weight(0, 1, "gate", INTER, HIDDEN)
+    up = synth.make_weight(0, 1, "up", INTER, HIDDEN)
+    down = synth.make_weight(0, 1, "down", HIDDEN, INTER)
+    x = synth.f32_to_bf16_bits(np.random.default_rng(0).standard_normal((TOKENS, HIDDEN)).astype(np.float32) * 8.0)
+    times = []
+    for _ in range(repeats):
+        start = time.perf_counter()
+        oracle.mlp_bf16(gate, up, down, HIDDEN, INTER, x, threads=threads)
+        times.append(time.perf_counter() - start)
+    return times
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle
+    threads = oracle.max_threads()
+    times = cpu_layer_seconds(threads, args.warmup + args.steps)[args.warmup:]
+    seconds = sum(times) / len(times)
+    value = layer_bytes() / seconds / 1e9
+    sample = "one full MLP layer (M=8, 5120 -> 2x17408 -> 5120) per step"
+    print(json.dumps({
+        "impl": "reference", "metric": "nvfp4_linear_m8_hbm_gbs", "value": value, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "config1: NVFP4 MLP block, M=8, hidden 5120, intermediate 17408; " + sample,
+                   "host_threads": threads},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+# ---------------------------------------------------------------------------------------------
+# this library
+# ---------------------------------------------------------------------------------------------
+def device_planes(torch, generator, rows, cols, device):
+    """Random compact planes made on the device: uniform codes, |N(0,1)|*0.5 scales (E4M3, RNE), in 0x01..0x7e."""
+    codes = torch.randint(0, 256, (rows, cols // 2), dtype=torch.uint8, device=device, generator=generator)
+    raw = (torch.randn((rows, cols // 16), device=device, generator=generator).abs() * 0.5).clamp(2.0 ** -9, 448.0)
+    scales = raw.to(torch.float8_e4m3fn).view(torch.uint8).clamp(1, 0x7E)
+    return codes, scales
+
+
+def build_layers(torch, host, abi, stream, device, world, rank, layers):
+    from augur_v100_b200 import synth
+    generator = torch.Generator(device=device)
+    generator.manual_seed(1234 + rank)
+    inter_shard = INTER // world
+    built = []
+    for _ in range(layers):
+        gc, gs = device_planes(torch, generator, inter_shard, HIDDEN, device)
+        uc, us = device_planes(torch, generator, inter_shard, HIDDEN, device)
+        gate_up = host.Nvfp4Sm100Weight.repack_device_planes(
+            stream, abi.LAYOUT_STREAM_PAIR, inter_shard, HIDDEN, gc, gs, synth.GLOBAL_SCALE, uc, us, synth.GLOBAL_SCALE)
+        dc, ds = device_planes(torch, generator, HIDDEN, inter_shard, device)
+        down = host.Nvfp4Sm100Weight.repack_device_planes(
+            stream, abi.LAYOUT_STREAM, HIDDEN, inter_shard, dc, ds, synth.GLOBAL_SCALE)
+        built.append((gate_up, down))
+        del gc, gs, uc, us, dc, ds
+    return built
+
+
+def prefill_probe(torch, host, abi, stream, device):
+    """Config 2 on one GPU: M=4096 GEMMs through the tcgen05 path; returns TFLOP/s or an error string."""
+    from augur_v100_b200 import synth
+    out = {}
+    try:
+        plan = host.Plan(stream, 1 << 20)
+        generator = torch.Generator(device=device)
+        generator.manual_seed(77)
+        tokens = 4096
+        for name, rows, cols in (("up_5120x17408", INTER, HIDDEN), ("down_17408x5120", HIDDEN, INTER)):
+            codes, scales = device_planes(torch, generator, rows, cols, device)
+            weight = host.Nvfp4Sm100Weight.repack_device_planes(stream, abi.LAYOUT_TCGEN05, rows, cols, codes, scales,
+                                                                synth.GLOBAL_SCALE)
+            x = torch.randn((tokens, cols), device=device, generator=generator).to(torch.bfloat16)
+            lin = host.Nvfp4Sm100PrefillLinear.bind(plan, weight, x, terms=1, activation_global_scale=2.0 ** -8)
+            lin.submit_for_plan()
+            stream.synchronize()
+            if plan.device_status() != 0:
+                out[name] = {"error": f"device status {plan.device_status():#x}"}
+                continue
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 10
+            start.record()
+            for _ in range(reps):
+                lin.submit_gemm()
+            end.record()
+            end.synchronize()
+            ms = start.elapsed_time(end) / reps
+            out[name] = {"ms": ms, "tflops": 2.0 * tokens * rows * cols / ms / 1e9, "tokens": tokens,
+                         "activation_terms": 1, "finite": bool(torch.isfinite(lin.out.float()).all())}
+            del weight, lin, x, codes, scales
+        plan.close()
+    except Exception as error:  # reported, never hidden
+        out["error"] = repr(error)
+    return out
+
+
+def run_library(args):
+    import torch
+    import torch.distributed as dist
+
+    from augur_v100_b200 import abi, host
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    if INTER % (world * 128) != 0:
+        raise SystemExit("intermediate size does not shard over this many GPUs")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    stream = host.Stream(local)
+    layers = build_layers(torch, host, abi, stream, device, world, rank, LAYERS)
+    plan = host.Plan(stream, host.mlp_scratch_bytes(HIDDEN, INTER // world))
+    x_host = torch.randn((TOKENS, HIDDEN), dtype=torch.float32).mul_(8.0).to(torch.bfloat16).pin_memory()
+    y_host = torch.empty((TOKENS, HIDDEN), dtype=torch.bfloat16).pin_memory()
+    x = x_host.to(device)
+    outs = [torch.empty((TOKENS, HIDDEN), dtype=torch.bfloat16, device=device) for _ in range(2)]
+    programs = [host.Nvfp4Sm100FfnProgram.bind(plan, gate_up, down, x, out=outs[index % 2])
+                for index, (gate_up, down) in enumerate(layers)]
+
+    def step():
+        for index, program in enumerate(programs):
+            program.submit_for_plan()
+            if world > 1:
+                dist.all_reduce(outs[index % 2])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(body, steps):
+        barrier()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            body()
+        end.record()
+        barrier()
+        ms = torch.tensor([start.elapsed_time(end)], device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches_before = host.launch_count()
+    total_ms = timed(step, args.steps)
+    launches = host.launch_count() - launches_before
+
+    def e2e_step():
+        x.copy_(x_host, non_blocking=True)
+        step()
+        y_host.copy_(outs[(LAYERS - 1) % 2], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    e2e_ms = timed(e2e_step, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    status = plan.device_status()
+    if status != 0:
+        raise SystemExit(f"device status word {status:#x}")
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    step_bytes = LAYERS * layer_bytes()
+    ms_per_step = total_ms / args.steps
+    value = step_bytes / (ms_per_step * 1e-3) / 1e9
+    e2e_value = step_bytes / (e2e_ms / args.steps * 1e-3) / 1e9
+    peak, peak_source = measured_peaks()
+    # Per GPU, per layer: the two launches of the streaming kernel read this rank's weight shard once.
+    per_gpu_layer_bytes = 3 * HIDDEN * (INTER // world) * 9 // 16 + 2 * TOKENS * HIDDEN * 2
+    launch_pair_ms = ms_per_step / LAYERS
+    achieved = per_gpu_layer_bytes / (launch_pair_ms * 1e-3) / 1e9
+    line = {
+        "metric": "nvfp4_linear_m8_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f16 products of E2M1xE4M3 weights and BF16 activations, f32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": f"config1: NVFP4 MLP block (gate|up+SwiGLU, down), M={TOKENS}, hidden {HIDDEN}, "
+                               f"intermediate {INTER}, {LAYERS} distinct layers per step",
+                   "l2": f"inputs larger than L2: {LAYERS * 3 * HIDDEN * INTER * 9 // 16 // world} weight bytes per GPU per step",
+                   "parallelism": f"tp{world}" if world > 1 else "single", "all_reduce": "NCCL bf16 8x5120 per layer" if world > 1 else None},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_source": peak_source,
+                     "kernel": "gemv_kernel (gate|up launch + down launch per layer; with N>1 the interval also holds the all-reduce)",
+                     "bytes_per_launch_pair": per_gpu_layer_bytes, "ms_per_launch_pair": launch_pair_ms},
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": TOKENS * HIDDEN * 2,
+                "d2h_bytes_per_step": TOKENS * HIDDEN * 2, "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": launches, "clocks": clocks,
+    }
+    if world == 1:
+        import oracle
+        threads = oracle.max_threads()
+        seconds = min(cpu_layer_seconds(threads, 2))
+        line["cpu_baseline"] = {"value": layer_bytes() / seconds / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+                                "sample": "one full MLP layer (M=8), best of 2, C restatement of the reference CPU path"}
+        if not args.no_prefill:
+            del programs, layers
+            torch.cuda.empty_cache()
+            line["prefill"] = prefill_probe(torch, host, abi, stream, device)
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", choices=["library", "reference"], default="library")
+    parser.add_argument("--no-prefill", action="store_true", help="skip the M=4096 tcgen05 probe at N=1")
+    parser.add_argument("--layers", type=int, default=LAYERS,
+                        help="distinct layers streamed per step (smaller values are for profiler captures only)")
+    args = parser.parse_args()
+    global LAYERS
+    LAYERS = args.layers
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_library(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,329 @@
+/* B200 (sm_100a) NVFP4 quantized-linear C ABI.
+ *
+ * A drop-in for the quantized-linear path of Augur's native CUDA layer
+ * (crates/augur-cuda-sys). It keeps that layer's calling contract:
+ *   - every operation is a pair  X_preflight_v1 / X_prevalidated_submit_v1
+ *     (contract: crates/augur-cuda-sys/native/augur_qwen35_nvfp4_qpn_abi.h:134-139);
+ *   - preflight (once per binding) validates the descriptor header, shapes,
+ *     exact byte extents, alignment and pairwise disjointness of every range,
+ *     then asks the driver who owns each range; it enqueues and allocates nothing;
+ *   - prevalidated_submit (hot) repeats the scalar/extent/overlap checks, skips
+ *     the driver queries, enqueues on the caller's stream and returns; it never
+ *     synchronises and never allocates;
+ *   - results are {status, raw_cuda_status}
+ *     (crates/augur-cuda-sys/native/augur_cuda_runtime.h:31-55);
+ *   - device addresses are opaque uint64 tokens, never dereferenced on the host
+ *     (augur_cuda_runtime.h:66-72); the ABI retains nothing the caller owns
+ *     (augur_cuda_runtime.h:4-12).
+ *
+ * The types shared with the reference header keep their names and layouts, so
+ * this header can be included next to it (guards below).
+ */
+#ifndef AUGUR_CUDA_NVFP4_SM100_H
+#define AUGUR_CUDA_NVFP4_SM100_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifndef AUGUR_CUDA_RUNTIME_H /* shared vocabulary of augur_cuda_runtime.h:17-72 */
+#if defined(_WIN32)
+#define AUGUR_CUDA_CALL __cdecl
+#else
+#define AUGUR_CUDA_CALL
+#endif
+#define AUGUR_CUDA_ABI_VERSION_V1 UINT32_C(1)
+typedef int32_t augur_cuda_status_t;
+enum {
+    AUGUR_CUDA_STATUS_OK = 0,
+    AUGUR_CUDA_STATUS_INVALID_ARGUMENT = -1,
+    AUGUR_CUDA_STATUS_UNSUPPORTED_DEVICE = -2,
+    AUGUR_CUDA_STATUS_OUT_OF_MEMORY = -3,
+    AUGUR_CUDA_STATUS_RUNTIME_FAILURE = -4,
+    AUGUR_CUDA_STATUS_SUBMISSION_FAILURE = -5,
+    AUGUR_CUDA_STATUS_COMPLETION_FAILURE = -6,
+    AUGUR_CUDA_STATUS_ABI_VERSION_MISMATCH = -7,
+    AUGUR_CUDA_STATUS_DIAGNOSTIC_FAULT_INJECTED = -8
+};
+typedef struct augur_cuda_result_v1 {
+    augur_cuda_status_t status;
+    int32_t raw_cuda_status;
+} augur_cuda_result_v1;
+/* Opaque stream handle; its private layout is {int32 ordinal; cudaStream_t stream}
+ * (crates/augur-cuda-sys/native/augur_cuda_internal.h:39-42). */
+typedef struct augur_cuda_stream_handle augur_cuda_stream_handle;
+typedef augur_cuda_stream_handle* augur_cuda_stream_t;
+typedef uint64_t augur_cuda_device_ptr_t;
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- physical layouts --------------------------------------------------- */
+/* COMPACT is what a checkpoint loader hands over (crates/augur-formats/src/fp4.rs:17-21,
+ * crates/augur-model-qwen35/src/checkpoint_quant.rs:93-152): codes [rows][cols/2]
+ * (even k in the low nibble), scales [rows][cols/16], one f32 global scale.
+ * The other three are lossless byte permutations of the same bits. */
+#define AUGUR_NVFP4_SM100_LAYOUT_COMPACT UINT32_C(0)
+/* 32-row x 128-k blocks of 2304 bytes in mma fragment order: the decode/verify stream. */
+#define AUGUR_NVFP4_SM100_LAYOUT_STREAM UINT32_C(1)
+/* Same, with 16 gate rows and the matching 16 up rows in each block (fused SwiGLU). */
+#define AUGUR_NVFP4_SM100_LAYOUT_STREAM_PAIR UINT32_C(2)
+/* Codes untouched (K-major rows, TMA-loadable) followed by block scales tiled into
+ * 128-row x 4-scale atoms for tcgen05 block-scaled MMA. */
+#define AUGUR_NVFP4_SM100_LAYOUT_TCGEN05 UINT32_C(3)
+
+#define AUGUR_NVFP4_SM100_EPILOGUE_LINEAR_BF16 UINT32_C(0)
+#define AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16 UINT32_C(1)
+#define AUGUR_NVFP4_SM100_EPILOGUE_LINEAR_F32 UINT32_C(2)
+
+#define AUGUR_NVFP4_SM100_MAX_SMALL_TOKENS UINT32_C(8)
+
+/* ---- identity ------------------------------------------------------------ */
+/* Replaces augur_cuda_abi_version (augur_cuda_runtime.h:74). */
+uint32_t AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_abi_version(void);
+/* Replaces augur_cuda_nvfp4_sm120_build_capability_v1
+ * (crates/augur-cuda-sys/native/augur_nvfp4_stub.cu:10-13): 100 when the
+ * library holds sm_100a code, 0 otherwise. */
+uint32_t AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_build_capability_v1(void);
+
+/* ---- stream handles (stand-alone use) -------------------------------------- */
+/* Inside Augur the handles come from augur_cuda_stream_create
+ * (augur_cuda_runtime.h:116-131) and are passed through unchanged. These three
+ * exist so the library can be used and tested without the rest of the runtime. */
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_stream_create_v1(
+    int32_t ordinal, augur_cuda_stream_t* out_stream);
+/* Wraps an existing cudaStream_t (for example the framework's current stream);
+ * destroying the handle does not destroy the wrapped stream. */
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_stream_adopt_v1(
+    int32_t ordinal, void* raw_cuda_stream, augur_cuda_stream_t* out_stream);
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_stream_synchronize_v1(
+    augur_cuda_stream_t stream);
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_stream_destroy_v1(
+    augur_cuda_stream_t stream);
+
+/* ---- plan: stream-owned scratch ------------------------------------------- */
+/* Replaces augur_cuda_qwen35_prefill_cublas_plan_v1 (augur_cuda_runtime.h:2019-2034):
+ * created once per stream at bind time, owns the scratch the kernels need
+ * (split-K partials, arrival counters, quantised-activation staging), and is
+ * only accepted together with the stream that created it. Creation and
+ * destruction are the only calls of this library that allocate device memory. */
+typedef struct augur_cuda_nvfp4_sm100_plan_v1 augur_cuda_nvfp4_sm100_plan_v1;
+
+typedef struct augur_cuda_nvfp4_sm100_plan_snapshot_v1 {
+    uint32_t abi_version;
+    uint32_t struct_size;
+    augur_cuda_device_ptr_t scratch;
+    uint64_t scratch_len_bytes;
+    uint32_t sm_count;
+    uint32_t reserved;
+} augur_cuda_nvfp4_sm100_plan_snapshot_v1;
+
+/* Bytes of plan scratch needed by a small-token linear / a prefill linear. */
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_scratch_extent_host_v1(
+    uint32_t rows, uint32_t cols, uint32_t tokens, uint64_t* out_bytes);
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_scratch_extent_host_v1(
+    uint32_t rows, uint32_t cols, uint32_t tokens, uint32_t activation_terms, uint64_t* out_bytes);
+
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_plan_create_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, uint64_t scratch_len_bytes,
+    augur_cuda_nvfp4_sm100_plan_v1** out_plan);
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_plan_describe_v1(
+    const augur_cuda_nvfp4_sm100_plan_v1* plan, augur_cuda_nvfp4_sm100_plan_snapshot_v1* out);
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_plan_destroy_v1(
+    augur_cuda_nvfp4_sm100_plan_v1* plan);
+
+/* ---- repack: compact planes -> hot layout ---------------------------------- */
+/* Replaces the pack_checkpoint pair (augur_qwen35_nvfp4_qpn_abi.h:14-18,146-148;
+ * CPU counterpart crates/augur-repack/src/fp4_cpu.rs:45-55). Scale bytes >= 127
+ * (sign bit or NaN) are the caller's to reject before upload, as the reference
+ * loader does (crates/augur-backend/src/cuda_qwen35_qpn.rs:59-72); the host
+ * repack below rejects them itself. */
+typedef struct augur_cuda_nvfp4_sm100_repack_args_v1 {
+    uint32_t abi_version;
+    uint32_t struct_size;
+    augur_cuda_device_ptr_t codes;      /* [rows][cols/2] */
+    uint64_t codes_len_bytes;
+    augur_cuda_device_ptr_t scales;     /* [rows][cols/16] */
+    uint64_t scales_len_bytes;
+    augur_cuda_device_ptr_t codes_b;    /* second matrix (up) for STREAM_PAIR, else 0 */
+    uint64_t codes_b_len_bytes;
+    augur_cuda_device_ptr_t scales_b;
+    uint64_t scales_b_len_bytes;
+    augur_cuda_device_ptr_t destination;
+    uint64_t destination_len_bytes;
+    uint32_t rows;                      /* of each source matrix */
+    uint32_t cols;
+    uint32_t layout;                    /* STREAM, STREAM_PAIR or TCGEN05 */
+    uint32_t reserved;
+} augur_cuda_nvfp4_sm100_repack_args_v1;
+
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_repack_extent_host_v1(
+    uint32_t layout, uint32_t rows, uint32_t cols, uint64_t* out_bytes);
+/* Host-memory twin of the device repack (same permutation, byte for byte) and its inverse. */
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_repack_host_v1(
+    uint32_t layout, uint32_t rows, uint32_t cols,
+    const uint8_t* codes, const uint8_t* scales, const uint8_t* codes_b, const uint8_t* scales_b,
+    uint8_t* destination, uint64_t destination_len_bytes);
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_unpack_host_v1(
+    uint32_t layout, uint32_t rows, uint32_t cols,
+    const uint8_t* source, uint64_t source_len_bytes,
+    uint8_t* codes, uint8_t* scales, uint8_t* codes_b, uint8_t* scales_b);
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_repack_preflight_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, const augur_cuda_nvfp4_sm100_repack_args_v1* args);
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_repack_prevalidated_submit_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, const augur_cuda_nvfp4_sm100_repack_args_v1* args);
+
+/* ---- dequantise to f32 (verification entry) -------------------------------- */
+/* Replaces the expand pair (augur_qwen35_nvfp4_qpn_abi.h:23-29,153). Output is
+ * bit-identical to Nvfp4CompactBlock::decode_ref (crates/augur-formats/src/fp4.rs:105-125):
+ * fl(e2m1 * fl(e4m3 * global)), code 8 -> +0.0. `layout` says how `weight` is laid out. */
+typedef struct augur_cuda_nvfp4_sm100_dequant_args_v1 {
+    uint32_t abi_version;
+    uint32_t struct_size;
+    augur_cuda_device_ptr_t weight;     /* COMPACT: codes plane; otherwise the repacked tensor */
+    uint64_t weight_len_bytes;
+    augur_cuda_device_ptr_t scales;     /* COMPACT only, else 0 */
+    uint64_t scales_len_bytes;
+    augur_cuda_device_ptr_t output_f32; /* [rows][cols]; STREAM_PAIR: gate rows then up rows */
+    uint64_t output_len_bytes;
+    uint32_t rows;
+    uint32_t cols;
+    uint32_t layout;
+    float global_scale;
+    float global_scale_b;               /* STREAM_PAIR: scale of the second matrix, else 0 */
+    uint32_t reserved;
+} augur_cuda_nvfp4_sm100_dequant_args_v1;
+
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_dequant_f32_preflight_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, const augur_cuda_nvfp4_sm100_dequant_args_v1* args);
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_dequant_f32_prevalidated_submit_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, const augur_cuda_nvfp4_sm100_dequant_args_v1* args);
+
+/* ---- small-token linear: tokens 1..8 (decode and the fixed B8 verify batch) -- */
+/* Replaces the project / prefill pairs for tokens <= 8
+ * (augur_qwen35_nvfp4_qpn_abi.h:30-36,60-70,154) and the fused gate+up / SiLU
+ * entries (same file :68-73,130-133). y[t][n] = bf16(global * sum_k w[n][k] x[t][k]),
+ * BF16 activations, f32 accumulation. With EPILOGUE_SWIGLU the weight is a
+ * STREAM_PAIR tensor and the output is bf16(silu(gate) * up), rows = intermediate size.
+ * With EPILOGUE_LINEAR_F32 the unrounded f32 sums are written (tensor-parallel partials). */
+typedef struct augur_cuda_nvfp4_sm100_gemv_args_v1 {
+    uint32_t abi_version;
+    uint32_t struct_size;
+    augur_cuda_device_ptr_t weight;
+    uint64_t weight_len_bytes;
+    augur_cuda_device_ptr_t input_bf16;   /* [tokens][cols] */
+    uint64_t input_len_bytes;
+    augur_cuda_device_ptr_t output;       /* [tokens][rows] bf16, or f32 for LINEAR_F32 */
+    uint64_t output_len_bytes;
+    uint32_t rows;
+    uint32_t cols;
+    uint32_t tokens;
+    uint32_t epilogue;
+    float global_scale;
+    float global_scale_b;                 /* SWIGLU: scale of the up matrix, else 0 */
+    uint32_t reserved0;
+    uint32_t reserved1;
+} augur_cuda_nvfp4_sm100_gemv_args_v1;
+
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_bf16_preflight_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_gemv_args_v1* args);
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_bf16_prevalidated_submit_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_gemv_args_v1* args);
+
+/* ---- MLP program: gate|up + SwiGLU, then down ------------------------------- */
+/* Replaces CudaQwen35QpnFfnProgramV1's two native steps
+ * (crates/augur-backend/src/cuda_qwen35_prefill_cublas/qpn.rs:391-394,465-492;
+ * native augur_qwen35_qpn_prefill.cuh:97-147): both members and every cross alias
+ * are validated before the first enqueue; down.input must be gate_up.output. */
+typedef struct augur_cuda_nvfp4_sm100_mlp_args_v1 {
+    uint32_t abi_version;
+    uint32_t struct_size;
+    augur_cuda_nvfp4_sm100_gemv_args_v1 gate_up;
+    augur_cuda_nvfp4_sm100_gemv_args_v1 down;
+} augur_cuda_nvfp4_sm100_mlp_args_v1;
+
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_mlp_preflight_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_mlp_args_v1* args);
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_mlp_prevalidated_submit_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_mlp_args_v1* args);
+
+/* ---- prefill: activation quantiser + tcgen05 block-scaled GEMM --------------- */
+/* Replaces the W4A4 interstage quantiser (augur_cuda_runtime.h:6983 ff.;
+ * native augur_nvfp4_cutlass_sm120.cu:455-503): BF16 rows -> E2M1 codes with one
+ * E4M3 scale per 16 (smallest scale >= amax/(6*global); nearest level, ties to
+ * the smaller magnitude). `terms` > 1 writes a residual series. */
+typedef struct augur_cuda_nvfp4_sm100_act_quant_args_v1 {
+    uint32_t abi_version;
+    uint32_t struct_size;
+    augur_cuda_device_ptr_t input_bf16;   /* [tokens][cols] */
+    uint64_t input_len_bytes;
+    augur_cuda_device_ptr_t destination;  /* [terms] x TCGEN05 layout of a tokens x cols tensor */
+    uint64_t destination_len_bytes;
+    uint32_t tokens;
+    uint32_t cols;
+    uint32_t terms;                       /* 1..3 */
+    float global_scale;
+} augur_cuda_nvfp4_sm100_act_quant_args_v1;
+
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_act_quant_preflight_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, const augur_cuda_nvfp4_sm100_act_quant_args_v1* args);
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_act_quant_prevalidated_submit_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, const augur_cuda_nvfp4_sm100_act_quant_args_v1* args);
+
+/* Replaces the CUTLASS W4A4 shape launches and the W4A16 kernel
+ * (augur_cuda_runtime.h:6930-6964,7631-7643; native augur_nvfp4_cutlass_sm120.cu:36-203,320-378)
+ * and the wide prefill projection (augur_qwen35_qpn_prefill.cuh:53-88):
+ * y[t][n] = bf16(g_w * g_a * sum_terms sum_k w[n][k] a_term[t][k]) on tcgen05
+ * kind::mxf4nvf4 with TMEM accumulators. tokens must be a multiple of 128. */
+typedef struct augur_cuda_nvfp4_sm100_gemm_args_v1 {
+    uint32_t abi_version;
+    uint32_t struct_size;
+    augur_cuda_device_ptr_t weight;        /* TCGEN05 layout, rows x cols */
+    uint64_t weight_len_bytes;
+    augur_cuda_device_ptr_t activation;    /* output of act_quant */
+    uint64_t activation_len_bytes;
+    augur_cuda_device_ptr_t output_bf16;   /* [tokens][rows] */
+    uint64_t output_len_bytes;
+    uint32_t rows;
+    uint32_t cols;
+    uint32_t tokens;
+    uint32_t activation_terms;
+    float weight_global_scale;
+    float activation_global_scale;
+} augur_cuda_nvfp4_sm100_gemm_args_v1;
+
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_bf16_preflight_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_gemm_args_v1* args);
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_bf16_prevalidated_submit_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_gemm_args_v1* args);
+
+/* ---- diagnostics ------------------------------------------------------------ */
+/* Host-side fault injection (the reference injects with a device trap,
+ * native augur_m306_k14_async_fault_sm70.cu:7-9,61; here nothing touches the GPU):
+ * the next `count` submits return AUGUR_CUDA_STATUS_DIAGNOSTIC_FAULT_INJECTED
+ * before any enqueue. */
+void AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_diagnostic_inject_submit_fault_v1(uint32_t count);
+/* Device allocations / frees made by this library so far; the counterpart of
+ * cuda_device_allocation_snapshot (crates/augur-backend/src/cuda_runtime.rs:528-535),
+ * used to prove the hot path allocates nothing. */
+void AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_allocation_snapshot_v1(
+    uint64_t* out_allocations, uint64_t* out_frees);
+/* Kernel launches enqueued by this library so far. */
+uint64_t AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_launch_count_v1(void);
+/* Device-side status word of the plan (0 = clean). Bounded waits inside the
+ * kernels record where they gave up here instead of spinning for ever; reading
+ * it synchronises the plan's stream. */
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_plan_device_status_v1(
+    augur_cuda_nvfp4_sm100_plan_v1* plan, uint32_t* out_status);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

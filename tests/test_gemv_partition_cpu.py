@@ -1,0 +1,120 @@
+"""Integer model of the small-token kernel's work split, checked exhaustively on the CPU.
+
+The kernel (csrc/nvfp4_gemv.cu) cuts the block space of each k-slab into equal contiguous
+spans per CTA and per warp and combines split row groups through warp slots, CTA
+contributions and arrival counters. This file restates that arithmetic and proves, for
+many shapes and SM counts, that every weight block is consumed exactly once and that each
+row group receives exactly the number of contributions its arrival counter waits for.
+"""
+import pytest
+
+WARPS, MAX_SLAB = 16, 40
+
+
+def geometry(rows, cols, pair, sms):
+    groups = rows // 16 if pair else rows // 32
+    kb = cols // 128
+    slabs = (kb + MAX_SLAB - 1) // MAX_SLAB
+    per_slab = min(max(sms // slabs, 1), groups * (kb // slabs))
+    max_contrib = slabs * ((per_slab + groups - 1) // groups + 1)
+    return groups, kb, slabs, per_slab, max_contrib
+
+
+def span_of(at, total, parts):
+    return ((at + 1) * parts - 1) // total
+
+
+def contributors(groups, kb, slabs, per_slab, group):
+    """(total, {(slab, cta): slot}) exactly as `contribute` computes them."""
+    total, slots = 0, {}
+    for s in range(slabs):
+        kbs = (s + 1) * kb // slabs - s * kb // slabs
+        blocks = groups * kbs
+        first = span_of(group * kbs, blocks, per_slab)
+        last = span_of((group + 1) * kbs - 1, blocks, per_slab)
+        for cta in range(first, last + 1):
+            slots[(s, cta)] = total + (cta - first)
+        total += last - first + 1
+    return total, slots
+
+
+def simulate(rows, cols, pair, sms):
+    groups, kb, slabs, per_slab, max_contrib = geometry(rows, cols, pair, sms)
+    assert per_slab >= 1
+    consumed = {}
+    contributions = {}   # group -> list of (slab, cta)
+    for s in range(slabs):
+        kb_lo = s * kb // slabs
+        kbs = (s + 1) * kb // slabs - kb_lo
+        assert 1 <= kbs <= MAX_SLAB
+        blocks = groups * kbs
+        for cta in range(per_slab):
+            c0, c1 = cta * blocks // per_slab, (cta + 1) * blocks // per_slab
+            length = c1 - c0
+            assert length >= 1
+            partial = {}          # (warp, slot) -> group
+            direct = []
+            for w in range(WARPS):
+                w0, w1 = c0 + w * length // WARPS, c0 + (w + 1) * length // WARPS
+                if w1 == w0:
+                    continue
+                first_group = w0 // kbs
+                seg_group, seg_first = first_group, w0 % kbs
+
+                def flush(group, first_kbi, last_kbi):
+                    if first_kbi == 0 and last_kbi + 1 == kbs:
+                        direct.append(group)
+                    else:
+                        slot = 0 if group == first_group else 1
+                        assert (w, slot) not in partial
+                        partial[(w, slot)] = group
+
+                for at in range(w0, w1):
+                    group, kbi = at // kbs, at % kbs
+                    if group != seg_group:
+                        flush(seg_group, seg_first, kbs - 1)
+                        seg_group, seg_first = group, 0
+                    key = (group, kb_lo + kbi)
+                    assert key not in consumed
+                    consumed[key] = (s, cta, w)
+                flush(seg_group, seg_first, (w1 - 1) % kbs)
+            # CTA-level assembly
+            assembled = []
+            first, count = c0 // kbs, (c1 - 1) // kbs - c0 // kbs + 1
+            for index in range(count):
+                group = first + index
+                lo, hi = max(group * kbs, c0), min((group + 1) * kbs, c1)
+                w_lo, w_hi = span_of(lo - c0, length, WARPS), span_of(hi - 1 - c0, length, WARPS)
+                if w_lo == w_hi and lo == group * kbs and hi == (group + 1) * kbs:
+                    assert group in direct
+                    continue
+                used = 0
+                for w in range(w_lo, w_hi + 1):
+                    b0, b1 = c0 + w * length // WARPS, c0 + (w + 1) * length // WARPS
+                    if b1 == b0:
+                        continue
+                    slot = 0 if b0 // kbs == group else 1
+                    assert partial.pop((w, slot)) == group
+                    used += 1
+                assert used >= 1
+                assembled.append(group)
+            assert not partial, "a warp partial was never combined"
+            for group in direct + assembled:
+                contributions.setdefault(group, []).append((s, cta))
+    assert len(consumed) == groups * kb
+    for group in range(groups):
+        total, slots = contributors(groups, kb, slabs, per_slab, group)
+        got = contributions.get(group, [])
+        assert len(got) == total == len(set(got)), (group, total, got)
+        assert total <= max_contrib
+        assert sorted(slots[c] for c in got) == list(range(total))
+
+
+@pytest.mark.parametrize("rows,cols,pair", [
+    (17408, 5120, False), (17408, 5120, True), (5120, 17408, False), (10240, 5120, False), (5120, 5120, False),
+    (5120, 10240, False), (2176, 5120, True), (5120, 2176, False), (4352, 5120, True), (5120, 4352, False),
+    (32, 128, False), (16, 128, True), (64, 256, False), (128, 17408, False), (96, 640, False), (48, 5120, True),
+    (32, 5248, False), (6144, 5120, False)])
+@pytest.mark.parametrize("sms", [148, 132, 7, 1])
+def test_every_block_once_and_counters_match(rows, cols, pair, sms):
+    simulate(rows, cols, pair, sms)

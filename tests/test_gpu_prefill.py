@@ -1,0 +1,157 @@
+"""GPU parity of the prefill path: activation quantiser and tcgen05 block-scaled GEMM."""
+from ctypes import byref
+
+import numpy as np
+import pytest
+
+import oracle
+from augur_v100_b200 import abi, synth
+from helpers import TOLERANCE, bits_from_torch_bf16, rel_error, torch_bf16_from_bits
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    import torch
+    from augur_v100_b200 import host
+    torch.cuda.set_device(0)
+    stream = host.Stream(0)
+    plan = host.Plan(stream, 1 << 20)
+    yield {"torch": torch, "host": host, "stream": stream, "plan": plan, "device": torch.device("cuda", 0)}
+    plan.close()
+    stream.close()
+
+
+@pytest.mark.parametrize("tokens,cols,terms,glob", [(128, 64, 1, 1.0), (128, 256, 2, 2.0 ** -8), (256, 2176, 3, 0.01),
+                                                    (384, 5120, 1, 2.0 ** -8)])
+def test_activation_quantiser_is_bit_exact(ctx, tokens, cols, terms, glob):
+    host, torch = ctx["host"], ctx["torch"]
+    rng = np.random.default_rng(tokens + cols)
+    x = rng.standard_normal((tokens, cols)).astype(np.float32)
+    x[0, :16] = 0.0                       # an all-zero group
+    x[1, 16:32] *= 1e-6                   # below the smallest scale
+    x[2, 32:48] *= 1e4                    # saturates the largest scale when glob is small
+    x[3, :8] = [0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, -0.25]   # ties (after scaling by an exact scale)
+    x_bits = synth.f32_to_bf16_bits(x)
+    weight = host.Nvfp4Sm100Weight(ctx["stream"], abi.LAYOUT_TCGEN05, 128, cols,
+                                   torch.zeros(host.repack_extent(abi.LAYOUT_TCGEN05, 128, cols), dtype=torch.uint8,
+                                               device=ctx["device"]), 1.0)
+    lin = host.Nvfp4Sm100PrefillLinear.bind(ctx["plan"], weight, torch_bf16_from_bits(x_bits, ctx["device"]),
+                                            terms=terms, activation_global_scale=glob)
+    lin.submit_quant()
+    ctx["stream"].synchronize()
+    codes, scales = lin.staged_planes()
+    want_codes, want_scales = oracle.act_quant(x_bits, tokens, cols, glob, terms)
+    assert np.array_equal(scales, want_scales)
+    assert np.array_equal(codes, want_codes)
+
+
+def _run_gemm(ctx, w_planes, a_codes, a_scales, rows, cols, tokens, terms, g_w, g_a):
+    """Uploads explicit weight and (already quantised) activation planes and runs the GEMM entry."""
+    host, torch = ctx["host"], ctx["torch"]
+    weight = host.Nvfp4Sm100Weight.upload_checkpoint_nvfp4(ctx["stream"], abi.LAYOUT_TCGEN05, rows, cols,
+                                                           w_planes[0], w_planes[1], g_w)
+    code_planes, scale_regions = [], []
+    for t in range(terms):
+        packed = host.repack_host(abi.LAYOUT_TCGEN05, tokens, cols, a_codes[t], a_scales[t])
+        code_planes.append(packed[: tokens * cols // 2])
+        scale_regions.append(packed[tokens * cols // 2:])
+    staged = torch.from_numpy(np.concatenate(code_planes + scale_regions)).to(ctx["device"])
+    out = torch.full((tokens, rows), float("nan"), dtype=torch.bfloat16, device=ctx["device"])
+    args = abi.header(abi.GemmArgs)
+    args.weight, args.weight_len_bytes = weight.packed.data_ptr(), weight.packed.numel()
+    args.activation, args.activation_len_bytes = staged.data_ptr(), staged.numel()
+    args.output_bf16, args.output_len_bytes = out.data_ptr(), out.numel() * 2
+    args.rows, args.cols, args.tokens, args.activation_terms = rows, cols, tokens, terms
+    args.weight_global_scale, args.activation_global_scale = g_w, g_a
+    s, plan, lib = ctx["stream"], ctx["plan"], abi.lib()
+    res = lib.augur_cuda_nvfp4_sm100_gemm_bf16_preflight_v1(s.ordinal, s.handle, plan.handle, byref(args))
+    assert res.status == 0, (res.status, res.raw_cuda_status)
+    res = lib.augur_cuda_nvfp4_sm100_gemm_bf16_prevalidated_submit_v1(s.ordinal, s.handle, plan.handle, byref(args))
+    assert res.status == 0, (res.status, res.raw_cuda_status)
+    s.synchronize()
+    status = plan.device_status()
+    assert status == 0, hex(status)
+    return bits_from_torch_bf16(out)
+
+
+def _check_gemm(ctx, rows, cols, tokens, terms=1, seed=0, unit_scales=False):
+    w_codes, w_scales, g_w = synth.make_weight(seed, 70, "w", rows, cols)
+    g_a = 2.0 ** -8
+    x_bits = synth.make_activation(seed, 70, "x", tokens, cols)
+    a_codes, a_scales = oracle.act_quant(x_bits, tokens, cols, g_a, terms)
+    if unit_scales:
+        w_scales = np.full_like(w_scales, 0x38)
+        a_scales = np.full_like(a_scales, 0x38)
+    got = _run_gemm(ctx, (w_codes, w_scales), a_codes, a_scales, rows, cols, tokens, terms, g_w, g_a)
+    a64 = oracle.act_dequant_f64(a_codes, a_scales, g_a, tokens, cols, terms)
+    y64 = oracle.linear_f64_xf64(w_codes, w_scales, g_w, rows, cols, a64, threads=oracle.max_threads())
+    err = rel_error(got, y64)
+    assert err <= TOLERANCE, err
+    return err
+
+
+# Ordered from the smallest exercise of the instruction to the full pipeline, so that a failure
+# localises: one MMA -> distinct scales -> four MMAs per stage -> N = 256 -> several stages -> many tiles.
+def test_gemm_single_mma_unit_scales(ctx):
+    _check_gemm(ctx, rows=128, cols=64, tokens=128, unit_scales=True)
+
+
+def test_gemm_single_mma_distinct_scales(ctx):
+    _check_gemm(ctx, rows=128, cols=64, tokens=128)
+
+
+def test_gemm_one_stage_four_mmas(ctx):
+    _check_gemm(ctx, rows=128, cols=256, tokens=128, seed=1)
+
+
+def test_gemm_n256_tile(ctx):
+    _check_gemm(ctx, rows=256, cols=256, tokens=128, seed=2)
+
+
+def test_gemm_ragged_k_and_n(ctx):
+    _check_gemm(ctx, rows=384, cols=320, tokens=128, seed=3)       # k tail of 64, n tail of 128
+
+
+def test_gemm_many_stages(ctx):
+    _check_gemm(ctx, rows=256, cols=2176, tokens=128, seed=4)      # 8.5 stages: ring wrap + tail
+
+
+def test_gemm_many_tiles_persistent(ctx):
+    _check_gemm(ctx, rows=5120, cols=512, tokens=1024, seed=5)     # 160 tiles > SM count
+
+
+def test_gemm_residual_terms(ctx):
+    e1 = _check_gemm(ctx, rows=256, cols=1024, tokens=128, terms=1, seed=6)
+    e3 = _check_gemm(ctx, rows=256, cols=1024, tokens=128, terms=3, seed=6)
+    assert e1 <= TOLERANCE and e3 <= TOLERANCE
+
+
+def test_prefill_linear_end_to_end_and_quantisation_error(ctx):
+    # BF16 activations in, BF16 out; reports how far W4A4 with 1..3 residual terms is from the
+    # BF16-activation oracle (the number the block-scaled MMA path trades for tensor throughput).
+    host = ctx["host"]
+    rows, cols, tokens = 512, 5120, 256
+    w_codes, w_scales, g_w = synth.make_weight(0, 2, "gate", rows, cols)
+    x_bits = synth.make_activation(0, 2, "x", tokens, cols)
+    weight = host.Nvfp4Sm100Weight.upload_checkpoint_nvfp4(ctx["stream"], abi.LAYOUT_TCGEN05, rows, cols, w_codes, w_scales, g_w)
+    x = torch_bf16_from_bits(x_bits, ctx["device"])
+    y64 = oracle.linear_f64(w_codes, w_scales, g_w, rows, cols, x_bits, threads=oracle.max_threads())
+    rms = np.sqrt(np.mean(y64 * y64))
+    errors = {}
+    for terms in (1, 2, 3):
+        lin = host.Nvfp4Sm100PrefillLinear.bind(ctx["plan"], weight, x, terms=terms, activation_global_scale=2.0 ** -8)
+        lin.submit_for_plan()
+        ctx["stream"].synchronize()
+        assert ctx["plan"].device_status() == 0
+        got = synth.bf16_bits_to_f32(bits_from_torch_bf16(lin.out)).astype(np.float64).reshape(y64.shape)
+        errors[terms] = float(np.sqrt(np.mean((got - y64) ** 2)) / rms)
+        # kernel error in isolation: fp64 oracle fed the very activations the quantiser produced
+        codes, scales = lin.staged_planes()
+        a64 = oracle.act_dequant_f64(codes, scales, 2.0 ** -8, tokens, cols, terms)
+        yq = oracle.linear_f64_xf64(w_codes, w_scales, g_w, rows, cols, a64, threads=oracle.max_threads())
+        assert rel_error(bits_from_torch_bf16(lin.out), yq) <= TOLERANCE
+    print("relative rms error vs BF16-activation oracle by residual terms:", errors)
+    assert errors[1] < 0.2 and errors[2] < errors[1] / 3 and errors[3] < errors[2] / 3
+    assert errors[3] <= TOLERANCE
