@@ -36,6 +36,13 @@ constexpr uint32_t kWarps = 16;
 constexpr uint32_t kDepth = 2;             // weight blocks in flight per warp
 constexpr uint32_t kMaxSlabBlocks = 40;    // 40 * 128 k = 5120 activations columns per slab (80 KB)
 constexpr uint32_t kSlotFloats = 256;      // one partial tile: 32 lanes x 8 f32
+// Plan scratch layout: two arrival-counter regions (one per member of a two-launch program)
+// at fixed offsets, then partial-sum slots. Counters must read zero when a launch starts and
+// every launch leaves them at zero; keeping them apart from the slots means no launch of any
+// shape can ever leave slot data where another launch expects counters.
+constexpr uint32_t kMaxGroups = 16384;
+constexpr uint64_t kCounterRegionBytes = static_cast<uint64_t>(kMaxGroups) * 4;
+constexpr uint64_t kCounterBytes = 2 * kCounterRegionBytes;
 
 struct GemvParams {
     const uint8_t* weight;
@@ -50,7 +57,7 @@ struct GemvParams {
 
 struct GemvGeometry {
     uint32_t groups, kb_count, slabs, ctas_per_slab, max_contrib;
-    uint64_t scratch_bytes;   // counters + partial slots
+    uint64_t partial_bytes;   // partial-sum slots
 };
 
 // Host-side geometry; `sm_count` CTAs at most.
@@ -66,8 +73,7 @@ GemvGeometry geometry(uint32_t rows, uint32_t cols, bool pair, uint32_t sm_count
     if (per_slab > least_blocks) per_slab = least_blocks;  // every CTA owns at least one block
     g.ctas_per_slab = static_cast<uint32_t>(per_slab);
     g.max_contrib = g.slabs * ((g.ctas_per_slab + g.groups - 1) / g.groups + 1);
-    g.scratch_bytes = (static_cast<uint64_t>(g.groups) * 4 + 255) / 256 * 256 +
-                      static_cast<uint64_t>(g.groups) * g.max_contrib * kSlotFloats * 4;
+    g.partial_bytes = static_cast<uint64_t>(g.groups) * g.max_contrib * kSlotFloats * 4;
     return g;
 }
 
@@ -421,8 +427,9 @@ void gemv_ranges(const augur_cuda_nvfp4_sm100_gemv_args_v1* a, Range (&r)[3]) {
     r[2] = {a->output, a->output_len_bytes, 4};
 }
 
+// `partial_offset`..`partial_limit` is the part of the plan scratch this launch may use for slots.
 bool check_gemv(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* plan,
-                const augur_cuda_nvfp4_sm100_gemv_args_v1* a, uint64_t scratch_offset, uint64_t scratch_limit,
+                const augur_cuda_nvfp4_sm100_gemv_args_v1* a, uint64_t partial_offset, uint64_t partial_limit,
                 bool full, augur_cuda_result_v1* failure) {
     *failure = invalid();
     if (!header_ok(d, s, a)) {
@@ -434,7 +441,10 @@ bool check_gemv(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_p
     bool pair = false;
     if (!plan_ok(plan, d, s) || !check_gemv_scalars(a, &pair)) return false;
     const GemvGeometry g = geometry(a->rows, a->cols, pair, plan->sm_count);
-    if (g.ctas_per_slab == 0 || scratch_offset + g.scratch_bytes > scratch_limit) return false;
+    if (g.ctas_per_slab == 0 || g.groups > kMaxGroups || partial_offset < kCounterBytes ||
+        partial_limit < partial_offset || g.partial_bytes > partial_limit - partial_offset) {
+        return false;
+    }
     Range r[4];
     Range base[3];
     gemv_ranges(a, base);
@@ -445,16 +455,15 @@ bool check_gemv(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_p
 }
 
 void launch_gemv(augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* plan,
-                 const augur_cuda_nvfp4_sm100_gemv_args_v1* a, uint64_t scratch_offset) {
+                 const augur_cuda_nvfp4_sm100_gemv_args_v1* a, uint32_t member, uint64_t partial_offset) {
     const bool pair = a->epilogue == AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16;
     const GemvGeometry g = geometry(a->rows, a->cols, pair, plan->sm_count);
     GemvParams p{};
     p.weight = reinterpret_cast<const uint8_t*>(a->weight);
     p.x = reinterpret_cast<const uint16_t*>(a->input_bf16);
     p.out = reinterpret_cast<void*>(a->output);
-    uint8_t* scratch = plan->scratch + scratch_offset;
-    p.counters = reinterpret_cast<uint32_t*>(scratch);
-    p.partials = reinterpret_cast<float*>(scratch + (static_cast<uint64_t>(g.groups) * 4 + 255) / 256 * 256);
+    p.counters = reinterpret_cast<uint32_t*>(plan->scratch + member * kCounterRegionBytes);
+    p.partials = reinterpret_cast<float*>(plan->scratch + partial_offset);
     p.groups = g.groups; p.kb_count = g.kb_count; p.slabs = g.slabs; p.ctas_per_slab = g.ctas_per_slab;
     p.max_contrib = g.max_contrib;
     p.rows = a->rows; p.cols = a->cols; p.tokens = a->tokens; p.epilogue = a->epilogue;
@@ -487,10 +496,10 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_scra
         if (!pair && rows % 32 != 0) continue;
         for (uint32_t sms = 1; sms <= 512; ++sms) {
             const GemvGeometry g = geometry(rows, cols, pair != 0, sms);
-            if (g.scratch_bytes > worst) worst = g.scratch_bytes;
+            if (g.partial_bytes > worst) worst = g.partial_bytes;
         }
     }
-    *out_bytes = worst;
+    *out_bytes = kCounterBytes + worst;
     return ok();
 }
 
@@ -498,24 +507,24 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_bf16
     int32_t d, augur_cuda_stream_t s, augur_cuda_nvfp4_sm100_plan_v1* plan,
     const augur_cuda_nvfp4_sm100_gemv_args_v1* a) {
     augur_cuda_result_v1 failure;
-    return check_gemv(d, s, plan, a, 0, plan ? plan->scratch_bytes : 0, true, &failure) ? ok() : failure;
+    return check_gemv(d, s, plan, a, kCounterBytes, plan ? plan->scratch_bytes : 0, true, &failure) ? ok() : failure;
 }
 
 extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_bf16_prevalidated_submit_v1(
     int32_t d, augur_cuda_stream_t s, augur_cuda_nvfp4_sm100_plan_v1* plan,
     const augur_cuda_nvfp4_sm100_gemv_args_v1* a) {
     augur_cuda_result_v1 failure;
-    if (!check_gemv(d, s, plan, a, 0, plan ? plan->scratch_bytes : 0, false, &failure)) return failure;
+    if (!check_gemv(d, s, plan, a, kCounterBytes, plan ? plan->scratch_bytes : 0, false, &failure)) return failure;
     if (consume_injected_fault()) return make_result(AUGUR_CUDA_STATUS_DIAGNOSTIC_FAULT_INJECTED);
     const cudaError_t e = cudaSetDevice(d);
     if (e != cudaSuccess) return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE, e);
-    launch_gemv(s, plan, a, 0);
+    launch_gemv(s, plan, a, 0, kCounterBytes);
     return submitted();
 }
 
 namespace {
-// Both members plus every cross alias, before anything is enqueued. The two members
-// use separate halves of the plan scratch so that their launches may overlap.
+// Both members plus every cross alias, before anything is enqueued. The two members use
+// separate counter regions and separate halves of the slot area, so their launches may overlap.
 bool check_mlp(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* plan,
                const augur_cuda_nvfp4_sm100_mlp_args_v1* a, bool full, uint64_t* down_offset,
                augur_cuda_result_v1* failure) {
@@ -527,10 +536,11 @@ bool check_mlp(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_pl
         return false;
     }
     if (!plan_ok(plan, d, s)) return false;
-    const uint64_t half = plan->scratch_bytes / 2 / 256 * 256;
-    *down_offset = half;
-    if (!check_gemv(d, s, plan, &a->gate_up, 0, half, false, failure)) return false;
-    if (!check_gemv(d, s, plan, &a->down, half, plan->scratch_bytes, false, failure)) return false;
+    if (plan->scratch_bytes < kCounterBytes) return false;
+    const uint64_t middle = kCounterBytes + (plan->scratch_bytes - kCounterBytes) / 2 / 256 * 256;
+    *down_offset = middle;
+    if (!check_gemv(d, s, plan, &a->gate_up, kCounterBytes, middle, false, failure)) return false;
+    if (!check_gemv(d, s, plan, &a->down, middle, plan->scratch_bytes, false, failure)) return false;
     *failure = invalid();
     if (a->gate_up.epilogue != AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16 ||
         a->down.epilogue == AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16) {
@@ -569,9 +579,9 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_mlp_preva
     if (consume_injected_fault()) return make_result(AUGUR_CUDA_STATUS_DIAGNOSTIC_FAULT_INJECTED);
     const cudaError_t e = cudaSetDevice(d);
     if (e != cudaSuccess) return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE, e);
-    launch_gemv(s, plan, &a->gate_up, 0);
+    launch_gemv(s, plan, &a->gate_up, 0, kCounterBytes);
     augur_cuda_result_v1 first = submitted();
     if (first.status != AUGUR_CUDA_STATUS_OK) return first;
-    launch_gemv(s, plan, &a->down, down_offset);
+    launch_gemv(s, plan, &a->down, 1, down_offset);
     return submitted();
 }

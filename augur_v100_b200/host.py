@@ -308,9 +308,9 @@ class Nvfp4Sm100FfnProgram:
 
 
 def mlp_scratch_bytes(hidden: int, intermediate: int, tokens: int = 8) -> int:
-    """Plan scratch for an FFN program: the two members use separate halves."""
+    """Plan scratch for an FFN program: counter regions plus one half of the slot area per member."""
     need = max(gemv_scratch_bytes(intermediate, hidden, tokens), gemv_scratch_bytes(hidden, intermediate, tokens))
-    return 2 * (need + 256)
+    return 2 * need + 512
 
 
 def allocation_snapshot() -> tuple[int, int]:

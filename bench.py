@@ -334,8 +334,7 @@ def main():
     parser.add_argument("--layers", type=int, default=LAYERS,
                         help="distinct layers streamed per step (smaller values are for profiler captures only)")
     args = parser.parse_args()
-    global LAYERS
-    LAYERS = args.layers
+    globals()["LAYERS"] = args.layers
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -30,3 +30,11 @@ def torch_bf16_from_bits(bits: np.ndarray, device):
 def bits_from_torch_bf16(t) -> np.ndarray:
     import torch
     return t.detach().contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def rms_error(y_bf16_bits: np.ndarray, y64: np.ndarray) -> float:
+    """max |y - y64| / rms(y64): for end-to-end chains whose intermediate is rounded to BF16,
+    where outputs near zero carry an absolute error of a few 1e-3 rms by construction."""
+    y = synth.bf16_bits_to_f32(np.asarray(y_bf16_bits, dtype=np.uint16)).astype(np.float64).reshape(y64.shape)
+    rms = float(np.sqrt(np.mean(y64 * y64))) or 1.0
+    return float(np.max(np.abs(y - y64)) / rms)

@@ -7,7 +7,7 @@ import pytest
 
 import oracle
 from augur_v100_b200 import abi, synth
-from helpers import TOLERANCE, bits_from_torch_bf16, rel_error, rel_error_f32, torch_bf16_from_bits
+from helpers import TOLERANCE, bits_from_torch_bf16, rel_error, rel_error_f32, rms_error, torch_bf16_from_bits
 
 pytestmark = pytest.mark.gpu
 
@@ -205,9 +205,10 @@ def test_mlp_program_matches_oracle(ctx, hidden, inter, tokens):
     y64_from_h = oracle.linear_f64(down[0], down[1], down[2], hidden, inter,
                                    bits_from_torch_bf16(program.intermediate), threads=4)
     assert rel_error(bits_from_torch_bf16(program.out), y64_from_h) <= TOLERANCE
+    # end to end against the oracle chain (whose intermediate is rounded independently): rms-relative
+    assert rms_error(bits_from_torch_bf16(program.out), y64) <= TOLERANCE
     h_ref, y_ref = oracle.mlp_bf16(gate, up, down, hidden, inter, x_bits, threads=4)
-    yr = synth.bf16_bits_to_f32(y_ref).astype(np.float64)
-    assert rel_error(bits_from_torch_bf16(program.out), yr) <= 2 * TOLERANCE
+    assert rms_error(bits_from_torch_bf16(program.out), synth.bf16_bits_to_f32(y_ref).astype(np.float64)) <= TOLERANCE
 
 
 def test_hot_path_allocates_nothing_and_counts_launches(ctx):
@@ -250,7 +251,7 @@ def test_cuda_graph_capture_and_replay_with_refreshed_inputs(ctx):
             graph.replay()
             side.synchronize()
             _, y64 = oracle.mlp_f64(gate, up, down, hidden, inter, x_bits, threads=2)
-            assert rel_error(bits_from_torch_bf16(program.out), y64) <= 2 * TOLERANCE
+            assert rms_error(bits_from_torch_bf16(program.out), y64) <= TOLERANCE
         plan.close()
 
 
