@@ -33,7 +33,9 @@ static_assert(sizeof(augur_cuda_nvfp4_sm100_gemv_args_v1) == 88, "gemv ABI");
 static_assert(sizeof(augur_cuda_nvfp4_sm100_mlp_args_v1) == 184, "mlp ABI");
 
 constexpr uint32_t kWarps = 16;
-constexpr uint32_t kDepth = 2;             // weight blocks in flight per warp
+constexpr uint32_t kDepth = 3;             // ring slots (weight blocks in flight) per warp
+constexpr uint32_t kScaleScratchBytes = 1024;   // per warp: the f32 block scales of the block being consumed
+constexpr uint32_t kWaitLimit = 1u << 18;   // bounded polls of a ring slot before the kernel gives up
 constexpr uint32_t kMaxSlabBlocks = 40;    // 40 * 128 k = 5120 activations columns per slab (80 KB)
 constexpr uint32_t kSlotFloats = 256;      // one partial tile: 32 lanes x 8 f32
 // Plan scratch layout: two arrival-counter regions (one per member of a two-launch program)
@@ -50,14 +52,21 @@ struct GemvParams {
     void* out;
     float* partials;
     uint32_t* counters;
-    uint32_t groups, kb_count, slabs, ctas_per_slab, max_contrib;
+    uint32_t* status_word;
+#ifdef AUGUR_GEMV_TRACE
+    unsigned long long* trace;   // [CTA][4] nanosecond stamps: start, staged, streamed, done
+#endif
+    const uint8_t* staged;     // activations as BF16 B fragments, [cols/32][32 lanes][16 bytes]
+    const float* factors;      // per token: two factors whose product undoes the staging exponent
+    uint32_t groups, kb_count, slabs, ctas_per_slab, max_contrib, unit;
     uint32_t rows, cols, tokens, epilogue;
     float global_a, global_b;
 };
 
 struct GemvGeometry {
-    uint32_t groups, kb_count, slabs, ctas_per_slab, max_contrib;
+    uint32_t groups, kb_count, slabs, ctas_per_slab, max_contrib, unit;
     uint64_t partial_bytes;   // partial-sum slots
+    uint64_t staged_bytes;    // staged activations + factors
 };
 
 // Host-side geometry; `sm_count` CTAs at most.
@@ -69,113 +78,146 @@ GemvGeometry geometry(uint32_t rows, uint32_t cols, bool pair, uint32_t sm_count
     const uint32_t min_kbs = g.kb_count / g.slabs;
     // CTAs never wait on one another, so the grid may exceed the SM count when slabs > SMs.
     uint64_t per_slab = sm_count / g.slabs ? sm_count / g.slabs : 1;
-    const uint64_t least_blocks = static_cast<uint64_t>(g.groups) * min_kbs;
-    if (per_slab > least_blocks) per_slab = least_blocks;  // every CTA owns at least one block
+    // With one k-slab and plenty of row groups per CTA, spans are cut at row-group boundaries:
+    // every group is then finished inside one CTA (no scratch, no fences) at the price of at
+    // most one group of imbalance. Otherwise spans are cut at single blocks.
+    g.unit = (g.slabs == 1 && g.groups >= 4 * per_slab) ? min_kbs : 1;
+    const uint64_t least_units = static_cast<uint64_t>(g.groups) * min_kbs / g.unit;
+    if (per_slab > least_units) per_slab = least_units;  // every CTA owns at least one unit
     g.ctas_per_slab = static_cast<uint32_t>(per_slab);
     g.max_contrib = g.slabs * ((g.ctas_per_slab + g.groups - 1) / g.groups + 1);
     g.partial_bytes = static_cast<uint64_t>(g.groups) * g.max_contrib * kSlotFloats * 4;
+    g.staged_bytes = static_cast<uint64_t>(cols) * 16 + 256;
     return g;
 }
 
-__device__ __forceinline__ uint4 ld_stream(const uint8_t* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
-}
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
-// Four bytes of two E2M1 codes each -> four f16x2 registers.
-__device__ __forceinline__ void cvt_e2m1x8(uint32_t word, uint32_t (&a)[4]) {
-    asm("{\n"
-        ".reg .b8 c0, c1, c2, c3;\n"
-        "mov.b32 {c0, c1, c2, c3}, %4;\n"
-        "cvt.rn.f16x2.e2m1x2 %0, c0;\n"
-        "cvt.rn.f16x2.e2m1x2 %1, c1;\n"
-        "cvt.rn.f16x2.e2m1x2 %2, c2;\n"
-        "cvt.rn.f16x2.e2m1x2 %3, c3;\n"
-        "}"
-        : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3])
-        : "r"(word));
+// ---- per-warp weight ring: bulk async copies (TMA engine) into shared memory ------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
-
-// Four E4M3 bytes -> two f16x2 registers (bytes 0,1 and bytes 2,3).
-__device__ __forceinline__ void cvt_e4m3x4(uint32_t word, uint32_t& lo, uint32_t& hi) {
-    asm("{\n"
-        ".reg .b16 h0, h1;\n"
-        "mov.b32 {h0, h1}, %2;\n"
-        "cvt.rn.f16x2.e4m3x2 %0, h0;\n"
-        "cvt.rn.f16x2.e4m3x2 %1, h1;\n"
-        "}"
-        : "=r"(lo), "=r"(hi)
-        : "r"(word));
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-
-__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, __half2 b) {
-    __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), b);
-    return *reinterpret_cast<uint32_t*>(&r);
-}
-
-__device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
     asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+// Issues the copy of one 2304-byte weight block into a ring slot (one lane calls this).
+__device__ __forceinline__ void issue_block(uint32_t slot_addr, uint32_t bar, const uint8_t* block) {
+    // order this warp's earlier generic-proxy reads of the slot before the async-proxy write
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    mbar_expect_tx(bar, kStreamBlockBytes);
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(slot_addr), "l"(block), "r"(kStreamBlockBytes), "r"(bar)
+                 : "memory");
 }
 
-struct WeightRegs {
-    uint4 code[4];   // [tile*2 + quad]
-    uint4 scale[2];  // [tile]
-};
+constexpr uint32_t kCodeMask = 0x81C081C0u;   // BF16 sign + two low exponent bits + top mantissa bit, twice
 
-__device__ __forceinline__ void load_block(WeightRegs& r, const uint8_t* block, uint32_t lane) {
+// Eight E4M3 bytes -> eight f32 values.
+__device__ __forceinline__ void cvt_e4m3x8(uint2 bytes, float (&out)[8]) {
+    uint32_t h[4];
+    asm("{\n"
+        ".reg .b16 a, b, c, d;\n"
+        "mov.b32 {a, b}, %4;\n"
+        "mov.b32 {c, d}, %5;\n"
+        "cvt.rn.f16x2.e4m3x2 %0, a;\n"
+        "cvt.rn.f16x2.e4m3x2 %1, b;\n"
+        "cvt.rn.f16x2.e4m3x2 %2, c;\n"
+        "cvt.rn.f16x2.e4m3x2 %3, d;\n"
+        "}"
+        : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3])
+        : "r"(bytes.x), "r"(bytes.y));
 #pragma unroll
-    for (uint32_t i = 0; i < 4; ++i) r.code[i] = ld_stream(block + (i * 32 + lane) * 16);
-#pragma unroll
-    for (uint32_t t = 0; t < 2; ++t) r.scale[t] = ld_stream(block + kStreamCodeBytes + (t * 8 + (lane >> 2)) * 16);
-}
-
-// acc[t*4 + i] += block(32 rows x 128 k) * activations, `act` points at this block's B fragments.
-__device__ __forceinline__ void compute_block(float (&acc)[8], const WeightRegs& r, const uint4* act, uint32_t lane) {
-    uint4 bfrag[4];
-#pragma unroll
-    for (uint32_t kp = 0; kp < 4; ++kp) bfrag[kp] = act[kp * 32 + lane];
-#pragma unroll
-    for (uint32_t t = 0; t < 2; ++t) {
-        // scale bytes: x,y = row g (k-steps 0..3, 4..7); z,w = row g+8
-        uint32_t sg[4], sh[4];  // f16x2 pairs: k-steps (0,1) (2,3) (4,5) (6,7)
-        cvt_e4m3x4(r.scale[t].x, sg[0], sg[1]);
-        cvt_e4m3x4(r.scale[t].y, sg[2], sg[3]);
-        cvt_e4m3x4(r.scale[t].z, sh[0], sh[1]);
-        cvt_e4m3x4(r.scale[t].w, sh[2], sh[3]);
-        float(&d)[4] = *reinterpret_cast<float(*)[4]>(&acc[t * 4]);
-#pragma unroll
-        for (uint32_t q = 0; q < 2; ++q) {
-            const uint4 cw = r.code[t * 2 + q];
-            const uint32_t words[4] = {cw.x, cw.y, cw.z, cw.w};
-#pragma unroll
-            for (uint32_t j = 0; j < 4; ++j) {
-                const uint32_t ks = q * 4 + j;
-                const __half2 pg = *reinterpret_cast<const __half2*>(&sg[ks >> 1]);
-                const __half2 ph = *reinterpret_cast<const __half2*>(&sh[ks >> 1]);
-                const __half2 scale_g = (ks & 1) ? __high2half2(pg) : __low2half2(pg);
-                const __half2 scale_h = (ks & 1) ? __high2half2(ph) : __low2half2(ph);
-                uint32_t a[4];
-                cvt_e2m1x8(words[j], a);
-                a[0] = hmul2_u32(a[0], scale_g);
-                a[1] = hmul2_u32(a[1], scale_h);
-                a[2] = hmul2_u32(a[2], scale_g);
-                a[3] = hmul2_u32(a[3], scale_h);
-                const uint4 b = bfrag[ks >> 1];
-                mma_f16(d, a, (ks & 1) ? b.z : b.x, (ks & 1) ? b.w : b.y);
-            }
-        }
+    for (uint32_t i = 0; i < 4; ++i) {
+        const float2 pair = __half22float2(*reinterpret_cast<const __half2*>(&h[i]));
+        out[2 * i] = pair.x;
+        out[2 * i + 1] = pair.y;
     }
 }
 
+// The 256 block scales of a weight block are needed as f32 by every lane of a quad alike.
+// Instead of each lane converting the bytes it needs (four times redundantly), the warp
+// converts them once - 8 bytes per lane - into a per-warp 1 KB scratch laid out so that one
+// 16-byte load gives a lane the {row g, row g+8} pairs of two consecutive k-steps:
+//   [tile t:2][k-step pair kp:4][g:8][k-step parity:2][row g / row g+8].
+__device__ __forceinline__ void convert_block_scales(const uint8_t* slot, float* scratch, uint32_t lane) {
+    // lane L owns source bytes [8L, 8L+8): tile L/16, row pair g = (L%16)/2, k-steps 4*(L%2)..+3
+    const uint2 bytes = *reinterpret_cast<const uint2*>(slot + kStreamCodeBytes + lane * 8);
+    float v[8];
+    cvt_e4m3x8(bytes, v);
+    const uint32_t t = lane >> 4, g = (lane >> 1) & 7, half = lane & 1;
+    float4* dst = reinterpret_cast<float4*>(scratch) + ((t * 4 + half * 2) * 8 + g);
+    dst[0] = make_float4(v[0], v[1], v[2], v[3]);      // k-step pair 2*half
+    dst[8] = make_float4(v[4], v[5], v[6], v[7]);      // k-step pair 2*half + 1
+}
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
+}
+
+// One k-step (16 k) of one 16-row tile: the code word becomes the four A-fragment registers
+// with shifts and masks only (each register is two BF16 numbers equal to e2m1 * 2^-126; the
+// tensor core takes the subnormal 0.5 * 2^-126 exactly), one MMA against the staged
+// activations, then the block scales of rows g and g+8 are applied to the 16 x 8 partial
+// product in f32.
+__device__ __forceinline__ void tile_step(float (&acc)[4], uint32_t w, float sg, float sh, uint32_t b0, uint32_t b1) {
+    uint32_t a[4];
+    a[0] = w & kCodeMask;
+    a[1] = (w << 3) & kCodeMask;
+    a[2] = (w << 6) & kCodeMask;
+    a[3] = (((w >> 10) & 0x001B001Bu) * 0x4108u) & kCodeMask;
+    float d[4];
+    mma_bf16(d, a, b0, b1);
+    acc[0] = fmaf(sg, d[0], acc[0]);
+    acc[1] = fmaf(sg, d[1], acc[1]);
+    acc[2] = fmaf(sh, d[2], acc[2]);
+    acc[3] = fmaf(sh, d[3], acc[3]);
+}
+
+// Four k-steps: one 16-byte code vector of this lane, two scale quads (k-step pairs), two
+// B-fragment quads.
+__device__ __forceinline__ void tile_quad(float (&acc)[4], const uint4& codes, const float4& s01, const float4& s23,
+                                          const uint4& b01, const uint4& b23) {
+    tile_step(acc, codes.x, s01.x, s01.y, b01.x, b01.y);
+    tile_step(acc, codes.y, s01.z, s01.w, b01.z, b01.w);
+    tile_step(acc, codes.z, s23.x, s23.y, b23.x, b23.y);
+    tile_step(acc, codes.w, s23.z, s23.w, b23.z, b23.w);
+}
+
+// acc[t*4 + i] += block (32 rows x 128 k, in a ring slot) * activations (this block's B fragments).
+__device__ __forceinline__ void compute_block(float (&acc)[8], const uint8_t* slot, const uint4* act, float* scale_scratch,
+                                              uint32_t lane) {
+    convert_block_scales(slot, scale_scratch, lane);
+    __syncwarp();
+    const uint4* codes = reinterpret_cast<const uint4*>(slot);
+    const float4* scales = reinterpret_cast<const float4*>(scale_scratch) + (lane >> 2);
+    const uint4 b0 = act[lane], b1 = act[32 + lane], b2 = act[64 + lane], b3 = act[96 + lane];
+    float(&d0)[4] = *reinterpret_cast<float(*)[4]>(&acc[0]);
+    float(&d1)[4] = *reinterpret_cast<float(*)[4]>(&acc[4]);
+    const uint4 c00 = codes[lane], c01 = codes[32 + lane], c10 = codes[64 + lane], c11 = codes[96 + lane];
+    tile_quad(d0, c00, scales[0], scales[8], b0, b1);          // tile 0, k-step pairs 0, 1
+    tile_quad(d1, c10, scales[32], scales[40], b0, b1);        // tile 1
+    tile_quad(d0, c01, scales[16], scales[24], b2, b3);        // tile 0, k-step pairs 2, 3
+    tile_quad(d1, c11, scales[48], scales[56], b2, b3);
+    __syncwarp();   // the scratch is rewritten for the next block
+}
+
 // Which of `parts` equal contiguous spans of [0, total) holds index `at`.
-__device__ __forceinline__ uint32_t span_of(uint64_t at, uint64_t total, uint32_t parts) {
-    return static_cast<uint32_t>(((at + 1) * parts - 1) / total);
+// All block indices fit 32 bits with room for this product: rows*cols <= 2^32 makes
+// groups*blocks-per-group <= 2^21, and `parts` is at most a few hundred.
+__device__ __forceinline__ uint32_t span_of(uint32_t at, uint32_t total, uint32_t parts) {
+    return ((at + 1) * parts - 1) / total;
 }
 
 __device__ __forceinline__ void epilogue(const GemvParams& p, uint32_t group, const float (&v)[8], uint32_t lane) {
@@ -209,15 +251,93 @@ __device__ __forceinline__ void epilogue(const GemvParams& p, uint32_t group, co
     }
 }
 
+// BF16 bits times 2^shift by exponent arithmetic: exact; zeros and subnormals become zero,
+// and anything that would leave the normal range on the way down is flushed to zero
+// (it is more than 2^200 below the row's largest magnitude). Infinities and NaNs pass through.
+__device__ __forceinline__ uint32_t shift_bf16(uint32_t bits, int shift) {
+    const int field = static_cast<int>((bits >> 7) & 0xff);
+    if (field == 0xff) return bits;
+    const int moved = field + shift;
+    if (field == 0 || moved < 1) return bits & 0x8000u;
+    return (bits & 0x807fu) | (static_cast<uint32_t>(moved > 254 ? 254 : moved) << 7);
+}
+
+// ---- activation staging --------------------------------------------------------------------
+// One CTA per token row: finds the row's largest magnitude, picks the exponent shift e that
+// puts it in [2^100, 2^101) (so that the 2^-126-scaled weight fragments meet activations
+// large enough to keep every product a normal f32), and writes x * 2^e as BF16 in the
+// mma B-fragment order the streaming kernel copies straight into shared memory:
+//   [k-step pair][lane = token*4 + t4][4 words: b0,b1 of the even k-step, b0,b1 of the odd one].
+// Runs once per activation tensor instead of once per CTA of the streaming kernel, which is
+// launched with programmatic stream serialisation and overlaps its weight prefetch with this.
+__global__ void __launch_bounds__(512) stage_kernel(const uint16_t* __restrict__ x, uint32_t* __restrict__ staged,
+                                                    float* __restrict__ factors, uint32_t cols, uint32_t tokens) {
+    // Launched with programmatic stream serialisation: it may become resident while the kernel
+    // before it is still running, so it waits for that kernel (which may produce x, and may
+    // still be reading an older staging of this region) before doing anything, then lets
+    // the streaming kernel behind it start its weight prefetch.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    __shared__ float s_amax[16];
+    __shared__ int s_shift;
+    const uint32_t token = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const bool live = token < tokens;
+    const uint32_t chunks = cols / 8;   // 16-byte chunks of 8 bf16
+    const uint4* row = reinterpret_cast<const uint4*>(x + static_cast<uint64_t>(token) * cols);
+    float amax = 0.0f;
+    if (live) {
+        for (uint32_t c = threadIdx.x; c < chunks; c += blockDim.x) {
+            const uint4 v = __ldg(row + c);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (uint32_t i = 0; i < 4; ++i) {
+                amax = fmaxf(amax, fabsf(__uint_as_float(w[i] << 16)));
+                amax = fmaxf(amax, fabsf(__uint_as_float(w[i] & 0xffff0000u)));
+            }
+        }
+    }
+#pragma unroll
+    for (uint32_t o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (lane == 0) s_amax[warp] = amax;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float m = 0.0f;
+        for (uint32_t i = 0; i < blockDim.x / 32; ++i) m = fmaxf(m, s_amax[i]);
+        int e = 0;   // zero or non-finite rows are staged unshifted
+        const int field = static_cast<int>((__float_as_uint(m) >> 23) & 0xff);
+        if (m > 0.0f && field != 0xff && field != 0) e = 227 - field;
+        s_shift = e;
+        // partial sums are multiplied by 2^(126 - e), split in two factors that are always finite
+        const int q = 126 - e, q0 = q / 2, q1 = q - q0;
+        factors[2 * token] = __uint_as_float(static_cast<uint32_t>(127 + q0) << 23);
+        factors[2 * token + 1] = __uint_as_float(static_cast<uint32_t>(127 + q1) << 23);
+    }
+    __syncthreads();
+    const int shift = s_shift;
+    for (uint32_t c = threadIdx.x; c < chunks; c += blockDim.x) {
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (live) v = __ldg(row + c);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        // chunk c holds k = 8c..8c+7: k-step c/2, fragment register c%2; word i is the pair
+        // k%16 = 8(c%2) + 2i, +1 and belongs to lane token*4 + i
+        const uint32_t kstep = c >> 1, reg = c & 1;
+        uint32_t* dst = staged + ((kstep >> 1) * 32 + token * 4) * 4 + (kstep & 1) * 2 + reg;
+#pragma unroll
+        for (uint32_t i = 0; i < 4; ++i) {
+            dst[i * 4] = shift_bf16(w[i] & 0xffffu, shift) | (shift_bf16(w[i] >> 16, shift) << 16);
+        }
+    }
+}
+
 // One CTA's finished share of row group `group` in k-slab `slab` (whole warp calls this).
 __device__ __forceinline__ void contribute(const GemvParams& p, uint32_t group, uint32_t slab, uint32_t cta_in_slab,
                                            const float (&v)[8], uint32_t lane) {
     uint32_t total = 0, mine = 0;
     for (uint32_t s = 0; s < p.slabs; ++s) {
         const uint32_t kbs = (s + 1) * p.kb_count / p.slabs - s * p.kb_count / p.slabs;
-        const uint64_t blocks = static_cast<uint64_t>(p.groups) * kbs;
-        const uint32_t first = span_of(static_cast<uint64_t>(group) * kbs, blocks, p.ctas_per_slab);
-        const uint32_t last = span_of(static_cast<uint64_t>(group + 1) * kbs - 1, blocks, p.ctas_per_slab);
+        const uint32_t units = p.groups * kbs / p.unit;
+        const uint32_t first = span_of(group * kbs / p.unit, units, p.ctas_per_slab);
+        const uint32_t last = span_of(((group + 1) * kbs - 1) / p.unit, units, p.ctas_per_slab);
         if (s == slab) mine = total + (cta_in_slab - first);
         total += last - first + 1;
     }
@@ -248,162 +368,229 @@ __device__ __forceinline__ void contribute(const GemvParams& p, uint32_t group, 
 }
 
 __global__ void __launch_bounds__(kWarps * 32, 1) gemv_kernel(const GemvParams p) {
-    extern __shared__ __align__(16) uint8_t smem[];
-    uint4* act = reinterpret_cast<uint4*>(smem);                                   // [kbs*4][32] x 16 B
-    float* warp_partial = reinterpret_cast<float*>(smem + kMaxSlabBlocks * 4 * 512);  // [warps][2][256]
-    __shared__ float s_amax[kWarps];
-    __shared__ float s_inv_scale[8];
-    __shared__ float s_scale[8];
-
+    extern __shared__ __align__(128) uint8_t smem[];
+#ifdef AUGUR_GEMV_TRACE
+    auto stamp = [&](uint32_t which) {
+        if (threadIdx.x == 0) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            p.trace[blockIdx.x * 4 + which] = t;
+        }
+    };
+    stamp(0);
+#endif
+    // Let the next kernel in the stream become resident on SMs as this grid drains; every
+    // kernel of this library defers its global reads of produced data, and all of its global
+    // writes, until its own griddepcontrol.wait.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    uint4* act = reinterpret_cast<uint4*>(smem);                              // [kbs*4][32] x 16 B
+    uint8_t* ring = smem + kMaxSlabBlocks * 4 * 512;                          // [warps][kDepth] x 2304 B
+    uint8_t* scale_area = ring + kWarps * kDepth * kStreamBlockBytes;         // [warps] x 1 KB
+    uint64_t* bars = reinterpret_cast<uint64_t*>(scale_area + kWarps * kScaleScratchBytes);   // ring slots, then one for act
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t slab = blockIdx.x / p.ctas_per_slab, cta_in_slab = blockIdx.x % p.ctas_per_slab;
     const uint32_t kb_lo = slab * p.kb_count / p.slabs;
     const uint32_t kbs = (slab + 1) * p.kb_count / p.slabs - kb_lo;
-    const uint64_t blocks = static_cast<uint64_t>(p.groups) * kbs;
-    const uint64_t c0 = cta_in_slab * blocks / p.ctas_per_slab, c1 = (cta_in_slab + 1) * blocks / p.ctas_per_slab;
-    const uint64_t len = c1 - c0;
-    const uint64_t w0 = c0 + warp * len / kWarps, w1 = c0 + (warp + 1) * len / kWarps;
+    const uint32_t units = p.groups * kbs / p.unit;
+    const uint32_t c0 = cta_in_slab * units / p.ctas_per_slab * p.unit, c1 = (cta_in_slab + 1) * units / p.ctas_per_slab * p.unit;
+    const uint32_t len = c1 - c0;
+    const uint32_t w0 = c0 + warp * len / kWarps, w1 = c0 + (warp + 1) * len / kWarps;
 
-    auto block_ptr = [&](uint64_t at) {
-        const uint64_t group = at / kbs, kbi = at % kbs;
-        return p.weight + (group * p.kb_count + kb_lo + kbi) * kStreamBlockBytes;
+    // A cursor over this warp's blocks: (row group, block inside the slab, address). Stepping it
+    // costs an add and a compare; no division in the streaming loop.
+    struct Cursor {
+        uint32_t group, kbi;
+        const uint8_t* ptr;
     };
+    const uint32_t group_skip = (p.kb_count - kbs) * kStreamBlockBytes;   // bytes of other slabs between row groups
+    auto cursor_at = [&](uint32_t at) {
+        Cursor c;
+        c.group = at / kbs;
+        c.kbi = at - c.group * kbs;
+        c.ptr = p.weight + (static_cast<uint64_t>(c.group) * p.kb_count + kb_lo + c.kbi) * kStreamBlockBytes;
+        return c;
+    };
+    auto step = [&](Cursor& c) {
+        c.ptr += kStreamBlockBytes;
+        if (++c.kbi == kbs) {
+            c.kbi = 0;
+            ++c.group;
+            c.ptr += group_skip;
+        }
+    };
+    Cursor fetch = cursor_at(w0);
+    uint8_t* my_ring = ring + warp * kDepth * kStreamBlockBytes;
+    const uint32_t my_bars = smem_u32(bars + warp * kDepth);
 
-    // Weight loads go out first so that HBM is busy while the activations are staged.
-    WeightRegs ring[kDepth];
-#pragma unroll
-    for (uint32_t d = 0; d < kDepth; ++d) {
-        if (w0 + d < w1) load_block(ring[d], block_ptr(w0 + d), lane);
+    if (threadIdx.x == 0) {
+        for (uint32_t i = 0; i <= kWarps * kDepth; ++i) mbar_init(smem_u32(bars + i), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    __syncthreads();
+    // Weight copies go out first so that HBM is busy while the activations are staged.
+#ifndef AUGUR_GEMV_PROBE_NO_LOAD
+    if (lane == 0) {
+        for (uint32_t d = 0; d < kDepth; ++d) {
+            if (w0 + d < w1) {
+                issue_block(smem_u32(my_ring + d * kStreamBlockBytes), my_bars + 8 * d, fetch.ptr);
+                step(fetch);
+            }
+        }
+    }
+#endif
 
-    // ---- stage activations of this k-slab as f16 B fragments ----
+    // ---- activations of this k-slab: staged by stage_kernel, copied in as they are ----
+    // Everything above touched only this CTA's shared memory and read-only weights, so it may
+    // run while the staging kernel is still in flight; from here on its output is needed.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t act_bar = smem_u32(bars + kWarps * kDepth);
     {
-        constexpr uint32_t kThreadsPerToken = kWarps * 32 / 8;
-        const uint32_t token = threadIdx.x / kThreadsPerToken, within = threadIdx.x % kThreadsPerToken;
-        const uint32_t chunks = kbs * (kStreamBlockK / 8);  // 16-byte chunks of 8 bf16 per token row
-        const uint4* row = reinterpret_cast<const uint4*>(p.x + static_cast<uint64_t>(token) * p.cols + kb_lo * kStreamBlockK);
-        const bool live = token < p.tokens;
-        float amax = 0.0f;
-        if (live) {
-            for (uint32_t c = within; c < chunks; c += kThreadsPerToken) {
-                const uint4 v = __ldg(row + c);
-                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                for (uint32_t i = 0; i < 4; ++i) {
-                    amax = fmaxf(amax, fabsf(__uint_as_float(w[i] << 16)));
-                    amax = fmaxf(amax, fabsf(__uint_as_float(w[i] & 0xffff0000u)));
-                }
-            }
-        }
-#pragma unroll
-        for (uint32_t o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        if (lane == 0) s_amax[warp] = amax;
+        const uint32_t act_bytes = kbs * 2048;             // 4 k-step pairs x 512 bytes per block
+        const uint8_t* src = p.staged + static_cast<uint64_t>(kb_lo) * 2048;
+        if (threadIdx.x == 0) mbar_expect_tx(act_bar, act_bytes);
         __syncthreads();
-        if (threadIdx.x < 8) {
-            constexpr uint32_t kWarpsPerToken = kWarps / 8;
-            float m = 0.0f;
-            for (uint32_t i = 0; i < kWarpsPerToken; ++i) m = fmaxf(m, s_amax[threadIdx.x * kWarpsPerToken + i]);
-            // power of two e with m * 2^e in [2^14, 2^15); e = 0 for zero or non-finite rows
-            int e = 0;
-            const uint32_t field = (__float_as_uint(m) >> 23) & 0xff;
-            if (m > 0.0f && field != 0xff) {
-                e = 141 - static_cast<int>(field);
-                e = e > 126 ? 126 : e;
-            }
-            s_scale[threadIdx.x] = __uint_as_float(static_cast<uint32_t>(127 + e) << 23);
-            s_inv_scale[threadIdx.x] = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
+        // one copy per warp, issued in parallel
+        const uint32_t per_warp = (kbs + kWarps - 1) / kWarps * 2048;
+        const uint32_t begin = warp * per_warp;
+        if (lane == 0 && begin < act_bytes) {
+            const uint32_t bytes = act_bytes - begin < per_warp ? act_bytes - begin : per_warp;
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(smem_u32(smem + begin)), "l"(src + begin), "r"(bytes), "r"(act_bar)
+                         : "memory");
         }
-        __syncthreads();
-        const float scale = s_scale[token];
-        for (uint32_t c = within; c < chunks; c += kThreadsPerToken) {
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (live) v = __ldg(row + c);
-            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-            // chunk c holds k = 8c..8c+7 of the slab: k-step c/2, fragment register c%2,
-            // word i of the chunk is the pair k%16 = 8(c%2) + 2i, +1  -> lane token*4 + i
-            const uint32_t kstep = c >> 1, reg = c & 1;
-            uint32_t* dst = reinterpret_cast<uint32_t*>(act) + ((kstep >> 1) * 32 + token * 4) * 4 + (kstep & 1) * 2 + reg;
-#pragma unroll
-            for (uint32_t i = 0; i < 4; ++i) {
-                const float lo = __uint_as_float(w[i] << 16) * scale;
-                const float hi = __uint_as_float(w[i] & 0xffff0000u) * scale;
-                const __half2 h = __floats2half2_rn(lo, hi);
-                dst[i * 4] = *reinterpret_cast<const uint32_t*>(&h);
-            }
+        uint32_t spin = 0;
+        bool arrived = true;
+        while (!mbar_try_wait(act_bar, 0)) {
+            if (++spin > kWaitLimit) { arrived = false; break; }
         }
-        __syncthreads();
+        if (!arrived && threadIdx.x == 0) atomicCAS(p.status_word, 0u, 0x202u);   // staged activations never arrived
     }
 
+#ifdef AUGUR_GEMV_TRACE
+    stamp(1);
+#endif
     const uint32_t t4 = lane & 3;
-    const float inv0 = s_inv_scale[2 * t4], inv1 = s_inv_scale[2 * t4 + 1];
-    const uint64_t first_group = w0 / kbs;
+    const float inv0a = __ldg(p.factors + 4 * t4), inv0b = __ldg(p.factors + 4 * t4 + 1);         // token 2*t4
+    const float inv1a = __ldg(p.factors + 4 * t4 + 2), inv1b = __ldg(p.factors + 4 * t4 + 3);     // token 2*t4 + 1
+    Cursor now = cursor_at(w0);
+    const uint32_t first_group = now.group;
 
     // ---- stream this warp's span of blocks ----
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    uint64_t seg_group = first_group;
-    uint32_t seg_first_kbi = static_cast<uint32_t>(w0 % kbs);
+    uint32_t seg_group = first_group;
+    uint32_t seg_first_kbi = now.kbi;
 
-    auto flush = [&](uint64_t group, uint32_t first_kbi, uint32_t last_kbi) {
+    // A segment that covers its row group completely is finished here; a partial one is kept
+    // (head in registers, tail in the accumulators) until this warp's ring is free to hold it.
+    float head[8];
+    bool have_head = false, have_tail = false;
+    auto flush = [&](uint32_t group, uint32_t first_kbi, uint32_t last_kbi, bool last_segment) {
         float v[8];
 #pragma unroll
-        for (uint32_t i = 0; i < 8; ++i) v[i] = acc[i] * ((i & 1) ? inv1 : inv0);
+        for (uint32_t i = 0; i < 8; ++i) v[i] = acc[i] * ((i & 1) ? inv1a : inv0a) * ((i & 1) ? inv1b : inv0b);
         if (first_kbi == 0 && last_kbi + 1 == kbs) {
-            contribute(p, static_cast<uint32_t>(group), slab, cta_in_slab, v, lane);
+            contribute(p, group, slab, cta_in_slab, v, lane);
+        } else if (group == first_group) {
+#pragma unroll
+            for (uint32_t i = 0; i < 8; ++i) head[i] = v[i];
+            have_head = true;
         } else {
-            const uint32_t slot = group == first_group ? 0 : 1;
-            float4* dst = reinterpret_cast<float4*>(warp_partial + (warp * 2 + slot) * kSlotFloats) + lane * 2;
-            dst[0] = make_float4(v[0], v[1], v[2], v[3]);
-            dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+            // only the last segment of a span can be a partial that is not the head
+#pragma unroll
+            for (uint32_t i = 0; i < 8; ++i) acc[i] = v[i];
+            have_tail = last_segment;
+            return;
         }
 #pragma unroll
         for (uint32_t i = 0; i < 8; ++i) acc[i] = 0.0f;
     };
 
-    for (uint64_t base = w0; base < w1; base += kDepth) {
-#pragma unroll
-        for (uint32_t d = 0; d < kDepth; ++d) {
-            const uint64_t at = base + d;
-            if (at < w1) {
-                const uint64_t group = at / kbs;
-                const uint32_t kbi = static_cast<uint32_t>(at % kbs);
-                if (group != seg_group) {
-                    flush(seg_group, seg_first_kbi, kbs - 1);
-                    seg_group = group;
-                    seg_first_kbi = 0;
-                }
-                compute_block(acc, ring[d], act + kbi * 128, lane);
-                if (at + kDepth < w1) load_block(ring[d], block_ptr(at + kDepth), lane);
-            }
+    bool ring_ok = true;
+    uint32_t slot = 0, parity = 0;
+    for (uint32_t at = w0; at < w1; ++at) {
+        const uint32_t kbi = now.kbi;
+        if (now.group != seg_group) {
+            flush(seg_group, seg_first_kbi, kbs - 1, false);
+            seg_group = now.group;
+            seg_first_kbi = 0;
+        }
+#ifndef AUGUR_GEMV_PROBE_NO_LOAD
+        uint32_t spin = 0;
+        while (!mbar_try_wait(my_bars + 8 * slot, parity)) {
+            if (++spin > kWaitLimit) { ring_ok = false; break; }
+        }
+        if (!ring_ok) break;
+#endif
+#ifndef AUGUR_GEMV_PROBE_NO_COMPUTE
+        compute_block(acc, my_ring + slot * kStreamBlockBytes, act + kbi * 128,
+                      reinterpret_cast<float*>(scale_area + warp * kScaleScratchBytes), lane);
+#else
+        acc[0] += __uint_as_float(*reinterpret_cast<const uint32_t*>(my_ring + slot * kStreamBlockBytes + lane * 16));
+#endif
+        __syncwarp();
+#ifndef AUGUR_GEMV_PROBE_NO_LOAD
+        if (lane == 0 && at + kDepth < w1) {
+            issue_block(smem_u32(my_ring + slot * kStreamBlockBytes), my_bars + 8 * slot, fetch.ptr);
+            step(fetch);
+        }
+#endif
+        step(now);
+        if (++slot == kDepth) {
+            slot = 0;
+            parity ^= 1;
         }
     }
-    if (w1 > w0) flush(seg_group, seg_first_kbi, static_cast<uint32_t>((w1 - 1) % kbs));
+    if (!ring_ok && lane == 0) atomicCAS(p.status_word, 0u, 0x201u);   // a weight copy never arrived
+    if (w1 > w0) flush(seg_group, seg_first_kbi, (w1 - 1) % kbs, true);
+    // This warp's ring is idle now (every copy it issued has landed and been read): park the
+    // partial segments in its first slot for the CTA-level combination below.
+    float* warp_partial = reinterpret_cast<float*>(ring);
+    constexpr uint32_t kWarpPartialFloats = kDepth * kStreamBlockBytes / 4;   // floats per warp ring
+    if (have_head) {
+        float4* dst = reinterpret_cast<float4*>(warp_partial + warp * kWarpPartialFloats) + lane * 2;
+        dst[0] = make_float4(head[0], head[1], head[2], head[3]);
+        dst[1] = make_float4(head[4], head[5], head[6], head[7]);
+    }
+    if (have_tail) {
+        float4* dst = reinterpret_cast<float4*>(warp_partial + warp * kWarpPartialFloats + kSlotFloats) + lane * 2;
+        dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    }
     __syncthreads();
+#ifdef AUGUR_GEMV_TRACE
+    stamp(2);
+#endif
 
     // ---- combine row groups that were split between warps of this CTA ----
     if (len == 0) return;
-    const uint64_t cta_first_group = c0 / kbs;
-    const uint32_t cta_groups = static_cast<uint32_t>((c1 - 1) / kbs - cta_first_group + 1);
+    const uint32_t cta_first_group = c0 / kbs;
+    const uint32_t cta_groups = (c1 - 1) / kbs - cta_first_group + 1;
     for (uint32_t index = warp; index < cta_groups; index += kWarps) {
-        const uint64_t group = cta_first_group + index;
-        const uint64_t lo = group * kbs > c0 ? group * kbs : c0;
-        const uint64_t hi = (group + 1) * kbs < c1 ? (group + 1) * kbs : c1;
+        const uint32_t group = cta_first_group + index;
+        const uint32_t lo = group * kbs > c0 ? group * kbs : c0;
+        const uint32_t hi = (group + 1) * kbs < c1 ? (group + 1) * kbs : c1;
         const uint32_t w_lo = span_of(lo - c0, len, kWarps), w_hi = span_of(hi - 1 - c0, len, kWarps);
         if (w_lo == w_hi && lo == group * kbs && hi == (group + 1) * kbs) continue;  // one warp had it all
         float sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         for (uint32_t w = w_lo; w <= w_hi; ++w) {
-            const uint64_t b0 = c0 + w * len / kWarps, b1 = c0 + (w + 1) * len / kWarps;
+            const uint32_t b0 = c0 + w * len / kWarps, b1 = c0 + (w + 1) * len / kWarps;
             if (b1 == b0) continue;
             const uint32_t slot = (b0 / kbs == group) ? 0 : 1;
-            const float4* src = reinterpret_cast<const float4*>(warp_partial + (w * 2 + slot) * kSlotFloats) + lane * 2;
+            const float4* src = reinterpret_cast<const float4*>(warp_partial + w * kWarpPartialFloats + slot * kSlotFloats) + lane * 2;
             const float4 a = src[0], b = src[1];
             sum[0] += a.x; sum[1] += a.y; sum[2] += a.z; sum[3] += a.w;
             sum[4] += b.x; sum[5] += b.y; sum[6] += b.z; sum[7] += b.w;
         }
-        contribute(p, static_cast<uint32_t>(group), slab, cta_in_slab, sum, lane);
+        contribute(p, group, slab, cta_in_slab, sum, lane);
     }
+#ifdef AUGUR_GEMV_TRACE
+    __syncthreads();
+    stamp(3);
+#endif
 }
 
-constexpr uint32_t kGemvSmemBytes = kMaxSlabBlocks * 4 * 512 + kWarps * 2 * kSlotFloats * 4;
+constexpr uint32_t kGemvSmemBytes = kMaxSlabBlocks * 4 * 512 + kWarps * kDepth * kStreamBlockBytes +
+                                    kWarps * kScaleScratchBytes + (kWarps * kDepth + 1) * 8;
 
 // ---- validation ---------------------------------------------------------------------------
 bool check_gemv_scalars(const augur_cuda_nvfp4_sm100_gemv_args_v1* a, bool* pair) {
@@ -427,7 +614,8 @@ void gemv_ranges(const augur_cuda_nvfp4_sm100_gemv_args_v1* a, Range (&r)[3]) {
     r[2] = {a->output, a->output_len_bytes, 4};
 }
 
-// `partial_offset`..`partial_limit` is the part of the plan scratch this launch may use for slots.
+// `partial_offset`..`partial_limit` is the part of the plan scratch this launch may use: the staged
+// activations come first, the partial-sum slots after them.
 bool check_gemv(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* plan,
                 const augur_cuda_nvfp4_sm100_gemv_args_v1* a, uint64_t partial_offset, uint64_t partial_limit,
                 bool full, augur_cuda_result_v1* failure) {
@@ -442,7 +630,7 @@ bool check_gemv(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_p
     if (!plan_ok(plan, d, s) || !check_gemv_scalars(a, &pair)) return false;
     const GemvGeometry g = geometry(a->rows, a->cols, pair, plan->sm_count);
     if (g.ctas_per_slab == 0 || g.groups > kMaxGroups || partial_offset < kCounterBytes ||
-        partial_limit < partial_offset || g.partial_bytes > partial_limit - partial_offset) {
+        partial_limit < partial_offset || g.staged_bytes + g.partial_bytes > partial_limit - partial_offset) {
         return false;
     }
     Range r[4];
@@ -463,13 +651,38 @@ void launch_gemv(augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* pl
     p.x = reinterpret_cast<const uint16_t*>(a->input_bf16);
     p.out = reinterpret_cast<void*>(a->output);
     p.counters = reinterpret_cast<uint32_t*>(plan->scratch + member * kCounterRegionBytes);
-    p.partials = reinterpret_cast<float*>(plan->scratch + partial_offset);
+    p.staged = plan->scratch + partial_offset;
+    p.factors = reinterpret_cast<const float*>(plan->scratch + partial_offset + static_cast<uint64_t>(a->cols) * 16);
+    p.partials = reinterpret_cast<float*>(plan->scratch + partial_offset + g.staged_bytes);
+    p.unit = g.unit;
+    p.status_word = plan->status_word;
+#ifdef AUGUR_GEMV_TRACE
+    p.trace = reinterpret_cast<unsigned long long*>(plan->scratch + plan->scratch_bytes - 65536) + member * 4096;
+#endif
     p.groups = g.groups; p.kb_count = g.kb_count; p.slabs = g.slabs; p.ctas_per_slab = g.ctas_per_slab;
     p.max_contrib = g.max_contrib;
     p.rows = a->rows; p.cols = a->cols; p.tokens = a->tokens; p.epilogue = a->epilogue;
     p.global_a = a->global_scale; p.global_b = a->global_scale_b;
-    gemv_kernel<<<g.slabs * g.ctas_per_slab, kWarps * 32, kGemvSmemBytes, s->stream>>>(p);
-    count_launch();
+    // Both kernels are launched with programmatic stream serialisation: each may become resident
+    // while its predecessor drains and waits for it in-kernel (griddepcontrol.wait).
+    cudaLaunchAttribute attribute{};
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t config{};
+    config.stream = s->stream;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    config.gridDim = dim3(AUGUR_NVFP4_SM100_MAX_SMALL_TOKENS);
+    config.blockDim = dim3(512);
+    config.dynamicSmemBytes = 0;
+    cudaLaunchKernelEx(&config, stage_kernel, p.x, reinterpret_cast<uint32_t*>(plan->scratch + partial_offset),
+                       reinterpret_cast<float*>(plan->scratch + partial_offset + static_cast<uint64_t>(a->cols) * 16),
+                       a->cols, a->tokens);
+    config.gridDim = dim3(g.slabs * g.ctas_per_slab);
+    config.blockDim = dim3(kWarps * 32);
+    config.dynamicSmemBytes = kGemvSmemBytes;
+    cudaLaunchKernelEx(&config, gemv_kernel, p);
+    count_launch(2);
 }
 
 }  // namespace
@@ -496,7 +709,7 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_scra
         if (!pair && rows % 32 != 0) continue;
         for (uint32_t sms = 1; sms <= 512; ++sms) {
             const GemvGeometry g = geometry(rows, cols, pair != 0, sms);
-            if (g.partial_bytes > worst) worst = g.partial_bytes;
+            if (g.staged_bytes + g.partial_bytes > worst) worst = g.staged_bytes + g.partial_bytes;
         }
     }
     *out_bytes = kCounterBytes + worst;

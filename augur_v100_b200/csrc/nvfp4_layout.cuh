@@ -15,11 +15,15 @@ namespace augur_sm100 {
 // The tensor is cut into blocks of 32 weight rows x 128 k (8 k-steps of 16). A block
 // is 2304 bytes: 2048 code bytes in mma.m16n8k16 A-fragment order, then 256 scale bytes.
 //   codes : [tile t:2][quad q:2][lane:32][16 bytes]; the 16 bytes of a lane are 4 words,
-//           word j = k-step 4q+j, byte b of a word = fragment register a_b:
-//             a0 (row g,   k 2t4..2t4+1)   a1 (row g+8, same k)
-//             a2 (row g,   k 2t4+8..+9)    a3 (row g+8, same k)      g = lane>>2, t4 = lane&3
-//           and every byte is the source byte itself (two adjacent-k codes, even k low).
-//   scales: [tile t:2][g:8][16 bytes] = {row g: k-steps 0..7, row g+8: k-steps 0..7}.
+//           word j = k-step 4q+j. A word carries the 8 codes of the lane's four fragment
+//           registers (g = lane>>2, t4 = lane&3):
+//             a0 (row g,   k 2t4, 2t4+1)   a1 (row g+8, same k)
+//             a2 (row g,   k 2t4+8, +9)    a3 (row g+8, same k)
+//           bit-permuted so that each register falls out of the word with at most a shift
+//           and a mask, already positioned as the low exponent bits and top mantissa bit
+//           of two BF16 numbers (see stream_pack_word). The even-k code of a register
+//           sits in the low 16 bits, the odd-k code in the high 16 bits.
+//   scales: [tile t:2][g:8][16 bytes] = k-steps 0..7, each {row g, row g+8}.
 // STREAM:      block row-group s holds rows 32s..32s+31, tile t = rows 32s+16t..+15.
 // STREAM_PAIR: block row-group s holds gate rows 16s..16s+15 (tile 0) and the
 //              matching up rows (tile 1).
@@ -28,9 +32,49 @@ constexpr uint32_t kStreamBlockBytes = 2304;
 constexpr uint32_t kStreamCodeBytes = 2048;
 constexpr uint32_t kStreamBlockK = 128;
 
+// An E2M1 code (s e1 e0 m) placed at BF16 bits (15; 8 7 6) reads as e2m1 * 2^-126 (the
+// subnormal 0.5 included), so a register of two codes needs no arithmetic to become two
+// BF16 values. Within each 16-bit half of a word the four registers' codes live at
+//   a0: s15 e8 e7 m6     -> a0 =  w        & 0x81C081C0
+//   a1: s12 e5 e4 m3     -> a1 = (w << 3)  & 0x81C081C0
+//   a2: s9  e2 e1 m0     -> a2 = (w << 6)  & 0x81C081C0
+//   a3: s11 e1@10 e0@14 m13 -> a3 = (((w >> 10) & 0x001B001B) * 0x4108) & 0x81C081C0
+// `bytes` are the four source bytes of a0..a3 (low nibble = even k).
+AUGUR_HD uint32_t stream_pack_word(uint32_t b0, uint32_t b1, uint32_t b2, uint32_t b3) {
+    const uint32_t bytes[4] = {b0, b1, b2, b3};
+    // destination bit of (sign, e1, e0, m) for each register, inside a 16-bit half
+    const uint32_t where[4][4] = {{15, 8, 7, 6}, {12, 5, 4, 3}, {9, 2, 1, 0}, {11, 10, 14, 13}};
+    uint32_t word = 0;
+    for (uint32_t j = 0; j < 4; ++j) {
+        for (uint32_t half = 0; half < 2; ++half) {
+            const uint32_t code = (bytes[j] >> (4 * half)) & 15u;
+            word |= ((code >> 3) & 1u) << (where[j][0] + 16 * half);
+            word |= ((code >> 2) & 1u) << (where[j][1] + 16 * half);
+            word |= ((code >> 1) & 1u) << (where[j][2] + 16 * half);
+            word |= (code & 1u) << (where[j][3] + 16 * half);
+        }
+    }
+    return word;
+}
+
+// Inverse of stream_pack_word: source byte of register j.
+AUGUR_HD uint32_t stream_unpack_byte(uint32_t word, uint32_t j) {
+    const uint32_t where[4][4] = {{15, 8, 7, 6}, {12, 5, 4, 3}, {9, 2, 1, 0}, {11, 10, 14, 13}};
+    uint32_t byte = 0;
+    for (uint32_t half = 0; half < 2; ++half) {
+        const uint32_t code = (((word >> (where[j][0] + 16 * half)) & 1u) << 3) |
+                              (((word >> (where[j][1] + 16 * half)) & 1u) << 2) |
+                              (((word >> (where[j][2] + 16 * half)) & 1u) << 1) |
+                              ((word >> (where[j][3] + 16 * half)) & 1u);
+        byte |= code << (4 * half);
+    }
+    return byte;
+}
+
 struct StreamCoord {
     uint64_t block;    // block index
-    uint32_t offset;   // byte offset inside the block
+    uint32_t offset;   // byte offset inside the block: of the WORD for codes, of the byte for scales
+    uint32_t slot;     // codes only: which register (0..3) of the word holds the source byte
 };
 
 // Where source code byte (matrix m, row r, byte column c) goes.
@@ -45,7 +89,8 @@ AUGUR_HD StreamCoord stream_code_coord(bool pair, uint32_t m, uint32_t r, uint32
     const uint32_t lane = g * 4 + t4;
     StreamCoord out;
     out.block = static_cast<uint64_t>(group) * kb_count + kb;
-    out.offset = ((t * 2 + q) * 32 + lane) * 16 + j * 4 + (hi + 2 * half);
+    out.offset = ((t * 2 + q) * 32 + lane) * 16 + j * 4;
+    out.slot = hi + 2 * half;
     return out;
 }
 
@@ -58,7 +103,8 @@ AUGUR_HD StreamCoord stream_scale_coord(bool pair, uint32_t m, uint32_t r, uint3
     const uint32_t rr = r & 15, g = rr & 7, hi = rr >> 3;
     StreamCoord out;
     out.block = static_cast<uint64_t>(group) * kb_count + kb;
-    out.offset = kStreamCodeBytes + (t * 8 + g) * 16 + hi * 8 + ks;
+    out.offset = kStreamCodeBytes + (t * 8 + g) * 16 + ks * 2 + hi;
+    out.slot = 0;
     return out;
 }
 

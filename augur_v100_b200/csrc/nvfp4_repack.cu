@@ -55,20 +55,24 @@ __global__ void repack_stream_kernel(const uint8_t* __restrict__ codes_a, const 
         const uint32_t kstep = kb * 8 + q * 4 + j;
         const uint8_t* source = (pair && t) ? codes_b : codes_a;
         const uint32_t row0 = pair ? group * 16 : group * 32 + t * 16;
+        uint32_t bytes[4];
 #pragma unroll
         for (uint32_t b = 0; b < 4; ++b) {
             const uint32_t row = row0 + g + (b & 1) * 8;
             const uint32_t column = kstep * 8 + (b >> 1) * 4 + t4;
-            value |= static_cast<uint32_t>(source[static_cast<uint64_t>(row) * (cols / 2) + column]) << (8 * b);
+            bytes[b] = source[static_cast<uint64_t>(row) * (cols / 2) + column];
         }
+        value = stream_pack_word(bytes[0], bytes[1], bytes[2], bytes[3]);
     } else {
+        // scale word sw of the block: tile t, quad-row g, k-steps 2p and 2p+1, each {row g, row g+8}
         const uint32_t sw = word - kStreamCodeBytes / 4;  // 0..63
-        const uint32_t half_ks = sw & 1, hi = (sw >> 1) & 1, g = (sw >> 2) & 7, t = sw >> 5;
+        const uint32_t p = sw & 3, g = (sw >> 2) & 7, t = sw >> 5;
         const uint8_t* source = (pair && t) ? scales_b : scales_a;
-        const uint32_t row = (pair ? group * 16 : group * 32 + t * 16) + g + hi * 8;
+        const uint32_t row0 = (pair ? group * 16 : group * 32 + t * 16) + g;
 #pragma unroll
         for (uint32_t b = 0; b < 4; ++b) {
-            const uint32_t sc = kb * 8 + half_ks * 4 + b;
+            const uint32_t row = row0 + (b & 1) * 8;
+            const uint32_t sc = kb * 8 + p * 2 + (b >> 1);
             value |= static_cast<uint32_t>(source[static_cast<uint64_t>(row) * (cols / 16) + sc]) << (8 * b);
         }
     }
@@ -149,7 +153,8 @@ __global__ void dequant_kernel(const uint8_t* __restrict__ weight, const uint8_t
 #pragma unroll
         for (uint32_t b = 0; b < 8; ++b) {
             const StreamCoord at = stream_code_coord(pair, m, row, group * 8 + b, cols);
-            code_bytes[b] = weight[at.block * kStreamBlockBytes + at.offset];
+            const uint32_t word = *reinterpret_cast<const uint32_t*>(weight + at.block * kStreamBlockBytes + at.offset);
+            code_bytes[b] = static_cast<uint8_t>(stream_unpack_byte(word, at.slot));
         }
         const StreamCoord at = stream_scale_coord(pair, m, row, group, cols);
         scale_byte = weight[at.block * kStreamBlockBytes + at.offset];
@@ -310,18 +315,28 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_repack_ho
         }
         return ok();
     }
+    // Each destination word holds four source bytes, bit-permuted: gather them first.
+    memset(destination, 0, destination_len_bytes);
     for (uint32_t m = 0; m < matrices; ++m) {
         const uint8_t* code_plane = m ? codes_b : codes;
         const uint8_t* scale_plane = m ? scales_b : scales;
         for (uint32_t r = 0; r < rows; ++r) {
             for (uint32_t c = 0; c < cols / 2; ++c) {
                 const StreamCoord at = stream_code_coord(pair, m, r, c, cols);
-                destination[at.block * kStreamBlockBytes + at.offset] = code_plane[static_cast<uint64_t>(r) * (cols / 2) + c];
+                // staged as plain bytes in slot order; permuted word by word below
+                destination[at.block * kStreamBlockBytes + at.offset + at.slot] = code_plane[static_cast<uint64_t>(r) * (cols / 2) + c];
             }
             for (uint32_t sc = 0; sc < cols / 16; ++sc) {
                 const StreamCoord at = stream_scale_coord(pair, m, r, sc, cols);
                 destination[at.block * kStreamBlockBytes + at.offset] = scale_plane[static_cast<uint64_t>(r) * (cols / 16) + sc];
             }
+        }
+    }
+    for (uint64_t block = 0; block < destination_len_bytes / kStreamBlockBytes; ++block) {
+        uint8_t* words = destination + block * kStreamBlockBytes;
+        for (uint32_t w = 0; w < kStreamCodeBytes; w += 4) {
+            const uint32_t packed = stream_pack_word(words[w], words[w + 1], words[w + 2], words[w + 3]);
+            memcpy(words + w, &packed, 4);
         }
     }
     return ok();
@@ -352,7 +367,9 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_unpack_ho
         for (uint32_t r = 0; r < rows; ++r) {
             for (uint32_t c = 0; c < cols / 2; ++c) {
                 const StreamCoord at = stream_code_coord(pair, m, r, c, cols);
-                code_plane[static_cast<uint64_t>(r) * (cols / 2) + c] = source[at.block * kStreamBlockBytes + at.offset];
+                uint32_t word;
+                memcpy(&word, source + at.block * kStreamBlockBytes + at.offset, 4);
+                code_plane[static_cast<uint64_t>(r) * (cols / 2) + c] = static_cast<uint8_t>(stream_unpack_byte(word, at.slot));
             }
             for (uint32_t sc = 0; sc < cols / 16; ++sc) {
                 const StreamCoord at = stream_scale_coord(pair, m, r, sc, cols);

@@ -58,6 +58,13 @@ class ClockSampler:
 
     def __init__(self, index: int):
         self.index, self.rows, self.proc = index, [], None
+        self.window = [None, None]     # wall-clock bounds of the timed region
+
+    def mark_begin(self):
+        self.window[0] = time.time()
+
+    def mark_end(self):
+        self.window[1] = time.time()
 
     def start(self):
         try:
@@ -70,7 +77,7 @@ class ClockSampler:
 
     def _pump(self):
         for line in self.proc.stdout:
-            self.rows.append([field.strip() for field in line.split(",")])
+            self.rows.append((time.time(), [field.strip() for field in line.split(",")]))
 
     def stop(self):
         if self.proc is not None:
@@ -80,8 +87,9 @@ class ClockSampler:
             except subprocess.TimeoutExpired:
                 self.proc.kill()
         sm, sm_max, reasons = [], [], set()
-        for row in self.rows:
-            if len(row) < 9:
+        begin, end = self.window
+        for stamp, row in self.rows:
+            if len(row) < 9 or (begin is not None and stamp < begin) or (end is not None and stamp > end + 0.05):
                 continue
             try:
                 sm.append(float(row[1]))
@@ -255,12 +263,13 @@ def run_library(args):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
-    for _ in range(max(args.warmup, 3)):
-        step()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+    for _ in range(max(args.warmup, 3)):
+        step()
     launches_before = host.launch_count()
+    sampler.mark_begin()
     total_ms = timed(step, args.steps)
     launches = host.launch_count() - launches_before
 
@@ -273,6 +282,7 @@ def run_library(args):
     for _ in range(3):
         e2e_step()
     e2e_ms = timed(e2e_step, args.steps)
+    sampler.mark_end()
     clocks = sampler.stop() if rank == 0 else None
     status = plan.device_status()
     if status != 0:
@@ -327,7 +337,7 @@ def run_library(args):
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--steps", type=int, default=1000)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", choices=["library", "reference"], default="library")
     parser.add_argument("--no-prefill", action="store_true", help="skip the M=4096 tcgen05 probe at N=1")

@@ -63,9 +63,10 @@ extern "C" {
 /* COMPACT is what a checkpoint loader hands over (crates/augur-formats/src/fp4.rs:17-21,
  * crates/augur-model-qwen35/src/checkpoint_quant.rs:93-152): codes [rows][cols/2]
  * (even k in the low nibble), scales [rows][cols/16], one f32 global scale.
- * The other three are lossless byte permutations of the same bits. */
+ * The other three are lossless permutations of the same bits. */
 #define AUGUR_NVFP4_SM100_LAYOUT_COMPACT UINT32_C(0)
-/* 32-row x 128-k blocks of 2304 bytes in mma fragment order: the decode/verify stream. */
+/* 32-row x 128-k blocks of 2304 bytes in mma fragment order, codes bit-permuted so that each
+ * fragment register is one shift-and-mask away: the decode/verify stream. */
 #define AUGUR_NVFP4_SM100_LAYOUT_STREAM UINT32_C(1)
 /* Same, with 16 gate rows and the matching 16 up rows in each block (fused SwiGLU). */
 #define AUGUR_NVFP4_SM100_LAYOUT_STREAM_PAIR UINT32_C(2)

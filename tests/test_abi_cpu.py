@@ -58,27 +58,58 @@ def test_host_repack_is_a_lossless_permutation(layout, rows, cols):
     if pair:
         assert np.array_equal(back[2], codes_b) and np.array_equal(back[3], scales_b)
     if layout != abi.LAYOUT_TCGEN05:
-        # a pure permutation: same multiset of bytes, nothing padded
-        assert np.array_equal(np.sort(packed), np.sort(np.concatenate(
-            [a.reshape(-1) for a in (codes, scales, codes_b, scales_b) if a is not None])))
+        # a pure bit permutation: same size, same number of set bits, nothing padded
+        source = np.concatenate([a.reshape(-1) for a in (codes, scales, codes_b, scales_b) if a is not None])
+        assert packed.size == source.size
+        assert int(np.unpackbits(packed).sum()) == int(np.unpackbits(source).sum())
+
+
+WHERE = [(15, 8, 7, 6), (12, 5, 4, 3), (9, 2, 1, 0), (11, 10, 14, 13)]   # (sign, e1, e0, m) per fragment register
+
+
+def _pack_word(source_bytes):
+    word = 0
+    for j, byte in enumerate(source_bytes):
+        for half in range(2):
+            code = (int(byte) >> (4 * half)) & 15
+            for bit, at in zip((3, 2, 1, 0), WHERE[j]):
+                word |= ((code >> bit) & 1) << (at + 16 * half)
+    return word
 
 
 def test_stream_layout_fragment_order():
-    # one block: lane (g, t4), word j, byte b must be source (row g + 8*(b&1), byte column 8*kstep + 4*(b>>1) + t4)
+    # one block: lane (g, t4), word j holds source bytes (row g + 8*(b&1), byte column 8*kstep + 4*(b>>1) + t4), b = 0..3,
+    # bit-permuted so that the kernel's shift/mask/multiply extractions yield e2m1 * 2^-126 as BF16 pairs
     rows, cols = 32, 128
-    codes = np.arange(rows * cols // 2, dtype=np.uint32).reshape(rows, cols // 2)
-    tag = (codes % 251).astype(np.uint8)
-    scales = np.zeros((rows, cols // 16), dtype=np.uint8)
+    rng = np.random.default_rng(0)
+    tag = rng.integers(0, 256, size=(rows, cols // 2), dtype=np.uint8)
+    scales = (np.arange(rows * cols // 16) % 127).astype(np.uint8).reshape(rows, cols // 16)
     packed = host.repack_host(abi.LAYOUT_STREAM, rows, cols, tag, scales)
+    words = packed[:2048].view(np.uint32)
+    e2m1 = oracle.E2M1_VALUES.astype(np.float64)
+    mask = 0x81C081C0
     for t in range(2):
         for q in range(2):
             for lane in (0, 5, 31):
                 for j in range(4):
+                    g, t4 = lane >> 2, lane & 3
+                    src = [tag[t * 16 + g + (b & 1) * 8, (q * 4 + j) * 8 + (b >> 1) * 4 + t4] for b in range(4)]
+                    w = int(words[((t * 2 + q) * 32 + lane) * 4 + j])
+                    assert w == _pack_word(src)
+                    regs = [w & mask, (w << 3) & mask & 0xFFFFFFFF, (w << 6) & mask & 0xFFFFFFFF,
+                            ((((w >> 10) & 0x001B001B) * 0x4108) & 0xFFFFFFFF) & mask]
                     for b in range(4):
-                        g, t4 = lane >> 2, lane & 3
-                        row = t * 16 + g + (b & 1) * 8
-                        col = (q * 4 + j) * 8 + (b >> 1) * 4 + t4
-                        assert packed[((t * 2 + q) * 32 + lane) * 16 + j * 4 + b] == tag[row, col]
+                        for half in range(2):
+                            bits = (regs[b] >> (16 * half)) & 0xFFFF
+                            value = float(np.array([bits << 16], dtype=np.uint32).view(np.float32)[0]) * 2.0 ** 126
+                            code = (int(src[b]) >> (4 * half)) & 15
+                            assert value == e2m1[code], (t, q, lane, j, b, half)
+    # scales: tile t, row pair g: bytes 2*ks + hi
+    for t in range(2):
+        for g in range(8):
+            for ks in range(8):
+                for hi in range(2):
+                    assert packed[2048 + (t * 8 + g) * 16 + ks * 2 + hi] == scales[t * 16 + g + 8 * hi, ks]
 
 
 def test_host_repack_rejects_bad_scales_and_shapes():

@@ -15,23 +15,26 @@ def geometry(rows, cols, pair, sms):
     groups = rows // 16 if pair else rows // 32
     kb = cols // 128
     slabs = (kb + MAX_SLAB - 1) // MAX_SLAB
-    per_slab = min(max(sms // slabs, 1), groups * (kb // slabs))
+    per_slab = max(sms // slabs, 1)
+    # one slab and many row groups per CTA: spans are cut at row-group boundaries (unit = blocks per group)
+    unit = kb // slabs if (slabs == 1 and groups >= 4 * per_slab) else 1
+    per_slab = min(per_slab, groups * (kb // slabs) // unit)
     max_contrib = slabs * ((per_slab + groups - 1) // groups + 1)
-    return groups, kb, slabs, per_slab, max_contrib
+    return groups, kb, slabs, per_slab, max_contrib, unit
 
 
 def span_of(at, total, parts):
     return ((at + 1) * parts - 1) // total
 
 
-def contributors(groups, kb, slabs, per_slab, group):
+def contributors(groups, kb, slabs, per_slab, unit, group):
     """(total, {(slab, cta): slot}) exactly as `contribute` computes them."""
     total, slots = 0, {}
     for s in range(slabs):
         kbs = (s + 1) * kb // slabs - s * kb // slabs
-        blocks = groups * kbs
-        first = span_of(group * kbs, blocks, per_slab)
-        last = span_of((group + 1) * kbs - 1, blocks, per_slab)
+        units = groups * kbs // unit
+        first = span_of(group * kbs // unit, units, per_slab)
+        last = span_of(((group + 1) * kbs - 1) // unit, units, per_slab)
         for cta in range(first, last + 1):
             slots[(s, cta)] = total + (cta - first)
         total += last - first + 1
@@ -39,7 +42,7 @@ def contributors(groups, kb, slabs, per_slab, group):
 
 
 def simulate(rows, cols, pair, sms):
-    groups, kb, slabs, per_slab, max_contrib = geometry(rows, cols, pair, sms)
+    groups, kb, slabs, per_slab, max_contrib, unit = geometry(rows, cols, pair, sms)
     assert per_slab >= 1
     consumed = {}
     contributions = {}   # group -> list of (slab, cta)
@@ -47,9 +50,9 @@ def simulate(rows, cols, pair, sms):
         kb_lo = s * kb // slabs
         kbs = (s + 1) * kb // slabs - kb_lo
         assert 1 <= kbs <= MAX_SLAB
-        blocks = groups * kbs
+        units = groups * kbs // unit
         for cta in range(per_slab):
-            c0, c1 = cta * blocks // per_slab, (cta + 1) * blocks // per_slab
+            c0, c1 = cta * units // per_slab * unit, (cta + 1) * units // per_slab * unit
             length = c1 - c0
             assert length >= 1
             partial = {}          # (warp, slot) -> group
@@ -103,7 +106,9 @@ def simulate(rows, cols, pair, sms):
                 contributions.setdefault(group, []).append((s, cta))
     assert len(consumed) == groups * kb
     for group in range(groups):
-        total, slots = contributors(groups, kb, slabs, per_slab, group)
+        total, slots = contributors(groups, kb, slabs, per_slab, unit, group)
+        if unit > 1:
+            assert total == 1
         got = contributions.get(group, [])
         assert len(got) == total == len(set(got)), (group, total, got)
         assert total <= max_contrib
