@@ -23,6 +23,8 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+
 #include "nvfp4_internal.h"
 #include "nvfp4_layout.cuh"
 
@@ -58,6 +60,8 @@ struct GemvParams {
 #endif
     const uint8_t* staged;     // activations as BF16 B fragments, [cols/32][32 lanes][16 bytes]
     const float* factors;      // per token: two factors whose product undoes the staging exponent
+    float fixed_factor;        // non-zero: both factors are this constant for every token (no table)
+    uint16_t* staged_out;      // SwiGLU epilogue: also write the result as staged fragments (or null)
     uint32_t groups, kb_count, slabs, ctas_per_slab, max_contrib, unit;
     uint32_t rows, cols, tokens, epilogue;
     float global_a, global_b;
@@ -68,6 +72,16 @@ struct GemvGeometry {
     uint64_t partial_bytes;   // partial-sum slots
     uint64_t staged_bytes;    // staged activations + factors
 };
+
+// AUGUR_NVFP4_SM100_GEMV_SPLIT=block forces single-block span boundaries (measurement aid);
+// anything else keeps the automatic choice described in geometry().
+int split_mode() {
+    static const int mode = [] {
+        const char* value = getenv("AUGUR_NVFP4_SM100_GEMV_SPLIT");
+        return (value && value[0] == 'b') ? 1 : 0;
+    }();
+    return mode;
+}
 
 // Host-side geometry; `sm_count` CTAs at most.
 GemvGeometry geometry(uint32_t rows, uint32_t cols, bool pair, uint32_t sm_count) {
@@ -81,7 +95,7 @@ GemvGeometry geometry(uint32_t rows, uint32_t cols, bool pair, uint32_t sm_count
     // With one k-slab and plenty of row groups per CTA, spans are cut at row-group boundaries:
     // every group is then finished inside one CTA (no scratch, no fences) at the price of at
     // most one group of imbalance. Otherwise spans are cut at single blocks.
-    g.unit = (g.slabs == 1 && g.groups >= 4 * per_slab) ? min_kbs : 1;
+    g.unit = (g.slabs == 1 && g.groups >= 4 * per_slab && split_mode() != 1) ? min_kbs : 1;
     const uint64_t least_units = static_cast<uint64_t>(g.groups) * min_kbs / g.unit;
     if (per_slab > least_units) per_slab = least_units;  // every CTA owns at least one unit
     g.ctas_per_slab = static_cast<uint32_t>(per_slab);
@@ -220,6 +234,23 @@ __device__ __forceinline__ uint32_t span_of(uint32_t at, uint32_t total, uint32_
     return ((at + 1) * parts - 1) / total;
 }
 
+// An intermediate produced inside a program (SiLU(gate)*up) is staged for the next projection
+// by the epilogue that computes it, with this fixed exponent shift instead of a per-token one
+// (no pass over the finished tensor is needed): exact for magnitudes in [2^-60, 2^62],
+// saturating above, flushing below.
+constexpr int kFixedStageShift = 64;
+
+// BF16 bits times 2^shift by exponent arithmetic: exact; zeros and subnormals become zero,
+// and anything that would leave the normal range on the way down is flushed to zero
+// (it is more than 2^200 below the row's largest magnitude). Infinities and NaNs pass through.
+__device__ __forceinline__ uint32_t shift_bf16(uint32_t bits, int shift) {
+    const int field = static_cast<int>((bits >> 7) & 0xff);
+    if (field == 0xff) return bits;
+    const int moved = field + shift;
+    if (field == 0 || moved < 1) return bits & 0x8000u;
+    return (bits & 0x807fu) | (static_cast<uint32_t>(moved > 254 ? 254 : moved) << 7);
+}
+
 __device__ __forceinline__ void epilogue(const GemvParams& p, uint32_t group, const float (&v)[8], uint32_t lane) {
     const uint32_t g = lane >> 2, t4 = lane & 3;
     if (p.epilogue == AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16) {
@@ -231,7 +262,16 @@ __device__ __forceinline__ void epilogue(const GemvParams& p, uint32_t group, co
             if (token < p.tokens) {
                 const float gate = v[i] * p.global_a;
                 const float up = v[4 + i] * p.global_b;
-                out[static_cast<uint64_t>(token) * p.rows + row] = __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
+                const __nv_bfloat16 h = __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
+                out[static_cast<uint64_t>(token) * p.rows + row] = h;
+                if (p.staged_out) {
+                    // The same value as the next projection's B fragment: k = row, so k-step = group,
+                    // fragment register i>>1 (rows g / g+8 are k%16 = g / g+8), pair g/2, half g%2;
+                    // shifted by the fixed staging exponent instead of a per-token one.
+                    const uint32_t word = ((group >> 1) * 32 + token * 4 + (g >> 1)) * 4 + (group & 1) * 2 + (i >> 1);
+                    p.staged_out[word * 2 + (g & 1)] =
+                        static_cast<uint16_t>(shift_bf16(__bfloat16_as_ushort(h), kFixedStageShift));
+                }
             }
         }
         return;
@@ -251,17 +291,6 @@ __device__ __forceinline__ void epilogue(const GemvParams& p, uint32_t group, co
     }
 }
 
-// BF16 bits times 2^shift by exponent arithmetic: exact; zeros and subnormals become zero,
-// and anything that would leave the normal range on the way down is flushed to zero
-// (it is more than 2^200 below the row's largest magnitude). Infinities and NaNs pass through.
-__device__ __forceinline__ uint32_t shift_bf16(uint32_t bits, int shift) {
-    const int field = static_cast<int>((bits >> 7) & 0xff);
-    if (field == 0xff) return bits;
-    const int moved = field + shift;
-    if (field == 0 || moved < 1) return bits & 0x8000u;
-    return (bits & 0x807fu) | (static_cast<uint32_t>(moved > 254 ? 254 : moved) << 7);
-}
-
 // ---- activation staging --------------------------------------------------------------------
 // One CTA per token row: finds the row's largest magnitude, picks the exponent shift e that
 // puts it in [2^100, 2^101) (so that the 2^-126-scaled weight fragments meet activations
@@ -272,12 +301,12 @@ __device__ __forceinline__ uint32_t shift_bf16(uint32_t bits, int shift) {
 // launched with programmatic stream serialisation and overlaps its weight prefetch with this.
 __global__ void __launch_bounds__(512) stage_kernel(const uint16_t* __restrict__ x, uint32_t* __restrict__ staged,
                                                     float* __restrict__ factors, uint32_t cols, uint32_t tokens) {
-    // Launched with programmatic stream serialisation: it may become resident while the kernel
-    // before it is still running, so it waits for that kernel (which may produce x, and may
-    // still be reading an older staging of this region) before doing anything, then lets
-    // the streaming kernel behind it start its weight prefetch.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // Launched with programmatic stream serialisation. The streaming kernel behind it is released
+    // at once (it only prefetches weights until its own wait, which covers this whole grid);
+    // this kernel then waits for the kernel before it, which may produce x and may still be
+    // reading an older staging of this region.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     __shared__ float s_amax[16];
     __shared__ int s_shift;
     const uint32_t token = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -470,8 +499,11 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_kernel(const GemvParams p
     stamp(1);
 #endif
     const uint32_t t4 = lane & 3;
-    const float inv0a = __ldg(p.factors + 4 * t4), inv0b = __ldg(p.factors + 4 * t4 + 1);         // token 2*t4
-    const float inv1a = __ldg(p.factors + 4 * t4 + 2), inv1b = __ldg(p.factors + 4 * t4 + 3);     // token 2*t4 + 1
+    float inv0a = p.fixed_factor, inv0b = p.fixed_factor, inv1a = p.fixed_factor, inv1b = p.fixed_factor;
+    if (p.fixed_factor == 0.0f) {
+        inv0a = __ldg(p.factors + 4 * t4); inv0b = __ldg(p.factors + 4 * t4 + 1);         // token 2*t4
+        inv1a = __ldg(p.factors + 4 * t4 + 2); inv1b = __ldg(p.factors + 4 * t4 + 3);     // token 2*t4 + 1
+    }
     Cursor now = cursor_at(w0);
     const uint32_t first_group = now.group;
 
@@ -642,8 +674,12 @@ bool check_gemv(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_p
     return !full || inspect_device_ranges(d, r, 3, failure);
 }
 
+// `staged_out_offset` (non-zero): the SwiGLU result is also written, staged, at that offset of the plan
+// scratch. `input_is_staged`: the activations were staged there by the producing launch (fixed
+// exponent), so no staging kernel runs.
 void launch_gemv(augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* plan,
-                 const augur_cuda_nvfp4_sm100_gemv_args_v1* a, uint32_t member, uint64_t partial_offset) {
+                 const augur_cuda_nvfp4_sm100_gemv_args_v1* a, uint32_t member, uint64_t partial_offset,
+                 uint64_t staged_out_offset = 0, bool input_is_staged = false) {
     const bool pair = a->epilogue == AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16;
     const GemvGeometry g = geometry(a->rows, a->cols, pair, plan->sm_count);
     GemvParams p{};
@@ -655,6 +691,8 @@ void launch_gemv(augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* pl
     p.factors = reinterpret_cast<const float*>(plan->scratch + partial_offset + static_cast<uint64_t>(a->cols) * 16);
     p.partials = reinterpret_cast<float*>(plan->scratch + partial_offset + g.staged_bytes);
     p.unit = g.unit;
+    p.fixed_factor = input_is_staged ? 0x1p31f : 0.0f;      // (2^31)^2 = 2^(126 - kFixedStageShift)
+    p.staged_out = staged_out_offset ? reinterpret_cast<uint16_t*>(plan->scratch + staged_out_offset) : nullptr;
     p.status_word = plan->status_word;
 #ifdef AUGUR_GEMV_TRACE
     p.trace = reinterpret_cast<unsigned long long*>(plan->scratch + plan->scratch_bytes - 65536) + member * 4096;
@@ -672,17 +710,20 @@ void launch_gemv(augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* pl
     config.stream = s->stream;
     config.attrs = &attribute;
     config.numAttrs = 1;
-    config.gridDim = dim3(AUGUR_NVFP4_SM100_MAX_SMALL_TOKENS);
-    config.blockDim = dim3(512);
-    config.dynamicSmemBytes = 0;
-    cudaLaunchKernelEx(&config, stage_kernel, p.x, reinterpret_cast<uint32_t*>(plan->scratch + partial_offset),
-                       reinterpret_cast<float*>(plan->scratch + partial_offset + static_cast<uint64_t>(a->cols) * 16),
-                       a->cols, a->tokens);
+    if (!input_is_staged) {
+        config.gridDim = dim3(AUGUR_NVFP4_SM100_MAX_SMALL_TOKENS);
+        config.blockDim = dim3(512);
+        config.dynamicSmemBytes = 0;
+        cudaLaunchKernelEx(&config, stage_kernel, p.x, reinterpret_cast<uint32_t*>(plan->scratch + partial_offset),
+                           reinterpret_cast<float*>(plan->scratch + partial_offset + static_cast<uint64_t>(a->cols) * 16),
+                           a->cols, a->tokens);
+        count_launch();
+    }
     config.gridDim = dim3(g.slabs * g.ctas_per_slab);
     config.blockDim = dim3(kWarps * 32);
     config.dynamicSmemBytes = kGemvSmemBytes;
     cudaLaunchKernelEx(&config, gemv_kernel, p);
-    count_launch(2);
+    count_launch();
 }
 
 }  // namespace
@@ -792,9 +833,10 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_mlp_preva
     if (consume_injected_fault()) return make_result(AUGUR_CUDA_STATUS_DIAGNOSTIC_FAULT_INJECTED);
     const cudaError_t e = cudaSetDevice(d);
     if (e != cudaSuccess) return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE, e);
-    launch_gemv(s, plan, &a->gate_up, 0, kCounterBytes);
+    // gate|up stages its own input, and its epilogue stages the intermediate where down expects it.
+    launch_gemv(s, plan, &a->gate_up, 0, kCounterBytes, down_offset, false);
     augur_cuda_result_v1 first = submitted();
     if (first.status != AUGUR_CUDA_STATUS_OK) return first;
-    launch_gemv(s, plan, &a->down, 1, down_offset);
+    launch_gemv(s, plan, &a->down, 1, down_offset, 0, true);
     return submitted();
 }
