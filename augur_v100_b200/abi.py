@@ -35,6 +35,7 @@ EPILOGUE_SWIGLU_BF16 = 1
 EPILOGUE_LINEAR_F32 = 2
 
 MAX_SMALL_TOKENS = 8
+STATIC_SCRATCH_BYTES = 4 << 20
 
 
 class Result(Structure):
@@ -119,6 +120,7 @@ EXPORTS = {
     "augur_cuda_nvfp4_sm100_dequant_f32_prevalidated_submit_v1": (Result, [c_int32, c_void_p, POINTER(DequantArgs)]),
     "augur_cuda_nvfp4_sm100_gemv_bf16_preflight_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(GemvArgs)]),
     "augur_cuda_nvfp4_sm100_gemv_bf16_prevalidated_submit_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(GemvArgs)]),
+    "augur_cuda_nvfp4_sm100_gemv_bf16_static_scratch_submit_v1": (Result, [c_int32, c_void_p, POINTER(GemvArgs)]),
     "augur_cuda_nvfp4_sm100_mlp_preflight_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(MlpArgs)]),
     "augur_cuda_nvfp4_sm100_mlp_prevalidated_submit_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(MlpArgs)]),
     "augur_cuda_nvfp4_sm100_act_quant_preflight_v1": (Result, [c_int32, c_void_p, POINTER(ActQuantArgs)]),

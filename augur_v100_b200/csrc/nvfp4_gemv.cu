@@ -24,6 +24,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdlib>
+#include <mutex>
 
 #include "nvfp4_internal.h"
 #include "nvfp4_layout.cuh"
@@ -838,5 +839,77 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_mlp_preva
     augur_cuda_result_v1 first = submitted();
     if (first.status != AUGUR_CUDA_STATUS_OK) return first;
     launch_gemv(s, plan, &a->down, 1, down_offset, 0, true);
+    return submitted();
+}
+
+// ---- one entry point that allocates nothing -------------------------------------------------
+// Plan creation calls cudaMalloc. A host that gave every byte of device memory to its own arena
+// at start-up, or that runs its serving loop under a no-allocation rule and audits it, cannot
+// create a plan once it is running. For such callers the small-token linear is also offered
+// with its scratch in this fixed array, which every GPU that loads the library carries from
+// load to exit.
+namespace {
+static __device__ __align__(256) uint8_t g_static_scratch[AUGUR_NVFP4_SM100_STATIC_SCRATCH_BYTES];
+
+struct StaticScratchDevice {
+    bool ready = false;
+    uint8_t* address = nullptr;   // device address of g_static_scratch on this device
+    uint32_t sm_count = 0;
+};
+StaticScratchDevice g_static_devices[64];
+std::mutex g_static_mutex;
+
+// Once per device, with that device current: the array's name is only a host-side handle, the
+// kernels need the address the runtime reports for it.
+cudaError_t static_scratch_setup(int32_t ordinal, StaticScratchDevice** out) {
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    StaticScratchDevice& device = g_static_devices[ordinal];
+    if (!device.ready) {
+        void* address = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&address, g_static_scratch);
+        if (e != cudaSuccess) return e;
+        int sms = 0;
+        e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, ordinal);
+        if (e != cudaSuccess) return e;
+        e = gemv_configure_device();
+        if (e != cudaSuccess) return e;
+        device.address = static_cast<uint8_t*>(address);
+        device.sm_count = static_cast<uint32_t>(sms);
+        device.ready = true;
+    }
+    *out = &device;
+    return cudaSuccess;
+}
+}  // namespace
+
+extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_bf16_static_scratch_submit_v1(
+    int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_gemv_args_v1* a) {
+    if (d < 0 || d >= 64 || !s || s->ordinal != d || !a) return invalid();
+    cudaError_t e = cudaSetDevice(d);
+    if (e != cudaSuccess) return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE, e);
+    StaticScratchDevice* device = nullptr;
+    e = static_scratch_setup(d, &device);
+    if (e != cudaSuccess) return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE, e);
+    // A plan-shaped view of the fixed array: status word in front, then the same layout a plan has.
+    augur_cuda_nvfp4_sm100_plan_v1 view{};
+    view.magic = kPlanMagic;
+    view.ordinal = d;
+    view.owner = s;
+    view.status_word = reinterpret_cast<uint32_t*>(device->address);
+    view.scratch = device->address + kPlanHeaderBytes;
+    view.scratch_bytes = AUGUR_NVFP4_SM100_STATIC_SCRATCH_BYTES - kPlanHeaderBytes;
+    view.sm_count = device->sm_count;
+    // The same checks as the plan-based submit; a shape whose scratch need exceeds the fixed
+    // array fails here with INVALID_ARGUMENT before anything is enqueued.
+    augur_cuda_result_v1 failure;
+    if (!check_gemv(d, s, &view, a, kCounterBytes, view.scratch_bytes, false, &failure)) return failure;
+    if (consume_injected_fault()) return make_result(AUGUR_CUDA_STATUS_DIAGNOSTIC_FAULT_INJECTED);
+    // The array keeps whatever the last call left. Arrival counters must read zero when the
+    // kernel starts, so they are cleared on the caller's stream first (a memset, not an allocation).
+    const bool pair = a->epilogue == AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16;
+    const uint32_t groups = pair ? a->rows / 16 : a->rows / 32;
+    e = cudaMemsetAsync(view.scratch, 0, static_cast<size_t>(groups) * 4, s->stream);
+    if (e != cudaSuccess) return make_result(AUGUR_CUDA_STATUS_SUBMISSION_FAILURE, e);
+    launch_gemv(s, &view, a, 0, kCounterBytes);
     return submitted();
 }

@@ -234,6 +234,24 @@ augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_bf16_prevalidat
     int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
     const augur_cuda_nvfp4_sm100_gemv_args_v1* args);
 
+/* No counterpart in the reference. The same small-token linear for callers that may not allocate:
+ * plan creation calls cudaMalloc, which a host cannot do once it has handed all device memory to
+ * its own arena, or while it runs under an audited no-allocation rule (the discipline Augur's own
+ * runtime applies to its serving loop). This entry needs no plan: its scratch is a fixed array of
+ * AUGUR_NVFP4_SM100_STATIC_SCRATCH_BYTES inside the library image, held by every GPU that loads the
+ * library until the process exits. It calls no cudaMalloc / cudaFree and no allocating library
+ * routine. The first call on a device looks the array's device address up and sets the kernel's
+ * shared-memory attribute; make that first call before any stream capture. Shapes whose scratch need
+ * is larger than the array return AUGUR_CUDA_STATUS_INVALID_ARGUMENT with nothing enqueued (the two
+ * MLP projections of the 27B profile, 17408 x 5120 and 5120 x 17408, fit). All calls share the one
+ * array, which keeps the previous call's contents (the arrival counters are cleared on the stream
+ * at the start of every call): two calls that overlap on the GPU race - keep them on one stream or
+ * order them with events. Same descriptor and same checks as gemv_bf16_prevalidated_submit_v1,
+ * without the driver queries of a preflight. */
+#define AUGUR_NVFP4_SM100_STATIC_SCRATCH_BYTES (UINT32_C(4) << 20)
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_bf16_static_scratch_submit_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, const augur_cuda_nvfp4_sm100_gemv_args_v1* args);
+
 /* ---- MLP program: gate|up + SwiGLU, then down ------------------------------- */
 /* Replaces CudaQwen35QpnFfnProgramV1's two native steps
  * (crates/augur-backend/src/cuda_qwen35_prefill_cublas/qpn.rs:391-394,465-492;
