@@ -1,24 +1,25 @@
 // Small-token (1..8) NVFP4 linear for sm_100a: a bandwidth-bound dequantising GEMV.
 //
-// Data path per weight block (32 rows x 128 k, 2304 bytes, already in mma fragment
-// order): six 128-bit coalesced loads per lane -> cvt.rn.f16x2.e2m1x2 (codes) and
-// cvt.rn.f16x2.e4m3x2 (block scales) -> one packed f16 multiply per fragment register
-// (e2m1 x e4m3 is exact in f16) -> mma.sync.m16n8k16 with the 8 token rows on the
-// MMA n dimension and f32 accumulators. An FP32 SIMT inner product cannot keep up
-// with HBM at 8 tokens (8 FMA per weight element), so the inner product is on the
-// tensor cores and the ALU work is the dequantisation only.
+// Data path per weight block (32 rows x 128 k, 2304 bytes, already in mma fragment order with
+// the codes bit-placed as BF16 fields): one bulk asynchronous copy into a per-warp ring in
+// shared memory -> per k-step a shift and a mask per fragment register (the register is then
+// two BF16 numbers e2m1 * 2^-126) -> mma.sync.m16n8k16 with the 8 token rows on the MMA n
+// dimension, f32 result -> four f32 FMAs that apply the block scales of the two rows a lane
+// holds. An FP32 SIMT inner product cannot keep up with HBM at 8 tokens (8 FMA per weight
+// element), so the inner product is on the tensor cores and the ALU work is the decoding only.
 //
-// Activations: each CTA stages the BF16 activations of its k-slab into shared memory
-// as f16 B fragments, multiplied per token by an exact power of two chosen so that the
-// largest magnitude lands in [2^14, 2^15); partial sums are scaled back before they
-// leave the warp, so CTAs need not agree on the exponent.
+// Activations are BF16 B fragments in shared memory, multiplied per token by an exact power of
+// two so that every product with a 2^-126-scaled weight is a normal f32; partial sums are
+// scaled back before they leave the warp, so CTAs need not agree on the exponent. A plain
+// input is staged by each CTA for its own k-slab; an intermediate produced by the SwiGLU
+// epilogue of this kernel is written staged (fixed exponent) and bulk-copied in.
 //
 // Work split (balanced over any grid): the block space of a k-slab is cut into equal
 // contiguous spans, one per CTA, and each CTA's span into equal contiguous spans, one
 // per warp. Row groups that straddle a warp boundary are combined in shared memory in
 // warp order; row groups that straddle a CTA or slab boundary are combined through
 // plan scratch with an arrival counter, the last arriver summing the slots in a fixed
-// order. Nothing spins, and the result does not depend on scheduling.
+// order. Nothing spins on another CTA, and the result does not depend on scheduling.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -59,9 +60,8 @@ struct GemvParams {
 #ifdef AUGUR_GEMV_TRACE
     unsigned long long* trace;   // [CTA][4] nanosecond stamps: start, staged, streamed, done
 #endif
-    const uint8_t* staged;     // activations as BF16 B fragments, [cols/32][32 lanes][16 bytes]
-    const float* factors;      // per token: two factors whose product undoes the staging exponent
-    float fixed_factor;        // non-zero: both factors are this constant for every token (no table)
+    const uint8_t* staged;     // activations already staged by the producing launch (fixed exponent), or unused
+    float fixed_factor;        // non-zero: input is `staged`, and both rescale factors are this constant
     uint16_t* staged_out;      // SwiGLU epilogue: also write the result as staged fragments (or null)
     uint32_t groups, kb_count, slabs, ctas_per_slab, max_contrib, unit;
     uint32_t rows, cols, tokens, epilogue;
@@ -293,68 +293,89 @@ __device__ __forceinline__ void epilogue(const GemvParams& p, uint32_t group, co
 }
 
 // ---- activation staging --------------------------------------------------------------------
-// One CTA per token row: finds the row's largest magnitude, picks the exponent shift e that
-// puts it in [2^100, 2^101) (so that the 2^-126-scaled weight fragments meet activations
-// large enough to keep every product a normal f32), and writes x * 2^e as BF16 in the
-// mma B-fragment order the streaming kernel copies straight into shared memory:
+// Plain BF16 activations are staged by every CTA for its own k-slab: the CTA finds each token
+// row's largest magnitude over the slab, picks the exponent shift e that puts it in
+// [2^100, 2^101) (so that the 2^-126-scaled weight fragments meet activations large enough to
+// keep every product a normal f32), and writes x * 2^e as BF16 into shared memory in the mma
+// B-fragment order
 //   [k-step pair][lane = token*4 + t4][4 words: b0,b1 of the even k-step, b0,b1 of the odd one].
-// Runs once per activation tensor instead of once per CTA of the streaming kernel, which is
-// launched with programmatic stream serialisation and overlaps its weight prefetch with this.
-__global__ void __launch_bounds__(512) stage_kernel(const uint16_t* __restrict__ x, uint32_t* __restrict__ staged,
-                                                    float* __restrict__ factors, uint32_t cols, uint32_t tokens) {
-    // Launched with programmatic stream serialisation. The streaming kernel behind it is released
-    // at once (it only prefetches weights until its own wait, which covers this whole grid);
-    // this kernel then waits for the kernel before it, which may produce x and may still be
-    // reading an older staging of this region.
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    __shared__ float s_amax[16];
-    __shared__ int s_shift;
-    const uint32_t token = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const bool live = token < tokens;
-    const uint32_t chunks = cols / 8;   // 16-byte chunks of 8 bf16
-    const uint4* row = reinterpret_cast<const uint4*>(x + static_cast<uint64_t>(token) * cols);
-    float amax = 0.0f;
-    if (live) {
-        for (uint32_t c = threadIdx.x; c < chunks; c += blockDim.x) {
-            const uint4 v = __ldg(row + c);
-            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+// The raw rows arrive by bulk copy in the same shared memory the fragments will occupy. A lane
+// handles one token (lane/4) and one 16-byte chunk (8 k) of every 16th k-step pair; it takes
+// all its chunks into registers before anything is rewritten, and - with the four words of a
+// chunk stored in an order rotated by token/2 - the 32 lanes of a store hit 32 different banks.
+constexpr uint32_t kStageChunks = kMaxSlabBlocks * 4 / kWarps;   // chunks per lane, at most
+
+// Returns the two factors (product 2^(126 - e)) in `factor_out[2*token], [2*token+1]` (shared).
+__device__ __forceinline__ void stage_activations(const GemvParams& p, uint32_t kbs, uint32_t* act_words,
+                                                  float* amax_scratch, float* factor_out, uint32_t lane, uint32_t warp) {
+    const uint32_t token = lane >> 2, cc = lane & 3;
+    const uint32_t pairs = kbs * 4;   // k-step pairs in the slab
+    const bool live = token < p.tokens;
+    // The slab's columns of every token row were bulk-copied, as they are, to the front of the
+    // activation area ([token][kbs*256 bytes]); each lane takes its chunks into registers, and the
+    // area is rewritten in fragment order once every lane has (the barrier below).
+    const uint4* row = reinterpret_cast<const uint4*>(act_words) + token * kbs * 16;
+    uint4 v[kStageChunks];
 #pragma unroll
-            for (uint32_t i = 0; i < 4; ++i) {
-                amax = fmaxf(amax, fabsf(__uint_as_float(w[i] << 16)));
-                amax = fmaxf(amax, fabsf(__uint_as_float(w[i] & 0xffff0000u)));
-            }
-        }
+    for (uint32_t j = 0; j < kStageChunks; ++j) {
+        const uint32_t q = warp + kWarps * j;
+        v[j] = make_uint4(0, 0, 0, 0);
+        if (live && q < pairs) v[j] = row[q * 4 + cc];
     }
+    // largest magnitude, two BF16 lanes at a time
+    __nv_bfloat162 amax2 = __float2bfloat162_rn(0.0f);
 #pragma unroll
-    for (uint32_t o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    if (lane == 0) s_amax[warp] = amax;
+    for (uint32_t j = 0; j < kStageChunks; ++j) {
+        const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+        for (uint32_t i = 0; i < 4; ++i) amax2 = __hmax2_nan(amax2, __habs2(*reinterpret_cast<const __nv_bfloat162*>(&w[i])));
+    }
+    float amax = fmaxf(__low2float(amax2), __high2float(amax2));
+    if (!(amax == amax)) amax = __int_as_float(0x7f800000);   // a NaN anywhere: the row is staged unshifted
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    if (cc == 0) amax_scratch[warp * 8 + token] = amax;
     __syncthreads();
-    if (threadIdx.x == 0) {
-        float m = 0.0f;
-        for (uint32_t i = 0; i < blockDim.x / 32; ++i) m = fmaxf(m, s_amax[i]);
-        int e = 0;   // zero or non-finite rows are staged unshifted
-        const int field = static_cast<int>((__float_as_uint(m) >> 23) & 0xff);
-        if (m > 0.0f && field != 0xff && field != 0) e = 227 - field;
-        s_shift = e;
+    float m = 0.0f;
+#pragma unroll
+    for (uint32_t w = 0; w < kWarps; ++w) m = fmaxf(m, amax_scratch[w * 8 + token]);
+    int e = 0;   // zero or non-finite rows are staged unshifted
+    const int field = static_cast<int>((__float_as_uint(m) >> 23) & 0xff);
+    if (m > 0.0f && field != 0xff && field != 0) e = 227 - field;
+    if (warp == 0 && cc == 0) {
         // partial sums are multiplied by 2^(126 - e), split in two factors that are always finite
         const int q = 126 - e, q0 = q / 2, q1 = q - q0;
-        factors[2 * token] = __uint_as_float(static_cast<uint32_t>(127 + q0) << 23);
-        factors[2 * token + 1] = __uint_as_float(static_cast<uint32_t>(127 + q1) << 23);
+        factor_out[2 * token] = __uint_as_float(static_cast<uint32_t>(127 + q0) << 23);
+        factor_out[2 * token + 1] = __uint_as_float(static_cast<uint32_t>(127 + q1) << 23);
     }
-    __syncthreads();
-    const int shift = s_shift;
-    for (uint32_t c = threadIdx.x; c < chunks; c += blockDim.x) {
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (live) v = __ldg(row + c);
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-        // chunk c holds k = 8c..8c+7: k-step c/2, fragment register c%2; word i is the pair
-        // k%16 = 8(c%2) + 2i, +1 and belongs to lane token*4 + i
-        const uint32_t kstep = c >> 1, reg = c & 1;
-        uint32_t* dst = staged + ((kstep >> 1) * 32 + token * 4) * 4 + (kstep & 1) * 2 + reg;
+#ifdef AUGUR_GEMV_TRACE
+    if (threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        p.trace[blockIdx.x * 10 + 5] = t;
+    }
+#endif
+    // x * 2^e as two exact BF16 multiplications by 2^(e/2) and 2^(e - e/2) (e is in [-27, 226]);
+    // the values only move toward the staged row's magnitude, so neither step can overflow.
+    const int e0 = e / 2, e1 = e - e0;
+    const __nv_bfloat162 f0 = __float2bfloat162_rn(__uint_as_float(static_cast<uint32_t>(127 + e0) << 23));
+    const __nv_bfloat162 f1 = __float2bfloat162_rn(__uint_as_float(static_cast<uint32_t>(127 + e1) << 23));
+    const uint32_t turn = token >> 1;
+#pragma unroll
+    for (uint32_t j = 0; j < kStageChunks; ++j) {
+        const uint32_t q = warp + kWarps * j;
+        if (q >= pairs) break;
+        // chunk (q, cc) holds k-step 2q + cc/2, fragment register cc%2; its word i is the pair
+        // k%16 = 8(cc%2) + 2i, +1 and belongs to B-fragment lane token*4 + i
+        uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+        if (turn & 1) { const uint32_t t = w[0]; w[0] = w[1]; w[1] = w[2]; w[2] = w[3]; w[3] = t; }
+        if (turn & 2) { uint32_t t = w[0]; w[0] = w[2]; w[2] = t; t = w[1]; w[1] = w[3]; w[3] = t; }
+        uint32_t* dst = act_words + q * 128 + token * 16 + cc;
 #pragma unroll
         for (uint32_t i = 0; i < 4; ++i) {
-            dst[i * 4] = shift_bf16(w[i] & 0xffffu, shift) | (shift_bf16(w[i] >> 16, shift) << 16);
+            const uint32_t word = (i + turn) & 3;
+            const __nv_bfloat162 moved = __hmul2(__hmul2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]), f0), f1);
+            dst[word * 4] = *reinterpret_cast<const uint32_t*>(&moved);
         }
     }
 }
@@ -362,14 +383,29 @@ __global__ void __launch_bounds__(512) stage_kernel(const uint16_t* __restrict__
 // One CTA's finished share of row group `group` in k-slab `slab` (whole warp calls this).
 __device__ __forceinline__ void contribute(const GemvParams& p, uint32_t group, uint32_t slab, uint32_t cta_in_slab,
                                            const float (&v)[8], uint32_t lane) {
+    // Spans cut at row-group boundaries (one k-slab): the group was finished inside this CTA.
+    if (p.unit != 1) {
+        epilogue(p, group, v, lane);
+        return;
+    }
+    // How many CTAs hold a share of this group, over all k-slabs, and which of them this one is.
     uint32_t total = 0, mine = 0;
-    for (uint32_t s = 0; s < p.slabs; ++s) {
-        const uint32_t kbs = (s + 1) * p.kb_count / p.slabs - s * p.kb_count / p.slabs;
-        const uint32_t units = p.groups * kbs / p.unit;
-        const uint32_t first = span_of(group * kbs / p.unit, units, p.ctas_per_slab);
-        const uint32_t last = span_of(((group + 1) * kbs - 1) / p.unit, units, p.ctas_per_slab);
-        if (s == slab) mine = total + (cta_in_slab - first);
-        total += last - first + 1;
+    if (p.kb_count % p.slabs == 0) {
+        // every slab is cut alike
+        const uint32_t kbs = p.kb_count / p.slabs, units = p.groups * kbs;
+        const uint32_t first = span_of(group * kbs, units, p.ctas_per_slab);
+        const uint32_t count = span_of((group + 1) * kbs - 1, units, p.ctas_per_slab) - first + 1;
+        total = p.slabs * count;
+        mine = slab * count + (cta_in_slab - first);
+    } else {
+        for (uint32_t s = 0; s < p.slabs; ++s) {
+            const uint32_t kbs = (s + 1) * p.kb_count / p.slabs - s * p.kb_count / p.slabs;
+            const uint32_t units = p.groups * kbs;
+            const uint32_t first = span_of(group * kbs, units, p.ctas_per_slab);
+            const uint32_t last = span_of((group + 1) * kbs - 1, units, p.ctas_per_slab);
+            if (s == slab) mine = total + (cta_in_slab - first);
+            total += last - first + 1;
+        }
     }
     if (total == 1) {
         epilogue(p, group, v, lane);
@@ -379,21 +415,54 @@ __device__ __forceinline__ void contribute(const GemvParams& p, uint32_t group, 
     float4* my_slot = reinterpret_cast<float4*>(slots + static_cast<uint64_t>(mine) * kSlotFloats) + lane * 2;
     my_slot[0] = make_float4(v[0], v[1], v[2], v[3]);
     my_slot[1] = make_float4(v[4], v[5], v[6], v[7]);
+#ifdef AUGUR_GEMV_TRACE
+    auto mark = [&](uint32_t which) {
+        if (threadIdx.x == 0) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            p.trace[blockIdx.x * 10 + which] = t;
+        }
+    };
+    mark(6);
+#endif
     __threadfence();
     __syncwarp();
+#ifdef AUGUR_GEMV_TRACE
+    mark(7);
+#endif
     uint32_t arrived = 0;
     if (lane == 0) arrived = atomicAdd(&p.counters[group], 1u);
     arrived = __shfl_sync(0xffffffffu, arrived, 0);
+#ifdef AUGUR_GEMV_TRACE
+    mark(8);
+#endif
     if (arrived + 1 != total) return;
     __threadfence();
+    // Slots are summed in slot order; four are fetched at a time so that their latencies overlap.
     float sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (uint32_t j = 0; j < total; ++j) {
-        const float4* slot = reinterpret_cast<const float4*>(slots + static_cast<uint64_t>(j) * kSlotFloats) + lane * 2;
-        const float4 a = __ldcg(slot), b = __ldcg(slot + 1);
-        sum[0] += a.x; sum[1] += a.y; sum[2] += a.z; sum[3] += a.w;
-        sum[4] += b.x; sum[5] += b.y; sum[6] += b.z; sum[7] += b.w;
+    for (uint32_t j0 = 0; j0 < total; j0 += 4) {
+        float4 a[4], b[4];
+#pragma unroll
+        for (uint32_t j = 0; j < 4; ++j) {
+            const float4* slot = reinterpret_cast<const float4*>(slots + static_cast<uint64_t>(j0 + j) * kSlotFloats) + lane * 2;
+            a[j] = b[j] = make_float4(0, 0, 0, 0);
+            if (j0 + j < total) {
+                a[j] = __ldcg(slot);
+                b[j] = __ldcg(slot + 1);
+            }
+        }
+#pragma unroll
+        for (uint32_t j = 0; j < 4; ++j) {
+            if (j0 + j < total) {
+                sum[0] += a[j].x; sum[1] += a[j].y; sum[2] += a[j].z; sum[3] += a[j].w;
+                sum[4] += b[j].x; sum[5] += b[j].y; sum[6] += b[j].z; sum[7] += b[j].w;
+            }
+        }
     }
     epilogue(p, group, sum, lane);
+#ifdef AUGUR_GEMV_TRACE
+    mark(9);
+#endif
     if (lane == 0) p.counters[group] = 0;  // leave the counter clean for the next launch
 }
 
@@ -404,7 +473,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_kernel(const GemvParams p
         if (threadIdx.x == 0) {
             unsigned long long t;
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-            p.trace[blockIdx.x * 4 + which] = t;
+            p.trace[blockIdx.x * 10 + which] = t;
         }
     };
     stamp(0);
@@ -469,23 +538,40 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_kernel(const GemvParams p
     }
 #endif
 
-    // ---- activations of this k-slab: staged by stage_kernel, copied in as they are ----
+    // ---- activations of this k-slab ----
     // Everything above touched only this CTA's shared memory and read-only weights, so it may
-    // run while the staging kernel is still in flight; from here on its output is needed.
+    // run while the kernel before this one is still in flight; from here on its output is needed.
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const uint32_t act_bar = smem_u32(bars + kWarps * kDepth);
+#ifdef AUGUR_GEMV_TRACE
+    stamp(4);
+#endif
+    float* stage_scratch = reinterpret_cast<float*>(scale_area);   // free until the streaming loop starts
+    const bool plain = p.fixed_factor == 0.0f;
     {
-        const uint32_t act_bytes = kbs * 2048;             // 4 k-step pairs x 512 bytes per block
-        const uint8_t* src = p.staged + static_cast<uint64_t>(kb_lo) * 2048;
+        // Plain BF16 input: the slab's columns of each token row, copied as they are and staged
+        // below. Otherwise the producing launch's epilogue staged them (fixed exponent) and they
+        // are copied in ready for use.
+        const uint32_t act_bar = smem_u32(bars + kWarps * kDepth);
+        const uint32_t row_bytes = kbs * 256;
+        const uint32_t act_bytes = plain ? p.tokens * row_bytes : kbs * 2048;   // staged: 4 k-step pairs x 512 bytes per block
         if (threadIdx.x == 0) mbar_expect_tx(act_bar, act_bytes);
         __syncthreads();
         // one copy per warp, issued in parallel
-        const uint32_t per_warp = (kbs + kWarps - 1) / kWarps * 2048;
-        const uint32_t begin = warp * per_warp;
-        if (lane == 0 && begin < act_bytes) {
-            const uint32_t bytes = act_bytes - begin < per_warp ? act_bytes - begin : per_warp;
+        const uint8_t* src;
+        uint32_t begin, bytes = 0;
+        if (plain) {
+            src = reinterpret_cast<const uint8_t*>(p.x) + (static_cast<uint64_t>(warp) * p.cols + kb_lo * kStreamBlockK) * 2;
+            begin = warp * row_bytes;
+            if (warp < p.tokens) bytes = row_bytes;
+        } else {
+            const uint32_t per_warp = (kbs + kWarps - 1) / kWarps * 2048;
+            begin = warp * per_warp;
+            src = p.staged + static_cast<uint64_t>(kb_lo) * 2048 + begin;
+            if (begin < act_bytes) bytes = act_bytes - begin < per_warp ? act_bytes - begin : per_warp;
+        }
+        if (lane == 0 && bytes) {
             asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                         ::"r"(smem_u32(smem + begin)), "l"(src + begin), "r"(bytes), "r"(act_bar)
+                         ::"r"(smem_u32(smem + begin)), "l"(src), "r"(bytes), "r"(act_bar)
                          : "memory");
         }
         uint32_t spin = 0;
@@ -493,7 +579,11 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_kernel(const GemvParams p
         while (!mbar_try_wait(act_bar, 0)) {
             if (++spin > kWaitLimit) { arrived = false; break; }
         }
-        if (!arrived && threadIdx.x == 0) atomicCAS(p.status_word, 0u, 0x202u);   // staged activations never arrived
+        if (!arrived && threadIdx.x == 0) atomicCAS(p.status_word, 0u, 0x202u);   // the activations never arrived
+    }
+    if (plain) {
+        stage_activations(p, kbs, reinterpret_cast<uint32_t*>(smem), stage_scratch, stage_scratch + kWarps * 8, lane, warp);
+        __syncthreads();
     }
 
 #ifdef AUGUR_GEMV_TRACE
@@ -501,9 +591,11 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_kernel(const GemvParams p
 #endif
     const uint32_t t4 = lane & 3;
     float inv0a = p.fixed_factor, inv0b = p.fixed_factor, inv1a = p.fixed_factor, inv1b = p.fixed_factor;
-    if (p.fixed_factor == 0.0f) {
-        inv0a = __ldg(p.factors + 4 * t4); inv0b = __ldg(p.factors + 4 * t4 + 1);         // token 2*t4
-        inv1a = __ldg(p.factors + 4 * t4 + 2); inv1b = __ldg(p.factors + 4 * t4 + 3);     // token 2*t4 + 1
+    if (plain) {
+        const float* factors = stage_scratch + kWarps * 8;
+        inv0a = factors[4 * t4]; inv0b = factors[4 * t4 + 1];         // token 2*t4
+        inv1a = factors[4 * t4 + 2]; inv1b = factors[4 * t4 + 3];     // token 2*t4 + 1
+        __syncthreads();   // the scratch becomes the block-scale area of the streaming loop
     }
     Cursor now = cursor_at(w0);
     const uint32_t first_group = now.group;
@@ -608,7 +700,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_kernel(const GemvParams p
         for (uint32_t w = w_lo; w <= w_hi; ++w) {
             const uint32_t b0 = c0 + w * len / kWarps, b1 = c0 + (w + 1) * len / kWarps;
             if (b1 == b0) continue;
-            const uint32_t slot = (b0 / kbs == group) ? 0 : 1;
+            const uint32_t slot = (b0 >= group * kbs) ? 0 : 1;   // the span's first row group parks in slot 0
             const float4* src = reinterpret_cast<const float4*>(warp_partial + w * kWarpPartialFloats + slot * kSlotFloats) + lane * 2;
             const float4 a = src[0], b = src[1];
             sum[0] += a.x; sum[1] += a.y; sum[2] += a.z; sum[3] += a.w;
@@ -689,21 +781,21 @@ void launch_gemv(augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* pl
     p.out = reinterpret_cast<void*>(a->output);
     p.counters = reinterpret_cast<uint32_t*>(plan->scratch + member * kCounterRegionBytes);
     p.staged = plan->scratch + partial_offset;
-    p.factors = reinterpret_cast<const float*>(plan->scratch + partial_offset + static_cast<uint64_t>(a->cols) * 16);
     p.partials = reinterpret_cast<float*>(plan->scratch + partial_offset + g.staged_bytes);
     p.unit = g.unit;
     p.fixed_factor = input_is_staged ? 0x1p31f : 0.0f;      // (2^31)^2 = 2^(126 - kFixedStageShift)
     p.staged_out = staged_out_offset ? reinterpret_cast<uint16_t*>(plan->scratch + staged_out_offset) : nullptr;
     p.status_word = plan->status_word;
 #ifdef AUGUR_GEMV_TRACE
-    p.trace = reinterpret_cast<unsigned long long*>(plan->scratch + plan->scratch_bytes - 65536) + member * 4096;
+    static uint32_t trace_sequence = 0;   // eight most recent launches, 2048 stamps each
+    p.trace = reinterpret_cast<unsigned long long*>(plan->scratch + plan->scratch_bytes - 131072) + (trace_sequence++ % 8) * 2048;
 #endif
     p.groups = g.groups; p.kb_count = g.kb_count; p.slabs = g.slabs; p.ctas_per_slab = g.ctas_per_slab;
     p.max_contrib = g.max_contrib;
     p.rows = a->rows; p.cols = a->cols; p.tokens = a->tokens; p.epilogue = a->epilogue;
     p.global_a = a->global_scale; p.global_b = a->global_scale_b;
-    // Both kernels are launched with programmatic stream serialisation: each may become resident
-    // while its predecessor drains and waits for it in-kernel (griddepcontrol.wait).
+    // Launched with programmatic stream serialisation: the grid may become resident while its
+    // predecessor drains, and waits for it in-kernel (griddepcontrol.wait).
     cudaLaunchAttribute attribute{};
     attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attribute.val.programmaticStreamSerializationAllowed = 1;
@@ -711,15 +803,6 @@ void launch_gemv(augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* pl
     config.stream = s->stream;
     config.attrs = &attribute;
     config.numAttrs = 1;
-    if (!input_is_staged) {
-        config.gridDim = dim3(AUGUR_NVFP4_SM100_MAX_SMALL_TOKENS);
-        config.blockDim = dim3(512);
-        config.dynamicSmemBytes = 0;
-        cudaLaunchKernelEx(&config, stage_kernel, p.x, reinterpret_cast<uint32_t*>(plan->scratch + partial_offset),
-                           reinterpret_cast<float*>(plan->scratch + partial_offset + static_cast<uint64_t>(a->cols) * 16),
-                           a->cols, a->tokens);
-        count_launch();
-    }
     config.gridDim = dim3(g.slabs * g.ctas_per_slab);
     config.blockDim = dim3(kWarps * 32);
     config.dynamicSmemBytes = kGemvSmemBytes;

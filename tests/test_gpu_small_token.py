@@ -227,7 +227,7 @@ def test_hot_path_allocates_nothing_and_counts_launches(ctx):
     ctx["stream"].synchronize()
     assert host.allocation_snapshot() == before_alloc
     assert torch.cuda.memory_stats()["allocation.all.allocated"] == torch_before
-    assert host.launch_count() - before_launch == 48     # per program: stage + gate|up + down
+    assert host.launch_count() - before_launch == 32     # per program: gate|up + down
 
 
 def test_cuda_graph_capture_and_replay_with_refreshed_inputs(ctx):
