@@ -305,14 +305,17 @@ def run_library(args):
     line = {
         "metric": "nvfp4_linear_m8_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "f16 products of E2M1xE4M3 weights and BF16 activations, f32 accumulate",
+        "vs_baseline": None, "dtype": "bf16 x bf16 -> f32 (E2M1 codes as BF16 fragments on mma.sync, E4M3 block scales applied in f32)",
         "data": "synthetic",
         "config": {"workload": f"config1: NVFP4 MLP block (gate|up+SwiGLU, down), M={TOKENS}, hidden {HIDDEN}, "
                                f"intermediate {INTER}, {LAYERS} distinct layers per step",
                    "l2": f"inputs larger than L2: {LAYERS * 3 * HIDDEN * INTER * 9 // 16 // world} weight bytes per GPU per step",
                    "parallelism": f"tp{world}" if world > 1 else "single", "all_reduce": "NCCL bf16 8x5120 per layer" if world > 1 else None},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_source": peak_source,
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one gate|up launch plus one down launch
+                     # (single GPU, full shapes), from the ncu capture summarised under profiles/
+                     "traffic": 155.05e6 if world == 1 else None, "traffic_unit": "bytes per launch pair (ncu)",
+                     "peak_source": peak_source,
                      "kernel": "gemv_kernel (gate|up launch + down launch per layer; with N>1 the interval also holds the all-reduce)",
                      "bytes_per_launch_pair": per_gpu_layer_bytes, "ms_per_launch_pair": launch_pair_ms},
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": TOKENS * HIDDEN * 2,
