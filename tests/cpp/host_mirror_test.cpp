@@ -1,0 +1,214 @@
+// Drives the library through the C++ owner types (include/augur_nvfp4_sm100.hpp) and checks the
+// results against the CPU oracle (test infrastructure; linked by tests only).
+//
+// Shaped after the reference's own backend tests of the retained FFN program
+// (crates/augur-backend/src/cuda_qwen35_qpn.rs:690-707): bind once, submit repeatedly, compare
+// with the CPU statement, and prove with the allocation snapshot that the hot loop allocates
+// nothing.
+//
+// Exit code 0 and a last line "ok" on success; any check that fails prints a line and exits 1.
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+
+#include "augur_nvfp4_sm100.hpp"
+#include "nvfp4_oracle.h"
+
+using namespace augur::nvfp4_sm100;
+
+namespace {
+struct Lcg {
+    uint64_t state;
+    uint32_t next() {
+        state = state * 6364136223846793005ull + 1442695040888963407ull;
+        return static_cast<uint32_t>(state >> 33);
+    }
+    double uniform() { return (next() & 0xffffff) / double(0x1000000); }
+    double normal() {
+        double u = uniform(), v = uniform();
+        if (u < 1e-12) u = 1e-12;
+        return std::sqrt(-2.0 * std::log(u)) * std::cos(6.283185307179586 * v);
+    }
+};
+
+struct Planes {
+    std::vector<uint8_t> codes, scales;
+    float global;
+};
+
+Planes make_planes(Lcg& rng, size_t rows, size_t cols) {
+    Planes p;
+    p.codes.resize(rows * cols / 2);
+    p.scales.resize(rows * cols / 16);
+    for (auto& b : p.codes) b = static_cast<uint8_t>(rng.next());
+    for (auto& b : p.scales) b = static_cast<uint8_t>(0x28 + rng.next() % 0x20);   // 2^-4 .. 2^0, all finite and positive
+    p.global = 1.0f / 64.0f;
+    return p;
+}
+
+uint16_t to_bf16(float value) {
+    uint32_t bits;
+    std::memcpy(&bits, &value, 4);
+    bits += 0x7fff + ((bits >> 16) & 1);
+    return static_cast<uint16_t>(bits >> 16);
+}
+double from_bf16(uint16_t bits) {
+    const uint32_t wide = static_cast<uint32_t>(bits) << 16;
+    float value;
+    std::memcpy(&value, &wide, 4);
+    return value;
+}
+
+int failures = 0;
+void expect(bool condition, const char* what) {
+    if (!condition) {
+        std::printf("FAILED: %s\n", what);
+        ++failures;
+    }
+}
+
+// Largest |got - want| relative to max(|want|, 1e-3 * rms(want)).
+double rel_error(const std::vector<double>& got, const std::vector<double>& want) {
+    double sum = 0.0;
+    for (double w : want) sum += w * w;
+    const double floor = 1e-3 * std::sqrt(sum / want.size());
+    double worst = 0.0;
+    for (size_t i = 0; i < want.size(); ++i) {
+        const double scale = std::fabs(want[i]) > floor ? std::fabs(want[i]) : floor;
+        const double e = std::fabs(got[i] - want[i]) / scale;
+        if (e > worst) worst = e;
+    }
+    return worst;
+}
+double rms_error(const std::vector<double>& got, const std::vector<double>& want) {
+    double num = 0.0, den = 0.0;
+    for (size_t i = 0; i < want.size(); ++i) {
+        num += (got[i] - want[i]) * (got[i] - want[i]);
+        den += want[i] * want[i];
+    }
+    return std::sqrt(num / den);
+}
+}  // namespace
+
+int main() {
+    try {
+        expect(augur_cuda_nvfp4_sm100_abi_version() == 1, "abi version");
+        expect(augur_cuda_nvfp4_sm100_build_capability_v1() == 100, "library holds sm_100a code");
+        Lcg rng{20260101};
+        const uint32_t hidden = 512, inter = 1024, tokens = 8;
+        const int threads = augur_oracle_max_threads();
+        auto stream = std::make_shared<Stream>(0);
+
+        // ---- FFN program, tokens = 8 ----
+        Planes gate = make_planes(rng, inter, hidden), up = make_planes(rng, inter, hidden), down = make_planes(rng, hidden, inter);
+        std::vector<uint16_t> x(tokens * hidden);
+        for (auto& v : x) v = to_bf16(static_cast<float>(rng.normal()));
+        const CheckpointNvfp4Matrix gate_m{gate.codes.data(), gate.scales.data(), gate.global};
+        const CheckpointNvfp4Matrix up_m{up.codes.data(), up.scales.data(), up.global};
+        const CheckpointNvfp4Matrix down_m{down.codes.data(), down.scales.data(), down.global};
+        auto gate_up_w = Nvfp4Sm100Weight::upload_checkpoint_nvfp4(stream, AUGUR_NVFP4_SM100_LAYOUT_STREAM_PAIR, inter, hidden, gate_m, &up_m);
+        auto down_w = Nvfp4Sm100Weight::upload_checkpoint_nvfp4(stream, AUGUR_NVFP4_SM100_LAYOUT_STREAM, hidden, inter, down_m);
+        auto plan = std::make_shared<Plan>(stream, mlp_scratch_bytes(hidden, inter));
+        auto x_dev = std::make_shared<DeviceBuffer>(0, x.size() * 2);
+        auto y_dev = std::make_shared<DeviceBuffer>(0, static_cast<uint64_t>(tokens) * hidden * 2);
+        x_dev->upload(*stream, x.data(), x.size() * 2);
+        auto program = Nvfp4Sm100FfnProgram::bind(plan, gate_up_w, down_w, x_dev, y_dev, tokens);
+        program->submit_for_plan();
+        stream->synchronize();
+        const auto before = allocation_snapshot();
+        const uint64_t launches_before = launch_count();
+        for (int i = 0; i < 10; ++i) program->submit_for_plan();
+        stream->synchronize();
+        expect(allocation_snapshot() == before, "the submit loop allocates nothing");
+        expect(launch_count() - launches_before == 20, "two launches per program");
+        expect(plan->device_status() == 0, "device status word clean");
+        std::vector<uint16_t> y(tokens * hidden), h(tokens * inter);
+        y_dev->download(*stream, y.data(), y.size() * 2);
+        program->intermediate()->download(*stream, h.data(), h.size() * 2);
+        std::vector<double> h64(h.size()), y64(y.size());
+        expect(augur_oracle_mlp_f64(gate.codes.data(), gate.scales.data(), gate.global, up.codes.data(), up.scales.data(), up.global,
+                                    down.codes.data(), down.scales.data(), down.global, hidden, inter, x.data(), tokens,
+                                    h64.data(), y64.data(), threads) == 0, "oracle mlp");
+        std::vector<double> got_h(h.size()), got_y(y.size());
+        for (size_t i = 0; i < h.size(); ++i) got_h[i] = from_bf16(h[i]);
+        for (size_t i = 0; i < y.size(); ++i) got_y[i] = from_bf16(y[i]);
+        const double e_h = rel_error(got_h, h64), e_y = rms_error(got_y, y64);
+        std::printf("ffn: intermediate max rel err %.3e, output rms err %.3e\n", e_h, e_y);
+        expect(e_h <= 2e-2, "SwiGLU intermediate within 2e-2 of the fp64 oracle");
+        expect(e_y <= 2e-2, "MLP output within 2e-2 (rms) of the fp64 oracle");
+
+        // ---- one projection, tokens = 3 ----
+        {
+            const uint32_t t3 = 3;
+            auto out = std::make_shared<DeviceBuffer>(0, static_cast<uint64_t>(t3) * hidden * 2);
+            auto h_dev = std::make_shared<DeviceBuffer>(0, static_cast<uint64_t>(t3) * inter * 2);
+            h_dev->upload(*stream, h.data(), static_cast<uint64_t>(t3) * inter * 2);
+            auto linear_plan = std::make_shared<Plan>(stream, gemv_scratch_bytes(hidden, inter, t3));
+            auto projection = Nvfp4Sm100Projection::bind(linear_plan, down_w, h_dev, out, t3);
+            projection->submit_for_plan();
+            std::vector<uint16_t> got(t3 * hidden);
+            out->download(*stream, got.data(), got.size() * 2);
+            std::vector<double> want(got.size()), have(got.size());
+            expect(augur_oracle_linear_f64(down.codes.data(), down.scales.data(), down.global, hidden, inter, h.data(), t3,
+                                           want.data(), threads) == 0, "oracle linear");
+            for (size_t i = 0; i < got.size(); ++i) have[i] = from_bf16(got[i]);
+            const double e = rel_error(have, want);
+            std::printf("projection: max rel err %.3e\n", e);
+            expect(e <= 2e-2, "projection within 2e-2 of the fp64 oracle");
+            // tokens beyond the small-token limit are refused at bind time, before anything runs
+            bool refused = false;
+            try {
+                auto wide_in = std::make_shared<DeviceBuffer>(0, 9ull * inter * 2);
+                auto wide_out = std::make_shared<DeviceBuffer>(0, 9ull * hidden * 2);
+                Nvfp4Sm100Projection::bind(linear_plan, down_w, wide_in, wide_out, 9);
+            } catch (const CudaRuntimeError& error) {
+                refused = error.status == AUGUR_CUDA_STATUS_INVALID_ARGUMENT;
+            }
+            expect(refused, "nine tokens refused with INVALID_ARGUMENT");
+            // a plan is only accepted with the stream that created it
+            bool wrong_stream = false;
+            try {
+                auto other = std::make_shared<Stream>(0);
+                auto other_plan = std::make_shared<Plan>(other, gemv_scratch_bytes(hidden, inter, t3));
+                Nvfp4Sm100Projection::bind(other_plan, down_w, h_dev, out, t3);
+            } catch (const std::invalid_argument&) {
+                wrong_stream = true;
+            }
+            expect(wrong_stream, "a plan of another stream is refused");
+        }
+
+        // ---- prefill linear, tokens = 128, three activation terms ----
+        {
+            const uint32_t rows = 256, cols = 512, wide = 128, terms = 3;
+            Planes w = make_planes(rng, rows, cols);
+            const CheckpointNvfp4Matrix w_m{w.codes.data(), w.scales.data(), w.global};
+            auto weight = Nvfp4Sm100Weight::upload_checkpoint_nvfp4(stream, AUGUR_NVFP4_SM100_LAYOUT_TCGEN05, rows, cols, w_m);
+            std::vector<uint16_t> a(wide * cols);
+            for (auto& v : a) v = to_bf16(static_cast<float>(rng.normal()));
+            auto a_dev = std::make_shared<DeviceBuffer>(0, a.size() * 2);
+            auto out = std::make_shared<DeviceBuffer>(0, static_cast<uint64_t>(wide) * rows * 2);
+            a_dev->upload(*stream, a.data(), a.size() * 2);
+            auto gemm_plan = std::make_shared<Plan>(stream, gemm_scratch_bytes(rows, cols, wide, terms) + 256);
+            auto linear = Nvfp4Sm100PrefillLinear::bind(gemm_plan, weight, a_dev, out, wide, terms, 1.0f / 256.0f);
+            linear->submit_for_plan();
+            std::vector<uint16_t> got(wide * rows);
+            out->download(*stream, got.data(), got.size() * 2);
+            expect(gemm_plan->device_status() == 0, "prefill device status word clean");
+            std::vector<double> want(got.size()), have(got.size());
+            expect(augur_oracle_linear_f64(w.codes.data(), w.scales.data(), w.global, rows, cols, a.data(), wide, want.data(), threads) == 0,
+                   "oracle prefill linear");
+            for (size_t i = 0; i < got.size(); ++i) have[i] = from_bf16(got[i]);
+            const double e = rms_error(have, want);
+            std::printf("prefill: rms err %.3e\n", e);
+            expect(e <= 2e-2, "prefill (3 terms) within 2e-2 (rms) of the fp64 oracle");
+        }
+    } catch (const std::exception& error) {
+        std::printf("FAILED: exception: %s\n", error.what());
+        return 1;
+    }
+    if (failures) return 1;
+    std::printf("ok\n");
+    return 0;
+}
