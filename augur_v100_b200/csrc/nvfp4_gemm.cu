@@ -17,6 +17,8 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+
 #include "nvfp4_internal.h"
 #include "nvfp4_layout.cuh"
 
@@ -310,6 +312,215 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant__
     }
 }
 
+// ---- two-CTA tiles ------------------------------------------------------------------------------
+// The 128 x 256 tile above pulls 54 KB through L2 -> shared memory per 256-deep k block, and that
+// path, not the tensor pipe, bounds it. Here two CTAs of a cluster (a pair of SMs) share one
+// 256 x 256 tile with tcgen05 cta_group::2: each CTA loads its own 128 token rows (A), its own
+// half of the 256 weight rows (B) and the scales of both, 38 KB per k block for the same
+// 128 x 256 x 256 of arithmetic per SM. The even CTA of the pair (the leader) issues the MMAs for
+// both; each CTA's accumulator half sits in its own tensor memory and is drained by its own
+// epilogue warps.
+//
+// Barriers (same offsets in both CTAs):
+//   full[s]   leader's only: one arrival (leader's producer, expecting the bytes of both CTAs);
+//             both producers' TMA loads complete on it (cta_group::2 loads, leader's address);
+//   empty[s]  one per CTA, arrived by the leader's tcgen05.commit multicast to both CTAs;
+//   tmem_full one per CTA, same multicast;   tmem_empty leader's only, 8 arrivals (4 epilogue
+//             warps of each CTA, the peer's through a cluster-scope arrive).
+constexpr uint32_t kPairStages = 5;
+constexpr uint32_t kPairBytesB = 128 * 128;                                            // this CTA's 128 weight rows
+constexpr uint32_t kPairStageBytes = kBytesA + kPairBytesB + kBytesSfA + kBytesSfB;   // 38912
+constexpr uint32_t kPairSmemBytes = kPairStages * kPairStageBytes + 1024 + 256;
+constexpr uint32_t kLeaderMask = 0xFEFFFFFFu;   // clears the CTA-rank bit of a shared::cluster address within a pair
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// TMA tile load whose bytes are counted on the barrier at `bar`'s offset in the pair's leader CTA.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t x, uint32_t y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar & kLeaderMask)
+        : "memory");
+}
+// Arrives on the barrier at this offset in both CTAs of the pair once the MMAs issued so far are done.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(static_cast<uint16_t>(3))
+                 : "memory");
+}
+__device__ __forceinline__ void tc_copy_sf_pair(uint32_t tmem, uint64_t desc) {
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %6, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n}"
+        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_leader(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar & kLeaderMask) : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant__ CUtensorMap map_weight,
+                 const __grid_constant__ CUtensorMap map_act_sf, const __grid_constant__ CUtensorMap map_weight_sf,
+                 const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kPairStages * kPairStageBytes);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kPairStages + 2);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();            // 0 = leader
+    const uint32_t pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + kPairStages);
+    const uint32_t bar_tmem_full = smem_u32(bars + 2 * kPairStages), bar_tmem_empty = smem_u32(bars + 2 * kPairStages + 1);
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < kPairStages; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        mbar_init(bar_tmem_full, 1);
+        mbar_init(bar_tmem_empty, 8);   // one arrival per epilogue warp of either CTA
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();   // the peer's barriers exist before anything can signal them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const uint32_t m_pairs = p.tokens / (2 * kTileM);
+    const uint32_t n_tiles = p.rows / kTileN;
+    const uint32_t total_tiles = m_pairs * n_tiles;
+    const uint32_t k_blocks = p.cols / kBlockK;
+    const uint32_t steps = k_blocks * p.terms;
+    const uint32_t atoms_per_row_block = p.cols / 64;
+    const uint32_t act_term_atoms = p.tokens / 128 * atoms_per_row_block;   // scale atoms of one activation term
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- TMA producer (both CTAs) ----------------
+        uint32_t stage = 0, phase = 0;
+        bool alive = true;
+        for (uint32_t tile = pair; alive && tile < total_tiles; tile += pairs) {
+            const uint32_t m_pair = tile % m_pairs, n_tile = tile / m_pairs;
+            for (uint32_t step = 0; step < steps; ++step) {
+                const uint32_t kb = step / p.terms, term = step % p.terms;
+                if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status_word, kErrProducerWait)) {
+                    alive = false;
+                    break;
+                }
+                const uint32_t base = smem_u32(smem + stage * kPairStageBytes);
+                const uint32_t full = bar_full + 8 * stage;
+                if (rank == 0) mbar_expect_tx(full, 2 * kPairStageBytes);
+                const uint32_t token_row = m_pair * 2 * kTileM + rank * kTileM;
+                tma_load_2d_pair(base, &map_act, kb * 128, term * p.tokens + token_row, full);
+                tma_load_2d_pair(base + kBytesA, &map_weight, kb * 128, n_tile * kTileN + rank * 128, full);
+                tma_load_2d_pair(base + kBytesA + kPairBytesB, &map_act_sf, 0,
+                                 term * act_term_atoms + (token_row / 128) * atoms_per_row_block + kb * 4, full);
+                tma_load_2d_pair(base + kBytesA + kPairBytesB + kBytesSfA, &map_weight_sf, 0,
+                                 (n_tile * 2) * atoms_per_row_block + kb * 4, full);
+                tma_load_2d_pair(base + kBytesA + kPairBytesB + 2 * kBytesSfA, &map_weight_sf, 0,
+                                 (n_tile * 2 + 1) * atoms_per_row_block + kb * 4, full);
+                if (++stage == kPairStages) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == 1 && lane == 0 && rank == 0) {
+        // ---------------- MMA issuer (leader only) ----------------
+        uint32_t stage = 0, phase = 0, tmem_phase = 0, sf_buffer = 0;
+        bool alive = true;
+        const uint32_t idesc = (1u << 7) | (1u << 10) | ((kTileN >> 3) << 17) | (((2 * kTileM) >> 4) << 24);
+        for (uint32_t tile = pair; alive && tile < total_tiles; tile += pairs) {
+            // the epilogues of both CTAs must have drained the previous tile's accumulator
+            if (!mbar_wait(bar_tmem_empty, tmem_phase ^ 1, abort_flag, p.status_word, kErrMmaWaitTmem)) break;
+            tc_fence_after();
+            for (uint32_t step = 0; step < steps; ++step) {
+                if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status_word, kErrMmaWaitFull)) {
+                    alive = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t base = smem_u32(smem + stage * kPairStageBytes);
+                const uint32_t sfa_smem = base + kBytesA + kPairBytesB, sfb_smem = sfa_smem + kBytesSfA;
+                const uint32_t tmem_sfa = tmem_base + kTmemSfA + sf_buffer * 16;
+                const uint32_t tmem_sfb = tmem_base + kTmemSfB + sf_buffer * 32;
+                const uint64_t a_desc = operand_desc(base), b_desc = operand_desc(base + kBytesA);
+                for (uint32_t k = 0; k < 4; ++k) {
+                    tc_copy_sf_pair(tmem_sfa + 4 * k, sf_desc(sfa_smem + k * kSfAtomBytes));
+                    tc_copy_sf_pair(tmem_sfb + 8 * k, sf_desc(sfb_smem + k * kSfAtomBytes));
+                    tc_copy_sf_pair(tmem_sfb + 8 * k + 4, sf_desc(sfb_smem + kBytesSfA + k * kSfAtomBytes));
+                    tc_mma_pair(tmem_base + kTmemAcc, a_desc + 2 * k, b_desc + 2 * k, idesc, tmem_sfa + 4 * k,
+                                tmem_sfb + 8 * k, (step | k) ? 1u : 0u);
+                }
+                tc_commit_pair(bar_empty + 8 * stage);   // frees the stage in both CTAs
+                sf_buffer ^= 1;
+                if (++stage == kPairStages) { stage = 0; phase ^= 1; }
+            }
+            if (alive) tc_commit_pair(bar_tmem_full);     // both accumulator halves complete
+            tmem_phase ^= 1;
+        }
+    } else if (warp >= 2) {
+        // ---------------- epilogue (both CTAs): own TMEM half -> BF16 -> global ----------------
+        const uint32_t quadrant = warp & 3;
+        uint32_t tmem_phase = 0;
+        for (uint32_t tile = pair; tile < total_tiles; tile += pairs) {
+            const uint32_t m_pair = tile % m_pairs, n_tile = tile / m_pairs;
+            if (!mbar_wait(bar_tmem_full, tmem_phase, abort_flag, p.status_word, kErrEpilogueWait)) break;
+            tc_fence_after();
+            const uint32_t token = m_pair * 2 * kTileM + rank * kTileM + quadrant * 32 + lane;
+            __nv_bfloat16* out_row = p.out + static_cast<uint64_t>(token) * p.rows + n_tile * kTileN;
+            for (uint32_t c = 0; c < kTileN; c += 32) {
+                uint32_t v[32];
+                tc_load32(tmem_base + kTmemAcc + ((quadrant * 32) << 16) + c, v);
+                tc_wait_ld();
+                uint32_t packed[16];
+#pragma unroll
+                for (uint32_t i = 0; i < 16; ++i) {
+                    const __nv_bfloat162 two = __floats2bfloat162_rn(__uint_as_float(v[2 * i]) * p.scale,
+                                                                     __uint_as_float(v[2 * i + 1]) * p.scale);
+                    packed[i] = *reinterpret_cast<const uint32_t*>(&two);
+                }
+                uint4* dst = reinterpret_cast<uint4*>(out_row + c);
+#pragma unroll
+                for (uint32_t i = 0; i < 4; ++i) {
+                    dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_leader(bar_tmem_empty);
+            tmem_phase ^= 1;
+        }
+    }
+
+    // Neither CTA may release tensor memory while the other can still be written by an MMA or read
+    // by an epilogue: every thread of the pair meets here (all waits above are bounded).
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
 // ---- activation quantiser ------------------------------------------------------------------
 // Smallest positive E4M3 code whose value is >= d (d > 0), 126 if none.
 __device__ __forceinline__ uint32_t e4m3_ceil_code(float d) {
@@ -432,6 +643,29 @@ bool make_code_map(CUtensorMap* map, uint64_t address, uint64_t rows, uint32_t c
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Block-scale atoms as a 2-D tensor [atoms][256 x u16] (512 bytes each); a box is the 4 atoms of
+// one 128-row block and one 256-deep k block.
+bool make_scale_map(CUtensorMap* map, uint64_t address, uint64_t atoms) {
+    const EncodeTiled encode = encode_entry();
+    if (!encode) return false;
+    const cuuint64_t dims[2] = {256, atoms};
+    const cuuint64_t strides[1] = {kSfAtomBytes};
+    const cuuint32_t box[2] = {256, 4};
+    const cuuint32_t element_strides[2] = {1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, reinterpret_cast<void*>(address), dims, strides, box,
+                  element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// AUGUR_NVFP4_SM100_GEMM_PAIR=0 keeps every shape on the one-CTA tiles (measurement aid).
+bool pair_tiles_enabled() {
+    static const bool enabled = [] {
+        const char* value = getenv("AUGUR_NVFP4_SM100_GEMM_PAIR");
+        return !(value && value[0] == '0');
+    }();
+    return enabled;
+}
+
 // ---- validation ------------------------------------------------------------------------------------
 bool act_shape_ok(uint32_t tokens, uint32_t cols, uint32_t terms) {
     return tokens && cols && tokens % kTileM == 0 && cols % 64 == 0 && terms >= 1 && terms <= 3 &&
@@ -490,7 +724,9 @@ bool check_gemm(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_p
 }  // namespace
 
 cudaError_t gemm_configure_device() {
-    return cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
+    const cudaError_t e = cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes);
 }
 
 }  // namespace augur_sm100
@@ -560,6 +796,22 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_bf16
     p.status_word = plan->status_word;
     p.rows = a->rows; p.cols = a->cols; p.tokens = a->tokens; p.terms = a->activation_terms;
     p.scale = a->weight_global_scale * a->activation_global_scale;
+    if (pair_tiles_enabled() && a->tokens % (2 * kTileM) == 0 && a->rows % kTileN == 0 && a->cols % kBlockK == 0 &&
+        plan->sm_count >= 2) {
+        // 256 x 256 tiles on pairs of CTAs (clusters of two); the grid is a whole number of pairs.
+        CUtensorMap map_act_sf, map_weight_sf;
+        const uint64_t atoms_per_row_block = a->cols / 64;
+        if (!make_scale_map(&map_weight_sf, reinterpret_cast<uint64_t>(p.weight_sf), (a->rows / 128) * atoms_per_row_block) ||
+            !make_scale_map(&map_act_sf, reinterpret_cast<uint64_t>(p.act_sf),
+                            static_cast<uint64_t>(a->activation_terms) * (a->tokens / 128) * atoms_per_row_block)) {
+            return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE);
+        }
+        uint32_t pairs = (a->tokens / (2 * kTileM)) * (a->rows / kTileN);
+        if (pairs > plan->sm_count / 2) pairs = plan->sm_count / 2;
+        gemm_pair_kernel<<<2 * pairs, kGemmThreads, kPairSmemBytes, s->stream>>>(map_act, map_weight, map_act_sf, map_weight_sf, p);
+        count_launch();
+        return submitted();
+    }
     const uint32_t m_tiles = a->tokens / kTileM, n_tiles = (a->rows + kTileN - 1) / kTileN;
     uint32_t grid = m_tiles * n_tiles;
     if (grid > plan->sm_count) grid = plan->sm_count;

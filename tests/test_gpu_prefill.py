@@ -122,6 +122,22 @@ def test_gemm_many_tiles_persistent(ctx):
     _check_gemm(ctx, rows=5120, cols=512, tokens=1024, seed=5)     # 160 tiles > SM count
 
 
+def test_gemm_pair_tile_single(ctx):
+    _check_gemm(ctx, rows=256, cols=256, tokens=256, seed=7)       # one 256 x 256 tile on one CTA pair, one stage
+
+
+def test_gemm_pair_tile_ring_wrap(ctx):
+    _check_gemm(ctx, rows=512, cols=2304, tokens=512, seed=8)      # 9 k blocks through the 5-stage ring, 4 tiles
+
+
+def test_gemm_pair_tile_residual_terms(ctx):
+    _check_gemm(ctx, rows=256, cols=1024, tokens=256, terms=3, seed=9)
+
+
+def test_gemm_pair_tiles_more_than_pairs(ctx):
+    _check_gemm(ctx, rows=2560, cols=256, tokens=2048, seed=10)    # 80 tiles over at most 74 pairs
+
+
 def test_gemm_residual_terms(ctx):
     e1 = _check_gemm(ctx, rows=256, cols=1024, tokens=128, terms=1, seed=6)
     e3 = _check_gemm(ctx, rows=256, cols=1024, tokens=128, terms=3, seed=6)
