@@ -327,10 +327,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant__
 //   empty[s]  one per CTA, arrived by the leader's tcgen05.commit multicast to both CTAs;
 //   tmem_full one per CTA, same multicast;   tmem_empty leader's only, 8 arrivals (4 epilogue
 //             warps of each CTA, the peer's through a cluster-scope arrive).
-constexpr uint32_t kPairStages = 5;
+constexpr uint32_t kPairStages = 4;
 constexpr uint32_t kPairBytesB = 128 * 128;                                            // this CTA's 128 weight rows
 constexpr uint32_t kPairStageBytes = kBytesA + kPairBytesB + kBytesSfA + kBytesSfB;   // 38912
-constexpr uint32_t kPairSmemBytes = kPairStages * kPairStageBytes + 1024 + 256;
+// Epilogue staging: each epilogue warp parks its 32 rows x 256 BF16 here (rows padded by 16 bytes
+// so that the row-per-lane writes spread over all banks), releases the accumulator, and only
+// then writes the rows out, one coalesced 512-byte row per store instruction.
+constexpr uint32_t kPairOutRowBytes = kTileN * 2 + 16;
+constexpr uint32_t kPairOutBytes = kTileM * kPairOutRowBytes;                          // 67584
+constexpr uint32_t kPairSmemBytes = kPairStages * kPairStageBytes + kPairOutBytes + 1024 + 256;
 constexpr uint32_t kLeaderMask = 0xFEFFFFFFu;   // clears the CTA-rank bit of a shared::cluster address within a pair
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -375,7 +380,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
                  const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kPairStages * kPairStageBytes);
+    uint8_t* out_stage = smem + kPairStages * kPairStageBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(out_stage + kPairOutBytes);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kPairStages + 2);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -484,8 +490,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
             const uint32_t m_pair = tile % m_pairs, n_tile = tile / m_pairs;
             if (!mbar_wait(bar_tmem_full, tmem_phase, abort_flag, p.status_word, kErrEpilogueWait)) break;
             tc_fence_after();
-            const uint32_t token = m_pair * 2 * kTileM + rank * kTileM + quadrant * 32 + lane;
-            __nv_bfloat16* out_row = p.out + static_cast<uint64_t>(token) * p.rows + n_tile * kTileN;
+            // accumulator -> BF16 -> this warp's staging rows (lane = row)
+            uint8_t* my_rows = out_stage + (quadrant * 32) * kPairOutRowBytes;
             for (uint32_t c = 0; c < kTileN; c += 32) {
                 uint32_t v[32];
                 tc_load32(tmem_base + kTmemAcc + ((quadrant * 32) << 16) + c, v);
@@ -497,16 +503,26 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
                                                                      __uint_as_float(v[2 * i + 1]) * p.scale);
                     packed[i] = *reinterpret_cast<const uint32_t*>(&two);
                 }
-                uint4* dst = reinterpret_cast<uint4*>(out_row + c);
+                uint4* dst = reinterpret_cast<uint4*>(my_rows + lane * kPairOutRowBytes + c * 2);
 #pragma unroll
                 for (uint32_t i = 0; i < 4; ++i) {
                     dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
                 }
             }
+            // the accumulator is free for the next tile's MMAs from here on
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_leader(bar_tmem_empty);
             tmem_phase ^= 1;
+            // staging rows -> global: one whole 512-byte row per instruction
+            const uint32_t first_token = m_pair * 2 * kTileM + rank * kTileM + quadrant * 32;
+            uint8_t* out_base = reinterpret_cast<uint8_t*>(p.out + static_cast<uint64_t>(first_token) * p.rows + n_tile * kTileN);
+#pragma unroll 4
+            for (uint32_t r = 0; r < 32; ++r) {
+                const uint4 value = *reinterpret_cast<const uint4*>(my_rows + r * kPairOutRowBytes + lane * 16);
+                *reinterpret_cast<uint4*>(out_base + static_cast<uint64_t>(r) * p.rows * 2 + lane * 16) = value;
+            }
+            __syncwarp();   // the rows are rewritten for the next tile
         }
     }
 
