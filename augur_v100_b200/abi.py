@@ -81,6 +81,16 @@ class MlpArgs(Structure):
                 ("gate_up", GemvArgs), ("down", GemvArgs)]
 
 
+MAX_TP_RANKS = 8
+
+
+class MlpTpArgs(Structure):
+    _fields_ = [("abi_version", c_uint32), ("struct_size", c_uint32),
+                ("gate_up", GemvArgs), ("down", GemvArgs),
+                ("exchange", c_uint64 * MAX_TP_RANKS), ("exchange_len_bytes", c_uint64),
+                ("world", c_uint32), ("rank", c_uint32), ("sequence", c_uint32), ("reserved", c_uint32)]
+
+
 class ActQuantArgs(Structure):
     _fields_ = [("abi_version", c_uint32), ("struct_size", c_uint32),
                 ("input_bf16", c_uint64), ("input_len_bytes", c_uint64),
@@ -123,6 +133,9 @@ EXPORTS = {
     "augur_cuda_nvfp4_sm100_gemv_bf16_static_scratch_submit_v1": (Result, [c_int32, c_void_p, POINTER(GemvArgs)]),
     "augur_cuda_nvfp4_sm100_mlp_preflight_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(MlpArgs)]),
     "augur_cuda_nvfp4_sm100_mlp_prevalidated_submit_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(MlpArgs)]),
+    "augur_cuda_nvfp4_sm100_mlp_tp_exchange_extent_host_v1": (Result, [c_uint32, c_uint32, POINTER(c_uint64)]),
+    "augur_cuda_nvfp4_sm100_mlp_tp_preflight_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(MlpTpArgs)]),
+    "augur_cuda_nvfp4_sm100_mlp_tp_prevalidated_submit_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(MlpTpArgs)]),
     "augur_cuda_nvfp4_sm100_act_quant_preflight_v1": (Result, [c_int32, c_void_p, POINTER(ActQuantArgs)]),
     "augur_cuda_nvfp4_sm100_act_quant_prevalidated_submit_v1": (Result, [c_int32, c_void_p, POINTER(ActQuantArgs)]),
     "augur_cuda_nvfp4_sm100_gemm_bf16_preflight_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(GemmArgs)]),

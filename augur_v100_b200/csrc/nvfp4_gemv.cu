@@ -66,6 +66,9 @@ struct GemvParams {
     uint32_t groups, kb_count, slabs, ctas_per_slab, max_contrib, unit;
     uint32_t rows, cols, tokens, epilogue;
     float global_a, global_b;
+    // Tensor-parallel exchange (tp_world == 0: none): every rank's exchange buffer as mapped here.
+    uint64_t exchange[AUGUR_NVFP4_SM100_MAX_TP_RANKS];
+    uint32_t tp_world, tp_rank, tp_sequence;
 };
 
 struct GemvGeometry {
@@ -252,7 +255,107 @@ __device__ __forceinline__ uint32_t shift_bf16(uint32_t bits, int shift) {
     return (bits & 0x807fu) | (static_cast<uint32_t>(moved > 254 ? 254 : moved) << 7);
 }
 
+// ---- tensor-parallel exchange ------------------------------------------------------------------
+// Row-parallel down projection over `tp_world` GPUs: every rank holds a k-slice and produces a
+// full-width partial sum; the all-reduce is done here, by the warp that finishes a row group,
+// instead of by a collective launched afterwards. Exchange buffer of a rank (same layout on all):
+//   [sequence parity][source rank][row group][32 lanes][4 lines of 16 bytes]
+// where a line is {value, sequence, value, sequence}: every 8-byte half carries its own flag, an
+// aligned 8-byte store becomes visible as a whole, so the receiver needs no fence - it polls the
+// lines themselves until both flags show the sequence it is waiting for. The warp stores its tile
+// (256 f32 as 128 lines) into the slot [parity][own rank][group] of every other rank's buffer
+// (peer stores over NVLink), then reads the other ranks' tiles of the same group from its own
+// buffer - waiting, bounded, for lines that have not arrived - and adds all tiles in rank order,
+// its own from registers. Every rank adds the same values in the same order, so all ranks hold
+// bit-identical results. Two parities suffice: a source can only overwrite a slot two sequences
+// later, and it cannot start the next sequence before this rank has delivered all of its tiles
+// of the current one, i.e. after this rank has finished the one before.
+constexpr uint32_t kExchangeWaitLimit = 1u << 22;   // polls: gives up after a fraction of a second
+constexpr uint32_t kExchangeTileBytes = kSlotFloats * 8;
+
+__host__ __device__ constexpr uint64_t exchange_extent(uint32_t world, uint32_t groups) {
+    return 2ull * world * groups * kExchangeTileBytes;
+}
+
+// exchange[r] by a chain of selects: a run-time index into kernel parameters would put the table on the stack.
+__device__ __forceinline__ uint64_t exchange_base(const GemvParams& p, uint32_t r) {
+    uint64_t base = p.exchange[0];
+#pragma unroll
+    for (uint32_t i = 1; i < AUGUR_NVFP4_SM100_MAX_TP_RANKS; ++i) {
+        if (r == i) base = p.exchange[i];
+    }
+    return base;
+}
+
+__device__ __forceinline__ void exchange_and_store(const GemvParams& p, uint32_t group, const float (&v)[8], uint32_t lane) {
+    const uint32_t world = p.tp_world, parity = p.tp_sequence & 1, seq = p.tp_sequence;
+    const uint64_t own = exchange_base(p, p.tp_rank);
+    auto slot_offset = [&](uint32_t src) {
+        return ((static_cast<uint64_t>(parity) * world + src) * p.groups + group) * kExchangeTileBytes + lane * 64;
+    };
+    float mine[8];
+#pragma unroll
+    for (uint32_t i = 0; i < 8; ++i) mine[i] = v[i] * p.global_a;
+    const uint64_t my_offset = slot_offset(p.tp_rank);
+#pragma unroll
+    for (uint32_t d = 0; d < AUGUR_NVFP4_SM100_MAX_TP_RANKS; ++d) {
+        if (d < world && d != p.tp_rank) {
+            const uint64_t dst = p.exchange[d] + my_offset;
+#pragma unroll
+            for (uint32_t j = 0; j < 4; ++j) {
+                asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %2};"
+                             ::"l"(dst + j * 16), "r"(__float_as_uint(mine[2 * j])), "r"(seq), "r"(__float_as_uint(mine[2 * j + 1]))
+                             : "memory");
+            }
+        }
+    }
+    float sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    bool arrived = true;
+    for (uint32_t src = 0; src < world; ++src) {
+        if (src == p.tp_rank) {
+#pragma unroll
+            for (uint32_t i = 0; i < 8; ++i) sum[i] += mine[i];
+            continue;
+        }
+        const uint64_t from = own + slot_offset(src);
+        uint32_t line[4][4];
+        uint32_t spin = 0;
+        for (;;) {
+            bool ready = true;
+#pragma unroll
+            for (uint32_t j = 0; j < 4; ++j) {
+                asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(line[j][0]), "=r"(line[j][1]), "=r"(line[j][2]), "=r"(line[j][3])
+                             : "l"(from + j * 16)
+                             : "memory");
+                ready = ready && line[j][1] == seq && line[j][3] == seq;
+            }
+            if (ready) break;
+            if (++spin > kExchangeWaitLimit) { arrived = false; break; }
+        }
+#pragma unroll
+        for (uint32_t j = 0; j < 4; ++j) {
+            sum[2 * j] += __uint_as_float(line[j][0]);
+            sum[2 * j + 1] += __uint_as_float(line[j][2]);
+        }
+    }
+    if (!__all_sync(0xffffffffu, arrived) && lane == 0) atomicCAS(p.status_word, 0u, 0x203u);   // a peer's tile never arrived
+    const uint32_t g = lane >> 2, t4 = lane & 3;
+#pragma unroll
+    for (uint32_t i = 0; i < 8; ++i) {
+        const uint32_t token = 2 * t4 + (i & 1);
+        const uint32_t row = group * 32 + (i >> 2) * 16 + g + ((i >> 1) & 1) * 8;
+        if (token < p.tokens) {
+            static_cast<__nv_bfloat16*>(p.out)[static_cast<uint64_t>(token) * p.rows + row] = __float2bfloat16_rn(sum[i]);
+        }
+    }
+}
+
 __device__ __forceinline__ void epilogue(const GemvParams& p, uint32_t group, const float (&v)[8], uint32_t lane) {
+    if (p.tp_world) {
+        exchange_and_store(p, group, v, lane);
+        return;
+    }
     const uint32_t g = lane >> 2, t4 = lane & 3;
     if (p.epilogue == AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16) {
         __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
@@ -772,7 +875,8 @@ bool check_gemv(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_p
 // exponent), so no staging kernel runs.
 void launch_gemv(augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* plan,
                  const augur_cuda_nvfp4_sm100_gemv_args_v1* a, uint32_t member, uint64_t partial_offset,
-                 uint64_t staged_out_offset = 0, bool input_is_staged = false) {
+                 uint64_t staged_out_offset = 0, bool input_is_staged = false,
+                 const augur_cuda_nvfp4_sm100_mlp_tp_args_v1* tp = nullptr) {
     const bool pair = a->epilogue == AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16;
     const GemvGeometry g = geometry(a->rows, a->cols, pair, plan->sm_count);
     GemvParams p{};
@@ -794,6 +898,10 @@ void launch_gemv(augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* pl
     p.max_contrib = g.max_contrib;
     p.rows = a->rows; p.cols = a->cols; p.tokens = a->tokens; p.epilogue = a->epilogue;
     p.global_a = a->global_scale; p.global_b = a->global_scale_b;
+    if (tp) {
+        for (uint32_t r = 0; r < tp->world; ++r) p.exchange[r] = tp->exchange[r];
+        p.tp_world = tp->world; p.tp_rank = tp->rank; p.tp_sequence = tp->sequence;
+    }
     // Launched with programmatic stream serialisation: the grid may become resident while its
     // predecessor drains, and waits for it in-kernel (griddepcontrol.wait).
     cudaLaunchAttribute attribute{};
@@ -922,6 +1030,86 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_mlp_preva
     augur_cuda_result_v1 first = submitted();
     if (first.status != AUGUR_CUDA_STATUS_OK) return first;
     launch_gemv(s, plan, &a->down, 1, down_offset, 0, true);
+    return submitted();
+}
+
+// ---- tensor-parallel MLP program -------------------------------------------------------------------
+namespace {
+static_assert(sizeof(augur_cuda_nvfp4_sm100_mlp_tp_args_v1) == 272, "mlp_tp ABI");
+
+bool check_mlp_tp(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* plan,
+                  const augur_cuda_nvfp4_sm100_mlp_tp_args_v1* a, bool full, uint64_t* down_offset,
+                  augur_cuda_result_v1* failure) {
+    *failure = invalid();
+    if (!header_ok(d, s, a)) {
+        if (a && s && d >= 0 && s->ordinal == d && a->abi_version != AUGUR_CUDA_ABI_VERSION_V1) {
+            *failure = make_result(AUGUR_CUDA_STATUS_ABI_VERSION_MISMATCH);
+        }
+        return false;
+    }
+    // The two members are checked exactly as a single-GPU program is.
+    augur_cuda_nvfp4_sm100_mlp_args_v1 local{};
+    local.abi_version = AUGUR_CUDA_ABI_VERSION_V1;
+    local.struct_size = sizeof(local);
+    local.gate_up = a->gate_up;
+    local.down = a->down;
+    if (!check_mlp(d, s, plan, &local, full, down_offset, failure)) return false;
+    *failure = invalid();
+    if (a->reserved || a->world < 1 || a->world > AUGUR_NVFP4_SM100_MAX_TP_RANKS || a->rank >= a->world || a->sequence == 0 ||
+        a->down.epilogue != AUGUR_NVFP4_SM100_EPILOGUE_LINEAR_BF16) {
+        return false;
+    }
+    if (a->exchange_len_bytes < exchange_extent(a->world, a->down.rows / 32)) return false;
+    for (uint32_t r = 0; r < AUGUR_NVFP4_SM100_MAX_TP_RANKS; ++r) {
+        if (r >= a->world) {
+            if (a->exchange[r]) return false;
+            continue;
+        }
+        if (!a->exchange[r] || a->exchange[r] % 256 != 0) return false;
+        for (uint32_t q = 0; q < r; ++q) {
+            if (!disjoint({a->exchange[r], a->exchange_len_bytes, 256}, {a->exchange[q], a->exchange_len_bytes, 256})) return false;
+        }
+    }
+    // This rank's own exchange buffer is local memory like any other range of the program.
+    const Range r[7] = {{a->gate_up.weight, a->gate_up.weight_len_bytes, 256},
+                        {a->gate_up.input_bf16, a->gate_up.input_len_bytes, 16},
+                        {a->gate_up.output, a->gate_up.output_len_bytes, 16},
+                        {a->down.weight, a->down.weight_len_bytes, 256},
+                        {a->down.output, a->down.output_len_bytes, 4},
+                        plan_scratch_range(plan),
+                        {a->exchange[a->rank], a->exchange_len_bytes, 256}};
+    return all_disjoint(r, 7);
+}
+}  // namespace
+
+extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_mlp_tp_exchange_extent_host_v1(
+    uint32_t rows, uint32_t world, uint64_t* out_bytes) {
+    if (!out_bytes || !rows || rows % 32 != 0 || world < 1 || world > AUGUR_NVFP4_SM100_MAX_TP_RANKS) return invalid();
+    *out_bytes = exchange_extent(world, rows / 32);
+    return ok();
+}
+
+extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_mlp_tp_preflight_v1(
+    int32_t d, augur_cuda_stream_t s, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_mlp_tp_args_v1* a) {
+    augur_cuda_result_v1 failure;
+    uint64_t down_offset = 0;
+    return check_mlp_tp(d, s, plan, a, true, &down_offset, &failure) ? ok() : failure;
+}
+
+extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_mlp_tp_prevalidated_submit_v1(
+    int32_t d, augur_cuda_stream_t s, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_mlp_tp_args_v1* a) {
+    augur_cuda_result_v1 failure;
+    uint64_t down_offset = 0;
+    if (!check_mlp_tp(d, s, plan, a, false, &down_offset, &failure)) return failure;
+    if (consume_injected_fault()) return make_result(AUGUR_CUDA_STATUS_DIAGNOSTIC_FAULT_INJECTED);
+    const cudaError_t e = cudaSetDevice(d);
+    if (e != cudaSuccess) return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE, e);
+    launch_gemv(s, plan, &a->gate_up, 0, kCounterBytes, down_offset, false);
+    augur_cuda_result_v1 first = submitted();
+    if (first.status != AUGUR_CUDA_STATUS_OK) return first;
+    launch_gemv(s, plan, &a->down, 1, down_offset, 0, true, a);
     return submitted();
 }
 

@@ -6,6 +6,13 @@ SiLU(gate)*up locally. Row-parallel down: rank r owns k-columns [r*I/p, (r+1)*I/
 down matrix (a strided slice: I/(2p) code bytes and I/(16p) scale bytes of every row) and
 produces a full-width [tokens, hidden] partial sum. One all-reduce (sum) of that partial
 completes the block; the reference has no multi-GPU code, this is the only exchange step.
+
+Two ways to do that exchange:
+
+* fused (default when the ranks can map each other's memory): the down launch itself delivers
+  every finished 32-row tile to all ranks over NVLink and adds the ranks' tiles in rank order
+  (``augur_cuda_nvfp4_sm100_mlp_tp_*``); f32 partial sums, one rounding, no collective launch;
+* NCCL: the local program writes a BF16 partial and ``torch.distributed.all_reduce`` sums it.
 """
 from __future__ import annotations
 
@@ -46,10 +53,89 @@ def shard_mlp(gate, up, down, rank: int, world: int):
     return (gc, gs, gate[2]), (uc, us, up[2]), (dc, ds, down[2])
 
 
-class TensorParallelMlp:
-    """One rank's share of the MLP block: local FFN program + all-reduce of the BF16 output."""
+def exchange_extent(hidden: int, world: int) -> int:
+    """Bytes of one rank's exchange buffer for a down projection with `hidden` output rows."""
+    from ctypes import byref, c_uint64
 
-    def __init__(self, plan, gate, up, down, x, rank: int, world: int, process_group=None):
+    from . import abi
+    out = c_uint64()
+    result = abi.lib().augur_cuda_nvfp4_sm100_mlp_tp_exchange_extent_host_v1(hidden, world, byref(out))
+    if result.status != abi.STATUS_OK:
+        raise ValueError(f"no exchange layout for hidden={hidden}, world={world}")
+    return int(out.value)
+
+
+class ExchangeBuffers:
+    """Peer-mapped exchange buffers of all ranks plus the sequence counter they share.
+
+    One object serves every layer with the same hidden size: layers run one after another on the
+    rank's stream, and the sequence number grows by one per submitted program on every rank alike.
+    Device memory comes from torch's symmetric-memory allocator (plumbing: it creates the
+    allocation, exchanges the handles between the processes and maps every peer's buffer here).
+    """
+
+    def __init__(self, hidden: int, rank: int, world: int, process_group=None):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        group = process_group if process_group is not None else dist.group.WORLD
+        self.rank, self.world, self.hidden = rank, world, hidden
+        self.bytes = exchange_extent(hidden, world)
+        self.tensor = symm.empty(self.bytes, dtype=torch.uint8, device=torch.device("cuda", torch.cuda.current_device()))
+        self.handle = symm.rendezvous(self.tensor, group)
+        self.pointers = [int(p) for p in self.handle.buffer_ptrs]
+        if len(self.pointers) != world or self.pointers[rank] != self.tensor.data_ptr():
+            raise RuntimeError("symmetric-memory rendezvous returned an unexpected pointer table")
+        self.tensor.zero_()
+        torch.cuda.synchronize()
+        dist.barrier(group=group)   # nobody publishes a flag before every buffer is zero
+        self.sequence = 0
+
+    def next_sequence(self) -> int:
+        self.sequence += 1
+        return self.sequence
+
+
+class FusedExchangeProgram:
+    """A bound FFN program of this rank's shards whose down launch also does the all-reduce."""
+
+    def __init__(self, program, exchange: ExchangeBuffers):
+        from ctypes import byref
+
+        from . import abi, host
+        down_rows = program.args.down.rows
+        if exchange.hidden != down_rows:
+            raise ValueError("exchange buffers were made for another hidden size")
+        args = abi.header(abi.MlpTpArgs)
+        args.gate_up, args.down = program.args.gate_up, program.args.down
+        for r, pointer in enumerate(exchange.pointers):
+            args.exchange[r] = pointer
+        args.exchange_len_bytes, args.world, args.rank, args.sequence = exchange.bytes, exchange.world, exchange.rank, 1
+        plan = program.plan
+        host._check("mlp_tp_preflight", abi.lib().augur_cuda_nvfp4_sm100_mlp_tp_preflight_v1(
+            plan.stream.ordinal, plan.stream.handle, plan.handle, byref(args)))
+        self.program, self.exchange, self.args = program, exchange, args
+
+    @property
+    def out(self):
+        return self.program.out
+
+    def submit_for_plan(self) -> None:
+        from ctypes import byref
+
+        from . import abi, host
+        self.args.sequence = self.exchange.next_sequence()
+        plan = self.program.plan
+        host._check("mlp_tp_submit", abi.lib().augur_cuda_nvfp4_sm100_mlp_tp_prevalidated_submit_v1(
+            plan.stream.ordinal, plan.stream.handle, plan.handle, byref(self.args)))
+
+
+class TensorParallelMlp:
+    """One rank's share of the MLP block, with the all-reduce fused into the down launch
+    (`exchange` given) or done by NCCL on the BF16 partial (`exchange` None)."""
+
+    def __init__(self, plan, gate, up, down, x, rank: int, world: int, process_group=None, exchange=None,
+                 out=None):
         from . import abi, host
         hidden, intermediate = gate[0].shape[1] * 2, gate[0].shape[0]
         check_shardable(hidden, intermediate, world)
@@ -59,15 +145,19 @@ class TensorParallelMlp:
         self.gate_up = host.Nvfp4Sm100Weight.upload_checkpoint_nvfp4(
             stream, abi.LAYOUT_STREAM_PAIR, shard, hidden, g[0], g[1], g[2], u[0], u[1], u[2])
         self.down = host.Nvfp4Sm100Weight.upload_checkpoint_nvfp4(stream, abi.LAYOUT_STREAM, hidden, shard, *d)
-        self.program = host.Nvfp4Sm100FfnProgram.bind(plan, self.gate_up, self.down, x)
+        self.program = host.Nvfp4Sm100FfnProgram.bind(plan, self.gate_up, self.down, x, out=out)
         self.world, self.group = world, process_group
+        self.fused = FusedExchangeProgram(self.program, exchange) if exchange is not None else None
 
     @property
     def out(self):
         return self.program.out
 
     def submit(self) -> None:
-        """Enqueue the local block and, with more than one rank, the all-reduce of its output."""
+        """Enqueue the block; the result is the full sum on every rank when the call's work is done."""
+        if self.fused is not None:
+            self.fused.submit_for_plan()
+            return
         self.program.submit_for_plan()
         if self.world > 1:
             import torch.distributed as dist

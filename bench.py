@@ -239,10 +239,32 @@ def run_library(args):
     programs = [host.Nvfp4Sm100FfnProgram.bind(plan, gate_up, down, x, out=outs[index % 2])
                 for index, (gate_up, down) in enumerate(layers)]
 
+    # With more than one rank the all-reduce is fused into the down launch (peer stores over NVLink);
+    # --allreduce nccl, or a failed symmetric-memory set-up (reported in the line), uses NCCL instead.
+    exchange_note = None
+    if world > 1 and args.allreduce == "fused":
+        from augur_v100_b200 import tp
+        failure = None
+        try:
+            exchange = tp.ExchangeBuffers(HIDDEN, rank, world)
+            fused_programs = [tp.FusedExchangeProgram(program, exchange) for program in programs]
+        except Exception as error:  # reported in the line, never hidden
+            failure = repr(error)
+        agree = torch.tensor([0 if failure else 1], device=device)
+        dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+        if int(agree.item()) == 1:
+            programs = fused_programs
+            exchange_note = "fused into the down launch: f32 tiles stored to every rank over NVLink, flags, rank-order sum"
+        else:
+            exchange_note = f"NCCL bf16 8x5120 per layer (fused exchange set-up failed on some rank: {failure})"
+    elif world > 1:
+        exchange_note = "NCCL bf16 8x5120 per layer"
+    use_nccl = world > 1 and not (exchange_note or "").startswith("fused")
+
     def step():
         for index, program in enumerate(programs):
             program.submit_for_plan()
-            if world > 1:
+            if use_nccl:
                 dist.all_reduce(outs[index % 2])
 
     def barrier():
@@ -310,7 +332,7 @@ def run_library(args):
         "config": {"workload": f"config1: NVFP4 MLP block (gate|up+SwiGLU, down), M={TOKENS}, hidden {HIDDEN}, "
                                f"intermediate {INTER}, {LAYERS} distinct layers per step",
                    "l2": f"inputs larger than L2: {LAYERS * 3 * HIDDEN * INTER * 9 // 16 // world} weight bytes per GPU per step",
-                   "parallelism": f"tp{world}" if world > 1 else "single", "all_reduce": "NCCL bf16 8x5120 per layer" if world > 1 else None},
+                   "parallelism": f"tp{world}" if world > 1 else "single", "all_reduce": exchange_note},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      # dram__bytes_read.sum + dram__bytes_write.sum of one gate|up launch plus one down launch
                      # (single GPU, full shapes), from the ncu capture summarised under profiles/
@@ -344,6 +366,8 @@ def main():
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", choices=["library", "reference"], default="library")
     parser.add_argument("--no-prefill", action="store_true", help="skip the M=4096 tcgen05 probe at N=1")
+    parser.add_argument("--allreduce", choices=["fused", "nccl"], default="fused",
+                        help="N>1: all-reduce inside the down launch over peer memory, or NCCL on the BF16 partials")
     parser.add_argument("--layers", type=int, default=LAYERS,
                         help="distinct layers streamed per step (smaller values are for profiler captures only)")
     args = parser.parse_args()

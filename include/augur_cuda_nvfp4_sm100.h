@@ -271,6 +271,45 @@ augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_mlp_prevalidated_sub
     int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
     const augur_cuda_nvfp4_sm100_mlp_args_v1* args);
 
+/* ---- tensor-parallel MLP program: the all-reduce inside the down launch --------- */
+/* No counterpart in the reference (it has no multi-GPU code). Column-parallel gate|up and
+ * row-parallel down over up to 8 GPUs of one box, one process per GPU: every rank passes its
+ * own shard in `gate_up` / `down` exactly as for mlp_*_v1, plus the exchange buffers of all
+ * ranks as they are mapped into this process (peer-accessible device memory of
+ * exchange_len_bytes each, zero-filled once before the first submit; exchange[rank] is this
+ * rank's own). The warp that completes a 32-row group of the down projection stores its f32
+ * tile, each value paired with `sequence` as its flag, into every other rank's buffer over
+ * NVLink, waits (bounded) for the same group of every other rank in its own buffer and writes
+ * bf16(sum over ranks, in rank order) to down.output: all ranks end up with the same
+ * full-width [tokens][rows] result and no collective is launched. `sequence` starts at 1 and grows by exactly 1 with every submit,
+ * in step on all ranks. All ranks' kernels must be able to run at the same time (one process
+ * and one GPU per rank). A wait that runs out sets the plan's status word to 0x203.
+ * Peer buffers cannot be inspected from this process: preflight checks them for alignment,
+ * size and overlap only. */
+#define AUGUR_NVFP4_SM100_MAX_TP_RANKS 8
+typedef struct augur_cuda_nvfp4_sm100_mlp_tp_args_v1 {
+    uint32_t abi_version;
+    uint32_t struct_size;
+    augur_cuda_nvfp4_sm100_gemv_args_v1 gate_up;
+    augur_cuda_nvfp4_sm100_gemv_args_v1 down;
+    augur_cuda_device_ptr_t exchange[AUGUR_NVFP4_SM100_MAX_TP_RANKS];  /* entries >= world are 0 */
+    uint64_t exchange_len_bytes;
+    uint32_t world;
+    uint32_t rank;
+    uint32_t sequence;
+    uint32_t reserved;
+} augur_cuda_nvfp4_sm100_mlp_tp_args_v1;
+
+/* Bytes of one rank's exchange buffer for a down projection with `rows` output rows. */
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_mlp_tp_exchange_extent_host_v1(
+    uint32_t rows, uint32_t world, uint64_t* out_bytes);
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_mlp_tp_preflight_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_mlp_tp_args_v1* args);
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_mlp_tp_prevalidated_submit_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_mlp_tp_args_v1* args);
+
 /* ---- prefill: activation quantiser + tcgen05 block-scaled GEMM --------------- */
 /* Replaces the W4A4 interstage quantiser (augur_cuda_runtime.h:6983 ff.;
  * native augur_nvfp4_cutlass_sm120.cu:455-503): BF16 rows -> E2M1 codes with one

@@ -34,6 +34,7 @@ def test_struct_sizes_match_the_static_asserts():
     assert ctypes.sizeof(abi.DequantArgs) == 80
     assert ctypes.sizeof(abi.GemvArgs) == 88
     assert ctypes.sizeof(abi.MlpArgs) == 184
+    assert ctypes.sizeof(abi.MlpTpArgs) == 272
     assert ctypes.sizeof(abi.ActQuantArgs) == 56
     assert ctypes.sizeof(abi.GemmArgs) == 80
     assert ctypes.sizeof(abi.Result) == 8
@@ -207,6 +208,22 @@ def test_null_and_foreign_handles_are_rejected():
     assert lib.augur_cuda_nvfp4_sm100_plan_create_v1(0, None, 1024, byref(out)).status == abi.STATUS_INVALID_ARGUMENT
     assert lib.augur_cuda_nvfp4_sm100_plan_destroy_v1(None).status == abi.STATUS_INVALID_ARGUMENT
     lib.augur_cuda_nvfp4_sm100_stream_destroy_v1(stream)
+
+
+def test_exchange_extent_and_tp_argument_checks():
+    lib = abi.lib()
+    out = ctypes.c_uint64()
+    # [2 parities][world][groups] tiles of 256 {value, flag} pairs
+    assert lib.augur_cuda_nvfp4_sm100_mlp_tp_exchange_extent_host_v1(5120, 8, ctypes.byref(out)).status == abi.STATUS_OK
+    assert out.value == 2 * 8 * 160 * 2048
+    assert lib.augur_cuda_nvfp4_sm100_mlp_tp_exchange_extent_host_v1(64, 2, ctypes.byref(out)).status == abi.STATUS_OK
+    assert out.value == 2 * 2 * 2 * 2048
+    for rows, world in ((5120, 0), (5120, 9), (5100, 2), (0, 2)):
+        assert lib.augur_cuda_nvfp4_sm100_mlp_tp_exchange_extent_host_v1(rows, world, ctypes.byref(out)).status == abi.STATUS_INVALID_ARGUMENT
+    # without a stream and a plan nothing is looked at, on either entry
+    args = abi.header(abi.MlpTpArgs)
+    assert lib.augur_cuda_nvfp4_sm100_mlp_tp_preflight_v1(0, None, None, ctypes.byref(args)).status == abi.STATUS_INVALID_ARGUMENT
+    assert lib.augur_cuda_nvfp4_sm100_mlp_tp_prevalidated_submit_v1(0, None, None, ctypes.byref(args)).status == abi.STATUS_INVALID_ARGUMENT
 
 
 def test_scratch_extents():

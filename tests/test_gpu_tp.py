@@ -1,4 +1,5 @@
-"""Tensor-parallel MLP on real GPUs (needs at least two): NCCL all-reduce of the BF16 partial outputs."""
+"""Tensor-parallel MLP on real GPUs (needs at least two): the all-reduce fused into the down launch
+(peer stores and flags over NVLink), and the NCCL all-reduce of BF16 partial outputs."""
 import os
 import socket
 
@@ -18,7 +19,7 @@ def _inputs():
     return gate, up, down, x
 
 
-def _worker(rank, world, port, queue):
+def _worker(rank, world, port, queue, fused):
     import torch
     import torch.distributed as dist
     from augur_v100_b200 import host, tp
@@ -30,21 +31,28 @@ def _worker(rank, world, port, queue):
     stream = host.Stream(rank)
     plan = host.Plan(stream, host.mlp_scratch_bytes(HIDDEN, INTER // world))
     x = torch.from_numpy(x_bits.view(np.int16)).to(torch.device("cuda", rank)).view(torch.bfloat16)
-    block = tp.TensorParallelMlp(plan, gate, up, down, x, rank, world)
-    for _ in range(2):
+    exchange = tp.ExchangeBuffers(HIDDEN, rank, world) if fused else None
+    block = tp.TensorParallelMlp(plan, gate, up, down, x, rank, world, exchange=exchange)
+    # Different inputs on consecutive submits: a tile or a flag left over from an earlier
+    # sequence (same parity two submits back) would show in the last result.
+    final = x.clone()
+    for scale in (0.5, 2.0, -1.0, 1.0):
+        x.copy_(final * scale)
         block.submit()
     torch.cuda.synchronize()
-    if rank == 0:
-        queue.put(block.out.view(torch.int16).cpu().numpy().view(np.uint16))
+    assert plan.device_status() == 0
+    queue.put((rank, block.out.view(torch.int16).cpu().numpy().view(np.uint16)))
     dist.barrier()
     dist.destroy_process_group()
     plan.close()
 
 
-def test_two_rank_tensor_parallel_mlp_matches_oracle():
+@pytest.mark.parametrize("world,fused", [(2, True), (2, False), (4, True), (8, True)],
+                         ids=["2-fused-exchange", "2-nccl", "4-fused-exchange", "8-fused-exchange"])
+def test_tensor_parallel_mlp_matches_oracle(world, fused):
     import torch
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
     import oracle
     from augur_v100_b200 import synth
@@ -53,10 +61,14 @@ def test_two_rank_tensor_parallel_mlp_matches_oracle():
         port = s.getsockname()[1]
     ctx = mp.get_context("spawn")
     queue = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, queue)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, queue, fused)) for r in range(world)]
     for p in procs:
         p.start()
-    got = queue.get(timeout=300)
+    results = dict(queue.get(timeout=300) for _ in range(world))
+    got = results[0]
+    if fused:   # every rank adds the same tiles in the same order
+        for rank in range(1, world):
+            assert np.array_equal(results[0], results[rank])
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
