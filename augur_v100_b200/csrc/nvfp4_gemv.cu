@@ -257,19 +257,25 @@ __device__ __forceinline__ uint32_t shift_bf16(uint32_t bits, int shift) {
 
 // ---- tensor-parallel exchange ------------------------------------------------------------------
 // Row-parallel down projection over `tp_world` GPUs: every rank holds a k-slice and produces a
-// full-width partial sum; the all-reduce is done here, by the warp that finishes a row group,
-// instead of by a collective launched afterwards. Exchange buffer of a rank (same layout on all):
+// full-width partial sum; the all-reduce is done inside this kernel instead of by a collective
+// launched afterwards. Exchange buffer of a rank (same layout on all):
 //   [sequence parity][source rank][row group][32 lanes][4 lines of 16 bytes]
 // where a line is {value, sequence, value, sequence}: every 8-byte half carries its own flag, an
-// aligned 8-byte store becomes visible as a whole, so the receiver needs no fence - it polls the
-// lines themselves until both flags show the sequence it is waiting for. The warp stores its tile
-// (256 f32 as 128 lines) into the slot [parity][own rank][group] of every other rank's buffer
-// (peer stores over NVLink), then reads the other ranks' tiles of the same group from its own
-// buffer - waiting, bounded, for lines that have not arrived - and adds all tiles in rank order,
-// its own from registers. Every rank adds the same values in the same order, so all ranks hold
-// bit-identical results. Two parities suffice: a source can only overwrite a slot two sequences
-// later, and it cannot start the next sequence before this rank has delivered all of its tiles
-// of the current one, i.e. after this rank has finished the one before.
+// aligned 8-byte store becomes visible as a whole, so a reader needs no fence - it polls the
+// lines themselves until both flags show the sequence it is waiting for.
+//   push   : the warp that finishes a row group stores its tile (256 f32 as 128 lines) into the
+//            slot [parity][own rank][group] of EVERY rank's buffer, its own included (peer
+//            stores over NVLink), and goes on;
+//   reduce : at the end of the kernel every row group is taken by one warp of the grid (static
+//            assignment, independent of who finished it), which reads the tiles of all ranks
+//            for that group from its own rank's buffer - waiting, bounded, for lines that have
+//            not arrived - adds them in rank order and writes the BF16 result.
+// Every rank adds the same values in the same order, so all ranks hold bit-identical results.
+// Two parities suffice: a source can only overwrite a slot two sequences later, and it cannot
+// start the next sequence before this rank has delivered all of its tiles of the current one,
+// i.e. after this rank has finished the one before. The reduce step waits for tiles that other
+// CTAs of the same grid produce, so the grid must be co-resident (the entry point checks that it
+// does not exceed the SM count).
 constexpr uint32_t kExchangeWaitLimit = 1u << 22;   // polls: gives up after a fraction of a second
 constexpr uint32_t kExchangeTileBytes = kSlotFloats * 8;
 
@@ -286,74 +292,90 @@ __device__ __forceinline__ uint64_t exchange_base(const GemvParams& p, uint32_t 
     }
     return base;
 }
+__device__ __forceinline__ uint64_t exchange_slot(const GemvParams& p, uint32_t src, uint32_t group, uint32_t lane) {
+    return ((static_cast<uint64_t>(p.tp_sequence & 1) * p.tp_world + src) * p.groups + group) * kExchangeTileBytes + lane * 64;
+}
 
-__device__ __forceinline__ void exchange_and_store(const GemvParams& p, uint32_t group, const float (&v)[8], uint32_t lane) {
-    const uint32_t world = p.tp_world, parity = p.tp_sequence & 1, seq = p.tp_sequence;
-    const uint64_t own = exchange_base(p, p.tp_rank);
-    auto slot_offset = [&](uint32_t src) {
-        return ((static_cast<uint64_t>(parity) * world + src) * p.groups + group) * kExchangeTileBytes + lane * 64;
-    };
-    float mine[8];
-#pragma unroll
-    for (uint32_t i = 0; i < 8; ++i) mine[i] = v[i] * p.global_a;
-    const uint64_t my_offset = slot_offset(p.tp_rank);
+__device__ __forceinline__ void exchange_push(const GemvParams& p, uint32_t group, const float (&v)[8], uint32_t lane) {
+    const uint64_t offset = exchange_slot(p, p.tp_rank, group, lane);
 #pragma unroll
     for (uint32_t d = 0; d < AUGUR_NVFP4_SM100_MAX_TP_RANKS; ++d) {
-        if (d < world && d != p.tp_rank) {
-            const uint64_t dst = p.exchange[d] + my_offset;
+        if (d < p.tp_world) {
+            const uint64_t dst = p.exchange[d] + offset;
 #pragma unroll
             for (uint32_t j = 0; j < 4; ++j) {
                 asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %2};"
-                             ::"l"(dst + j * 16), "r"(__float_as_uint(mine[2 * j])), "r"(seq), "r"(__float_as_uint(mine[2 * j + 1]))
+                             ::"l"(dst + j * 16), "r"(__float_as_uint(v[2 * j] * p.global_a)), "r"(p.tp_sequence),
+                               "r"(__float_as_uint(v[2 * j + 1] * p.global_a))
                              : "memory");
             }
-        }
-    }
-    float sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    bool arrived = true;
-    for (uint32_t src = 0; src < world; ++src) {
-        if (src == p.tp_rank) {
-#pragma unroll
-            for (uint32_t i = 0; i < 8; ++i) sum[i] += mine[i];
-            continue;
-        }
-        const uint64_t from = own + slot_offset(src);
-        uint32_t line[4][4];
-        uint32_t spin = 0;
-        for (;;) {
-            bool ready = true;
-#pragma unroll
-            for (uint32_t j = 0; j < 4; ++j) {
-                asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                             : "=r"(line[j][0]), "=r"(line[j][1]), "=r"(line[j][2]), "=r"(line[j][3])
-                             : "l"(from + j * 16)
-                             : "memory");
-                ready = ready && line[j][1] == seq && line[j][3] == seq;
-            }
-            if (ready) break;
-            if (++spin > kExchangeWaitLimit) { arrived = false; break; }
-        }
-#pragma unroll
-        for (uint32_t j = 0; j < 4; ++j) {
-            sum[2 * j] += __uint_as_float(line[j][0]);
-            sum[2 * j + 1] += __uint_as_float(line[j][2]);
-        }
-    }
-    if (!__all_sync(0xffffffffu, arrived) && lane == 0) atomicCAS(p.status_word, 0u, 0x203u);   // a peer's tile never arrived
-    const uint32_t g = lane >> 2, t4 = lane & 3;
-#pragma unroll
-    for (uint32_t i = 0; i < 8; ++i) {
-        const uint32_t token = 2 * t4 + (i & 1);
-        const uint32_t row = group * 32 + (i >> 2) * 16 + g + ((i >> 1) & 1) * 8;
-        if (token < p.tokens) {
-            static_cast<__nv_bfloat16*>(p.out)[static_cast<uint64_t>(token) * p.rows + row] = __float2bfloat16_rn(sum[i]);
         }
     }
 }
 
+// Whole warps call this once, after everything else the kernel does.
+__device__ __forceinline__ void exchange_reduce(const GemvParams& p, uint32_t warp, uint32_t lane) {
+    const uint32_t world = p.tp_world, seq = p.tp_sequence;
+    const uint64_t own = exchange_base(p, p.tp_rank);
+    constexpr uint32_t kBatch = 4;   // sources polled together, so that their load latencies overlap
+    bool arrived = true;
+    for (uint32_t group = blockIdx.x + gridDim.x * warp; group < p.groups; group += gridDim.x * kWarps) {
+        float sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (uint32_t first = 0; first < world; first += kBatch) {
+            uint32_t line[kBatch][4][4];
+            uint32_t spin = 0;
+            for (;;) {
+                bool ready = true;
+#pragma unroll
+                for (uint32_t q = 0; q < kBatch; ++q) {
+                    if (first + q < world) {
+                        const uint64_t from = own + exchange_slot(p, first + q, group, lane);
+#pragma unroll
+                        for (uint32_t j = 0; j < 4; ++j) {
+                            asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                         : "=r"(line[q][j][0]), "=r"(line[q][j][1]), "=r"(line[q][j][2]), "=r"(line[q][j][3])
+                                         : "l"(from + j * 16)
+                                         : "memory");
+                        }
+                    }
+                }
+#pragma unroll
+                for (uint32_t q = 0; q < kBatch; ++q) {
+                    if (first + q < world) {
+#pragma unroll
+                        for (uint32_t j = 0; j < 4; ++j) ready = ready && line[q][j][1] == seq && line[q][j][3] == seq;
+                    }
+                }
+                if (ready) break;
+                if (++spin > kExchangeWaitLimit) { arrived = false; break; }
+            }
+#pragma unroll
+            for (uint32_t q = 0; q < kBatch; ++q) {
+                if (first + q < world) {
+#pragma unroll
+                    for (uint32_t j = 0; j < 4; ++j) {
+                        sum[2 * j] += __uint_as_float(line[q][j][0]);
+                        sum[2 * j + 1] += __uint_as_float(line[q][j][2]);
+                    }
+                }
+            }
+        }
+        const uint32_t g = lane >> 2, t4 = lane & 3;
+#pragma unroll
+        for (uint32_t i = 0; i < 8; ++i) {
+            const uint32_t token = 2 * t4 + (i & 1);
+            const uint32_t row = group * 32 + (i >> 2) * 16 + g + ((i >> 1) & 1) * 8;
+            if (token < p.tokens) {
+                static_cast<__nv_bfloat16*>(p.out)[static_cast<uint64_t>(token) * p.rows + row] = __float2bfloat16_rn(sum[i]);
+            }
+        }
+    }
+    if (!__all_sync(0xffffffffu, arrived) && lane == 0) atomicCAS(p.status_word, 0u, 0x203u);   // a tile never arrived
+}
+
 __device__ __forceinline__ void epilogue(const GemvParams& p, uint32_t group, const float (&v)[8], uint32_t lane) {
     if (p.tp_world) {
-        exchange_and_store(p, group, v, lane);
+        exchange_push(p, group, v, lane);   // the sum over ranks is written by exchange_reduce
         return;
     }
     const uint32_t g = lane >> 2, t4 = lane & 3;
@@ -790,27 +812,30 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_kernel(const GemvParams p
 #endif
 
     // ---- combine row groups that were split between warps of this CTA ----
-    if (len == 0) return;
-    const uint32_t cta_first_group = c0 / kbs;
-    const uint32_t cta_groups = (c1 - 1) / kbs - cta_first_group + 1;
-    for (uint32_t index = warp; index < cta_groups; index += kWarps) {
-        const uint32_t group = cta_first_group + index;
-        const uint32_t lo = group * kbs > c0 ? group * kbs : c0;
-        const uint32_t hi = (group + 1) * kbs < c1 ? (group + 1) * kbs : c1;
-        const uint32_t w_lo = span_of(lo - c0, len, kWarps), w_hi = span_of(hi - 1 - c0, len, kWarps);
-        if (w_lo == w_hi && lo == group * kbs && hi == (group + 1) * kbs) continue;  // one warp had it all
-        float sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (uint32_t w = w_lo; w <= w_hi; ++w) {
-            const uint32_t b0 = c0 + w * len / kWarps, b1 = c0 + (w + 1) * len / kWarps;
-            if (b1 == b0) continue;
-            const uint32_t slot = (b0 >= group * kbs) ? 0 : 1;   // the span's first row group parks in slot 0
-            const float4* src = reinterpret_cast<const float4*>(warp_partial + w * kWarpPartialFloats + slot * kSlotFloats) + lane * 2;
-            const float4 a = src[0], b = src[1];
-            sum[0] += a.x; sum[1] += a.y; sum[2] += a.z; sum[3] += a.w;
-            sum[4] += b.x; sum[5] += b.y; sum[6] += b.z; sum[7] += b.w;
+    if (len != 0) {
+        const uint32_t cta_first_group = c0 / kbs;
+        const uint32_t cta_groups = (c1 - 1) / kbs - cta_first_group + 1;
+        for (uint32_t index = warp; index < cta_groups; index += kWarps) {
+            const uint32_t group = cta_first_group + index;
+            const uint32_t lo = group * kbs > c0 ? group * kbs : c0;
+            const uint32_t hi = (group + 1) * kbs < c1 ? (group + 1) * kbs : c1;
+            const uint32_t w_lo = span_of(lo - c0, len, kWarps), w_hi = span_of(hi - 1 - c0, len, kWarps);
+            if (w_lo == w_hi && lo == group * kbs && hi == (group + 1) * kbs) continue;  // one warp had it all
+            float sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            for (uint32_t w = w_lo; w <= w_hi; ++w) {
+                const uint32_t b0 = c0 + w * len / kWarps, b1 = c0 + (w + 1) * len / kWarps;
+                if (b1 == b0) continue;
+                const uint32_t slot = (b0 >= group * kbs) ? 0 : 1;   // the span's first row group parks in slot 0
+                const float4* src = reinterpret_cast<const float4*>(warp_partial + w * kWarpPartialFloats + slot * kSlotFloats) + lane * 2;
+                const float4 a = src[0], b = src[1];
+                sum[0] += a.x; sum[1] += a.y; sum[2] += a.z; sum[3] += a.w;
+                sum[4] += b.x; sum[5] += b.y; sum[6] += b.z; sum[7] += b.w;
+            }
+            contribute(p, group, slab, cta_in_slab, sum, lane);
         }
-        contribute(p, group, slab, cta_in_slab, sum, lane);
     }
+    // ---- tensor-parallel: add the ranks' tiles of the row groups assigned to this warp ----
+    if (p.tp_world) exchange_reduce(p, warp, lane);
 #ifdef AUGUR_GEMV_TRACE
     __syncthreads();
     stamp(3);
@@ -1060,6 +1085,9 @@ bool check_mlp_tp(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100
         return false;
     }
     if (a->exchange_len_bytes < exchange_extent(a->world, a->down.rows / 32)) return false;
+    // The reduce step polls for tiles that other CTAs of the same grid deliver: all of them must be resident.
+    const GemvGeometry down_geometry = geometry(a->down.rows, a->down.cols, false, plan->sm_count);
+    if (down_geometry.slabs * down_geometry.ctas_per_slab > plan->sm_count) return false;
     for (uint32_t r = 0; r < AUGUR_NVFP4_SM100_MAX_TP_RANKS; ++r) {
         if (r >= a->world) {
             if (a->exchange[r]) return false;
