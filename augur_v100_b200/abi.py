@@ -35,6 +35,8 @@ EPILOGUE_SWIGLU_BF16 = 1
 EPILOGUE_LINEAR_F32 = 2
 
 MAX_SMALL_TOKENS = 8
+SCALE_COMPRESSED_TENSORS = 0
+SCALE_MODELOPT = 1
 STATIC_SCRATCH_BYTES = 4 << 20
 
 
@@ -124,6 +126,10 @@ EXPORTS = {
     "augur_cuda_nvfp4_sm100_repack_extent_host_v1": (Result, [c_uint32, c_uint32, c_uint32, POINTER(c_uint64)]),
     "augur_cuda_nvfp4_sm100_repack_host_v1": (Result, [c_uint32, c_uint32, c_uint32, _U8P, _U8P, _U8P, _U8P, _U8P, c_uint64]),
     "augur_cuda_nvfp4_sm100_unpack_host_v1": (Result, [c_uint32, c_uint32, c_uint32, _U8P, c_uint64, _U8P, _U8P, _U8P, _U8P]),
+    "augur_cuda_nvfp4_sm100_checkpoint_global_scale_host_v1": (Result, [c_uint32, c_float, POINTER(c_float)]),
+    "augur_cuda_nvfp4_sm100_checkpoint_validate_host_v1": (Result, [c_uint64, c_uint64, _U8P, c_uint64, _U8P, c_uint64]),
+    "augur_cuda_nvfp4_sm100_planes_to_ggml36_host_v1": (Result, [c_uint64, c_uint64, _U8P, _U8P, _U8P, c_uint64]),
+    "augur_cuda_nvfp4_sm100_ggml36_to_planes_host_v1": (Result, [c_uint64, c_uint64, _U8P, c_uint64, _U8P, _U8P]),
     "augur_cuda_nvfp4_sm100_repack_preflight_v1": (Result, [c_int32, c_void_p, POINTER(RepackArgs)]),
     "augur_cuda_nvfp4_sm100_repack_prevalidated_submit_v1": (Result, [c_int32, c_void_p, POINTER(RepackArgs)]),
     "augur_cuda_nvfp4_sm100_dequant_f32_preflight_v1": (Result, [c_int32, c_void_p, POINTER(DequantArgs)]),

@@ -327,7 +327,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant__
 //   empty[s]  one per CTA, arrived by the leader's tcgen05.commit multicast to both CTAs;
 //   tmem_full one per CTA, same multicast;   tmem_empty leader's only, 8 arrivals (4 epilogue
 //             warps of each CTA, the peer's through a cluster-scope arrive).
-constexpr uint32_t kPairStages = 4;
+#ifndef AUGUR_GEMM_PAIR_STAGES
+#define AUGUR_GEMM_PAIR_STAGES 4
+#endif
+constexpr uint32_t kPairStages = AUGUR_GEMM_PAIR_STAGES;
 constexpr uint32_t kPairBytesB = 128 * 128;                                            // this CTA's 128 weight rows
 constexpr uint32_t kPairStageBytes = kBytesA + kPairBytesB + kBytesSfA + kBytesSfB;   // 38912
 // Epilogue staging: each epilogue warp parks its 32 rows x 256 BF16 here (rows padded by 16 bytes

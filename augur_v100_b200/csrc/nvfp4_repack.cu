@@ -2,6 +2,8 @@
 // bit-exact f32 dequantiser used for verification.
 #include <cuda_runtime.h>
 
+#include <cmath>
+
 #include <cstring>
 
 #include "nvfp4_internal.h"
@@ -374,6 +376,93 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_unpack_ho
             for (uint32_t sc = 0; sc < cols / 16; ++sc) {
                 const StreamCoord at = stream_scale_coord(pair, m, r, sc, cols);
                 scale_plane[static_cast<uint64_t>(r) * (cols / 16) + sc] = source[at.block * kStreamBlockBytes + at.offset];
+            }
+        }
+    }
+    return ok();
+}
+
+// ---- checkpoint formats ----------------------------------------------------------------------------
+// A checkpoint hands NVFP4 weights over as the COMPACT planes plus one typed scalar
+// (crates/augur-model-qwen35/src/checkpoint_quant.rs:10-58): compressed-tensors stores
+// weight_global_scale and DIVIDES by it, ModelOpt stores weight_scale_2 and MULTIPLIES by it.
+// The kernels of this library multiply, so the scalar is converted once at load time.
+extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_checkpoint_global_scale_host_v1(
+    uint32_t convention, float checkpoint_scalar, float* out_global_scale) {
+    if (!out_global_scale || !std::isfinite(checkpoint_scalar) || checkpoint_scalar <= 0.0f) return invalid();
+    float multiplier;
+    if (convention == AUGUR_NVFP4_SM100_SCALE_COMPRESSED_TENSORS) {
+        multiplier = 1.0f / checkpoint_scalar;
+    } else if (convention == AUGUR_NVFP4_SM100_SCALE_MODELOPT) {
+        multiplier = checkpoint_scalar;
+    } else {
+        return invalid();
+    }
+    if (!scale_ok(multiplier)) return invalid();
+    *out_global_scale = multiplier;
+    return ok();
+}
+
+// The same validation the reference applies to checkpoint planes before anything is uploaded
+// (checkpoint_quant.rs:113-133): non-empty shape, cols % 16, exact plane extents, no negative or
+// NaN block scale.
+extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_checkpoint_validate_host_v1(
+    uint64_t rows, uint64_t cols, const uint8_t* codes, uint64_t codes_len_bytes, const uint8_t* scales,
+    uint64_t scales_len_bytes) {
+    if (!rows || !cols || cols % 16 != 0 || !codes || !scales) return invalid();
+    if (rows > UINT64_MAX / cols) return invalid();
+    const uint64_t count = rows * cols;
+    if (codes_len_bytes != count / 2 || scales_len_bytes != count / 16) return invalid();
+    for (uint64_t i = 0; i < scales_len_bytes; ++i) {
+        if (scales[i] >= 127) return invalid();
+    }
+    return ok();
+}
+
+// GGML36 wire blocks (checkpoint_quant.rs:157-189): 64 elements = 4 scale bytes, then four
+// 8-byte groups; byte j of a group holds element j of the group's 16 in its low nibble and
+// element j + 8 in its high nibble. Lossless in both directions; the global scalar stays apart.
+extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_planes_to_ggml36_host_v1(
+    uint64_t rows, uint64_t cols, const uint8_t* codes, const uint8_t* scales, uint8_t* wire, uint64_t wire_len_bytes) {
+    if (!rows || !cols || cols % 64 != 0 || !codes || !scales || !wire || rows > UINT64_MAX / cols) return invalid();
+    const uint64_t blocks = rows * cols / 64;
+    if (wire_len_bytes != blocks * 36) return invalid();
+    for (uint64_t b = 0; b < blocks; ++b) {
+        uint8_t* out = wire + b * 36;
+        memcpy(out, scales + b * 4, 4);
+        for (uint32_t group = 0; group < 4; ++group) {
+            const uint8_t* src = codes + b * 32 + group * 8;   // 16 elements, two per byte, even element low
+            for (uint32_t j = 0; j < 8; ++j) {
+                const uint32_t first = (src[j / 2] >> ((j & 1) * 4)) & 15u;               // element j
+                const uint32_t second = (src[(j + 8) / 2] >> (((j + 8) & 1) * 4)) & 15u;  // element j + 8
+                out[4 + group * 8 + j] = static_cast<uint8_t>(first | (second << 4));
+            }
+        }
+    }
+    return ok();
+}
+
+extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_ggml36_to_planes_host_v1(
+    uint64_t rows, uint64_t cols, const uint8_t* wire, uint64_t wire_len_bytes, uint8_t* codes, uint8_t* scales) {
+    if (!rows || !cols || cols % 64 != 0 || !codes || !scales || !wire || rows > UINT64_MAX / cols) return invalid();
+    const uint64_t blocks = rows * cols / 64;
+    if (wire_len_bytes != blocks * 36) return invalid();
+    for (uint64_t b = 0; b < blocks; ++b) {
+        const uint8_t* in = wire + b * 36;
+        for (uint32_t i = 0; i < 4; ++i) {
+            if (in[i] >= 127) return invalid();   // negative or NaN block scale
+        }
+        memcpy(scales + b * 4, in, 4);
+        for (uint32_t group = 0; group < 4; ++group) {
+            uint8_t* dst = codes + b * 32 + group * 8;
+            for (uint32_t byte = 0; byte < 8; ++byte) {
+                uint32_t value = 0;
+                for (uint32_t half = 0; half < 2; ++half) {
+                    const uint32_t element = byte * 2 + half;   // 0..15 inside the group
+                    const uint32_t code = (in[4 + group * 8 + (element & 7)] >> ((element >> 3) * 4)) & 15u;
+                    value |= code << (half * 4);
+                }
+                dst[byte] = static_cast<uint8_t>(value);
             }
         }
     }

@@ -175,6 +175,31 @@ augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_repack_preflight_v1(
 augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_repack_prevalidated_submit_v1(
     int32_t ordinal, augur_cuda_stream_t stream, const augur_cuda_nvfp4_sm100_repack_args_v1* args);
 
+/* ---- checkpoint formats (host side, load time) -------------------------------------- */
+/* How a checkpoint's per-tensor scalar enters the value
+ * (crates/augur-model-qwen35/src/checkpoint_quant.rs:10-58): compressed-tensors divides by
+ * weight_global_scale, ModelOpt (W4A4 and W4A16 exports alike) multiplies by weight_scale_2.
+ * Activation scales of either format are not part of the weight and are not touched here. */
+#define AUGUR_NVFP4_SM100_SCALE_COMPRESSED_TENSORS UINT32_C(0)
+#define AUGUR_NVFP4_SM100_SCALE_MODELOPT UINT32_C(1)
+/* The multiplier the kernels of this library take as global_scale. Rejects non-finite or
+ * non-positive scalars (checkpoint_quant.rs:27-47) and results outside [2^-32, 24]. */
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_checkpoint_global_scale_host_v1(
+    uint32_t convention, float checkpoint_scalar, float* out_global_scale);
+/* CheckpointNvfp4Matrix::new's checks (checkpoint_quant.rs:113-133): non-empty, cols % 16,
+ * exact plane extents, every block scale byte < 127. Rows need not be a tile multiple here. */
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_checkpoint_validate_host_v1(
+    uint64_t rows, uint64_t cols, const uint8_t* codes, uint64_t codes_len_bytes,
+    const uint8_t* scales, uint64_t scales_len_bytes);
+/* Planes <-> GGML36 wire blocks (to_ggml_planes_into, checkpoint_quant.rs:157-189, and its
+ * inverse): 36 bytes per 64 elements, lossless, cols % 64. The inverse rejects scale bytes >= 127. */
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_planes_to_ggml36_host_v1(
+    uint64_t rows, uint64_t cols, const uint8_t* codes, const uint8_t* scales,
+    uint8_t* wire, uint64_t wire_len_bytes);
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_ggml36_to_planes_host_v1(
+    uint64_t rows, uint64_t cols, const uint8_t* wire, uint64_t wire_len_bytes,
+    uint8_t* codes, uint8_t* scales);
+
 /* ---- dequantise to f32 (verification entry) -------------------------------- */
 /* Replaces the expand pair (augur_qwen35_nvfp4_qpn_abi.h:23-29,153). Output is
  * bit-identical to Nvfp4CompactBlock::decode_ref (crates/augur-formats/src/fp4.rs:105-125):
