@@ -471,10 +471,18 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
                 const uint32_t tmem_sfa = tmem_base + kTmemSfA + sf_buffer * 16;
                 const uint32_t tmem_sfb = tmem_base + kTmemSfB + sf_buffer * 32;
                 const uint64_t a_desc = operand_desc(base), b_desc = operand_desc(base + kBytesA);
+                // all block scales of the stage first, then its four MMAs: the MMAs wait for the
+                // copies once per stage instead of once per MMA
                 for (uint32_t k = 0; k < 4; ++k) {
+#ifdef AUGUR_GEMM_PROBE_NO_SF_COPY
+                    if (step >= 2) break;
+#endif
                     tc_copy_sf_pair(tmem_sfa + 4 * k, sf_desc(sfa_smem + k * kSfAtomBytes));
                     tc_copy_sf_pair(tmem_sfb + 8 * k, sf_desc(sfb_smem + k * kSfAtomBytes));
                     tc_copy_sf_pair(tmem_sfb + 8 * k + 4, sf_desc(sfb_smem + kBytesSfA + k * kSfAtomBytes));
+                }
+                for (uint32_t k = 0; k < 4; ++k) {
+                    // each MMA consumes 64 k = 32 bytes of every row: advance the start address by 32 >> 4
                     tc_mma_pair(tmem_base + kTmemAcc, a_desc + 2 * k, b_desc + 2 * k, idesc, tmem_sfa + 4 * k,
                                 tmem_sfb + 8 * k, (step | k) ? 1u : 0u);
                 }
@@ -521,6 +529,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
             const uint32_t first_token = m_pair * 2 * kTileM + rank * kTileM + quadrant * 32;
             uint8_t* out_base = reinterpret_cast<uint8_t*>(p.out + static_cast<uint64_t>(first_token) * p.rows + n_tile * kTileN);
 #pragma unroll 4
+#ifdef AUGUR_GEMM_PROBE_NO_STORE
+            if (p.scale == 12345.0f)
+#endif
             for (uint32_t r = 0; r < 32; ++r) {
                 const uint4 value = *reinterpret_cast<const uint4*>(my_rows + r * kPairOutRowBytes + lane * 16);
                 *reinterpret_cast<uint4*>(out_base + static_cast<uint64_t>(r) * p.rows * 2 + lane * 16) = value;
