@@ -149,6 +149,7 @@ struct GemmParams {
     __nv_bfloat16* out;
     uint32_t* status_word;
     uint32_t rows, cols, tokens, terms;
+    uint32_t padded_tokens;        // tokens rounded up to whole 128-row tiles: row stride of the staged activation planes
     float scale;                   // g_w * g_a
 };
 
@@ -188,7 +189,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant__
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const uint32_t m_tiles = p.tokens / kTileM;
+    const uint32_t m_tiles = p.padded_tokens / kTileM;
     const uint32_t n_tiles = (p.rows + kTileN - 1) / kTileN;
     const uint32_t total_tiles = m_tiles * n_tiles;
     const uint32_t k_blocks = (p.cols + kBlockK - 1) / kBlockK;
@@ -214,7 +215,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant__
                 const uint32_t full = bar_full + 8 * stage;
                 const uint32_t row_blocks_b = n_rows / 128;
                 mbar_expect_tx(full, kBytesA + n_rows * 128 + sf_bytes * (1 + row_blocks_b));
-                tma_load_2d(smem_u32(base), &map_act, kb * 128, term * p.tokens + m_tile * kTileM, full);
+                tma_load_2d(smem_u32(base), &map_act, kb * 128, term * p.padded_tokens + m_tile * kTileM, full);
                 tma_load_2d(smem_u32(base + kBytesA), &map_weight, kb * 128, n_tile * kTileN, full);
                 if (n_rows > 128) {
                     tma_load_2d(smem_u32(base + kBytesA + 128 * 128), &map_weight, kb * 128, n_tile * kTileN + 128, full);
@@ -284,6 +285,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant__
                 uint32_t v[32];
                 tc_load32(tmem_base + kTmemAcc + ((quadrant * 32) << 16) + c, v);
                 tc_wait_ld();
+                if (token >= p.tokens) continue;   // padding rows of the last tile are computed, never stored
                 uint32_t packed[16];
 #pragma unroll
                 for (uint32_t i = 0; i < 16; ++i) {
@@ -416,13 +418,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const uint32_t m_pairs = p.tokens / (2 * kTileM);
+    const uint32_t m_pairs = p.padded_tokens / (2 * kTileM);
     const uint32_t n_tiles = p.rows / kTileN;
     const uint32_t total_tiles = m_pairs * n_tiles;
     const uint32_t k_blocks = p.cols / kBlockK;
     const uint32_t steps = k_blocks * p.terms;
     const uint32_t atoms_per_row_block = p.cols / 64;
-    const uint32_t act_term_atoms = p.tokens / 128 * atoms_per_row_block;   // scale atoms of one activation term
+    const uint32_t act_term_atoms = p.padded_tokens / 128 * atoms_per_row_block;   // scale atoms of one activation term
 
     if (warp == 0 && lane == 0) {
         // ---------------- TMA producer (both CTAs) ----------------
@@ -440,7 +442,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
                 const uint32_t full = bar_full + 8 * stage;
                 if (rank == 0) mbar_expect_tx(full, 2 * kPairStageBytes);
                 const uint32_t token_row = m_pair * 2 * kTileM + rank * kTileM;
-                tma_load_2d_pair(base, &map_act, kb * 128, term * p.tokens + token_row, full);
+                tma_load_2d_pair(base, &map_act, kb * 128, term * p.padded_tokens + token_row, full);
                 tma_load_2d_pair(base + kBytesA, &map_weight, kb * 128, n_tile * kTileN + rank * 128, full);
                 tma_load_2d_pair(base + kBytesA + kPairBytesB, &map_act_sf, 0,
                                  term * act_term_atoms + (token_row / 128) * atoms_per_row_block + kb * 4, full);
@@ -533,6 +535,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
             if (p.scale == 12345.0f)
 #endif
             for (uint32_t r = 0; r < 32; ++r) {
+                if (first_token + r >= p.tokens) break;   // padding rows of the last tile are computed, never stored
                 const uint4 value = *reinterpret_cast<const uint4*>(my_rows + r * kPairOutRowBytes + lane * 16);
                 *reinterpret_cast<uint4*>(out_base + static_cast<uint64_t>(r) * p.rows * 2 + lane * 16) = value;
             }
@@ -552,6 +555,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
 }
 
 // ---- activation quantiser ------------------------------------------------------------------
+__host__ __device__ constexpr uint32_t padded_tokens(uint32_t tokens) { return (tokens + kTileM - 1) / kTileM * kTileM; }
+// Bytes of the staged activations of one term: code plane of whole tiles, then the scale atoms.
+__host__ __device__ constexpr uint64_t staged_term_bytes(uint32_t tokens, uint32_t cols) {
+    return tcgen05_extent_bytes(padded_tokens(tokens), cols);
+}
+
 // Smallest positive E4M3 code whose value is >= d (d > 0), 126 if none.
 __device__ __forceinline__ uint32_t e4m3_ceil_code(float d) {
     if (d > 448.0f) return 126;
@@ -610,7 +619,9 @@ __global__ void act_quant_kernel(const uint16_t* __restrict__ x, uint8_t* __rest
         residual[2 * i] = __uint_as_float(words[i] << 16);
         residual[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000u);
     }
-    const uint64_t code_bytes = tcgen05_codes_bytes(tokens, cols), scale_bytes = tcgen05_scale_bytes(tokens, cols);
+    // every term's code plane has whole 128-row tiles (the rows past `tokens` are never written and
+    // only ever feed output rows that are not stored)
+    const uint64_t code_bytes = tcgen05_codes_bytes(padded_tokens(tokens), cols), scale_bytes = tcgen05_scale_bytes(tokens, cols);
     for (uint32_t term = 0; term < terms; ++term) {
         float maximum = 0.0f;
 #pragma unroll
@@ -698,8 +709,8 @@ bool pair_tiles_enabled() {
 
 // ---- validation ------------------------------------------------------------------------------------
 bool act_shape_ok(uint32_t tokens, uint32_t cols, uint32_t terms) {
-    return tokens && cols && tokens % kTileM == 0 && cols % 64 == 0 && terms >= 1 && terms <= 3 &&
-           static_cast<uint64_t>(tokens) * cols <= UINT32_MAX;
+    return tokens && cols && tokens <= (1u << 24) && cols % 64 == 0 && terms >= 1 && terms <= 3 &&
+           static_cast<uint64_t>(padded_tokens(tokens)) * cols <= UINT32_MAX;
 }
 
 bool check_act_quant(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_act_quant_args_v1* a, bool full,
@@ -715,7 +726,7 @@ bool check_act_quant(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm
         return false;
     }
     if (a->input_len_bytes != static_cast<uint64_t>(a->tokens) * a->cols * 2 ||
-        a->destination_len_bytes != a->terms * tcgen05_extent_bytes(a->tokens, a->cols)) {
+        a->destination_len_bytes != a->terms * staged_term_bytes(a->tokens, a->cols)) {
         return false;
     }
     const Range r[2] = {{a->input_bf16, a->input_len_bytes, 16}, {a->destination, a->destination_len_bytes, 256}};
@@ -739,7 +750,7 @@ bool check_gemm(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_p
         return false;
     }
     if (a->weight_len_bytes != tcgen05_extent_bytes(a->rows, a->cols) ||
-        a->activation_len_bytes != a->activation_terms * tcgen05_extent_bytes(a->tokens, a->cols) ||
+        a->activation_len_bytes != a->activation_terms * staged_term_bytes(a->tokens, a->cols) ||
         a->output_len_bytes != static_cast<uint64_t>(a->tokens) * a->rows * 2) {
         return false;
     }
@@ -768,7 +779,7 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_scra
     if (!out_bytes || !rows || rows % 128 != 0 || !act_shape_ok(tokens, cols, activation_terms)) return invalid();
     // The GEMM itself needs no scratch; a caller that lets the plan stage the quantised
     // activations needs this much.
-    *out_bytes = activation_terms * tcgen05_extent_bytes(tokens, cols);
+    *out_bytes = activation_terms * staged_term_bytes(tokens, cols);
     return ok();
 }
 
@@ -786,7 +797,8 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_act_quant
     const cudaError_t e = cudaSetDevice(d);
     if (e != cudaSuccess) return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE, e);
     const uint64_t groups = static_cast<uint64_t>(a->tokens) * (a->cols / 16);
-    // Padding scale bytes of the destination are never read for tokens % 128 == 0.
+    // Rows past `tokens` in the last 128-row tile (codes and scale bytes) are left as they are: they only
+    // feed output rows that the GEMM never stores.
     act_quant_kernel<<<static_cast<uint32_t>((groups + 255) / 256), 256, 0, s->stream>>>(
         reinterpret_cast<const uint16_t*>(a->input_bf16), reinterpret_cast<uint8_t*>(a->destination), a->tokens,
         a->cols, a->terms, a->global_scale);
@@ -815,34 +827,36 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_bf16
     // The activation map spans the stacked code planes of all terms (terms * tokens rows).
     CUtensorMap map_act, map_weight;
     if (!make_code_map(&map_weight, a->weight, a->rows, a->cols) ||
-        !make_code_map(&map_act, a->activation, static_cast<uint64_t>(a->activation_terms) * a->tokens, a->cols)) {
+        !make_code_map(&map_act, a->activation, static_cast<uint64_t>(a->activation_terms) * padded_tokens(a->tokens), a->cols)) {
         return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE);
     }
     GemmParams p{};
     p.weight_sf = reinterpret_cast<const uint8_t*>(a->weight) + tcgen05_codes_bytes(a->rows, a->cols);
-    p.act_sf = reinterpret_cast<const uint8_t*>(a->activation) + a->activation_terms * tcgen05_codes_bytes(a->tokens, a->cols);
+    const uint32_t padded = padded_tokens(a->tokens);
+    p.act_sf = reinterpret_cast<const uint8_t*>(a->activation) + a->activation_terms * tcgen05_codes_bytes(padded, a->cols);
     p.act_term_stride = tcgen05_scale_bytes(a->tokens, a->cols);
     p.out = reinterpret_cast<__nv_bfloat16*>(a->output_bf16);
     p.status_word = plan->status_word;
     p.rows = a->rows; p.cols = a->cols; p.tokens = a->tokens; p.terms = a->activation_terms;
+    p.padded_tokens = padded;
     p.scale = a->weight_global_scale * a->activation_global_scale;
-    if (pair_tiles_enabled() && a->tokens % (2 * kTileM) == 0 && a->rows % kTileN == 0 && a->cols % kBlockK == 0 &&
+    if (pair_tiles_enabled() && padded % (2 * kTileM) == 0 && a->rows % kTileN == 0 && a->cols % kBlockK == 0 &&
         plan->sm_count >= 2) {
         // 256 x 256 tiles on pairs of CTAs (clusters of two); the grid is a whole number of pairs.
         CUtensorMap map_act_sf, map_weight_sf;
         const uint64_t atoms_per_row_block = a->cols / 64;
         if (!make_scale_map(&map_weight_sf, reinterpret_cast<uint64_t>(p.weight_sf), (a->rows / 128) * atoms_per_row_block) ||
             !make_scale_map(&map_act_sf, reinterpret_cast<uint64_t>(p.act_sf),
-                            static_cast<uint64_t>(a->activation_terms) * (a->tokens / 128) * atoms_per_row_block)) {
+                            static_cast<uint64_t>(a->activation_terms) * (padded / 128) * atoms_per_row_block)) {
             return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE);
         }
-        uint32_t pairs = (a->tokens / (2 * kTileM)) * (a->rows / kTileN);
+        uint32_t pairs = (padded / (2 * kTileM)) * (a->rows / kTileN);
         if (pairs > plan->sm_count / 2) pairs = plan->sm_count / 2;
         gemm_pair_kernel<<<2 * pairs, kGemmThreads, kPairSmemBytes, s->stream>>>(map_act, map_weight, map_act_sf, map_weight_sf, p);
         count_launch();
         return submitted();
     }
-    const uint32_t m_tiles = a->tokens / kTileM, n_tiles = (a->rows + kTileN - 1) / kTileN;
+    const uint32_t m_tiles = padded / kTileM, n_tiles = (a->rows + kTileN - 1) / kTileN;
     uint32_t grid = m_tiles * n_tiles;
     if (grid > plan->sm_count) grid = plan->sm_count;
     gemm_kernel<<<grid, kGemmThreads, kGemmSmemBytes, s->stream>>>(map_act, map_weight, p);

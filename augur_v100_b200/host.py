@@ -104,6 +104,13 @@ def gemv_scratch_bytes(rows: int, cols: int, tokens: int = 8) -> int:
     return int(out.value)
 
 
+def gemm_scratch_bytes(rows: int, cols: int, tokens: int, terms: int) -> int:
+    """Bytes of the staged (quantised) activations of a prefill linear: whole 128-row tiles per term."""
+    out = c_uint64()
+    _check("gemm_scratch_extent", abi.lib().augur_cuda_nvfp4_sm100_gemm_scratch_extent_host_v1(rows, cols, tokens, terms, byref(out)))
+    return int(out.value)
+
+
 def repack_extent(layout: int, rows: int, cols: int) -> int:
     out = c_uint64()
     _check("repack_extent", abi.lib().augur_cuda_nvfp4_sm100_repack_extent_host_v1(layout, rows, cols, byref(out)))
@@ -341,8 +348,7 @@ class Nvfp4Sm100PrefillLinear:
         assert weight.layout == abi.LAYOUT_TCGEN05
         self.plan, self.weight, self.x, self.out, self.terms = plan, weight, x, out, terms
         tokens, cols = x.shape
-        self.staged = torch.empty(terms * repack_extent(abi.LAYOUT_TCGEN05, tokens, cols), dtype=torch.uint8,
-                                  device=x.device)
+        self.staged = torch.empty(gemm_scratch_bytes(weight.rows, cols, tokens, terms), dtype=torch.uint8, device=x.device)
         q = abi.header(abi.ActQuantArgs)
         q.input_bf16, q.input_len_bytes = _ptr(x), _nbytes(x)
         q.destination, q.destination_len_bytes = _ptr(self.staged), _nbytes(self.staged)
@@ -383,13 +389,48 @@ class Nvfp4Sm100PrefillLinear:
     def staged_planes(self):
         """Quantised activations back on the host: (codes [terms, tokens, cols/2], scales [terms, tokens, cols/16])."""
         tokens, cols = self.x.shape
+        padded = (tokens + 127) // 128 * 128
         raw = self.staged.cpu().numpy()
-        code_bytes = tokens * cols // 2
-        sf_bytes = repack_extent(abi.LAYOUT_TCGEN05, tokens, cols) - code_bytes
-        codes = raw[: self.terms * code_bytes].reshape(self.terms, tokens, cols // 2).copy()
+        code_bytes = padded * cols // 2
+        sf_bytes = repack_extent(abi.LAYOUT_TCGEN05, padded, cols) - code_bytes
+        codes = raw[: self.terms * code_bytes].reshape(self.terms, padded, cols // 2)[:, :tokens].copy()
         scales = np.zeros((self.terms, tokens, cols // 16), dtype=np.uint8)
         for term in range(self.terms):
-            packed = np.concatenate([codes[term].reshape(-1),
+            packed = np.concatenate([raw[term * code_bytes: (term + 1) * code_bytes],
                                      raw[self.terms * code_bytes + term * sf_bytes: self.terms * code_bytes + (term + 1) * sf_bytes]])
-            _, scales[term] = unpack_host(abi.LAYOUT_TCGEN05, tokens, cols, packed)
+            _, full = unpack_host(abi.LAYOUT_TCGEN05, padded, cols, packed)
+            scales[term] = full[:tokens]
         return codes, scales
+
+
+SHAPE_SMALL_BATCH = "small-batch"
+SHAPE_PREFILL = "prefill"
+
+
+def classify_tokens(tokens: int) -> str:
+    """The reference's batch classes (crates/augur-kernel-api/src/key.rs:354-365): up to 8 token rows are the
+    small-batch class (decode and the fixed B8 verify batch), anything wider is prefill."""
+    if tokens < 1:
+        raise ValueError("at least one token row")
+    return SHAPE_SMALL_BATCH if tokens <= abi.MAX_SMALL_TOKENS else SHAPE_PREFILL
+
+
+class Nvfp4Sm100Linear:
+    """One weight matrix, any number of token rows: the dispatch a model runtime does per call site.
+
+    Keeps the weight in both hot layouts (the small-token stream layout and the tcgen05 layout) and
+    binds the kernel its shape class calls for: tokens <= 8 -> `Nvfp4Sm100Projection`, otherwise
+    `Nvfp4Sm100PrefillLinear` (activation quantiser with `terms` residual terms, then the block-scaled
+    GEMM). Bindings are made per (input, output) pair, exactly like the two classes it chooses between.
+    """
+
+    def __init__(self, stream: Stream, rows: int, cols: int, codes, scales, global_scale: float):
+        self.rows, self.cols = rows, cols
+        self.small = Nvfp4Sm100Weight.upload_checkpoint_nvfp4(stream, abi.LAYOUT_STREAM, rows, cols, codes, scales, global_scale)
+        self.wide = Nvfp4Sm100Weight.upload_checkpoint_nvfp4(stream, abi.LAYOUT_TCGEN05, rows, cols, codes, scales, global_scale)
+
+    def bind(self, plan: Plan, x: torch.Tensor, out: torch.Tensor | None = None, terms: int = 3,
+             activation_global_scale: float = 2.0 ** -8):
+        if classify_tokens(x.shape[0]) == SHAPE_SMALL_BATCH:
+            return Nvfp4Sm100Projection.bind(plan, self.small, x, out)
+        return Nvfp4Sm100PrefillLinear.bind(plan, self.wide, x, out, terms=terms, activation_global_scale=activation_global_scale)

@@ -345,7 +345,7 @@ typedef struct augur_cuda_nvfp4_sm100_act_quant_args_v1 {
     uint32_t struct_size;
     augur_cuda_device_ptr_t input_bf16;   /* [tokens][cols] */
     uint64_t input_len_bytes;
-    augur_cuda_device_ptr_t destination;  /* [terms] x TCGEN05 layout of a tokens x cols tensor */
+    augur_cuda_device_ptr_t destination;  /* [terms] x TCGEN05 layout of a ceil128(tokens) x cols tensor */
     uint64_t destination_len_bytes;
     uint32_t tokens;
     uint32_t cols;
@@ -362,7 +362,10 @@ augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_act_quant_prevalidat
  * (augur_cuda_runtime.h:6930-6964,7631-7643; native augur_nvfp4_cutlass_sm120.cu:36-203,320-378)
  * and the wide prefill projection (augur_qwen35_qpn_prefill.cuh:53-88):
  * y[t][n] = bf16(g_w * g_a * sum_terms sum_k w[n][k] a_term[t][k]) on tcgen05
- * kind::mxf4nvf4 with TMEM accumulators. tokens must be a multiple of 128. */
+ * kind::mxf4nvf4 with TMEM accumulators. Any token count >= 1: the staged activations hold whole
+ * 128-row tiles per term (gemm_scratch_extent_host_v1 gives the size act_quant writes and the GEMM
+ * reads), rows past `tokens` are computed and never stored; input and output have exactly
+ * `tokens` rows. */
 typedef struct augur_cuda_nvfp4_sm100_gemm_args_v1 {
     uint32_t abi_version;
     uint32_t struct_size;

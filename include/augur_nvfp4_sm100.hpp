@@ -356,7 +356,7 @@ public:
         if (plan->stream() != weight->stream()) throw std::invalid_argument("plan and weight belong to different streams");
         std::unique_ptr<Nvfp4Sm100PrefillLinear> binding(new Nvfp4Sm100PrefillLinear());
         const Stream& s = *plan->stream();
-        const uint64_t staged_bytes = terms * repack_extent(AUGUR_NVFP4_SM100_LAYOUT_TCGEN05, tokens, weight->cols());
+        const uint64_t staged_bytes = gemm_scratch_bytes(weight->rows(), weight->cols(), tokens, terms);
         binding->staged_ = std::make_shared<DeviceBuffer>(s.ordinal(), staged_bytes);
         binding->quant_ = header<augur_cuda_nvfp4_sm100_act_quant_args_v1>();
         binding->quant_.input_bf16 = input->address();
@@ -402,6 +402,40 @@ private:
     std::shared_ptr<Plan> plan_;
     std::shared_ptr<Nvfp4Sm100Weight> weight_;
     std::shared_ptr<DeviceBuffer> input_, staged_, output_;
+};
+
+// The reference's batch classes (crates/augur-kernel-api/src/key.rs:354-365): up to 8 token rows are the
+// small-batch class (decode and the fixed B8 verify batch), anything wider is prefill.
+enum class BatchClass { SmallBatch, Prefill };
+inline BatchClass classify_tokens(uint32_t tokens) {
+    if (tokens < 1) throw std::invalid_argument("at least one token row");
+    return tokens <= AUGUR_NVFP4_SM100_MAX_SMALL_TOKENS ? BatchClass::SmallBatch : BatchClass::Prefill;
+}
+
+// One weight matrix in both hot layouts; `bind_*` picks the kernel the token count calls for.
+class Nvfp4Sm100Linear {
+public:
+    Nvfp4Sm100Linear(const std::shared_ptr<Stream>& stream, uint32_t rows, uint32_t cols, const CheckpointNvfp4Matrix& matrix)
+        : small_(Nvfp4Sm100Weight::upload_checkpoint_nvfp4(stream, AUGUR_NVFP4_SM100_LAYOUT_STREAM, rows, cols, matrix)),
+          wide_(Nvfp4Sm100Weight::upload_checkpoint_nvfp4(stream, AUGUR_NVFP4_SM100_LAYOUT_TCGEN05, rows, cols, matrix)) {}
+    const std::shared_ptr<Nvfp4Sm100Weight>& small_batch_weight() const { return small_; }
+    const std::shared_ptr<Nvfp4Sm100Weight>& prefill_weight() const { return wide_; }
+    // tokens <= 8
+    std::unique_ptr<Nvfp4Sm100Projection> bind_small_batch(std::shared_ptr<Plan> plan, std::shared_ptr<DeviceBuffer> input,
+                                                           std::shared_ptr<DeviceBuffer> output, uint32_t tokens) const {
+        if (classify_tokens(tokens) != BatchClass::SmallBatch) throw std::invalid_argument("more than 8 token rows: bind_prefill");
+        return Nvfp4Sm100Projection::bind(std::move(plan), small_, std::move(input), std::move(output), tokens);
+    }
+    // tokens > 8 (any count)
+    std::unique_ptr<Nvfp4Sm100PrefillLinear> bind_prefill(std::shared_ptr<Plan> plan, std::shared_ptr<DeviceBuffer> input,
+                                                          std::shared_ptr<DeviceBuffer> output, uint32_t tokens, uint32_t terms = 3,
+                                                          float activation_global_scale = 1.0f / 256.0f) const {
+        return Nvfp4Sm100PrefillLinear::bind(std::move(plan), wide_, std::move(input), std::move(output), tokens, terms,
+                                             activation_global_scale);
+    }
+
+private:
+    std::shared_ptr<Nvfp4Sm100Weight> small_, wide_;
 };
 
 // Device allocations / frees made by the library so far (cuda_device_allocation_snapshot,

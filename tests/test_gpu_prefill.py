@@ -6,7 +6,7 @@ import pytest
 
 import oracle
 from augur_v100_b200 import abi, synth
-from helpers import TOLERANCE, bits_from_torch_bf16, rel_error, torch_bf16_from_bits
+from helpers import TOLERANCE, bits_from_torch_bf16, rel_error, rms_error, torch_bf16_from_bits
 
 pytestmark = pytest.mark.gpu
 
@@ -24,7 +24,7 @@ def ctx():
 
 
 @pytest.mark.parametrize("tokens,cols,terms,glob", [(128, 64, 1, 1.0), (128, 256, 2, 2.0 ** -8), (256, 2176, 3, 0.01),
-                                                    (384, 5120, 1, 2.0 ** -8)])
+                                                    (384, 5120, 1, 2.0 ** -8), (5, 128, 2, 0.5), (200, 320, 3, 2.0 ** -8)])
 def test_activation_quantiser_is_bit_exact(ctx, tokens, cols, terms, glob):
     host, torch = ctx["host"], ctx["torch"]
     rng = np.random.default_rng(tokens + cols)
@@ -52,13 +52,27 @@ def _run_gemm(ctx, w_planes, a_codes, a_scales, rows, cols, tokens, terms, g_w, 
     host, torch = ctx["host"], ctx["torch"]
     weight = host.Nvfp4Sm100Weight.upload_checkpoint_nvfp4(ctx["stream"], abi.LAYOUT_TCGEN05, rows, cols,
                                                            w_planes[0], w_planes[1], g_w)
+    # staged activations hold whole 128-row tiles per term; rows past `tokens` are filled with NaN scales and
+    # arbitrary codes here, to show that nothing of them reaches the stored rows
+    padded = (tokens + 127) // 128 * 128
     code_planes, scale_regions = [], []
     for t in range(terms):
-        packed = host.repack_host(abi.LAYOUT_TCGEN05, tokens, cols, a_codes[t], a_scales[t])
-        code_planes.append(packed[: tokens * cols // 2])
-        scale_regions.append(packed[tokens * cols // 2:])
+        codes = np.full((padded, cols // 2), 0xF7, dtype=np.uint8)
+        scales = np.full((padded, cols // 16), 0x7E, dtype=np.uint8)
+        codes[:tokens], scales[:tokens] = a_codes[t], a_scales[t]
+        packed = host.repack_host(abi.LAYOUT_TCGEN05, padded, cols, codes, scales)
+        packed = packed.copy()
+        region = packed[padded * cols // 2:]
+        if padded != tokens:   # poison the scale bytes of the padding rows with the E4M3 NaN pattern
+            probe_scales = np.zeros((padded, cols // 16), dtype=np.uint8)
+            probe_scales[tokens:] = 1
+            marks = host.repack_host(abi.LAYOUT_TCGEN05, padded, cols, np.zeros_like(codes), probe_scales)[padded * cols // 2:]
+            region[marks == 1] = 0x7F
+        code_planes.append(packed[: padded * cols // 2])
+        scale_regions.append(region)
     staged = torch.from_numpy(np.concatenate(code_planes + scale_regions)).to(ctx["device"])
-    out = torch.full((tokens, rows), float("nan"), dtype=torch.bfloat16, device=ctx["device"])
+    guard = torch.full(((tokens + 2) * rows,), float("nan"), dtype=torch.bfloat16, device=ctx["device"])
+    out = guard[rows:(tokens + 1) * rows].view(tokens, rows)
     args = abi.header(abi.GemmArgs)
     args.weight, args.weight_len_bytes = weight.packed.data_ptr(), weight.packed.numel()
     args.activation, args.activation_len_bytes = staged.data_ptr(), staged.numel()
@@ -73,6 +87,8 @@ def _run_gemm(ctx, w_planes, a_codes, a_scales, rows, cols, tokens, terms, g_w, 
     s.synchronize()
     status = plan.device_status()
     assert status == 0, hex(status)
+    # nothing is written before the first or after the last token row
+    assert bool(torch.isnan(guard[:rows]).all()) and bool(torch.isnan(guard[(tokens + 1) * rows:]).all())
     return bits_from_torch_bf16(out)
 
 
@@ -138,6 +154,12 @@ def test_gemm_pair_tiles_more_than_pairs(ctx):
     _check_gemm(ctx, rows=2560, cols=256, tokens=2048, seed=10)    # 80 tiles over at most 74 pairs
 
 
+@pytest.mark.parametrize("tokens", [1, 9, 100, 129, 300, 511])
+def test_gemm_any_token_count(ctx, tokens):
+    # the last 128-row tile is partly padding: computed, never stored
+    _check_gemm(ctx, rows=512, cols=512, tokens=tokens, seed=11, terms=2 if tokens == 300 else 1)
+
+
 def test_gemm_residual_terms(ctx):
     e1 = _check_gemm(ctx, rows=256, cols=1024, tokens=128, terms=1, seed=6)
     e3 = _check_gemm(ctx, rows=256, cols=1024, tokens=128, terms=3, seed=6)
@@ -171,3 +193,20 @@ def test_prefill_linear_end_to_end_and_quantisation_error(ctx):
     print("relative rms error vs BF16-activation oracle by residual terms:", errors)
     assert errors[1] < 0.2 and errors[2] < errors[1] / 3 and errors[3] < errors[2] / 3
     assert errors[3] <= TOLERANCE
+
+
+@pytest.mark.parametrize("tokens", [1, 8, 9, 200])
+def test_linear_dispatch_by_token_count(ctx, tokens):
+    # tokens <= 8 take the small-token kernel, wider inputs the quantiser + GEMM; both within the bound
+    host = ctx["host"]
+    rows, cols = 256, 1024
+    codes, scales, glob = synth.make_weight(3, 71, "w", rows, cols)
+    linear = host.Nvfp4Sm100Linear(ctx["stream"], rows, cols, codes, scales, glob)
+    x_bits = synth.make_activation(3, 71, "x", tokens, cols)
+    binding = linear.bind(ctx["plan"], torch_bf16_from_bits(x_bits, ctx["device"]))
+    assert isinstance(binding, host.Nvfp4Sm100Projection if tokens <= 8 else host.Nvfp4Sm100PrefillLinear)
+    assert host.classify_tokens(tokens) == (host.SHAPE_SMALL_BATCH if tokens <= 8 else host.SHAPE_PREFILL)
+    binding.submit_for_plan()
+    ctx["stream"].synchronize()
+    y64 = oracle.linear_f64(codes, scales, glob, rows, cols, x_bits, threads=oracle.max_threads())
+    assert rms_error(bits_from_torch_bf16(binding.out), y64) <= TOLERANCE
