@@ -151,7 +151,34 @@ struct GemmParams {
     uint32_t rows, cols, tokens, terms;
     uint32_t padded_tokens;        // tokens rounded up to whole 128-row tiles: row stride of the staged activation planes
     float scale;                   // g_w * g_a
+    float scale_b;                 // SwiGLU: g_w of the up rows * g_a
+    uint32_t swiglu;               // weight rows alternate 16 gate / 16 up; output is bf16(silu(gate) * up), rows / 2 wide
 };
+
+// 32 accumulator columns of one token row -> packed BF16. Plain: 32 outputs. SwiGLU: the weight rows
+// alternate 16 gate / 16 up, so columns 0..15 are gate sums and 16..31 the matching up sums of 16
+// intermediate columns; the 16 outputs bf16(silu(gate) * up) fill packed[0..8).
+__device__ __forceinline__ void convert_chunk(const uint32_t (&v)[32], float scale, float scale_b, bool swiglu, uint32_t (&packed)[16]) {
+    if (!swiglu) {
+#pragma unroll
+        for (uint32_t i = 0; i < 16; ++i) {
+            const __nv_bfloat162 two = __floats2bfloat162_rn(__uint_as_float(v[2 * i]) * scale, __uint_as_float(v[2 * i + 1]) * scale);
+            packed[i] = *reinterpret_cast<const uint32_t*>(&two);
+        }
+        return;
+    }
+    float h[16];
+#pragma unroll
+    for (uint32_t i = 0; i < 16; ++i) {
+        const float gate = __uint_as_float(v[i]) * scale, up = __uint_as_float(v[16 + i]) * scale_b;
+        h[i] = gate / (1.0f + expf(-gate)) * up;
+    }
+#pragma unroll
+    for (uint32_t i = 0; i < 8; ++i) {
+        const __nv_bfloat162 two = __floats2bfloat162_rn(h[2 * i], h[2 * i + 1]);
+        packed[i] = *reinterpret_cast<const uint32_t*>(&two);
+    }
+}
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant__ CUtensorMap map_weight,
@@ -280,23 +307,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant__
             if (!mbar_wait(bar_tmem_full, tmem_phase, abort_flag, p.status_word, kErrEpilogueWait)) break;
             tc_fence_after();
             const uint32_t token = m_tile * kTileM + quadrant * 32 + lane;
-            __nv_bfloat16* out_row = p.out + static_cast<uint64_t>(token) * p.rows + n_tile * kTileN;
+            // SwiGLU halves the output width: 32 accumulator columns give 16 outputs
+            const uint32_t out_width = p.swiglu ? p.rows / 2 : p.rows, out_first = p.swiglu ? n_tile * kTileN / 2 : n_tile * kTileN;
+            __nv_bfloat16* out_row = p.out + static_cast<uint64_t>(token) * out_width + out_first;
             for (uint32_t c = 0; c < n_rows; c += 32) {
                 uint32_t v[32];
                 tc_load32(tmem_base + kTmemAcc + ((quadrant * 32) << 16) + c, v);
                 tc_wait_ld();
                 if (token >= p.tokens) continue;   // padding rows of the last tile are computed, never stored
                 uint32_t packed[16];
+                convert_chunk(v, p.scale, p.scale_b, p.swiglu != 0, packed);
+                if (p.swiglu) {
+                    uint4* dst = reinterpret_cast<uint4*>(out_row + c / 2);
+                    dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                } else {
+                    uint4* dst = reinterpret_cast<uint4*>(out_row + c);
 #pragma unroll
-                for (uint32_t i = 0; i < 16; ++i) {
-                    const __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(v[2 * i]) * p.scale,
-                                                                      __uint_as_float(v[2 * i + 1]) * p.scale);
-                    packed[i] = *reinterpret_cast<const uint32_t*>(&pair);
-                }
-                uint4* dst = reinterpret_cast<uint4*>(out_row + c);
-#pragma unroll
-                for (uint32_t i = 0; i < 4; ++i) {
-                    dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+                    for (uint32_t i = 0; i < 4; ++i) {
+                        dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+                    }
                 }
             }
             tc_fence_before();
@@ -510,16 +540,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
                 tc_load32(tmem_base + kTmemAcc + ((quadrant * 32) << 16) + c, v);
                 tc_wait_ld();
                 uint32_t packed[16];
+                convert_chunk(v, p.scale, p.scale_b, p.swiglu != 0, packed);
+                if (p.swiglu) {
+                    uint4* dst = reinterpret_cast<uint4*>(my_rows + lane * kPairOutRowBytes + c);
+                    dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                } else {
+                    uint4* dst = reinterpret_cast<uint4*>(my_rows + lane * kPairOutRowBytes + c * 2);
 #pragma unroll
-                for (uint32_t i = 0; i < 16; ++i) {
-                    const __nv_bfloat162 two = __floats2bfloat162_rn(__uint_as_float(v[2 * i]) * p.scale,
-                                                                     __uint_as_float(v[2 * i + 1]) * p.scale);
-                    packed[i] = *reinterpret_cast<const uint32_t*>(&two);
-                }
-                uint4* dst = reinterpret_cast<uint4*>(my_rows + lane * kPairOutRowBytes + c * 2);
-#pragma unroll
-                for (uint32_t i = 0; i < 4; ++i) {
-                    dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+                    for (uint32_t i = 0; i < 4; ++i) {
+                        dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+                    }
                 }
             }
             // the accumulator is free for the next tile's MMAs from here on
@@ -527,17 +558,27 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
             __syncwarp();
             if (lane == 0) mbar_arrive_leader(bar_tmem_empty);
             tmem_phase ^= 1;
-            // staging rows -> global: one whole 512-byte row per instruction
+            // staging rows -> global, whole rows per instruction: 512 bytes (one row), or with SwiGLU
+            // 256 bytes (two rows per instruction)
             const uint32_t first_token = m_pair * 2 * kTileM + rank * kTileM + quadrant * 32;
-            uint8_t* out_base = reinterpret_cast<uint8_t*>(p.out + static_cast<uint64_t>(first_token) * p.rows + n_tile * kTileN);
+            if (p.swiglu) {
+                const uint32_t out_width = p.rows / 2;
+                uint8_t* out_base = reinterpret_cast<uint8_t*>(p.out + static_cast<uint64_t>(first_token) * out_width + n_tile * (kTileN / 2));
 #pragma unroll 4
-#ifdef AUGUR_GEMM_PROBE_NO_STORE
-            if (p.scale == 12345.0f)
-#endif
-            for (uint32_t r = 0; r < 32; ++r) {
-                if (first_token + r >= p.tokens) break;   // padding rows of the last tile are computed, never stored
-                const uint4 value = *reinterpret_cast<const uint4*>(my_rows + r * kPairOutRowBytes + lane * 16);
-                *reinterpret_cast<uint4*>(out_base + static_cast<uint64_t>(r) * p.rows * 2 + lane * 16) = value;
+                for (uint32_t r2 = 0; r2 < 32; r2 += 2) {
+                    const uint32_t r = r2 + (lane >> 4), piece = lane & 15;
+                    if (first_token + r >= p.tokens) continue;   // padding rows of the last tile are computed, never stored
+                    const uint4 value = *reinterpret_cast<const uint4*>(my_rows + r * kPairOutRowBytes + piece * 16);
+                    *reinterpret_cast<uint4*>(out_base + static_cast<uint64_t>(r) * out_width * 2 + piece * 16) = value;
+                }
+            } else {
+                uint8_t* out_base = reinterpret_cast<uint8_t*>(p.out + static_cast<uint64_t>(first_token) * p.rows + n_tile * kTileN);
+#pragma unroll 4
+                for (uint32_t r = 0; r < 32; ++r) {
+                    if (first_token + r >= p.tokens) break;   // padding rows of the last tile are computed, never stored
+                    const uint4 value = *reinterpret_cast<const uint4*>(my_rows + r * kPairOutRowBytes + lane * 16);
+                    *reinterpret_cast<uint4*>(out_base + static_cast<uint64_t>(r) * p.rows * 2 + lane * 16) = value;
+                }
             }
             __syncwarp();   // the rows are rewritten for the next tile
         }
@@ -735,7 +776,8 @@ bool check_act_quant(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm
 }
 
 bool check_gemm(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* plan,
-                const augur_cuda_nvfp4_sm100_gemm_args_v1* a, bool full, augur_cuda_result_v1* failure) {
+                const augur_cuda_nvfp4_sm100_gemm_args_v1* a, bool full, augur_cuda_result_v1* failure,
+                bool output_is_half_width = false) {
     *failure = invalid();
     if (!header_ok(d, s, a)) {
         if (a && s && d >= 0 && s->ordinal == d && a->abi_version != AUGUR_CUDA_ABI_VERSION_V1) {
@@ -751,7 +793,7 @@ bool check_gemm(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_p
     }
     if (a->weight_len_bytes != tcgen05_extent_bytes(a->rows, a->cols) ||
         a->activation_len_bytes != a->activation_terms * staged_term_bytes(a->tokens, a->cols) ||
-        a->output_len_bytes != static_cast<uint64_t>(a->tokens) * a->rows * 2) {
+        a->output_len_bytes != static_cast<uint64_t>(a->tokens) * (output_is_half_width ? a->rows / 2 : a->rows) * 2) {
         return false;
     }
     const Range r[4] = {{a->weight, a->weight_len_bytes, 256},
@@ -815,16 +857,13 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_bf16
     return make_code_map(&probe, a->weight, a->rows, a->cols) ? ok() : make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE);
 }
 
-extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_bf16_prevalidated_submit_v1(
-    int32_t d, augur_cuda_stream_t s, augur_cuda_nvfp4_sm100_plan_v1* plan,
-    const augur_cuda_nvfp4_sm100_gemm_args_v1* a) {
-    augur_cuda_result_v1 failure;
-    if (!check_gemm(d, s, plan, a, false, &failure)) return failure;
-    if (consume_injected_fault()) return make_result(AUGUR_CUDA_STATUS_DIAGNOSTIC_FAULT_INJECTED);
-    const cudaError_t e = cudaSetDevice(d);
-    if (e != cudaSuccess) return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE, e);
+namespace {
+// Enqueues the GEMM of a validated descriptor. `swiglu`: a->rows counts the physical weight rows
+// (gate and up interleaved), the output is a->rows / 2 wide.
+augur_cuda_result_v1 launch_gemm(augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* plan,
+                                 const augur_cuda_nvfp4_sm100_gemm_args_v1* a, bool swiglu, float up_global_scale) {
     // Tensor maps are encoded on the host into kernel parameter space: no allocation, no driver query.
-    // The activation map spans the stacked code planes of all terms (terms * tokens rows).
+    // The activation map spans the stacked code planes of all terms (terms * padded tokens rows).
     CUtensorMap map_act, map_weight;
     if (!make_code_map(&map_weight, a->weight, a->rows, a->cols) ||
         !make_code_map(&map_act, a->activation, static_cast<uint64_t>(a->activation_terms) * padded_tokens(a->tokens), a->cols)) {
@@ -840,6 +879,8 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_bf16
     p.rows = a->rows; p.cols = a->cols; p.tokens = a->tokens; p.terms = a->activation_terms;
     p.padded_tokens = padded;
     p.scale = a->weight_global_scale * a->activation_global_scale;
+    p.scale_b = up_global_scale * a->activation_global_scale;
+    p.swiglu = swiglu ? 1u : 0u;
     if (pair_tiles_enabled() && padded % (2 * kTileM) == 0 && a->rows % kTileN == 0 && a->cols % kBlockK == 0 &&
         plan->sm_count >= 2) {
         // 256 x 256 tiles on pairs of CTAs (clusters of two); the grid is a whole number of pairs.
@@ -862,4 +903,74 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_bf16
     gemm_kernel<<<grid, kGemmThreads, kGemmSmemBytes, s->stream>>>(map_act, map_weight, p);
     count_launch();
     return submitted();
+}
+
+static_assert(sizeof(augur_cuda_nvfp4_sm100_gemm_swiglu_args_v1) == 88, "gemm_swiglu ABI");
+
+// The fused form as a plain GEMM descriptor over the physical (interleaved) weight rows; false if the
+// descriptor's own fields are bad. Output extent is checked here (it is half as wide).
+bool swiglu_as_gemm(const augur_cuda_nvfp4_sm100_gemm_swiglu_args_v1* a, augur_cuda_nvfp4_sm100_gemm_args_v1* g) {
+    if (a->reserved || !a->rows || a->rows % 64 != 0 || a->rows > (1u << 30) || !scale_ok(a->up_global_scale)) return false;
+    if (a->output_len_bytes != static_cast<uint64_t>(a->tokens) * a->rows * 2) return false;
+    *g = augur_cuda_nvfp4_sm100_gemm_args_v1{};
+    g->abi_version = a->abi_version;
+    g->struct_size = sizeof(*g);
+    g->weight = a->weight; g->weight_len_bytes = a->weight_len_bytes;
+    g->activation = a->activation; g->activation_len_bytes = a->activation_len_bytes;
+    g->output_bf16 = a->output_bf16;
+    g->rows = 2 * a->rows; g->cols = a->cols; g->tokens = a->tokens; g->activation_terms = a->activation_terms;
+    g->output_len_bytes = static_cast<uint64_t>(a->tokens) * g->rows * 2;   // what check_gemm expects for 2*rows columns
+    g->weight_global_scale = a->gate_global_scale; g->activation_global_scale = a->activation_global_scale;
+    return true;
+}
+}  // namespace
+
+extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_bf16_prevalidated_submit_v1(
+    int32_t d, augur_cuda_stream_t s, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_gemm_args_v1* a) {
+    augur_cuda_result_v1 failure;
+    if (!check_gemm(d, s, plan, a, false, &failure)) return failure;
+    if (consume_injected_fault()) return make_result(AUGUR_CUDA_STATUS_DIAGNOSTIC_FAULT_INJECTED);
+    const cudaError_t e = cudaSetDevice(d);
+    if (e != cudaSuccess) return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE, e);
+    return launch_gemm(s, plan, a, false, 0.0f);
+}
+
+extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_swiglu_bf16_preflight_v1(
+    int32_t d, augur_cuda_stream_t s, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_gemm_swiglu_args_v1* a) {
+    if (!header_ok(d, s, a)) {
+        if (a && s && d >= 0 && s->ordinal == d && a->abi_version != AUGUR_CUDA_ABI_VERSION_V1) {
+            return make_result(AUGUR_CUDA_STATUS_ABI_VERSION_MISMATCH);
+        }
+        return invalid();
+    }
+    augur_cuda_nvfp4_sm100_gemm_args_v1 g;
+    if (!swiglu_as_gemm(a, &g)) return invalid();
+    augur_cuda_result_v1 failure;
+    // the output range handed to the range checks is the real (half-width) one
+    g.output_len_bytes = a->output_len_bytes;
+    if (!check_gemm(d, s, plan, &g, true, &failure, /*output_is_half_width=*/true)) return failure;
+    CUtensorMap probe;
+    return make_code_map(&probe, g.weight, g.rows, g.cols) ? ok() : make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE);
+}
+
+extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_swiglu_bf16_prevalidated_submit_v1(
+    int32_t d, augur_cuda_stream_t s, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_gemm_swiglu_args_v1* a) {
+    if (!header_ok(d, s, a)) {
+        if (a && s && d >= 0 && s->ordinal == d && a->abi_version != AUGUR_CUDA_ABI_VERSION_V1) {
+            return make_result(AUGUR_CUDA_STATUS_ABI_VERSION_MISMATCH);
+        }
+        return invalid();
+    }
+    augur_cuda_nvfp4_sm100_gemm_args_v1 g;
+    if (!swiglu_as_gemm(a, &g)) return invalid();
+    augur_cuda_result_v1 failure;
+    g.output_len_bytes = a->output_len_bytes;
+    if (!check_gemm(d, s, plan, &g, false, &failure, /*output_is_half_width=*/true)) return failure;
+    if (consume_injected_fault()) return make_result(AUGUR_CUDA_STATUS_DIAGNOSTIC_FAULT_INJECTED);
+    const cudaError_t e = cudaSetDevice(d);
+    if (e != cudaSuccess) return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE, e);
+    return launch_gemm(s, plan, &g, true, a->up_global_scale);
 }

@@ -469,6 +469,24 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_ggml36_to
     return ok();
 }
 
+extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_interleave_gate_up_host_v1(
+    uint32_t rows, uint32_t cols, const uint8_t* gate_codes, const uint8_t* gate_scales, const uint8_t* up_codes,
+    const uint8_t* up_scales, uint8_t* out_codes, uint8_t* out_scales) {
+    if (!rows || !cols || rows % 16 != 0 || cols % 16 != 0 || rows > INT_MAX / 2 || !gate_codes || !gate_scales || !up_codes ||
+        !up_scales || !out_codes || !out_scales) {
+        return invalid();
+    }
+    const uint64_t code_row = cols / 2, scale_row = cols / 16;
+    for (uint32_t r = 0; r < rows; ++r) {
+        const uint64_t gate_at = static_cast<uint64_t>(r / 16) * 32 + r % 16, up_at = gate_at + 16;
+        memcpy(out_codes + gate_at * code_row, gate_codes + r * code_row, code_row);
+        memcpy(out_codes + up_at * code_row, up_codes + r * code_row, code_row);
+        memcpy(out_scales + gate_at * scale_row, gate_scales + r * scale_row, scale_row);
+        memcpy(out_scales + up_at * scale_row, up_scales + r * scale_row, scale_row);
+    }
+    return ok();
+}
+
 extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_repack_preflight_v1(
     int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_repack_args_v1* a) {
     augur_cuda_result_v1 failure;

@@ -403,6 +403,91 @@ class Nvfp4Sm100PrefillLinear:
         return codes, scales
 
 
+def upload_gate_up_interleaved(stream: Stream, inter: int, hidden: int, gate_codes, gate_scales, gate_global: float,
+                               up_codes, up_scales, up_global: float) -> Nvfp4Sm100Weight:
+    """The gate and up matrices as ONE tcgen05 weight of 2 * inter rows, 16 gate rows alternating with the
+    matching 16 up rows, which is what the SwiGLU-fusing GEMM epilogue expects."""
+    Nvfp4Sm100Weight.checked_checkpoint(inter, hidden, np.asarray(gate_codes), np.asarray(gate_scales), gate_global)
+    Nvfp4Sm100Weight.checked_checkpoint(inter, hidden, np.asarray(up_codes), np.asarray(up_scales), up_global)
+    gc, gs = np.ascontiguousarray(gate_codes, dtype=np.uint8), np.ascontiguousarray(gate_scales, dtype=np.uint8)
+    uc, us = np.ascontiguousarray(up_codes, dtype=np.uint8), np.ascontiguousarray(up_scales, dtype=np.uint8)
+    codes = np.empty((2 * inter, hidden // 2), dtype=np.uint8)
+    scales = np.empty((2 * inter, hidden // 16), dtype=np.uint8)
+    _check("interleave_gate_up", abi.lib().augur_cuda_nvfp4_sm100_interleave_gate_up_host_v1(
+        inter, hidden, _u8p(gc), _u8p(gs), _u8p(uc), _u8p(us), _u8p(codes), _u8p(scales)))
+    weight = Nvfp4Sm100Weight.upload_checkpoint_nvfp4(stream, abi.LAYOUT_TCGEN05, 2 * inter, hidden, codes, scales, gate_global)
+    weight.global_scale_b = float(up_global)
+    return weight
+
+
+class Nvfp4Sm100PrefillFfnProgram:
+    """The MLP block for wide inputs: quantise x, gate|up GEMM with SiLU(gate)*up in its epilogue,
+    quantise the intermediate, down GEMM. Four launches, all members preflighted at bind time.
+
+    The wide-token counterpart of `Nvfp4Sm100FfnProgram` (the reference runs this shape as
+    stage -> two GEMMs -> silu/pack -> stage -> GEMM, crates/augur-cuda-sys/native/augur_qwen35_qpn_prefill.cuh:97-147).
+    """
+
+    def __init__(self, plan: Plan, gate_up: Nvfp4Sm100Weight, down: Nvfp4Sm100Weight, x: torch.Tensor, out: torch.Tensor,
+                 terms: int, input_global_scale: float, intermediate_global_scale: float):
+        assert gate_up.layout == abi.LAYOUT_TCGEN05 and down.layout == abi.LAYOUT_TCGEN05
+        tokens, hidden = x.shape
+        inter = gate_up.rows // 2
+        if gate_up.cols != hidden or down.cols != inter or down.rows != out.shape[1] or out.shape[0] != tokens:
+            raise ValueError("gate|up, down, input and output shapes do not fit together")
+        self.plan, self.gate_up, self.down, self.x, self.out, self.terms = plan, gate_up, down, x, out, terms
+        self.intermediate = torch.empty((tokens, inter), dtype=torch.bfloat16, device=x.device)
+        self.staged_x = torch.empty(gemm_scratch_bytes(gate_up.rows, hidden, tokens, terms), dtype=torch.uint8, device=x.device)
+        self.staged_h = torch.empty(gemm_scratch_bytes(down.rows, inter, tokens, terms), dtype=torch.uint8, device=x.device)
+
+        def quant(source, staged, cols, scale):
+            q = abi.header(abi.ActQuantArgs)
+            q.input_bf16, q.input_len_bytes = _ptr(source), _nbytes(source)
+            q.destination, q.destination_len_bytes = _ptr(staged), _nbytes(staged)
+            q.tokens, q.cols, q.terms, q.global_scale = tokens, cols, terms, scale
+            return q
+
+        self.quant_x = quant(x, self.staged_x, hidden, input_global_scale)
+        self.quant_h = quant(self.intermediate, self.staged_h, inter, intermediate_global_scale)
+        g = abi.header(abi.GemmSwigluArgs)
+        g.weight, g.weight_len_bytes = _ptr(gate_up.packed), _nbytes(gate_up.packed)
+        g.activation, g.activation_len_bytes = _ptr(self.staged_x), _nbytes(self.staged_x)
+        g.output_bf16, g.output_len_bytes = _ptr(self.intermediate), _nbytes(self.intermediate)
+        g.rows, g.cols, g.tokens, g.activation_terms = inter, hidden, tokens, terms
+        g.gate_global_scale, g.up_global_scale, g.activation_global_scale = gate_up.global_scale, gate_up.global_scale_b, input_global_scale
+        d = abi.header(abi.GemmArgs)
+        d.weight, d.weight_len_bytes = _ptr(down.packed), _nbytes(down.packed)
+        d.activation, d.activation_len_bytes = _ptr(self.staged_h), _nbytes(self.staged_h)
+        d.output_bf16, d.output_len_bytes = _ptr(out), _nbytes(out)
+        d.rows, d.cols, d.tokens, d.activation_terms = down.rows, inter, tokens, terms
+        d.weight_global_scale, d.activation_global_scale = down.global_scale, intermediate_global_scale
+        self.gate_up_args, self.down_args = g, d
+
+    @classmethod
+    def bind(cls, plan: Plan, gate_up: Nvfp4Sm100Weight, down: Nvfp4Sm100Weight, x: torch.Tensor,
+             out: torch.Tensor | None = None, terms: int = 3, input_global_scale: float = 2.0 ** -8,
+             intermediate_global_scale: float = 2.0 ** -8):
+        if out is None:
+            out = torch.empty((x.shape[0], down.rows), dtype=torch.bfloat16, device=x.device)
+        self = cls(plan, gate_up, down, x, out, terms, input_global_scale, intermediate_global_scale)
+        s, lib = plan.stream, abi.lib()
+        _check("act_quant_preflight", lib.augur_cuda_nvfp4_sm100_act_quant_preflight_v1(s.ordinal, s.handle, byref(self.quant_x)))
+        _check("gemm_swiglu_preflight", lib.augur_cuda_nvfp4_sm100_gemm_swiglu_bf16_preflight_v1(
+            s.ordinal, s.handle, plan.handle, byref(self.gate_up_args)))
+        _check("act_quant_preflight", lib.augur_cuda_nvfp4_sm100_act_quant_preflight_v1(s.ordinal, s.handle, byref(self.quant_h)))
+        _check("gemm_preflight", lib.augur_cuda_nvfp4_sm100_gemm_bf16_preflight_v1(s.ordinal, s.handle, plan.handle, byref(self.down_args)))
+        return self
+
+    def submit_for_plan(self) -> None:
+        s, lib = self.plan.stream, abi.lib()
+        _check("act_quant_submit", lib.augur_cuda_nvfp4_sm100_act_quant_prevalidated_submit_v1(s.ordinal, s.handle, byref(self.quant_x)))
+        _check("gemm_swiglu_submit", lib.augur_cuda_nvfp4_sm100_gemm_swiglu_bf16_prevalidated_submit_v1(
+            s.ordinal, s.handle, self.plan.handle, byref(self.gate_up_args)))
+        _check("act_quant_submit", lib.augur_cuda_nvfp4_sm100_act_quant_prevalidated_submit_v1(s.ordinal, s.handle, byref(self.quant_h)))
+        _check("gemm_submit", lib.augur_cuda_nvfp4_sm100_gemm_bf16_prevalidated_submit_v1(
+            s.ordinal, s.handle, self.plan.handle, byref(self.down_args)))
+
+
 SHAPE_SMALL_BATCH = "small-batch"
 SHAPE_PREFILL = "prefill"
 

@@ -390,6 +390,46 @@ augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_bf16_prevalidat
     int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
     const augur_cuda_nvfp4_sm100_gemm_args_v1* args);
 
+/* The gate|up projection of an MLP at prefill with SiLU(gate) * up in the GEMM epilogue; the
+ * counterpart of the reference's interstage step (native augur_nvfp4_cutlass_sm120.cu:455-503 computes
+ * silu(gate) * up from two GEMM outputs in a separate pass; augur_qwen35_qpn_prefill.cuh:120-147 fuses
+ * it with the staging of the down projection's input). `weight` is the TCGEN05 layout of ONE matrix of
+ * 2 * rows physical rows in which 16 gate rows alternate with the matching 16 up rows
+ * (interleave_gate_up_host_v1 builds its compact planes), so that 32 consecutive accumulator columns
+ * of a token hold the gate and up sums of 16 intermediate columns:
+ * out[t][n] = bf16(silu(g_gate * g_a * sum gate) * (g_up * g_a * sum up)), rows = intermediate size
+ * (a multiple of 64). Nothing of the 2 * rows wide gate|up tensor is ever written to memory. */
+typedef struct augur_cuda_nvfp4_sm100_gemm_swiglu_args_v1 {
+    uint32_t abi_version;
+    uint32_t struct_size;
+    augur_cuda_device_ptr_t weight;        /* TCGEN05 layout, (2 * rows) x cols, gate/up interleaved by 16 rows */
+    uint64_t weight_len_bytes;
+    augur_cuda_device_ptr_t activation;    /* output of act_quant */
+    uint64_t activation_len_bytes;
+    augur_cuda_device_ptr_t output_bf16;   /* [tokens][rows] */
+    uint64_t output_len_bytes;
+    uint32_t rows;
+    uint32_t cols;
+    uint32_t tokens;
+    uint32_t activation_terms;
+    float gate_global_scale;
+    float up_global_scale;
+    float activation_global_scale;
+    uint32_t reserved;
+} augur_cuda_nvfp4_sm100_gemm_swiglu_args_v1;
+
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_swiglu_bf16_preflight_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_gemm_swiglu_args_v1* args);
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_swiglu_bf16_prevalidated_submit_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_gemm_swiglu_args_v1* args);
+/* Compact planes of the interleaved gate|up matrix: physical row 32 j + i is gate row 16 j + i for
+ * i < 16 and up row 16 j + i - 16 otherwise. rows % 16 == 0, cols % 16 == 0; outputs hold 2 * rows rows. */
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_interleave_gate_up_host_v1(
+    uint32_t rows, uint32_t cols, const uint8_t* gate_codes, const uint8_t* gate_scales,
+    const uint8_t* up_codes, const uint8_t* up_scales, uint8_t* out_codes, uint8_t* out_scales);
+
 /* ---- diagnostics ------------------------------------------------------------ */
 /* Host-side fault injection (the reference injects with a device trap,
  * native augur_m306_k14_async_fault_sm70.cu:7-9,61; here nothing touches the GPU):

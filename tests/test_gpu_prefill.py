@@ -210,3 +210,41 @@ def test_linear_dispatch_by_token_count(ctx, tokens):
     ctx["stream"].synchronize()
     y64 = oracle.linear_f64(codes, scales, glob, rows, cols, x_bits, threads=oracle.max_threads())
     assert rms_error(bits_from_torch_bf16(binding.out), y64) <= TOLERANCE
+
+
+@pytest.mark.parametrize("hidden,inter,tokens", [(512, 1024, 256), (512, 1024, 100), (1024, 2176, 384)])
+def test_prefill_mlp_program_with_fused_swiglu(ctx, hidden, inter, tokens):
+    # quantise x -> gate|up GEMM with SiLU(gate)*up in the epilogue -> quantise h -> down GEMM, three residual terms
+    host = ctx["host"]
+    gate = synth.make_weight(4, 72, "gate", inter, hidden)
+    up = synth.make_weight(4, 72, "up", inter, hidden)
+    down = synth.make_weight(4, 72, "down", hidden, inter)
+    up = (up[0], up[1], float(np.float32(up[2]) * np.float32(1.5)))     # distinct global scales for gate and up
+    x_bits = synth.f32_to_bf16_bits(np.random.default_rng(23).standard_normal((tokens, hidden)).astype(np.float32) * 8.0)
+    h64, y64 = oracle.mlp_f64(gate, up, down, hidden, inter, x_bits, threads=oracle.max_threads())
+    gate_up_w = host.upload_gate_up_interleaved(ctx["stream"], inter, hidden, *gate, *up)
+    down_w = host.Nvfp4Sm100Weight.upload_checkpoint_nvfp4(ctx["stream"], abi.LAYOUT_TCGEN05, hidden, inter, *down)
+    x = torch_bf16_from_bits(x_bits, ctx["device"])
+    program = host.Nvfp4Sm100PrefillFfnProgram.bind(
+        ctx["plan"], gate_up_w, down_w, x, terms=3,
+        input_global_scale=host.default_activation_global_scale(float(np.abs(synth.bf16_bits_to_f32(x_bits)).max())),
+        intermediate_global_scale=host.default_activation_global_scale(float(np.abs(h64).max()) * 1.05))
+    before = host.allocation_snapshot()
+    for _ in range(2):
+        program.submit_for_plan()
+    ctx["stream"].synchronize()
+    assert host.allocation_snapshot() == before and ctx["plan"].device_status() == 0
+    # SiLU(gate)*up is heavy-tailed (largest values 20-30 x the rms), so each element is held to 2e-2 of
+    # its own magnitude or of the rms, whichever is larger
+    def worst(bits, want):
+        got = synth.bf16_bits_to_f32(bits).astype(np.float64).reshape(want.shape)
+        rms = np.sqrt(np.mean(want * want))
+        return float(np.max(np.abs(got - want) / np.maximum(np.abs(want), rms)))
+
+    # the intermediate is the product of two GEMM outputs, each within the bound: (1 + e)^2
+    assert worst(bits_from_torch_bf16(program.intermediate), h64) <= 2 * TOLERANCE
+    assert worst(bits_from_torch_bf16(program.out), y64) <= TOLERANCE
+    # the intermediate the down projection consumed is the one in memory: redo the down step from it in the oracle
+    y64_from_h = oracle.linear_f64(down[0], down[1], down[2], hidden, inter, bits_from_torch_bf16(program.intermediate),
+                                   threads=oracle.max_threads())
+    assert worst(bits_from_torch_bf16(program.out), y64_from_h) <= TOLERANCE

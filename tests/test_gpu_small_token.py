@@ -107,6 +107,14 @@ def test_linear_matches_fp64_oracle(ctx, rows, cols, tokens):
     assert np.max(np.abs(a - b) / np.maximum(np.abs(b), 1e-3 * np.sqrt(np.mean(b * b)))) <= 2.0 ** -7
 
 
+@pytest.mark.parametrize("rows,cols", [(10240, 5120), (5120, 5120), (5120, 10240)])
+def test_whole_model_sweep_projection_shapes(ctx, rows, cols):
+    # the stand-ins for the attention / GDN in- and out-projections of the M = 8 whole-model sweep, full size
+    codes, scales, glob, x_bits, proj = _linear_case(ctx, rows, cols, 8, seed=rows // 512 + cols // 1024)
+    y64 = oracle.linear_f64(codes, scales, glob, rows, cols, x_bits, threads=oracle.max_threads())
+    assert rel_error(bits_from_torch_bf16(proj.out), y64) <= TOLERANCE
+
+
 def test_one_hot_activations_read_back_the_weights_exactly(ctx):
     # x = e_k makes y[n] = bf16(w[n][k]): checks every fragment position of the layout
     rows, cols, tokens = 64, 256, 8
