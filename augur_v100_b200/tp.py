@@ -162,3 +162,56 @@ class TensorParallelMlp:
         if self.world > 1:
             import torch.distributed as dist
             dist.all_reduce(self.program.out, group=self.group)
+
+
+class TensorParallelPrefillMlp:
+    """One rank's share of the MLP block for wide inputs, processed in chunks of token rows.
+
+    Per chunk: quantise x, gate|up GEMM with fused SwiGLU on this rank's intermediate slice, quantise the
+    slice, down GEMM over this rank's k-slice -> a full-width BF16 partial; then one all-reduce (NCCL,
+    BF16, sum) of the chunk's [rows, hidden] output. The all-reduce of chunk c runs on its own stream
+    while the compute stream is already working on chunk c + 1, so that only the last chunk's
+    collective is exposed.
+    """
+
+    def __init__(self, plan, gate, up, down, x, rank: int, world: int, chunk_tokens: int = 4096, terms: int = 3,
+                 input_global_scale: float = 2.0 ** -8, intermediate_global_scale: float = 2.0 ** -8,
+                 process_group=None):
+        import torch
+
+        from . import abi, host
+        hidden, intermediate = gate[0].shape[1] * 2, gate[0].shape[0]
+        check_shardable(hidden, intermediate, world)
+        if (intermediate // world) % 64 != 0:
+            raise ValueError("each rank's slice of the intermediate dimension must be a multiple of 64")
+        g, u, d = shard_mlp(gate, up, down, rank, world)
+        shard = intermediate // world
+        stream = plan.stream
+        self.gate_up = host.upload_gate_up_interleaved(stream, shard, hidden, g[0], g[1], g[2], u[0], u[1], u[2])
+        self.down = host.Nvfp4Sm100Weight.upload_checkpoint_nvfp4(stream, abi.LAYOUT_TCGEN05, hidden, shard, *d)
+        tokens = x.shape[0]
+        self.out = torch.empty((tokens, hidden), dtype=torch.bfloat16, device=x.device)
+        self.chunks = []
+        for first in range(0, tokens, chunk_tokens):
+            last = min(first + chunk_tokens, tokens)
+            self.chunks.append(host.Nvfp4Sm100PrefillFfnProgram.bind(
+                plan, self.gate_up, self.down, x[first:last], out=self.out[first:last], terms=terms,
+                input_global_scale=input_global_scale, intermediate_global_scale=intermediate_global_scale))
+        self.world, self.group, self.plan = world, process_group, plan
+        self.compute = stream.torch_stream
+        self.comm = torch.cuda.Stream(device=x.device) if world > 1 else None
+        self.events = [torch.cuda.Event() for _ in self.chunks] if world > 1 else []
+
+    def submit(self) -> None:
+        """Enqueue all chunks; when it returns, the compute stream is ordered after the last all-reduce."""
+        import torch
+        import torch.distributed as dist
+        for index, chunk in enumerate(self.chunks):
+            chunk.submit_for_plan()
+            if self.world > 1:
+                self.events[index].record(self.compute)
+                with torch.cuda.stream(self.comm):
+                    self.comm.wait_event(self.events[index])
+                    dist.all_reduce(chunk.out, group=self.group)
+        if self.world > 1:
+            self.compute.wait_stream(self.comm)

@@ -76,3 +76,71 @@ def test_tensor_parallel_mlp_matches_oracle(world, fused):
     _, y64 = oracle.mlp_f64(gate, up, down, HIDDEN, INTER, x_bits, threads=4)
     y = synth.bf16_bits_to_f32(got).astype(np.float64).reshape(y64.shape)
     assert np.max(np.abs(y - y64)) / np.sqrt(np.mean(y64 * y64)) <= 4e-2
+
+
+P_HIDDEN, P_INTER, P_TOKENS, P_CHUNK = 512, 1024, 640, 256
+
+
+def _prefill_inputs():
+    from augur_v100_b200 import synth
+    gate = synth.make_weight(1, 82, "gate", P_INTER, P_HIDDEN)
+    up = synth.make_weight(1, 82, "up", P_INTER, P_HIDDEN)
+    down = synth.make_weight(1, 82, "down", P_HIDDEN, P_INTER)
+    x = synth.f32_to_bf16_bits(np.random.default_rng(82).standard_normal((P_TOKENS, P_HIDDEN)).astype(np.float32) * 8)
+    return gate, up, down, x
+
+
+def _prefill_worker(rank, world, port, queue, h_absmax):
+    import torch
+    import torch.distributed as dist
+    from augur_v100_b200 import host, synth, tp
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    gate, up, down, x_bits = _prefill_inputs()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        stream = host.Stream(rank, side)
+        plan = host.Plan(stream, 1 << 20)
+        x = torch.from_numpy(x_bits.view(np.int16)).to(torch.device("cuda", rank)).view(torch.bfloat16)
+        block = tp.TensorParallelPrefillMlp(
+            plan, gate, up, down, x, rank, world, chunk_tokens=P_CHUNK, terms=3,
+            input_global_scale=host.default_activation_global_scale(float(np.abs(synth.bf16_bits_to_f32(x_bits)).max())),
+            intermediate_global_scale=host.default_activation_global_scale(h_absmax * 1.05))
+        for _ in range(2):
+            block.submit()
+        side.synchronize()
+        assert plan.device_status() == 0
+        queue.put((rank, block.out.view(torch.int16).cpu().numpy().view(np.uint16)))
+        dist.barrier()
+    dist.destroy_process_group()
+    plan.close()
+
+
+def test_two_rank_chunked_prefill_mlp_matches_oracle():
+    # 640 token rows in chunks of 256 (the last one ragged), each chunk's all-reduce on its own stream
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    import oracle
+    from augur_v100_b200 import synth
+    gate, up, down, x_bits = _prefill_inputs()
+    h64, y64 = oracle.mlp_f64(gate, up, down, P_HIDDEN, P_INTER, x_bits, threads=8)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    procs = [ctx.Process(target=_prefill_worker, args=(r, 2, port, queue, float(np.abs(h64).max()))) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = dict(queue.get(timeout=300) for _ in range(2))
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert np.array_equal(results[0], results[1])
+    y = synth.bf16_bits_to_f32(results[0]).astype(np.float64).reshape(y64.shape)
+    rms = np.sqrt(np.mean(y64 * y64))
+    assert np.max(np.abs(y - y64) / np.maximum(np.abs(y64), rms)) <= 2e-2
