@@ -171,7 +171,9 @@ __device__ __forceinline__ void convert_chunk(const uint32_t (&v)[32], float sca
 #pragma unroll
     for (uint32_t i = 0; i < 16; ++i) {
         const float gate = __uint_as_float(v[i]) * scale, up = __uint_as_float(v[16 + i]) * scale_b;
-        h[i] = gate / (1.0f + expf(-gate)) * up;
+        // fast exponential and reciprocal (a few 1e-7 relative): this runs between the accumulator read and
+        // its release, in front of the next tile's MMAs. A gate below -87 gives exp = inf and h = -0.
+        h[i] = __fdividef(gate, 1.0f + __expf(-gate)) * up;
     }
 #pragma unroll
     for (uint32_t i = 0; i < 8; ++i) {
@@ -624,22 +626,36 @@ __device__ __forceinline__ float e4m3_positive_value(uint32_t code) {
                          : __uint_as_float(((exponent + 120) << 23) | (mantissa << 20));
 }
 
-// Nearest E2M1 level; a tie goes to the smaller magnitude; zero is always code 0.
+// Nearest E2M1 level; a tie goes to the smaller magnitude; zero is always code 0. |v| <= 6.
+// From 1 upward E2M1 is a float with one mantissa bit, so rounding the f32 pattern to that bit with
+// "ties down" (add half an ulp minus one, truncate) gives exponent and mantissa at once:
+// 1 -> code 2, 1.5 -> 3, 2 -> 4, 3 -> 5, 4 -> 6, 6 -> 7. Below 1 the levels are 0, 0.5 and 1.
 __device__ __forceinline__ uint32_t e2m1_nearest(float v, float* level) {
     const float a = fabsf(v);
     uint32_t m;
-    float l;
-    if (a <= 0.25f) { m = 0; l = 0.0f; }
-    else if (a <= 0.75f) { m = 1; l = 0.5f; }
-    else if (a <= 1.25f) { m = 2; l = 1.0f; }
-    else if (a <= 1.75f) { m = 3; l = 1.5f; }
-    else if (a <= 2.5f) { m = 4; l = 2.0f; }
-    else if (a <= 3.5f) { m = 5; l = 3.0f; }
-    else if (a <= 5.0f) { m = 6; l = 4.0f; }
-    else { m = 7; l = 6.0f; }
+    if (a < 1.0f) {
+        m = (a > 0.25f ? 1u : 0u) + (a > 0.75f ? 1u : 0u);
+    } else {
+        m = ((__float_as_uint(a) + 0x1fffffu) >> 22) - 252u;
+    }
+    const float l = m < 2 ? 0.5f * static_cast<float>(m) : __uint_as_float((m + 252u) << 22);
     const bool negative = v < 0.0f && m != 0;
     *level = negative ? -l : l;
     return negative ? (m | 8u) : m;
+}
+
+// x / d, correctly rounded, for many x and one d: with y = RN(1/d), two Newton steps on the quotient
+// (each an exact FMA residual) end on the correctly rounded quotient whenever nothing leaves the
+// normal range on the way; `safe` says so for this x (the caller falls back to a full division
+// otherwise, and d itself is checked once per group).
+__device__ __forceinline__ float divide_by(float x, float d, float y, bool d_safe) {
+    const uint32_t field = (__float_as_uint(x) >> 23) & 0xffu;
+    if (!d_safe || field < 64u || field > 190u) return __fdiv_rn(x, d);   // zero and tiny values come here too
+    float q = x * y;
+    float r = fmaf(-q, d, x);
+    q = fmaf(r, y, q);
+    r = fmaf(-q, d, x);
+    return fmaf(r, y, q);
 }
 
 // One thread per (token, 16-element group). Destination: the code planes of all terms
@@ -675,10 +691,14 @@ __global__ void act_quant_kernel(const uint16_t* __restrict__ x, uint8_t* __rest
             scale = e4m3_positive_value(scale_code);
         }
         const float divisor = __fmul_rn(scale, global_scale);
+        const uint32_t divisor_field = (__float_as_uint(divisor) >> 23) & 0xffu;
+        // the shortcut needs a divisor well inside the normal range and not of the all-ones mantissa form
+        const bool divisor_safe = divisor_field >= 64u && divisor_field <= 190u && (__float_as_uint(divisor) & 0x7fffffu) != 0x7fffffu;
+        const float reciprocal = divisor_safe ? __frcp_rn(divisor) : 0.0f;
         uint32_t packed[2] = {0, 0};
 #pragma unroll
         for (uint32_t i = 0; i < 16; ++i) {
-            float normalized = divisor == 0.0f ? 0.0f : __fdiv_rn(residual[i], divisor);
+            float normalized = divisor == 0.0f ? 0.0f : divide_by(residual[i], divisor, reciprocal, divisor_safe);
             normalized = fminf(fmaxf(normalized, -6.0f), 6.0f);
             float level;
             const uint32_t code = e2m1_nearest(normalized, &level);

@@ -174,22 +174,16 @@ class TensorParallelPrefillMlp:
     collective is exposed.
     """
 
-    def __init__(self, plan, gate, up, down, x, rank: int, world: int, chunk_tokens: int = 4096, terms: int = 3,
+    def __init__(self, plan, gate_up_weight, down_weight, x, world: int, chunk_tokens: int = 4096, terms: int = 3,
                  input_global_scale: float = 2.0 ** -8, intermediate_global_scale: float = 2.0 ** -8,
                  process_group=None):
+        """`gate_up_weight` / `down_weight`: this rank's shards, already on the device (interleaved gate|up rows
+        of its intermediate slice; the matching k-slice of down), both in the tcgen05 layout."""
         import torch
 
-        from . import abi, host
-        hidden, intermediate = gate[0].shape[1] * 2, gate[0].shape[0]
-        check_shardable(hidden, intermediate, world)
-        if (intermediate // world) % 64 != 0:
-            raise ValueError("each rank's slice of the intermediate dimension must be a multiple of 64")
-        g, u, d = shard_mlp(gate, up, down, rank, world)
-        shard = intermediate // world
-        stream = plan.stream
-        self.gate_up = host.upload_gate_up_interleaved(stream, shard, hidden, g[0], g[1], g[2], u[0], u[1], u[2])
-        self.down = host.Nvfp4Sm100Weight.upload_checkpoint_nvfp4(stream, abi.LAYOUT_TCGEN05, hidden, shard, *d)
-        tokens = x.shape[0]
+        from . import host
+        self.gate_up, self.down = gate_up_weight, down_weight
+        tokens, hidden = x.shape
         self.out = torch.empty((tokens, hidden), dtype=torch.bfloat16, device=x.device)
         self.chunks = []
         for first in range(0, tokens, chunk_tokens):
@@ -198,9 +192,23 @@ class TensorParallelPrefillMlp:
                 plan, self.gate_up, self.down, x[first:last], out=self.out[first:last], terms=terms,
                 input_global_scale=input_global_scale, intermediate_global_scale=intermediate_global_scale))
         self.world, self.group, self.plan = world, process_group, plan
-        self.compute = stream.torch_stream
+        self.compute = plan.stream.torch_stream
         self.comm = torch.cuda.Stream(device=x.device) if world > 1 else None
         self.events = [torch.cuda.Event() for _ in self.chunks] if world > 1 else []
+
+    @classmethod
+    def from_checkpoint(cls, plan, gate, up, down, x, rank: int, world: int, **options):
+        """Shards full (codes, scales, global) matrices for `rank` and uploads the shards."""
+        from . import abi, host
+        hidden, intermediate = gate[0].shape[1] * 2, gate[0].shape[0]
+        check_shardable(hidden, intermediate, world)
+        if (intermediate // world) % 64 != 0:
+            raise ValueError("each rank's slice of the intermediate dimension must be a multiple of 64")
+        g, u, d = shard_mlp(gate, up, down, rank, world)
+        shard = intermediate // world
+        gate_up_weight = host.upload_gate_up_interleaved(plan.stream, shard, hidden, g[0], g[1], g[2], u[0], u[1], u[2])
+        down_weight = host.Nvfp4Sm100Weight.upload_checkpoint_nvfp4(plan.stream, abi.LAYOUT_TCGEN05, hidden, shard, *d)
+        return cls(plan, gate_up_weight, down_weight, x, world, **options)
 
     def submit(self) -> None:
         """Enqueue all chunks; when it returns, the compute stream is ordered after the last all-reduce."""

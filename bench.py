@@ -224,6 +224,57 @@ def prefill_probe(torch, host, abi, stream, device):
     return out
 
 
+def prefill_mlp_probe(torch, host, abi, stream, device, world, rank, tokens, chunk, terms):
+    """Config 4 (long-prefill chunked MLP, tensor-parallel): returns whole-job TFLOP/s of useful 2*M*N*K."""
+    import torch.distributed as dist
+
+    from augur_v100_b200 import synth, tp
+    generator = torch.Generator(device=device)
+    generator.manual_seed(4321 + rank)
+    shard = INTER // world
+    gc, gs = device_planes(torch, generator, shard, HIDDEN, device)
+    uc, us = device_planes(torch, generator, shard, HIDDEN, device)
+
+    def interleave(gate_plane, up_plane):   # 16 gate rows, then the matching 16 up rows
+        width = gate_plane.shape[1]
+        return torch.stack([gate_plane.view(shard // 16, 16, width), up_plane.view(shard // 16, 16, width)], dim=1).reshape(2 * shard, width).contiguous()
+
+    gate_up = host.Nvfp4Sm100Weight.repack_device_planes(stream, abi.LAYOUT_TCGEN05, 2 * shard, HIDDEN, interleave(gc, uc),
+                                                         interleave(gs, us), synth.GLOBAL_SCALE)
+    gate_up.global_scale_b = synth.GLOBAL_SCALE
+    dc, ds = device_planes(torch, generator, HIDDEN, shard, device)
+    down = host.Nvfp4Sm100Weight.repack_device_planes(stream, abi.LAYOUT_TCGEN05, HIDDEN, shard, dc, ds, synth.GLOBAL_SCALE)
+    del gc, gs, uc, us, dc, ds
+    plan = host.Plan(stream, 1 << 20)
+    x = torch.randn((tokens, HIDDEN), device=device, generator=generator).to(torch.bfloat16)
+    block = tp.TensorParallelPrefillMlp(plan, gate_up, down, x, world, chunk_tokens=chunk, terms=terms,
+                                        input_global_scale=2.0 ** -8, intermediate_global_scale=2.0 ** -6)
+    block.submit()
+    stream.synchronize()
+    if plan.device_status() != 0:
+        return {"error": f"device status {plan.device_status():#x}"}
+    if world > 1:
+        dist.barrier()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 3
+    start.record()
+    for _ in range(reps):
+        block.submit()
+    end.record()
+    end.synchronize()
+    ms = torch.tensor([start.elapsed_time(end) / reps], device=device)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms.item())
+    flops = 2.0 * tokens * 3 * HIDDEN * INTER
+    result = {"workload": f"chunked MLP, M={tokens} in chunks of {chunk}, hidden {HIDDEN}, intermediate {INTER}, tp{world}, "
+                          "per-chunk NCCL all-reduce overlapped with the next chunk",
+              "ms": ms, "tflops_useful": flops / ms / 1e9, "activation_terms": terms,
+              "finite": bool(torch.isfinite(block.out.float()).all())}
+    plan.close()
+    return result
+
+
 def run_library(args):
     import torch
     import torch.distributed as dist
@@ -240,6 +291,8 @@ def run_library(args):
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     if world > 1:
+        # NCCL writes its version / debug lines to stdout by default; stdout carries the one JSON line only
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=device)
 
     # Everything runs on one non-default stream, so that a step can also be captured into a CUDA graph.
@@ -352,6 +405,17 @@ def run_library(args):
     if status != 0:
         raise SystemExit(f"device status word {status:#x}")
 
+    prefill_mlp = None
+    if args.prefill_mlp:
+        # every rank takes part (collectives inside); the decode layers are released first
+        del programs, layers
+        torch.cuda.empty_cache()
+        prefill_mlp = {}
+        for terms in (1, 3):
+            prefill_mlp[f"terms_{terms}"] = prefill_mlp_probe(torch, host, abi, stream, device, world, rank,
+                                                              args.prefill_mlp_tokens, 4096, terms)
+        programs, layers = [], []
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -398,6 +462,8 @@ def run_library(args):
             del programs, layers
             torch.cuda.empty_cache()
             line["prefill"] = prefill_probe(torch, host, abi, stream, device)
+    if prefill_mlp is not None:
+        line["prefill_mlp"] = prefill_mlp
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -410,6 +476,9 @@ def main():
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", choices=["library", "reference"], default="library")
     parser.add_argument("--no-prefill", action="store_true", help="skip the M=4096 tcgen05 probe at N=1")
+    parser.add_argument("--prefill-mlp", action="store_true",
+                        help="also time the chunked tensor-parallel prefill MLP (reported under prefill_mlp)")
+    parser.add_argument("--prefill-mlp-tokens", type=int, default=32768)
     parser.add_argument("--allreduce", choices=["fused", "nccl"], default="fused",
                         help="N>1: all-reduce inside the down launch over peer memory, or NCCL on the BF16 partials")
     parser.add_argument("--layers", type=int, default=LAYERS,

@@ -104,7 +104,7 @@ def _prefill_worker(rank, world, port, queue, h_absmax):
         stream = host.Stream(rank, side)
         plan = host.Plan(stream, 1 << 20)
         x = torch.from_numpy(x_bits.view(np.int16)).to(torch.device("cuda", rank)).view(torch.bfloat16)
-        block = tp.TensorParallelPrefillMlp(
+        block = tp.TensorParallelPrefillMlp.from_checkpoint(
             plan, gate, up, down, x, rank, world, chunk_tokens=P_CHUNK, terms=3,
             input_global_scale=host.default_activation_global_scale(float(np.abs(synth.bf16_bits_to_f32(x_bits)).max())),
             intermediate_global_scale=host.default_activation_global_scale(h_absmax * 1.05))
