@@ -404,6 +404,112 @@ private:
     std::shared_ptr<DeviceBuffer> input_, staged_, output_;
 };
 
+// The gate and up matrices as ONE tcgen05 weight of 2 * inter rows, 16 gate rows alternating with the matching
+// 16 up rows: what the SwiGLU-fusing GEMM epilogue expects. rows() of the result is 2 * inter.
+inline std::shared_ptr<Nvfp4Sm100Weight> upload_gate_up_interleaved(const std::shared_ptr<Stream>& stream, uint32_t inter,
+                                                                   uint32_t hidden, const CheckpointNvfp4Matrix& gate,
+                                                                   const CheckpointNvfp4Matrix& up, float* up_global_scale_out) {
+    std::vector<uint8_t> codes(static_cast<size_t>(2) * inter * hidden / 2), scales(static_cast<size_t>(2) * inter * hidden / 16);
+    check("interleave_gate_up", augur_cuda_nvfp4_sm100_interleave_gate_up_host_v1(inter, hidden, gate.codes, gate.scales, up.codes,
+                                                                                 up.scales, codes.data(), scales.data()));
+    if (!(up.global_scale > 0.0f) || up.global_scale > 3.0e38f) throw std::invalid_argument("global scale must be finite and positive");
+    for (size_t i = static_cast<size_t>(inter) * hidden / 16; i-- > 0;) {
+        if (up.scales[i] >= 0x7f) throw std::invalid_argument("block scale byte is negative or NaN");
+    }
+    const CheckpointNvfp4Matrix both{codes.data(), scales.data(), gate.global_scale};
+    *up_global_scale_out = up.global_scale;
+    return Nvfp4Sm100Weight::upload_checkpoint_nvfp4(stream, AUGUR_NVFP4_SM100_LAYOUT_TCGEN05, 2 * inter, hidden, both);
+}
+
+// The MLP block for wide inputs (any token count): quantise x, gate|up GEMM with SiLU(gate)*up in its epilogue,
+// quantise the intermediate, down GEMM. Four launches; every member is preflighted at bind time.
+class Nvfp4Sm100PrefillFfnProgram {
+public:
+    static std::unique_ptr<Nvfp4Sm100PrefillFfnProgram> bind(std::shared_ptr<Plan> plan, std::shared_ptr<Nvfp4Sm100Weight> gate_up,
+                                                            float up_global_scale, std::shared_ptr<Nvfp4Sm100Weight> down,
+                                                            std::shared_ptr<DeviceBuffer> input, std::shared_ptr<DeviceBuffer> output,
+                                                            uint32_t tokens, uint32_t terms, float input_global_scale,
+                                                            float intermediate_global_scale) {
+        if (gate_up->layout() != AUGUR_NVFP4_SM100_LAYOUT_TCGEN05 || down->layout() != AUGUR_NVFP4_SM100_LAYOUT_TCGEN05) {
+            throw std::invalid_argument("both weights must be in the tcgen05 layout");
+        }
+        if (plan->stream() != gate_up->stream() || plan->stream() != down->stream()) {
+            throw std::invalid_argument("plan and weights belong to different streams");
+        }
+        const uint32_t hidden = gate_up->cols(), inter = gate_up->rows() / 2;
+        if (down->cols() != inter) throw std::invalid_argument("gate|up and down shapes do not fit together");
+        std::unique_ptr<Nvfp4Sm100PrefillFfnProgram> p(new Nvfp4Sm100PrefillFfnProgram());
+        const Stream& s = *plan->stream();
+        const int32_t d = s.ordinal();
+        p->intermediate_ = std::make_shared<DeviceBuffer>(d, static_cast<uint64_t>(tokens) * inter * 2);
+        p->staged_x_ = std::make_shared<DeviceBuffer>(d, gemm_scratch_bytes(gate_up->rows(), hidden, tokens, terms));
+        p->staged_h_ = std::make_shared<DeviceBuffer>(d, gemm_scratch_bytes(down->rows(), inter, tokens, terms));
+        auto quant = [&](const DeviceBuffer& source, const DeviceBuffer& staged, uint32_t cols, float scale) {
+            auto q = header<augur_cuda_nvfp4_sm100_act_quant_args_v1>();
+            q.input_bf16 = source.address();
+            q.input_len_bytes = static_cast<uint64_t>(tokens) * cols * 2;
+            q.destination = staged.address();
+            q.destination_len_bytes = staged.bytes();
+            q.tokens = tokens; q.cols = cols; q.terms = terms; q.global_scale = scale;
+            return q;
+        };
+        p->quant_x_ = quant(*input, *p->staged_x_, hidden, input_global_scale);
+        p->quant_h_ = quant(*p->intermediate_, *p->staged_h_, inter, intermediate_global_scale);
+        p->gate_up_args_ = header<augur_cuda_nvfp4_sm100_gemm_swiglu_args_v1>();
+        p->gate_up_args_.weight = gate_up->packed()->address();
+        p->gate_up_args_.weight_len_bytes = gate_up->packed()->bytes();
+        p->gate_up_args_.activation = p->staged_x_->address();
+        p->gate_up_args_.activation_len_bytes = p->staged_x_->bytes();
+        p->gate_up_args_.output_bf16 = p->intermediate_->address();
+        p->gate_up_args_.output_len_bytes = static_cast<uint64_t>(tokens) * inter * 2;
+        p->gate_up_args_.rows = inter; p->gate_up_args_.cols = hidden; p->gate_up_args_.tokens = tokens;
+        p->gate_up_args_.activation_terms = terms;
+        p->gate_up_args_.gate_global_scale = gate_up->global_scale();
+        p->gate_up_args_.up_global_scale = up_global_scale;
+        p->gate_up_args_.activation_global_scale = input_global_scale;
+        p->down_args_ = header<augur_cuda_nvfp4_sm100_gemm_args_v1>();
+        p->down_args_.weight = down->packed()->address();
+        p->down_args_.weight_len_bytes = down->packed()->bytes();
+        p->down_args_.activation = p->staged_h_->address();
+        p->down_args_.activation_len_bytes = p->staged_h_->bytes();
+        p->down_args_.output_bf16 = output->address();
+        p->down_args_.output_len_bytes = static_cast<uint64_t>(tokens) * down->rows() * 2;
+        p->down_args_.rows = down->rows(); p->down_args_.cols = inter; p->down_args_.tokens = tokens;
+        p->down_args_.activation_terms = terms;
+        p->down_args_.weight_global_scale = down->global_scale();
+        p->down_args_.activation_global_scale = intermediate_global_scale;
+        check("act_quant_preflight", augur_cuda_nvfp4_sm100_act_quant_preflight_v1(d, s.handle(), &p->quant_x_));
+        check("gemm_swiglu_preflight", augur_cuda_nvfp4_sm100_gemm_swiglu_bf16_preflight_v1(d, s.handle(), plan->raw(), &p->gate_up_args_));
+        check("act_quant_preflight", augur_cuda_nvfp4_sm100_act_quant_preflight_v1(d, s.handle(), &p->quant_h_));
+        check("gemm_bf16_preflight", augur_cuda_nvfp4_sm100_gemm_bf16_preflight_v1(d, s.handle(), plan->raw(), &p->down_args_));
+        p->plan_ = std::move(plan);
+        p->gate_up_ = std::move(gate_up);
+        p->down_ = std::move(down);
+        p->input_ = std::move(input);
+        p->output_ = std::move(output);
+        return p;
+    }
+    void submit_for_plan() const {
+        const Stream& s = *plan_->stream();
+        const int32_t d = s.ordinal();
+        check("act_quant_submit", augur_cuda_nvfp4_sm100_act_quant_prevalidated_submit_v1(d, s.handle(), &quant_x_));
+        check("gemm_swiglu_submit", augur_cuda_nvfp4_sm100_gemm_swiglu_bf16_prevalidated_submit_v1(d, s.handle(), plan_->raw(), &gate_up_args_));
+        check("act_quant_submit", augur_cuda_nvfp4_sm100_act_quant_prevalidated_submit_v1(d, s.handle(), &quant_h_));
+        check("gemm_bf16_submit", augur_cuda_nvfp4_sm100_gemm_bf16_prevalidated_submit_v1(d, s.handle(), plan_->raw(), &down_args_));
+    }
+    const std::shared_ptr<DeviceBuffer>& intermediate() const { return intermediate_; }
+    const std::shared_ptr<DeviceBuffer>& output() const { return output_; }
+
+private:
+    Nvfp4Sm100PrefillFfnProgram() = default;
+    augur_cuda_nvfp4_sm100_act_quant_args_v1 quant_x_{}, quant_h_{};
+    augur_cuda_nvfp4_sm100_gemm_swiglu_args_v1 gate_up_args_{};
+    augur_cuda_nvfp4_sm100_gemm_args_v1 down_args_{};
+    std::shared_ptr<Plan> plan_;
+    std::shared_ptr<Nvfp4Sm100Weight> gate_up_, down_;
+    std::shared_ptr<DeviceBuffer> input_, intermediate_, staged_x_, staged_h_, output_;
+};
+
 // The reference's batch classes (crates/augur-kernel-api/src/key.rs:354-365): up to 8 token rows are the
 // small-batch class (decode and the fixed B8 verify batch), anything wider is prefill.
 enum class BatchClass { SmallBatch, Prefill };

@@ -204,6 +204,38 @@ int main() {
             std::printf("prefill: rms err %.3e\n", e);
             expect(e <= 2e-2, "prefill (3 terms) within 2e-2 (rms) of the fp64 oracle");
         }
+        // ---- prefill FFN program with the SwiGLU fused into the gate|up GEMM, 200 token rows (ragged last tile) ----
+        {
+            const uint32_t wide = 200, terms = 3;
+            std::vector<uint16_t> a(wide * hidden);
+            for (auto& v : a) v = to_bf16(static_cast<float>(rng.normal()));
+            std::vector<double> h64(static_cast<size_t>(wide) * inter), y64(static_cast<size_t>(wide) * hidden);
+            expect(augur_oracle_mlp_f64(gate.codes.data(), gate.scales.data(), gate.global, up.codes.data(), up.scales.data(), up.global,
+                                        down.codes.data(), down.scales.data(), down.global, hidden, inter, a.data(), wide,
+                                        h64.data(), y64.data(), threads) == 0, "oracle prefill mlp");
+            double x_max = 0.0, h_max = 0.0;
+            for (uint16_t v : a) x_max = std::fmax(x_max, std::fabs(from_bf16(v)));
+            for (double v : h64) h_max = std::fmax(h_max, std::fabs(v));
+            float up_scale = 0.0f;
+            auto wide_gate_up = upload_gate_up_interleaved(stream, inter, hidden, gate_m, up_m, &up_scale);
+            auto wide_down = Nvfp4Sm100Weight::upload_checkpoint_nvfp4(stream, AUGUR_NVFP4_SM100_LAYOUT_TCGEN05, hidden, inter, down_m);
+            auto a_dev = std::make_shared<DeviceBuffer>(0, a.size() * 2);
+            auto out = std::make_shared<DeviceBuffer>(0, static_cast<uint64_t>(wide) * hidden * 2);
+            a_dev->upload(*stream, a.data(), a.size() * 2);
+            auto wide_plan = std::make_shared<Plan>(stream, 4096);
+            auto ffn = Nvfp4Sm100PrefillFfnProgram::bind(wide_plan, wide_gate_up, up_scale, wide_down, a_dev, out, wide, terms,
+                                                         static_cast<float>(x_max / (448.0 * 6.0)),
+                                                         static_cast<float>(h_max * 1.05 / (448.0 * 6.0)));
+            ffn->submit_for_plan();
+            std::vector<uint16_t> got(static_cast<size_t>(wide) * hidden);
+            out->download(*stream, got.data(), got.size() * 2);
+            expect(wide_plan->device_status() == 0, "prefill FFN device status word clean");
+            std::vector<double> have(got.size());
+            for (size_t i = 0; i < got.size(); ++i) have[i] = from_bf16(got[i]);
+            const double e = rms_error(have, y64);
+            std::printf("prefill ffn: rms err %.3e\n", e);
+            expect(e <= 2e-2, "prefill FFN within 2e-2 (rms) of the fp64 oracle");
+        }
     } catch (const std::exception& error) {
         std::printf("FAILED: exception: %s\n", error.what());
         return 1;
