@@ -42,6 +42,7 @@ constexpr uint32_t kScaleScratchBytes = 1024;   // per warp: the f32 block scale
 constexpr uint32_t kWaitLimit = 1u << 18;   // bounded polls of a ring slot before the kernel gives up
 constexpr uint32_t kMaxSlabBlocks = 40;    // 40 * 128 k = 5120 activations columns per slab (80 KB)
 constexpr uint32_t kSlotFloats = 256;      // one partial tile: 32 lanes x 8 f32
+constexpr uint32_t kCombineBlocks = 48;    // weight blocks a CTA streams in the time of one cross-CTA combine
 // Plan scratch layout: two arrival-counter regions (one per member of a two-launch program)
 // at fixed offsets, then partial-sum slots. Counters must read zero when a launch starts and
 // every launch leaves them at zero; keeping them apart from the slots means no launch of any
@@ -96,10 +97,19 @@ GemvGeometry geometry(uint32_t rows, uint32_t cols, bool pair, uint32_t sm_count
     const uint32_t min_kbs = g.kb_count / g.slabs;
     // CTAs never wait on one another, so the grid may exceed the SM count when slabs > SMs.
     uint64_t per_slab = sm_count / g.slabs ? sm_count / g.slabs : 1;
-    // With one k-slab and plenty of row groups per CTA, spans are cut at row-group boundaries:
-    // every group is then finished inside one CTA (no scratch, no fences) at the price of at
-    // most one group of imbalance. Otherwise spans are cut at single blocks.
-    g.unit = (g.slabs == 1 && g.groups >= 4 * per_slab && split_mode() != 1) ? min_kbs : 1;
+    // With one k-slab, spans may be cut at row-group boundaries: every group is then finished inside
+    // one CTA (no scratch, no fences, no atomics) at the price of whole groups of imbalance; cutting at
+    // single blocks balances perfectly but ends every launch with the cross-CTA combine. The first wins
+    // while the imbalance, in blocks per CTA, stays below what that combine costs (about 3 us, the time
+    // a CTA streams kCombineBlocks blocks in).
+    bool aligned = false;
+    if (g.slabs == 1 && split_mode() != 1) {
+        const uint64_t ctas = per_slab < g.groups ? per_slab : g.groups;
+        const uint64_t most = (g.groups + ctas - 1) / ctas;                  // groups of the busiest CTA
+        // imbalance = most - groups / sm_count groups, compared in blocks and scaled by sm_count to stay in integers
+        aligned = (most * sm_count - g.groups) * min_kbs <= static_cast<uint64_t>(kCombineBlocks) * sm_count;
+    }
+    g.unit = aligned ? min_kbs : 1;
     const uint64_t least_units = static_cast<uint64_t>(g.groups) * min_kbs / g.unit;
     if (per_slab > least_units) per_slab = least_units;  // every CTA owns at least one unit
     g.ctas_per_slab = static_cast<uint32_t>(per_slab);

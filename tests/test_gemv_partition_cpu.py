@@ -16,8 +16,14 @@ def geometry(rows, cols, pair, sms):
     kb = cols // 128
     slabs = (kb + MAX_SLAB - 1) // MAX_SLAB
     per_slab = max(sms // slabs, 1)
-    # one slab and many row groups per CTA: spans are cut at row-group boundaries (unit = blocks per group)
-    unit = kb // slabs if (slabs == 1 and groups >= 4 * per_slab) else 1
+    # one slab: spans are cut at row-group boundaries (unit = blocks per group) while the imbalance that costs,
+    # in blocks per CTA, stays below the price of a cross-CTA combine (48 blocks)
+    aligned = False
+    if slabs == 1:
+        ctas = min(per_slab, groups)
+        most = (groups + ctas - 1) // ctas
+        aligned = (most * sms - groups) * kb <= 48 * sms
+    unit = kb if aligned else 1
     per_slab = min(per_slab, groups * (kb // slabs) // unit)
     max_contrib = slabs * ((per_slab + groups - 1) // groups + 1)
     return groups, kb, slabs, per_slab, max_contrib, unit
