@@ -75,8 +75,12 @@ class ExchangeBuffers:
     """
 
     def __init__(self, hidden: int, rank: int, world: int, process_group=None):
+        import os
+
         import torch
         import torch.distributed as dist
+        # Only plain peer stores are used: the buffers need no NVLink multicast object bound to them.
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm
         group = process_group if process_group is not None else dist.group.WORLD
         self.rank, self.world, self.hidden = rank, world, hidden
@@ -92,7 +96,8 @@ class ExchangeBuffers:
         self.sequence = 0
 
     def next_sequence(self) -> int:
-        self.sequence += 1
+        # 1, 2, ..., 0xFFFFFFFE, 1, ...: never 0 (the value of a fresh buffer), and the parity alternates across the wrap
+        self.sequence = 1 if self.sequence >= 0xFFFFFFFE else self.sequence + 1
         return self.sequence
 
 
