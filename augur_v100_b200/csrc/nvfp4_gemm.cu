@@ -46,7 +46,7 @@ constexpr uint32_t kTmemSfB = 320;        // 2 x 32 columns
 constexpr uint32_t kWaitLimit = 20u * 1000u * 1000u;
 
 constexpr uint32_t kErrProducerWait = 0x101, kErrMmaWaitFull = 0x102, kErrMmaWaitTmem = 0x103,
-                   kErrEpilogueWait = 0x104;
+                   kErrEpilogueWait = 0x104, kErrCopyWait = 0x105, kErrMmaWaitScales = 0x106;
 
 // ---- PTX wrappers ---------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -373,6 +373,7 @@ constexpr uint32_t kPairStageBytes = kBytesA + kPairBytesB + kBytesSfA + kBytesS
 constexpr uint32_t kPairOutRowBytes = kTileN * 2 + 16;
 constexpr uint32_t kPairOutBytes = kTileM * kPairOutRowBytes;                          // 67584
 constexpr uint32_t kPairSmemBytes = kPairStages * kPairStageBytes + kPairOutBytes + 1024 + 256;
+constexpr uint32_t kPairThreads = 224;          // TMA warp, MMA warp, 4 epilogue warps, scale-copy warp
 constexpr uint32_t kLeaderMask = 0xFEFFFFFFu;   // clears the CTA-rank bit of a shared::cluster address within a pair
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -396,6 +397,10 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
                  ::"r"(bar), "h"(static_cast<uint16_t>(3))
                  : "memory");
 }
+// Arrives on this CTA's barrier only, once the cta_group::2 operations this thread issued so far are done.
+__device__ __forceinline__ void tc_commit_pair_local(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
 __device__ __forceinline__ void tc_copy_sf_pair(uint32_t tmem, uint64_t desc) {
     asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem), "l"(desc) : "memory");
 }
@@ -411,7 +416,7 @@ __device__ __forceinline__ void mbar_arrive_leader(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar & kLeaderMask) : "memory");
 }
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant__ CUtensorMap map_weight,
                  const __grid_constant__ CUtensorMap map_act_sf, const __grid_constant__ CUtensorMap map_weight_sf,
                  const GemmParams p) {
@@ -419,7 +424,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* out_stage = smem + kPairStages * kPairStageBytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(out_stage + kPairOutBytes);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kPairStages + 2);
+    // full[S], empty[S], tmem_full, tmem_empty, scales_full[2], scales_empty[2]; then the TMEM base and the abort flag
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kPairStages + 6);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -427,11 +433,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
     const uint32_t pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
     const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + kPairStages);
     const uint32_t bar_tmem_full = smem_u32(bars + 2 * kPairStages), bar_tmem_empty = smem_u32(bars + 2 * kPairStages + 1);
+    const uint32_t bar_scales_full = smem_u32(bars + 2 * kPairStages + 2), bar_scales_empty = smem_u32(bars + 2 * kPairStages + 4);
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kPairStages; ++s) {
             mbar_init(bar_full + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (uint32_t b = 0; b < 2; ++b) {
+            mbar_init(bar_scales_full + 8 * b, 1);
+            mbar_init(bar_scales_empty + 8 * b, 1);
         }
         mbar_init(bar_tmem_full, 1);
         mbar_init(bar_tmem_empty, 8);   // one arrival per epilogue warp of either CTA
@@ -453,7 +464,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
     const uint32_t m_pairs = p.padded_tokens / (2 * kTileM);
     const uint32_t n_tiles = p.rows / kTileN;
     const uint32_t total_tiles = m_pairs * n_tiles;
-    const uint32_t k_blocks = p.cols / kBlockK;
+    // A last k block that is only partly inside the tensor is loaded like the others (the TMA fills what lies past
+    // the edge); the MMA issuer only consumes the k steps inside.
+    const uint32_t k_blocks = (p.cols + kBlockK - 1) / kBlockK;
     const uint32_t steps = k_blocks * p.terms;
     const uint32_t atoms_per_row_block = p.cols / 64;
     const uint32_t act_term_atoms = p.padded_tokens / 128 * atoms_per_row_block;   // scale atoms of one activation term
@@ -487,47 +500,103 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
         }
     } else if (warp == 1 && lane == 0 && rank == 0) {
         // ---------------- MMA issuer (leader only) ----------------
-        uint32_t stage = 0, phase = 0, tmem_phase = 0, sf_buffer = 0;
+        // Issuing a tcgen05 operation keeps a thread busy for tens of cycles, and one thread issuing the
+        // 12 scale copies and the 4 MMAs of every stage could not keep the tensor pipe fed; the copies are
+        // issued by a thread of their own (below) into the double-buffered scale columns, this thread
+        // issues only the MMAs. Descriptors advance by additions (their low bits hold address >> 4).
+        uint32_t stage = 0, phase = 0, tmem_phase = 0, sf_buffer = 0, sf_phase = 0;
         bool alive = true;
         const uint32_t idesc = (1u << 7) | (1u << 10) | ((kTileN >> 3) << 17) | (((2 * kTileM) >> 4) << 24);
+        const uint32_t smem_base = smem_u32(smem);
+        const uint64_t a_desc0 = operand_desc(smem_base), b_desc0 = operand_desc(smem_base + kBytesA);
+        constexpr uint64_t kStageStep = kPairStageBytes >> 4;
+        const uint32_t last_k_steps = (p.cols - (k_blocks - 1) * kBlockK) / 64;   // 1..4 k steps of 64 in the last k block
         for (uint32_t tile = pair; alive && tile < total_tiles; tile += pairs) {
             // the epilogues of both CTAs must have drained the previous tile's accumulator
             if (!mbar_wait(bar_tmem_empty, tmem_phase ^ 1, abort_flag, p.status_word, kErrMmaWaitTmem)) break;
             tc_fence_after();
+            uint32_t accumulate = 0, term = 0, kb = 0;
             for (uint32_t step = 0; step < steps; ++step) {
-                if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status_word, kErrMmaWaitFull)) {
+                // operands in shared memory (TMA) and block scales in tensor memory (copy thread)
+                if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status_word, kErrMmaWaitFull) ||
+                    !mbar_wait(bar_scales_full + 8 * sf_buffer, sf_phase, abort_flag, p.status_word, kErrMmaWaitScales)) {
                     alive = false;
                     break;
                 }
                 tc_fence_after();
-                const uint32_t base = smem_u32(smem + stage * kPairStageBytes);
-                const uint32_t sfa_smem = base + kBytesA + kPairBytesB, sfb_smem = sfa_smem + kBytesSfA;
+                const uint64_t a_desc = a_desc0 + stage * kStageStep, b_desc = b_desc0 + stage * kStageStep;
                 const uint32_t tmem_sfa = tmem_base + kTmemSfA + sf_buffer * 16;
                 const uint32_t tmem_sfb = tmem_base + kTmemSfB + sf_buffer * 32;
-                const uint64_t a_desc = operand_desc(base), b_desc = operand_desc(base + kBytesA);
-                // all block scales of the stage first, then its four MMAs: the MMAs wait for the
-                // copies once per stage instead of once per MMA
-                for (uint32_t k = 0; k < 4; ++k) {
-#ifdef AUGUR_GEMM_PROBE_NO_SF_COPY
-                    if (step >= 2) break;
-#endif
-                    tc_copy_sf_pair(tmem_sfa + 4 * k, sf_desc(sfa_smem + k * kSfAtomBytes));
-                    tc_copy_sf_pair(tmem_sfb + 8 * k, sf_desc(sfb_smem + k * kSfAtomBytes));
-                    tc_copy_sf_pair(tmem_sfb + 8 * k + 4, sf_desc(sfb_smem + kBytesSfA + k * kSfAtomBytes));
+                // each MMA consumes 64 k = 32 bytes of every row: start address + 2; only k steps inside the tensor
+                const uint32_t k_steps = (kb + 1 < k_blocks) ? 4u : last_k_steps;
+                if (k_steps == 4) {
+#pragma unroll
+                    for (uint32_t k = 0; k < 4; ++k) {
+                        tc_mma_pair(tmem_base + kTmemAcc, a_desc + 2 * k, b_desc + 2 * k, idesc, tmem_sfa + 4 * k, tmem_sfb + 8 * k,
+                                    accumulate | k);
+                    }
+                } else {
+                    for (uint32_t k = 0; k < k_steps; ++k) {
+                        tc_mma_pair(tmem_base + kTmemAcc, a_desc + 2 * k, b_desc + 2 * k, idesc, tmem_sfa + 4 * k, tmem_sfb + 8 * k,
+                                    accumulate | k);
+                    }
                 }
-                for (uint32_t k = 0; k < 4; ++k) {
-                    // each MMA consumes 64 k = 32 bytes of every row: advance the start address by 32 >> 4
-                    tc_mma_pair(tmem_base + kTmemAcc, a_desc + 2 * k, b_desc + 2 * k, idesc, tmem_sfa + 4 * k,
-                                tmem_sfb + 8 * k, (step | k) ? 1u : 0u);
-                }
-                tc_commit_pair(bar_empty + 8 * stage);   // frees the stage in both CTAs
-                sf_buffer ^= 1;
+                accumulate = 1;
+                tc_commit_pair(bar_empty + 8 * stage);                     // frees the stage in both CTAs
+                tc_commit_pair_local(bar_scales_empty + 8 * sf_buffer);    // and this half of the scale columns
+                if ((sf_buffer ^= 1) == 0) sf_phase ^= 1;
+                if (++term == p.terms) { term = 0; ++kb; }
                 if (++stage == kPairStages) { stage = 0; phase ^= 1; }
             }
             if (alive) tc_commit_pair(bar_tmem_full);     // both accumulator halves complete
             tmem_phase ^= 1;
         }
-    } else if (warp >= 2) {
+    } else if (warp == 6 && lane == 0 && rank == 0) {
+        // ---------------- scale-copy issuer (leader only): shared memory -> tensor memory, both CTAs ----------------
+        uint32_t stage = 0, phase = 0, sf_buffer = 0, sf_phase = 0;
+        const uint32_t smem_base = smem_u32(smem);
+        const uint64_t sfa_desc0 = sf_desc(smem_base + kBytesA + kPairBytesB), sfb_desc0 = sf_desc(smem_base + kBytesA + kPairBytesB + kBytesSfA);
+        constexpr uint64_t kStageStep = kPairStageBytes >> 4, kAtomStep = kSfAtomBytes >> 4, kRowBlockStep = kBytesSfA >> 4;
+        const uint32_t last_k_steps = (p.cols - (k_blocks - 1) * kBlockK) / 64;
+        bool alive = true;
+        for (uint32_t tile = pair; alive && tile < total_tiles; tile += pairs) {
+            uint32_t term = 0, kb = 0;
+            for (uint32_t step = 0; step < steps; ++step) {
+                // the stage's scale atoms have landed, and the MMAs that read this half of the scale columns are done
+                if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status_word, kErrCopyWait) ||
+                    !mbar_wait(bar_scales_empty + 8 * sf_buffer, sf_phase ^ 1, abort_flag, p.status_word, kErrCopyWait)) {
+                    alive = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint64_t sfa_desc = sfa_desc0 + stage * kStageStep, sfb_desc = sfb_desc0 + stage * kStageStep;
+                const uint32_t tmem_sfa = tmem_base + kTmemSfA + sf_buffer * 16;
+                const uint32_t tmem_sfb = tmem_base + kTmemSfB + sf_buffer * 32;
+                const uint32_t k_steps = (kb + 1 < k_blocks) ? 4u : last_k_steps;
+                if (k_steps == 4) {
+#pragma unroll
+                    for (uint32_t k = 0; k < 4; ++k) {
+#ifdef AUGUR_GEMM_PROBE_NO_SF_COPY
+                        if (step >= 2) break;
+#endif
+                        tc_copy_sf_pair(tmem_sfa + 4 * k, sfa_desc + k * kAtomStep);
+                        tc_copy_sf_pair(tmem_sfb + 8 * k, sfb_desc + k * kAtomStep);
+                        tc_copy_sf_pair(tmem_sfb + 8 * k + 4, sfb_desc + kRowBlockStep + k * kAtomStep);
+                    }
+                } else {
+                    for (uint32_t k = 0; k < k_steps; ++k) {
+                        tc_copy_sf_pair(tmem_sfa + 4 * k, sfa_desc + k * kAtomStep);
+                        tc_copy_sf_pair(tmem_sfb + 8 * k, sfb_desc + k * kAtomStep);
+                        tc_copy_sf_pair(tmem_sfb + 8 * k + 4, sfb_desc + kRowBlockStep + k * kAtomStep);
+                    }
+                }
+                tc_commit_pair_local(bar_scales_full + 8 * sf_buffer);
+                if ((sf_buffer ^= 1) == 0) sf_phase ^= 1;
+                if (++term == p.terms) { term = 0; ++kb; }
+                if (++stage == kPairStages) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp >= 2 && warp < 6) {
         // ---------------- epilogue (both CTAs): own TMEM half -> BF16 -> global ----------------
         const uint32_t quadrant = warp & 3;
         uint32_t tmem_phase = 0;
@@ -901,8 +970,7 @@ augur_cuda_result_v1 launch_gemm(augur_cuda_stream_t s, const augur_cuda_nvfp4_s
     p.scale = a->weight_global_scale * a->activation_global_scale;
     p.scale_b = up_global_scale * a->activation_global_scale;
     p.swiglu = swiglu ? 1u : 0u;
-    if (pair_tiles_enabled() && padded % (2 * kTileM) == 0 && a->rows % kTileN == 0 && a->cols % kBlockK == 0 &&
-        plan->sm_count >= 2) {
+    if (pair_tiles_enabled() && padded % (2 * kTileM) == 0 && a->rows % kTileN == 0 && plan->sm_count >= 2) {
         // 256 x 256 tiles on pairs of CTAs (clusters of two); the grid is a whole number of pairs.
         CUtensorMap map_act_sf, map_weight_sf;
         const uint64_t atoms_per_row_block = a->cols / 64;
@@ -913,7 +981,7 @@ augur_cuda_result_v1 launch_gemm(augur_cuda_stream_t s, const augur_cuda_nvfp4_s
         }
         uint32_t pairs = (padded / (2 * kTileM)) * (a->rows / kTileN);
         if (pairs > plan->sm_count / 2) pairs = plan->sm_count / 2;
-        gemm_pair_kernel<<<2 * pairs, kGemmThreads, kPairSmemBytes, s->stream>>>(map_act, map_weight, map_act_sf, map_weight_sf, p);
+        gemm_pair_kernel<<<2 * pairs, kPairThreads, kPairSmemBytes, s->stream>>>(map_act, map_weight, map_act_sf, map_weight_sf, p);
         count_launch();
         return submitted();
     }

@@ -160,6 +160,12 @@ def test_gemm_any_token_count(ctx, tokens):
     _check_gemm(ctx, rows=512, cols=512, tokens=tokens, seed=11, terms=2 if tokens == 300 else 1)
 
 
+def test_gemm_pair_tile_ragged_k_and_tokens(ctx):
+    # 256 x 256 pair tile whose last k block is a quarter full and whose token rows end at 200 of 256
+    _check_gemm(ctx, rows=256, cols=320, tokens=200, seed=12)
+    _check_gemm(ctx, rows=512, cols=2176, tokens=256, seed=13, terms=2)    # the tp-8 k slice of the down projection
+
+
 def test_gemm_residual_terms(ctx):
     e1 = _check_gemm(ctx, rows=256, cols=1024, tokens=128, terms=1, seed=6)
     e3 = _check_gemm(ctx, rows=256, cols=1024, tokens=128, terms=3, seed=6)
