@@ -85,3 +85,24 @@ def test_two_gloo_ranks_all_reduce_to_the_full_result():
     _, full = oracle.mlp_f64(gate, up, down, HIDDEN, INTER, _x())
     rms = np.sqrt(np.mean(full * full))
     assert np.max(np.abs(reduced - full)) / rms <= 2e-2
+
+
+def test_exchange_sequence_never_yields_zero_and_alternates_parity_across_the_wrap():
+    from augur_v100_b200 import tp
+    exchange = tp.ExchangeBuffers.__new__(tp.ExchangeBuffers)   # the counter alone; no device is touched
+    exchange.sequence = 0
+    assert [exchange.next_sequence() for _ in range(3)] == [1, 2, 3]
+    exchange.sequence = 0xFFFFFFFC
+    wrapped = [exchange.next_sequence() for _ in range(4)]
+    assert wrapped == [0xFFFFFFFD, 0xFFFFFFFE, 1, 2]
+    assert all((a ^ b) & 1 for a, b in zip(wrapped, wrapped[1:]))
+
+
+def test_exchange_extent_matches_the_layout():
+    from augur_v100_b200 import tp
+    # [2 parities][world][hidden / 32 row groups] tiles of 256 {value, flag} pairs (8 bytes each)
+    assert tp.exchange_extent(5120, 8) == 2 * 8 * 160 * 256 * 8
+    assert tp.exchange_extent(1024, 2) == 2 * 2 * 32 * 2048
+    import pytest
+    with pytest.raises(ValueError):
+        tp.exchange_extent(5120, 9)
