@@ -907,7 +907,7 @@ bool check_gemv(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_p
 
 // `staged_out_offset` (non-zero): the SwiGLU result is also written, staged, at that offset of the plan
 // scratch. `input_is_staged`: the activations were staged there by the producing launch (fixed
-// exponent), so no staging kernel runs.
+// exponent) and are copied in as they are instead of being staged by the kernel.
 void launch_gemv(augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* plan,
                  const augur_cuda_nvfp4_sm100_gemv_args_v1* a, uint32_t member, uint64_t partial_offset,
                  uint64_t staged_out_offset = 0, bool input_is_staged = false,

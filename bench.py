@@ -4,7 +4,7 @@
     python bench.py --gpus N --steps K --warmup W            # this library (sm_100a kernels)
     python bench.py --impl reference --gpus N --steps K ...  # the reference's CPU path, timed on host cores
 
-Workload (BASELINE config 1): the 27B-class NVFP4 MLP block at the fixed 8-row
+Workload (configuration 1 of the benchmark definition): the 27B-class NVFP4 MLP block at the fixed 8-row
 verify batch — gate|up 5120 -> 2x17408 fused with SiLU(gate)*up, then down
 17408 -> 5120 — with synthetic weights of the benchmark's value distributions.
 One step streams LAYERS distinct layers (2.4 GB of weights at N=1, far more than

@@ -158,7 +158,7 @@ def test_f32_epilogue_returns_unrounded_sums(ctx):
 
 
 def test_config0_full_size_linear(ctx):
-    # BASELINE config 0: M=8, K=5120, N=17408, seed 0
+    # configuration 0 of the benchmark definition: M=8, K=5120, N=17408, seed 0
     rows, cols, tokens = 17408, 5120, 8
     host = ctx["host"]
     codes, scales, glob = synth.make_weight(0, 0, "weight", rows, cols)
