@@ -115,6 +115,15 @@ def test_whole_model_sweep_projection_shapes(ctx, rows, cols):
     assert rel_error(bits_from_torch_bf16(proj.out), y64) <= TOLERANCE
 
 
+@pytest.mark.parametrize("rows,cols,tokens", [(12288, 5120, 8), (1024, 5120, 8), (6144, 5120, 1), (5120, 6144, 8), (48 + 16, 5120, 8)])
+def test_attention_and_gdn_projection_shapes(ctx, rows, cols, tokens):
+    # the real model's attention / GDN projections (crates/augur-model-qwen35/src/checkpoint_profile.rs:29-104):
+    # 12288 / 1024 / 6144 x 5120 inputs, 5120 x 6144 output; the 48-row gates are padded to the 32-row group (64)
+    codes, scales, glob, x_bits, proj = _linear_case(ctx, rows, cols, tokens, seed=rows // 64 + cols // 128 + tokens)
+    y64 = oracle.linear_f64(codes, scales, glob, rows, cols, x_bits, threads=oracle.max_threads())
+    assert rel_error(bits_from_torch_bf16(proj.out), y64) <= TOLERANCE
+
+
 def test_one_hot_activations_read_back_the_weights_exactly(ctx):
     # x = e_k makes y[n] = bf16(w[n][k]): checks every fragment position of the layout
     rows, cols, tokens = 64, 256, 8
