@@ -774,10 +774,15 @@ __global__ void act_quant_kernel(const uint16_t* __restrict__ x, uint8_t* __rest
             packed[i >> 3] |= code << (4 * (i & 7));
             residual[i] = __fsub_rn(residual[i], __fmul_rn(level, divisor));
         }
+#ifdef AUGUR_QUANT_PROBE_NO_CODE_STORE
+        if (packed[0] == 0x12345678u)
+#endif
         *reinterpret_cast<uint2*>(destination + term * code_bytes + static_cast<uint64_t>(token) * (cols / 2) + group * 8) =
             make_uint2(packed[0], packed[1]);
+#ifndef AUGUR_QUANT_PROBE_NO_SCALE_STORE
         destination[terms * code_bytes + term * scale_bytes + tcgen05_scale_offset(token, group, cols)] =
             static_cast<uint8_t>(scale_code);
+#endif
     }
 }
 
