@@ -713,18 +713,34 @@ __device__ __forceinline__ uint32_t e2m1_nearest(float v, float* level) {
     return negative ? (m | 8u) : m;
 }
 
-// x / d, correctly rounded, for many x and one d: with y = RN(1/d), two Newton steps on the quotient
-// (each an exact FMA residual) end on the correctly rounded quotient whenever nothing leaves the
-// normal range on the way; `safe` says so for this x (the caller falls back to a full division
-// otherwise, and d itself is checked once per group).
-__device__ __forceinline__ float divide_by(float x, float d, float y, bool d_safe) {
-    const uint32_t field = (__float_as_uint(x) >> 23) & 0xffu;
-    if (!d_safe || field < 64u || field > 190u) return __fdiv_rn(x, d);   // zero and tiny values come here too
-    float q = x * y;
-    float r = fmaf(-q, d, x);
-    q = fmaf(r, y, q);
-    r = fmaf(-q, d, x);
-    return fmaf(r, y, q);
+// The 16 quotients of a group share one divisor. With y = RN(1/d), two Newton steps on the quotient (each
+// an exact FMA residual) end on the correctly rounded x / d whenever d and x are well inside the normal
+// range and d is not of the all-ones mantissa form; the kernel checks that once per group (`kFast`) and
+// otherwise divides. An x below 2^-65 (d is at least 2^-63 here) has a quotient under a quarter, i.e. code 0
+// whatever the last bits are, and is not sent through the steps, which could leave the normal range.
+template <bool kFast>
+__device__ __forceinline__ void quantise_group(float (&residual)[16], float divisor, float reciprocal, bool more_terms,
+                                               uint32_t (&packed)[2]) {
+#pragma unroll
+    for (uint32_t i = 0; i < 16; ++i) {
+        const float x = residual[i];
+        float normalized;
+        if (kFast) {
+            float q = x * reciprocal;
+            float r = fmaf(-q, divisor, x);
+            q = fmaf(r, reciprocal, q);
+            r = fmaf(-q, divisor, x);
+            q = fmaf(r, reciprocal, q);
+            normalized = fabsf(x) < 0x1p-65f ? 0.0f : q;
+        } else {
+            normalized = divisor == 0.0f ? 0.0f : __fdiv_rn(x, divisor);
+        }
+        normalized = fminf(fmaxf(normalized, -6.0f), 6.0f);
+        float level;
+        const uint32_t code = e2m1_nearest(normalized, &level);
+        packed[i >> 3] |= code << (4 * (i & 7));
+        if (more_terms) residual[i] = __fsub_rn(x, __fmul_rn(level, divisor));
+    }
 }
 
 // One thread per (token, 16-element group). Destination: the code planes of all terms
@@ -733,9 +749,10 @@ __device__ __forceinline__ float divide_by(float x, float d, float y, bool d_saf
 __global__ void act_quant_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ destination, uint32_t tokens,
                                  uint32_t cols, uint32_t terms, float global_scale) {
     const uint32_t groups = cols / 16;
-    const uint64_t index = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (index >= static_cast<uint64_t>(tokens) * groups) return;
-    const uint32_t token = static_cast<uint32_t>(index / groups), group = static_cast<uint32_t>(index % groups);
+    // tokens * cols fits 32 bits, so the group index does too
+    const uint32_t index = blockIdx.x * blockDim.x + threadIdx.x;
+    if (index >= tokens * groups) return;
+    const uint32_t token = index / groups, group = index - token * groups;
     const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<uint64_t>(token) * cols + group * 16);
     const uint4 lo = __ldg(src), hi = __ldg(src + 1);
     const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
@@ -760,29 +777,28 @@ __global__ void act_quant_kernel(const uint16_t* __restrict__ x, uint8_t* __rest
             scale = e4m3_positive_value(scale_code);
         }
         const float divisor = __fmul_rn(scale, global_scale);
-        const uint32_t divisor_field = (__float_as_uint(divisor) >> 23) & 0xffu;
-        // the shortcut needs a divisor well inside the normal range and not of the all-ones mantissa form
-        const bool divisor_safe = divisor_field >= 64u && divisor_field <= 190u && (__float_as_uint(divisor) & 0x7fffffu) != 0x7fffffu;
-        const float reciprocal = divisor_safe ? __frcp_rn(divisor) : 0.0f;
+        const uint32_t divisor_field = (__float_as_uint(divisor) >> 23) & 0xffu, largest_field = (__float_as_uint(maximum) >> 23) & 0xffu;
+        const bool fast = divisor_field >= 64u && divisor_field <= 190u && (__float_as_uint(divisor) & 0x7fffffu) != 0x7fffffu &&
+                          largest_field <= 190u;
         uint32_t packed[2] = {0, 0};
-#pragma unroll
-        for (uint32_t i = 0; i < 16; ++i) {
-            float normalized = divisor == 0.0f ? 0.0f : divide_by(residual[i], divisor, reciprocal, divisor_safe);
-            normalized = fminf(fmaxf(normalized, -6.0f), 6.0f);
-            float level;
-            const uint32_t code = e2m1_nearest(normalized, &level);
-            packed[i >> 3] |= code << (4 * (i & 7));
-            residual[i] = __fsub_rn(residual[i], __fmul_rn(level, divisor));
+        if (fast) {
+            quantise_group<true>(residual, divisor, __frcp_rn(divisor), term + 1 < terms, packed);
+        } else {
+            quantise_group<false>(residual, divisor, 0.0f, term + 1 < terms, packed);
         }
-#ifdef AUGUR_QUANT_PROBE_NO_CODE_STORE
-        if (packed[0] == 0x12345678u)
-#endif
         *reinterpret_cast<uint2*>(destination + term * code_bytes + static_cast<uint64_t>(token) * (cols / 2) + group * 8) =
             make_uint2(packed[0], packed[1]);
-#ifndef AUGUR_QUANT_PROBE_NO_SCALE_STORE
-        destination[terms * code_bytes + term * scale_bytes + tcgen05_scale_offset(token, group, cols)] =
-            static_cast<uint8_t>(scale_code);
-#endif
+        // The scales of four consecutive groups of a token are four consecutive bytes of an atom: lanes are
+        // consecutive groups (cols / 16 is a multiple of 4, so a quad of lanes never straddles a token or the
+        // end of the grid), and the first lane of every quad stores the four as one word.
+        const uint32_t active = __activemask();
+        uint32_t quad = scale_code;
+        quad |= __shfl_down_sync(active, scale_code, 1) << 8;
+        quad |= __shfl_down_sync(active, scale_code, 2) << 16;
+        quad |= __shfl_down_sync(active, scale_code, 3) << 24;
+        if ((group & 3u) == 0) {
+            *reinterpret_cast<uint32_t*>(destination + terms * code_bytes + term * scale_bytes + tcgen05_scale_offset(token, group, cols)) = quad;
+        }
     }
 }
 
