@@ -119,6 +119,17 @@ class GemmSwigluArgs(Structure):
                 ("reserved", c_uint32)]
 
 
+class GemmSwigluQuantArgs(Structure):
+    _fields_ = [("abi_version", c_uint32), ("struct_size", c_uint32),
+                ("weight", c_uint64), ("weight_len_bytes", c_uint64),
+                ("activation", c_uint64), ("activation_len_bytes", c_uint64),
+                ("output_bf16", c_uint64), ("output_len_bytes", c_uint64),
+                ("destination", c_uint64), ("destination_len_bytes", c_uint64),
+                ("rows", c_uint32), ("cols", c_uint32), ("tokens", c_uint32), ("activation_terms", c_uint32),
+                ("gate_global_scale", c_float), ("up_global_scale", c_float), ("activation_global_scale", c_float),
+                ("destination_global_scale", c_float), ("destination_terms", c_uint32), ("reserved", c_uint32)]
+
+
 # Every symbol the header declares: name -> (restype, argtypes).
 _U8P = POINTER(c_uint8)
 EXPORTS = {
@@ -158,6 +169,8 @@ EXPORTS = {
     "augur_cuda_nvfp4_sm100_gemm_bf16_prevalidated_submit_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(GemmArgs)]),
     "augur_cuda_nvfp4_sm100_gemm_swiglu_bf16_preflight_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(GemmSwigluArgs)]),
     "augur_cuda_nvfp4_sm100_gemm_swiglu_bf16_prevalidated_submit_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(GemmSwigluArgs)]),
+    "augur_cuda_nvfp4_sm100_gemm_swiglu_quant_preflight_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(GemmSwigluQuantArgs)]),
+    "augur_cuda_nvfp4_sm100_gemm_swiglu_quant_prevalidated_submit_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(GemmSwigluQuantArgs)]),
     "augur_cuda_nvfp4_sm100_interleave_gate_up_host_v1": (Result, [c_uint32, c_uint32, _U8P, _U8P, _U8P, _U8P, _U8P, _U8P]),
     "augur_cuda_nvfp4_sm100_diagnostic_inject_submit_fault_v1": (None, [c_uint32]),
     "augur_cuda_nvfp4_sm100_allocation_snapshot_v1": (None, [POINTER(c_uint64), POINTER(c_uint64)]),

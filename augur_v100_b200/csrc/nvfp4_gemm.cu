@@ -153,7 +153,115 @@ struct GemmParams {
     float scale;                   // g_w * g_a
     float scale_b;                 // SwiGLU: g_w of the up rows * g_a
     uint32_t swiglu;               // weight rows alternate 16 gate / 16 up; output is bf16(silu(gate) * up), rows / 2 wide
+    // SwiGLU on pair tiles only: the intermediate is also (or only, if `out` is null) quantised for the next GEMM
+    uint8_t* quant_out;            // staged activations: [terms] code planes of whole tiles, then the scale regions
+    uint32_t quant_terms;
+    float quant_global_scale;
 };
+
+// ---- activation quantiser ------------------------------------------------------------------
+__host__ __device__ constexpr uint32_t padded_tokens(uint32_t tokens) { return (tokens + kTileM - 1) / kTileM * kTileM; }
+// Bytes of the staged activations of one term: code plane of whole tiles, then the scale atoms.
+__host__ __device__ constexpr uint64_t staged_term_bytes(uint32_t tokens, uint32_t cols) {
+    return tcgen05_extent_bytes(padded_tokens(tokens), cols);
+}
+
+// Smallest positive E4M3 code whose value is >= d (d > 0), 126 if none.
+__device__ __forceinline__ uint32_t e4m3_ceil_code(float d) {
+    if (d > 448.0f) return 126;
+    if (d <= 0x1p-6f) {                          // subnormal range: multiples of 2^-9, and 2^-6 itself
+        const float steps = d * 512.0f;          // exact
+        uint32_t m = static_cast<uint32_t>(ceilf(steps));
+        return m < 1 ? 1 : m;                     // m == 8 is code 8 = 2^-6
+    }
+    const uint32_t bits = __float_as_uint(d);
+    uint32_t exponent = (bits >> 23) - 127 + 7;  // E4M3 biased exponent, >= 1 here
+    uint32_t mantissa = (bits >> 20) & 7;
+    if (bits & 0xfffffu) ++mantissa;             // round up
+    if (mantissa == 8) { mantissa = 0; ++exponent; }
+    return exponent * 8 + mantissa;
+}
+
+__device__ __forceinline__ float e4m3_positive_value(uint32_t code) {
+    const uint32_t exponent = code >> 3, mantissa = code & 7;
+    return exponent == 0 ? static_cast<float>(mantissa) * 0x1p-9f
+                         : __uint_as_float(((exponent + 120) << 23) | (mantissa << 20));
+}
+
+// Nearest E2M1 level; a tie goes to the smaller magnitude; zero is always code 0. |v| <= 6.
+// From 1 upward E2M1 is a float with one mantissa bit, so rounding the f32 pattern to that bit with
+// "ties down" (add half an ulp minus one, truncate) gives exponent and mantissa at once:
+// 1 -> code 2, 1.5 -> 3, 2 -> 4, 3 -> 5, 4 -> 6, 6 -> 7. Below 1 the levels are 0, 0.5 and 1.
+__device__ __forceinline__ uint32_t e2m1_nearest(float v, float* level) {
+    const float a = fabsf(v);
+    uint32_t m;
+    if (a < 1.0f) {
+        m = (a > 0.25f ? 1u : 0u) + (a > 0.75f ? 1u : 0u);
+    } else {
+        m = ((__float_as_uint(a) + 0x1fffffu) >> 22) - 252u;
+    }
+    const float l = m < 2 ? 0.5f * static_cast<float>(m) : __uint_as_float((m + 252u) << 22);
+    const bool negative = v < 0.0f && m != 0;
+    *level = negative ? -l : l;
+    return negative ? (m | 8u) : m;
+}
+
+// The 16 quotients of a group share one divisor. With y = RN(1/d), two Newton steps on the quotient (each
+// an exact FMA residual) end on the correctly rounded x / d whenever d and x are well inside the normal
+// range and d is not of the all-ones mantissa form; the kernel checks that once per group (`kFast`) and
+// otherwise divides. An x below 2^-65 (d is at least 2^-63 here) has a quotient under a quarter, i.e. code 0
+// whatever the last bits are, and is not sent through the steps, which could leave the normal range.
+template <bool kFast>
+__device__ __forceinline__ void quantise_group(float (&residual)[16], float divisor, float reciprocal, bool more_terms,
+                                               uint32_t (&packed)[2]) {
+#pragma unroll
+    for (uint32_t i = 0; i < 16; ++i) {
+        const float x = residual[i];
+        float normalized;
+        if (kFast) {
+            float q = x * reciprocal;
+            float r = fmaf(-q, divisor, x);
+            q = fmaf(r, reciprocal, q);
+            r = fmaf(-q, divisor, x);
+            q = fmaf(r, reciprocal, q);
+            normalized = fabsf(x) < 0x1p-65f ? 0.0f : q;
+        } else {
+            normalized = divisor == 0.0f ? 0.0f : __fdiv_rn(x, divisor);
+        }
+        normalized = fminf(fmaxf(normalized, -6.0f), 6.0f);
+        float level;
+        const uint32_t code = e2m1_nearest(normalized, &level);
+        packed[i >> 3] |= code << (4 * (i & 7));
+        if (more_terms) residual[i] = __fsub_rn(x, __fmul_rn(level, divisor));
+    }
+}
+
+// One residual term of one 16-element group: the block scale (smallest E4M3 value >= amax / (6 g)), the 16 codes
+// (nearest level of x / (scale * g), ties toward zero) and, if another term follows, the residual it quantises.
+__device__ __forceinline__ void quantise_term(float (&residual)[16], float global_scale, bool more_terms, uint32_t (&packed)[2],
+                                              uint32_t* scale_code_out) {
+    float maximum = 0.0f;
+#pragma unroll
+    for (uint32_t i = 0; i < 16; ++i) maximum = fmaxf(maximum, fabsf(residual[i]));
+    const float desired = __fdiv_rn(maximum, __fmul_rn(6.0f, global_scale));
+    uint32_t scale_code = 0;
+    float scale = 0.0f;
+    if (desired > 0.0f) {
+        scale_code = e4m3_ceil_code(desired);
+        scale = e4m3_positive_value(scale_code);
+    }
+    const float divisor = __fmul_rn(scale, global_scale);
+    const uint32_t divisor_field = (__float_as_uint(divisor) >> 23) & 0xffu, largest_field = (__float_as_uint(maximum) >> 23) & 0xffu;
+    const bool fast = divisor_field >= 64u && divisor_field <= 190u && (__float_as_uint(divisor) & 0x7fffffu) != 0x7fffffu &&
+                      largest_field <= 190u;
+    packed[0] = packed[1] = 0;
+    if (fast) {
+        quantise_group<true>(residual, divisor, __frcp_rn(divisor), more_terms, packed);
+    } else {
+        quantise_group<false>(residual, divisor, 0.0f, more_terms, packed);
+    }
+    *scale_code_out = scale_code;
+}
 
 // 32 accumulator columns of one token row -> packed BF16. Plain: 32 outputs. SwiGLU: the weight rows
 // alternate 16 gate / 16 up, so columns 0..15 are gate sums and 16..31 the matching up sums of 16
@@ -634,13 +742,51 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
             const uint32_t first_token = m_pair * 2 * kTileM + rank * kTileM + quadrant * 32;
             if (p.swiglu) {
                 const uint32_t out_width = p.rows / 2;
-                uint8_t* out_base = reinterpret_cast<uint8_t*>(p.out + static_cast<uint64_t>(first_token) * out_width + n_tile * (kTileN / 2));
+                if (p.out) {
+                    uint8_t* out_base = reinterpret_cast<uint8_t*>(p.out + static_cast<uint64_t>(first_token) * out_width + n_tile * (kTileN / 2));
 #pragma unroll 4
-                for (uint32_t r2 = 0; r2 < 32; r2 += 2) {
-                    const uint32_t r = r2 + (lane >> 4), piece = lane & 15;
-                    if (first_token + r >= p.tokens) continue;   // padding rows of the last tile are computed, never stored
-                    const uint4 value = *reinterpret_cast<const uint4*>(my_rows + r * kPairOutRowBytes + piece * 16);
-                    *reinterpret_cast<uint4*>(out_base + static_cast<uint64_t>(r) * out_width * 2 + piece * 16) = value;
+                    for (uint32_t r2 = 0; r2 < 32; r2 += 2) {
+                        const uint32_t r = r2 + (lane >> 4), piece = lane & 15;
+                        if (first_token + r >= p.tokens) continue;   // padding rows of the last tile are computed, never stored
+                        const uint4 value = *reinterpret_cast<const uint4*>(my_rows + r * kPairOutRowBytes + piece * 16);
+                        *reinterpret_cast<uint4*>(out_base + static_cast<uint64_t>(r) * out_width * 2 + piece * 16) = value;
+                    }
+                }
+                if (p.quant_out) {
+                    // The same BF16 values, quantised for the next GEMM while the next tile's MMAs run: a lane takes
+                    // one 16-value group (8 lanes per row, 4 rows per step); the 8 code bytes of a row's 8 groups are
+                    // 64 contiguous bytes, the scale bytes of 4 groups one word of an atom.
+                    const uint64_t code_bytes = tcgen05_codes_bytes(p.padded_tokens, out_width);
+                    const uint64_t scale_bytes = tcgen05_scale_bytes(p.padded_tokens, out_width);
+                    for (uint32_t r4 = 0; r4 < 32; r4 += 4) {
+                        const uint32_t r = r4 + (lane >> 3), piece = lane & 7;
+                        const uint32_t token = first_token + r, group = n_tile * (kTileN / 32) + piece;
+                        const uint4* src = reinterpret_cast<const uint4*>(my_rows + r * kPairOutRowBytes + piece * 32);
+                        const uint4 lo = src[0], hi = src[1];
+                        const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+                        float residual[16];
+#pragma unroll
+                        for (uint32_t i = 0; i < 8; ++i) {
+                            residual[2 * i] = __uint_as_float(words[i] << 16);
+                            residual[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000u);
+                        }
+                        for (uint32_t term = 0; term < p.quant_terms; ++term) {
+                            uint32_t codes[2], scale_code;
+                            quantise_term(residual, p.quant_global_scale, term + 1 < p.quant_terms, codes, &scale_code);
+                            uint32_t quad = scale_code;
+                            quad |= __shfl_down_sync(0xffffffffu, scale_code, 1) << 8;
+                            quad |= __shfl_down_sync(0xffffffffu, scale_code, 2) << 16;
+                            quad |= __shfl_down_sync(0xffffffffu, scale_code, 3) << 24;
+                            if (token < p.tokens) {
+                                *reinterpret_cast<uint2*>(p.quant_out + term * code_bytes + static_cast<uint64_t>(token) * (out_width / 2) + group * 8) =
+                                    make_uint2(codes[0], codes[1]);
+                                if ((piece & 3u) == 0) {
+                                    *reinterpret_cast<uint32_t*>(p.quant_out + p.quant_terms * code_bytes + term * scale_bytes +
+                                                                 tcgen05_scale_offset(token, group, out_width)) = quad;
+                                }
+                            }
+                        }
+                    }
                 }
             } else {
                 uint8_t* out_base = reinterpret_cast<uint8_t*>(p.out + static_cast<uint64_t>(first_token) * p.rows + n_tile * kTileN);
@@ -666,83 +812,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
     }
 }
 
-// ---- activation quantiser ------------------------------------------------------------------
-__host__ __device__ constexpr uint32_t padded_tokens(uint32_t tokens) { return (tokens + kTileM - 1) / kTileM * kTileM; }
-// Bytes of the staged activations of one term: code plane of whole tiles, then the scale atoms.
-__host__ __device__ constexpr uint64_t staged_term_bytes(uint32_t tokens, uint32_t cols) {
-    return tcgen05_extent_bytes(padded_tokens(tokens), cols);
-}
-
-// Smallest positive E4M3 code whose value is >= d (d > 0), 126 if none.
-__device__ __forceinline__ uint32_t e4m3_ceil_code(float d) {
-    if (d > 448.0f) return 126;
-    if (d <= 0x1p-6f) {                          // subnormal range: multiples of 2^-9, and 2^-6 itself
-        const float steps = d * 512.0f;          // exact
-        uint32_t m = static_cast<uint32_t>(ceilf(steps));
-        return m < 1 ? 1 : m;                     // m == 8 is code 8 = 2^-6
-    }
-    const uint32_t bits = __float_as_uint(d);
-    uint32_t exponent = (bits >> 23) - 127 + 7;  // E4M3 biased exponent, >= 1 here
-    uint32_t mantissa = (bits >> 20) & 7;
-    if (bits & 0xfffffu) ++mantissa;             // round up
-    if (mantissa == 8) { mantissa = 0; ++exponent; }
-    return exponent * 8 + mantissa;
-}
-
-__device__ __forceinline__ float e4m3_positive_value(uint32_t code) {
-    const uint32_t exponent = code >> 3, mantissa = code & 7;
-    return exponent == 0 ? static_cast<float>(mantissa) * 0x1p-9f
-                         : __uint_as_float(((exponent + 120) << 23) | (mantissa << 20));
-}
-
-// Nearest E2M1 level; a tie goes to the smaller magnitude; zero is always code 0. |v| <= 6.
-// From 1 upward E2M1 is a float with one mantissa bit, so rounding the f32 pattern to that bit with
-// "ties down" (add half an ulp minus one, truncate) gives exponent and mantissa at once:
-// 1 -> code 2, 1.5 -> 3, 2 -> 4, 3 -> 5, 4 -> 6, 6 -> 7. Below 1 the levels are 0, 0.5 and 1.
-__device__ __forceinline__ uint32_t e2m1_nearest(float v, float* level) {
-    const float a = fabsf(v);
-    uint32_t m;
-    if (a < 1.0f) {
-        m = (a > 0.25f ? 1u : 0u) + (a > 0.75f ? 1u : 0u);
-    } else {
-        m = ((__float_as_uint(a) + 0x1fffffu) >> 22) - 252u;
-    }
-    const float l = m < 2 ? 0.5f * static_cast<float>(m) : __uint_as_float((m + 252u) << 22);
-    const bool negative = v < 0.0f && m != 0;
-    *level = negative ? -l : l;
-    return negative ? (m | 8u) : m;
-}
-
-// The 16 quotients of a group share one divisor. With y = RN(1/d), two Newton steps on the quotient (each
-// an exact FMA residual) end on the correctly rounded x / d whenever d and x are well inside the normal
-// range and d is not of the all-ones mantissa form; the kernel checks that once per group (`kFast`) and
-// otherwise divides. An x below 2^-65 (d is at least 2^-63 here) has a quotient under a quarter, i.e. code 0
-// whatever the last bits are, and is not sent through the steps, which could leave the normal range.
-template <bool kFast>
-__device__ __forceinline__ void quantise_group(float (&residual)[16], float divisor, float reciprocal, bool more_terms,
-                                               uint32_t (&packed)[2]) {
-#pragma unroll
-    for (uint32_t i = 0; i < 16; ++i) {
-        const float x = residual[i];
-        float normalized;
-        if (kFast) {
-            float q = x * reciprocal;
-            float r = fmaf(-q, divisor, x);
-            q = fmaf(r, reciprocal, q);
-            r = fmaf(-q, divisor, x);
-            q = fmaf(r, reciprocal, q);
-            normalized = fabsf(x) < 0x1p-65f ? 0.0f : q;
-        } else {
-            normalized = divisor == 0.0f ? 0.0f : __fdiv_rn(x, divisor);
-        }
-        normalized = fminf(fmaxf(normalized, -6.0f), 6.0f);
-        float level;
-        const uint32_t code = e2m1_nearest(normalized, &level);
-        packed[i >> 3] |= code << (4 * (i & 7));
-        if (more_terms) residual[i] = __fsub_rn(x, __fmul_rn(level, divisor));
-    }
-}
-
+// ---- activation quantiser kernel ---------------------------------------------------------------
 // One thread per (token, 16-element group). Destination: the code planes of all terms
 // stacked ([terms][tokens][cols/2], one TMA tensor of terms*tokens rows), then the scale
 // regions of all terms.
@@ -766,26 +836,8 @@ __global__ void act_quant_kernel(const uint16_t* __restrict__ x, uint8_t* __rest
     // only ever feed output rows that are not stored)
     const uint64_t code_bytes = tcgen05_codes_bytes(padded_tokens(tokens), cols), scale_bytes = tcgen05_scale_bytes(tokens, cols);
     for (uint32_t term = 0; term < terms; ++term) {
-        float maximum = 0.0f;
-#pragma unroll
-        for (uint32_t i = 0; i < 16; ++i) maximum = fmaxf(maximum, fabsf(residual[i]));
-        const float desired = __fdiv_rn(maximum, __fmul_rn(6.0f, global_scale));
-        uint32_t scale_code = 0;
-        float scale = 0.0f;
-        if (desired > 0.0f) {
-            scale_code = e4m3_ceil_code(desired);
-            scale = e4m3_positive_value(scale_code);
-        }
-        const float divisor = __fmul_rn(scale, global_scale);
-        const uint32_t divisor_field = (__float_as_uint(divisor) >> 23) & 0xffu, largest_field = (__float_as_uint(maximum) >> 23) & 0xffu;
-        const bool fast = divisor_field >= 64u && divisor_field <= 190u && (__float_as_uint(divisor) & 0x7fffffu) != 0x7fffffu &&
-                          largest_field <= 190u;
-        uint32_t packed[2] = {0, 0};
-        if (fast) {
-            quantise_group<true>(residual, divisor, __frcp_rn(divisor), term + 1 < terms, packed);
-        } else {
-            quantise_group<false>(residual, divisor, 0.0f, term + 1 < terms, packed);
-        }
+        uint32_t packed[2], scale_code;
+        quantise_term(residual, global_scale, term + 1 < terms, packed, &scale_code);
         *reinterpret_cast<uint2*>(destination + term * code_bytes + static_cast<uint64_t>(token) * (cols / 2) + group * 8) =
             make_uint2(packed[0], packed[1]);
         // The scales of four consecutive groups of a token are four consecutive bytes of an atom: lanes are
@@ -885,9 +937,12 @@ bool check_act_quant(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm
     return !full || inspect_device_ranges(d, r, 2, failure);
 }
 
+// What `output_bf16` of a GEMM descriptor is: [tokens][rows], [tokens][rows / 2] (fused SwiGLU), or absent.
+enum class GemmOutput { kFull, kHalfWidth, kNone };
+
 bool check_gemm(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* plan,
                 const augur_cuda_nvfp4_sm100_gemm_args_v1* a, bool full, augur_cuda_result_v1* failure,
-                bool output_is_half_width = false) {
+                GemmOutput output = GemmOutput::kFull) {
     *failure = invalid();
     if (!header_ok(d, s, a)) {
         if (a && s && d >= 0 && s->ordinal == d && a->abi_version != AUGUR_CUDA_ABI_VERSION_V1) {
@@ -902,16 +957,23 @@ bool check_gemm(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_p
         return false;
     }
     if (a->weight_len_bytes != tcgen05_extent_bytes(a->rows, a->cols) ||
-        a->activation_len_bytes != a->activation_terms * staged_term_bytes(a->tokens, a->cols) ||
-        a->output_len_bytes != static_cast<uint64_t>(a->tokens) * (output_is_half_width ? a->rows / 2 : a->rows) * 2) {
+        a->activation_len_bytes != a->activation_terms * staged_term_bytes(a->tokens, a->cols)) {
         return false;
     }
-    const Range r[4] = {{a->weight, a->weight_len_bytes, 256},
-                        {a->activation, a->activation_len_bytes, 256},
-                        {a->output_bf16, a->output_len_bytes, 16},
-                        plan_scratch_range(plan)};
-    if (!all_disjoint(r, 4)) return false;
-    return !full || inspect_device_ranges(d, r, 3, failure);
+    Range r[4] = {{a->weight, a->weight_len_bytes, 256}, {a->activation, a->activation_len_bytes, 256}, plan_scratch_range(plan), {}};
+    size_t count = 3;
+    if (output != GemmOutput::kNone) {
+        const uint64_t width = output == GemmOutput::kHalfWidth ? a->rows / 2 : a->rows;
+        if (a->output_len_bytes != static_cast<uint64_t>(a->tokens) * width * 2) return false;
+        r[count++] = {a->output_bf16, a->output_len_bytes, 16};
+    } else if (a->output_bf16 || a->output_len_bytes) {
+        return false;
+    }
+    if (!all_disjoint(r, count)) return false;
+    if (!full) return true;
+    // the plan's scratch was inspected when the plan was made
+    if (!inspect_device_ranges(d, r, 2, failure)) return false;
+    return output == GemmOutput::kNone || inspect_device_ranges(d, r + 3, 1, failure);
 }
 
 }  // namespace
@@ -970,8 +1032,15 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_bf16
 namespace {
 // Enqueues the GEMM of a validated descriptor. `swiglu`: a->rows counts the physical weight rows
 // (gate and up interleaved), the output is a->rows / 2 wide.
+struct QuantTarget {
+    uint64_t destination = 0;
+    uint32_t terms = 0;
+    float global_scale = 0.0f;
+};
+
 augur_cuda_result_v1 launch_gemm(augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* plan,
-                                 const augur_cuda_nvfp4_sm100_gemm_args_v1* a, bool swiglu, float up_global_scale) {
+                                 const augur_cuda_nvfp4_sm100_gemm_args_v1* a, bool swiglu, float up_global_scale,
+                                 QuantTarget quant = QuantTarget()) {
     // Tensor maps are encoded on the host into kernel parameter space: no allocation, no driver query.
     // The activation map spans the stacked code planes of all terms (terms * padded tokens rows).
     CUtensorMap map_act, map_weight;
@@ -991,7 +1060,10 @@ augur_cuda_result_v1 launch_gemm(augur_cuda_stream_t s, const augur_cuda_nvfp4_s
     p.scale = a->weight_global_scale * a->activation_global_scale;
     p.scale_b = up_global_scale * a->activation_global_scale;
     p.swiglu = swiglu ? 1u : 0u;
-    if (pair_tiles_enabled() && padded % (2 * kTileM) == 0 && a->rows % kTileN == 0 && plan->sm_count >= 2) {
+    p.quant_out = reinterpret_cast<uint8_t*>(quant.destination);
+    p.quant_terms = quant.terms;
+    p.quant_global_scale = quant.global_scale;
+    if ((quant.destination || pair_tiles_enabled()) && padded % (2 * kTileM) == 0 && a->rows % kTileN == 0 && plan->sm_count >= 2) {
         // 256 x 256 tiles on pairs of CTAs (clusters of two); the grid is a whole number of pairs.
         CUtensorMap map_act_sf, map_weight_sf;
         const uint64_t atoms_per_row_block = a->cols / 64;
@@ -1059,7 +1131,7 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_swig
     augur_cuda_result_v1 failure;
     // the output range handed to the range checks is the real (half-width) one
     g.output_len_bytes = a->output_len_bytes;
-    if (!check_gemm(d, s, plan, &g, true, &failure, /*output_is_half_width=*/true)) return failure;
+    if (!check_gemm(d, s, plan, &g, true, &failure, GemmOutput::kHalfWidth)) return failure;
     CUtensorMap probe;
     return make_code_map(&probe, g.weight, g.rows, g.cols) ? ok() : make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE);
 }
@@ -1077,9 +1149,82 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_swig
     if (!swiglu_as_gemm(a, &g)) return invalid();
     augur_cuda_result_v1 failure;
     g.output_len_bytes = a->output_len_bytes;
-    if (!check_gemm(d, s, plan, &g, false, &failure, /*output_is_half_width=*/true)) return failure;
+    if (!check_gemm(d, s, plan, &g, false, &failure, GemmOutput::kHalfWidth)) return failure;
     if (consume_injected_fault()) return make_result(AUGUR_CUDA_STATUS_DIAGNOSTIC_FAULT_INJECTED);
     const cudaError_t e = cudaSetDevice(d);
     if (e != cudaSuccess) return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE, e);
     return launch_gemm(s, plan, &g, true, a->up_global_scale);
+}
+
+namespace {
+static_assert(sizeof(augur_cuda_nvfp4_sm100_gemm_swiglu_quant_args_v1) == 112, "gemm_swiglu_quant ABI");
+
+// Pair tiles only: padded tokens a multiple of 256 and an intermediate size that is a multiple of 128.
+bool check_swiglu_quant(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* plan,
+                        const augur_cuda_nvfp4_sm100_gemm_swiglu_quant_args_v1* a, bool full,
+                        augur_cuda_nvfp4_sm100_gemm_args_v1* g, augur_cuda_result_v1* failure) {
+    *failure = invalid();
+    if (!header_ok(d, s, a)) {
+        if (a && s && d >= 0 && s->ordinal == d && a->abi_version != AUGUR_CUDA_ABI_VERSION_V1) {
+            *failure = make_result(AUGUR_CUDA_STATUS_ABI_VERSION_MISMATCH);
+        }
+        return false;
+    }
+    if (a->reserved || !a->rows || a->rows % 128 != 0 || a->rows > (1u << 30) || !scale_ok(a->up_global_scale) ||
+        a->destination_terms < 1 || a->destination_terms > 3 || !std::isfinite(a->destination_global_scale) ||
+        a->destination_global_scale <= 0.0f || !a->tokens || padded_tokens(a->tokens) % (2 * kTileM) != 0 || !plan ||
+        plan->sm_count < 2) {
+        return false;
+    }
+    const bool writes_bf16 = a->output_bf16 != 0;
+    if (!act_shape_ok(a->tokens, a->rows, a->destination_terms) ||
+        a->destination_len_bytes != a->destination_terms * staged_term_bytes(a->tokens, a->rows)) {
+        return false;
+    }
+    // the members it shares with the plain GEMM, over the physical (interleaved) weight rows
+    *g = augur_cuda_nvfp4_sm100_gemm_args_v1{};
+    g->abi_version = a->abi_version;
+    g->struct_size = sizeof(*g);
+    g->weight = a->weight; g->weight_len_bytes = a->weight_len_bytes;
+    g->activation = a->activation; g->activation_len_bytes = a->activation_len_bytes;
+    g->output_bf16 = a->output_bf16; g->output_len_bytes = a->output_len_bytes;
+    g->rows = 2 * a->rows; g->cols = a->cols; g->tokens = a->tokens; g->activation_terms = a->activation_terms;
+    g->weight_global_scale = a->gate_global_scale; g->activation_global_scale = a->activation_global_scale;
+    if (!check_gemm(d, s, plan, g, full, failure, writes_bf16 ? GemmOutput::kHalfWidth : GemmOutput::kNone)) return false;
+    *failure = invalid();
+    // the staged destination against every other range
+    const Range destination = {a->destination, a->destination_len_bytes, 256};
+    const Range others[4] = {{a->weight, a->weight_len_bytes, 256}, {a->activation, a->activation_len_bytes, 256},
+                             plan_scratch_range(plan), {a->output_bf16, a->output_len_bytes, 16}};
+    for (size_t i = 0; i < (writes_bf16 ? 4u : 3u); ++i) {
+        if (!disjoint(destination, others[i])) return false;
+    }
+    return !full || inspect_device_ranges(d, &destination, 1, failure);
+}
+}  // namespace
+
+extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_swiglu_quant_preflight_v1(
+    int32_t d, augur_cuda_stream_t s, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_gemm_swiglu_quant_args_v1* a) {
+    augur_cuda_nvfp4_sm100_gemm_args_v1 g;
+    augur_cuda_result_v1 failure;
+    if (!check_swiglu_quant(d, s, plan, a, true, &g, &failure)) return failure;
+    CUtensorMap probe;
+    return make_code_map(&probe, g.weight, g.rows, g.cols) ? ok() : make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE);
+}
+
+extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_swiglu_quant_prevalidated_submit_v1(
+    int32_t d, augur_cuda_stream_t s, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_gemm_swiglu_quant_args_v1* a) {
+    augur_cuda_nvfp4_sm100_gemm_args_v1 g;
+    augur_cuda_result_v1 failure;
+    if (!check_swiglu_quant(d, s, plan, a, false, &g, &failure)) return failure;
+    if (consume_injected_fault()) return make_result(AUGUR_CUDA_STATUS_DIAGNOSTIC_FAULT_INJECTED);
+    const cudaError_t e = cudaSetDevice(d);
+    if (e != cudaSuccess) return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE, e);
+    QuantTarget quant;
+    quant.destination = a->destination;
+    quant.terms = a->destination_terms;
+    quant.global_scale = a->destination_global_scale;
+    return launch_gemm(s, plan, &g, true, a->up_global_scale, quant);
 }

@@ -429,7 +429,8 @@ class Nvfp4Sm100PrefillFfnProgram:
     """
 
     def __init__(self, plan: Plan, gate_up: Nvfp4Sm100Weight, down: Nvfp4Sm100Weight, x: torch.Tensor, out: torch.Tensor,
-                 terms: int, input_global_scale: float, intermediate_global_scale: float):
+                 terms: int, input_global_scale: float, intermediate_global_scale: float, fuse_quantiser: bool = True,
+                 keep_intermediate: bool = False):
         assert gate_up.layout == abi.LAYOUT_TCGEN05 and down.layout == abi.LAYOUT_TCGEN05
         tokens, hidden = x.shape
         inter = gate_up.rows // 2
@@ -462,28 +463,54 @@ class Nvfp4Sm100PrefillFfnProgram:
         d.rows, d.cols, d.tokens, d.activation_terms = down.rows, inter, tokens, terms
         d.weight_global_scale, d.activation_global_scale = down.global_scale, intermediate_global_scale
         self.gate_up_args, self.down_args = g, d
+        # On the two-CTA tiles the gate|up GEMM can quantise its result for the down GEMM in its own epilogue.
+        padded = (tokens + 127) // 128 * 128
+        self.fused = fuse_quantiser and padded % 256 == 0 and inter % 128 == 0
+        if self.fused:
+            f = abi.header(abi.GemmSwigluQuantArgs)
+            f.weight, f.weight_len_bytes = g.weight, g.weight_len_bytes
+            f.activation, f.activation_len_bytes = g.activation, g.activation_len_bytes
+            if keep_intermediate:
+                f.output_bf16, f.output_len_bytes = g.output_bf16, g.output_len_bytes
+            f.destination, f.destination_len_bytes = _ptr(self.staged_h), _nbytes(self.staged_h)
+            f.rows, f.cols, f.tokens, f.activation_terms = inter, hidden, tokens, terms
+            f.gate_global_scale, f.up_global_scale = g.gate_global_scale, g.up_global_scale
+            f.activation_global_scale, f.destination_global_scale = input_global_scale, intermediate_global_scale
+            f.destination_terms = terms
+            self.fused_args = f
 
     @classmethod
     def bind(cls, plan: Plan, gate_up: Nvfp4Sm100Weight, down: Nvfp4Sm100Weight, x: torch.Tensor,
              out: torch.Tensor | None = None, terms: int = 3, input_global_scale: float = 2.0 ** -8,
-             intermediate_global_scale: float = 2.0 ** -8):
+             intermediate_global_scale: float = 2.0 ** -8, fuse_quantiser: bool = True, keep_intermediate: bool = False):
+        """`fuse_quantiser`: quantise the intermediate inside the gate|up GEMM when the shape allows it (three
+        launches instead of four); `keep_intermediate`: also write its BF16 form then (it is always written otherwise)."""
         if out is None:
             out = torch.empty((x.shape[0], down.rows), dtype=torch.bfloat16, device=x.device)
-        self = cls(plan, gate_up, down, x, out, terms, input_global_scale, intermediate_global_scale)
+        self = cls(plan, gate_up, down, x, out, terms, input_global_scale, intermediate_global_scale, fuse_quantiser,
+                   keep_intermediate)
         s, lib = plan.stream, abi.lib()
         _check("act_quant_preflight", lib.augur_cuda_nvfp4_sm100_act_quant_preflight_v1(s.ordinal, s.handle, byref(self.quant_x)))
-        _check("gemm_swiglu_preflight", lib.augur_cuda_nvfp4_sm100_gemm_swiglu_bf16_preflight_v1(
-            s.ordinal, s.handle, plan.handle, byref(self.gate_up_args)))
-        _check("act_quant_preflight", lib.augur_cuda_nvfp4_sm100_act_quant_preflight_v1(s.ordinal, s.handle, byref(self.quant_h)))
+        if self.fused:
+            _check("gemm_swiglu_quant_preflight", lib.augur_cuda_nvfp4_sm100_gemm_swiglu_quant_preflight_v1(
+                s.ordinal, s.handle, plan.handle, byref(self.fused_args)))
+        else:
+            _check("gemm_swiglu_preflight", lib.augur_cuda_nvfp4_sm100_gemm_swiglu_bf16_preflight_v1(
+                s.ordinal, s.handle, plan.handle, byref(self.gate_up_args)))
+            _check("act_quant_preflight", lib.augur_cuda_nvfp4_sm100_act_quant_preflight_v1(s.ordinal, s.handle, byref(self.quant_h)))
         _check("gemm_preflight", lib.augur_cuda_nvfp4_sm100_gemm_bf16_preflight_v1(s.ordinal, s.handle, plan.handle, byref(self.down_args)))
         return self
 
     def submit_for_plan(self) -> None:
         s, lib = self.plan.stream, abi.lib()
         _check("act_quant_submit", lib.augur_cuda_nvfp4_sm100_act_quant_prevalidated_submit_v1(s.ordinal, s.handle, byref(self.quant_x)))
-        _check("gemm_swiglu_submit", lib.augur_cuda_nvfp4_sm100_gemm_swiglu_bf16_prevalidated_submit_v1(
-            s.ordinal, s.handle, self.plan.handle, byref(self.gate_up_args)))
-        _check("act_quant_submit", lib.augur_cuda_nvfp4_sm100_act_quant_prevalidated_submit_v1(s.ordinal, s.handle, byref(self.quant_h)))
+        if self.fused:
+            _check("gemm_swiglu_quant_submit", lib.augur_cuda_nvfp4_sm100_gemm_swiglu_quant_prevalidated_submit_v1(
+                s.ordinal, s.handle, self.plan.handle, byref(self.fused_args)))
+        else:
+            _check("gemm_swiglu_submit", lib.augur_cuda_nvfp4_sm100_gemm_swiglu_bf16_prevalidated_submit_v1(
+                s.ordinal, s.handle, self.plan.handle, byref(self.gate_up_args)))
+            _check("act_quant_submit", lib.augur_cuda_nvfp4_sm100_act_quant_prevalidated_submit_v1(s.ordinal, s.handle, byref(self.quant_h)))
         _check("gemm_submit", lib.augur_cuda_nvfp4_sm100_gemm_bf16_prevalidated_submit_v1(
             s.ordinal, s.handle, self.plan.handle, byref(self.down_args)))
 

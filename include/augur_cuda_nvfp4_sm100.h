@@ -424,6 +424,43 @@ augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_swiglu_bf16_pre
 augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_swiglu_bf16_prevalidated_submit_v1(
     int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
     const augur_cuda_nvfp4_sm100_gemm_swiglu_args_v1* args);
+/* The same fused gate|up projection, with its result also - or only - quantised for the down
+ * projection inside the epilogue (the reference's interstage step produces the quantised tensor
+ * directly from the two GEMM outputs, augur_nvfp4_cutlass_sm120.cu:455-503): `destination` receives
+ * exactly what act_quant would write for the BF16 intermediate (same rule, same layout,
+ * `destination_terms` residual terms, `destination_global_scale`), while the next tile's MMAs run.
+ * `output_bf16` may be 0 (with output_len_bytes 0): the BF16 intermediate is then never written.
+ * Runs on the two-CTA tiles only: ceil128(tokens) must be a multiple of 256 and rows a multiple of
+ * 128; other shapes get INVALID_ARGUMENT and use gemm_swiglu_bf16 followed by act_quant. */
+typedef struct augur_cuda_nvfp4_sm100_gemm_swiglu_quant_args_v1 {
+    uint32_t abi_version;
+    uint32_t struct_size;
+    augur_cuda_device_ptr_t weight;        /* TCGEN05 layout, (2 * rows) x cols, gate/up interleaved by 16 rows */
+    uint64_t weight_len_bytes;
+    augur_cuda_device_ptr_t activation;    /* output of act_quant */
+    uint64_t activation_len_bytes;
+    augur_cuda_device_ptr_t output_bf16;   /* [tokens][rows], or 0 */
+    uint64_t output_len_bytes;
+    augur_cuda_device_ptr_t destination;   /* [destination_terms] x TCGEN05 layout of a ceil128(tokens) x rows tensor */
+    uint64_t destination_len_bytes;
+    uint32_t rows;
+    uint32_t cols;
+    uint32_t tokens;
+    uint32_t activation_terms;
+    float gate_global_scale;
+    float up_global_scale;
+    float activation_global_scale;
+    float destination_global_scale;
+    uint32_t destination_terms;
+    uint32_t reserved;
+} augur_cuda_nvfp4_sm100_gemm_swiglu_quant_args_v1;
+
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_swiglu_quant_preflight_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_gemm_swiglu_quant_args_v1* args);
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_swiglu_quant_prevalidated_submit_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_gemm_swiglu_quant_args_v1* args);
 /* Compact planes of the interleaved gate|up matrix: physical row 32 j + i is gate row 16 j + i for
  * i < 16 and up row 16 j + i - 16 otherwise. rows % 16 == 0, cols % 16 == 0; outputs hold 2 * rows rows. */
 augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_interleave_gate_up_host_v1(

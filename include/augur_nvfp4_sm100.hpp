@@ -478,9 +478,34 @@ public:
         p->down_args_.activation_terms = terms;
         p->down_args_.weight_global_scale = down->global_scale();
         p->down_args_.activation_global_scale = intermediate_global_scale;
+        // On the two-CTA tiles the gate|up GEMM quantises its result for the down GEMM in its own epilogue
+        // (three launches instead of four; the BF16 intermediate is still written here).
+        const uint32_t padded = (tokens + 127) / 128 * 128;
+        p->fused_ = padded % 256 == 0 && inter % 128 == 0;
         check("act_quant_preflight", augur_cuda_nvfp4_sm100_act_quant_preflight_v1(d, s.handle(), &p->quant_x_));
-        check("gemm_swiglu_preflight", augur_cuda_nvfp4_sm100_gemm_swiglu_bf16_preflight_v1(d, s.handle(), plan->raw(), &p->gate_up_args_));
-        check("act_quant_preflight", augur_cuda_nvfp4_sm100_act_quant_preflight_v1(d, s.handle(), &p->quant_h_));
+        if (p->fused_) {
+            p->fused_args_ = header<augur_cuda_nvfp4_sm100_gemm_swiglu_quant_args_v1>();
+            p->fused_args_.weight = p->gate_up_args_.weight;
+            p->fused_args_.weight_len_bytes = p->gate_up_args_.weight_len_bytes;
+            p->fused_args_.activation = p->gate_up_args_.activation;
+            p->fused_args_.activation_len_bytes = p->gate_up_args_.activation_len_bytes;
+            p->fused_args_.output_bf16 = p->gate_up_args_.output_bf16;
+            p->fused_args_.output_len_bytes = p->gate_up_args_.output_len_bytes;
+            p->fused_args_.destination = p->staged_h_->address();
+            p->fused_args_.destination_len_bytes = p->staged_h_->bytes();
+            p->fused_args_.rows = inter; p->fused_args_.cols = hidden; p->fused_args_.tokens = tokens;
+            p->fused_args_.activation_terms = terms;
+            p->fused_args_.gate_global_scale = gate_up->global_scale();
+            p->fused_args_.up_global_scale = up_global_scale;
+            p->fused_args_.activation_global_scale = input_global_scale;
+            p->fused_args_.destination_global_scale = intermediate_global_scale;
+            p->fused_args_.destination_terms = terms;
+            check("gemm_swiglu_quant_preflight",
+                  augur_cuda_nvfp4_sm100_gemm_swiglu_quant_preflight_v1(d, s.handle(), plan->raw(), &p->fused_args_));
+        } else {
+            check("gemm_swiglu_preflight", augur_cuda_nvfp4_sm100_gemm_swiglu_bf16_preflight_v1(d, s.handle(), plan->raw(), &p->gate_up_args_));
+            check("act_quant_preflight", augur_cuda_nvfp4_sm100_act_quant_preflight_v1(d, s.handle(), &p->quant_h_));
+        }
         check("gemm_bf16_preflight", augur_cuda_nvfp4_sm100_gemm_bf16_preflight_v1(d, s.handle(), plan->raw(), &p->down_args_));
         p->plan_ = std::move(plan);
         p->gate_up_ = std::move(gate_up);
@@ -493,8 +518,13 @@ public:
         const Stream& s = *plan_->stream();
         const int32_t d = s.ordinal();
         check("act_quant_submit", augur_cuda_nvfp4_sm100_act_quant_prevalidated_submit_v1(d, s.handle(), &quant_x_));
-        check("gemm_swiglu_submit", augur_cuda_nvfp4_sm100_gemm_swiglu_bf16_prevalidated_submit_v1(d, s.handle(), plan_->raw(), &gate_up_args_));
-        check("act_quant_submit", augur_cuda_nvfp4_sm100_act_quant_prevalidated_submit_v1(d, s.handle(), &quant_h_));
+        if (fused_) {
+            check("gemm_swiglu_quant_submit",
+                  augur_cuda_nvfp4_sm100_gemm_swiglu_quant_prevalidated_submit_v1(d, s.handle(), plan_->raw(), &fused_args_));
+        } else {
+            check("gemm_swiglu_submit", augur_cuda_nvfp4_sm100_gemm_swiglu_bf16_prevalidated_submit_v1(d, s.handle(), plan_->raw(), &gate_up_args_));
+            check("act_quant_submit", augur_cuda_nvfp4_sm100_act_quant_prevalidated_submit_v1(d, s.handle(), &quant_h_));
+        }
         check("gemm_bf16_submit", augur_cuda_nvfp4_sm100_gemm_bf16_prevalidated_submit_v1(d, s.handle(), plan_->raw(), &down_args_));
     }
     const std::shared_ptr<DeviceBuffer>& intermediate() const { return intermediate_; }
@@ -504,6 +534,8 @@ private:
     Nvfp4Sm100PrefillFfnProgram() = default;
     augur_cuda_nvfp4_sm100_act_quant_args_v1 quant_x_{}, quant_h_{};
     augur_cuda_nvfp4_sm100_gemm_swiglu_args_v1 gate_up_args_{};
+    augur_cuda_nvfp4_sm100_gemm_swiglu_quant_args_v1 fused_args_{};
+    bool fused_ = false;
     augur_cuda_nvfp4_sm100_gemm_args_v1 down_args_{};
     std::shared_ptr<Plan> plan_;
     std::shared_ptr<Nvfp4Sm100Weight> gate_up_, down_;

@@ -206,7 +206,7 @@ int main() {
         }
         // ---- prefill FFN program with the SwiGLU fused into the gate|up GEMM, 200 token rows (ragged last tile) ----
         {
-            const uint32_t wide = 200, terms = 3;
+            const uint32_t wide = 200, terms = 3;   // padded to 256: the fused-quantiser path on a pair tile, ragged rows
             std::vector<uint16_t> a(wide * hidden);
             for (auto& v : a) v = to_bf16(static_cast<float>(rng.normal()));
             std::vector<double> h64(static_cast<size_t>(wide) * inter), y64(static_cast<size_t>(wide) * hidden);

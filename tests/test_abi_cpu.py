@@ -38,6 +38,7 @@ def test_struct_sizes_match_the_static_asserts():
     assert ctypes.sizeof(abi.ActQuantArgs) == 56
     assert ctypes.sizeof(abi.GemmArgs) == 80
     assert ctypes.sizeof(abi.GemmSwigluArgs) == 88
+    assert ctypes.sizeof(abi.GemmSwigluQuantArgs) == 112
     assert ctypes.sizeof(abi.Result) == 8
 
 

@@ -232,9 +232,10 @@ def test_prefill_mlp_program_with_fused_swiglu(ctx, hidden, inter, tokens):
     down_w = host.Nvfp4Sm100Weight.upload_checkpoint_nvfp4(ctx["stream"], abi.LAYOUT_TCGEN05, hidden, inter, *down)
     x = torch_bf16_from_bits(x_bits, ctx["device"])
     program = host.Nvfp4Sm100PrefillFfnProgram.bind(
-        ctx["plan"], gate_up_w, down_w, x, terms=3,
+        ctx["plan"], gate_up_w, down_w, x, terms=3, keep_intermediate=True,
         input_global_scale=host.default_activation_global_scale(float(np.abs(synth.bf16_bits_to_f32(x_bits)).max())),
         intermediate_global_scale=host.default_activation_global_scale(float(np.abs(h64).max()) * 1.05))
+    assert program.fused == (tokens % 256 == 0 or (tokens + 127) // 128 * 128 % 256 == 0)
     before = host.allocation_snapshot()
     for _ in range(2):
         program.submit_for_plan()
@@ -254,3 +255,48 @@ def test_prefill_mlp_program_with_fused_swiglu(ctx, hidden, inter, tokens):
     y64_from_h = oracle.linear_f64(down[0], down[1], down[2], hidden, inter, bits_from_torch_bf16(program.intermediate),
                                    threads=oracle.max_threads())
     assert worst(bits_from_torch_bf16(program.out), y64_from_h) <= TOLERANCE
+
+
+def test_fused_intermediate_quantiser_equals_the_quantiser_kernel(ctx):
+    # gate|up GEMM that quantises its SiLU(gate)*up result in the epilogue against the same GEMM followed by act_quant:
+    # identical staged bytes for every token row, identical final output; with and without the BF16 intermediate
+    host, torch = ctx["host"], ctx["torch"]
+    hidden, inter, tokens = 512, 1024, 500          # padded to 512: two pair tiles of token rows, the second ragged
+    gate = synth.make_weight(5, 73, "gate", inter, hidden)
+    up = synth.make_weight(5, 73, "up", inter, hidden)
+    down = synth.make_weight(5, 73, "down", hidden, inter)
+    x_bits = synth.f32_to_bf16_bits(np.random.default_rng(29).standard_normal((tokens, hidden)).astype(np.float32) * 8.0)
+    gate_up_w = host.upload_gate_up_interleaved(ctx["stream"], inter, hidden, *gate, *up)
+    down_w = host.Nvfp4Sm100Weight.upload_checkpoint_nvfp4(ctx["stream"], abi.LAYOUT_TCGEN05, hidden, inter, *down)
+    x = torch_bf16_from_bits(x_bits, ctx["device"])
+    options = dict(terms=3, input_global_scale=0.02, intermediate_global_scale=0.004)
+    plain = host.Nvfp4Sm100PrefillFfnProgram.bind(ctx["plan"], gate_up_w, down_w, x, fuse_quantiser=False, **options)
+    fused = host.Nvfp4Sm100PrefillFfnProgram.bind(ctx["plan"], gate_up_w, down_w, x, keep_intermediate=True, **options)
+    lean = host.Nvfp4Sm100PrefillFfnProgram.bind(ctx["plan"], gate_up_w, down_w, x, **options)
+    assert not plain.fused and fused.fused and lean.fused
+    lean.intermediate.fill_(float("nan"))
+    for program in (plain, fused, lean):
+        program.submit_for_plan()
+    ctx["stream"].synchronize()
+    assert ctx["plan"].device_status() == 0
+    padded, terms = 512, 3
+    code_bytes = padded * inter // 2
+
+    def staged_rows(program):
+        raw = program.staged_h.cpu().numpy()
+        codes = raw[: terms * code_bytes].reshape(terms, padded, inter // 2)[:, :tokens]
+        scales = []
+        sf_bytes = host.repack_extent(abi.LAYOUT_TCGEN05, padded, inter) - code_bytes
+        for term in range(terms):
+            packed = np.concatenate([raw[term * code_bytes:(term + 1) * code_bytes],
+                                     raw[terms * code_bytes + term * sf_bytes: terms * code_bytes + (term + 1) * sf_bytes]])
+            scales.append(host.unpack_host(abi.LAYOUT_TCGEN05, padded, inter, packed)[1][:tokens])
+        return codes, np.stack(scales)
+
+    want_codes, want_scales = staged_rows(plain)
+    for program in (fused, lean):
+        got_codes, got_scales = staged_rows(program)
+        assert np.array_equal(got_scales, want_scales) and np.array_equal(got_codes, want_codes)
+        assert torch.equal(program.out.view(torch.int16), plain.out.view(torch.int16))
+    assert torch.equal(fused.intermediate.view(torch.int16), plain.intermediate.view(torch.int16))
+    assert bool(torch.isnan(lean.intermediate).all())     # never written when not asked for
