@@ -106,20 +106,33 @@ class ClockSampler:
 # ---------------------------------------------------------------------------------------------
 # reference arm: the CPU path (C restatement of the reference's Rust, all host threads)
 # ---------------------------------------------------------------------------------------------
-def cpu_layer_seconds(threads: int, repeats: int):
-    """Times `repeats` passes of one full MLP layer (M=8) through the CPU oracle."""
-    import oracle
+def cpu_mlp_planes(inter: int):
+    """Synthetic gate / up / down planes of an MLP block with intermediate size `inter` (a multiple of 128)."""
     from augur_v100_b200 import synth
-    gate = synth.make_weight(0, 1, "gate", INTER, HIDDEN)
-    up = synth.make_weight(0, 1, "up", INTER, HIDDEN)
-    down = synth.make_weight(0, 1, "down", HIDDEN, INTER)
+    gate = synth.make_weight(0, 1, "gate", inter, HIDDEN)
+    up = synth.make_weight(0, 1, "up", inter, HIDDEN)
+    down = synth.make_weight(0, 1, "down", HIDDEN, inter)
     x = synth.f32_to_bf16_bits(np.random.default_rng(0).standard_normal((TOKENS, HIDDEN)).astype(np.float32) * 8.0)
+    return gate, up, down, x
+
+
+def cpu_layer_seconds(threads: int, repeats: int, inter: int = INTER):
+    """Times `repeats` passes of one MLP layer (M=8) with intermediate size `inter` through the CPU oracle."""
+    import oracle
+    gate, up, down, x = cpu_mlp_planes(inter)
     times = []
     for _ in range(repeats):
         start = time.perf_counter()
-        oracle.mlp_bf16(gate, up, down, HIDDEN, INTER, x, threads=threads)
+        oracle.mlp_bf16(gate, up, down, HIDDEN, inter, x, threads=threads)
         times.append(time.perf_counter() - start)
     return times
+
+
+def mlp_bytes(inter: int) -> int:
+    return 3 * HIDDEN * inter * 9 // 16 + 2 * TOKENS * HIDDEN * 2
+
+
+REFERENCE_BUDGET_SECONDS = 150.0
 
 
 def run_reference(args):
@@ -128,10 +141,18 @@ def run_reference(args):
         return
     import oracle
     threads = oracle.max_threads()
-    times = cpu_layer_seconds(threads, args.warmup + args.steps)[args.warmup:]
+    # A step is one pass over a slice of the layer (the first `inter` intermediate columns of gate, up and
+    # down: the same arithmetic per byte), sized so that warm-up plus timed steps fit the budget.
+    probe_inter = 1024
+    probe = min(cpu_layer_seconds(threads, 2, probe_inter))
+    per_step = REFERENCE_BUDGET_SECONDS / max(args.warmup + args.steps, 1)
+    inter = int(min(INTER, max(128, per_step / probe * probe_inter))) // 128 * 128
+    times = cpu_layer_seconds(threads, args.warmup + args.steps, inter)[args.warmup:]
     seconds = sum(times) / len(times)
-    value = layer_bytes() / seconds / 1e9
-    sample = "one full MLP layer (M=8, 5120 -> 2x17408 -> 5120) per step"
+    value = mlp_bytes(inter) / seconds / 1e9
+    sample = (f"one MLP layer (M=8, 5120 -> 2x{inter} -> 5120) per step"
+              + ("" if inter == INTER else f": the first {inter} of {INTER} intermediate columns, to fit {args.warmup}+{args.steps} steps in "
+                 f"{REFERENCE_BUDGET_SECONDS:.0f} s"))
     print(json.dumps({
         "impl": "reference", "metric": "nvfp4_linear_m8_hbm_gbs", "value": value, "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds * 1e3,
