@@ -286,7 +286,7 @@ __device__ __forceinline__ uint32_t shift_bf16(uint32_t bits, int shift) {
 // i.e. after this rank has finished the one before. The reduce step waits for tiles that other
 // CTAs of the same grid produce, so the grid must be co-resident (the entry point checks that it
 // does not exceed the SM count).
-constexpr uint32_t kExchangeWaitLimit = 1u << 22;   // polls: gives up after a fraction of a second
+constexpr uint32_t kExchangeWaitLimit = 1u << 20;   // polls of about a microsecond: gives up after about a second
 constexpr uint32_t kExchangeTileBytes = kSlotFloats * 8;
 
 __host__ __device__ constexpr uint64_t exchange_extent(uint32_t world, uint32_t groups) {

@@ -438,3 +438,32 @@ def test_exchange_reduce_with_eight_sources_on_one_gpu(ctx):
         pushed = buffers[r].cpu().numpy().view(np.uint32).reshape(2, world, groups, 32, 4, 4)
         assert np.all(pushed[seq & 1, 0, :, :, :, 1] == seq) and np.all(pushed[seq & 1, 0, :, :, :, 3] == seq)
         assert not pushed[1 - (seq & 1)].any() and not pushed[seq & 1, 1:].any()
+
+
+def test_exchange_wait_that_runs_out_is_reported_and_leaves_the_context_usable(ctx):
+    # Failure detection without a fault: rank 0 of 2 runs alone, the tiles of rank 1 never arrive, every wait of
+    # the reduce step runs out (bounded polls), the launch ends by itself, the plan's status word says which wait
+    # gave up, and the same stream goes on working.
+    host, torch = ctx["host"], ctx["torch"]
+    hidden, inter, tokens, world = 128, 256, 8, 2
+    gate, up, down, gate_up, down_w = _mlp_weights(ctx, hidden, inter, seed=23)
+    x = torch_bf16_from_bits(synth.make_activation(23, 63, "x", tokens, hidden), ctx["device"])
+    plan = host.Plan(ctx["stream"], host.mlp_scratch_bytes(hidden, inter))
+    program = host.Nvfp4Sm100FfnProgram.bind(plan, gate_up, down_w, x)
+    extent = ctypes.c_uint64()
+    assert abi.lib().augur_cuda_nvfp4_sm100_mlp_tp_exchange_extent_host_v1(hidden, world, byref(extent)).status == 0
+    buffers = [torch.zeros(extent.value, dtype=torch.uint8, device=ctx["device"]) for _ in range(world)]
+    args = abi.header(abi.MlpTpArgs)
+    args.gate_up, args.down = program.args.gate_up, program.args.down
+    for r in range(world):
+        args.exchange[r] = buffers[r].data_ptr()
+    args.exchange_len_bytes, args.world, args.rank, args.sequence = extent.value, world, 0, 1
+    s, lib = ctx["stream"], abi.lib()
+    assert lib.augur_cuda_nvfp4_sm100_mlp_tp_prevalidated_submit_v1(s.ordinal, s.handle, plan.handle, byref(args)).status == 0
+    s.synchronize()                              # returns: the waits are bounded
+    assert plan.device_status() == 0x203
+    plan.close()
+    # the context is intact: an ordinary program on the same stream still matches the oracle
+    codes, scales, glob, x_bits, proj = _linear_case(ctx, 64, 256, 4, seed=24)
+    y64 = oracle.linear_f64(codes, scales, glob, 64, 256, x_bits, threads=2)
+    assert rel_error(bits_from_torch_bf16(proj.out), y64) <= TOLERANCE
