@@ -613,6 +613,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
         // issued by a thread of their own (below) into the double-buffered scale columns, this thread
         // issues only the MMAs. Descriptors advance by additions (their low bits hold address >> 4).
         uint32_t stage = 0, phase = 0, tmem_phase = 0, sf_buffer = 0, sf_phase = 0;
+        uint32_t kb_parity = 0;   // toggles with every k block, across tiles: consecutive k blocks never share a buffer
         bool alive = true;
         const uint32_t idesc = (1u << 7) | (1u << 10) | ((kTileN >> 3) << 17) | (((2 * kTileM) >> 4) << 24);
         const uint32_t smem_base = smem_u32(smem);
@@ -633,8 +634,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
                 }
                 tc_fence_after();
                 const uint64_t a_desc = a_desc0 + stage * kStageStep, b_desc = b_desc0 + stage * kStageStep;
+                // the token rows' scales change with every step (term), the weight rows' scales only with the k block
                 const uint32_t tmem_sfa = tmem_base + kTmemSfA + sf_buffer * 16;
-                const uint32_t tmem_sfb = tmem_base + kTmemSfB + sf_buffer * 32;
+                const uint32_t tmem_sfb = tmem_base + kTmemSfB + kb_parity * 32;
                 // each MMA consumes 64 k = 32 bytes of every row: start address + 2; only k steps inside the tensor
                 const uint32_t k_steps = (kb + 1 < k_blocks) ? 4u : last_k_steps;
                 if (k_steps == 4) {
@@ -653,7 +655,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
                 tc_commit_pair(bar_empty + 8 * stage);                     // frees the stage in both CTAs
                 tc_commit_pair_local(bar_scales_empty + 8 * sf_buffer);    // and this half of the scale columns
                 if ((sf_buffer ^= 1) == 0) sf_phase ^= 1;
-                if (++term == p.terms) { term = 0; ++kb; }
+                if (++term == p.terms) { term = 0; ++kb; kb_parity ^= 1; }
                 if (++stage == kPairStages) { stage = 0; phase ^= 1; }
             }
             if (alive) tc_commit_pair(bar_tmem_full);     // both accumulator halves complete
@@ -661,7 +663,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
         }
     } else if (warp == 6 && lane == 0 && rank == 0) {
         // ---------------- scale-copy issuer (leader only): shared memory -> tensor memory, both CTAs ----------------
-        uint32_t stage = 0, phase = 0, sf_buffer = 0, sf_phase = 0;
+        uint32_t stage = 0, phase = 0, sf_buffer = 0, sf_phase = 0, kb_parity = 0;
         const uint32_t smem_base = smem_u32(smem);
         const uint64_t sfa_desc0 = sf_desc(smem_base + kBytesA + kPairBytesB), sfb_desc0 = sf_desc(smem_base + kBytesA + kPairBytesB + kBytesSfA);
         constexpr uint64_t kStageStep = kPairStageBytes >> 4, kAtomStep = kSfAtomBytes >> 4, kRowBlockStep = kBytesSfA >> 4;
@@ -678,8 +680,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
                 }
                 tc_fence_after();
                 const uint64_t sfa_desc = sfa_desc0 + stage * kStageStep, sfb_desc = sfb_desc0 + stage * kStageStep;
+                // Token-row scales: one buffer per step parity. Weight-row scales are the same for all activation
+                // terms of a k block: copied with term 0 only, into the buffer of the k block's parity (counted across
+                // tiles). That buffer was last read by the steps of the k block before the previous one, which are older than the step whose completion
+                // was awaited above (operations complete in order), so it is free.
                 const uint32_t tmem_sfa = tmem_base + kTmemSfA + sf_buffer * 16;
-                const uint32_t tmem_sfb = tmem_base + kTmemSfB + sf_buffer * 32;
+                const uint32_t tmem_sfb = tmem_base + kTmemSfB + kb_parity * 32;
                 const uint32_t k_steps = (kb + 1 < k_blocks) ? 4u : last_k_steps;
                 if (k_steps == 4) {
 #pragma unroll
@@ -688,19 +694,29 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
                         if (step >= 2) break;
 #endif
                         tc_copy_sf_pair(tmem_sfa + 4 * k, sfa_desc + k * kAtomStep);
-                        tc_copy_sf_pair(tmem_sfb + 8 * k, sfb_desc + k * kAtomStep);
-                        tc_copy_sf_pair(tmem_sfb + 8 * k + 4, sfb_desc + kRowBlockStep + k * kAtomStep);
+                    }
+                    if (term == 0) {
+#pragma unroll
+                        for (uint32_t k = 0; k < 4; ++k) {
+#ifdef AUGUR_GEMM_PROBE_NO_SF_COPY
+                            if (step >= 2) break;
+#endif
+                            tc_copy_sf_pair(tmem_sfb + 8 * k, sfb_desc + k * kAtomStep);
+                            tc_copy_sf_pair(tmem_sfb + 8 * k + 4, sfb_desc + kRowBlockStep + k * kAtomStep);
+                        }
                     }
                 } else {
                     for (uint32_t k = 0; k < k_steps; ++k) {
                         tc_copy_sf_pair(tmem_sfa + 4 * k, sfa_desc + k * kAtomStep);
-                        tc_copy_sf_pair(tmem_sfb + 8 * k, sfb_desc + k * kAtomStep);
-                        tc_copy_sf_pair(tmem_sfb + 8 * k + 4, sfb_desc + kRowBlockStep + k * kAtomStep);
+                        if (term == 0) {
+                            tc_copy_sf_pair(tmem_sfb + 8 * k, sfb_desc + k * kAtomStep);
+                            tc_copy_sf_pair(tmem_sfb + 8 * k + 4, sfb_desc + kRowBlockStep + k * kAtomStep);
+                        }
                     }
                 }
                 tc_commit_pair_local(bar_scales_full + 8 * sf_buffer);
                 if ((sf_buffer ^= 1) == 0) sf_phase ^= 1;
-                if (++term == p.terms) { term = 0; ++kb; }
+                if (++term == p.terms) { term = 0; ++kb; kb_parity ^= 1; }
                 if (++stage == kPairStages) { stage = 0; phase ^= 1; }
             }
         }

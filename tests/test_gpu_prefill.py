@@ -166,6 +166,12 @@ def test_gemm_pair_tile_ragged_k_and_tokens(ctx):
     _check_gemm(ctx, rows=512, cols=2176, tokens=256, seed=13, terms=2)    # the tp-8 k slice of the down projection
 
 
+def test_gemm_pair_tiles_terms_share_weight_scales_across_tiles(ctx):
+    # an odd number of k blocks (3), two activation terms and more tiles than CTA pairs: the weight-row scale
+    # buffers alternate per k block across the tile boundary while two terms share each copy
+    _check_gemm(ctx, rows=2560, cols=768, tokens=2048, terms=2, seed=14)
+
+
 def test_gemm_residual_terms(ctx):
     e1 = _check_gemm(ctx, rows=256, cols=1024, tokens=128, terms=1, seed=6)
     e3 = _check_gemm(ctx, rows=256, cols=1024, tokens=128, terms=3, seed=6)
