@@ -83,6 +83,17 @@ class MlpArgs(Structure):
                 ("gate_up", GemvArgs), ("down", GemvArgs)]
 
 
+class NormGroupArgs(Structure):
+    _fields_ = [("abi_version", c_uint32), ("struct_size", c_uint32),
+                ("add_a", c_uint64), ("add_b", c_uint64), ("add_len_bytes", c_uint64),
+                ("input_f32", c_uint64), ("input_len_bytes", c_uint64),
+                ("weight_f32", c_uint64), ("weight_len_bytes", c_uint64),
+                ("output_f32", c_uint64), ("output_len_bytes", c_uint64),
+                ("staged_bf16", c_uint64), ("staged_len_bytes", c_uint64),
+                ("tokens", c_uint32), ("cols", c_uint32), ("epsilon", c_float), ("residual", c_uint32),
+                ("count", c_uint32), ("reserved", c_uint32), ("projections", GemvArgs * 4)]
+
+
 MAX_TP_RANKS = 8
 
 
@@ -160,6 +171,8 @@ EXPORTS = {
     "augur_cuda_nvfp4_sm100_gemv_bf16_static_scratch_submit_v1": (Result, [c_int32, c_void_p, POINTER(GemvArgs)]),
     "augur_cuda_nvfp4_sm100_mlp_preflight_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(MlpArgs)]),
     "augur_cuda_nvfp4_sm100_mlp_prevalidated_submit_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(MlpArgs)]),
+    "augur_cuda_nvfp4_sm100_norm_group_preflight_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(NormGroupArgs)]),
+    "augur_cuda_nvfp4_sm100_norm_group_prevalidated_submit_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(NormGroupArgs)]),
     "augur_cuda_nvfp4_sm100_mlp_tp_exchange_extent_host_v1": (Result, [c_uint32, c_uint32, POINTER(c_uint64)]),
     "augur_cuda_nvfp4_sm100_mlp_tp_preflight_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(MlpTpArgs)]),
     "augur_cuda_nvfp4_sm100_mlp_tp_prevalidated_submit_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(MlpTpArgs)]),

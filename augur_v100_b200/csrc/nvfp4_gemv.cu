@@ -1151,6 +1151,153 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_mlp_tp_pr
     return submitted();
 }
 
+// ---- norm group: [residual add] -> RMSNorm -> BF16 stage -> up to four small-token projections ----------------
+// The B200 counterpart of the reference's fused norm stage and grouped projections
+// (crates/augur-cuda-sys/native/augur_qwen35_gdn_input_b8.cuh:19-49,92 ff.): one validated program,
+// 1 + count launches chained by programmatic stream serialisation.
+namespace augur_sm100 {
+namespace {
+static_assert(sizeof(augur_cuda_nvfp4_sm100_norm_group_args_v1) == 472, "norm_group ABI");
+
+constexpr uint32_t kNormThreads = 256;
+
+// One CTA per token row. The arithmetic order is the reference kernel's, so that the F32 output is
+// reproducible on a CPU: lane l accumulates value * value over columns l, l + 256, ... (multiply and
+// add, never fused), the 256 partial sums are folded by halving strides, y = (value * scale) * weight.
+// scale = 1 / sqrt(mean + epsilon) with correctly rounded operations (the reference's rsqrtf is a
+// hardware approximation); the staged copy is BF16.
+__global__ void __launch_bounds__(kNormThreads) norm_stage_kernel(const float* __restrict__ add_a, const float* __restrict__ add_b,
+                                                                   float* __restrict__ input, const float* __restrict__ weight,
+                                                                   float* __restrict__ output, __nv_bfloat16* __restrict__ staged,
+                                                                   uint32_t cols, float epsilon, uint32_t residual) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // the inputs may come from the launch before this one
+    __shared__ float partial[kNormThreads];
+    const uint32_t lane = threadIdx.x;
+    const uint64_t base = static_cast<uint64_t>(blockIdx.x) * cols;
+    float sum = 0.0f;
+    for (uint32_t col = lane; col < cols; col += kNormThreads) {
+        float value;
+        if (residual) {
+            value = __fadd_rn(__ldcg(add_a + base + col), __ldcg(add_b + base + col));
+            input[base + col] = value;
+        } else {
+            value = __ldcg(input + base + col);
+        }
+        sum = __fadd_rn(sum, __fmul_rn(value, value));
+    }
+    partial[lane] = sum;
+    __syncthreads();
+    for (uint32_t stride = kNormThreads / 2; stride != 0; stride >>= 1) {
+        if (lane < stride) partial[lane] = __fadd_rn(partial[lane], partial[lane + stride]);
+        __syncthreads();
+    }
+    const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(partial[0], static_cast<float>(cols)), epsilon)));
+    for (uint32_t col = lane; col < cols; col += kNormThreads) {
+        // this thread wrote input[base + col] itself when there is a residual
+        const float y = __fmul_rn(__fmul_rn(input[base + col], scale), __ldg(weight + col));
+        output[base + col] = y;
+        staged[base + col] = __float2bfloat16_rn(y);
+    }
+}
+
+bool check_norm_group(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* plan,
+                      const augur_cuda_nvfp4_sm100_norm_group_args_v1* a, bool full, augur_cuda_result_v1* failure) {
+    *failure = invalid();
+    if (!header_ok(d, s, a)) {
+        if (a && s && d >= 0 && s->ordinal == d && a->abi_version != AUGUR_CUDA_ABI_VERSION_V1) {
+            *failure = make_result(AUGUR_CUDA_STATUS_ABI_VERSION_MISMATCH);
+        }
+        return false;
+    }
+    if (!plan_ok(plan, d, s) || plan->scratch_bytes < kCounterBytes) return false;
+    if (a->reserved || a->residual > 1 || a->count < 1 || a->count > 4 || a->tokens < 1 ||
+        a->tokens > AUGUR_NVFP4_SM100_MAX_SMALL_TOKENS || !a->cols || a->cols % kNormThreads != 0 || a->cols > INT_MAX ||
+        !std::isfinite(a->epsilon) || a->epsilon < 0.0f) {
+        return false;
+    }
+    const uint64_t elements = static_cast<uint64_t>(a->tokens) * a->cols;
+    if (a->input_len_bytes != elements * 4 || a->output_len_bytes != elements * 4 || a->staged_len_bytes != elements * 2 ||
+        a->weight_len_bytes != static_cast<uint64_t>(a->cols) * 4) {
+        return false;
+    }
+    Range r[16];
+    size_t n = 0;
+    r[n++] = {a->input_f32, a->input_len_bytes, 16};
+    r[n++] = {a->weight_f32, a->weight_len_bytes, 4};
+    r[n++] = {a->output_f32, a->output_len_bytes, 16};
+    r[n++] = {a->staged_bf16, a->staged_len_bytes, 16};
+    if (a->residual) {
+        if (a->add_len_bytes != a->input_len_bytes) return false;
+        r[n++] = {a->add_a, a->add_len_bytes, 16};
+        r[n++] = {a->add_b, a->add_len_bytes, 16};
+    } else if (a->add_a || a->add_b || a->add_len_bytes) {
+        return false;
+    }
+    for (uint32_t i = 0; i < 4; ++i) {
+        const augur_cuda_nvfp4_sm100_gemv_args_v1& m = a->projections[i];
+        if (i >= a->count) {
+            // unused members are all zero
+            const uint8_t* bytes = reinterpret_cast<const uint8_t*>(&m);
+            for (size_t k = 0; k < sizeof(m); ++k) {
+                if (bytes[k]) return false;
+            }
+            continue;
+        }
+        // each member exactly as a stand-alone small-token linear (launches are stream-ordered and share the scratch)
+        if (!check_gemv(d, s, plan, &m, kCounterBytes, plan->scratch_bytes, false, failure)) return false;
+        *failure = invalid();
+        if (m.epilogue == AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16 || m.input_bf16 != a->staged_bf16 ||
+            m.input_len_bytes != a->staged_len_bytes || m.tokens != a->tokens || m.cols != a->cols) {
+            return false;
+        }
+        r[n++] = {m.weight, m.weight_len_bytes, 256};
+        r[n++] = {m.output, m.output_len_bytes, 4};
+    }
+    r[n++] = plan_scratch_range(plan);
+    if (!all_disjoint(r, n)) return false;
+    return !full || inspect_device_ranges(d, r, n - 1, failure);
+}
+}  // namespace
+}  // namespace augur_sm100
+
+extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_norm_group_preflight_v1(
+    int32_t d, augur_cuda_stream_t s, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_norm_group_args_v1* a) {
+    augur_cuda_result_v1 failure;
+    return check_norm_group(d, s, plan, a, true, &failure) ? ok() : failure;
+}
+
+extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_norm_group_prevalidated_submit_v1(
+    int32_t d, augur_cuda_stream_t s, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_norm_group_args_v1* a) {
+    augur_cuda_result_v1 failure;
+    if (!check_norm_group(d, s, plan, a, false, &failure)) return failure;
+    if (consume_injected_fault()) return make_result(AUGUR_CUDA_STATUS_DIAGNOSTIC_FAULT_INJECTED);
+    const cudaError_t e = cudaSetDevice(d);
+    if (e != cudaSuccess) return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE, e);
+    cudaLaunchAttribute attribute{};
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t config{};
+    config.stream = s->stream;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    config.gridDim = dim3(a->tokens);
+    config.blockDim = dim3(kNormThreads);
+    cudaLaunchKernelEx(&config, norm_stage_kernel, reinterpret_cast<const float*>(a->add_a), reinterpret_cast<const float*>(a->add_b),
+                       reinterpret_cast<float*>(a->input_f32), reinterpret_cast<const float*>(a->weight_f32),
+                       reinterpret_cast<float*>(a->output_f32), reinterpret_cast<__nv_bfloat16*>(a->staged_bf16), a->cols,
+                       a->epsilon, a->residual);
+    count_launch();
+    augur_cuda_result_v1 result = submitted();
+    for (uint32_t i = 0; i < a->count && result.status == AUGUR_CUDA_STATUS_OK; ++i) {
+        launch_gemv(s, plan, &a->projections[i], 0, kCounterBytes);
+        result = submitted();
+    }
+    return result;
+}
+
 // ---- one entry point that allocates nothing -------------------------------------------------
 // Plan creation calls cudaMalloc. A host that gave every byte of device memory to its own arena
 // at start-up, or that runs its serving loop under a no-allocation rule and audits it, cannot

@@ -515,6 +515,53 @@ class Nvfp4Sm100PrefillFfnProgram:
             s.ordinal, s.handle, self.plan.handle, byref(self.down_args)))
 
 
+class Nvfp4Sm100NormGroupProgram:
+    """[residual add] -> RMSNorm -> BF16 stage -> one to four small-token projections, as one validated program.
+
+    Mirrors the reference's fused norm stage with grouped projections
+    (crates/augur-cuda-sys/native/augur_qwen35_gdn_input_b8.cuh; the GDN input group and the post-attention group):
+    `input_f32` is the residual stream [tokens, cols] (with `add_a` / `add_b` it is first overwritten by their
+    sum), `norm_weight_f32` the RMSNorm weight, `weights` the projections (STREAM layout) that all read the
+    normalised, BF16-rounded activations.
+    """
+
+    def __init__(self, plan: Plan, weights, input_f32: torch.Tensor, norm_weight_f32: torch.Tensor, epsilon: float,
+                 add_a: torch.Tensor | None, add_b: torch.Tensor | None):
+        tokens, cols = input_f32.shape
+        self.plan, self.weights, self.input, self.norm_weight = plan, list(weights), input_f32, norm_weight_f32
+        self.add_a, self.add_b = add_a, add_b
+        self.normalised = torch.empty((tokens, cols), dtype=torch.float32, device=input_f32.device)
+        self.staged = torch.empty((tokens, cols), dtype=torch.bfloat16, device=input_f32.device)
+        self.outputs = [torch.empty((tokens, w.rows), dtype=torch.bfloat16, device=input_f32.device) for w in self.weights]
+        a = abi.header(abi.NormGroupArgs)
+        if add_a is not None:
+            a.add_a, a.add_b, a.add_len_bytes, a.residual = _ptr(add_a), _ptr(add_b), _nbytes(add_a), 1
+        a.input_f32, a.input_len_bytes = _ptr(input_f32), _nbytes(input_f32)
+        a.weight_f32, a.weight_len_bytes = _ptr(norm_weight_f32), _nbytes(norm_weight_f32)
+        a.output_f32, a.output_len_bytes = _ptr(self.normalised), _nbytes(self.normalised)
+        a.staged_bf16, a.staged_len_bytes = _ptr(self.staged), _nbytes(self.staged)
+        a.tokens, a.cols, a.epsilon, a.count = tokens, cols, epsilon, len(self.weights)
+        for index, (weight, out) in enumerate(zip(self.weights, self.outputs)):
+            a.projections[index] = gemv_args(weight, self.staged, out, abi.EPILOGUE_LINEAR_BF16)
+        self.args = a
+
+    @classmethod
+    def bind(cls, plan: Plan, weights, input_f32: torch.Tensor, norm_weight_f32: torch.Tensor, epsilon: float = 1e-6,
+             add_a: torch.Tensor | None = None, add_b: torch.Tensor | None = None):
+        if (add_a is None) != (add_b is None):
+            raise ValueError("the residual add takes both operands or none")
+        self = cls(plan, weights, input_f32, norm_weight_f32, epsilon, add_a, add_b)
+        s = plan.stream
+        _check("norm_group_preflight", abi.lib().augur_cuda_nvfp4_sm100_norm_group_preflight_v1(
+            s.ordinal, s.handle, plan.handle, byref(self.args)))
+        return self
+
+    def submit_for_plan(self) -> None:
+        s = self.plan.stream
+        _check("norm_group_submit", abi.lib().augur_cuda_nvfp4_sm100_norm_group_prevalidated_submit_v1(
+            s.ordinal, s.handle, self.plan.handle, byref(self.args)))
+
+
 SHAPE_SMALL_BATCH = "small-batch"
 SHAPE_PREFILL = "prefill"
 

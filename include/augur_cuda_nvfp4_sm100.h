@@ -296,6 +296,46 @@ augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_mlp_prevalidated_sub
     int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
     const augur_cuda_nvfp4_sm100_mlp_args_v1* args);
 
+/* ---- norm group: [residual add] -> RMSNorm -> BF16 stage -> 1..4 small-token projections ----- */
+/* Replaces augur_cuda_qwen35_qpn_norm_group_b8_{preflight,prevalidated_submit}_v1
+ * (native augur_qwen35_gdn_input_b8.cuh:19-49,50-110): GDN input (norm, then the in-projections)
+ * and post-attention (residual add, norm, then gate|up or separate projections) as one validated
+ * program. The norm stage keeps the reference kernel's arithmetic order (per-lane serial sums over
+ * columns l, l+256, ..., halving-stride fold, y = value * scale * weight left to right), with
+ * scale = 1 / sqrt(mean + epsilon) correctly rounded (the reference uses the approximate rsqrtf)
+ * and a BF16 staged copy instead of FP16. With `residual` the value add_a + add_b is stored to
+ * input_f32 first. Every projection must take staged_bf16 as its input (same tokens and cols);
+ * unused members are zero. tokens 1..8, cols a multiple of 256. Launches: 1 + count. */
+typedef struct augur_cuda_nvfp4_sm100_norm_group_args_v1 {
+    uint32_t abi_version;
+    uint32_t struct_size;
+    augur_cuda_device_ptr_t add_a;         /* residual only, else 0: [tokens][cols] f32 */
+    augur_cuda_device_ptr_t add_b;
+    uint64_t add_len_bytes;
+    augur_cuda_device_ptr_t input_f32;     /* [tokens][cols]; read, or written when residual */
+    uint64_t input_len_bytes;
+    augur_cuda_device_ptr_t weight_f32;    /* [cols] */
+    uint64_t weight_len_bytes;
+    augur_cuda_device_ptr_t output_f32;    /* [tokens][cols] normalised */
+    uint64_t output_len_bytes;
+    augur_cuda_device_ptr_t staged_bf16;   /* [tokens][cols] = bf16(output): the projections' input */
+    uint64_t staged_len_bytes;
+    uint32_t tokens;
+    uint32_t cols;
+    float epsilon;
+    uint32_t residual;
+    uint32_t count;
+    uint32_t reserved;
+    augur_cuda_nvfp4_sm100_gemv_args_v1 projections[4];
+} augur_cuda_nvfp4_sm100_norm_group_args_v1;
+
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_norm_group_preflight_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_norm_group_args_v1* args);
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_norm_group_prevalidated_submit_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_norm_group_args_v1* args);
+
 /* ---- tensor-parallel MLP program: the all-reduce inside the down launch --------- */
 /* No counterpart in the reference (it has no multi-GPU code). Column-parallel gate|up and
  * row-parallel down over up to 8 GPUs of one box, one process per GPU: every rank passes its

@@ -276,6 +276,28 @@ def act_dequant_f64(codes, scales, global_scale: float, tokens: int, cols: int, 
     return out
 
 
+def rmsnorm_stage(input_f32, weight_f32, epsilon: float, add_a=None, add_b=None):
+    """[residual add] -> RMSNorm -> (input actually normalised, F32 output, BF16 staged bits)."""
+    weight = np.ascontiguousarray(weight_f32, dtype=np.float32)
+    residual = add_a is not None
+    if residual:
+        a, b = np.ascontiguousarray(add_a, dtype=np.float32), np.ascontiguousarray(add_b, dtype=np.float32)
+        x = np.zeros_like(a)
+    else:
+        a = b = None
+        x = np.array(input_f32, dtype=np.float32, order="C", copy=True)
+    tokens, cols = x.shape
+    out = np.zeros((tokens, cols), dtype=np.float32)
+    staged = np.zeros((tokens, cols), dtype=np.uint16)
+    fp = ctypes.POINTER(ctypes.c_float)
+    _check(lib().augur_oracle_rmsnorm_stage(
+        a.ctypes.data_as(fp) if residual else None, b.ctypes.data_as(fp) if residual else None,
+        x.ctypes.data_as(fp), weight.ctypes.data_as(fp), ctypes.c_size_t(tokens), ctypes.c_size_t(cols),
+        ctypes.c_float(epsilon), ctypes.c_int(1 if residual else 0), out.ctypes.data_as(fp),
+        staged.ctypes.data_as(ctypes.POINTER(ctypes.c_uint16))))
+    return x, out, staged
+
+
 def max_threads() -> int:
     return int(lib().augur_oracle_max_threads())
 

@@ -263,6 +263,58 @@ int augur_oracle_dequant_planes_f32(const uint8_t* codes, const uint8_t* scales,
     return AUGUR_ORACLE_OK;
 }
 
+/* [residual add] -> RMSNorm -> F32 output and its BF16 rounding: the CPU statement of the
+ * reference's norm stage (crates/augur-cuda-sys/native/augur_qwen35_gdn_input_b8.cuh:19-49, which
+ * keeps prefill_rmsnorm_kernel's order, augur_qwen35_prefill_cublas_sm70.cu:1008-1029): 256 lanes
+ * per token row, lane l adds value*value over columns l, l+256, ... in that order (a multiply and
+ * an add, no fused operation), the 256 partial sums are folded by halving strides
+ * (partial[l] += partial[l + stride], stride 128 .. 1), y = value * scale * weight[col] evaluated
+ * left to right. Two deliberate differences: scale = 1 / sqrt(mean + epsilon) with correctly
+ * rounded division and square root (the reference's rsqrtf is a hardware approximation that no
+ * CPU code can restate bit for bit), and the staged copy is BF16 (bf16_round), not FP16, because
+ * the B200 kernels take BF16 activations. With `residual` the value is add_a + add_b and is stored
+ * to `input` first (one F32 add per element, as the reference does). */
+int augur_oracle_rmsnorm_stage(const float* add_a, const float* add_b, float* input, const float* weight,
+                               size_t tokens, size_t cols, float epsilon, int residual,
+                               float* output_f32, uint16_t* staged_bf16) {
+    if (!input || !weight || !output_f32 || !staged_bf16 || tokens == 0 || cols == 0 || cols % 256 != 0) return -1;
+    if (residual && (!add_a || !add_b)) return -1;
+    for (size_t token = 0; token < tokens; ++token) {
+        const size_t base = token * cols;
+        float partial[256];
+        for (size_t lane = 0; lane < 256; ++lane) {
+            float sum = 0.0f;
+            for (size_t col = lane; col < cols; col += 256) {
+                float value;
+                if (residual) {
+                    value = add_a[base + col] + add_b[base + col];
+                    input[base + col] = value;
+                } else {
+                    value = input[base + col];
+                }
+                const float square = value * value;
+                sum = sum + square;
+            }
+            partial[lane] = sum;
+        }
+        for (size_t stride = 128; stride != 0; stride >>= 1) {
+            for (size_t lane = 0; lane < stride; ++lane) partial[lane] = partial[lane] + partial[lane + stride];
+        }
+        const float mean = partial[0] / (float)cols;
+        const float scale = 1.0f / sqrtf(mean + epsilon);
+        for (size_t col = 0; col < cols; ++col) {
+            const float scaled = input[base + col] * scale;
+            const float y = scaled * weight[col];
+            output_f32[base + col] = y;
+            const float rounded = augur_oracle_bf16_round(y);
+            uint32_t bits;
+            memcpy(&bits, &rounded, 4);
+            staged_bf16[base + col] = (uint16_t)(bits >> 16);
+        }
+    }
+    return 0;
+}
+
 int augur_oracle_max_threads(void) {
     const long count = sysconf(_SC_NPROCESSORS_ONLN);
     return count < 1 ? 1 : (int)count;

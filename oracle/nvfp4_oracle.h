@@ -115,6 +115,11 @@ int augur_oracle_act_quant(const uint16_t* x_bf16, size_t tokens, size_t cols, f
 int augur_oracle_act_dequant_f64(const uint8_t* codes, const uint8_t* scales, float global_scale,
                                  size_t tokens, size_t cols, int terms, double* out);
 
+/* [residual add] -> RMSNorm -> F32 output + BF16 staged copy; see nvfp4_oracle.c. cols % 256 == 0. */
+int augur_oracle_rmsnorm_stage(const float* add_a, const float* add_b, float* input, const float* weight,
+                               size_t tokens, size_t cols, float epsilon, int residual,
+                               float* output_f32, uint16_t* staged_bf16);
+
 int augur_oracle_max_threads(void);
 
 #ifdef __cplusplus

@@ -35,6 +35,7 @@ def test_struct_sizes_match_the_static_asserts():
     assert ctypes.sizeof(abi.GemvArgs) == 88
     assert ctypes.sizeof(abi.MlpArgs) == 184
     assert ctypes.sizeof(abi.MlpTpArgs) == 272
+    assert ctypes.sizeof(abi.NormGroupArgs) == 472
     assert ctypes.sizeof(abi.ActQuantArgs) == 56
     assert ctypes.sizeof(abi.GemmArgs) == 80
     assert ctypes.sizeof(abi.GemmSwigluArgs) == 88

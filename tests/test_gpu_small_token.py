@@ -467,3 +467,71 @@ def test_exchange_wait_that_runs_out_is_reported_and_leaves_the_context_usable(c
     codes, scales, glob, x_bits, proj = _linear_case(ctx, 64, 256, 4, seed=24)
     y64 = oracle.linear_f64(codes, scales, glob, 64, 256, x_bits, threads=2)
     assert rel_error(bits_from_torch_bf16(proj.out), y64) <= TOLERANCE
+
+
+@pytest.mark.parametrize("residual", [False, True], ids=["gdn-input", "post-attention"])
+def test_norm_group_program(ctx, residual):
+    # [residual add] -> RMSNorm -> BF16 stage -> projections, one program (the reference's GDN-input and post-attention groups)
+    host, torch = ctx["host"], ctx["torch"]
+    tokens, cols, eps = 8, 5120, 1e-6
+    shapes = [(10240, cols), (6144, cols), (64, cols)] if not residual else [(1024, cols), (2048, cols)]
+    rng = np.random.default_rng(31)
+    a = rng.standard_normal((tokens, cols)).astype(np.float32) * 3
+    b = rng.standard_normal((tokens, cols)).astype(np.float32)
+    norm_weight = (1.0 + 0.1 * rng.standard_normal(cols)).astype(np.float32)
+    planes = [synth.make_weight(7, 64, f"w{i}", rows, cols) for i, (rows, _) in enumerate(shapes)]
+    weights = [host.Nvfp4Sm100Weight.upload_checkpoint_nvfp4(ctx["stream"], abi.LAYOUT_STREAM, rows, cols, *planes[i])
+               for i, (rows, _) in enumerate(shapes)]
+    device = ctx["device"]
+    if residual:
+        x_dev = torch.zeros((tokens, cols), dtype=torch.float32, device=device)
+        program = host.Nvfp4Sm100NormGroupProgram.bind(ctx["plan"], weights, x_dev, torch.from_numpy(norm_weight).to(device), eps,
+                                                       torch.from_numpy(a).to(device), torch.from_numpy(b).to(device))
+        want_x, want_y, want_staged = oracle.rmsnorm_stage(None, norm_weight, eps, a, b)
+    else:
+        x_dev = torch.from_numpy(a).to(device)
+        program = host.Nvfp4Sm100NormGroupProgram.bind(ctx["plan"], weights, x_dev, torch.from_numpy(norm_weight).to(device), eps)
+        want_x, want_y, want_staged = oracle.rmsnorm_stage(a, norm_weight, eps)
+    before = host.allocation_snapshot(), host.launch_count()
+    program.submit_for_plan()
+    ctx["stream"].synchronize()
+    assert host.allocation_snapshot() == before[0] and host.launch_count() - before[1] == 1 + len(shapes)
+    assert ctx["plan"].device_status() == 0
+    # the norm stage is bit-exact with the CPU statement of the reference kernel's order
+    assert np.array_equal(x_dev.cpu().numpy().view(np.uint32), want_x.view(np.uint32))
+    assert np.array_equal(program.normalised.cpu().numpy().view(np.uint32), want_y.view(np.uint32))
+    assert np.array_equal(bits_from_torch_bf16(program.staged).reshape(want_staged.shape), want_staged)
+    for (rows, _), (codes, scales, glob), out in zip(shapes, planes, program.outputs):
+        y64 = oracle.linear_f64(codes, scales, glob, rows, cols, want_staged, threads=oracle.max_threads())
+        assert rel_error(bits_from_torch_bf16(out), y64) <= TOLERANCE
+
+
+def test_norm_group_rejects_inconsistent_members(ctx):
+    host, torch = ctx["host"], ctx["torch"]
+    tokens, cols = 4, 512
+    codes, scales, glob = synth.make_weight(8, 65, "w", 64, cols)
+    weight = host.Nvfp4Sm100Weight.upload_checkpoint_nvfp4(ctx["stream"], abi.LAYOUT_STREAM, 64, cols, codes, scales, glob)
+    x = torch.zeros((tokens, cols), dtype=torch.float32, device=ctx["device"])
+    w = torch.ones(cols, dtype=torch.float32, device=ctx["device"])
+    program = host.Nvfp4Sm100NormGroupProgram.bind(ctx["plan"], [weight], x, w)
+    s, plan, lib = ctx["stream"], ctx["plan"], abi.lib()
+
+    def status(mutate):
+        args = abi.NormGroupArgs.from_buffer_copy(program.args)
+        mutate(args)
+        launches = host.launch_count()
+        result = lib.augur_cuda_nvfp4_sm100_norm_group_prevalidated_submit_v1(s.ordinal, s.handle, plan.handle, byref(args))
+        assert host.launch_count() == launches      # nothing was enqueued
+        return result.status
+
+    program.submit_for_plan()                       # the unmodified descriptor is accepted
+    s.synchronize()
+    for mutate in (lambda a: setattr(a, "count", 0), lambda a: setattr(a, "count", 5), lambda a: setattr(a, "residual", 2),
+                   lambda a: setattr(a, "cols", cols + 128), lambda a: setattr(a, "tokens", 9), lambda a: setattr(a, "epsilon", -1.0),
+                   lambda a: setattr(a, "add_a", a.input_f32), lambda a: setattr(a, "staged_bf16", a.output_f32),
+                   lambda a: setattr(a.projections[0], "input_bf16", a.output_f32),
+                   lambda a: setattr(a.projections[0], "tokens", 3),
+                   lambda a: setattr(a.projections[1], "rows", 32),
+                   lambda a: setattr(a.projections[0], "output", a.staged_bf16),
+                   lambda a: setattr(a, "abi_version", 2)):
+        assert status(mutate) in (abi.STATUS_INVALID_ARGUMENT, abi.STATUS_ABI_VERSION_MISMATCH)

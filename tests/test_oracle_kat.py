@@ -185,3 +185,20 @@ def test_activation_quantiser_rule():
         d = oracle.act_dequant_f64(c, s, 2.0 ** -8, 4, 64, terms)
         errs.append(np.abs(d - xf).max())
     assert errs[0] > errs[1] > errs[2] and errs[2] < 2e-2
+
+
+def test_rmsnorm_stage_known_answers():
+    # all twos, weight one half, no epsilon: mean square 4, scale 1/2, y = 2 * 1/2 * 1/2
+    x = np.full((1, 256), 2.0, dtype=np.float32)
+    used, y, staged = oracle.rmsnorm_stage(x, np.full(256, 0.5, dtype=np.float32), 0.0)
+    assert np.array_equal(used, x) and np.all(y == 0.5) and np.all(staged == 0x3F00)
+    # the residual is one F32 add per element, stored back; the result follows the f64 definition closely
+    rng = np.random.default_rng(3)
+    a, b = rng.standard_normal((3, 512)).astype(np.float32), rng.standard_normal((3, 512)).astype(np.float32)
+    w = (1 + 0.1 * rng.standard_normal(512)).astype(np.float32)
+    used, y, staged = oracle.rmsnorm_stage(None, w, 1e-6, a, b)
+    assert np.array_equal(used, a + b)
+    exact = used.astype(np.float64) / np.sqrt((used.astype(np.float64) ** 2).mean(axis=1, keepdims=True) + 1e-6) * w
+    assert np.max(np.abs(y - exact)) <= 4e-7 * np.max(np.abs(exact))
+    from augur_v100_b200 import synth
+    assert np.array_equal(staged, synth.f32_to_bf16_bits(y))
