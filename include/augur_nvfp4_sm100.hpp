@@ -542,6 +542,73 @@ private:
     std::shared_ptr<DeviceBuffer> input_, intermediate_, staged_x_, staged_h_, output_;
 };
 
+// [residual add] -> RMSNorm -> BF16 stage -> one to four small-token projections as one validated program
+// (the reference's GDN-input and post-attention groups, native augur_qwen35_gdn_input_b8.cuh).
+class Nvfp4Sm100NormGroupProgram {
+public:
+    // `input_f32` is the residual stream [tokens][cols]; with `add_a` / `add_b` it is overwritten by their sum first.
+    static std::unique_ptr<Nvfp4Sm100NormGroupProgram> bind(std::shared_ptr<Plan> plan,
+                                                           std::vector<std::shared_ptr<Nvfp4Sm100Weight>> weights,
+                                                           std::shared_ptr<DeviceBuffer> input_f32,
+                                                           std::shared_ptr<DeviceBuffer> norm_weight_f32, uint32_t tokens, uint32_t cols,
+                                                           float epsilon, std::shared_ptr<DeviceBuffer> add_a = nullptr,
+                                                           std::shared_ptr<DeviceBuffer> add_b = nullptr) {
+        if (weights.empty() || weights.size() > 4) throw std::invalid_argument("one to four projections");
+        if (static_cast<bool>(add_a) != static_cast<bool>(add_b)) throw std::invalid_argument("the residual add takes both operands or none");
+        std::unique_ptr<Nvfp4Sm100NormGroupProgram> p(new Nvfp4Sm100NormGroupProgram());
+        const Stream& s = *plan->stream();
+        const int32_t d = s.ordinal();
+        const uint64_t elements = static_cast<uint64_t>(tokens) * cols;
+        p->normalised_ = std::make_shared<DeviceBuffer>(d, elements * 4);
+        p->staged_ = std::make_shared<DeviceBuffer>(d, elements * 2);
+        p->args_ = header<augur_cuda_nvfp4_sm100_norm_group_args_v1>();
+        if (add_a) {
+            p->args_.add_a = add_a->address();
+            p->args_.add_b = add_b->address();
+            p->args_.add_len_bytes = elements * 4;
+            p->args_.residual = 1;
+        }
+        p->args_.input_f32 = input_f32->address();
+        p->args_.input_len_bytes = elements * 4;
+        p->args_.weight_f32 = norm_weight_f32->address();
+        p->args_.weight_len_bytes = static_cast<uint64_t>(cols) * 4;
+        p->args_.output_f32 = p->normalised_->address();
+        p->args_.output_len_bytes = elements * 4;
+        p->args_.staged_bf16 = p->staged_->address();
+        p->args_.staged_len_bytes = elements * 2;
+        p->args_.tokens = tokens; p->args_.cols = cols; p->args_.epsilon = epsilon;
+        p->args_.count = static_cast<uint32_t>(weights.size());
+        for (size_t i = 0; i < weights.size(); ++i) {
+            if (plan->stream() != weights[i]->stream()) throw std::invalid_argument("plan and weight belong to different streams");
+            p->outputs_.push_back(std::make_shared<DeviceBuffer>(d, static_cast<uint64_t>(tokens) * weights[i]->rows() * 2));
+            p->args_.projections[i] = gemv_args(*weights[i], *p->staged_, *p->outputs_[i], tokens, AUGUR_NVFP4_SM100_EPILOGUE_LINEAR_BF16);
+        }
+        check("norm_group_preflight", augur_cuda_nvfp4_sm100_norm_group_preflight_v1(d, s.handle(), plan->raw(), &p->args_));
+        p->plan_ = std::move(plan);
+        p->weights_ = std::move(weights);
+        p->input_ = std::move(input_f32);
+        p->norm_weight_ = std::move(norm_weight_f32);
+        p->add_a_ = std::move(add_a);
+        p->add_b_ = std::move(add_b);
+        return p;
+    }
+    void submit_for_plan() const {
+        const Stream& s = *plan_->stream();
+        check("norm_group_submit", augur_cuda_nvfp4_sm100_norm_group_prevalidated_submit_v1(s.ordinal(), s.handle(), plan_->raw(), &args_));
+    }
+    const std::shared_ptr<DeviceBuffer>& normalised() const { return normalised_; }
+    const std::shared_ptr<DeviceBuffer>& staged() const { return staged_; }
+    const std::vector<std::shared_ptr<DeviceBuffer>>& outputs() const { return outputs_; }
+
+private:
+    Nvfp4Sm100NormGroupProgram() = default;
+    augur_cuda_nvfp4_sm100_norm_group_args_v1 args_{};
+    std::shared_ptr<Plan> plan_;
+    std::vector<std::shared_ptr<Nvfp4Sm100Weight>> weights_;
+    std::shared_ptr<DeviceBuffer> input_, norm_weight_, add_a_, add_b_, normalised_, staged_;
+    std::vector<std::shared_ptr<DeviceBuffer>> outputs_;
+};
+
 // The reference's batch classes (crates/augur-kernel-api/src/key.rs:354-365): up to 8 token rows are the
 // small-batch class (decode and the fixed B8 verify batch), anything wider is prefill.
 enum class BatchClass { SmallBatch, Prefill };

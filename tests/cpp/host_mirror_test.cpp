@@ -236,6 +236,46 @@ int main() {
             std::printf("prefill ffn: rms err %.3e\n", e);
             expect(e <= 2e-2, "prefill FFN within 2e-2 (rms) of the fp64 oracle");
         }
+        // ---- norm group: residual add -> RMSNorm -> BF16 stage -> two projections, 8 token rows ----
+        {
+            const uint32_t rows_a = 256, rows_b = 64;
+            Planes wa = make_planes(rng, rows_a, hidden), wb = make_planes(rng, rows_b, hidden);
+            const CheckpointNvfp4Matrix wa_m{wa.codes.data(), wa.scales.data(), wa.global}, wb_m{wb.codes.data(), wb.scales.data(), wb.global};
+            auto weight_a = Nvfp4Sm100Weight::upload_checkpoint_nvfp4(stream, AUGUR_NVFP4_SM100_LAYOUT_STREAM, rows_a, hidden, wa_m);
+            auto weight_b = Nvfp4Sm100Weight::upload_checkpoint_nvfp4(stream, AUGUR_NVFP4_SM100_LAYOUT_STREAM, rows_b, hidden, wb_m);
+            std::vector<float> add_a(tokens * hidden), add_b(tokens * hidden), norm_weight(hidden), used(tokens * hidden), want_y(tokens * hidden);
+            for (auto& v : add_a) v = static_cast<float>(rng.normal() * 3.0);
+            for (auto& v : add_b) v = static_cast<float>(rng.normal());
+            for (auto& v : norm_weight) v = static_cast<float>(1.0 + 0.1 * rng.normal());
+            std::vector<uint16_t> want_staged(tokens * hidden);
+            expect(augur_oracle_rmsnorm_stage(add_a.data(), add_b.data(), used.data(), norm_weight.data(), tokens, hidden, 1e-6f, 1,
+                                              want_y.data(), want_staged.data()) == 0, "oracle norm stage");
+            auto a_dev = std::make_shared<DeviceBuffer>(0, add_a.size() * 4), b_dev = std::make_shared<DeviceBuffer>(0, add_b.size() * 4);
+            auto x_dev32 = std::make_shared<DeviceBuffer>(0, used.size() * 4), w_dev = std::make_shared<DeviceBuffer>(0, norm_weight.size() * 4);
+            a_dev->upload(*stream, add_a.data(), add_a.size() * 4);
+            b_dev->upload(*stream, add_b.data(), add_b.size() * 4);
+            w_dev->upload(*stream, norm_weight.data(), norm_weight.size() * 4);
+            auto group_plan = std::make_shared<Plan>(stream, gemv_scratch_bytes(rows_a, hidden, tokens));
+            auto group = Nvfp4Sm100NormGroupProgram::bind(group_plan, {weight_a, weight_b}, x_dev32, w_dev, tokens, hidden, 1e-6f, a_dev, b_dev);
+            group->submit_for_plan();
+            std::vector<float> got_x(used.size()), got_y(want_y.size());
+            std::vector<uint16_t> got_staged(want_staged.size());
+            x_dev32->download(*stream, got_x.data(), got_x.size() * 4);
+            group->normalised()->download(*stream, got_y.data(), got_y.size() * 4);
+            group->staged()->download(*stream, got_staged.data(), got_staged.size() * 2);
+            expect(std::memcmp(got_x.data(), used.data(), used.size() * 4) == 0, "residual sum bit-exact");
+            expect(std::memcmp(got_y.data(), want_y.data(), want_y.size() * 4) == 0, "normalised output bit-exact");
+            expect(std::memcmp(got_staged.data(), want_staged.data(), want_staged.size() * 2) == 0, "staged BF16 bit-exact");
+            std::vector<uint16_t> out_a(tokens * rows_a);
+            group->outputs()[0]->download(*stream, out_a.data(), out_a.size() * 2);
+            std::vector<double> want(out_a.size()), have(out_a.size());
+            expect(augur_oracle_linear_f64(wa.codes.data(), wa.scales.data(), wa.global, rows_a, hidden, want_staged.data(), tokens,
+                                           want.data(), threads) == 0, "oracle group projection");
+            for (size_t i = 0; i < out_a.size(); ++i) have[i] = from_bf16(out_a[i]);
+            const double e = rel_error(have, want);
+            std::printf("norm group: projection max rel err %.3e\n", e);
+            expect(e <= 2e-2 && group_plan->device_status() == 0, "norm group projection within 2e-2 of the fp64 oracle");
+        }
     } catch (const std::exception& error) {
         std::printf("FAILED: exception: %s\n", error.what());
         return 1;
