@@ -473,6 +473,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant__
 #define AUGUR_GEMM_PAIR_STAGES 4
 #endif
 constexpr uint32_t kPairStages = AUGUR_GEMM_PAIR_STAGES;
+// Tensor memory of the pair kernel: 256 accumulator columns, then one set of token-row scale columns per stage
+// (16 each) and one set of weight-row scale columns per k-block slot (32 each).
+constexpr uint32_t kTmemPairSfA = 256;
+constexpr uint32_t kTmemPairSfB = kTmemPairSfA + kPairStages * 16;
+static_assert(kTmemPairSfB + kPairStages * 32 <= kTmemCols, "scale columns of all stages fit beside the accumulator");
 constexpr uint32_t kPairBytesB = 128 * 128;                                            // this CTA's 128 weight rows
 constexpr uint32_t kPairStageBytes = kBytesA + kPairBytesB + kBytesSfA + kBytesSfB;   // 38912
 // Epilogue staging: each epilogue warp parks its 32 rows x 256 BF16 here (rows padded by 16 bytes
@@ -532,8 +537,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* out_stage = smem + kPairStages * kPairStageBytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(out_stage + kPairOutBytes);
-    // full[S], empty[S], tmem_full, tmem_empty, scales_full[2], scales_empty[2]; then the TMEM base and the abort flag
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kPairStages + 6);
+    // full[S], empty[S], tmem_full, tmem_empty, scales_ready[S]; then the TMEM base and the abort flag
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * kPairStages + 2);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -541,16 +546,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
     const uint32_t pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
     const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + kPairStages);
     const uint32_t bar_tmem_full = smem_u32(bars + 2 * kPairStages), bar_tmem_empty = smem_u32(bars + 2 * kPairStages + 1);
-    const uint32_t bar_scales_full = smem_u32(bars + 2 * kPairStages + 2), bar_scales_empty = smem_u32(bars + 2 * kPairStages + 4);
+    const uint32_t bar_scales_ready = smem_u32(bars + 2 * kPairStages + 2);
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kPairStages; ++s) {
             mbar_init(bar_full + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, 1);
-        }
-        for (uint32_t b = 0; b < 2; ++b) {
-            mbar_init(bar_scales_full + 8 * b, 1);
-            mbar_init(bar_scales_empty + 8 * b, 1);
+            mbar_init(bar_scales_ready + 8 * s, 1);
         }
         mbar_init(bar_tmem_full, 1);
         mbar_init(bar_tmem_empty, 8);   // one arrival per epilogue warp of either CTA
@@ -583,6 +585,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
         // ---------------- TMA producer (both CTAs) ----------------
         uint32_t stage = 0, phase = 0;
         bool alive = true;
+#ifdef AUGUR_GEMM_PROBE_MMA_ONLY
+        alive = false;
+#endif
         for (uint32_t tile = pair; alive && tile < total_tiles; tile += pairs) {
             const uint32_t m_pair = tile % m_pairs, n_tile = tile / m_pairs;
             for (uint32_t step = 0; step < steps; ++step) {
@@ -593,10 +598,18 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
                 }
                 const uint32_t base = smem_u32(smem + stage * kPairStageBytes);
                 const uint32_t full = bar_full + 8 * stage;
+#ifdef AUGUR_GEMM_PROBE_NO_SF_TMA
+                if (rank == 0) mbar_expect_tx(full, 2 * (kBytesA + kPairBytesB));
+#else
                 if (rank == 0) mbar_expect_tx(full, 2 * kPairStageBytes);
+#endif
                 const uint32_t token_row = m_pair * 2 * kTileM + rank * kTileM;
                 tma_load_2d_pair(base, &map_act, kb * 128, term * p.padded_tokens + token_row, full);
                 tma_load_2d_pair(base + kBytesA, &map_weight, kb * 128, n_tile * kTileN + rank * 128, full);
+#ifdef AUGUR_GEMM_PROBE_NO_SF_TMA
+                if (++stage == kPairStages) { stage = 0; phase ^= 1; }
+                continue;
+#endif
                 tma_load_2d_pair(base + kBytesA + kPairBytesB, &map_act_sf, 0,
                                  term * act_term_atoms + (token_row / 128) * atoms_per_row_block + kb * 4, full);
                 tma_load_2d_pair(base + kBytesA + kPairBytesB + kBytesSfA, &map_weight_sf, 0,
@@ -610,10 +623,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
         // ---------------- MMA issuer (leader only) ----------------
         // Issuing a tcgen05 operation keeps a thread busy for tens of cycles, and one thread issuing the
         // 12 scale copies and the 4 MMAs of every stage could not keep the tensor pipe fed; the copies are
-        // issued by a thread of their own (below) into the double-buffered scale columns, this thread
-        // issues only the MMAs. Descriptors advance by additions (their low bits hold address >> 4).
-        uint32_t stage = 0, phase = 0, tmem_phase = 0, sf_buffer = 0, sf_phase = 0;
-        uint32_t kb_parity = 0;   // toggles with every k block, across tiles: consecutive k blocks never share a buffer
+        // issued by a thread of their own (below) into the stage's scale columns, this thread issues
+        // only the MMAs. Descriptors advance by additions (their low bits hold address >> 4).
+        uint32_t stage = 0, phase = 0, tmem_phase = 0;
+        uint32_t kb_slot = 0;   // k blocks counted across tiles, modulo kPairStages: the weight-row scale buffer
         bool alive = true;
         const uint32_t idesc = (1u << 7) | (1u << 10) | ((kTileN >> 3) << 17) | (((2 * kTileM) >> 4) << 24);
         const uint32_t smem_base = smem_u32(smem);
@@ -622,21 +635,31 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
         const uint32_t last_k_steps = (p.cols - (k_blocks - 1) * kBlockK) / 64;   // 1..4 k steps of 64 in the last k block
         for (uint32_t tile = pair; alive && tile < total_tiles; tile += pairs) {
             // the epilogues of both CTAs must have drained the previous tile's accumulator
+#ifndef AUGUR_GEMM_PROBE_NO_DRAIN_WAIT
             if (!mbar_wait(bar_tmem_empty, tmem_phase ^ 1, abort_flag, p.status_word, kErrMmaWaitTmem)) break;
+#endif
             tc_fence_after();
             uint32_t accumulate = 0, term = 0, kb = 0;
             for (uint32_t step = 0; step < steps; ++step) {
                 // operands in shared memory (TMA) and block scales in tensor memory (copy thread)
-                if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status_word, kErrMmaWaitFull) ||
-                    !mbar_wait(bar_scales_full + 8 * sf_buffer, sf_phase, abort_flag, p.status_word, kErrMmaWaitScales)) {
+#if defined(AUGUR_GEMM_PROBE_MMA_ONLY)
+#elif defined(AUGUR_GEMM_PROBE_NO_SCALES_WAIT)
+                if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status_word, kErrMmaWaitFull)) {
                     alive = false;
                     break;
                 }
+#else
+                if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status_word, kErrMmaWaitFull) ||
+                    !mbar_wait(bar_scales_ready + 8 * stage, phase, abort_flag, p.status_word, kErrMmaWaitScales)) {
+                    alive = false;
+                    break;
+                }
+#endif
                 tc_fence_after();
                 const uint64_t a_desc = a_desc0 + stage * kStageStep, b_desc = b_desc0 + stage * kStageStep;
                 // the token rows' scales change with every step (term), the weight rows' scales only with the k block
-                const uint32_t tmem_sfa = tmem_base + kTmemSfA + sf_buffer * 16;
-                const uint32_t tmem_sfb = tmem_base + kTmemSfB + kb_parity * 32;
+                const uint32_t tmem_sfa = tmem_base + kTmemPairSfA + stage * 16;
+                const uint32_t tmem_sfb = tmem_base + kTmemPairSfB + kb_slot * 32;
                 // each MMA consumes 64 k = 32 bytes of every row: start address + 2; only k steps inside the tensor
                 const uint32_t k_steps = (kb + 1 < k_blocks) ? 4u : last_k_steps;
                 if (k_steps == 4) {
@@ -652,10 +675,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
                     }
                 }
                 accumulate = 1;
-                tc_commit_pair(bar_empty + 8 * stage);                     // frees the stage in both CTAs
-                tc_commit_pair_local(bar_scales_empty + 8 * sf_buffer);    // and this half of the scale columns
-                if ((sf_buffer ^= 1) == 0) sf_phase ^= 1;
-                if (++term == p.terms) { term = 0; ++kb; kb_parity ^= 1; }
+                tc_commit_pair(bar_empty + 8 * stage);   // frees the stage, and with it the stage's scale columns, in both CTAs
+                if (++term == p.terms) {
+                    term = 0;
+                    ++kb;
+                    if (++kb_slot == kPairStages) kb_slot = 0;
+                }
                 if (++stage == kPairStages) { stage = 0; phase ^= 1; }
             }
             if (alive) tc_commit_pair(bar_tmem_full);     // both accumulator halves complete
@@ -663,29 +688,33 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
         }
     } else if (warp == 6 && lane == 0 && rank == 0) {
         // ---------------- scale-copy issuer (leader only): shared memory -> tensor memory, both CTAs ----------------
-        uint32_t stage = 0, phase = 0, sf_buffer = 0, sf_phase = 0, kb_parity = 0;
+        uint32_t stage = 0, phase = 0, kb_slot = 0;
         const uint32_t smem_base = smem_u32(smem);
         const uint64_t sfa_desc0 = sf_desc(smem_base + kBytesA + kPairBytesB), sfb_desc0 = sf_desc(smem_base + kBytesA + kPairBytesB + kBytesSfA);
         constexpr uint64_t kStageStep = kPairStageBytes >> 4, kAtomStep = kSfAtomBytes >> 4, kRowBlockStep = kBytesSfA >> 4;
         const uint32_t last_k_steps = (p.cols - (k_blocks - 1) * kBlockK) / 64;
         bool alive = true;
+#ifdef AUGUR_GEMM_PROBE_MMA_ONLY
+        alive = false;
+#endif
         for (uint32_t tile = pair; alive && tile < total_tiles; tile += pairs) {
             uint32_t term = 0, kb = 0;
             for (uint32_t step = 0; step < steps; ++step) {
-                // the stage's scale atoms have landed, and the MMAs that read this half of the scale columns are done
-                if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status_word, kErrCopyWait) ||
-                    !mbar_wait(bar_scales_empty + 8 * sf_buffer, sf_phase ^ 1, abort_flag, p.status_word, kErrCopyWait)) {
+                // The stage's scale atoms have landed. The producer refilled the stage only after the MMAs of the
+                // step that used it last (kPairStages steps ago) were complete, and operations complete in
+                // order, so every older MMA is complete too: the stage's token-row scale columns are free, and
+                // so are the weight-row scale columns of this k block's slot, last read by the k block
+                // kPairStages before it (at least kPairStages steps ago for any number of terms).
+                if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status_word, kErrCopyWait)) {
                     alive = false;
                     break;
                 }
                 tc_fence_after();
                 const uint64_t sfa_desc = sfa_desc0 + stage * kStageStep, sfb_desc = sfb_desc0 + stage * kStageStep;
-                // Token-row scales: one buffer per step parity. Weight-row scales are the same for all activation
-                // terms of a k block: copied with term 0 only, into the buffer of the k block's parity (counted across
-                // tiles). That buffer was last read by the steps of the k block before the previous one, which are older than the step whose completion
-                // was awaited above (operations complete in order), so it is free.
-                const uint32_t tmem_sfa = tmem_base + kTmemSfA + sf_buffer * 16;
-                const uint32_t tmem_sfb = tmem_base + kTmemSfB + kb_parity * 32;
+                // Token-row scales change with every step; weight-row scales are the same for all activation
+                // terms of a k block and are copied with term 0 only.
+                const uint32_t tmem_sfa = tmem_base + kTmemPairSfA + stage * 16;
+                const uint32_t tmem_sfb = tmem_base + kTmemPairSfB + kb_slot * 32;
                 const uint32_t k_steps = (kb + 1 < k_blocks) ? 4u : last_k_steps;
                 if (k_steps == 4) {
 #pragma unroll
@@ -714,9 +743,19 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
                         }
                     }
                 }
-                tc_commit_pair_local(bar_scales_full + 8 * sf_buffer);
-                if ((sf_buffer ^= 1) == 0) sf_phase ^= 1;
-                if (++term == p.terms) { term = 0; ++kb; kb_parity ^= 1; }
+#ifdef AUGUR_GEMM_SCALES_COMPLETE
+                tc_commit_pair_local(bar_scales_ready + 8 * stage);   // arrives when the copies are complete
+#else
+                // The copies only have to be issued before the MMAs that read them: a copy and a later MMA
+                // execute in issue order, and the fences on either side of this arrival order the two threads' issues.
+                tc_fence_before();
+                mbar_arrive(bar_scales_ready + 8 * stage);
+#endif
+                if (++term == p.terms) {
+                    term = 0;
+                    ++kb;
+                    if (++kb_slot == kPairStages) kb_slot = 0;
+                }
                 if (++stage == kPairStages) { stage = 0; phase ^= 1; }
             }
         }
