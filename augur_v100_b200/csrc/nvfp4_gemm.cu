@@ -467,8 +467,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant__
 //   full[s]   leader's only: one arrival (leader's producer, expecting the bytes of both CTAs);
 //             both producers' TMA loads complete on it (cta_group::2 loads, leader's address);
 //   empty[s]  one per CTA, arrived by the leader's tcgen05.commit multicast to both CTAs;
-//   tmem_full one per CTA, same multicast;   tmem_empty leader's only, 8 arrivals (4 epilogue
-//             warps of each CTA, the peer's through a cluster-scope arrive).
+//   tmem_full one per CTA, same multicast;   tmem_empty leader's only, one arrival per epilogue
+//             warp of either CTA (the peer's through a cluster-scope arrive);
+//   scales_landed[s] leader's only: the stage's block-scale atoms of both CTAs have landed (loaded before
+//             the operand tiles);   scales_ready[s] leader's only: the copy thread has issued the stage's
+//             shared -> tensor memory scale copies.
 #ifndef AUGUR_GEMM_PAIR_STAGES
 #define AUGUR_GEMM_PAIR_STAGES 4
 #endif
@@ -486,7 +489,9 @@ constexpr uint32_t kPairStageBytes = kBytesA + kPairBytesB + kBytesSfA + kBytesS
 constexpr uint32_t kPairOutRowBytes = kTileN * 2 + 16;
 constexpr uint32_t kPairOutBytes = kTileM * kPairOutRowBytes;                          // 67584
 constexpr uint32_t kPairSmemBytes = kPairStages * kPairStageBytes + kPairOutBytes + 1024 + 256;
-constexpr uint32_t kPairThreads = 224;          // TMA warp, MMA warp, 4 epilogue warps, scale-copy warp
+constexpr uint32_t kPairEpilogueWarps = 8;      // two per tensor-memory lane quadrant
+constexpr uint32_t kPairCopyWarp = 2 + kPairEpilogueWarps;
+constexpr uint32_t kPairThreads = 32 * (kPairCopyWarp + 1);   // TMA warp, MMA warp, epilogue warps, scale-copy warp
 constexpr uint32_t kLeaderMask = 0xFEFFFFFFu;   // clears the CTA-rank bit of a shared::cluster address within a pair
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -537,8 +542,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* out_stage = smem + kPairStages * kPairStageBytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(out_stage + kPairOutBytes);
-    // full[S], empty[S], tmem_full, tmem_empty, scales_ready[S]; then the TMEM base and the abort flag
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * kPairStages + 2);
+    // full[S], empty[S], tmem_full, tmem_empty, scales_ready[S], scales_landed[S]; then the TMEM base and the abort flag
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * kPairStages + 2);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -546,16 +551,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
     const uint32_t pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
     const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + kPairStages);
     const uint32_t bar_tmem_full = smem_u32(bars + 2 * kPairStages), bar_tmem_empty = smem_u32(bars + 2 * kPairStages + 1);
-    const uint32_t bar_scales_ready = smem_u32(bars + 2 * kPairStages + 2);
+    const uint32_t bar_scales_ready = smem_u32(bars + 2 * kPairStages + 2), bar_scales_landed = smem_u32(bars + 3 * kPairStages + 2);
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kPairStages; ++s) {
             mbar_init(bar_full + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, 1);
             mbar_init(bar_scales_ready + 8 * s, 1);
+            mbar_init(bar_scales_landed + 8 * s, 1);
         }
         mbar_init(bar_tmem_full, 1);
-        mbar_init(bar_tmem_empty, 8);   // one arrival per epilogue warp of either CTA
+        mbar_init(bar_tmem_empty, 2 * kPairEpilogueWarps);   // one arrival per epilogue warp of either CTA
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -598,24 +604,24 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
                 }
                 const uint32_t base = smem_u32(smem + stage * kPairStageBytes);
                 const uint32_t full = bar_full + 8 * stage;
-#ifdef AUGUR_GEMM_PROBE_NO_SF_TMA
-                if (rank == 0) mbar_expect_tx(full, 2 * (kBytesA + kPairBytesB));
-#else
-                if (rank == 0) mbar_expect_tx(full, 2 * kPairStageBytes);
-#endif
+                // The block scales go first, on a barrier of their own: they are small and land early, so the copy
+                // thread has them in tensor memory by the time the operand tiles arrive.
+                const uint32_t landed = bar_scales_landed + 8 * stage;
                 const uint32_t token_row = m_pair * 2 * kTileM + rank * kTileM;
+#ifndef AUGUR_GEMM_PROBE_NO_SF_TMA
+                if (rank == 0) mbar_expect_tx(landed, 2 * (kBytesSfA + kBytesSfB));
+                tma_load_2d_pair(base + kBytesA + kPairBytesB, &map_act_sf, 0,
+                                 term * act_term_atoms + (token_row / 128) * atoms_per_row_block + kb * 4, landed);
+                tma_load_2d_pair(base + kBytesA + kPairBytesB + kBytesSfA, &map_weight_sf, 0,
+                                 (n_tile * 2) * atoms_per_row_block + kb * 4, landed);
+                tma_load_2d_pair(base + kBytesA + kPairBytesB + 2 * kBytesSfA, &map_weight_sf, 0,
+                                 (n_tile * 2 + 1) * atoms_per_row_block + kb * 4, landed);
+#else
+                if (rank == 0) mbar_arrive(landed);
+#endif
+                if (rank == 0) mbar_expect_tx(full, 2 * (kBytesA + kPairBytesB));
                 tma_load_2d_pair(base, &map_act, kb * 128, term * p.padded_tokens + token_row, full);
                 tma_load_2d_pair(base + kBytesA, &map_weight, kb * 128, n_tile * kTileN + rank * 128, full);
-#ifdef AUGUR_GEMM_PROBE_NO_SF_TMA
-                if (++stage == kPairStages) { stage = 0; phase ^= 1; }
-                continue;
-#endif
-                tma_load_2d_pair(base + kBytesA + kPairBytesB, &map_act_sf, 0,
-                                 term * act_term_atoms + (token_row / 128) * atoms_per_row_block + kb * 4, full);
-                tma_load_2d_pair(base + kBytesA + kPairBytesB + kBytesSfA, &map_weight_sf, 0,
-                                 (n_tile * 2) * atoms_per_row_block + kb * 4, full);
-                tma_load_2d_pair(base + kBytesA + kPairBytesB + 2 * kBytesSfA, &map_weight_sf, 0,
-                                 (n_tile * 2 + 1) * atoms_per_row_block + kb * 4, full);
                 if (++stage == kPairStages) { stage = 0; phase ^= 1; }
             }
         }
@@ -642,7 +648,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
             uint32_t accumulate = 0, term = 0, kb = 0;
             for (uint32_t step = 0; step < steps; ++step) {
                 // operands in shared memory (TMA) and block scales in tensor memory (copy thread)
-#if defined(AUGUR_GEMM_PROBE_MMA_ONLY)
+#if defined(AUGUR_GEMM_PROBE_MMA_ONLY) || defined(AUGUR_GEMM_PROBE_NO_FULL_WAIT)
 #elif defined(AUGUR_GEMM_PROBE_NO_SCALES_WAIT)
                 if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status_word, kErrMmaWaitFull)) {
                     alive = false;
@@ -665,6 +671,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
                 if (k_steps == 4) {
 #pragma unroll
                     for (uint32_t k = 0; k < 4; ++k) {
+#ifdef AUGUR_GEMM_PROBE_TMA_ONLY
+                        break;
+#endif
                         tc_mma_pair(tmem_base + kTmemAcc, a_desc + 2 * k, b_desc + 2 * k, idesc, tmem_sfa + 4 * k, tmem_sfb + 8 * k,
                                     accumulate | k);
                     }
@@ -686,7 +695,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
             if (alive) tc_commit_pair(bar_tmem_full);     // both accumulator halves complete
             tmem_phase ^= 1;
         }
-    } else if (warp == 6 && lane == 0 && rank == 0) {
+    } else if (warp == kPairCopyWarp && lane == 0 && rank == 0) {
         // ---------------- scale-copy issuer (leader only): shared memory -> tensor memory, both CTAs ----------------
         uint32_t stage = 0, phase = 0, kb_slot = 0;
         const uint32_t smem_base = smem_u32(smem);
@@ -694,7 +703,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
         constexpr uint64_t kStageStep = kPairStageBytes >> 4, kAtomStep = kSfAtomBytes >> 4, kRowBlockStep = kBytesSfA >> 4;
         const uint32_t last_k_steps = (p.cols - (k_blocks - 1) * kBlockK) / 64;
         bool alive = true;
-#ifdef AUGUR_GEMM_PROBE_MMA_ONLY
+#if defined(AUGUR_GEMM_PROBE_MMA_ONLY) || defined(AUGUR_GEMM_PROBE_NO_SCALES_WAIT)
         alive = false;
 #endif
         for (uint32_t tile = pair; alive && tile < total_tiles; tile += pairs) {
@@ -705,7 +714,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
                 // order, so every older MMA is complete too: the stage's token-row scale columns are free, and
                 // so are the weight-row scale columns of this k block's slot, last read by the k block
                 // kPairStages before it (at least kPairStages steps ago for any number of terms).
-                if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status_word, kErrCopyWait)) {
+                if (!mbar_wait(bar_scales_landed + 8 * stage, phase, abort_flag, p.status_word, kErrCopyWait)) {
                     alive = false;
                     break;
                 }
@@ -759,49 +768,55 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
                 if (++stage == kPairStages) { stage = 0; phase ^= 1; }
             }
         }
-    } else if (warp >= 2 && warp < 6) {
+    } else if (warp >= 2 && warp < 2 + kPairEpilogueWarps) {
         // ---------------- epilogue (both CTAs): own TMEM half -> BF16 -> global ----------------
-        const uint32_t quadrant = warp & 3;
+        // Two warps per lane quadrant, 128 accumulator columns each. A warp reads its columns into registers
+        // in one go and releases the accumulator at once; conversion, staging and the stores to global memory
+        // run while the next tile's MMAs are already under way.
+        const uint32_t quadrant = warp & 3, half = (warp - 2) >> 2;
         uint32_t tmem_phase = 0;
+        // this warp's part of the staging rows (lane = row): BF16 columns half*128.. (plain) or outputs half*64.. (SwiGLU)
+        uint8_t* my_rows = out_stage + (quadrant * 32) * kPairOutRowBytes + half * (p.swiglu ? 128u : 256u);
         for (uint32_t tile = pair; tile < total_tiles; tile += pairs) {
             const uint32_t m_pair = tile % m_pairs, n_tile = tile / m_pairs;
             if (!mbar_wait(bar_tmem_full, tmem_phase, abort_flag, p.status_word, kErrEpilogueWait)) break;
             tc_fence_after();
-            // accumulator -> BF16 -> this warp's staging rows (lane = row)
-            uint8_t* my_rows = out_stage + (quadrant * 32) * kPairOutRowBytes;
-            for (uint32_t c = 0; c < kTileN; c += 32) {
-                uint32_t v[32];
-                tc_load32(tmem_base + kTmemAcc + ((quadrant * 32) << 16) + c, v);
-                tc_wait_ld();
+            uint32_t v[4][32];
+#pragma unroll
+            for (uint32_t c = 0; c < 4; ++c) tc_load32(tmem_base + kTmemAcc + ((quadrant * 32) << 16) + half * 128 + c * 32, v[c]);
+            tc_wait_ld();
+            // the accumulator is free for the next tile's MMAs from here on
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_leader(bar_tmem_empty);
+            tmem_phase ^= 1;
+#pragma unroll
+            for (uint32_t c = 0; c < 4; ++c) {
                 uint32_t packed[16];
-                convert_chunk(v, p.scale, p.scale_b, p.swiglu != 0, packed);
+                convert_chunk(v[c], p.scale, p.scale_b, p.swiglu != 0, packed);
                 if (p.swiglu) {
-                    uint4* dst = reinterpret_cast<uint4*>(my_rows + lane * kPairOutRowBytes + c);
+                    uint4* dst = reinterpret_cast<uint4*>(my_rows + lane * kPairOutRowBytes + c * 32);
                     dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                     dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
                 } else {
-                    uint4* dst = reinterpret_cast<uint4*>(my_rows + lane * kPairOutRowBytes + c * 2);
+                    uint4* dst = reinterpret_cast<uint4*>(my_rows + lane * kPairOutRowBytes + c * 64);
 #pragma unroll
                     for (uint32_t i = 0; i < 4; ++i) {
                         dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
                     }
                 }
             }
-            // the accumulator is free for the next tile's MMAs from here on
-            tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive_leader(bar_tmem_empty);
-            tmem_phase ^= 1;
-            // staging rows -> global, whole rows per instruction: 512 bytes (one row), or with SwiGLU
-            // 256 bytes (two rows per instruction)
+            // staging rows -> global: 256 contiguous bytes of a row per half warp, or with SwiGLU 128 bytes per quarter warp
             const uint32_t first_token = m_pair * 2 * kTileM + rank * kTileM + quadrant * 32;
             if (p.swiglu) {
                 const uint32_t out_width = p.rows / 2;
                 if (p.out) {
-                    uint8_t* out_base = reinterpret_cast<uint8_t*>(p.out + static_cast<uint64_t>(first_token) * out_width + n_tile * (kTileN / 2));
+                    uint8_t* out_base = reinterpret_cast<uint8_t*>(p.out + static_cast<uint64_t>(first_token) * out_width +
+                                                                   n_tile * (kTileN / 2) + half * 64);
 #pragma unroll 4
-                    for (uint32_t r2 = 0; r2 < 32; r2 += 2) {
-                        const uint32_t r = r2 + (lane >> 4), piece = lane & 15;
+                    for (uint32_t r4 = 0; r4 < 32; r4 += 4) {
+                        const uint32_t r = r4 + (lane >> 3), piece = lane & 7;
                         if (first_token + r >= p.tokens) continue;   // padding rows of the last tile are computed, never stored
                         const uint4 value = *reinterpret_cast<const uint4*>(my_rows + r * kPairOutRowBytes + piece * 16);
                         *reinterpret_cast<uint4*>(out_base + static_cast<uint64_t>(r) * out_width * 2 + piece * 16) = value;
@@ -809,13 +824,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
                 }
                 if (p.quant_out) {
                     // The same BF16 values, quantised for the next GEMM while the next tile's MMAs run: a lane takes
-                    // one 16-value group (8 lanes per row, 4 rows per step); the 8 code bytes of a row's 8 groups are
-                    // 64 contiguous bytes, the scale bytes of 4 groups one word of an atom.
+                    // one 16-value group (4 lanes per row, 8 rows per step); the code bytes of a row's 4 groups are
+                    // 32 contiguous bytes, their scale bytes one word of an atom.
                     const uint64_t code_bytes = tcgen05_codes_bytes(p.padded_tokens, out_width);
                     const uint64_t scale_bytes = tcgen05_scale_bytes(p.padded_tokens, out_width);
-                    for (uint32_t r4 = 0; r4 < 32; r4 += 4) {
-                        const uint32_t r = r4 + (lane >> 3), piece = lane & 7;
-                        const uint32_t token = first_token + r, group = n_tile * (kTileN / 32) + piece;
+                    for (uint32_t r8 = 0; r8 < 32; r8 += 8) {
+                        const uint32_t r = r8 + (lane >> 2), piece = lane & 3;
+                        const uint32_t token = first_token + r, group = n_tile * (kTileN / 32) + half * 4 + piece;
                         const uint4* src = reinterpret_cast<const uint4*>(my_rows + r * kPairOutRowBytes + piece * 32);
                         const uint4 lo = src[0], hi = src[1];
                         const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
@@ -835,7 +850,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
                             if (token < p.tokens) {
                                 *reinterpret_cast<uint2*>(p.quant_out + term * code_bytes + static_cast<uint64_t>(token) * (out_width / 2) + group * 8) =
                                     make_uint2(codes[0], codes[1]);
-                                if ((piece & 3u) == 0) {
+                                if (piece == 0) {
                                     *reinterpret_cast<uint32_t*>(p.quant_out + p.quant_terms * code_bytes + term * scale_bytes +
                                                                  tcgen05_scale_offset(token, group, out_width)) = quad;
                                 }
@@ -844,12 +859,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
                     }
                 }
             } else {
-                uint8_t* out_base = reinterpret_cast<uint8_t*>(p.out + static_cast<uint64_t>(first_token) * p.rows + n_tile * kTileN);
+                uint8_t* out_base = reinterpret_cast<uint8_t*>(p.out + static_cast<uint64_t>(first_token) * p.rows + n_tile * kTileN + half * 128);
 #pragma unroll 4
-                for (uint32_t r = 0; r < 32; ++r) {
-                    if (first_token + r >= p.tokens) break;   // padding rows of the last tile are computed, never stored
-                    const uint4 value = *reinterpret_cast<const uint4*>(my_rows + r * kPairOutRowBytes + lane * 16);
-                    *reinterpret_cast<uint4*>(out_base + static_cast<uint64_t>(r) * p.rows * 2 + lane * 16) = value;
+                for (uint32_t r2 = 0; r2 < 32; r2 += 2) {
+                    const uint32_t r = r2 + (lane >> 4), piece = lane & 15;
+                    if (first_token + r >= p.tokens) continue;   // padding rows of the last tile are computed, never stored
+                    const uint4 value = *reinterpret_cast<const uint4*>(my_rows + r * kPairOutRowBytes + piece * 16);
+                    *reinterpret_cast<uint4*>(out_base + static_cast<uint64_t>(r) * p.rows * 2 + piece * 16) = value;
                 }
             }
             __syncwarp();   // the rows are rewritten for the next tile
