@@ -473,7 +473,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant__
 //             the operand tiles);   scales_ready[s] leader's only: the copy thread has issued the stage's
 //             shared -> tensor memory scale copies.
 #ifndef AUGUR_GEMM_PAIR_STAGES
-#define AUGUR_GEMM_PAIR_STAGES 4
+#define AUGUR_GEMM_PAIR_STAGES 5
 #endif
 constexpr uint32_t kPairStages = AUGUR_GEMM_PAIR_STAGES;
 // Tensor memory of the pair kernel: 256 accumulator columns, then one set of token-row scale columns per stage
@@ -483,13 +483,13 @@ constexpr uint32_t kTmemPairSfB = kTmemPairSfA + kPairStages * 16;
 static_assert(kTmemPairSfB + kPairStages * 32 <= kTmemCols, "scale columns of all stages fit beside the accumulator");
 constexpr uint32_t kPairBytesB = 128 * 128;                                            // this CTA's 128 weight rows
 constexpr uint32_t kPairStageBytes = kBytesA + kPairBytesB + kBytesSfA + kBytesSfB;   // 38912
-// Epilogue staging: each epilogue warp parks its 32 rows x 256 BF16 here (rows padded by 16 bytes
-// so that the row-per-lane writes spread over all banks), releases the accumulator, and only
-// then writes the rows out, one coalesced 512-byte row per store instruction.
-constexpr uint32_t kPairOutRowBytes = kTileN * 2 + 16;
-constexpr uint32_t kPairOutBytes = kTileM * kPairOutRowBytes;                          // 67584
-constexpr uint32_t kPairSmemBytes = kPairStages * kPairStageBytes + kPairOutBytes + 1024 + 256;
+// Epilogue transposition rows: an epilogue warp holds one accumulator row per lane; to store row pieces that are
+// contiguous in global memory it parks one 32-column chunk (64 bytes of BF16 per row, rows padded by 16 bytes so
+// that the row-per-lane writes spread over all banks) and reads it back with 4 lanes per row.
 constexpr uint32_t kPairEpilogueWarps = 8;      // two per tensor-memory lane quadrant
+constexpr uint32_t kPairOutRowBytes = 64 + 16;
+constexpr uint32_t kPairOutBytes = kPairEpilogueWarps * 32 * kPairOutRowBytes;         // 20480
+constexpr uint32_t kPairSmemBytes = kPairStages * kPairStageBytes + kPairOutBytes + 1024 + 256;
 constexpr uint32_t kPairCopyWarp = 2 + kPairEpilogueWarps;
 constexpr uint32_t kPairThreads = 32 * (kPairCopyWarp + 1);   // TMA warp, MMA warp, epilogue warps, scale-copy warp
 constexpr uint32_t kLeaderMask = 0xFEFFFFFFu;   // clears the CTA-rank bit of a shared::cluster address within a pair
@@ -775,8 +775,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
         // run while the next tile's MMAs are already under way.
         const uint32_t quadrant = warp & 3, half = (warp - 2) >> 2;
         uint32_t tmem_phase = 0;
-        // this warp's part of the staging rows (lane = row): BF16 columns half*128.. (plain) or outputs half*64.. (SwiGLU)
-        uint8_t* my_rows = out_stage + (quadrant * 32) * kPairOutRowBytes + half * (p.swiglu ? 128u : 256u);
+        // this warp's transposition rows (lane = row): one 32-column chunk at a time
+        uint8_t* my_rows = out_stage + (warp - 2) * 32 * kPairOutRowBytes;
         for (uint32_t tile = pair; tile < total_tiles; tile += pairs) {
             const uint32_t m_pair = tile % m_pairs, n_tile = tile / m_pairs;
             if (!mbar_wait(bar_tmem_full, tmem_phase, abort_flag, p.status_word, kErrEpilogueWait)) break;
@@ -790,85 +790,90 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
             __syncwarp();
             if (lane == 0) mbar_arrive_leader(bar_tmem_empty);
             tmem_phase ^= 1;
+
+            const uint32_t first_token = m_pair * 2 * kTileM + rank * kTileM + quadrant * 32;
+            if (p.swiglu) {
+                // 32 accumulator columns = gate and up sums of 16 intermediate columns = one quantisation group per row
+                const uint32_t out_width = p.rows / 2;
+                const uint64_t code_bytes = tcgen05_codes_bytes(p.padded_tokens, out_width);
+                const uint64_t scale_bytes = tcgen05_scale_bytes(p.padded_tokens, out_width);
+                const uint32_t token = first_token + lane;
+                uint32_t scale_words[3] = {0, 0, 0};   // the scale bytes of this row's 4 groups, per term: one word of an atom
 #pragma unroll
-            for (uint32_t c = 0; c < 4; ++c) {
-                uint32_t packed[16];
-                convert_chunk(v[c], p.scale, p.scale_b, p.swiglu != 0, packed);
-                if (p.swiglu) {
-                    uint4* dst = reinterpret_cast<uint4*>(my_rows + lane * kPairOutRowBytes + c * 32);
-                    dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                    dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                } else {
-                    uint4* dst = reinterpret_cast<uint4*>(my_rows + lane * kPairOutRowBytes + c * 64);
+                for (uint32_t c = 0; c < 4; ++c) {
+                    uint32_t packed[16];
+                    convert_chunk(v[c], p.scale, p.scale_b, true, packed);
+                    if (p.quant_out) {
+                        // The BF16 values this lane holds, quantised for the next GEMM while the next tile's MMAs run.
+                        const uint32_t group = n_tile * (kTileN / 32) + half * 4 + c;
+                        float residual[16];
+#pragma unroll
+                        for (uint32_t i = 0; i < 8; ++i) {
+                            residual[2 * i] = __uint_as_float(packed[i] << 16);
+                            residual[2 * i + 1] = __uint_as_float(packed[i] & 0xffff0000u);
+                        }
+#pragma unroll
+                        for (uint32_t term = 0; term < 3; ++term) {
+                            if (term >= p.quant_terms) break;
+                            uint32_t codes[2], scale_code;
+                            quantise_term(residual, p.quant_global_scale, term + 1 < p.quant_terms, codes, &scale_code);
+                            scale_words[term] |= scale_code << (8 * c);
+                            if (token < p.tokens) {
+                                *reinterpret_cast<uint2*>(p.quant_out + term * code_bytes + static_cast<uint64_t>(token) * (out_width / 2) + group * 8) =
+                                    make_uint2(codes[0], codes[1]);
+                            }
+                        }
+                    }
+                    if (p.out) {
+                        // transpose through shared memory: 32 bytes of every row, written out as 2 lanes per row
+                        uint4* dst = reinterpret_cast<uint4*>(my_rows + lane * kPairOutRowBytes);
+                        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                        __syncwarp();
+                        uint8_t* out_base = reinterpret_cast<uint8_t*>(p.out + static_cast<uint64_t>(first_token) * out_width +
+                                                                       n_tile * (kTileN / 2) + half * 64 + c * 16);
+#pragma unroll
+                        for (uint32_t r16 = 0; r16 < 32; r16 += 16) {
+                            const uint32_t r = r16 + (lane >> 1), piece = lane & 1;
+                            if (first_token + r >= p.tokens) continue;   // padding rows of the last tile are computed, never stored
+                            const uint4 value = *reinterpret_cast<const uint4*>(my_rows + r * kPairOutRowBytes + piece * 16);
+                            *reinterpret_cast<uint4*>(out_base + static_cast<uint64_t>(r) * out_width * 2 + piece * 16) = value;
+                        }
+                        __syncwarp();   // the rows are rewritten for the next chunk
+                    }
+                }
+                if (p.quant_out && token < p.tokens) {
+#pragma unroll
+                    for (uint32_t term = 0; term < 3; ++term) {
+                        if (term >= p.quant_terms) break;
+                        *reinterpret_cast<uint32_t*>(p.quant_out + p.quant_terms * code_bytes + term * scale_bytes +
+                                                     tcgen05_scale_offset(token, n_tile * (kTileN / 32) + half * 4, out_width)) = scale_words[term];
+                    }
+                }
+            } else {
+#pragma unroll
+                for (uint32_t c = 0; c < 4; ++c) {
+                    uint32_t packed[16];
+                    convert_chunk(v[c], p.scale, p.scale_b, false, packed);
+                    // transpose through shared memory: 64 bytes of every row, written out as 4 lanes per row
+                    uint4* dst = reinterpret_cast<uint4*>(my_rows + lane * kPairOutRowBytes);
 #pragma unroll
                     for (uint32_t i = 0; i < 4; ++i) {
                         dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
                     }
-                }
-            }
-            __syncwarp();
-            // staging rows -> global: 256 contiguous bytes of a row per half warp, or with SwiGLU 128 bytes per quarter warp
-            const uint32_t first_token = m_pair * 2 * kTileM + rank * kTileM + quadrant * 32;
-            if (p.swiglu) {
-                const uint32_t out_width = p.rows / 2;
-                if (p.out) {
-                    uint8_t* out_base = reinterpret_cast<uint8_t*>(p.out + static_cast<uint64_t>(first_token) * out_width +
-                                                                   n_tile * (kTileN / 2) + half * 64);
-#pragma unroll 4
-                    for (uint32_t r4 = 0; r4 < 32; r4 += 4) {
-                        const uint32_t r = r4 + (lane >> 3), piece = lane & 7;
-                        if (first_token + r >= p.tokens) continue;   // padding rows of the last tile are computed, never stored
-                        const uint4 value = *reinterpret_cast<const uint4*>(my_rows + r * kPairOutRowBytes + piece * 16);
-                        *reinterpret_cast<uint4*>(out_base + static_cast<uint64_t>(r) * out_width * 2 + piece * 16) = value;
-                    }
-                }
-                if (p.quant_out) {
-                    // The same BF16 values, quantised for the next GEMM while the next tile's MMAs run: a lane takes
-                    // one 16-value group (4 lanes per row, 8 rows per step); the code bytes of a row's 4 groups are
-                    // 32 contiguous bytes, their scale bytes one word of an atom.
-                    const uint64_t code_bytes = tcgen05_codes_bytes(p.padded_tokens, out_width);
-                    const uint64_t scale_bytes = tcgen05_scale_bytes(p.padded_tokens, out_width);
+                    __syncwarp();
+                    uint8_t* out_base = reinterpret_cast<uint8_t*>(p.out + static_cast<uint64_t>(first_token) * p.rows + n_tile * kTileN +
+                                                                   half * 128 + c * 32);
+#pragma unroll
                     for (uint32_t r8 = 0; r8 < 32; r8 += 8) {
                         const uint32_t r = r8 + (lane >> 2), piece = lane & 3;
-                        const uint32_t token = first_token + r, group = n_tile * (kTileN / 32) + half * 4 + piece;
-                        const uint4* src = reinterpret_cast<const uint4*>(my_rows + r * kPairOutRowBytes + piece * 32);
-                        const uint4 lo = src[0], hi = src[1];
-                        const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-                        float residual[16];
-#pragma unroll
-                        for (uint32_t i = 0; i < 8; ++i) {
-                            residual[2 * i] = __uint_as_float(words[i] << 16);
-                            residual[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000u);
-                        }
-                        for (uint32_t term = 0; term < p.quant_terms; ++term) {
-                            uint32_t codes[2], scale_code;
-                            quantise_term(residual, p.quant_global_scale, term + 1 < p.quant_terms, codes, &scale_code);
-                            uint32_t quad = scale_code;
-                            quad |= __shfl_down_sync(0xffffffffu, scale_code, 1) << 8;
-                            quad |= __shfl_down_sync(0xffffffffu, scale_code, 2) << 16;
-                            quad |= __shfl_down_sync(0xffffffffu, scale_code, 3) << 24;
-                            if (token < p.tokens) {
-                                *reinterpret_cast<uint2*>(p.quant_out + term * code_bytes + static_cast<uint64_t>(token) * (out_width / 2) + group * 8) =
-                                    make_uint2(codes[0], codes[1]);
-                                if (piece == 0) {
-                                    *reinterpret_cast<uint32_t*>(p.quant_out + p.quant_terms * code_bytes + term * scale_bytes +
-                                                                 tcgen05_scale_offset(token, group, out_width)) = quad;
-                                }
-                            }
-                        }
+                        if (first_token + r >= p.tokens) continue;   // padding rows of the last tile are computed, never stored
+                        const uint4 value = *reinterpret_cast<const uint4*>(my_rows + r * kPairOutRowBytes + piece * 16);
+                        *reinterpret_cast<uint4*>(out_base + static_cast<uint64_t>(r) * p.rows * 2 + piece * 16) = value;
                     }
-                }
-            } else {
-                uint8_t* out_base = reinterpret_cast<uint8_t*>(p.out + static_cast<uint64_t>(first_token) * p.rows + n_tile * kTileN + half * 128);
-#pragma unroll 4
-                for (uint32_t r2 = 0; r2 < 32; r2 += 2) {
-                    const uint32_t r = r2 + (lane >> 4), piece = lane & 15;
-                    if (first_token + r >= p.tokens) continue;   // padding rows of the last tile are computed, never stored
-                    const uint4 value = *reinterpret_cast<const uint4*>(my_rows + r * kPairOutRowBytes + piece * 16);
-                    *reinterpret_cast<uint4*>(out_base + static_cast<uint64_t>(r) * p.rows * 2 + piece * 16) = value;
+                    __syncwarp();   // the rows are rewritten for the next chunk
                 }
             }
-            __syncwarp();   // the rows are rewritten for the next tile
         }
     }
 
