@@ -152,6 +152,7 @@ EXPORTS = {
     "augur_cuda_nvfp4_sm100_stream_destroy_v1": (Result, [c_void_p]),
     "augur_cuda_nvfp4_sm100_gemv_scratch_extent_host_v1": (Result, [c_uint32, c_uint32, c_uint32, POINTER(c_uint64)]),
     "augur_cuda_nvfp4_sm100_gemm_scratch_extent_host_v1": (Result, [c_uint32, c_uint32, c_uint32, c_uint32, POINTER(c_uint64)]),
+    "augur_cuda_nvfp4_sm100_gemm_plan_scratch_extent_host_v1": (Result, [c_uint32, POINTER(c_uint64)]),
     "augur_cuda_nvfp4_sm100_plan_create_v1": (Result, [c_int32, c_void_p, c_uint64, POINTER(c_void_p)]),
     "augur_cuda_nvfp4_sm100_plan_describe_v1": (Result, [c_void_p, POINTER(PlanSnapshot)]),
     "augur_cuda_nvfp4_sm100_plan_destroy_v1": (Result, [c_void_p]),

@@ -46,7 +46,8 @@ constexpr uint32_t kTmemSfB = 320;        // 2 x 32 columns
 constexpr uint32_t kWaitLimit = 20u * 1000u * 1000u;
 
 constexpr uint32_t kErrProducerWait = 0x101, kErrMmaWaitFull = 0x102, kErrMmaWaitTmem = 0x103,
-                   kErrEpilogueWait = 0x104, kErrCopyWait = 0x105, kErrMmaWaitScales = 0x106;
+                   kErrEpilogueWait = 0x104, kErrCopyWait = 0x105, kErrMmaWaitScales = 0x106,
+                   kErrSplitWait = 0x107;
 
 // ---- PTX wrappers ---------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -157,6 +158,10 @@ struct GemmParams {
     uint8_t* quant_out;            // staged activations: [terms] code planes of whole tiles, then the scale regions
     uint32_t quant_terms;
     float quant_global_scale;
+    // Pair tiles whose count is not a multiple of the pairs: the tiles left over are cut along k between all pairs
+    // (null: whole tiles only). Partial accumulators pass through `split_slots`, announced by `split_flags`.
+    float* split_slots;            // [pair][CTA of the pair][epilogue warp][128 columns / 4][lane] x float4
+    uint32_t* split_flags;         // [pair][CTA of the pair][epilogue warp], zero between launches
 };
 
 // ---- activation quantiser ------------------------------------------------------------------
@@ -492,6 +497,8 @@ constexpr uint32_t kPairOutBytes = kPairEpilogueWarps * 32 * kPairOutRowBytes;  
 constexpr uint32_t kPairSmemBytes = kPairStages * kPairStageBytes + kPairOutBytes + 1024 + 256;
 constexpr uint32_t kPairCopyWarp = 2 + kPairEpilogueWarps;
 constexpr uint32_t kPairThreads = 32 * (kPairCopyWarp + 1);   // TMA warp, MMA warp, epilogue warps, scale-copy warp
+constexpr uint32_t kSplitWaitLimit = 1u << 20;  // polls of a handed-over part's flag (each a round trip to L2) before giving up
+constexpr uint64_t kSplitSlotBytes = 2ull * kPairEpilogueWarps * 32 * 128 * 4;   // one pair's accumulator: 256 x 256 f32
 constexpr uint32_t kLeaderMask = 0xFEFFFFFFu;   // clears the CTA-rank bit of a shared::cluster address within a pair
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -516,7 +523,7 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
                  : "memory");
 }
 // Arrives on this CTA's barrier only, once the cta_group::2 operations this thread issued so far are done.
-__device__ __forceinline__ void tc_commit_pair_local(uint32_t bar) {
+[[maybe_unused]] __device__ __forceinline__ void tc_commit_pair_local(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void tc_copy_sf_pair(uint32_t tmem, uint64_t desc) {
@@ -532,6 +539,63 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t d, uint64_t a, uint64_t b, 
 }
 __device__ __forceinline__ void mbar_arrive_leader(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar & kLeaderMask) : "memory");
+}
+
+// The work of one CTA pair, in the order it is done: the head or middle part of a leftover tile (its partial
+// accumulator is handed to the pair that finishes the tile), the part that finishes a leftover tile, then the
+// pair's whole tiles. Tiles are numbered m-pair fastest; whole tiles of pair p are p, p + pairs, ...; with `split` the
+// tiles past the last full round are cut along k into equal contiguous ranges, one per pair, so that every pair
+// issues the same number of k blocks. A range is at most one tile long: it holds the tail of one tile, the head
+// of the next, or both. A part handed over is its pair's first item and nothing waits in front of it; a
+// finishing part follows, and only its epilogue warps wait (for first items of other pairs, about as long as
+// its own), with the accumulator already released; the reads of the handed-over sums then run under the
+// MMAs of the whole tiles that follow.
+struct PairItem {
+    uint32_t tile, kb0, kb1;
+    uint32_t kind;           // 0: whole tile, 1: part handed over, 2: part that finishes the tile
+    uint32_t first_giver;    // kind 2: the pairs first_giver .. this pair - 1 hand their parts over
+};
+struct PairWork {
+    uint32_t items, whole;
+    PairItem given, finishing;
+    bool gives, finishes;
+    __device__ PairItem item(uint32_t index, uint32_t pair, uint32_t pairs, uint32_t k_blocks) const {
+        const uint32_t parts = (gives ? 1u : 0u) + (finishes ? 1u : 0u);
+        if (gives && index == 0) return given;
+        if (finishes && index + 1 == parts) return finishing;
+        return PairItem{pair + (index - parts) * pairs, 0, k_blocks, 0, 0};
+    }
+};
+__device__ __forceinline__ PairWork pair_work(uint32_t pair, uint32_t pairs, uint32_t tiles, uint32_t k_blocks, bool split) {
+    PairWork w{};
+    if (!split) {
+        w.whole = tiles > pair ? (tiles - pair + pairs - 1) / pairs : 0;
+        w.items = w.whole;
+        return w;
+    }
+    w.whole = tiles / pairs;
+    const uint32_t first_left = w.whole * pairs;
+    const uint64_t units = static_cast<uint64_t>(tiles - first_left) * k_blocks;   // k blocks of the leftover tiles
+    const uint64_t x0 = pair * units / pairs, x1 = (pair + 1) * units / pairs;      // this pair's range (not empty: units >= pairs)
+    const uint32_t a = static_cast<uint32_t>(x0 / k_blocks), b = static_cast<uint32_t>((x1 - 1) / k_blocks);
+    const uint64_t a_begin = static_cast<uint64_t>(a) * k_blocks, a_end = a_begin + k_blocks;
+    if (x1 >= a_end) {
+        // the range holds the tail of tile a: every pair from the one that owns the tile's first k block hands over
+        w.finishes = true;
+        w.finishing = PairItem{first_left + a, static_cast<uint32_t>(x0 - a_begin), k_blocks, 2,
+                               static_cast<uint32_t>(((a_begin + 1) * pairs - 1) / units)};
+        if (w.finishing.first_giver == pair) w.finishing.kind = 0;   // the whole tile
+    } else {
+        w.gives = true;
+        w.given = PairItem{first_left + a, static_cast<uint32_t>(x0 - a_begin), static_cast<uint32_t>(x1 - a_begin), 1, 0};
+    }
+    if (b > a) {
+        // and the head of tile b (never all of it: the range is at most one tile long)
+        w.gives = true;
+        w.given = PairItem{first_left + b, 0, static_cast<uint32_t>(x1 - static_cast<uint64_t>(b) * k_blocks), 1, 0};
+    }
+    w.items = w.whole + (w.gives ? 1u : 0u) + (w.finishes ? 1u : 0u);
+    return w;
 }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
@@ -583,9 +647,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
     // A last k block that is only partly inside the tensor is loaded like the others (the TMA fills what lies past
     // the edge); the MMA issuer only consumes the k steps inside.
     const uint32_t k_blocks = (p.cols + kBlockK - 1) / kBlockK;
-    const uint32_t steps = k_blocks * p.terms;
     const uint32_t atoms_per_row_block = p.cols / 64;
     const uint32_t act_term_atoms = p.padded_tokens / 128 * atoms_per_row_block;   // scale atoms of one activation term
+    const PairWork work = pair_work(pair, pairs, total_tiles, k_blocks, p.split_slots != nullptr);
 
     if (warp == 0 && lane == 0) {
         // ---------------- TMA producer (both CTAs) ----------------
@@ -594,10 +658,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
 #ifdef AUGUR_GEMM_PROBE_MMA_ONLY
         alive = false;
 #endif
-        for (uint32_t tile = pair; alive && tile < total_tiles; tile += pairs) {
-            const uint32_t m_pair = tile % m_pairs, n_tile = tile / m_pairs;
-            for (uint32_t step = 0; step < steps; ++step) {
-                const uint32_t kb = step / p.terms, term = step % p.terms;
+        for (uint32_t index = 0; alive && index < work.items; ++index) {
+            const PairItem item = work.item(index, pair, pairs, k_blocks);
+            const uint32_t m_pair = item.tile % m_pairs, n_tile = item.tile / m_pairs;
+            const uint32_t item_steps = (item.kb1 - item.kb0) * p.terms;
+            for (uint32_t step = 0; step < item_steps; ++step) {
+                const uint32_t kb = item.kb0 + step / p.terms, term = step % p.terms;
                 if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status_word, kErrProducerWait)) {
                     alive = false;
                     break;
@@ -639,14 +705,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
         const uint64_t a_desc0 = operand_desc(smem_base), b_desc0 = operand_desc(smem_base + kBytesA);
         constexpr uint64_t kStageStep = kPairStageBytes >> 4;
         const uint32_t last_k_steps = (p.cols - (k_blocks - 1) * kBlockK) / 64;   // 1..4 k steps of 64 in the last k block
-        for (uint32_t tile = pair; alive && tile < total_tiles; tile += pairs) {
+        for (uint32_t index = 0; alive && index < work.items; ++index) {
+            const PairItem item = work.item(index, pair, pairs, k_blocks);
+            const uint32_t item_steps = (item.kb1 - item.kb0) * p.terms;
             // the epilogues of both CTAs must have drained the previous tile's accumulator
 #ifndef AUGUR_GEMM_PROBE_NO_DRAIN_WAIT
             if (!mbar_wait(bar_tmem_empty, tmem_phase ^ 1, abort_flag, p.status_word, kErrMmaWaitTmem)) break;
 #endif
             tc_fence_after();
-            uint32_t accumulate = 0, term = 0, kb = 0;
-            for (uint32_t step = 0; step < steps; ++step) {
+            uint32_t accumulate = 0, term = 0, kb = item.kb0;
+            for (uint32_t step = 0; step < item_steps; ++step) {
                 // operands in shared memory (TMA) and block scales in tensor memory (copy thread)
 #if defined(AUGUR_GEMM_PROBE_MMA_ONLY) || defined(AUGUR_GEMM_PROBE_NO_FULL_WAIT)
 #elif defined(AUGUR_GEMM_PROBE_NO_SCALES_WAIT)
@@ -706,9 +774,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
 #if defined(AUGUR_GEMM_PROBE_MMA_ONLY) || defined(AUGUR_GEMM_PROBE_NO_SCALES_WAIT)
         alive = false;
 #endif
-        for (uint32_t tile = pair; alive && tile < total_tiles; tile += pairs) {
-            uint32_t term = 0, kb = 0;
-            for (uint32_t step = 0; step < steps; ++step) {
+        for (uint32_t index = 0; alive && index < work.items; ++index) {
+            const PairItem item = work.item(index, pair, pairs, k_blocks);
+            const uint32_t item_steps = (item.kb1 - item.kb0) * p.terms;
+            uint32_t term = 0, kb = item.kb0;
+            for (uint32_t step = 0; step < item_steps; ++step) {
                 // The stage's scale atoms have landed. The producer refilled the stage only after the MMAs of the
                 // step that used it last (kPairStages steps ago) were complete, and operations complete in
                 // order, so every older MMA is complete too: the stage's token-row scale columns are free, and
@@ -777,8 +847,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
         uint32_t tmem_phase = 0;
         // this warp's transposition rows (lane = row): one 32-column chunk at a time
         uint8_t* my_rows = out_stage + (warp - 2) * 32 * kPairOutRowBytes;
-        for (uint32_t tile = pair; tile < total_tiles; tile += pairs) {
-            const uint32_t m_pair = tile % m_pairs, n_tile = tile / m_pairs;
+        for (uint32_t index = 0; index < work.items; ++index) {
+            const PairItem item = work.item(index, pair, pairs, k_blocks);
+            const uint32_t m_pair = item.tile % m_pairs, n_tile = item.tile / m_pairs;
             if (!mbar_wait(bar_tmem_full, tmem_phase, abort_flag, p.status_word, kErrEpilogueWait)) break;
             tc_fence_after();
             uint32_t v[4][32];
@@ -790,6 +861,61 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
             __syncwarp();
             if (lane == 0) mbar_arrive_leader(bar_tmem_empty);
             tmem_phase ^= 1;
+
+            if (item.kind == 1) {
+                // a part of a leftover tile: the sums go, as they are, to the pair that finishes the tile
+                const uint32_t slot = (pair * 2 + rank) * kPairEpilogueWarps + (warp - 2);
+                float4* dst = reinterpret_cast<float4*>(p.split_slots) + static_cast<uint64_t>(slot) * (32 * 32) + lane;
+#pragma unroll
+                for (uint32_t c = 0; c < 4; ++c) {
+#pragma unroll
+                    for (uint32_t i = 0; i < 8; ++i) {
+                        dst[(c * 8 + i) * 32] = make_float4(__uint_as_float(v[c][4 * i]), __uint_as_float(v[c][4 * i + 1]),
+                                                            __uint_as_float(v[c][4 * i + 2]), __uint_as_float(v[c][4 * i + 3]));
+                    }
+                }
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) atomicExch(p.split_flags + slot, 1u);
+                continue;
+            }
+            if (item.kind == 2) {
+                // the part that finishes a leftover tile: add the parts handed over, in pair order
+                bool arrived = true;
+                for (uint32_t giver = item.first_giver; giver < pair; ++giver) {
+                    const uint32_t slot = (giver * 2 + rank) * kPairEpilogueWarps + (warp - 2);
+                    if (lane == 0) {
+                        uint32_t spin = 0;
+                        while (atomicAdd(p.split_flags + slot, 0u) == 0u) {
+                            if (++spin > kSplitWaitLimit || ((spin & 255u) == 255u && *abort_flag)) { arrived = false; break; }
+                        }
+                    }
+                    arrived = __shfl_sync(0xffffffffu, arrived, 0);
+                    if (!arrived) break;
+                    __threadfence();
+                    const float4* src = reinterpret_cast<const float4*>(p.split_slots) + static_cast<uint64_t>(slot) * (32 * 32) + lane;
+#pragma unroll
+                    for (uint32_t c = 0; c < 4; ++c) {
+#pragma unroll
+                        for (uint32_t i = 0; i < 8; ++i) {
+                            const float4 part = __ldcg(src + (c * 8 + i) * 32);
+                            v[c][4 * i] = __float_as_uint(__uint_as_float(v[c][4 * i]) + part.x);
+                            v[c][4 * i + 1] = __float_as_uint(__uint_as_float(v[c][4 * i + 1]) + part.y);
+                            v[c][4 * i + 2] = __float_as_uint(__uint_as_float(v[c][4 * i + 2]) + part.z);
+                            v[c][4 * i + 3] = __float_as_uint(__uint_as_float(v[c][4 * i + 3]) + part.w);
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) p.split_flags[slot] = 0;   // the flags read zero again when the launch is over
+                }
+                if (!arrived) {
+                    if (lane == 0) {
+                        *abort_flag = 1;
+                        atomicCAS(p.status_word, 0u, kErrSplitWait);
+                    }
+                    break;
+                }
+            }
 
             const uint32_t first_token = m_pair * 2 * kTileM + rank * kTileM + quadrant * 32;
             if (p.swiglu) {
@@ -986,6 +1112,15 @@ bool pair_tiles_enabled() {
     return enabled;
 }
 
+// AUGUR_NVFP4_SM100_GEMM_SPLIT=0 keeps leftover tiles whole (measurement aid).
+bool split_tiles_enabled() {
+    static const bool enabled = [] {
+        const char* value = getenv("AUGUR_NVFP4_SM100_GEMM_SPLIT");
+        return !(value && value[0] == '0');
+    }();
+    return enabled;
+}
+
 // ---- validation ------------------------------------------------------------------------------------
 bool act_shape_ok(uint32_t tokens, uint32_t cols, uint32_t terms) {
     return tokens && cols && tokens <= (1u << 24) && cols % 64 == 0 && terms >= 1 && terms <= 3 &&
@@ -1063,6 +1198,13 @@ cudaError_t gemm_configure_device() {
 }  // namespace augur_sm100
 
 using namespace augur_sm100;
+
+extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_plan_scratch_extent_host_v1(
+    uint32_t sm_count, uint64_t* out_bytes) {
+    if (!out_bytes || !sm_count || sm_count > 4096) return invalid();
+    *out_bytes = kCounterBytes + static_cast<uint64_t>(sm_count / 2) * kSplitSlotBytes;
+    return ok();
+}
 
 extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_scratch_extent_host_v1(
     uint32_t rows, uint32_t cols, uint32_t tokens, uint32_t activation_terms, uint64_t* out_bytes) {
@@ -1148,8 +1290,18 @@ augur_cuda_result_v1 launch_gemm(augur_cuda_stream_t s, const augur_cuda_nvfp4_s
                             static_cast<uint64_t>(a->activation_terms) * (padded / 128) * atoms_per_row_block)) {
             return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE);
         }
-        uint32_t pairs = (padded / (2 * kTileM)) * (a->rows / kTileN);
+        const uint32_t tiles = (padded / (2 * kTileM)) * (a->rows / kTileN);
+        uint32_t pairs = tiles;
         if (pairs > plan->sm_count / 2) pairs = plan->sm_count / 2;
+        // Tiles past the last full round of the pairs are cut along k between all pairs when the plan's scratch
+        // has room for the partial accumulators handed over (one slot per pair behind the counter regions, whose
+        // first words serve as the flags) and the leftover tiles hold at least one k block per pair.
+        const uint32_t k_blocks = (a->cols + kBlockK - 1) / kBlockK;
+        if (split_tiles_enabled() && tiles % pairs != 0 && static_cast<uint64_t>(tiles % pairs) * k_blocks >= pairs &&
+            plan->scratch_bytes >= kCounterBytes + pairs * kSplitSlotBytes) {
+            p.split_flags = reinterpret_cast<uint32_t*>(plan->scratch);
+            p.split_slots = reinterpret_cast<float*>(plan->scratch + kCounterBytes);
+        }
         gemm_pair_kernel<<<2 * pairs, kPairThreads, kPairSmemBytes, s->stream>>>(map_act, map_weight, map_act_sf, map_weight_sf, p);
         count_launch();
         return submitted();

@@ -43,13 +43,6 @@ constexpr uint32_t kWaitLimit = 1u << 18;   // bounded polls of a ring slot befo
 constexpr uint32_t kMaxSlabBlocks = 40;    // 40 * 128 k = 5120 activations columns per slab (80 KB)
 constexpr uint32_t kSlotFloats = 256;      // one partial tile: 32 lanes x 8 f32
 constexpr uint32_t kCombineBlocks = 48;    // weight blocks a CTA streams in the time of one cross-CTA combine
-// Plan scratch layout: two arrival-counter regions (one per member of a two-launch program)
-// at fixed offsets, then partial-sum slots. Counters must read zero when a launch starts and
-// every launch leaves them at zero; keeping them apart from the slots means no launch of any
-// shape can ever leave slot data where another launch expects counters.
-constexpr uint32_t kMaxGroups = 16384;
-constexpr uint64_t kCounterRegionBytes = static_cast<uint64_t>(kMaxGroups) * 4;
-constexpr uint64_t kCounterBytes = 2 * kCounterRegionBytes;
 
 struct GemvParams {
     const uint8_t* weight;

@@ -75,6 +75,14 @@ inline augur_cuda_result_v1 invalid() { return make_result(AUGUR_CUDA_STATUS_INV
 // `ordinal` and lie inside one allocation. Also gates on compute capability 10.x.
 bool inspect_device_ranges(int32_t ordinal, const Range* ranges, size_t count,
                            augur_cuda_result_v1* failure);
+// Plan scratch layout: two arrival-counter regions (one per member of a two-launch program)
+// at fixed offsets, then partial-sum slots. Counters must read zero when a launch starts and
+// every launch leaves them at zero; keeping them apart from the slots means no launch of any
+// shape can ever leave slot data where another launch expects counters.
+constexpr uint32_t kMaxGroups = 16384;
+constexpr uint64_t kCounterRegionBytes = static_cast<uint64_t>(kMaxGroups) * 4;
+constexpr uint64_t kCounterBytes = 2 * kCounterRegionBytes;
+
 bool plan_ok(const augur_cuda_nvfp4_sm100_plan_v1* plan, int32_t ordinal, augur_cuda_stream_t stream);
 Range plan_scratch_range(const augur_cuda_nvfp4_sm100_plan_v1* plan);
 

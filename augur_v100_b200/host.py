@@ -104,6 +104,16 @@ def gemv_scratch_bytes(rows: int, cols: int, tokens: int = 8) -> int:
     return int(out.value)
 
 
+def gemm_plan_scratch_bytes(sm_count: int = 0) -> int:
+    """Plan scratch with which the prefill GEMM can cut its leftover tiles along k (0: this device's SM count)."""
+    if not sm_count:
+        import torch
+        sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    out = c_uint64(0)
+    _check("gemm_plan_scratch_extent", abi.lib().augur_cuda_nvfp4_sm100_gemm_plan_scratch_extent_host_v1(sm_count, byref(out)))
+    return out.value
+
+
 def gemm_scratch_bytes(rows: int, cols: int, tokens: int, terms: int) -> int:
     """Bytes of the staged (quantised) activations of a prefill linear: whole 128-row tiles per term."""
     out = c_uint64()

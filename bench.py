@@ -200,7 +200,7 @@ def prefill_probe(torch, host, abi, stream, device):
     from augur_v100_b200 import synth
     out = {}
     try:
-        plan = host.Plan(stream, 1 << 20)
+        plan = host.Plan(stream, host.gemm_plan_scratch_bytes())   # room to cut the leftover tiles along k
         generator = torch.Generator(device=device)
         generator.manual_seed(77)
         tokens = 4096
@@ -266,7 +266,7 @@ def prefill_mlp_probe(torch, host, abi, stream, device, world, rank, tokens, chu
     dc, ds = device_planes(torch, generator, HIDDEN, shard, device)
     down = host.Nvfp4Sm100Weight.repack_device_planes(stream, abi.LAYOUT_TCGEN05, HIDDEN, shard, dc, ds, synth.GLOBAL_SCALE)
     del gc, gs, uc, us, dc, ds
-    plan = host.Plan(stream, 1 << 20)
+    plan = host.Plan(stream, host.gemm_plan_scratch_bytes())   # room to cut the leftover tiles along k
     x = torch.randn((tokens, HIDDEN), device=device, generator=generator).to(torch.bfloat16)
     block = tp.TensorParallelPrefillMlp(plan, gate_up, down, x, world, chunk_tokens=chunk, terms=terms,
                                         input_global_scale=2.0 ** -8, intermediate_global_scale=2.0 ** -6)

@@ -125,6 +125,13 @@ augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_scratch_extent_
     uint32_t rows, uint32_t cols, uint32_t tokens, uint64_t* out_bytes);
 augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_scratch_extent_host_v1(
     uint32_t rows, uint32_t cols, uint32_t tokens, uint32_t activation_terms, uint64_t* out_bytes);
+/* Bytes of plan scratch with which the prefill GEMM balances its last round of tiles on a device of
+ * `sm_count` SMs: when the 256 x 256 tiles are not a multiple of the CTA pairs, the tiles left over are cut
+ * along k between all pairs and the partial accumulators pass through the plan's scratch (one 256 KB slot
+ * per pair behind the counter regions). With a smaller plan the GEMM keeps every tile whole; results agree
+ * to f32 summation order. */
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_plan_scratch_extent_host_v1(
+    uint32_t sm_count, uint64_t* out_bytes);
 
 augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_plan_create_v1(
     int32_t ordinal, augur_cuda_stream_t stream, uint64_t scratch_len_bytes,

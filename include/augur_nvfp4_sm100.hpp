@@ -163,6 +163,12 @@ inline uint64_t gemm_scratch_bytes(uint32_t rows, uint32_t cols, uint32_t tokens
     check("gemm_scratch_extent", augur_cuda_nvfp4_sm100_gemm_scratch_extent_host_v1(rows, cols, tokens, terms, &bytes));
     return bytes;
 }
+// Plan scratch with which the prefill GEMM can cut its leftover tiles along k on a device of `sm_count` SMs.
+inline uint64_t gemm_plan_scratch_bytes(uint32_t sm_count) {
+    uint64_t bytes = 0;
+    check("gemm_plan_scratch_extent", augur_cuda_nvfp4_sm100_gemm_plan_scratch_extent_host_v1(sm_count, &bytes));
+    return bytes;
+}
 inline uint64_t repack_extent(uint32_t layout, uint32_t rows, uint32_t cols) {
     uint64_t bytes = 0;
     check("repack_extent", augur_cuda_nvfp4_sm100_repack_extent_host_v1(layout, rows, cols, &bytes));

@@ -129,3 +129,64 @@ def simulate(rows, cols, pair, sms):
 @pytest.mark.parametrize("sms", [148, 132, 7, 1])
 def test_every_block_once_and_counters_match(rows, cols, pair, sms):
     simulate(rows, cols, pair, sms)
+
+
+# ---- pair-tile GEMM: leftover tiles cut along k (csrc/nvfp4_gemm.cu, pair_work) -----------------------------
+def pair_work(pair, pairs, tiles, k_blocks):
+    """The items of one CTA pair in the order the kernel does them: (tile, kb0, kb1, kind, first_giver)."""
+    whole = tiles // pairs
+    first_left = whole * pairs
+    units = (tiles - first_left) * k_blocks
+    x0, x1 = pair * units // pairs, (pair + 1) * units // pairs
+    a, b = x0 // k_blocks, (x1 - 1) // k_blocks
+    a_begin, a_end = a * k_blocks, (a + 1) * k_blocks
+    given = finishing = None
+    if x1 >= a_end:
+        first_giver = ((a_begin + 1) * pairs - 1) // units
+        finishing = (first_left + a, x0 - a_begin, k_blocks, 0 if first_giver == pair else 2, first_giver)
+    else:
+        given = (first_left + a, x0 - a_begin, x1 - a_begin, 1, 0)
+    if b > a:
+        assert given is None
+        given = (first_left + b, 0, x1 - b * k_blocks, 1, 0)
+    return ([given] if given else []) + ([finishing] if finishing else []) + [(pair + i * pairs, 0, k_blocks, 0, 0) for i in range(whole)]
+
+
+@pytest.mark.parametrize("tiles,pairs,k_blocks", [(320, 74, 68), (80, 74, 13), (80, 74, 20), (272, 74, 20), (1088, 74, 20),
+                                                  (75, 74, 74), (147, 74, 2), (5, 2, 7), (9, 4, 5), (320, 66, 34)])
+def test_pair_tile_leftover_split(tiles, pairs, k_blocks):
+    left = tiles % pairs
+    assert left and left * k_blocks >= pairs        # the condition under which the host enables the split
+    done = {}
+    givers = {}
+    finisher = {}
+    load = []
+    for pair in range(pairs):
+        items = pair_work(pair, pairs, tiles, k_blocks)
+        kinds = [item[3] for item in items]
+        assert kinds.count(1) <= 1 and kinds.count(2) <= 1
+        assert all(k != 1 for k in kinds[1:]) and all(k != 2 for k in kinds[2:])    # handed-over first, finishing next
+        assert 2 not in kinds[1:] or kinds[0] == 1
+        blocks = 0
+        for tile, kb0, kb1, kind, first_giver in items:
+            assert 0 <= kb0 < kb1 <= k_blocks
+            for kb in range(kb0, kb1):
+                assert (tile, kb) not in done
+                done[(tile, kb)] = pair
+            blocks += kb1 - kb0
+            if kind == 1:
+                givers.setdefault(tile, []).append(pair)
+            elif kind == 2:
+                finisher[tile] = (pair, first_giver)
+            elif kb0 == 0 and kb1 == k_blocks:
+                pass
+            else:
+                raise AssertionError("a partial item must hand over or finish")
+        load.append(blocks)
+    assert len(done) == tiles * k_blocks
+    assert max(load) - min(load) <= 1                # every pair issues the same number of k blocks
+    for tile, who in givers.items():
+        pair, first_giver = finisher[tile]
+        assert who == list(range(first_giver, pair))  # exactly the pairs the finisher waits for, in order
+    for tile, (pair, first_giver) in finisher.items():
+        assert first_giver < pair and tile in givers

@@ -47,7 +47,7 @@ def test_activation_quantiser_is_bit_exact(ctx, tokens, cols, terms, glob):
     assert np.array_equal(codes, want_codes)
 
 
-def _run_gemm(ctx, w_planes, a_codes, a_scales, rows, cols, tokens, terms, g_w, g_a):
+def _run_gemm(ctx, w_planes, a_codes, a_scales, rows, cols, tokens, terms, g_w, g_a, plan=None):
     """Uploads explicit weight and (already quantised) activation planes and runs the GEMM entry."""
     host, torch = ctx["host"], ctx["torch"]
     weight = host.Nvfp4Sm100Weight.upload_checkpoint_nvfp4(ctx["stream"], abi.LAYOUT_TCGEN05, rows, cols,
@@ -79,7 +79,7 @@ def _run_gemm(ctx, w_planes, a_codes, a_scales, rows, cols, tokens, terms, g_w, 
     args.output_bf16, args.output_len_bytes = out.data_ptr(), out.numel() * 2
     args.rows, args.cols, args.tokens, args.activation_terms = rows, cols, tokens, terms
     args.weight_global_scale, args.activation_global_scale = g_w, g_a
-    s, plan, lib = ctx["stream"], ctx["plan"], abi.lib()
+    s, plan, lib = ctx["stream"], plan or ctx["plan"], abi.lib()
     res = lib.augur_cuda_nvfp4_sm100_gemm_bf16_preflight_v1(s.ordinal, s.handle, plan.handle, byref(args))
     assert res.status == 0, (res.status, res.raw_cuda_status)
     res = lib.augur_cuda_nvfp4_sm100_gemm_bf16_prevalidated_submit_v1(s.ordinal, s.handle, plan.handle, byref(args))
@@ -92,7 +92,7 @@ def _run_gemm(ctx, w_planes, a_codes, a_scales, rows, cols, tokens, terms, g_w, 
     return bits_from_torch_bf16(out)
 
 
-def _check_gemm(ctx, rows, cols, tokens, terms=1, seed=0, unit_scales=False):
+def _check_gemm(ctx, rows, cols, tokens, terms=1, seed=0, unit_scales=False, plan=None):
     w_codes, w_scales, g_w = synth.make_weight(seed, 70, "w", rows, cols)
     g_a = 2.0 ** -8
     x_bits = synth.make_activation(seed, 70, "x", tokens, cols)
@@ -100,7 +100,7 @@ def _check_gemm(ctx, rows, cols, tokens, terms=1, seed=0, unit_scales=False):
     if unit_scales:
         w_scales = np.full_like(w_scales, 0x38)
         a_scales = np.full_like(a_scales, 0x38)
-    got = _run_gemm(ctx, (w_codes, w_scales), a_codes, a_scales, rows, cols, tokens, terms, g_w, g_a)
+    got = _run_gemm(ctx, (w_codes, w_scales), a_codes, a_scales, rows, cols, tokens, terms, g_w, g_a, plan=plan)
     a64 = oracle.act_dequant_f64(a_codes, a_scales, g_a, tokens, cols, terms)
     y64 = oracle.linear_f64_xf64(w_codes, w_scales, g_w, rows, cols, a64, threads=oracle.max_threads())
     err = rel_error(got, y64)
@@ -170,6 +170,22 @@ def test_gemm_pair_tiles_terms_share_weight_scales_across_tiles(ctx):
     # an odd number of k blocks (3), two activation terms and more tiles than CTA pairs: the weight-row scale
     # buffers alternate per k block across the tile boundary while two terms share each copy
     _check_gemm(ctx, rows=2560, cols=768, tokens=2048, terms=2, seed=14)
+
+
+@pytest.mark.parametrize("cols,terms", [(3328, 1), (1280, 2), (320, 1)])
+def test_gemm_pair_tiles_leftover_round_cut_along_k(ctx, cols, terms):
+    # 80 pair tiles for at most 74 pairs: with a plan that has room for the handed-over accumulators the 6 tiles
+    # of the last round are cut along k between all pairs (13 k blocks: about one per pair; 5 k blocks with two
+    # terms and 2 k blocks, the last one a quarter full: fewer k blocks than pairs, so some ranges hold one
+    # k block and the tiles stay whole when there are not enough)
+    host = ctx["host"]
+    big = host.Plan(ctx["stream"], host.gemm_plan_scratch_bytes())
+    try:
+        _check_gemm(ctx, rows=2560, cols=cols, tokens=2048, terms=terms, seed=21, plan=big)
+        # the flags are back at zero: a second launch on the same plan gives the same result
+        _check_gemm(ctx, rows=2560, cols=cols, tokens=2048, terms=terms, seed=21, plan=big)
+    finally:
+        big.close()
 
 
 def test_gemm_residual_terms(ctx):
