@@ -162,6 +162,7 @@ struct GemmParams {
     // (null: whole tiles only). Partial accumulators pass through `split_slots`, announced by `split_flags`.
     float* split_slots;            // [pair][CTA of the pair][epilogue warp][128 columns / 4][lane] x float4
     uint32_t* split_flags;         // [pair][CTA of the pair][epilogue warp], zero between launches
+    uint32_t split_sharers;        // pairs that share the leftover tiles (0: whole tiles only)
 };
 
 // ---- activation quantiser ------------------------------------------------------------------
@@ -497,6 +498,8 @@ constexpr uint32_t kPairOutBytes = kPairEpilogueWarps * 32 * kPairOutRowBytes;  
 constexpr uint32_t kPairSmemBytes = kPairStages * kPairStageBytes + kPairOutBytes + 1024 + 256;
 constexpr uint32_t kPairCopyWarp = 2 + kPairEpilogueWarps;
 constexpr uint32_t kPairThreads = 32 * (kPairCopyWarp + 1);   // TMA warp, MMA warp, epilogue warps, scale-copy warp
+constexpr uint32_t kSplitWorthSteps = 16;       // pipeline steps a pair issues in the time a hand-over costs
+constexpr uint32_t kSplitWays = 8;              // a leftover tile is cut into this many parts at most
 constexpr uint32_t kSplitWaitLimit = 1u << 20;  // polls of a handed-over part's flag (each a round trip to L2) before giving up
 constexpr uint64_t kSplitSlotBytes = 2ull * kPairEpilogueWarps * 32 * 128 * 4;   // one pair's accumulator: 256 x 256 f32
 constexpr uint32_t kLeaderMask = 0xFEFFFFFFu;   // clears the CTA-rank bit of a shared::cluster address within a pair
@@ -566,24 +569,27 @@ struct PairWork {
         return PairItem{pair + (index - parts) * pairs, 0, k_blocks, 0, 0};
     }
 };
-__device__ __forceinline__ PairWork pair_work(uint32_t pair, uint32_t pairs, uint32_t tiles, uint32_t k_blocks, bool split) {
+// `sharers` (0: whole tiles only): the first `sharers` pairs share the leftover tiles (at most kSplitWays per tile).
+__device__ __forceinline__ PairWork pair_work(uint32_t pair, uint32_t pairs, uint32_t tiles, uint32_t k_blocks, uint32_t sharers) {
     PairWork w{};
-    if (!split) {
+    if (!sharers) {
         w.whole = tiles > pair ? (tiles - pair + pairs - 1) / pairs : 0;
         w.items = w.whole;
         return w;
     }
     w.whole = tiles / pairs;
+    w.items = w.whole;
+    if (pair >= sharers) return w;
     const uint32_t first_left = w.whole * pairs;
     const uint64_t units = static_cast<uint64_t>(tiles - first_left) * k_blocks;   // k blocks of the leftover tiles
-    const uint64_t x0 = pair * units / pairs, x1 = (pair + 1) * units / pairs;      // this pair's range (not empty: units >= pairs)
+    const uint64_t x0 = pair * units / sharers, x1 = (pair + 1) * units / sharers;  // this pair's range (not empty: units >= sharers)
     const uint32_t a = static_cast<uint32_t>(x0 / k_blocks), b = static_cast<uint32_t>((x1 - 1) / k_blocks);
     const uint64_t a_begin = static_cast<uint64_t>(a) * k_blocks, a_end = a_begin + k_blocks;
     if (x1 >= a_end) {
         // the range holds the tail of tile a: every pair from the one that owns the tile's first k block hands over
         w.finishes = true;
         w.finishing = PairItem{first_left + a, static_cast<uint32_t>(x0 - a_begin), k_blocks, 2,
-                               static_cast<uint32_t>(((a_begin + 1) * pairs - 1) / units)};
+                               static_cast<uint32_t>(((a_begin + 1) * sharers - 1) / units)};
         if (w.finishing.first_giver == pair) w.finishing.kind = 0;   // the whole tile
     } else {
         w.gives = true;
@@ -649,7 +655,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
     const uint32_t k_blocks = (p.cols + kBlockK - 1) / kBlockK;
     const uint32_t atoms_per_row_block = p.cols / 64;
     const uint32_t act_term_atoms = p.padded_tokens / 128 * atoms_per_row_block;   // scale atoms of one activation term
-    const PairWork work = pair_work(pair, pairs, total_tiles, k_blocks, p.split_slots != nullptr);
+    const PairWork work = pair_work(pair, pairs, total_tiles, k_blocks, p.split_sharers);
 
     if (warp == 0 && lane == 0) {
         // ---------------- TMA producer (both CTAs) ----------------
@@ -1291,14 +1297,23 @@ augur_cuda_result_v1 launch_gemm(augur_cuda_stream_t s, const augur_cuda_nvfp4_s
             return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE);
         }
         const uint32_t tiles = (padded / (2 * kTileM)) * (a->rows / kTileN);
-        uint32_t pairs = tiles;
-        if (pairs > plan->sm_count / 2) pairs = plan->sm_count / 2;
-        // Tiles past the last full round of the pairs are cut along k between all pairs when the plan's scratch
-        // has room for the partial accumulators handed over (one slot per pair behind the counter regions, whose
-        // first words serve as the flags) and the leftover tiles hold at least one k block per pair.
+        const uint32_t all_pairs = plan->sm_count / 2;
+        uint32_t pairs = tiles < all_pairs ? tiles : all_pairs;
+        // Tiles past the last full round of the pairs (all tiles, when there are fewer tiles than pairs) are cut
+        // along k between all pairs when the plan's scratch has room for the partial accumulators handed over
+        // (one slot per pair behind the counter regions, whose first words serve as the flags) and those tiles
+        // hold at least one k block per pair.
         const uint32_t k_blocks = (a->cols + kBlockK - 1) / kBlockK;
-        if (split_tiles_enabled() && tiles % pairs != 0 && static_cast<uint64_t>(tiles % pairs) * k_blocks >= pairs &&
-            plan->scratch_bytes >= kCounterBytes + pairs * kSplitSlotBytes) {
+        const uint32_t left = tiles % all_pairs;
+        uint32_t sharers = left * kSplitWays < all_pairs ? left * kSplitWays : all_pairs;   // a tile is cut in kSplitWays parts at most
+        if (sharers > static_cast<uint64_t>(left) * k_blocks) sharers = left * k_blocks;      // and every part holds a k block
+        // Handing parts over costs about as much as 16 pipeline steps (k block x term) of a pair: the cut is made
+        // when the pairs would otherwise idle for longer than that, on average, in the last round.
+        const uint64_t idle_steps = static_cast<uint64_t>(all_pairs - left) * k_blocks * a->activation_terms;
+        if (split_tiles_enabled() && left != 0 && sharers > left && idle_steps >= static_cast<uint64_t>(kSplitWorthSteps) * all_pairs &&
+            plan->scratch_bytes >= kCounterBytes + sharers * kSplitSlotBytes) {
+            if (pairs < sharers) pairs = sharers;
+            p.split_sharers = sharers;
             p.split_flags = reinterpret_cast<uint32_t*>(plan->scratch);
             p.split_slots = reinterpret_cast<float*>(plan->scratch + kCounterBytes);
         }

@@ -132,37 +132,54 @@ def test_every_block_once_and_counters_match(rows, cols, pair, sms):
 
 
 # ---- pair-tile GEMM: leftover tiles cut along k (csrc/nvfp4_gemm.cu, pair_work) -----------------------------
-def pair_work(pair, pairs, tiles, k_blocks):
+SPLIT_WAYS = 8
+
+
+def pair_geometry(tiles, sm_pairs, k_blocks):
+    """(pairs launched, pairs that share the leftover tiles) as the host side picks them; sharers 0: whole tiles only."""
+    pairs = min(tiles, sm_pairs)
+    left = tiles % sm_pairs
+    sharers = min(left * SPLIT_WAYS, sm_pairs, left * k_blocks)
+    if left == 0 or sharers <= left:
+        return pairs, 0
+    return max(pairs, sharers), sharers
+
+
+def pair_work(pair, pairs, tiles, k_blocks, sharers):
     """The items of one CTA pair in the order the kernel does them: (tile, kb0, kb1, kind, first_giver)."""
+    if not sharers:
+        return [(tile, 0, k_blocks, 0, 0) for tile in range(pair, tiles, pairs)]
     whole = tiles // pairs
+    items = [(pair + i * pairs, 0, k_blocks, 0, 0) for i in range(whole)]
+    if pair >= sharers:
+        return items
     first_left = whole * pairs
     units = (tiles - first_left) * k_blocks
-    x0, x1 = pair * units // pairs, (pair + 1) * units // pairs
+    x0, x1 = pair * units // sharers, (pair + 1) * units // sharers
+    assert x1 > x0
     a, b = x0 // k_blocks, (x1 - 1) // k_blocks
     a_begin, a_end = a * k_blocks, (a + 1) * k_blocks
     given = finishing = None
     if x1 >= a_end:
-        first_giver = ((a_begin + 1) * pairs - 1) // units
+        first_giver = ((a_begin + 1) * sharers - 1) // units
         finishing = (first_left + a, x0 - a_begin, k_blocks, 0 if first_giver == pair else 2, first_giver)
     else:
         given = (first_left + a, x0 - a_begin, x1 - a_begin, 1, 0)
     if b > a:
         assert given is None
         given = (first_left + b, 0, x1 - b * k_blocks, 1, 0)
-    return ([given] if given else []) + ([finishing] if finishing else []) + [(pair + i * pairs, 0, k_blocks, 0, 0) for i in range(whole)]
+    return ([given] if given else []) + ([finishing] if finishing else []) + items
 
 
-@pytest.mark.parametrize("tiles,pairs,k_blocks", [(320, 74, 68), (80, 74, 13), (80, 74, 20), (272, 74, 20), (1088, 74, 20),
-                                                  (75, 74, 74), (147, 74, 2), (5, 2, 7), (9, 4, 5), (320, 66, 34)])
-def test_pair_tile_leftover_split(tiles, pairs, k_blocks):
-    left = tiles % pairs
-    assert left and left * k_blocks >= pairs        # the condition under which the host enables the split
-    done = {}
-    givers = {}
-    finisher = {}
-    load = []
+@pytest.mark.parametrize("tiles,sm_pairs,k_blocks", [(320, 74, 68), (80, 74, 13), (80, 74, 20), (272, 74, 20), (1088, 74, 20),
+                                                     (75, 74, 74), (147, 74, 2), (5, 2, 7), (9, 4, 5), (320, 66, 34), (20, 74, 68),
+                                                     (1, 74, 80), (73, 74, 2), (2, 74, 20), (80, 74, 1), (148, 74, 20), (3, 74, 3)])
+def test_pair_tile_leftover_split(tiles, sm_pairs, k_blocks):
+    pairs, sharers = pair_geometry(tiles, sm_pairs, k_blocks)
+    assert pairs <= sm_pairs
+    done, givers, finisher, load = {}, {}, {}, []
     for pair in range(pairs):
-        items = pair_work(pair, pairs, tiles, k_blocks)
+        items = pair_work(pair, pairs, tiles, k_blocks, sharers)
         kinds = [item[3] for item in items]
         assert kinds.count(1) <= 1 and kinds.count(2) <= 1
         assert all(k != 1 for k in kinds[1:]) and all(k != 2 for k in kinds[2:])    # handed-over first, finishing next
@@ -178,15 +195,16 @@ def test_pair_tile_leftover_split(tiles, pairs, k_blocks):
                 givers.setdefault(tile, []).append(pair)
             elif kind == 2:
                 finisher[tile] = (pair, first_giver)
-            elif kb0 == 0 and kb1 == k_blocks:
-                pass
             else:
-                raise AssertionError("a partial item must hand over or finish")
+                assert kb0 == 0 and kb1 == k_blocks, "a partial item must hand over or finish"
         load.append(blocks)
     assert len(done) == tiles * k_blocks
-    assert max(load) - min(load) <= 1                # every pair issues the same number of k blocks
+    if sharers:
+        assert max(load[:sharers]) - min(load[:sharers]) <= 1     # the sharers issue the same number of k blocks
+        assert sharers == pairs or max(load[sharers:]) <= min(load[:sharers])
     for tile, who in givers.items():
         pair, first_giver = finisher[tile]
         assert who == list(range(first_giver, pair))  # exactly the pairs the finisher waits for, in order
+        assert len(who) < SPLIT_WAYS + 1
     for tile, (pair, first_giver) in finisher.items():
         assert first_giver < pair and tile in givers

@@ -172,18 +172,28 @@ def test_gemm_pair_tiles_terms_share_weight_scales_across_tiles(ctx):
     _check_gemm(ctx, rows=2560, cols=768, tokens=2048, terms=2, seed=14)
 
 
-@pytest.mark.parametrize("cols,terms", [(3328, 1), (1280, 2), (320, 1)])
+@pytest.mark.parametrize("cols,terms", [(4864, 1), (2560, 2), (320, 1)])
 def test_gemm_pair_tiles_leftover_round_cut_along_k(ctx, cols, terms):
     # 80 pair tiles for at most 74 pairs: with a plan that has room for the handed-over accumulators the 6 tiles
-    # of the last round are cut along k between all pairs (13 k blocks: about one per pair; 5 k blocks with two
-    # terms and 2 k blocks, the last one a quarter full: fewer k blocks than pairs, so some ranges hold one
-    # k block and the tiles stay whole when there are not enough)
+    # of the last round are cut along k between the pairs (19 k blocks, 8 parts per tile; 10 k blocks with two
+    # terms); with 2 k blocks the idle time saved is not worth a hand-over and the tiles stay whole
     host = ctx["host"]
     big = host.Plan(ctx["stream"], host.gemm_plan_scratch_bytes())
     try:
         _check_gemm(ctx, rows=2560, cols=cols, tokens=2048, terms=terms, seed=21, plan=big)
         # the flags are back at zero: a second launch on the same plan gives the same result
         _check_gemm(ctx, rows=2560, cols=cols, tokens=2048, terms=terms, seed=21, plan=big)
+    finally:
+        big.close()
+
+
+def test_gemm_fewer_pair_tiles_than_pairs_all_cut_along_k(ctx):
+    # 2 pair tiles of 20 k blocks: with room in the plan every tile is cut between the pairs of the whole device
+    host = ctx["host"]
+    big = host.Plan(ctx["stream"], host.gemm_plan_scratch_bytes())
+    try:
+        _check_gemm(ctx, rows=512, cols=5120, tokens=256, seed=22, plan=big)
+        _check_gemm(ctx, rows=256, cols=17408, tokens=200, terms=2, seed=23, plan=big)   # one tile, 68 k blocks, ragged tokens
     finally:
         big.close()
 
