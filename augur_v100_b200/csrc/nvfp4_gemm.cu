@@ -217,9 +217,8 @@ __device__ __forceinline__ uint32_t e2m1_nearest(float v, float* level) {
 // range and d is not of the all-ones mantissa form; the kernel checks that once per group (`kFast`) and
 // otherwise divides. An x below 2^-65 (d is at least 2^-63 here) has a quotient under a quarter, i.e. code 0
 // whatever the last bits are, and is not sent through the steps, which could leave the normal range.
-template <bool kFast>
-__device__ __forceinline__ void quantise_group(float (&residual)[16], float divisor, float reciprocal, bool more_terms,
-                                               uint32_t (&packed)[2]) {
+template <bool kFast, bool kMoreTerms>
+__device__ __forceinline__ void quantise_group(float (&residual)[16], float divisor, float reciprocal, uint32_t (&packed)[2]) {
 #pragma unroll
     for (uint32_t i = 0; i < 16; ++i) {
         const float x = residual[i];
@@ -238,14 +237,16 @@ __device__ __forceinline__ void quantise_group(float (&residual)[16], float divi
         float level;
         const uint32_t code = e2m1_nearest(normalized, &level);
         packed[i >> 3] |= code << (4 * (i & 7));
-        if (more_terms) residual[i] = __fsub_rn(x, __fmul_rn(level, divisor));
+        if (kMoreTerms) residual[i] = __fsub_rn(x, __fmul_rn(level, divisor));
     }
 }
 
 // One residual term of one 16-element group: the block scale (smallest E4M3 value >= amax / (6 g)), the 16 codes
 // (nearest level of x / (scale * g), ties toward zero) and, if another term follows, the residual it quantises.
-__device__ __forceinline__ void quantise_term(float (&residual)[16], float global_scale, bool more_terms, uint32_t (&packed)[2],
-                                              uint32_t* scale_code_out) {
+// `kMoreTerms` is a compile-time choice: the last term of a group needs neither the levels nor the residual.
+template <bool kMoreTerms>
+__device__ __forceinline__ void quantise_term_as(float (&residual)[16], float global_scale, uint32_t (&packed)[2],
+                                                 uint32_t* scale_code_out) {
     float maximum = 0.0f;
 #pragma unroll
     for (uint32_t i = 0; i < 16; ++i) maximum = fmaxf(maximum, fabsf(residual[i]));
@@ -262,11 +263,19 @@ __device__ __forceinline__ void quantise_term(float (&residual)[16], float globa
                       largest_field <= 190u;
     packed[0] = packed[1] = 0;
     if (fast) {
-        quantise_group<true>(residual, divisor, __frcp_rn(divisor), more_terms, packed);
+        quantise_group<true, kMoreTerms>(residual, divisor, __frcp_rn(divisor), packed);
     } else {
-        quantise_group<false>(residual, divisor, 0.0f, more_terms, packed);
+        quantise_group<false, kMoreTerms>(residual, divisor, 0.0f, packed);
     }
     *scale_code_out = scale_code;
+}
+__device__ __forceinline__ void quantise_term(float (&residual)[16], float global_scale, bool more_terms, uint32_t (&packed)[2],
+                                              uint32_t* scale_code_out) {
+    if (more_terms) {
+        quantise_term_as<true>(residual, global_scale, packed, scale_code_out);
+    } else {
+        quantise_term_as<false>(residual, global_scale, packed, scale_code_out);
+    }
 }
 
 // 32 accumulator columns of one token row -> packed BF16. Plain: 32 outputs. SwiGLU: the weight rows
