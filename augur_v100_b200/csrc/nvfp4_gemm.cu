@@ -656,7 +656,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const uint32_t m_pairs = p.padded_tokens / (2 * kTileM);
+    // An odd number of 128-row token tiles leaves the second CTA of the last pair without rows of its own: it
+    // loads whatever follows (the next term's rows, or the fill value past the tensor) and stores nothing.
+    const uint32_t m_pairs = (p.padded_tokens + 2 * kTileM - 1) / (2 * kTileM);
     const uint32_t n_tiles = p.rows / kTileN;
     const uint32_t total_tiles = m_pairs * n_tiles;
     // A last k block that is only partly inside the tensor is loaded like the others (the TMA fills what lies past
@@ -1296,7 +1298,7 @@ augur_cuda_result_v1 launch_gemm(augur_cuda_stream_t s, const augur_cuda_nvfp4_s
     p.quant_out = reinterpret_cast<uint8_t*>(quant.destination);
     p.quant_terms = quant.terms;
     p.quant_global_scale = quant.global_scale;
-    if ((quant.destination || pair_tiles_enabled()) && padded % (2 * kTileM) == 0 && a->rows % kTileN == 0 && plan->sm_count >= 2) {
+    if ((quant.destination || pair_tiles_enabled()) && a->rows % kTileN == 0 && plan->sm_count >= 2) {
         // 256 x 256 tiles on pairs of CTAs (clusters of two); the grid is a whole number of pairs.
         CUtensorMap map_act_sf, map_weight_sf;
         const uint64_t atoms_per_row_block = a->cols / 64;
@@ -1305,7 +1307,7 @@ augur_cuda_result_v1 launch_gemm(augur_cuda_stream_t s, const augur_cuda_nvfp4_s
                             static_cast<uint64_t>(a->activation_terms) * (padded / 128) * atoms_per_row_block)) {
             return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE);
         }
-        const uint32_t tiles = (padded / (2 * kTileM)) * (a->rows / kTileN);
+        const uint32_t tiles = ((padded + 2 * kTileM - 1) / (2 * kTileM)) * (a->rows / kTileN);
         const uint32_t all_pairs = plan->sm_count / 2;
         uint32_t pairs = tiles < all_pairs ? tiles : all_pairs;
         // Tiles past the last full round of the pairs (all tiles, when there are fewer tiles than pairs) are cut
@@ -1424,7 +1426,7 @@ bool check_swiglu_quant(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4
     }
     if (a->reserved || !a->rows || a->rows % 128 != 0 || a->rows > (1u << 30) || !scale_ok(a->up_global_scale) ||
         a->destination_terms < 1 || a->destination_terms > 3 || !std::isfinite(a->destination_global_scale) ||
-        a->destination_global_scale <= 0.0f || !a->tokens || padded_tokens(a->tokens) % (2 * kTileM) != 0 || !plan ||
+        a->destination_global_scale <= 0.0f || !a->tokens || !plan ||
         plan->sm_count < 2) {
         return false;
     }

@@ -474,8 +474,7 @@ class Nvfp4Sm100PrefillFfnProgram:
         d.weight_global_scale, d.activation_global_scale = down.global_scale, intermediate_global_scale
         self.gate_up_args, self.down_args = g, d
         # On the two-CTA tiles the gate|up GEMM can quantise its result for the down GEMM in its own epilogue.
-        padded = (tokens + 127) // 128 * 128
-        self.fused = fuse_quantiser and padded % 256 == 0 and inter % 128 == 0
+        self.fused = fuse_quantiser and inter % 128 == 0
         if self.fused:
             f = abi.header(abi.GemmSwigluQuantArgs)
             f.weight, f.weight_len_bytes = g.weight, g.weight_len_bytes

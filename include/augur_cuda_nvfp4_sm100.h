@@ -477,8 +477,8 @@ augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemm_swiglu_bf16_pre
  * exactly what act_quant would write for the BF16 intermediate (same rule, same layout,
  * `destination_terms` residual terms, `destination_global_scale`), while the next tile's MMAs run.
  * `output_bf16` may be 0 (with output_len_bytes 0): the BF16 intermediate is then never written.
- * Runs on the two-CTA tiles only: ceil128(tokens) must be a multiple of 256 and rows a multiple of
- * 128; other shapes get INVALID_ARGUMENT and use gemm_swiglu_bf16 followed by act_quant. */
+ * Runs on the two-CTA tiles only: rows must be a multiple of 128 (any token count); other shapes get
+ * INVALID_ARGUMENT and use gemm_swiglu_bf16 followed by act_quant. */
 typedef struct augur_cuda_nvfp4_sm100_gemm_swiglu_quant_args_v1 {
     uint32_t abi_version;
     uint32_t struct_size;

@@ -486,8 +486,7 @@ public:
         p->down_args_.activation_global_scale = intermediate_global_scale;
         // On the two-CTA tiles the gate|up GEMM quantises its result for the down GEMM in its own epilogue
         // (three launches instead of four; the BF16 intermediate is still written here).
-        const uint32_t padded = (tokens + 127) / 128 * 128;
-        p->fused_ = padded % 256 == 0 && inter % 128 == 0;
+        p->fused_ = inter % 128 == 0;
         check("act_quant_preflight", augur_cuda_nvfp4_sm100_act_quant_preflight_v1(d, s.handle(), &p->quant_x_));
         if (p->fused_) {
             p->fused_args_ = header<augur_cuda_nvfp4_sm100_gemm_swiglu_quant_args_v1>();

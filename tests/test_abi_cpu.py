@@ -236,6 +236,11 @@ def test_scratch_extents():
         host.gemv_scratch_bytes(17408, 5120, 9)       # more than the small-token limit
     with pytest.raises(host.CudaRuntimeError):
         host.gemv_scratch_bytes(17408, 5100, 8)
+    # prefill plans: the two counter regions, then one 256 x 256 f32 accumulator slot per CTA pair
+    assert host.gemm_plan_scratch_bytes(148) == 2 * 65536 + 74 * 256 * 256 * 4
+    assert host.gemm_plan_scratch_bytes(2) == 2 * 65536 + 256 * 256 * 4
+    with pytest.raises(host.CudaRuntimeError):
+        host.gemm_plan_scratch_bytes(5000)
 
 
 def test_synthetic_generator_is_deterministic_and_in_range():

@@ -267,7 +267,7 @@ def test_prefill_mlp_program_with_fused_swiglu(ctx, hidden, inter, tokens):
         ctx["plan"], gate_up_w, down_w, x, terms=3, keep_intermediate=True,
         input_global_scale=host.default_activation_global_scale(float(np.abs(synth.bf16_bits_to_f32(x_bits)).max())),
         intermediate_global_scale=host.default_activation_global_scale(float(np.abs(h64).max()) * 1.05))
-    assert program.fused == (tokens % 256 == 0 or (tokens + 127) // 128 * 128 % 256 == 0)
+    assert program.fused   # any token count: an odd last 128-row tile leaves one CTA of a pair without rows
     before = host.allocation_snapshot()
     for _ in range(2):
         program.submit_for_plan()
