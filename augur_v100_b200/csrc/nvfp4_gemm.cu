@@ -539,7 +539,15 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void tc_copy_sf_pair(uint32_t tmem, uint64_t desc) {
+#if defined(AUGUR_GEMM_PROBE_CP_SHAPE) && AUGUR_GEMM_PROBE_CP_SHAPE == 1
+    // timing probe (results not valid): same number of copies, 128 bytes each
+    asm volatile("tcgen05.cp.cta_group::2.4x256b [%0], %1;" ::"r"(tmem), "l"(desc) : "memory");
+#elif defined(AUGUR_GEMM_PROBE_CP_SHAPE) && AUGUR_GEMM_PROBE_CP_SHAPE == 2
+    // timing probe (results not valid): same number of copies, 4 KB each
+    asm volatile("tcgen05.cp.cta_group::2.128x256b [%0], %1;" ::"r"(tmem), "l"(desc) : "memory");
+#else
     asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem), "l"(desc) : "memory");
+#endif
 }
 __device__ __forceinline__ void tc_mma_pair(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t sfa, uint32_t sfb,
                                             uint32_t accumulate) {
@@ -827,7 +835,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
                             if (step >= 2) break;
 #endif
                             tc_copy_sf_pair(tmem_sfb + 8 * k, sfb_desc + k * kAtomStep);
+#ifndef AUGUR_GEMM_PROBE_HALF_SFB_COPIES
                             tc_copy_sf_pair(tmem_sfb + 8 * k + 4, sfb_desc + kRowBlockStep + k * kAtomStep);
+#endif
                         }
                     }
                 } else {
