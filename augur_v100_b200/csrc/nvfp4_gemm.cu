@@ -198,16 +198,18 @@ __device__ __forceinline__ float e4m3_positive_value(uint32_t code) {
 // From 1 upward E2M1 is a float with one mantissa bit, so rounding the f32 pattern to that bit with
 // "ties down" (add half an ulp minus one, truncate) gives exponent and mantissa at once:
 // 1 -> code 2, 1.5 -> 3, 2 -> 4, 3 -> 5, 4 -> 6, 6 -> 7. Below 1 the levels are 0, 0.5 and 1.
+// `v` is the quotient as computed; the clamp to [-6, 6] is folded in: the magnitude is cut at 6, and a NaN
+// quotient, which fmin(fmax(v, -6), 6) sends to -6, is negative here as well.
 __device__ __forceinline__ uint32_t e2m1_nearest(float v, float* level) {
-    const float a = fabsf(v);
+    const float a = fminf(fabsf(v), 6.0f);
     uint32_t m;
     if (a < 1.0f) {
         m = (a > 0.25f ? 1u : 0u) + (a > 0.75f ? 1u : 0u);
     } else {
-        m = ((__float_as_uint(a) + 0x1fffffu) >> 22) - 252u;
+        m = (__float_as_uint(a) + (0x1fffffu - (252u << 22))) >> 22;   // round to one mantissa bit, ties toward zero
     }
     const float l = m < 2 ? 0.5f * static_cast<float>(m) : __uint_as_float((m + 252u) << 22);
-    const bool negative = v < 0.0f && m != 0;
+    const bool negative = !(v >= 0.0f) && m != 0;
     *level = negative ? -l : l;
     return negative ? (m | 8u) : m;
 }
@@ -233,10 +235,9 @@ __device__ __forceinline__ void quantise_group(float (&residual)[16], float divi
         } else {
             normalized = divisor == 0.0f ? 0.0f : __fdiv_rn(x, divisor);
         }
-        normalized = fminf(fmaxf(normalized, -6.0f), 6.0f);
         float level;
         const uint32_t code = e2m1_nearest(normalized, &level);
-        packed[i >> 3] |= code << (4 * (i & 7));
+        packed[i >> 3] += code << (4 * (i & 7));   // disjoint fields: a sum, so that shift and add fuse
         if (kMoreTerms) residual[i] = __fsub_rn(x, __fmul_rn(level, divisor));
     }
 }
