@@ -170,6 +170,7 @@ EXPORTS = {
     "augur_cuda_nvfp4_sm100_gemv_bf16_preflight_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(GemvArgs)]),
     "augur_cuda_nvfp4_sm100_gemv_bf16_prevalidated_submit_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(GemvArgs)]),
     "augur_cuda_nvfp4_sm100_gemv_bf16_static_scratch_submit_v1": (Result, [c_int32, c_void_p, POINTER(GemvArgs)]),
+    "augur_cuda_nvfp4_sm100_static_scratch_status_v1": (Result, [c_int32, c_void_p, POINTER(c_uint32)]),
     "augur_cuda_nvfp4_sm100_mlp_preflight_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(MlpArgs)]),
     "augur_cuda_nvfp4_sm100_mlp_prevalidated_submit_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(MlpArgs)]),
     "augur_cuda_nvfp4_sm100_norm_group_preflight_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(NormGroupArgs)]),

@@ -17,7 +17,6 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
-#include <cstdlib>
 
 #include "nvfp4_internal.h"
 #include "nvfp4_layout.cuh"
@@ -488,10 +487,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant__
 //   scales_landed[s] leader's only: the stage's block-scale atoms of both CTAs have landed (loaded before
 //             the operand tiles);   scales_ready[s] leader's only: the copy thread has issued the stage's
 //             shared -> tensor memory scale copies.
-#ifndef AUGUR_GEMM_PAIR_STAGES
-#define AUGUR_GEMM_PAIR_STAGES 5
-#endif
-constexpr uint32_t kPairStages = AUGUR_GEMM_PAIR_STAGES;
+constexpr uint32_t kPairStages = 5;
 // Tensor memory of the pair kernel: 256 accumulator columns, then one set of token-row scale columns per stage
 // (16 each) and one set of weight-row scale columns per k-block slot (32 each).
 constexpr uint32_t kTmemPairSfA = 256;
@@ -535,20 +531,8 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
                  ::"r"(bar), "h"(static_cast<uint16_t>(3))
                  : "memory");
 }
-// Arrives on this CTA's barrier only, once the cta_group::2 operations this thread issued so far are done.
-[[maybe_unused]] __device__ __forceinline__ void tc_commit_pair_local(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
 __device__ __forceinline__ void tc_copy_sf_pair(uint32_t tmem, uint64_t desc) {
-#if defined(AUGUR_GEMM_PROBE_CP_SHAPE) && AUGUR_GEMM_PROBE_CP_SHAPE == 1
-    // timing probe (results not valid): same number of copies, 128 bytes each
-    asm volatile("tcgen05.cp.cta_group::2.4x256b [%0], %1;" ::"r"(tmem), "l"(desc) : "memory");
-#elif defined(AUGUR_GEMM_PROBE_CP_SHAPE) && AUGUR_GEMM_PROBE_CP_SHAPE == 2
-    // timing probe (results not valid): same number of copies, 4 KB each
-    asm volatile("tcgen05.cp.cta_group::2.128x256b [%0], %1;" ::"r"(tmem), "l"(desc) : "memory");
-#else
     asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem), "l"(desc) : "memory");
-#endif
 }
 __device__ __forceinline__ void tc_mma_pair(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t sfa, uint32_t sfb,
                                             uint32_t accumulate) {
@@ -681,9 +665,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
         // ---------------- TMA producer (both CTAs) ----------------
         uint32_t stage = 0, phase = 0;
         bool alive = true;
-#ifdef AUGUR_GEMM_PROBE_MMA_ONLY
-        alive = false;
-#endif
         for (uint32_t index = 0; alive && index < work.items; ++index) {
             const PairItem item = work.item(index, pair, pairs, k_blocks);
             const uint32_t m_pair = item.tile % m_pairs, n_tile = item.tile / m_pairs;
@@ -700,7 +681,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
                 // thread has them in tensor memory by the time the operand tiles arrive.
                 const uint32_t landed = bar_scales_landed + 8 * stage;
                 const uint32_t token_row = m_pair * 2 * kTileM + rank * kTileM;
-#ifndef AUGUR_GEMM_PROBE_NO_SF_TMA
                 if (rank == 0) mbar_expect_tx(landed, 2 * (kBytesSfA + kBytesSfB));
                 tma_load_2d_pair(base + kBytesA + kPairBytesB, &map_act_sf, 0,
                                  term * act_term_atoms + (token_row / 128) * atoms_per_row_block + kb * 4, landed);
@@ -708,9 +688,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
                                  (n_tile * 2) * atoms_per_row_block + kb * 4, landed);
                 tma_load_2d_pair(base + kBytesA + kPairBytesB + 2 * kBytesSfA, &map_weight_sf, 0,
                                  (n_tile * 2 + 1) * atoms_per_row_block + kb * 4, landed);
-#else
-                if (rank == 0) mbar_arrive(landed);
-#endif
                 if (rank == 0) mbar_expect_tx(full, 2 * (kBytesA + kPairBytesB));
                 tma_load_2d_pair(base, &map_act, kb * 128, term * p.padded_tokens + token_row, full);
                 tma_load_2d_pair(base + kBytesA, &map_weight, kb * 128, n_tile * kTileN + rank * 128, full);
@@ -735,26 +712,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
             const PairItem item = work.item(index, pair, pairs, k_blocks);
             const uint32_t item_steps = (item.kb1 - item.kb0) * p.terms;
             // the epilogues of both CTAs must have drained the previous tile's accumulator
-#ifndef AUGUR_GEMM_PROBE_NO_DRAIN_WAIT
             if (!mbar_wait(bar_tmem_empty, tmem_phase ^ 1, abort_flag, p.status_word, kErrMmaWaitTmem)) break;
-#endif
             tc_fence_after();
             uint32_t accumulate = 0, term = 0, kb = item.kb0;
             for (uint32_t step = 0; step < item_steps; ++step) {
                 // operands in shared memory (TMA) and block scales in tensor memory (copy thread)
-#if defined(AUGUR_GEMM_PROBE_MMA_ONLY) || defined(AUGUR_GEMM_PROBE_NO_FULL_WAIT)
-#elif defined(AUGUR_GEMM_PROBE_NO_SCALES_WAIT)
-                if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status_word, kErrMmaWaitFull)) {
-                    alive = false;
-                    break;
-                }
-#else
                 if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status_word, kErrMmaWaitFull) ||
                     !mbar_wait(bar_scales_ready + 8 * stage, phase, abort_flag, p.status_word, kErrMmaWaitScales)) {
                     alive = false;
                     break;
                 }
-#endif
                 tc_fence_after();
                 const uint64_t a_desc = a_desc0 + stage * kStageStep, b_desc = b_desc0 + stage * kStageStep;
                 // the token rows' scales change with every step (term), the weight rows' scales only with the k block
@@ -765,9 +732,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
                 if (k_steps == 4) {
 #pragma unroll
                     for (uint32_t k = 0; k < 4; ++k) {
-#ifdef AUGUR_GEMM_PROBE_TMA_ONLY
-                        break;
-#endif
                         tc_mma_pair(tmem_base + kTmemAcc, a_desc + 2 * k, b_desc + 2 * k, idesc, tmem_sfa + 4 * k, tmem_sfb + 8 * k,
                                     accumulate | k);
                     }
@@ -797,9 +761,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
         constexpr uint64_t kStageStep = kPairStageBytes >> 4, kAtomStep = kSfAtomBytes >> 4, kRowBlockStep = kBytesSfA >> 4;
         const uint32_t last_k_steps = (p.cols - (k_blocks - 1) * kBlockK) / 64;
         bool alive = true;
-#if defined(AUGUR_GEMM_PROBE_MMA_ONLY) || defined(AUGUR_GEMM_PROBE_NO_SCALES_WAIT)
-        alive = false;
-#endif
         for (uint32_t index = 0; alive && index < work.items; ++index) {
             const PairItem item = work.item(index, pair, pairs, k_blocks);
             const uint32_t item_steps = (item.kb1 - item.kb0) * p.terms;
@@ -824,21 +785,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
                 if (k_steps == 4) {
 #pragma unroll
                     for (uint32_t k = 0; k < 4; ++k) {
-#ifdef AUGUR_GEMM_PROBE_NO_SF_COPY
-                        if (step >= 2) break;
-#endif
                         tc_copy_sf_pair(tmem_sfa + 4 * k, sfa_desc + k * kAtomStep);
                     }
                     if (term == 0) {
 #pragma unroll
                         for (uint32_t k = 0; k < 4; ++k) {
-#ifdef AUGUR_GEMM_PROBE_NO_SF_COPY
-                            if (step >= 2) break;
-#endif
                             tc_copy_sf_pair(tmem_sfb + 8 * k, sfb_desc + k * kAtomStep);
-#ifndef AUGUR_GEMM_PROBE_HALF_SFB_COPIES
                             tc_copy_sf_pair(tmem_sfb + 8 * k + 4, sfb_desc + kRowBlockStep + k * kAtomStep);
-#endif
                         }
                     }
                 } else {
@@ -850,14 +803,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
                         }
                     }
                 }
-#ifdef AUGUR_GEMM_SCALES_COMPLETE
-                tc_commit_pair_local(bar_scales_ready + 8 * stage);   // arrives when the copies are complete
-#else
                 // The copies only have to be issued before the MMAs that read them: a copy and a later MMA
                 // execute in issue order, and the fences on either side of this arrival order the two threads' issues.
                 tc_fence_before();
                 mbar_arrive(bar_scales_ready + 8 * stage);
-#endif
                 if (++term == p.terms) {
                     term = 0;
                     ++kb;
@@ -940,6 +889,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
                     if (lane == 0) {
                         *abort_flag = 1;
                         atomicCAS(p.status_word, 0u, kErrSplitWait);
+                        // The launch has failed and says so; the flags of the parts it gave up on go back to zero all
+                        // the same, so that a late giver cannot leave one set for the next launch on this plan.
+                        for (uint32_t giver = item.first_giver; giver < pair; ++giver) {
+                            p.split_flags[(giver * 2 + rank) * kPairEpilogueWarps + (warp - 2)] = 0;
+                        }
                     }
                     break;
                 }
@@ -1131,24 +1085,6 @@ bool make_scale_map(CUtensorMap* map, uint64_t address, uint64_t atoms) {
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// AUGUR_NVFP4_SM100_GEMM_PAIR=0 keeps every shape on the one-CTA tiles (measurement aid).
-bool pair_tiles_enabled() {
-    static const bool enabled = [] {
-        const char* value = getenv("AUGUR_NVFP4_SM100_GEMM_PAIR");
-        return !(value && value[0] == '0');
-    }();
-    return enabled;
-}
-
-// AUGUR_NVFP4_SM100_GEMM_SPLIT=0 keeps leftover tiles whole (measurement aid).
-bool split_tiles_enabled() {
-    static const bool enabled = [] {
-        const char* value = getenv("AUGUR_NVFP4_SM100_GEMM_SPLIT");
-        return !(value && value[0] == '0');
-    }();
-    return enabled;
-}
-
 // ---- validation ------------------------------------------------------------------------------------
 bool act_shape_ok(uint32_t tokens, uint32_t cols, uint32_t terms) {
     return tokens && cols && tokens <= (1u << 24) && cols % 64 == 0 && terms >= 1 && terms <= 3 &&
@@ -1216,6 +1152,29 @@ bool check_gemm(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_p
 }
 
 }  // namespace
+
+// How many two-CTA clusters of the pair kernel fit the current device at once. The leftover-tile split lets
+// a pair wait for parts that lower-numbered pairs produce, so every pair of the grid has to be resident:
+// the grid is capped with this number (it can be below SMs / 2 when cluster placement leaves SMs unused).
+uint32_t gemm_pair_resident_clusters() {
+    cudaLaunchConfig_t config{};
+    config.gridDim = dim3(2);
+    config.blockDim = dim3(kPairThreads);
+    config.dynamicSmemBytes = kPairSmemBytes;
+    cudaLaunchAttribute attribute{};
+    attribute.id = cudaLaunchAttributeClusterDimension;
+    attribute.val.clusterDim.x = 2;
+    attribute.val.clusterDim.y = 1;
+    attribute.val.clusterDim.z = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, gemm_pair_kernel, &config) != cudaSuccess || clusters < 1) {
+        cudaGetLastError();
+        return 0;
+    }
+    return static_cast<uint32_t>(clusters);
+}
 
 cudaError_t gemm_configure_device() {
     const cudaError_t e = cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
@@ -1309,7 +1268,7 @@ augur_cuda_result_v1 launch_gemm(augur_cuda_stream_t s, const augur_cuda_nvfp4_s
     p.quant_out = reinterpret_cast<uint8_t*>(quant.destination);
     p.quant_terms = quant.terms;
     p.quant_global_scale = quant.global_scale;
-    if ((quant.destination || pair_tiles_enabled()) && a->rows % kTileN == 0 && plan->sm_count >= 2) {
+    if (a->rows % kTileN == 0 && plan->sm_count >= 2) {
         // 256 x 256 tiles on pairs of CTAs (clusters of two); the grid is a whole number of pairs.
         CUtensorMap map_act_sf, map_weight_sf;
         const uint64_t atoms_per_row_block = a->cols / 64;
@@ -1319,7 +1278,7 @@ augur_cuda_result_v1 launch_gemm(augur_cuda_stream_t s, const augur_cuda_nvfp4_s
             return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE);
         }
         const uint32_t tiles = ((padded + 2 * kTileM - 1) / (2 * kTileM)) * (a->rows / kTileN);
-        const uint32_t all_pairs = plan->sm_count / 2;
+        const uint32_t all_pairs = plan->pair_clusters;   // pairs that are resident together (at most SMs / 2)
         uint32_t pairs = tiles < all_pairs ? tiles : all_pairs;
         // Tiles past the last full round of the pairs (all tiles, when there are fewer tiles than pairs) are cut
         // along k between all pairs when the plan's scratch has room for the partial accumulators handed over
@@ -1332,7 +1291,7 @@ augur_cuda_result_v1 launch_gemm(augur_cuda_stream_t s, const augur_cuda_nvfp4_s
         // Handing parts over costs about as much as 16 pipeline steps (k block x term) of a pair: the cut is made
         // when the pairs would otherwise idle for longer than that, on average, in the last round.
         const uint64_t idle_steps = static_cast<uint64_t>(all_pairs - left) * k_blocks * a->activation_terms;
-        if (split_tiles_enabled() && left != 0 && sharers > left && idle_steps >= static_cast<uint64_t>(kSplitWorthSteps) * all_pairs &&
+        if (left != 0 && sharers > left && idle_steps >= static_cast<uint64_t>(kSplitWorthSteps) * all_pairs &&
             plan->scratch_bytes >= kCounterBytes + sharers * kSplitSlotBytes) {
             if (pairs < sharers) pairs = sharers;
             p.split_sharers = sharers;

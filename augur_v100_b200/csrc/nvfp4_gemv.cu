@@ -24,7 +24,6 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
-#include <cstdlib>
 #include <mutex>
 
 #include "nvfp4_internal.h"
@@ -51,9 +50,6 @@ struct GemvParams {
     float* partials;
     uint32_t* counters;
     uint32_t* status_word;
-#ifdef AUGUR_GEMV_TRACE
-    unsigned long long* trace;   // [CTA][4] nanosecond stamps: start, staged, streamed, done
-#endif
     const uint8_t* staged;     // activations already staged by the producing launch (fixed exponent), or unused
     float fixed_factor;        // non-zero: input is `staged`, and both rescale factors are this constant
     uint16_t* staged_out;      // SwiGLU epilogue: also write the result as staged fragments (or null)
@@ -62,7 +58,9 @@ struct GemvParams {
     float global_a, global_b;
     // Tensor-parallel exchange (tp_world == 0: none): every rank's exchange buffer as mapped here.
     uint64_t exchange[AUGUR_NVFP4_SM100_MAX_TP_RANKS];
-    uint32_t tp_world, tp_rank, tp_sequence;
+    uint32_t tp_world, tp_rank;
+    uint32_t tp_sequence;      // host-counted sequence, or 0: the launch takes it from `tp_counter`
+    uint32_t* tp_counter;      // {launches counted so far, CTAs of the running launch that are done}, in this rank's exchange buffer
 };
 
 struct GemvGeometry {
@@ -70,16 +68,6 @@ struct GemvGeometry {
     uint64_t partial_bytes;   // partial-sum slots
     uint64_t staged_bytes;    // staged activations + factors
 };
-
-// AUGUR_NVFP4_SM100_GEMV_SPLIT=block forces single-block span boundaries (measurement aid);
-// anything else keeps the automatic choice described in geometry().
-int split_mode() {
-    static const int mode = [] {
-        const char* value = getenv("AUGUR_NVFP4_SM100_GEMV_SPLIT");
-        return (value && value[0] == 'b') ? 1 : 0;
-    }();
-    return mode;
-}
 
 // Host-side geometry; `sm_count` CTAs at most.
 GemvGeometry geometry(uint32_t rows, uint32_t cols, bool pair, uint32_t sm_count) {
@@ -96,7 +84,7 @@ GemvGeometry geometry(uint32_t rows, uint32_t cols, bool pair, uint32_t sm_count
     // while the imbalance, in blocks per CTA, stays below what that combine costs (about 3 us, the time
     // a CTA streams kCombineBlocks blocks in).
     bool aligned = false;
-    if (g.slabs == 1 && split_mode() != 1) {
+    if (g.slabs == 1) {
         const uint64_t ctas = per_slab < g.groups ? per_slab : g.groups;
         const uint64_t most = (g.groups + ctas - 1) / ctas;                  // groups of the busiest CTA
         // imbalance = most - groups / sm_count groups, compared in blocks and scaled by sm_count to stay in integers
@@ -282,9 +270,19 @@ __device__ __forceinline__ uint32_t shift_bf16(uint32_t bits, int shift) {
 constexpr uint32_t kExchangeWaitLimit = 1u << 20;   // polls of about a microsecond: gives up after about a second
 constexpr uint32_t kExchangeTileBytes = kSlotFloats * 8;
 
-__host__ __device__ constexpr uint64_t exchange_extent(uint32_t world, uint32_t groups) {
+// The tiles of both parities, then 256 bytes that hold the device-side sequence counter of this rank.
+__host__ __device__ constexpr uint64_t exchange_tiles_bytes(uint32_t world, uint32_t groups) {
     return 2ull * world * groups * kExchangeTileBytes;
 }
+__host__ __device__ constexpr uint64_t exchange_extent(uint32_t world, uint32_t groups) {
+    return exchange_tiles_bytes(world, groups) + 256;
+}
+
+// Sequence of a launch that counts on the device: launches 0, 1, 2, ... map to 1, 2, ..., 0xFFFFFFFE, 1, ...
+// (never 0, the value of a fresh buffer; the parity alternates across the wrap). Every rank runs the same
+// launches in the same order, so the ranks' counters agree without talking to each other, and a captured
+// CUDA graph can be replayed: nothing about the sequence is baked into the launch parameters.
+__device__ __forceinline__ uint32_t sequence_of(uint32_t launches) { return launches % 0xFFFFFFFEu + 1u; }
 
 // exchange[r] by a chain of selects: a run-time index into kernel parameters would put the table on the stack.
 __device__ __forceinline__ uint64_t exchange_base(const GemvParams& p, uint32_t r) {
@@ -295,12 +293,12 @@ __device__ __forceinline__ uint64_t exchange_base(const GemvParams& p, uint32_t 
     }
     return base;
 }
-__device__ __forceinline__ uint64_t exchange_slot(const GemvParams& p, uint32_t src, uint32_t group, uint32_t lane) {
-    return ((static_cast<uint64_t>(p.tp_sequence & 1) * p.tp_world + src) * p.groups + group) * kExchangeTileBytes + lane * 64;
+__device__ __forceinline__ uint64_t exchange_slot(const GemvParams& p, uint32_t seq, uint32_t src, uint32_t group, uint32_t lane) {
+    return ((static_cast<uint64_t>(seq & 1) * p.tp_world + src) * p.groups + group) * kExchangeTileBytes + lane * 64;
 }
 
-__device__ __forceinline__ void exchange_push(const GemvParams& p, uint32_t group, const float (&v)[8], uint32_t lane) {
-    const uint64_t offset = exchange_slot(p, p.tp_rank, group, lane);
+__device__ __forceinline__ void exchange_push(const GemvParams& p, uint32_t seq, uint32_t group, const float (&v)[8], uint32_t lane) {
+    const uint64_t offset = exchange_slot(p, seq, p.tp_rank, group, lane);
 #pragma unroll
     for (uint32_t d = 0; d < AUGUR_NVFP4_SM100_MAX_TP_RANKS; ++d) {
         if (d < p.tp_world) {
@@ -308,7 +306,7 @@ __device__ __forceinline__ void exchange_push(const GemvParams& p, uint32_t grou
 #pragma unroll
             for (uint32_t j = 0; j < 4; ++j) {
                 asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %2};"
-                             ::"l"(dst + j * 16), "r"(__float_as_uint(v[2 * j] * p.global_a)), "r"(p.tp_sequence),
+                             ::"l"(dst + j * 16), "r"(__float_as_uint(v[2 * j] * p.global_a)), "r"(seq),
                                "r"(__float_as_uint(v[2 * j + 1] * p.global_a))
                              : "memory");
             }
@@ -317,8 +315,8 @@ __device__ __forceinline__ void exchange_push(const GemvParams& p, uint32_t grou
 }
 
 // Whole warps call this once, after everything else the kernel does.
-__device__ __forceinline__ void exchange_reduce(const GemvParams& p, uint32_t warp, uint32_t lane) {
-    const uint32_t world = p.tp_world, seq = p.tp_sequence;
+__device__ __forceinline__ void exchange_reduce(const GemvParams& p, uint32_t seq, uint32_t warp, uint32_t lane) {
+    const uint32_t world = p.tp_world;
     const uint64_t own = exchange_base(p, p.tp_rank);
     constexpr uint32_t kBatch = 4;   // sources polled together, so that their load latencies overlap
     bool arrived = true;
@@ -332,7 +330,7 @@ __device__ __forceinline__ void exchange_reduce(const GemvParams& p, uint32_t wa
 #pragma unroll
                 for (uint32_t q = 0; q < kBatch; ++q) {
                     if (first + q < world) {
-                        const uint64_t from = own + exchange_slot(p, first + q, group, lane);
+                        const uint64_t from = own + exchange_slot(p, seq, first + q, group, lane);
 #pragma unroll
                         for (uint32_t j = 0; j < 4; ++j) {
                             asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
@@ -376,9 +374,9 @@ __device__ __forceinline__ void exchange_reduce(const GemvParams& p, uint32_t wa
     if (!__all_sync(0xffffffffu, arrived) && lane == 0) atomicCAS(p.status_word, 0u, 0x203u);   // a tile never arrived
 }
 
-__device__ __forceinline__ void epilogue(const GemvParams& p, uint32_t group, const float (&v)[8], uint32_t lane) {
+__device__ __forceinline__ void epilogue(const GemvParams& p, uint32_t seq, uint32_t group, const float (&v)[8], uint32_t lane) {
     if (p.tp_world) {
-        exchange_push(p, group, v, lane);   // the sum over ranks is written by exchange_reduce
+        exchange_push(p, seq, group, v, lane);   // the sum over ranks is written by exchange_reduce
         return;
     }
     const uint32_t g = lane >> 2, t4 = lane & 3;
@@ -476,13 +474,6 @@ __device__ __forceinline__ void stage_activations(const GemvParams& p, uint32_t 
         factor_out[2 * token] = __uint_as_float(static_cast<uint32_t>(127 + q0) << 23);
         factor_out[2 * token + 1] = __uint_as_float(static_cast<uint32_t>(127 + q1) << 23);
     }
-#ifdef AUGUR_GEMV_TRACE
-    if (threadIdx.x == 0) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        p.trace[blockIdx.x * 10 + 5] = t;
-    }
-#endif
     // x * 2^e as two exact BF16 multiplications by 2^(e/2) and 2^(e - e/2) (e is in [-27, 226]);
     // the values only move toward the staged row's magnitude, so neither step can overflow.
     const int e0 = e / 2, e1 = e - e0;
@@ -509,11 +500,11 @@ __device__ __forceinline__ void stage_activations(const GemvParams& p, uint32_t 
 }
 
 // One CTA's finished share of row group `group` in k-slab `slab` (whole warp calls this).
-__device__ __forceinline__ void contribute(const GemvParams& p, uint32_t group, uint32_t slab, uint32_t cta_in_slab,
+__device__ __forceinline__ void contribute(const GemvParams& p, uint32_t seq, uint32_t group, uint32_t slab, uint32_t cta_in_slab,
                                            const float (&v)[8], uint32_t lane) {
     // Spans cut at row-group boundaries (one k-slab): the group was finished inside this CTA.
     if (p.unit != 1) {
-        epilogue(p, group, v, lane);
+        epilogue(p, seq, group, v, lane);
         return;
     }
     // How many CTAs hold a share of this group, over all k-slabs, and which of them this one is.
@@ -536,34 +527,18 @@ __device__ __forceinline__ void contribute(const GemvParams& p, uint32_t group, 
         }
     }
     if (total == 1) {
-        epilogue(p, group, v, lane);
+        epilogue(p, seq, group, v, lane);
         return;
     }
     float* slots = p.partials + static_cast<uint64_t>(group) * p.max_contrib * kSlotFloats;
     float4* my_slot = reinterpret_cast<float4*>(slots + static_cast<uint64_t>(mine) * kSlotFloats) + lane * 2;
     my_slot[0] = make_float4(v[0], v[1], v[2], v[3]);
     my_slot[1] = make_float4(v[4], v[5], v[6], v[7]);
-#ifdef AUGUR_GEMV_TRACE
-    auto mark = [&](uint32_t which) {
-        if (threadIdx.x == 0) {
-            unsigned long long t;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-            p.trace[blockIdx.x * 10 + which] = t;
-        }
-    };
-    mark(6);
-#endif
     __threadfence();
     __syncwarp();
-#ifdef AUGUR_GEMV_TRACE
-    mark(7);
-#endif
     uint32_t arrived = 0;
     if (lane == 0) arrived = atomicAdd(&p.counters[group], 1u);
     arrived = __shfl_sync(0xffffffffu, arrived, 0);
-#ifdef AUGUR_GEMV_TRACE
-    mark(8);
-#endif
     if (arrived + 1 != total) return;
     __threadfence();
     // Slots are summed in slot order; four are fetched at a time so that their latencies overlap.
@@ -587,25 +562,12 @@ __device__ __forceinline__ void contribute(const GemvParams& p, uint32_t group, 
             }
         }
     }
-    epilogue(p, group, sum, lane);
-#ifdef AUGUR_GEMV_TRACE
-    mark(9);
-#endif
+    epilogue(p, seq, group, sum, lane);
     if (lane == 0) p.counters[group] = 0;  // leave the counter clean for the next launch
 }
 
 __global__ void __launch_bounds__(kWarps * 32, 1) gemv_kernel(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
-#ifdef AUGUR_GEMV_TRACE
-    auto stamp = [&](uint32_t which) {
-        if (threadIdx.x == 0) {
-            unsigned long long t;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-            p.trace[blockIdx.x * 10 + which] = t;
-        }
-    };
-    stamp(0);
-#endif
     // Let the next kernel in the stream become resident on SMs as this grid drains; every
     // kernel of this library defers its global reads of produced data, and all of its global
     // writes, until its own griddepcontrol.wait.
@@ -655,7 +617,6 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_kernel(const GemvParams p
     }
     __syncthreads();
     // Weight copies go out first so that HBM is busy while the activations are staged.
-#ifndef AUGUR_GEMV_PROBE_NO_LOAD
     if (lane == 0) {
         for (uint32_t d = 0; d < kDepth; ++d) {
             if (w0 + d < w1) {
@@ -664,15 +625,19 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_kernel(const GemvParams p
             }
         }
     }
-#endif
 
     // ---- activations of this k-slab ----
     // Everything above touched only this CTA's shared memory and read-only weights, so it may
     // run while the kernel before this one is still in flight; from here on its output is needed.
     asm volatile("griddepcontrol.wait;" ::: "memory");
-#ifdef AUGUR_GEMV_TRACE
-    stamp(4);
-#endif
+    // Tensor-parallel launches that count their sequence on the device read the counter here: the launch
+    // before this one is complete, and nobody advances the counter before every CTA of this grid is done.
+    uint32_t seq = p.tp_sequence;
+    uint32_t launches_before = 0;
+    if (p.tp_world && seq == 0) {
+        launches_before = *reinterpret_cast<volatile uint32_t*>(p.tp_counter);
+        seq = sequence_of(launches_before);
+    }
     float* stage_scratch = reinterpret_cast<float*>(scale_area);   // free until the streaming loop starts
     const bool plain = p.fixed_factor == 0.0f;
     {
@@ -714,9 +679,6 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_kernel(const GemvParams p
         __syncthreads();
     }
 
-#ifdef AUGUR_GEMV_TRACE
-    stamp(1);
-#endif
     const uint32_t t4 = lane & 3;
     float inv0a = p.fixed_factor, inv0b = p.fixed_factor, inv1a = p.fixed_factor, inv1b = p.fixed_factor;
     if (plain) {
@@ -742,7 +704,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_kernel(const GemvParams p
 #pragma unroll
         for (uint32_t i = 0; i < 8; ++i) v[i] = acc[i] * ((i & 1) ? inv1a : inv0a) * ((i & 1) ? inv1b : inv0b);
         if (first_kbi == 0 && last_kbi + 1 == kbs) {
-            contribute(p, group, slab, cta_in_slab, v, lane);
+            contribute(p, seq, group, slab, cta_in_slab, v, lane);
         } else if (group == first_group) {
 #pragma unroll
             for (uint32_t i = 0; i < 8; ++i) head[i] = v[i];
@@ -767,26 +729,18 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_kernel(const GemvParams p
             seg_group = now.group;
             seg_first_kbi = 0;
         }
-#ifndef AUGUR_GEMV_PROBE_NO_LOAD
         uint32_t spin = 0;
         while (!mbar_try_wait(my_bars + 8 * slot, parity)) {
             if (++spin > kWaitLimit) { ring_ok = false; break; }
         }
         if (!ring_ok) break;
-#endif
-#ifndef AUGUR_GEMV_PROBE_NO_COMPUTE
         compute_block(acc, my_ring + slot * kStreamBlockBytes, act + kbi * 128,
                       reinterpret_cast<float*>(scale_area + warp * kScaleScratchBytes), lane);
-#else
-        acc[0] += __uint_as_float(*reinterpret_cast<const uint32_t*>(my_ring + slot * kStreamBlockBytes + lane * 16));
-#endif
         __syncwarp();
-#ifndef AUGUR_GEMV_PROBE_NO_LOAD
         if (lane == 0 && at + kDepth < w1) {
             issue_block(smem_u32(my_ring + slot * kStreamBlockBytes), my_bars + 8 * slot, fetch.ptr);
             step(fetch);
         }
-#endif
         step(now);
         if (++slot == kDepth) {
             slot = 0;
@@ -810,9 +764,6 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_kernel(const GemvParams p
         dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
     }
     __syncthreads();
-#ifdef AUGUR_GEMV_TRACE
-    stamp(2);
-#endif
 
     // ---- combine row groups that were split between warps of this CTA ----
     if (len != 0) {
@@ -834,15 +785,24 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_kernel(const GemvParams p
                 sum[0] += a.x; sum[1] += a.y; sum[2] += a.z; sum[3] += a.w;
                 sum[4] += b.x; sum[5] += b.y; sum[6] += b.z; sum[7] += b.w;
             }
-            contribute(p, group, slab, cta_in_slab, sum, lane);
+            contribute(p, seq, group, slab, cta_in_slab, sum, lane);
         }
     }
     // ---- tensor-parallel: add the ranks' tiles of the row groups assigned to this warp ----
-    if (p.tp_world) exchange_reduce(p, warp, lane);
-#ifdef AUGUR_GEMV_TRACE
-    __syncthreads();
-    stamp(3);
-#endif
+    if (p.tp_world) {
+        exchange_reduce(p, seq, warp, lane);
+        if (p.tp_sequence == 0) {
+            // the last CTA to get here advances the counter for the next launch and clears the arrivals
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                __threadfence();
+                if (atomicAdd(p.tp_counter + 1, 1u) + 1 == gridDim.x) {
+                    p.tp_counter[1] = 0;
+                    p.tp_counter[0] = launches_before + 1;
+                }
+            }
+        }
+    }
 }
 
 constexpr uint32_t kGemvSmemBytes = kMaxSlabBlocks * 4 * 512 + kWarps * kDepth * kStreamBlockBytes +
@@ -918,10 +878,6 @@ void launch_gemv(augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* pl
     p.fixed_factor = input_is_staged ? 0x1p31f : 0.0f;      // (2^31)^2 = 2^(126 - kFixedStageShift)
     p.staged_out = staged_out_offset ? reinterpret_cast<uint16_t*>(plan->scratch + staged_out_offset) : nullptr;
     p.status_word = plan->status_word;
-#ifdef AUGUR_GEMV_TRACE
-    static uint32_t trace_sequence = 0;   // eight most recent launches, 2048 stamps each
-    p.trace = reinterpret_cast<unsigned long long*>(plan->scratch + plan->scratch_bytes - 131072) + (trace_sequence++ % 8) * 2048;
-#endif
     p.groups = g.groups; p.kb_count = g.kb_count; p.slabs = g.slabs; p.ctas_per_slab = g.ctas_per_slab;
     p.max_contrib = g.max_contrib;
     p.rows = a->rows; p.cols = a->cols; p.tokens = a->tokens; p.epilogue = a->epilogue;
@@ -929,6 +885,7 @@ void launch_gemv(augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* pl
     if (tp) {
         for (uint32_t r = 0; r < tp->world; ++r) p.exchange[r] = tp->exchange[r];
         p.tp_world = tp->world; p.tp_rank = tp->rank; p.tp_sequence = tp->sequence;
+        p.tp_counter = reinterpret_cast<uint32_t*>(tp->exchange[tp->rank] + exchange_tiles_bytes(tp->world, a->rows / 32));
     }
     // Launched with programmatic stream serialisation: the grid may become resident while its
     // predecessor drains, and waits for it in-kernel (griddepcontrol.wait).
@@ -1083,7 +1040,7 @@ bool check_mlp_tp(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100
     local.down = a->down;
     if (!check_mlp(d, s, plan, &local, full, down_offset, failure)) return false;
     *failure = invalid();
-    if (a->reserved || a->world < 1 || a->world > AUGUR_NVFP4_SM100_MAX_TP_RANKS || a->rank >= a->world || a->sequence == 0 ||
+    if (a->reserved || a->world < 1 || a->world > AUGUR_NVFP4_SM100_MAX_TP_RANKS || a->rank >= a->world ||
         a->down.epilogue != AUGUR_NVFP4_SM100_EPILOGUE_LINEAR_BF16) {
         return false;
     }
@@ -1314,10 +1271,16 @@ cudaError_t static_scratch_setup(int32_t ordinal, StaticScratchDevice** out) {
     std::lock_guard<std::mutex> lock(g_static_mutex);
     StaticScratchDevice& device = g_static_devices[ordinal];
     if (!device.ready) {
-        void* address = nullptr;
-        cudaError_t e = cudaGetSymbolAddress(&address, g_static_scratch);
+        int major = 0, sms = 0;
+        cudaError_t e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, ordinal);
         if (e != cudaSuccess) return e;
-        int sms = 0;
+        if (major != 10) {   // the image holds sm_100a code only; the array does not exist elsewhere
+            *out = nullptr;
+            return cudaSuccess;
+        }
+        void* address = nullptr;
+        e = cudaGetSymbolAddress(&address, g_static_scratch);
+        if (e != cudaSuccess) return e;
         e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, ordinal);
         if (e != cudaSuccess) return e;
         e = gemv_configure_device();
@@ -1339,11 +1302,13 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_bf16
     StaticScratchDevice* device = nullptr;
     e = static_scratch_setup(d, &device);
     if (e != cudaSuccess) return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE, e);
+    if (!device) return make_result(AUGUR_CUDA_STATUS_UNSUPPORTED_DEVICE);
     // A plan-shaped view of the fixed array: status word in front, then the same layout a plan has.
     augur_cuda_nvfp4_sm100_plan_v1 view{};
     view.magic = kPlanMagic;
     view.ordinal = d;
     view.owner = s;
+    view.owner_stream = s->stream;
     view.status_word = reinterpret_cast<uint32_t*>(device->address);
     view.scratch = device->address + kPlanHeaderBytes;
     view.scratch_bytes = AUGUR_NVFP4_SM100_STATIC_SCRATCH_BYTES - kPlanHeaderBytes;
@@ -1361,4 +1326,23 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_bf16
     if (e != cudaSuccess) return make_result(AUGUR_CUDA_STATUS_SUBMISSION_FAILURE, e);
     launch_gemv(s, &view, a, 0, kCounterBytes);
     return submitted();
+}
+
+// The status word of the fixed array (its first four bytes), for the entry above: what
+// plan_device_status_v1 is to a plan. Copies the word back on `s` and waits for the stream; a
+// non-zero word is then set back to zero (a memset on the same stream), so every give-up is
+// reported once. Like the submit entry it allocates nothing.
+extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_static_scratch_status_v1(
+    int32_t d, augur_cuda_stream_t s, uint32_t* out_status) {
+    if (d < 0 || d >= 64 || !s || s->ordinal != d || !out_status) return invalid();
+    cudaError_t e = cudaSetDevice(d);
+    if (e != cudaSuccess) return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE, e);
+    StaticScratchDevice* device = nullptr;
+    e = static_scratch_setup(d, &device);
+    if (e != cudaSuccess) return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE, e);
+    if (!device) return make_result(AUGUR_CUDA_STATUS_UNSUPPORTED_DEVICE);
+    e = cudaMemcpyAsync(out_status, device->address, sizeof(uint32_t), cudaMemcpyDeviceToHost, s->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s->stream);
+    if (e == cudaSuccess && *out_status != 0) e = cudaMemsetAsync(device->address, 0, sizeof(uint32_t), s->stream);
+    return e == cudaSuccess ? ok() : make_result(AUGUR_CUDA_STATUS_COMPLETION_FAILURE, e);
 }

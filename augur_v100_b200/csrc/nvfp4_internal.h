@@ -17,6 +17,7 @@ struct augur_cuda_stream_handle {
     int32_t ordinal;
     cudaStream_t stream;
     int32_t owned;
+    int32_t plans;   // live plans made on this handle; the handle is not destroyed while any exist
 };
 
 struct augur_cuda_nvfp4_sm100_plan_v1 {
@@ -27,6 +28,10 @@ struct augur_cuda_nvfp4_sm100_plan_v1 {
     uint64_t scratch_bytes;
     uint32_t* status_word;     // device, 256 bytes reserved in front of scratch
     uint32_t sm_count;
+    // Copied from the owner when the plan is made: destroy and status read-back must not dereference a
+    // stream handle that its owner may already have closed. `owner` itself only serves the identity check.
+    cudaStream_t owner_stream;
+    uint32_t pair_clusters;    // two-CTA clusters of the pair GEMM that can be resident at once on this device
 };
 
 namespace augur_sm100 {
@@ -96,5 +101,7 @@ augur_cuda_result_v1 submitted();  // maps cudaGetLastError to SUBMISSION_FAILUR
 // One-time per-device kernel attribute setup, called from plan creation (bind time).
 cudaError_t gemv_configure_device();
 cudaError_t gemm_configure_device();
+// Two-CTA clusters of the pair GEMM that the device can hold at once (0 if the query fails).
+uint32_t gemm_pair_resident_clusters();
 
 }  // namespace augur_sm100

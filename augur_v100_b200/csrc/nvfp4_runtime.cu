@@ -130,7 +130,7 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_stream_cr
     cudaStream_t raw = nullptr;
     e = cudaStreamCreateWithFlags(&raw, cudaStreamNonBlocking);
     if (e != cudaSuccess) return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE, e);
-    auto* handle = new (std::nothrow) augur_cuda_stream_handle{ordinal, raw, 1};
+    auto* handle = new (std::nothrow) augur_cuda_stream_handle{ordinal, raw, 1, 0};
     if (!handle) {
         cudaStreamDestroy(raw);
         return make_result(AUGUR_CUDA_STATUS_OUT_OF_MEMORY);
@@ -143,7 +143,7 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_stream_ad
     int32_t ordinal, void* raw_cuda_stream, augur_cuda_stream_t* out_stream) {
     if (ordinal < 0 || !out_stream) return invalid();
     auto* handle = new (std::nothrow)
-        augur_cuda_stream_handle{ordinal, static_cast<cudaStream_t>(raw_cuda_stream), 0};
+        augur_cuda_stream_handle{ordinal, static_cast<cudaStream_t>(raw_cuda_stream), 0, 0};
     if (!handle) return make_result(AUGUR_CUDA_STATUS_OUT_OF_MEMORY);
     *out_stream = handle;
     return ok();
@@ -161,6 +161,8 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_stream_sy
 extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_stream_destroy_v1(
     augur_cuda_stream_t stream) {
     if (!stream) return invalid();
+    // Plans keep a pointer to their owner for the identity check of every call: close them first.
+    if (stream->plans != 0) return invalid();
     cudaError_t e = cudaSuccess;
     if (stream->owned) {
         cudaSetDevice(stream->ordinal);
@@ -214,6 +216,10 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_plan_crea
     plan->scratch = static_cast<uint8_t*>(memory) + kPlanHeaderBytes;
     plan->scratch_bytes = rounded;
     plan->sm_count = static_cast<uint32_t>(sms);
+    plan->owner_stream = stream->stream;
+    ++stream->plans;
+    const uint32_t resident = gemm_pair_resident_clusters();
+    plan->pair_clusters = resident && resident < plan->sm_count / 2 ? resident : plan->sm_count / 2;
     *out_plan = plan;
     return ok();
 }
@@ -235,10 +241,11 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_plan_dest
     augur_cuda_nvfp4_sm100_plan_v1* plan) {
     if (!plan || plan->magic != kPlanMagic) return invalid();
     cudaSetDevice(plan->ordinal);
-    cudaError_t e = cudaStreamSynchronize(plan->owner->stream);
+    cudaError_t e = cudaStreamSynchronize(plan->owner_stream);
     const cudaError_t freed = cudaFree(plan->status_word);
     count_free();
     if (e == cudaSuccess) e = freed;
+    --plan->owner->plans;   // the handle is alive: it cannot be destroyed while this plan exists
     plan->magic = 0;
     delete plan;
     return e == cudaSuccess ? ok() : make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE, e);
@@ -250,9 +257,9 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_plan_devi
     cudaError_t e = cudaSetDevice(plan->ordinal);
     if (e == cudaSuccess) {
         e = cudaMemcpyAsync(out_status, plan->status_word, sizeof(uint32_t), cudaMemcpyDeviceToHost,
-                            plan->owner->stream);
+                            plan->owner_stream);
     }
-    if (e == cudaSuccess) e = cudaStreamSynchronize(plan->owner->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(plan->owner_stream);
     return e == cudaSuccess ? ok() : make_result(AUGUR_CUDA_STATUS_COMPLETION_FAILURE, e);
 }
 

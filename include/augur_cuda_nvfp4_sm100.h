@@ -100,6 +100,9 @@ augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_stream_adopt_v1(
     int32_t ordinal, void* raw_cuda_stream, augur_cuda_stream_t* out_stream);
 augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_stream_synchronize_v1(
     augur_cuda_stream_t stream);
+/* Order of destruction: plans first, then the handle they were made on. A handle that still has
+ * live plans is not destroyed (INVALID_ARGUMENT), because every plan call checks the plan against
+ * the handle it was made on. */
 augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_stream_destroy_v1(
     augur_cuda_stream_t stream);
 
@@ -283,6 +286,13 @@ augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_bf16_prevalidat
 #define AUGUR_NVFP4_SM100_STATIC_SCRATCH_BYTES (UINT32_C(4) << 20)
 augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_bf16_static_scratch_submit_v1(
     int32_t ordinal, augur_cuda_stream_t stream, const augur_cuda_nvfp4_sm100_gemv_args_v1* args);
+/* No counterpart in the reference. The device-side status word of that entry (0 = clean): the kernel's
+ * bounded waits record where they gave up in the first four bytes of the fixed array, as they do in a
+ * plan's status word. Copies the word to `out_status` on `stream` and waits for the stream; a non-zero
+ * word is set back to zero afterwards, so a give-up is reported once. Allocates nothing. Devices other
+ * than compute capability 10.x get AUGUR_CUDA_STATUS_UNSUPPORTED_DEVICE from both entries. */
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_static_scratch_status_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, uint32_t* out_status);
 
 /* ---- MLP program: gate|up + SwiGLU, then down ------------------------------- */
 /* Replaces CudaQwen35QpnFfnProgramV1's two native steps

@@ -4,8 +4,9 @@ Some hosts give all device memory to their own arena when they start, or run the
 under a checked no-allocation rule; such a host cannot create a plan (plan creation calls
 cudaMalloc). `augur_cuda_nvfp4_sm100_gemv_bf16_static_scratch_submit_v1` serves them from a fixed
 scratch array inside the library. This test calls it through the C ABI, twice in a row, and checks
-each result against the plan-based entry point on the same inputs; it also checks that the call
-allocates nothing and that a shape too large for the fixed array is refused.
+each result against the plan-based entry point on the same inputs and against the CPU oracle; it
+also checks that the call allocates nothing, that the entry's status word reads clean, that the
+other two epilogues work from the fixed array, and that a shape too large for it is refused.
 
 Collected last on purpose (file name), so that a run that stops at the first failure has already
 executed every other test.
@@ -15,8 +16,11 @@ from ctypes import byref
 import numpy as np
 import pytest
 
+from ctypes import c_uint32
+
+import oracle
 from augur_v100_b200 import abi, synth
-from helpers import TOLERANCE, bits_from_torch_bf16, torch_bf16_from_bits
+from helpers import TOLERANCE, bits_from_torch_bf16, rel_error, rel_error_f32, torch_bf16_from_bits
 
 pytestmark = pytest.mark.gpu
 
@@ -56,6 +60,39 @@ def test_static_scratch_entry_matches_plan_entry_twice_and_allocates_nothing():
             assert torch.cuda.memory_stats()["allocation.all.allocated"] == torch_allocations
             got, want = bits_from_torch_bf16(out), bits_from_torch_bf16(reference.out)
             assert _max_rel_diff(got, want) <= TOLERANCE, call
+            # and against the reference arithmetic itself, not only against this library's other entry
+            y64 = oracle.linear_f64(codes, scales, glob, rows, cols, synth.make_activation(call, 95, "x", tokens, cols),
+                                    threads=oracle.max_threads())
+            assert rel_error(got, y64) <= TOLERANCE, call
+            word = c_uint32(0xFFFFFFFF)
+            result = lib.augur_cuda_nvfp4_sm100_static_scratch_status_v1(stream.ordinal, stream.handle, byref(word))
+            assert result.status == abi.STATUS_OK and word.value == 0
+        # the f32 epilogue from the fixed array
+        out32 = torch.full((tokens, rows), float("nan"), dtype=torch.float32, device=device)
+        args = host.gemv_args(weight, x, out32, abi.EPILOGUE_LINEAR_F32)
+        result = lib.augur_cuda_nvfp4_sm100_gemv_bf16_static_scratch_submit_v1(stream.ordinal, stream.handle, byref(args))
+        assert result.status == abi.STATUS_OK, (result.status, result.raw_cuda_status)
+        stream.synchronize()
+        assert rel_error_f32(out32.cpu().numpy(), y64) <= TOLERANCE
+        # the fused SiLU(gate) * up epilogue (paired layout), against the plan entry bit for bit
+        pair_rows = 1024
+        gate = synth.make_weight(4, 95, "gate", pair_rows, cols)
+        up = synth.make_weight(4, 95, "up", pair_rows, cols)
+        pair = host.Nvfp4Sm100Weight.upload_checkpoint_nvfp4(stream, abi.LAYOUT_STREAM_PAIR, pair_rows, cols, *gate, *up)
+        pair_plan = host.Plan(stream, host.gemv_scratch_bytes(pair_rows, cols, tokens))
+        try:
+            reference = host.Nvfp4Sm100Projection.bind(pair_plan, pair, x)
+            reference.submit_for_plan()
+            stream.synchronize()
+            out = torch.full((tokens, pair_rows), float("nan"), dtype=torch.bfloat16, device=device)
+            args = host.gemv_args(pair, x, out, abi.EPILOGUE_SWIGLU_BF16)
+            result = lib.augur_cuda_nvfp4_sm100_gemv_bf16_static_scratch_submit_v1(stream.ordinal, stream.handle, byref(args))
+            assert result.status == abi.STATUS_OK, (result.status, result.raw_cuda_status)
+            stream.synchronize()
+            assert torch.equal(out.view(torch.int16), reference.out.view(torch.int16))
+        finally:
+            pair_plan.close()
+        out = torch.empty((tokens, rows), dtype=torch.bfloat16, device=device)
         # too large for the fixed array: refused before anything is enqueued
         big_rows, big_cols = 32768, 17408
         launches = host.launch_count()
