@@ -104,6 +104,13 @@ class MlpTpArgs(Structure):
                 ("world", c_uint32), ("rank", c_uint32), ("sequence", c_uint32), ("reserved", c_uint32)]
 
 
+class GemvTpArgs(Structure):
+    _fields_ = [("abi_version", c_uint32), ("struct_size", c_uint32),
+                ("linear", GemvArgs),
+                ("exchange", c_uint64 * MAX_TP_RANKS), ("exchange_len_bytes", c_uint64),
+                ("world", c_uint32), ("rank", c_uint32), ("sequence", c_uint32), ("reserved", c_uint32)]
+
+
 class ActQuantArgs(Structure):
     _fields_ = [("abi_version", c_uint32), ("struct_size", c_uint32),
                 ("input_bf16", c_uint64), ("input_len_bytes", c_uint64),
@@ -178,6 +185,8 @@ EXPORTS = {
     "augur_cuda_nvfp4_sm100_mlp_tp_exchange_extent_host_v1": (Result, [c_uint32, c_uint32, POINTER(c_uint64)]),
     "augur_cuda_nvfp4_sm100_mlp_tp_preflight_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(MlpTpArgs)]),
     "augur_cuda_nvfp4_sm100_mlp_tp_prevalidated_submit_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(MlpTpArgs)]),
+    "augur_cuda_nvfp4_sm100_gemv_tp_preflight_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(GemvTpArgs)]),
+    "augur_cuda_nvfp4_sm100_gemv_tp_prevalidated_submit_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(GemvTpArgs)]),
     "augur_cuda_nvfp4_sm100_act_quant_preflight_v1": (Result, [c_int32, c_void_p, POINTER(ActQuantArgs)]),
     "augur_cuda_nvfp4_sm100_act_quant_prevalidated_submit_v1": (Result, [c_int32, c_void_p, POINTER(ActQuantArgs)]),
     "augur_cuda_nvfp4_sm100_gemm_bf16_preflight_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(GemmArgs)]),

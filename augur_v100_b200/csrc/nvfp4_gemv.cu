@@ -858,13 +858,18 @@ bool check_gemv(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_p
     return !full || inspect_device_ranges(d, r, 3, failure);
 }
 
+// The tensor-parallel part of a launch: every rank's exchange buffer as mapped here.
+struct ExchangeTable {
+    const uint64_t* exchange;
+    uint32_t world, rank, sequence;
+};
+
 // `staged_out_offset` (non-zero): the SwiGLU result is also written, staged, at that offset of the plan
 // scratch. `input_is_staged`: the activations were staged there by the producing launch (fixed
 // exponent) and are copied in as they are instead of being staged by the kernel.
 void launch_gemv(augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* plan,
                  const augur_cuda_nvfp4_sm100_gemv_args_v1* a, uint32_t member, uint64_t partial_offset,
-                 uint64_t staged_out_offset = 0, bool input_is_staged = false,
-                 const augur_cuda_nvfp4_sm100_mlp_tp_args_v1* tp = nullptr) {
+                 uint64_t staged_out_offset = 0, bool input_is_staged = false, const ExchangeTable* tp = nullptr) {
     const bool pair = a->epilogue == AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16;
     const GemvGeometry g = geometry(a->rows, a->cols, pair, plan->sm_count);
     GemvParams p{};
@@ -1022,6 +1027,26 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_mlp_preva
 namespace {
 static_assert(sizeof(augur_cuda_nvfp4_sm100_mlp_tp_args_v1) == 272, "mlp_tp ABI");
 
+// The exchange buffers of a row-parallel linear `m`: extent, alignment, no two alike, and a grid that is
+// resident as a whole (the reduce step polls for tiles that other CTAs of the same grid deliver).
+bool exchange_table_ok(const augur_cuda_nvfp4_sm100_plan_v1* plan, const augur_cuda_nvfp4_sm100_gemv_args_v1& m,
+                       const uint64_t (&exchange)[AUGUR_NVFP4_SM100_MAX_TP_RANKS], uint64_t exchange_len_bytes, uint32_t world) {
+    if (exchange_len_bytes < exchange_extent(world, m.rows / 32)) return false;
+    const GemvGeometry g = geometry(m.rows, m.cols, false, plan->sm_count);
+    if (g.slabs * g.ctas_per_slab > plan->sm_count) return false;
+    for (uint32_t r = 0; r < AUGUR_NVFP4_SM100_MAX_TP_RANKS; ++r) {
+        if (r >= world) {
+            if (exchange[r]) return false;
+            continue;
+        }
+        if (!exchange[r] || exchange[r] % 256 != 0) return false;
+        for (uint32_t q = 0; q < r; ++q) {
+            if (!disjoint({exchange[r], exchange_len_bytes, 256}, {exchange[q], exchange_len_bytes, 256})) return false;
+        }
+    }
+    return true;
+}
+
 bool check_mlp_tp(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* plan,
                   const augur_cuda_nvfp4_sm100_mlp_tp_args_v1* a, bool full, uint64_t* down_offset,
                   augur_cuda_result_v1* failure) {
@@ -1044,20 +1069,7 @@ bool check_mlp_tp(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100
         a->down.epilogue != AUGUR_NVFP4_SM100_EPILOGUE_LINEAR_BF16) {
         return false;
     }
-    if (a->exchange_len_bytes < exchange_extent(a->world, a->down.rows / 32)) return false;
-    // The reduce step polls for tiles that other CTAs of the same grid deliver: all of them must be resident.
-    const GemvGeometry down_geometry = geometry(a->down.rows, a->down.cols, false, plan->sm_count);
-    if (down_geometry.slabs * down_geometry.ctas_per_slab > plan->sm_count) return false;
-    for (uint32_t r = 0; r < AUGUR_NVFP4_SM100_MAX_TP_RANKS; ++r) {
-        if (r >= a->world) {
-            if (a->exchange[r]) return false;
-            continue;
-        }
-        if (!a->exchange[r] || a->exchange[r] % 256 != 0) return false;
-        for (uint32_t q = 0; q < r; ++q) {
-            if (!disjoint({a->exchange[r], a->exchange_len_bytes, 256}, {a->exchange[q], a->exchange_len_bytes, 256})) return false;
-        }
-    }
+    if (!exchange_table_ok(plan, a->down, a->exchange, a->exchange_len_bytes, a->world)) return false;
     // This rank's own exchange buffer is local memory like any other range of the program.
     const Range r[7] = {{a->gate_up.weight, a->gate_up.weight_len_bytes, 256},
                         {a->gate_up.input_bf16, a->gate_up.input_len_bytes, 16},
@@ -1097,7 +1109,57 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_mlp_tp_pr
     launch_gemv(s, plan, &a->gate_up, 0, kCounterBytes, down_offset, false);
     augur_cuda_result_v1 first = submitted();
     if (first.status != AUGUR_CUDA_STATUS_OK) return first;
-    launch_gemv(s, plan, &a->down, 1, down_offset, 0, true, a);
+    const ExchangeTable table{a->exchange, a->world, a->rank, a->sequence};
+    launch_gemv(s, plan, &a->down, 1, down_offset, 0, true, &table);
+    return submitted();
+}
+
+// ---- a single row-parallel linear with the exchange ------------------------------------------------
+namespace {
+static_assert(sizeof(augur_cuda_nvfp4_sm100_gemv_tp_args_v1) == 184, "gemv_tp ABI");
+
+bool check_gemv_tp(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* plan,
+                   const augur_cuda_nvfp4_sm100_gemv_tp_args_v1* a, bool full, augur_cuda_result_v1* failure) {
+    *failure = invalid();
+    if (!header_ok(d, s, a)) {
+        if (a && s && d >= 0 && s->ordinal == d && a->abi_version != AUGUR_CUDA_ABI_VERSION_V1) {
+            *failure = make_result(AUGUR_CUDA_STATUS_ABI_VERSION_MISMATCH);
+        }
+        return false;
+    }
+    if (!check_gemv(d, s, plan, &a->linear, kCounterBytes, plan ? plan->scratch_bytes : 0, full, failure)) return false;
+    *failure = invalid();
+    if (a->reserved || a->world < 1 || a->world > AUGUR_NVFP4_SM100_MAX_TP_RANKS || a->rank >= a->world ||
+        a->linear.epilogue != AUGUR_NVFP4_SM100_EPILOGUE_LINEAR_BF16) {
+        return false;
+    }
+    if (!exchange_table_ok(plan, a->linear, a->exchange, a->exchange_len_bytes, a->world)) return false;
+    const Range r[5] = {{a->linear.weight, a->linear.weight_len_bytes, 256},
+                        {a->linear.input_bf16, a->linear.input_len_bytes, 16},
+                        {a->linear.output, a->linear.output_len_bytes, 4},
+                        plan_scratch_range(plan),
+                        {a->exchange[a->rank], a->exchange_len_bytes, 256}};
+    return all_disjoint(r, 5);
+}
+}  // namespace
+
+extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_tp_preflight_v1(
+    int32_t d, augur_cuda_stream_t s, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_gemv_tp_args_v1* a) {
+    augur_cuda_result_v1 failure;
+    return check_gemv_tp(d, s, plan, a, true, &failure) ? ok() : failure;
+}
+
+extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_tp_prevalidated_submit_v1(
+    int32_t d, augur_cuda_stream_t s, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_gemv_tp_args_v1* a) {
+    augur_cuda_result_v1 failure;
+    if (!check_gemv_tp(d, s, plan, a, false, &failure)) return failure;
+    if (consume_injected_fault()) return make_result(AUGUR_CUDA_STATUS_DIAGNOSTIC_FAULT_INJECTED);
+    const cudaError_t e = cudaSetDevice(d);
+    if (e != cudaSuccess) return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE, e);
+    const ExchangeTable table{a->exchange, a->world, a->rank, a->sequence};
+    launch_gemv(s, plan, &a->linear, 0, kCounterBytes, 0, false, &table);
     return submitted();
 }
 

@@ -66,15 +66,18 @@ def exchange_extent(hidden: int, world: int) -> int:
 
 
 class ExchangeBuffers:
-    """Peer-mapped exchange buffers of all ranks plus the sequence counter they share.
+    """Peer-mapped exchange buffers of all ranks.
 
-    One object serves every layer with the same hidden size: layers run one after another on the
-    rank's stream, and the sequence number grows by one per submitted program on every rank alike.
+    One object serves every program with the same output width: programs run one after another on the
+    rank's stream, and every launch that uses the buffers advances a sequence number, on every rank alike.
+    By default the launches count that sequence themselves (a counter in the tail of each rank's own
+    buffer), so that bound programs can be captured into a CUDA graph and replayed; with
+    `host_counted=True` the number is counted here and passed with every submit instead.
     Device memory comes from torch's symmetric-memory allocator (plumbing: it creates the
     allocation, exchanges the handles between the processes and maps every peer's buffer here).
     """
 
-    def __init__(self, hidden: int, rank: int, world: int, process_group=None):
+    def __init__(self, hidden: int, rank: int, world: int, process_group=None, host_counted: bool = False):
         import os
 
         import torch
@@ -93,12 +96,23 @@ class ExchangeBuffers:
         self.tensor.zero_()
         torch.cuda.synchronize()
         dist.barrier(group=group)   # nobody publishes a flag before every buffer is zero
+        self.host_counted = host_counted
         self.sequence = 0
 
     def next_sequence(self) -> int:
+        """The `sequence` member of the next submit: 0 when the launches count on the device."""
+        if not self.host_counted:
+            return 0
         # 1, 2, ..., 0xFFFFFFFE, 1, ...: never 0 (the value of a fresh buffer), and the parity alternates across the wrap
         self.sequence = 1 if self.sequence >= 0xFFFFFFFE else self.sequence + 1
         return self.sequence
+
+    def fill(self, args) -> None:
+        """Writes the pointer table and this rank's place in it into an `MlpTpArgs` / `GemvTpArgs`."""
+        for r, pointer in enumerate(self.pointers):
+            args.exchange[r] = pointer
+        args.exchange_len_bytes, args.world, args.rank = self.bytes, self.world, self.rank
+        args.sequence = 0 if not self.host_counted else 1
 
 
 class FusedExchangeProgram:
@@ -113,9 +127,7 @@ class FusedExchangeProgram:
             raise ValueError("exchange buffers were made for another hidden size")
         args = abi.header(abi.MlpTpArgs)
         args.gate_up, args.down = program.args.gate_up, program.args.down
-        for r, pointer in enumerate(exchange.pointers):
-            args.exchange[r] = pointer
-        args.exchange_len_bytes, args.world, args.rank, args.sequence = exchange.bytes, exchange.world, exchange.rank, 1
+        exchange.fill(args)
         plan = program.plan
         host._check("mlp_tp_preflight", abi.lib().augur_cuda_nvfp4_sm100_mlp_tp_preflight_v1(
             plan.stream.ordinal, plan.stream.handle, plan.handle, byref(args)))
@@ -132,6 +144,38 @@ class FusedExchangeProgram:
         self.args.sequence = self.exchange.next_sequence()
         plan = self.program.plan
         host._check("mlp_tp_submit", abi.lib().augur_cuda_nvfp4_sm100_mlp_tp_prevalidated_submit_v1(
+            plan.stream.ordinal, plan.stream.handle, plan.handle, byref(self.args)))
+
+
+class RowParallelLinear:
+    """A bound small-token projection over this rank's k-slice whose launch also does the all-reduce
+    (the output projections outside the MLP block: every rank ends up with the full sum)."""
+
+    def __init__(self, projection, exchange: ExchangeBuffers):
+        from ctypes import byref
+
+        from . import abi, host
+        if exchange.hidden != projection.args.rows:
+            raise ValueError("exchange buffers were made for another output width")
+        args = abi.header(abi.GemvTpArgs)
+        args.linear = projection.args
+        exchange.fill(args)
+        plan = projection.plan
+        host._check("gemv_tp_preflight", abi.lib().augur_cuda_nvfp4_sm100_gemv_tp_preflight_v1(
+            plan.stream.ordinal, plan.stream.handle, plan.handle, byref(args)))
+        self.projection, self.exchange, self.args = projection, exchange, args
+
+    @property
+    def out(self):
+        return self.projection.out
+
+    def submit_for_plan(self) -> None:
+        from ctypes import byref
+
+        from . import abi, host
+        self.args.sequence = self.exchange.next_sequence()
+        plan = self.projection.plan
+        host._check("gemv_tp_submit", abi.lib().augur_cuda_nvfp4_sm100_gemv_tp_prevalidated_submit_v1(
             plan.stream.ordinal, plan.stream.handle, plan.handle, byref(self.args)))
 
 

@@ -4,23 +4,28 @@
     python bench.py --gpus N --steps K --warmup W            # this library (sm_100a kernels)
     python bench.py --impl reference --gpus N --steps K ...  # the reference's CPU path, timed on host cores
 
-Workload (configuration 1 of the benchmark definition): the 27B-class NVFP4 MLP block at the fixed 8-row
-verify batch — gate|up 5120 -> 2x17408 fused with SiLU(gate)*up, then down
-17408 -> 5120 — with synthetic weights of the benchmark's value distributions.
-One step streams LAYERS distinct layers (2.4 GB of weights at N=1, far more than
-L2), so every weight byte of a step comes from HBM. With N > 1 the block is
-tensor-parallel: column-parallel gate|up, row-parallel down, one NCCL all-reduce
-of the 8 x 5120 BF16 output per layer.
+Headline workload (configuration 1 of the benchmark definition): the 27B-class NVFP4 MLP block at the
+fixed 8-row verify batch - gate|up 5120 -> 2x17408 fused with SiLU(gate)*up, then down 17408 -> 5120 -
+with synthetic weights of the benchmark's value distributions. One pass streams LAYERS distinct layers
+(2.4 GB of weights at N=1, far more than L2), so every weight byte comes from HBM; one step is PASSES
+such passes, so that the timed region of a default run lasts about a second. With N > 1 the block is
+tensor-parallel: column-parallel gate|up, row-parallel down, the all-reduce of the 8 x 5120 output
+inside the down launch (peer stores over NVLink) or by NCCL.
 
-Prints one JSON line (rank 0). `value` is whole-job GB/s of algorithmic bytes
-with inputs resident in HBM; `e2e` is the same through the public host API with
-the activations copied from pinned host memory and the result read back every step.
+Prints one JSON line (rank 0). `value` is whole-job GB/s of algorithmic bytes with inputs resident in
+HBM; `e2e` is the same through the public host API with the activations copied from pinned host memory
+and the result read back for every pass. The other configurations of the benchmark definition are
+reported under their own keys of the same line, each outside the headline's timed region:
+`config0` (single 17408 x 5120 linear, M=8), `config1_m1` (the MLP block at M=1), `config2_prefill`
+(M=4096 GEMMs), `config3_sweep` (64-layer whole-model linear sweep at M=8), `config4_prefill_mlp`
+(chunked tensor-parallel prefill MLP).
 """
 from __future__ import annotations
 
 import argparse
 import json
 import os
+import re
 import statistics
 import subprocess
 import sys
@@ -30,23 +35,43 @@ import time
 import numpy as np
 
 HIDDEN, INTER, TOKENS, LAYERS = 5120, 17408, 8, 16
+PASSES = 64
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 
-def layer_bytes() -> int:
+def layer_bytes(tokens: int = TOKENS) -> int:
     """Algorithmic bytes of one MLP layer: every weight byte once + the input + the output (whole job)."""
     weights = 3 * HIDDEN * INTER * 9 // 16          # 0.5 B code + 1/16 B scale per element
-    return weights + 2 * TOKENS * HIDDEN * 2
+    return weights + 2 * tokens * HIDDEN * 2
+
+
+def linear_bytes(rows: int, cols: int, tokens: int) -> int:
+    return rows * cols * 9 // 16 + tokens * cols * 2 + tokens * rows * 2
 
 
 def measured_peaks():
+    """(HBM GB/s, dense BF16 TFLOP/s burst, source) from the driver-written file, else the stated fallback."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as handle:
             data = json.load(handle)
-        return float(data["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
-    return 6650.0, "fallback (earlier measurement on this pool)"
+        return float(data["hbm_gbs"]), float(data["bf16_tflops"]), "measured (MEASURED_PEAKS.json)"
+    return 6650.0, 1590.0, "fallback (earlier measurement on this pool)"
+
+
+DATASHEET_FP4_TFLOPS = 9000.0    # dense NVFP4 per B200; no measured FP4 figure exists on this pool
+
+
+def recorded_traffic():
+    """DRAM bytes of one gate|up + down launch pair from the tracked ncu summary of the decode kernel, or None."""
+    path = os.path.join(ROOT, "profiles", "gemv_kernel_mlp_m8.md")
+    try:
+        with open(path) as handle:
+            match = re.search(r"dram_bytes_per_launch_pair:\s*([0-9.eE+]+)", handle.read())
+        return float(match.group(1)) if match else None
+    except OSError:
+        return None
 
 
 class ClockSampler:
@@ -104,7 +129,8 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------------------------
-# reference arm: the CPU path (C restatement of the reference's Rust, all host threads)
+# the CPU path (C restatement of the reference's Rust, all host threads): the reference arm, and
+# the cpu_baseline of the library arm. One procedure for both.
 # ---------------------------------------------------------------------------------------------
 def cpu_mlp_planes(inter: int):
     """Synthetic gate / up / down planes of an MLP block with intermediate size `inter` (a multiple of 128)."""
@@ -135,24 +161,29 @@ def mlp_bytes(inter: int) -> int:
 REFERENCE_BUDGET_SECONDS = 150.0
 
 
+def cpu_reference_run(warmup: int, steps: int, budget_seconds: float):
+    """`warmup` untimed and `steps` timed CPU steps within the budget; returns (GB/s, seconds per step, sample, threads).
+
+    A step is one pass over one MLP layer, or over a slice of it (the first `inter` intermediate columns of
+    gate, up and down: the same arithmetic per byte) when whole layers would not fit the budget."""
+    import oracle
+    threads = oracle.max_threads()
+    probe_inter = 1024
+    probe = min(cpu_layer_seconds(threads, 2, probe_inter))
+    per_step = budget_seconds / max(warmup + steps, 1)
+    inter = int(min(INTER, max(128, per_step / probe * probe_inter))) // 128 * 128
+    times = cpu_layer_seconds(threads, warmup + steps, inter)[warmup:]
+    seconds = sum(times) / len(times)
+    sample = (f"one MLP layer (M=8, 5120 -> 2x{inter} -> 5120) per step, mean of {steps} steps after {warmup} warm-up"
+              + ("" if inter == INTER else f": the first {inter} of {INTER} intermediate columns, to fit the steps in {budget_seconds:.0f} s"))
+    return mlp_bytes(inter) / seconds / 1e9, seconds, sample, threads
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    import oracle
-    threads = oracle.max_threads()
-    # A step is one pass over a slice of the layer (the first `inter` intermediate columns of gate, up and
-    # down: the same arithmetic per byte), sized so that warm-up plus timed steps fit the budget.
-    probe_inter = 1024
-    probe = min(cpu_layer_seconds(threads, 2, probe_inter))
-    per_step = REFERENCE_BUDGET_SECONDS / max(args.warmup + args.steps, 1)
-    inter = int(min(INTER, max(128, per_step / probe * probe_inter))) // 128 * 128
-    times = cpu_layer_seconds(threads, args.warmup + args.steps, inter)[args.warmup:]
-    seconds = sum(times) / len(times)
-    value = mlp_bytes(inter) / seconds / 1e9
-    sample = (f"one MLP layer (M=8, 5120 -> 2x{inter} -> 5120) per step"
-              + ("" if inter == INTER else f": the first {inter} of {INTER} intermediate columns, to fit {args.warmup}+{args.steps} steps in "
-                 f"{REFERENCE_BUDGET_SECONDS:.0f} s"))
+    value, seconds, sample, threads = cpu_reference_run(args.warmup, args.steps, REFERENCE_BUDGET_SECONDS)
     print(json.dumps({
         "impl": "reference", "metric": "nvfp4_linear_m8_hbm_gbs", "value": value, "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds * 1e3,
@@ -176,124 +207,288 @@ def device_planes(torch, generator, rows, cols, device):
     return codes, scales
 
 
-def build_layers(torch, host, abi, stream, device, world, rank, layers):
+class Context:
+    """What every part of the run shares: device, stream, ranks, timing helpers."""
+
+    def __init__(self, torch, dist, host, abi, device, stream, side, world, rank):
+        self.torch, self.dist, self.host, self.abi = torch, dist, host, abi
+        self.device, self.stream, self.side, self.world, self.rank = device, stream, side, world, rank
+        self.hbm_peak, self.bf16_peak, self.peak_source = measured_peaks()
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def timed(self, body, steps):
+        """Milliseconds for `steps` calls of `body`: CUDA events on the launching stream, barrier and device
+        synchronisation on both sides, the maximum over ranks."""
+        torch = self.torch
+        self.barrier()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            body()
+        end.record()
+        self.barrier()
+        ms = torch.tensor([start.elapsed_time(end)], device=self.device)
+        if self.world > 1:
+            self.dist.all_reduce(ms, op=self.dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    def hbm_entry(self, per_gpu_bytes, total_bytes, ms):
+        achieved = per_gpu_bytes / (ms * 1e-3) / 1e9
+        return {"ms": ms, "gbs": total_bytes / (ms * 1e-3) / 1e9,
+                "roofline": {"bound": "hbm", "achieved": achieved, "peak": self.hbm_peak, "unit": "GB/s",
+                             "frac": achieved / self.hbm_peak, "peak_source": self.peak_source, "traffic": None}}
+
+
+def build_mlp_layers(ctx, layers, keep_first_planes=False):
+    """`layers` distinct MLP layers of this rank's shard; optionally the compact planes of the first, on the host."""
     from augur_v100_b200 import synth
-    generator = torch.Generator(device=device)
-    generator.manual_seed(1234 + rank)
-    inter_shard = INTER // world
-    built = []
-    for _ in range(layers):
-        gc, gs = device_planes(torch, generator, inter_shard, HIDDEN, device)
-        uc, us = device_planes(torch, generator, inter_shard, HIDDEN, device)
+    torch, host, abi = ctx.torch, ctx.host, ctx.abi
+    generator = torch.Generator(device=ctx.device)
+    generator.manual_seed(1234 + ctx.rank)
+    shard = INTER // ctx.world
+    built, first = [], None
+    for index in range(layers):
+        gc, gs = device_planes(torch, generator, shard, HIDDEN, ctx.device)
+        uc, us = device_planes(torch, generator, shard, HIDDEN, ctx.device)
         gate_up = host.Nvfp4Sm100Weight.repack_device_planes(
-            stream, abi.LAYOUT_STREAM_PAIR, inter_shard, HIDDEN, gc, gs, synth.GLOBAL_SCALE, uc, us, synth.GLOBAL_SCALE)
-        dc, ds = device_planes(torch, generator, HIDDEN, inter_shard, device)
+            ctx.stream, abi.LAYOUT_STREAM_PAIR, shard, HIDDEN, gc, gs, synth.GLOBAL_SCALE, uc, us, synth.GLOBAL_SCALE)
+        dc, ds = device_planes(torch, generator, HIDDEN, shard, ctx.device)
         down = host.Nvfp4Sm100Weight.repack_device_planes(
-            stream, abi.LAYOUT_STREAM, HIDDEN, inter_shard, dc, ds, synth.GLOBAL_SCALE)
+            ctx.stream, abi.LAYOUT_STREAM, HIDDEN, shard, dc, ds, synth.GLOBAL_SCALE)
+        if index == 0 and keep_first_planes:
+            first = tuple((c.cpu().numpy(), s.cpu().numpy(), synth.GLOBAL_SCALE) for c, s in ((gc, gs), (uc, us), (dc, ds)))
         built.append((gate_up, down))
         del gc, gs, uc, us, dc, ds
-    return built
+    return built, first
 
 
-def prefill_probe(torch, host, abi, stream, device):
-    """Config 2 on one GPU: M=4096 GEMMs through the tcgen05 path; returns TFLOP/s or an error string."""
+def bits(t):
+    import torch
+    return t.detach().contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def rel_error(y_bits, y64):
+    """max |y - y64| / max(|y64|, 1e-3 rms(y64)): the bound of one GEMM output against the fp64 oracle."""
     from augur_v100_b200 import synth
+    y = synth.bf16_bits_to_f32(y_bits).astype(np.float64).reshape(y64.shape)
+    rms = float(np.sqrt(np.mean(y64 * y64))) or 1.0
+    return float(np.max(np.abs(y - y64) / np.maximum(np.abs(y64), 1e-3 * rms)))
+
+
+def rms_error(y_bits, y64):
+    """max |y - y64| / rms(y64)."""
+    from augur_v100_b200 import synth
+    y = synth.bf16_bits_to_f32(y_bits).astype(np.float64).reshape(y64.shape)
+    rms = float(np.sqrt(np.mean(y64 * y64))) or 1.0
+    return float(np.max(np.abs(y - y64)) / rms)
+
+
+def config0_probe(ctx):
+    """Configuration 0: the single 17408 x 5120 linear at M=8, eight distinct weights in rotation (400 MB, more than L2)."""
+    import oracle
+    from augur_v100_b200 import synth
+    torch, host, abi = ctx.torch, ctx.host, ctx.abi
+    generator = torch.Generator(device=ctx.device)
+    generator.manual_seed(99)
+    rows, cols, count = INTER, HIDDEN, 8
+    plan = host.Plan(ctx.stream, host.gemv_scratch_bytes(rows, cols, TOKENS))
+    x = torch.randn((TOKENS, cols), device=ctx.device, generator=generator).to(torch.bfloat16)
+    projections, first = [], None
+    for index in range(count):
+        codes, scales = device_planes(torch, generator, rows, cols, ctx.device)
+        weight = host.Nvfp4Sm100Weight.repack_device_planes(ctx.stream, abi.LAYOUT_STREAM, rows, cols, codes, scales, synth.GLOBAL_SCALE)
+        if index == 0:
+            first = (codes.cpu().numpy(), scales.cpu().numpy())
+        projections.append(host.Nvfp4Sm100Projection.bind(plan, weight, x))
+        del codes, scales
+
+    def sweep():
+        for projection in projections:
+            projection.submit_for_plan()
+
+    for _ in range(3):
+        sweep()
+    rounds = 50
+    ms = ctx.timed(sweep, rounds) / (rounds * count)
+    entry = ctx.hbm_entry(linear_bytes(rows, cols, TOKENS), linear_bytes(rows, cols, TOKENS), ms)
+    entry["workload"] = f"config0: single NVFP4 linear, M={TOKENS}, K={cols}, N={rows}; {count} distinct weights in rotation"
+    y64 = oracle.linear_f64(first[0], first[1], synth.GLOBAL_SCALE, rows, cols, bits(x), threads=oracle.max_threads())
+    projections[0].submit_for_plan()
+    ctx.stream.synchronize()
+    entry["parity"] = {"rel_error_vs_fp64_oracle": rel_error(bits(projections[0].out), y64), "bound": 2e-2}
+    entry["device_status"] = plan.device_status()
+    del projections
+    plan.close()
+    return entry
+
+
+def prefill_probe(ctx):
+    """Configuration 2 on one GPU: the M=4096 GEMMs through the tcgen05 path. Per shape: the mode that is
+    accurate against the BF16-activation reference (three residual activation terms; the rate counts the
+    useful 2*M*N*K once although three times as many MMAs run) and the plain W4A4 mode (one term), each
+    with a roofline object and a parity check on sampled token rows outside the timed region."""
+    import oracle
+    from augur_v100_b200 import synth
+    torch, host, abi = ctx.torch, ctx.host, ctx.abi
     out = {}
-    try:
-        plan = host.Plan(stream, host.gemm_plan_scratch_bytes())   # room to cut the leftover tiles along k
-        generator = torch.Generator(device=device)
-        generator.manual_seed(77)
-        tokens = 4096
-        for name, rows, cols in (("up_5120x17408", INTER, HIDDEN), ("down_17408x5120", HIDDEN, INTER)):
-            codes, scales = device_planes(torch, generator, rows, cols, device)
-            weight = host.Nvfp4Sm100Weight.repack_device_planes(stream, abi.LAYOUT_TCGEN05, rows, cols, codes, scales,
-                                                                synth.GLOBAL_SCALE)
-            x = torch.randn((tokens, cols), device=device, generator=generator).to(torch.bfloat16)
-            lin = host.Nvfp4Sm100PrefillLinear.bind(plan, weight, x, terms=1, activation_global_scale=2.0 ** -8)
+    plan = host.Plan(ctx.stream, host.gemm_plan_scratch_bytes())   # room to cut the leftover tiles along k
+    generator = torch.Generator(device=ctx.device)
+    generator.manual_seed(77)
+    tokens, sampled, g_a = 4096, 16, 2.0 ** -8
+    pick = np.sort(np.random.default_rng(7).choice(tokens, size=sampled, replace=False))
+    threads = oracle.max_threads()
+    for name, rows, cols in (("up_17408x5120", INTER, HIDDEN), ("down_5120x17408", HIDDEN, INTER)):
+        codes, scales = device_planes(torch, generator, rows, cols, ctx.device)
+        weight = host.Nvfp4Sm100Weight.repack_device_planes(ctx.stream, abi.LAYOUT_TCGEN05, rows, cols, codes, scales,
+                                                            synth.GLOBAL_SCALE)
+        codes_host, scales_host = codes.cpu().numpy(), scales.cpu().numpy()
+        del codes, scales
+        x = torch.randn((tokens, cols), device=ctx.device, generator=generator).to(torch.bfloat16)
+        x_bits = bits(x)[pick]
+        y64_reference = oracle.linear_f64(codes_host, scales_host, synth.GLOBAL_SCALE, rows, cols, x_bits, threads=threads)
+        flops = 2.0 * tokens * rows * cols
+        shape = {"tokens": tokens, "rows": rows, "cols": cols}
+        for key, terms in (("bf16_accurate", 3), ("w4a4", 1)):
+            lin = host.Nvfp4Sm100PrefillLinear.bind(plan, weight, x, terms=terms, activation_global_scale=g_a)
             lin.submit_for_plan()
-            stream.synchronize()
-            if plan.device_status() != 0:
-                out[name] = {"error": f"device status {plan.device_status():#x}"}
-                continue
-            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ctx.stream.synchronize()
+            status = plan.device_status()
             reps = 10
-            start.record()
-            for _ in range(reps):
-                lin.submit_gemm()
-            end.record()
-            end.synchronize()
-            ms = start.elapsed_time(end) / reps
-            out[name] = {"ms": ms, "tflops": 2.0 * tokens * rows * cols / ms / 1e9, "tokens": tokens,
-                         "activation_terms": 1, "finite": bool(torch.isfinite(lin.out.float()).all())}
-            # Three residual activation terms bring the result within 2e-2 of the BF16-activation oracle;
-            # the rate below counts the useful 2*M*N*K once, although three times as many MMAs run.
+            ms_gemm = ctx.timed(lin.submit_gemm, reps) / reps
+            ms_all = ctx.timed(lin.submit_for_plan, reps) / reps
+            a_codes, a_scales = lin.staged_planes()
+            a64 = oracle.act_dequant_f64(np.ascontiguousarray(a_codes[:, pick]), np.ascontiguousarray(a_scales[:, pick]),
+                                         g_a, sampled, cols, terms)
+            y64 = oracle.linear_f64_xf64(codes_host, scales_host, synth.GLOBAL_SCALE, rows, cols, a64, threads=threads)
+            got = bits(lin.out[torch.from_numpy(pick).to(ctx.device)])
+            tflops = flops / ms_all / 1e9
+            shape[key] = {
+                "activation_terms": terms, "ms": ms_all, "ms_gemm_only": ms_gemm, "tflops": tflops,
+                "tflops_gemm_only": flops / ms_gemm / 1e9,
+                "note": "useful 2*M*N*K per second, activation quantiser launch included" + (
+                    "; the tensor pipe runs three MMAs per useful one" if terms == 3 else
+                    "; plain W4A4: about 10 % rms from the BF16-activation reference, reported as the kernel's raw rate only"),
+                "roofline": {"bound": "tensor", "achieved": tflops, "peak": DATASHEET_FP4_TFLOPS, "unit": "TFLOP/s",
+                             "frac": tflops / DATASHEET_FP4_TFLOPS,
+                             "peak_source": "datasheet dense NVFP4 (no measured FP4 peak on this pool)",
+                             "frac_of_measured_bf16_peak": tflops / ctx.bf16_peak, "traffic": None},
+                "parity": {"sampled_token_rows": sampled,
+                           "rel_error_vs_fp64_oracle_same_staged_activations": rel_error(got, y64),
+                           "max_error_over_rms_vs_bf16_activation_oracle": rms_error(got, y64_reference),
+                           "bound": 2e-2},
+                "device_status": status,
+            }
             del lin
-            lin3 = host.Nvfp4Sm100PrefillLinear.bind(plan, weight, x, terms=3, activation_global_scale=2.0 ** -8)
-            lin3.submit_for_plan()
-            stream.synchronize()
-            start.record()
-            for _ in range(reps):
-                lin3.submit_gemm()
-            end.record()
-            end.synchronize()
-            ms3 = start.elapsed_time(end) / reps
-            out[name]["three_terms"] = {"ms": ms3, "tflops_useful": 2.0 * tokens * rows * cols / ms3 / 1e9}
-            del weight, lin3, x, codes, scales
-        plan.close()
-    except Exception as error:  # reported, never hidden
-        out["error"] = repr(error)
+        out[name] = shape
+        del weight, x
+    plan.close()
     return out
 
 
-def prefill_mlp_probe(torch, host, abi, stream, device, world, rank, tokens, chunk, terms):
-    """Config 4 (long-prefill chunked MLP, tensor-parallel): returns whole-job TFLOP/s of useful 2*M*N*K."""
-    import torch.distributed as dist
-
+def prefill_mlp_probe(ctx, tokens, chunk, terms):
+    """Configuration 4 (long-prefill chunked MLP, tensor-parallel): whole-job TFLOP/s of the useful 2*M*N*K."""
     from augur_v100_b200 import synth, tp
-    generator = torch.Generator(device=device)
-    generator.manual_seed(4321 + rank)
-    shard = INTER // world
-    gc, gs = device_planes(torch, generator, shard, HIDDEN, device)
-    uc, us = device_planes(torch, generator, shard, HIDDEN, device)
+    torch, host, abi = ctx.torch, ctx.host, ctx.abi
+    generator = torch.Generator(device=ctx.device)
+    generator.manual_seed(4321 + ctx.rank)
+    shard = INTER // ctx.world
+    gc, gs = device_planes(torch, generator, shard, HIDDEN, ctx.device)
+    uc, us = device_planes(torch, generator, shard, HIDDEN, ctx.device)
 
     def interleave(gate_plane, up_plane):   # 16 gate rows, then the matching 16 up rows
         width = gate_plane.shape[1]
         return torch.stack([gate_plane.view(shard // 16, 16, width), up_plane.view(shard // 16, 16, width)], dim=1).reshape(2 * shard, width).contiguous()
 
-    gate_up = host.Nvfp4Sm100Weight.repack_device_planes(stream, abi.LAYOUT_TCGEN05, 2 * shard, HIDDEN, interleave(gc, uc),
+    gate_up = host.Nvfp4Sm100Weight.repack_device_planes(ctx.stream, abi.LAYOUT_TCGEN05, 2 * shard, HIDDEN, interleave(gc, uc),
                                                          interleave(gs, us), synth.GLOBAL_SCALE)
     gate_up.global_scale_b = synth.GLOBAL_SCALE
-    dc, ds = device_planes(torch, generator, HIDDEN, shard, device)
-    down = host.Nvfp4Sm100Weight.repack_device_planes(stream, abi.LAYOUT_TCGEN05, HIDDEN, shard, dc, ds, synth.GLOBAL_SCALE)
+    dc, ds = device_planes(torch, generator, HIDDEN, shard, ctx.device)
+    down = host.Nvfp4Sm100Weight.repack_device_planes(ctx.stream, abi.LAYOUT_TCGEN05, HIDDEN, shard, dc, ds, synth.GLOBAL_SCALE)
     del gc, gs, uc, us, dc, ds
-    plan = host.Plan(stream, host.gemm_plan_scratch_bytes())   # room to cut the leftover tiles along k
-    x = torch.randn((tokens, HIDDEN), device=device, generator=generator).to(torch.bfloat16)
-    block = tp.TensorParallelPrefillMlp(plan, gate_up, down, x, world, chunk_tokens=chunk, terms=terms,
+    plan = host.Plan(ctx.stream, host.gemm_plan_scratch_bytes())   # room to cut the leftover tiles along k
+    x = torch.randn((tokens, HIDDEN), device=ctx.device, generator=generator).to(torch.bfloat16)
+    block = tp.TensorParallelPrefillMlp(plan, gate_up, down, x, ctx.world, chunk_tokens=chunk, terms=terms,
                                         input_global_scale=2.0 ** -8, intermediate_global_scale=2.0 ** -6)
     block.submit()
-    stream.synchronize()
-    if plan.device_status() != 0:
-        return {"error": f"device status {plan.device_status():#x}"}
-    if world > 1:
-        dist.barrier()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ctx.stream.synchronize()
+    status = plan.device_status()
     reps = 3
-    start.record()
-    for _ in range(reps):
-        block.submit()
-    end.record()
-    end.synchronize()
-    ms = torch.tensor([start.elapsed_time(end) / reps], device=device)
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    ms = float(ms.item())
+    ms = ctx.timed(block.submit, reps) / reps
     flops = 2.0 * tokens * 3 * HIDDEN * INTER
-    result = {"workload": f"chunked MLP, M={tokens} in chunks of {chunk}, hidden {HIDDEN}, intermediate {INTER}, tp{world}, "
-                          "per-chunk NCCL all-reduce overlapped with the next chunk",
-              "ms": ms, "tflops_useful": flops / ms / 1e9, "activation_terms": terms,
+    result = {"ms": ms, "tflops_useful": flops / ms / 1e9, "activation_terms": terms, "device_status": status,
               "finite": bool(torch.isfinite(block.out.float()).all())}
+    del block
     plan.close()
     return result
+
+
+SWEEP_LAYERS = 64
+SWEEP_SHAPES = ((10240, 5120, "column"), (5120, 5120, "column"), (5120, 10240, "row"))   # rows, cols, how it shards
+
+
+def sweep_probe(ctx, exchange):
+    """Configuration 3: 64 layers, each the MLP block plus the projections 5120 -> 10240, 5120 -> 5120 and
+    10240 -> 5120, all NVFP4 at M=8. With N > 1 the first two are column-parallel (row slices, outputs stay
+    sharded), the third is row-parallel (k slices) with the all-reduce inside its launch, the MLP as in the
+    headline. Reports the weight bytes streamed per verify pass, whole job."""
+    from augur_v100_b200 import synth, tp
+    torch, host, abi = ctx.torch, ctx.host, ctx.abi
+    world = ctx.world
+    generator = torch.Generator(device=ctx.device)
+    generator.manual_seed(555 + ctx.rank)
+    scratch = max([host.mlp_scratch_bytes(HIDDEN, INTER // world)] +
+                  [2 * host.gemv_scratch_bytes(rows // world if how == "column" else rows,
+                                               cols if how == "column" else cols // world, TOKENS) for rows, cols, how in SWEEP_SHAPES])
+    plan = host.Plan(ctx.stream, scratch)
+    x = torch.randn((TOKENS, HIDDEN), device=ctx.device, generator=generator).to(torch.bfloat16)
+    wide = torch.randn((TOKENS, 10240 // world), device=ctx.device, generator=generator).to(torch.bfloat16)
+    mlp_layers, _ = build_mlp_layers(ctx, SWEEP_LAYERS)
+    outs = [torch.empty((TOKENS, HIDDEN), dtype=torch.bfloat16, device=ctx.device) for _ in range(2)]
+    programs = []
+    for index, (gate_up, down) in enumerate(mlp_layers):
+        layer = []
+        for rows, cols, how in SWEEP_SHAPES:
+            r, c = (rows // world, cols) if how == "column" else (rows, cols // world)
+            codes, scales = device_planes(torch, generator, r, c, ctx.device)
+            weight = host.Nvfp4Sm100Weight.repack_device_planes(ctx.stream, abi.LAYOUT_STREAM, r, c, codes, scales, synth.GLOBAL_SCALE)
+            del codes, scales
+            projection = host.Nvfp4Sm100Projection.bind(plan, weight, x if how == "column" else wide)
+            if how == "row" and exchange is not None:
+                projection = tp.RowParallelLinear(projection, exchange)
+            layer.append(projection)
+        program = host.Nvfp4Sm100FfnProgram.bind(plan, gate_up, down, x, out=outs[index % 2])
+        if exchange is not None:
+            program = tp.FusedExchangeProgram(program, exchange)
+        layer.append(program)
+        programs.append(layer)
+    use_nccl = world > 1 and exchange is None
+
+    def verify_pass():
+        for layer in programs:
+            for member in layer:
+                member.submit_for_plan()
+                if use_nccl and member is not layer[0] and member is not layer[1]:
+                    ctx.dist.all_reduce(member.out)
+
+    for _ in range(3):
+        verify_pass()
+    reps = 10
+    launches_before = host.launch_count()
+    ms = ctx.timed(verify_pass, reps) / reps
+    launches = (host.launch_count() - launches_before) // reps
+    weights_total = SWEEP_LAYERS * (3 * HIDDEN * INTER + sum(rows * cols for rows, cols, _ in SWEEP_SHAPES)) * 9 // 16
+    entry = ctx.hbm_entry(weights_total // world, weights_total, ms)
+    entry.update({"workload": f"config3: {SWEEP_LAYERS} layers x (MLP 5120 -> 2x17408 -> 5120, 5120 -> 10240, 5120 -> 5120, 10240 -> 5120), "
+                              f"M={TOKENS}, tp{world}", "weight_bytes_per_verify_pass": weights_total,
+                  "weight_bytes_per_gpu": weights_total // world, "launches_per_pass": launches,
+                  "device_status": plan.device_status()})
+    del programs, mlp_layers
+    plan.close()
+    return entry
 
 
 def run_library(args):
@@ -316,11 +511,12 @@ def run_library(args):
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=device)
 
-    # Everything runs on one non-default stream, so that a step can also be captured into a CUDA graph.
+    # Everything runs on one non-default stream, so that a pass can also be captured into a CUDA graph.
     side = torch.cuda.Stream(device)
     torch.cuda.set_stream(side)
     stream = host.Stream(local, side)
-    layers = build_layers(torch, host, abi, stream, device, world, rank, LAYERS)
+    ctx = Context(torch, dist, host, abi, device, stream, side, world, rank)
+    layers, first_planes = build_mlp_layers(ctx, LAYERS, keep_first_planes=(world == 1 and rank == 0))
     plan = host.Plan(stream, host.mlp_scratch_bytes(HIDDEN, INTER // world))
     x_host = torch.randn((TOKENS, HIDDEN), dtype=torch.float32).mul_(8.0).to(torch.bfloat16).pin_memory()
     y_host = torch.empty((TOKENS, HIDDEN), dtype=torch.bfloat16).pin_memory()
@@ -328,52 +524,45 @@ def run_library(args):
     outs = [torch.empty((TOKENS, HIDDEN), dtype=torch.bfloat16, device=device) for _ in range(2)]
     programs = [host.Nvfp4Sm100FfnProgram.bind(plan, gate_up, down, x, out=outs[index % 2])
                 for index, (gate_up, down) in enumerate(layers)]
+    x1 = x[:1].contiguous()
+    outs1 = [torch.empty((1, HIDDEN), dtype=torch.bfloat16, device=device) for _ in range(2)]
+    programs_m1 = [host.Nvfp4Sm100FfnProgram.bind(plan, gate_up, down, x1, out=outs1[index % 2])
+                   for index, (gate_up, down) in enumerate(layers)]
 
     # With more than one rank the all-reduce is fused into the down launch (peer stores over NVLink);
     # --allreduce nccl, or a failed symmetric-memory set-up (reported in the line), uses NCCL instead.
-    exchange_note = None
+    exchange, exchange_note = None, None
     if world > 1 and args.allreduce == "fused":
         from augur_v100_b200 import tp
         failure = None
         try:
             exchange = tp.ExchangeBuffers(HIDDEN, rank, world)
             fused_programs = [tp.FusedExchangeProgram(program, exchange) for program in programs]
+            fused_m1 = [tp.FusedExchangeProgram(program, exchange) for program in programs_m1]
         except Exception as error:  # reported in the line, never hidden
             failure = repr(error)
         agree = torch.tensor([0 if failure else 1], device=device)
         dist.all_reduce(agree, op=dist.ReduceOp.MIN)
         if int(agree.item()) == 1:
-            programs = fused_programs
-            exchange_note = "fused into the down launch: f32 tiles stored to every rank over NVLink, flags, rank-order sum"
+            programs, programs_m1 = fused_programs, fused_m1
+            exchange_note = ("fused into the down launch: f32 tiles stored to every rank over NVLink, flags, rank-order sum; "
+                             "the launches count the exchange sequence on the device")
         else:
+            exchange = None
             exchange_note = f"NCCL bf16 8x5120 per layer (fused exchange set-up failed on some rank: {failure})"
     elif world > 1:
         exchange_note = "NCCL bf16 8x5120 per layer"
-    use_nccl = world > 1 and not (exchange_note or "").startswith("fused")
+    use_nccl = world > 1 and exchange is None
 
-    def step():
+    def one_pass():
         for index, program in enumerate(programs):
             program.submit_for_plan()
             if use_nccl:
                 dist.all_reduce(outs[index % 2])
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(body, steps):
-        barrier()
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for _ in range(steps):
-            body()
-        end.record()
-        barrier()
-        ms = torch.tensor([start.elapsed_time(end)], device=device)
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
+    def step():
+        for _ in range(PASSES):
+            one_pass()
 
     sampler = ClockSampler(local)
     if rank == 0:
@@ -382,74 +571,140 @@ def run_library(args):
         step()
     launches_before = host.launch_count()
     sampler.mark_begin()
-    total_ms = timed(step, args.steps)
+    total_ms = ctx.timed(step, args.steps)
     launches = host.launch_count() - launches_before
 
-    def e2e_step():
+    # End to end: every pass copies its activations in from pinned host memory and its result back.
+    def e2e_pass():
         x.copy_(x_host, non_blocking=True)
-        step()
+        one_pass()
         y_host.copy_(outs[(LAYERS - 1) % 2], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        side.synchronize()
+
+    def e2e_step(body):
+        def run():
+            for _ in range(PASSES):
+                body()
+        return run
 
     for _ in range(3):
-        e2e_step()
-    e2e_ms = timed(e2e_step, args.steps)
-    e2e_submission, e2e_direct_ms = "direct calls of the public API", None
-    if world == 1:
+        e2e_pass()
+    e2e_direct_ms = ctx.timed(e2e_step(e2e_pass), args.steps)
+    e2e_ms, e2e_submission = e2e_direct_ms, "direct calls of the public API"
+    graph_ok = torch.tensor([1], device=device)
+    graph = None
+    if not use_nccl:
         # The way a serving loop drives it (the reference captures its programs into CUDA graphs,
-        # crates/augur-backend/src/cuda_qwen35_prefill_cublas/qpn.rs:507-515): the same calls captured once, replayed per step.
+        # crates/augur-backend/src/cuda_qwen35_prefill_cublas/qpn.rs:507-515): the same calls captured once, replayed per pass.
         try:
             reference_bits = y_host.view(torch.int16).clone()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=side):
                 x.copy_(x_host, non_blocking=True)
-                step()
+                one_pass()
                 y_host.copy_(outs[(LAYERS - 1) % 2], non_blocking=True)
-
-            def e2e_graph_step():
-                graph.replay()
-                side.synchronize()
-
-            y_host.zero_()
-            for _ in range(3):
-                e2e_graph_step()
-            if not torch.equal(y_host.view(torch.int16), reference_bits):
-                raise RuntimeError("graph replay and direct calls disagree")
-            graph_ms = timed(e2e_graph_step, args.steps)
-            e2e_direct_ms, e2e_ms = e2e_ms, graph_ms
-            e2e_submission = "CUDA graph replay of the step's public-API calls (H2D copy, all launches, D2H copy)"
         except Exception as error:  # reported, never hidden
+            graph_ok[0] = 0
             e2e_submission = f"direct calls of the public API (graph capture failed: {error!r})"
+    else:
+        graph_ok[0] = 0
+    if world > 1:
+        dist.all_reduce(graph_ok, op=dist.ReduceOp.MIN)
+    if int(graph_ok.item()) == 1:
+        def e2e_graph_pass():
+            graph.replay()
+            side.synchronize()
+
+        y_host.zero_()
+        for _ in range(3):
+            e2e_graph_pass()
+        same = torch.tensor([1 if torch.equal(y_host.view(torch.int16), reference_bits) else 0], device=device)
+        if world > 1:
+            dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        if int(same.item()) == 1:
+            e2e_ms = ctx.timed(e2e_step(e2e_graph_pass), args.steps)
+            e2e_submission = "CUDA graph replay of one pass's public-API calls (H2D copy, all launches, D2H copy), one replay per pass"
+        else:
+            e2e_submission = "direct calls of the public API (graph replay and direct calls disagreed)"
     sampler.mark_end()
     clocks = sampler.stop() if rank == 0 else None
     status = plan.device_status()
     if status != 0:
         raise SystemExit(f"device status word {status:#x}")
 
-    prefill_mlp = None
-    if args.prefill_mlp:
-        # every rank takes part (collectives inside); the decode layers are released first
-        del programs, layers
+    extras = {}
+    # M=1 on the same layers (decode), all ranks
+    def m1_pass():
+        for index, program in enumerate(programs_m1):
+            program.submit_for_plan()
+            if use_nccl:
+                dist.all_reduce(outs1[index % 2])
+
+    for _ in range(3):
+        m1_pass()
+    reps = 50
+    m1_ms = ctx.timed(m1_pass, reps) / (reps * LAYERS)
+    per_gpu_m1 = 3 * HIDDEN * (INTER // world) * 9 // 16 + 2 * HIDDEN * 2
+    extras["config1_m1"] = ctx.hbm_entry(per_gpu_m1, layer_bytes(1), m1_ms)
+    extras["config1_m1"]["workload"] = f"config1 at M=1: the same {LAYERS} layers, one token row; ms per layer"
+
+    # parity of the timed programs against the CPU oracle (one GPU: the first layer, both token counts)
+    parity = None
+    if first_planes is not None:
+        import oracle
+        gate, up, down = first_planes
+        parity = {"bound": 2e-2}
+        for label, program, source in (("m8", programs[0], x), ("m1", programs_m1[0], x1)):
+            program.submit_for_plan()
+            stream.synchronize()
+            h64, y64 = oracle.mlp_f64(gate, up, down, HIDDEN, INTER, bits(source), threads=oracle.max_threads())
+            h_bits = bits(program.intermediate)
+            y64_from_h = oracle.linear_f64(down[0], down[1], down[2], HIDDEN, INTER, h_bits, threads=oracle.max_threads())
+            parity[label] = {"gate_up_rel_error_vs_fp64_oracle": rel_error(h_bits, h64),
+                             "down_rel_error_vs_fp64_oracle": rel_error(bits(program.out), y64_from_h),
+                             "block_max_error_over_rms": rms_error(bits(program.out), y64)}
+        worst = max(max(v.values()) for k, v in parity.items() if k != "bound")
+        if worst > 2e-2:
+            raise SystemExit(f"parity of the timed MLP programs failed: {parity}")
+
+    del programs, programs_m1, layers, graph
+    torch.cuda.empty_cache()
+    if not args.headline_only:
+        try:
+            extras["config3_sweep"] = sweep_probe(ctx, exchange)
+        except Exception as error:  # reported, never hidden
+            extras["config3_sweep"] = {"error": repr(error)}
         torch.cuda.empty_cache()
-        prefill_mlp = {}
-        for terms in (1, 3):
-            prefill_mlp[f"terms_{terms}"] = prefill_mlp_probe(torch, host, abi, stream, device, world, rank,
-                                                              args.prefill_mlp_tokens, 4096, terms)
-        programs, layers = [], []
+        try:
+            extras["config4_prefill_mlp"] = {
+                "workload": f"config4: chunked MLP, M={args.prefill_mlp_tokens} in chunks of 4096, hidden {HIDDEN}, intermediate {INTER}, "
+                            f"tp{world}, per-chunk NCCL all-reduce overlapped with the next chunk",
+                "bf16_accurate": prefill_mlp_probe(ctx, args.prefill_mlp_tokens, 4096, 3),
+                "w4a4": prefill_mlp_probe(ctx, args.prefill_mlp_tokens, 4096, 1)}
+        except Exception as error:
+            extras["config4_prefill_mlp"] = {"error": repr(error)}
+        torch.cuda.empty_cache()
+        if world == 1:
+            for key, probe in (("config0", config0_probe), ("config2_prefill", prefill_probe)):
+                try:
+                    extras[key] = probe(ctx)
+                except Exception as error:
+                    extras[key] = {"error": repr(error)}
+                torch.cuda.empty_cache()
 
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
 
-    step_bytes = LAYERS * layer_bytes()
+    pass_bytes = LAYERS * layer_bytes()
     ms_per_step = total_ms / args.steps
-    value = step_bytes / (ms_per_step * 1e-3) / 1e9
-    e2e_value = step_bytes / (e2e_ms / args.steps * 1e-3) / 1e9
-    peak, peak_source = measured_peaks()
+    ms_per_pass = ms_per_step / PASSES
+    value = pass_bytes / (ms_per_pass * 1e-3) / 1e9
+    e2e_pass_ms = e2e_ms / args.steps / PASSES
     # Per GPU, per layer: the two launches of the streaming kernel read this rank's weight shard once.
     per_gpu_layer_bytes = 3 * HIDDEN * (INTER // world) * 9 // 16 + 2 * TOKENS * HIDDEN * 2
-    launch_pair_ms = ms_per_step / LAYERS
+    launch_pair_ms = ms_per_pass / LAYERS
     achieved = per_gpu_layer_bytes / (launch_pair_ms * 1e-3) / 1e9
     line = {
         "metric": "nvfp4_linear_m8_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
@@ -457,34 +712,28 @@ def run_library(args):
         "vs_baseline": None, "dtype": "bf16 x bf16 -> f32 (E2M1 codes as BF16 fragments on mma.sync, E4M3 block scales applied in f32)",
         "data": "synthetic",
         "config": {"workload": f"config1: NVFP4 MLP block (gate|up+SwiGLU, down), M={TOKENS}, hidden {HIDDEN}, "
-                               f"intermediate {INTER}, {LAYERS} distinct layers per step",
-                   "l2": f"inputs larger than L2: {LAYERS * 3 * HIDDEN * INTER * 9 // 16 // world} weight bytes per GPU per step",
+                               f"intermediate {INTER}; one step = {PASSES} passes over {LAYERS} distinct layers",
+                   "passes_per_step": PASSES, "layers_per_pass": LAYERS, "ms_per_pass": ms_per_pass,
+                   "l2": f"inputs larger than L2: {LAYERS * 3 * HIDDEN * INTER * 9 // 16 // world} weight bytes per GPU per pass",
                    "parallelism": f"tp{world}" if world > 1 else "single", "all_reduce": exchange_note},
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": ctx.hbm_peak, "unit": "GB/s", "frac": achieved / ctx.hbm_peak,
                      # dram__bytes_read.sum + dram__bytes_write.sum of one gate|up launch plus one down launch
-                     # (single GPU, full shapes), from the ncu capture summarised under profiles/
-                     "traffic": 155.05e6 if world == 1 else None, "traffic_unit": "bytes per launch pair (ncu)",
-                     "peak_source": peak_source,
+                     # (single GPU, full shapes) as recorded in the tracked ncu summary of this kernel
+                     "traffic": recorded_traffic() if world == 1 else None, "traffic_unit": "bytes per launch pair (ncu)",
+                     "peak_source": ctx.peak_source,
                      "kernel": "gemv_kernel (gate|up launch + down launch per layer; with N>1 the interval also holds the all-reduce)",
                      "bytes_per_launch_pair": per_gpu_layer_bytes, "ms_per_launch_pair": launch_pair_ms},
-        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": TOKENS * HIDDEN * 2,
-                "d2h_bytes_per_step": TOKENS * HIDDEN * 2, "ms_per_step": e2e_ms / args.steps,
-                "submission": e2e_submission,
-                "direct_calls_value": None if e2e_direct_ms is None else step_bytes / (e2e_direct_ms / args.steps * 1e-3) / 1e9},
-        "gpu_launches": launches, "clocks": clocks,
+        "e2e": {"value": pass_bytes / (e2e_pass_ms * 1e-3) / 1e9, "unit": "GB/s",
+                "h2d_bytes_per_step": PASSES * TOKENS * HIDDEN * 2, "d2h_bytes_per_step": PASSES * TOKENS * HIDDEN * 2,
+                "ms_per_step": e2e_ms / args.steps, "submission": e2e_submission,
+                "direct_calls_value": pass_bytes / (e2e_direct_ms / args.steps / PASSES * 1e-3) / 1e9},
+        "gpu_launches": launches, "clocks": clocks, "parity": parity,
     }
+    line.update(extras)
     if world == 1:
-        import oracle
-        threads = oracle.max_threads()
-        seconds = min(cpu_layer_seconds(threads, 2))
-        line["cpu_baseline"] = {"value": layer_bytes() / seconds / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
-                                "sample": "one full MLP layer (M=8), best of 2, C restatement of the reference CPU path"}
-        if not args.no_prefill:
-            del programs, layers
-            torch.cuda.empty_cache()
-            line["prefill"] = prefill_probe(torch, host, abi, stream, device)
-    if prefill_mlp is not None:
-        line["prefill_mlp"] = prefill_mlp
+        cpu_value, _, sample, threads = cpu_reference_run(1, 5, 20.0)
+        line["cpu_baseline"] = {"value": cpu_value, "unit": "GB/s", "cores": threads, "kind": "port",
+                                "sample": sample + "; C restatement of the reference CPU path"}
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -493,19 +742,20 @@ def run_library(args):
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=1000)
+    parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", choices=["library", "reference"], default="library")
-    parser.add_argument("--no-prefill", action="store_true", help="skip the M=4096 tcgen05 probe at N=1")
-    parser.add_argument("--prefill-mlp", action="store_true",
-                        help="also time the chunked tensor-parallel prefill MLP (reported under prefill_mlp)")
+    parser.add_argument("--headline-only", action="store_true",
+                        help="time configuration 1 only (skips the other configurations' entries)")
     parser.add_argument("--prefill-mlp-tokens", type=int, default=32768)
     parser.add_argument("--allreduce", choices=["fused", "nccl"], default="fused",
                         help="N>1: all-reduce inside the down launch over peer memory, or NCCL on the BF16 partials")
     parser.add_argument("--layers", type=int, default=LAYERS,
-                        help="distinct layers streamed per step (smaller values are for profiler captures only)")
+                        help="distinct layers streamed per pass (smaller values are for profiler captures only)")
+    parser.add_argument("--passes", type=int, default=PASSES, help="passes over the layers per step")
     args = parser.parse_args()
     globals()["LAYERS"] = args.layers
+    globals()["PASSES"] = args.passes
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -363,9 +363,17 @@ augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_norm_group_prevalida
  * tile, each value paired with `sequence` as its flag, into every other rank's buffer over
  * NVLink, waits (bounded) for the same group of every other rank in its own buffer and writes
  * bf16(sum over ranks, in rank order) to down.output: all ranks end up with the same
- * full-width [tokens][rows] result and no collective is launched. `sequence` starts at 1 and grows by exactly 1 with every submit,
- * in step on all ranks. All ranks' kernels must be able to run at the same time (one process
- * and one GPU per rank). A wait that runs out sets the plan's status word to 0x203.
+ * full-width [tokens][rows] result and no collective is launched. `sequence` = 0 lets the
+ * launches count their own sequence in the last 256 bytes of this rank's exchange buffer
+ * (zero-filled with the rest): nothing that changes from submit to submit is then part of the
+ * launch parameters, so a program captured into a CUDA graph can be replayed, which is how the
+ * reference's serving loop drives its programs
+ * (crates/augur-backend/src/cuda_qwen35_prefill_cublas/qpn.rs:507-515). A non-zero `sequence`
+ * is counted by the caller instead: it starts at 1 and grows by exactly 1 with every submit
+ * that uses these buffers, in step on all ranks (1, ..., 0xFFFFFFFE, 1, ...); the two ways of
+ * counting are not mixed on one set of buffers. All ranks' kernels must be able to run at the
+ * same time (one process and one GPU per rank). A wait that runs out sets the plan's status
+ * word to 0x203.
  * Peer buffers cannot be inspected from this process: preflight checks them for alignment,
  * size and overlap only. */
 #define AUGUR_NVFP4_SM100_MAX_TP_RANKS 8
@@ -391,6 +399,29 @@ augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_mlp_tp_preflight_v1(
 augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_mlp_tp_prevalidated_submit_v1(
     int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
     const augur_cuda_nvfp4_sm100_mlp_tp_args_v1* args);
+
+/* A single row-parallel small-token linear with the same exchange: every rank holds a k-slice of the
+ * weight (`linear`, epilogue LINEAR_BF16) and its matching slice of the activations, and every rank
+ * ends up with bf16(sum over ranks) in linear.output. For the projections outside the MLP block
+ * (attention / GDN output projections). No counterpart in the reference. */
+typedef struct augur_cuda_nvfp4_sm100_gemv_tp_args_v1 {
+    uint32_t abi_version;
+    uint32_t struct_size;
+    augur_cuda_nvfp4_sm100_gemv_args_v1 linear;
+    augur_cuda_device_ptr_t exchange[AUGUR_NVFP4_SM100_MAX_TP_RANKS];  /* entries >= world are 0 */
+    uint64_t exchange_len_bytes;
+    uint32_t world;
+    uint32_t rank;
+    uint32_t sequence;                    /* as in mlp_tp_args_v1 */
+    uint32_t reserved;
+} augur_cuda_nvfp4_sm100_gemv_tp_args_v1;
+
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_tp_preflight_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_gemv_tp_args_v1* args);
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_tp_prevalidated_submit_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_gemv_tp_args_v1* args);
 
 /* ---- prefill: activation quantiser + tcgen05 block-scaled GEMM --------------- */
 /* Replaces the W4A4 interstage quantiser (augur_cuda_runtime.h:6983 ff.;

@@ -216,17 +216,21 @@ def test_null_and_foreign_handles_are_rejected():
 def test_exchange_extent_and_tp_argument_checks():
     lib = abi.lib()
     out = ctypes.c_uint64()
-    # [2 parities][world][groups] tiles of 256 {value, flag} pairs
+    # [2 parities][world][groups] tiles of 256 {value, flag} pairs, then 256 bytes for the device-side sequence counter
     assert lib.augur_cuda_nvfp4_sm100_mlp_tp_exchange_extent_host_v1(5120, 8, ctypes.byref(out)).status == abi.STATUS_OK
-    assert out.value == 2 * 8 * 160 * 2048
+    assert out.value == 2 * 8 * 160 * 2048 + 256
     assert lib.augur_cuda_nvfp4_sm100_mlp_tp_exchange_extent_host_v1(64, 2, ctypes.byref(out)).status == abi.STATUS_OK
-    assert out.value == 2 * 2 * 2 * 2048
+    assert out.value == 2 * 2 * 2 * 2048 + 256
     for rows, world in ((5120, 0), (5120, 9), (5100, 2), (0, 2)):
         assert lib.augur_cuda_nvfp4_sm100_mlp_tp_exchange_extent_host_v1(rows, world, ctypes.byref(out)).status == abi.STATUS_INVALID_ARGUMENT
     # without a stream and a plan nothing is looked at, on either entry
     args = abi.header(abi.MlpTpArgs)
     assert lib.augur_cuda_nvfp4_sm100_mlp_tp_preflight_v1(0, None, None, ctypes.byref(args)).status == abi.STATUS_INVALID_ARGUMENT
     assert lib.augur_cuda_nvfp4_sm100_mlp_tp_prevalidated_submit_v1(0, None, None, ctypes.byref(args)).status == abi.STATUS_INVALID_ARGUMENT
+    single = abi.header(abi.GemvTpArgs)
+    assert ctypes.sizeof(abi.GemvTpArgs) == 184
+    assert lib.augur_cuda_nvfp4_sm100_gemv_tp_preflight_v1(0, None, None, ctypes.byref(single)).status == abi.STATUS_INVALID_ARGUMENT
+    assert lib.augur_cuda_nvfp4_sm100_gemv_tp_prevalidated_submit_v1(0, None, None, ctypes.byref(single)).status == abi.STATUS_INVALID_ARGUMENT
 
 
 def test_scratch_extents():

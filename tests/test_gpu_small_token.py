@@ -390,12 +390,14 @@ def test_mlp_program_cross_validation(ctx):
     assert host.launch_count() == launches
 
 
-def test_exchange_reduce_with_eight_sources_on_one_gpu(ctx):
+@pytest.mark.parametrize("counted_on", ["host", "device"])
+def test_exchange_reduce_with_eight_sources_on_one_gpu(ctx, counted_on):
     # The tensor-parallel down launch for rank 0 of 8, on one GPU: the tiles of ranks 1..7 are written into rank 0's
     # exchange buffer from the host beforehand (so nothing waits), the launch pushes its own tiles into eight
     # buffers, and its reduce step must deliver bf16(own + the seven others, in rank order) for every row group.
     host, torch = ctx["host"], ctx["torch"]
-    hidden, inter, tokens, world, seq = 256, 512, 8, 8, 3
+    # sequence 3 passed by the host, or the first launch of a fresh buffer counting for itself (sequence 1)
+    hidden, inter, tokens, world, seq = 256, 512, 8, 8, (3 if counted_on == "host" else 1)
     gate, up, down, gate_up, down_w = _mlp_weights(ctx, hidden, inter, seed=21)
     x_bits = synth.f32_to_bf16_bits(np.random.default_rng(21).standard_normal((tokens, hidden)).astype(np.float32) * 8.0)
     x = torch_bf16_from_bits(x_bits, ctx["device"])
@@ -415,14 +417,15 @@ def test_exchange_reduce_with_eight_sources_on_one_gpu(ctx):
                 row = group * 32 + (i >> 2) * 16 + g + ((i >> 1) & 1) * 8
                 image[seq & 1, source, group, lane, i // 2, (i & 1) * 2] = others[source, token, row].view(np.uint32)
                 image[seq & 1, source, group, lane, i // 2, (i & 1) * 2 + 1] = seq
-    assert image.nbytes == extent.value
+    assert image.nbytes + 256 == extent.value     # the tiles, then the sequence counter
     buffers = [torch.zeros(extent.value, dtype=torch.uint8, device=ctx["device"]) for _ in range(world)]
-    buffers[0].copy_(torch.from_numpy(image.view(np.uint8).reshape(-1)))
+    buffers[0][:image.nbytes].copy_(torch.from_numpy(image.view(np.uint8).reshape(-1)))
     args = abi.header(abi.MlpTpArgs)
     args.gate_up, args.down = program.args.gate_up, program.args.down
     for r in range(world):
         args.exchange[r] = buffers[r].data_ptr()
-    args.exchange_len_bytes, args.world, args.rank, args.sequence = extent.value, world, 0, seq
+    args.exchange_len_bytes, args.world, args.rank = extent.value, world, 0
+    args.sequence = seq if counted_on == "host" else 0
     s, plan, lib = ctx["stream"], ctx["plan"], abi.lib()
     assert lib.augur_cuda_nvfp4_sm100_mlp_tp_preflight_v1(s.ordinal, s.handle, plan.handle, byref(args)).status == 0
     assert lib.augur_cuda_nvfp4_sm100_mlp_tp_prevalidated_submit_v1(s.ordinal, s.handle, plan.handle, byref(args)).status == 0
@@ -431,11 +434,14 @@ def test_exchange_reduce_with_eight_sources_on_one_gpu(ctx):
     h_bits = bits_from_torch_bf16(program.intermediate)
     own = oracle.linear_f64(down[0], down[1], down[2], hidden, inter, h_bits, threads=4)
     want = own + others[1:].astype(np.float64).sum(axis=0)
-    got = synth.bf16_bits_to_f32(bits_from_torch_bf16(program.out)).astype(np.float64).reshape(want.shape)
-    assert np.max(np.abs(got - want) / np.maximum(np.abs(want), np.sqrt(np.mean(want * want)))) <= TOLERANCE
+    # the others' tiles are f32 values, so the fp64 sum of all eight is what one BF16 rounding of the f32 sum must match
+    assert rel_error(bits_from_torch_bf16(program.out), want) <= TOLERANCE
+    # the counter in the tail of rank 0's buffer: one launch counted and no arrivals left, or untouched
+    tail = buffers[0][image.nbytes:].cpu().numpy().view(np.uint32)
+    assert list(tail[:2]) == ([1, 0] if counted_on == "device" else [0, 0])
     # its own tiles arrived in every buffer, flagged with the sequence number
     for r in range(1, world):
-        pushed = buffers[r].cpu().numpy().view(np.uint32).reshape(2, world, groups, 32, 4, 4)
+        pushed = buffers[r][:image.nbytes].cpu().numpy().view(np.uint32).reshape(2, world, groups, 32, 4, 4)
         assert np.all(pushed[seq & 1, 0, :, :, :, 1] == seq) and np.all(pushed[seq & 1, 0, :, :, :, 3] == seq)
         assert not pushed[1 - (seq & 1)].any() and not pushed[seq & 1, 1:].any()
 

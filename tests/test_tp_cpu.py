@@ -90,19 +90,27 @@ def test_two_gloo_ranks_all_reduce_to_the_full_result():
 def test_exchange_sequence_never_yields_zero_and_alternates_parity_across_the_wrap():
     from augur_v100_b200 import tp
     exchange = tp.ExchangeBuffers.__new__(tp.ExchangeBuffers)   # the counter alone; no device is touched
-    exchange.sequence = 0
+    exchange.sequence, exchange.host_counted = 0, True
     assert [exchange.next_sequence() for _ in range(3)] == [1, 2, 3]
     exchange.sequence = 0xFFFFFFFC
     wrapped = [exchange.next_sequence() for _ in range(4)]
     assert wrapped == [0xFFFFFFFD, 0xFFFFFFFE, 1, 2]
     assert all((a ^ b) & 1 for a, b in zip(wrapped, wrapped[1:]))
+    # launches that count on the device are passed 0 every time
+    exchange.host_counted = False
+    assert [exchange.next_sequence() for _ in range(2)] == [0, 0]
+    # the device-side rule (launch count -> sequence) is the same series: never 0, parity alternating across the wrap
+    assert [launches % 0xFFFFFFFE + 1 for launches in (0, 1, 2)] == [1, 2, 3]
+    device = [launches % 0xFFFFFFFE + 1 for launches in (0xFFFFFFFC, 0xFFFFFFFD, 0xFFFFFFFE, 0xFFFFFFFF, 0, 1)]   # the u32 counter wraps too
+    assert 0 not in device and all((a ^ b) & 1 for a, b in zip(device, device[1:]))
 
 
 def test_exchange_extent_matches_the_layout():
     from augur_v100_b200 import tp
     # [2 parities][world][hidden / 32 row groups] tiles of 256 {value, flag} pairs (8 bytes each)
-    assert tp.exchange_extent(5120, 8) == 2 * 8 * 160 * 256 * 8
-    assert tp.exchange_extent(1024, 2) == 2 * 2 * 32 * 2048
+    # and 256 bytes at the end for the sequence counter of launches that count on the device
+    assert tp.exchange_extent(5120, 8) == 2 * 8 * 160 * 256 * 8 + 256
+    assert tp.exchange_extent(1024, 2) == 2 * 2 * 32 * 2048 + 256
     import pytest
     with pytest.raises(ValueError):
         tp.exchange_extent(5120, 9)
