@@ -101,6 +101,7 @@ augur_cuda_result_v1 submitted();  // maps cudaGetLastError to SUBMISSION_FAILUR
 // One-time per-device kernel attribute setup, called from plan creation (bind time).
 cudaError_t gemv_configure_device();
 cudaError_t gemm_configure_device();
+cudaError_t gemv_tc_configure_device();
 // Two-CTA clusters of the pair GEMM that the device can hold at once (0 if the query fails).
 uint32_t gemm_pair_resident_clusters();
 

@@ -191,6 +191,7 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_plan_crea
     if (major != 10) return make_result(AUGUR_CUDA_STATUS_UNSUPPORTED_DEVICE);
     e = gemv_configure_device();
     if (e == cudaSuccess) e = gemm_configure_device();
+    if (e == cudaSuccess) e = gemv_tc_configure_device();
     if (e != cudaSuccess) return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE, e);
     const uint64_t rounded = (scratch_len_bytes + 255) / 256 * 256;
     void* memory = nullptr;

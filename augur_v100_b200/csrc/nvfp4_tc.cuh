@@ -1,0 +1,221 @@
+// tcgen05 / TMA / mbarrier wrappers, shared-memory and instruction descriptors, and the BF16 -> NVFP4
+// quantiser arithmetic shared by the tensor-memory kernels of this library (prefill GEMM and the
+// small-token tensor-memory linear).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace augur_sm100 {
+namespace tc {
+
+constexpr uint32_t kTileM = 128;          // rows of the 128-row MMA operand per tile
+constexpr uint32_t kWaitLimit = 20u * 1000u * 1000u;
+
+// ---- PTX wrappers ---------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+// Bounded wait. Returns false (after raising the abort flag) if the phase never completes
+// or if another role already aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                          uint32_t* status_word, uint32_t code) {
+    for (uint32_t spin = 0; spin < kWaitLimit; ++spin) {
+        if (mbar_test(bar, parity)) return true;
+        if ((spin & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicCAS(status_word, 0u, code);
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t x, uint32_t y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_copy_sf(uint32_t tmem, uint64_t desc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                       uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %6, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n}"
+        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tc_load32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptors (64-bit): start address >> 4 in bits [0,14), leading
+// byte offset >> 4 in [16,30), stride byte offset >> 4 in [32,46), descriptor version 1 in
+// [46,48), swizzle mode in [61,64) (0 = none, 2 = 128-byte).
+// K-major 128-byte-swizzled operand tile: rows are 128 bytes apart, 8-row groups 1024 bytes.
+__device__ __forceinline__ uint64_t operand_desc(uint32_t smem_addr) {
+    return static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) |
+           (uint64_t(1) << 46) | (uint64_t(2) << 61);
+}
+// Scale-factor atom for tcgen05.cp 32x128b: 32 rows of 16 bytes, 8-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t sf_desc(uint32_t smem_addr) {
+    return static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4) | (uint64_t(128 >> 4) << 32) | (uint64_t(1) << 46);
+}
+// Instruction descriptor, block-scaled: A/B format E2M1 (1) at bits [7,10) / [10,13), both
+// K-major, N >> 3 at [17,23), scale format UE4M3 (0) at bit 23, M >> 4 at [24,29), K = 64.
+__device__ __forceinline__ uint32_t instr_desc(uint32_t n) {
+    return (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((kTileM >> 4) << 24);
+}
+
+
+// Smallest positive E4M3 code whose value is >= d (d > 0), 126 if none.
+__device__ __forceinline__ uint32_t e4m3_ceil_code(float d) {
+    if (d > 448.0f) return 126;
+    if (d <= 0x1p-6f) {                          // subnormal range: multiples of 2^-9, and 2^-6 itself
+        const float steps = d * 512.0f;          // exact
+        uint32_t m = static_cast<uint32_t>(ceilf(steps));
+        return m < 1 ? 1 : m;                     // m == 8 is code 8 = 2^-6
+    }
+    const uint32_t bits = __float_as_uint(d);
+    uint32_t exponent = (bits >> 23) - 127 + 7;  // E4M3 biased exponent, >= 1 here
+    uint32_t mantissa = (bits >> 20) & 7;
+    if (bits & 0xfffffu) ++mantissa;             // round up
+    if (mantissa == 8) { mantissa = 0; ++exponent; }
+    return exponent * 8 + mantissa;
+}
+
+__device__ __forceinline__ float e4m3_positive_value(uint32_t code) {
+    const uint32_t exponent = code >> 3, mantissa = code & 7;
+    return exponent == 0 ? static_cast<float>(mantissa) * 0x1p-9f
+                         : __uint_as_float(((exponent + 120) << 23) | (mantissa << 20));
+}
+
+// Nearest E2M1 level; a tie goes to the smaller magnitude; zero is always code 0. |v| <= 6.
+// From 1 upward E2M1 is a float with one mantissa bit, so rounding the f32 pattern to that bit with
+// "ties down" (add half an ulp minus one, truncate) gives exponent and mantissa at once:
+// 1 -> code 2, 1.5 -> 3, 2 -> 4, 3 -> 5, 4 -> 6, 6 -> 7. Below 1 the levels are 0, 0.5 and 1.
+// `v` is the quotient as computed; the clamp to [-6, 6] is folded in: the magnitude is cut at 6, and a NaN
+// quotient, which fmin(fmax(v, -6), 6) sends to -6, is negative here as well.
+__device__ __forceinline__ uint32_t e2m1_nearest(float v, float* level) {
+    const float a = fminf(fabsf(v), 6.0f);
+    uint32_t m;
+    if (a < 1.0f) {
+        m = (a > 0.25f ? 1u : 0u) + (a > 0.75f ? 1u : 0u);
+    } else {
+        m = (__float_as_uint(a) + (0x1fffffu - (252u << 22))) >> 22;   // round to one mantissa bit, ties toward zero
+    }
+    const float l = m < 2 ? 0.5f * static_cast<float>(m) : __uint_as_float((m + 252u) << 22);
+    const bool negative = !(v >= 0.0f) && m != 0;
+    *level = negative ? -l : l;
+    return negative ? (m | 8u) : m;
+}
+
+// The 16 quotients of a group share one divisor. With y = RN(1/d), two Newton steps on the quotient (each
+// an exact FMA residual) end on the correctly rounded x / d whenever d and x are well inside the normal
+// range and d is not of the all-ones mantissa form; the kernel checks that once per group (`kFast`) and
+// otherwise divides. An x below 2^-65 (d is at least 2^-63 here) has a quotient under a quarter, i.e. code 0
+// whatever the last bits are, and is not sent through the steps, which could leave the normal range.
+template <bool kFast, bool kMoreTerms>
+__device__ __forceinline__ void quantise_group(float (&residual)[16], float divisor, float reciprocal, uint32_t (&packed)[2]) {
+#pragma unroll
+    for (uint32_t i = 0; i < 16; ++i) {
+        const float x = residual[i];
+        float normalized;
+        if (kFast) {
+            float q = x * reciprocal;
+            float r = fmaf(-q, divisor, x);
+            q = fmaf(r, reciprocal, q);
+            r = fmaf(-q, divisor, x);
+            q = fmaf(r, reciprocal, q);
+            normalized = fabsf(x) < 0x1p-65f ? 0.0f : q;
+        } else {
+            normalized = divisor == 0.0f ? 0.0f : __fdiv_rn(x, divisor);
+        }
+        float level;
+        const uint32_t code = e2m1_nearest(normalized, &level);
+        packed[i >> 3] += code << (4 * (i & 7));   // disjoint fields: a sum, so that shift and add fuse
+        if (kMoreTerms) residual[i] = __fsub_rn(x, __fmul_rn(level, divisor));
+    }
+}
+
+// One residual term of one 16-element group: the block scale (smallest E4M3 value >= amax / (6 g)), the 16 codes
+// (nearest level of x / (scale * g), ties toward zero) and, if another term follows, the residual it quantises.
+// `kMoreTerms` is a compile-time choice: the last term of a group needs neither the levels nor the residual.
+template <bool kMoreTerms>
+__device__ __forceinline__ void quantise_term_as(float (&residual)[16], float global_scale, uint32_t (&packed)[2],
+                                                 uint32_t* scale_code_out) {
+    float maximum = 0.0f;
+#pragma unroll
+    for (uint32_t i = 0; i < 16; ++i) maximum = fmaxf(maximum, fabsf(residual[i]));
+    const float desired = __fdiv_rn(maximum, __fmul_rn(6.0f, global_scale));
+    uint32_t scale_code = 0;
+    float scale = 0.0f;
+    if (desired > 0.0f) {
+        scale_code = e4m3_ceil_code(desired);
+        scale = e4m3_positive_value(scale_code);
+    }
+    const float divisor = __fmul_rn(scale, global_scale);
+    const uint32_t divisor_field = (__float_as_uint(divisor) >> 23) & 0xffu, largest_field = (__float_as_uint(maximum) >> 23) & 0xffu;
+    const bool fast = divisor_field >= 64u && divisor_field <= 190u && (__float_as_uint(divisor) & 0x7fffffu) != 0x7fffffu &&
+                      largest_field <= 190u;
+    packed[0] = packed[1] = 0;
+    if (fast) {
+        quantise_group<true, kMoreTerms>(residual, divisor, __frcp_rn(divisor), packed);
+    } else {
+        quantise_group<false, kMoreTerms>(residual, divisor, 0.0f, packed);
+    }
+    *scale_code_out = scale_code;
+}
+__device__ __forceinline__ void quantise_term(float (&residual)[16], float global_scale, bool more_terms, uint32_t (&packed)[2],
+                                              uint32_t* scale_code_out) {
+    if (more_terms) {
+        quantise_term_as<true>(residual, global_scale, packed, scale_code_out);
+    } else {
+        quantise_term_as<false>(residual, global_scale, packed, scale_code_out);
+    }
+}
+
+}  // namespace tc
+}  // namespace augur_sm100

@@ -290,6 +290,46 @@ class Nvfp4Sm100Projection:
             s.ordinal, s.handle, self.plan.handle, byref(self.args)))
 
 
+def gemv_tc_scratch_bytes(rows: int, cols: int, epilogue: int = abi.EPILOGUE_LINEAR_BF16) -> int:
+    out = c_uint64()
+    _check("gemv_tc_scratch_extent", abi.lib().augur_cuda_nvfp4_sm100_gemv_tc_scratch_extent_host_v1(rows, cols, epilogue, byref(out)))
+    return int(out.value)
+
+
+class Nvfp4Sm100TcProjection:
+    """A retained small-token projection on the tensor-memory path: the weight is in the tcgen05 layout
+    (the one the prefill GEMM uses; for the SwiGLU epilogue the interleaved gate|up tensor of
+    `upload_gate_up_interleaved`), the kernel is `gemv_tc`. Same contract as `Nvfp4Sm100Projection`."""
+
+    def __init__(self, plan: Plan, weight: Nvfp4Sm100Weight, x: torch.Tensor, out: torch.Tensor, epilogue: int):
+        assert weight.layout == abi.LAYOUT_TCGEN05
+        self.plan, self.weight, self.x, self.out = plan, weight, x, out
+        args = gemv_args(weight, x, out, epilogue)
+        if epilogue == abi.EPILOGUE_SWIGLU_BF16:
+            args.rows = weight.rows // 2          # the output width; the weight holds gate and up rows
+        else:
+            args.global_scale_b = 0.0
+        self.args = args
+
+    @classmethod
+    def bind(cls, plan: Plan, weight: Nvfp4Sm100Weight, x: torch.Tensor, out: torch.Tensor | None = None,
+             epilogue: int = abi.EPILOGUE_LINEAR_BF16):
+        width = weight.rows // 2 if epilogue == abi.EPILOGUE_SWIGLU_BF16 else weight.rows
+        if out is None:
+            dtype = torch.float32 if epilogue == abi.EPILOGUE_LINEAR_F32 else torch.bfloat16
+            out = torch.empty((x.shape[0], width), dtype=dtype, device=x.device)
+        self = cls(plan, weight, x, out, epilogue)
+        s = plan.stream
+        _check("gemv_tc_preflight", abi.lib().augur_cuda_nvfp4_sm100_gemv_tc_bf16_preflight_v1(
+            s.ordinal, s.handle, plan.handle, byref(self.args)))
+        return self
+
+    def submit_for_plan(self) -> None:
+        s = self.plan.stream
+        _check("gemv_tc_submit", abi.lib().augur_cuda_nvfp4_sm100_gemv_tc_bf16_prevalidated_submit_v1(
+            s.ordinal, s.handle, self.plan.handle, byref(self.args)))
+
+
 class Nvfp4Sm100FfnProgram:
     """gate|up + SwiGLU, then down, as one validated program.
 

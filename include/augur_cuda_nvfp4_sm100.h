@@ -269,6 +269,22 @@ augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_bf16_prevalidat
     int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
     const augur_cuda_nvfp4_sm100_gemv_args_v1* args);
 
+/* The same small-token linear on the tensor-memory path: `weight` is in AUGUR_NVFP4_SM100_LAYOUT_TCGEN05
+ * (for EPILOGUE_SWIGLU_BF16: one tensor of 2 * rows physical rows, 16 gate rows alternating with the
+ * matching 16 up rows, as interleave_gate_up_host_v1 makes it), rows (physical) a multiple of 128, cols a
+ * multiple of 64. The weights reach the tensor cores (tcgen05.mma kind::mxf4nvf4) as TMA delivers them;
+ * the BF16 activations are split by the kernel into six NVFP4 residual terms, which reproduces them to
+ * about 3e-7 of a 16-element group's largest magnitude. Replaces the same reference entry points as
+ * gemv_bf16_*_v1 (augur_qwen35_nvfp4_qpn_abi.h:134-156), with one weight layout for every token count. */
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_tc_scratch_extent_host_v1(
+    uint32_t rows, uint32_t cols, uint32_t epilogue, uint64_t* out_bytes);
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_tc_bf16_preflight_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_gemv_args_v1* args);
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_tc_bf16_prevalidated_submit_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_gemv_args_v1* args);
+
 /* No counterpart in the reference. The same small-token linear for callers that may not allocate:
  * plan creation calls cudaMalloc, which a host cannot do once it has handed all device memory to
  * its own arena, or while it runs under an audited no-allocation rule (the discipline Augur's own

@@ -1,0 +1,148 @@
+"""GPU parity of the small-token linear on the tensor-memory path (`gemv_tc`), through the C ABI.
+
+Ordered from the smallest exercise of the instruction to the benchmark's shapes, so that a failure localises:
+one MMA -> four MMAs of one stage -> several stages -> ring wrap -> several row tiles -> k slabs with the
+hand-over through plan scratch -> configuration 0 at full size.
+Bound of every case: helpers.rel_error <= 2e-2 against the fp64 oracle fed the BF16 activations, and at most
+one BF16 ulp from bf16_round(sequential f32), as for the other small-token kernel.
+"""
+import numpy as np
+import pytest
+
+import oracle
+from augur_v100_b200 import abi, synth
+from helpers import TOLERANCE, bits_from_torch_bf16, rel_error, rel_error_f32, torch_bf16_from_bits
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    import torch
+    from augur_v100_b200 import host
+    torch.cuda.set_device(0)
+    stream = host.Stream(0)
+    plan = host.Plan(stream, 64 << 20)
+    yield {"torch": torch, "host": host, "stream": stream, "plan": plan, "device": torch.device("cuda", 0)}
+    plan.close()
+    stream.close()
+
+
+def _case(ctx, rows, cols, tokens, seed, epilogue=abi.EPILOGUE_LINEAR_BF16, x_bits=None, scale=1.0):
+    host = ctx["host"]
+    codes, scales, glob = synth.make_weight(seed, 90, "w", rows, cols)
+    if x_bits is None:
+        x = synth.bf16_bits_to_f32(synth.make_activation(seed, 90, "x", tokens, cols)) * np.float32(scale)
+        x_bits = synth.f32_to_bf16_bits(x)
+    w = host.Nvfp4Sm100Weight.upload_checkpoint_nvfp4(ctx["stream"], abi.LAYOUT_TCGEN05, rows, cols, codes, scales, glob)
+    x = torch_bf16_from_bits(x_bits, ctx["device"])
+    proj = host.Nvfp4Sm100TcProjection.bind(ctx["plan"], w, x, epilogue=epilogue)
+    proj.submit_for_plan()
+    ctx["stream"].synchronize()
+    assert ctx["plan"].device_status() == 0, hex(ctx["plan"].device_status())
+    return codes, scales, glob, x_bits, proj
+
+
+def _check(ctx, rows, cols, tokens, seed, scale=1.0):
+    codes, scales, glob, x_bits, proj = _case(ctx, rows, cols, tokens, seed, scale=scale)
+    got = bits_from_torch_bf16(proj.out)
+    y64 = oracle.linear_f64(codes, scales, glob, rows, cols, x_bits, threads=oracle.max_threads())
+    err = rel_error(got, y64)
+    assert err <= TOLERANCE, err
+    ref_bits = oracle.linear_bf16(codes, scales, glob, rows, cols, x_bits, threads=oracle.max_threads())
+    a = synth.bf16_bits_to_f32(got).astype(np.float64)
+    b = synth.bf16_bits_to_f32(ref_bits).astype(np.float64).reshape(a.shape)
+    assert np.max(np.abs(a - b) / np.maximum(np.abs(b), 1e-3 * np.sqrt(np.mean(b * b)))) <= 2.0 ** -7
+    return err
+
+
+def test_single_mma(ctx):
+    _check(ctx, rows=128, cols=64, tokens=8, seed=1)
+
+
+def test_one_stage_four_mmas(ctx):
+    _check(ctx, rows=128, cols=256, tokens=8, seed=2)
+
+
+def test_several_stages_and_ragged_last_stage(ctx):
+    _check(ctx, rows=128, cols=1216, tokens=8, seed=3)      # 4.75 stages
+
+
+def test_fewer_tokens(ctx):
+    for tokens in (1, 3, 5):
+        _check(ctx, rows=256, cols=512, tokens=tokens, seed=4 + tokens)
+
+
+def test_ring_wrap_and_row_tiles(ctx):
+    _check(ctx, rows=2560, cols=2048, tokens=8, seed=5)     # one slab of 8 stages; CTAs with several tiles on small grids
+
+
+def test_k_slabs_hand_over_through_scratch(ctx):
+    _check(ctx, rows=256, cols=5120, tokens=8, seed=6)      # 20 stages: at least 3 slabs
+    _check(ctx, rows=384, cols=17408, tokens=8, seed=7)     # 68 stages: at least 9 slabs
+    # a second launch on the same plan finds the counters clean
+    _check(ctx, rows=384, cols=17408, tokens=8, seed=7)
+
+
+def test_activation_magnitudes(ctx):
+    # tiny, huge and mixed magnitudes: the split's per-token power-of-two scale follows the row
+    for scale in (2.0 ** -60, 1e-3, 8.0, 1e4, 2.0 ** 60):
+        _check(ctx, rows=128, cols=1024, tokens=8, seed=8, scale=scale)
+    rows, cols, tokens = 128, 1024, 8
+    x = np.random.default_rng(9).standard_normal((tokens, cols)).astype(np.float32)
+    x[0] = 0.0
+    x[1, ::7] *= 1e4         # outlier channels
+    x[2, :16] *= 1e-6        # one group far below the rest of its row
+    x[3, 5] = 3e4
+    codes, scales, glob, x_bits, proj = _case(ctx, rows, cols, tokens, 10, x_bits=synth.f32_to_bf16_bits(x))
+    got = bits_from_torch_bf16(proj.out).reshape(tokens, rows)
+    y64 = oracle.linear_f64(codes, scales, glob, rows, cols, x_bits, threads=4)
+    for t in range(tokens):
+        assert rel_error(got[t], y64[t]) <= TOLERANCE, t
+    assert np.all(got[0] & 0x7FFF == 0)
+
+
+def test_f32_epilogue(ctx):
+    rows, cols, tokens = 256, 2176, 8
+    codes, scales, glob, x_bits, proj = _case(ctx, rows, cols, tokens, 11, epilogue=abi.EPILOGUE_LINEAR_F32)
+    y64 = oracle.linear_f64(codes, scales, glob, rows, cols, x_bits, threads=4)
+    # the six-term split of the activations and f32 accumulation: far inside the BF16 rounding step
+    assert rel_error_f32(proj.out.cpu().numpy(), y64) <= 1e-3
+
+
+def test_swiglu_epilogue(ctx):
+    host = ctx["host"]
+    inter, hidden, tokens = 512, 1024, 8
+    gate = synth.make_weight(12, 90, "gate", inter, hidden)
+    up = synth.make_weight(12, 90, "up", inter, hidden)
+    up = (up[0], up[1], float(np.float32(up[2]) * np.float32(1.5)))
+    weight = host.upload_gate_up_interleaved(ctx["stream"], inter, hidden, *gate, *up)
+    x_bits = synth.f32_to_bf16_bits(np.random.default_rng(12).standard_normal((tokens, hidden)).astype(np.float32) * 8.0)
+    x = torch_bf16_from_bits(x_bits, ctx["device"])
+    proj = host.Nvfp4Sm100TcProjection.bind(ctx["plan"], weight, x, epilogue=abi.EPILOGUE_SWIGLU_BF16)
+    proj.submit_for_plan()
+    ctx["stream"].synchronize()
+    assert ctx["plan"].device_status() == 0
+    down = synth.make_weight(12, 90, "down", hidden, inter)
+    h64, _ = oracle.mlp_f64(gate, up, down, hidden, inter, x_bits, threads=4)
+    assert rel_error(bits_from_torch_bf16(proj.out), h64) <= TOLERANCE
+
+
+def test_config0_full_size(ctx):
+    rows, cols, tokens = 17408, 5120, 8
+    codes, scales, glob = synth.make_weight(0, 0, "weight", rows, cols)
+    x_bits = synth.make_activation(0, 0, "activation", tokens, cols)
+    host = ctx["host"]
+    w = host.Nvfp4Sm100Weight.upload_checkpoint_nvfp4(ctx["stream"], abi.LAYOUT_TCGEN05, rows, cols, codes, scales, glob)
+    x = torch_bf16_from_bits(x_bits, ctx["device"])
+    proj = host.Nvfp4Sm100TcProjection.bind(ctx["plan"], w, x)
+    proj.submit_for_plan()
+    ctx["stream"].synchronize()
+    assert ctx["plan"].device_status() == 0
+    first = bits_from_torch_bf16(proj.out).copy()
+    y64 = oracle.linear_f64(codes, scales, glob, rows, cols, x_bits, threads=oracle.max_threads())
+    assert rel_error(first, y64) <= TOLERANCE
+    proj.out.zero_()
+    proj.submit_for_plan()
+    ctx["stream"].synchronize()
+    assert np.array_equal(bits_from_torch_bf16(proj.out), first)    # fixed-order sums: the same bits again
