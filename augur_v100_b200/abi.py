@@ -179,6 +179,8 @@ EXPORTS = {
     "augur_cuda_nvfp4_sm100_gemv_tc_scratch_extent_host_v1": (Result, [c_uint32, c_uint32, c_uint32, POINTER(c_uint64)]),
     "augur_cuda_nvfp4_sm100_gemv_tc_bf16_preflight_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(GemvArgs)]),
     "augur_cuda_nvfp4_sm100_gemv_tc_bf16_prevalidated_submit_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(GemvArgs)]),
+    "augur_cuda_nvfp4_sm100_mlp_tc_preflight_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(MlpArgs)]),
+    "augur_cuda_nvfp4_sm100_mlp_tc_prevalidated_submit_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(MlpArgs)]),
     "augur_cuda_nvfp4_sm100_gemv_bf16_static_scratch_submit_v1": (Result, [c_int32, c_void_p, POINTER(GemvArgs)]),
     "augur_cuda_nvfp4_sm100_static_scratch_status_v1": (Result, [c_int32, c_void_p, POINTER(c_uint32)]),
     "augur_cuda_nvfp4_sm100_mlp_preflight_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(MlpArgs)]),

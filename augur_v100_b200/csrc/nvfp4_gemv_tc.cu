@@ -1,29 +1,35 @@
-// Small-token (1..8) NVFP4 linear for sm_100a on the tensor-memory path: the weights go from HBM to the
-// tensor cores without a single per-element instruction on the SMs.
+// Small-token (1..8) NVFP4 linear and MLP block for sm_100a on the tensor-memory path: the weights go from HBM to
+// the tensor cores without a single per-element instruction on the SMs, and a whole MLP block is ONE launch in
+// which the weight stream never stops.
 //
 //   weights      TCGEN05 layout (codes K-major as in the checkpoint, block scales in 512-byte atoms), the
 //                128-row operand of tcgen05.mma kind::mxf4nvf4: TMA brings 128 rows x 256 k (16 KB of codes
 //                plus 2 KB of scales) per stage into a ring in shared memory, tcgen05.cp moves the scales on
 //                to tensor memory, the MMA reads the codes where the TMA put them;
-//   activations  BF16 in global memory. A block-scaled FP4 MMA wants FP4 on both sides, so every CTA splits
-//                the activations of its own k-slab, once, into kTerms NVFP4 residual terms (term t holds
-//                the part of x that terms 0..t-1 left over) with power-of-two per-token global scales; the
-//                terms sit side by side on the MMA n dimension (column = term * 8 + token), resident in
-//                shared memory and their block scales resident in tensor memory for the whole launch. Six
-//                terms reproduce a BF16 value to about 3e-7 of its group's largest magnitude, below the f32
-//                accumulation noise; one MMA per 64 k covers all tokens and all terms;
+//   activations  BF16 in global memory. A block-scaled FP4 MMA wants FP4 on both sides, so the launch first
+//                splits them - every CTA a slice, once - into kTerms NVFP4 residual terms (term t holds what
+//                terms 0..t-1 left over) with power-of-two per-token global scales. The terms sit side by side
+//                on the MMA n dimension (column = term * 8 + token); their codes and block scales (8 KB per
+//                256 k, L2-resident) ride along with every weight stage. Six terms reproduce a BF16 value to
+//                about 3e-7 of its group's largest magnitude, below the f32 accumulation noise; one MMA per
+//                64 k covers all tokens and all terms;
 //   accumulator  128 weight rows x 48 columns of f32 in tensor memory, two buffers; the epilogue warps add
-//                the terms of a token with their scales and either finish the rows or, when the k dimension
-//                is cut into slabs, hand a partial sum over through plan scratch.
+//                the terms of a token with their scales and finish the rows.
 //
-// Work split: the k dimension is cut into `slabs` (a slab's activations must fit shared memory), every CTA
-// belongs to one slab and owns a contiguous range of 128-row tiles. A row tile is complete when all slabs
-// have delivered: partial sums go to plan scratch with an arrival counter per 32 rows, the last arriver adds
-// them in slab order and finishes the rows. Nothing spins on another CTA; results are bit-reproducible.
-// The kernel is bandwidth-bound: a CTA with fewer tiles ends early and the others take up its share of HBM.
+// A launch runs one phase (a linear) or two (gate|up with SiLU(gate) * up, then down, whose activations are the
+// first phase's output). Per phase a CTA owns whole 128-row tiles over the whole k range whenever there are at
+// least as many tiles as resident CTAs (two per SM); otherwise every tile is cut along k into equal parts, one
+// per CTA: partial sums go to plan scratch with an arrival counter per 32 rows, and the last arriver adds them in
+// part order and finishes the rows. Results are bit-reproducible.
 //
-// Every mbarrier wait is bounded; a wait that runs out records a code in the plan's status word, raises a
-// CTA-wide abort flag, and all roles fall through to the common exit where tensor memory is released.
+// Roles of a CTA: one thread streams the weight stages of all its work, both phases back to back, and keeps
+// doing so while activations are not ready yet (the ring buffers that time); one thread copies block scales to
+// tensor memory; one issues the MMAs; four warps split activations and run the epilogues. The split needs
+// every CTA's slice before any CTA can use it, and the second phase needs every CTA's output of the first:
+// the grid meets at barriers in global memory (all CTAs are resident: the grid never exceeds two CTAs per SM).
+//
+// Every wait is bounded; a wait that runs out records a code in the plan's status word, raises a CTA-wide abort
+// flag, and all roles fall through to the common exit where tensor memory is released.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -39,37 +45,62 @@ using namespace tc;
 constexpr uint32_t kTerms = 6;                         // residual terms of the activation split
 constexpr uint32_t kCols = 8 * kTerms;                 // MMA n: column = term * 8 + token
 constexpr uint32_t kStageK = 256;                      // k per ring stage = one 128-byte swizzled row of codes
-constexpr uint32_t kStageCodeBytes = kTileM * 128;     // 16 KB
-constexpr uint32_t kStageSfBytes = 4 * kSfAtomBytes;   // 2 KB: the 4 scale atoms of the stage
-constexpr uint32_t kStageBytes = kStageCodeBytes + kStageSfBytes;
-constexpr uint32_t kStages = 8;
-constexpr uint32_t kMaxSlabStages = 8;                 // k-slab of a CTA: at most 2048 k
-constexpr uint32_t kChunkBytes = kCols * 128;          // activation codes of one 256-k chunk: 48 rows x 128 bytes
-constexpr uint32_t kActCodeBytes = kMaxSlabStages * kChunkBytes;
-constexpr uint32_t kActSfBytes = kMaxSlabStages * 4 * kSfAtomBytes;
-constexpr uint32_t kThreads = 320;                     // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue, all ten quantise
-constexpr uint32_t kSmemBytes = kStages * kStageBytes + kActCodeBytes + kActSfBytes + 1024 /*alignment*/ + 1024 /*small state*/;
+constexpr uint32_t kStageCodeBytes = kTileM * 128;     // 16 KB of weight codes
+constexpr uint32_t kStageSfBytes = 4 * kSfAtomBytes;   // 2 KB: the 4 scale atoms of a stage (weights; activations alike)
+constexpr uint32_t kChunkBytes = kCols * 128;          // 6 KB: activation codes of one 256-k chunk, 48 rows x 128 bytes
+constexpr uint32_t kStageActCodes = kStageCodeBytes + kStageSfBytes;        // offsets inside a stage
+constexpr uint32_t kStageActSf = kStageActCodes + kChunkBytes;
+constexpr uint32_t kStageBytes = kStageActSf + kStageSfBytes;               // 26 KB
+constexpr uint32_t kStages = 4;                        // per CTA; two CTAs share an SM
+constexpr uint32_t kThreads = 224;                     // warp 0 TMA, warp 1 MMA, warps 2..5 split and epilogue, warp 6 scale copies
+constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + 1024 /*small state*/;
+constexpr uint32_t kCtasPerSm = 2;                     // half of an SM's shared and tensor memory each: a CTA of the next launch
+                                                       // moves in (and fills its ring) as soon as one of this launch leaves
 constexpr uint32_t kTmemAcc = 0;                       // two accumulators of 64 columns (48 used)
-constexpr uint32_t kTmemSfAct = 128;                   // 4 columns per 64 k of the slab: 128 columns
-constexpr uint32_t kTmemSfWeight = 256;                // 16 columns per ring stage
-constexpr uint32_t kTmemColumns = 512;
-static_assert(kTmemSfWeight + kStages * 16 <= kTmemColumns, "tensor memory columns");
+constexpr uint32_t kTmemSfWeight = 128;                // 16 columns per ring stage
+constexpr uint32_t kTmemSfAct = kTmemSfWeight + kStages * 16;
+constexpr uint32_t kTmemColumns = 256;
+static_assert(kTmemSfAct + kStages * 16 <= kTmemColumns, "tensor memory columns");
+static_assert(kCtasPerSm * kSmemBytes <= 227 * 1024, "two CTAs per SM");
+static_assert(kStageBytes % 1024 == 0 && kStageActCodes % 1024 == 0, "swizzled operand tiles are 1024-byte aligned");
 constexpr uint32_t kSlotFloats = 256;                  // one partial: 32 rows x 8 tokens
+constexpr uint32_t kWorkers = 128;                     // the four split / epilogue warps
+constexpr uint32_t kMaxPhases = 2;
+constexpr uint32_t kGridWaitLimit = 1u << 22;          // polls of the grid barrier (a fraction of a microsecond each) before giving up
 
-constexpr uint32_t kErrTcProducer = 0x301, kErrTcFull = 0x302, kErrTcAccEmpty = 0x303, kErrTcAccFull = 0x304;
+constexpr uint32_t kErrTcProducer = 0x301, kErrTcFull = 0x302, kErrTcAccEmpty = 0x303, kErrTcAccFull = 0x304,
+                   kErrTcScalesLanded = 0x305, kErrTcScalesReady = 0x306, kErrTcGridBarrier = 0x307;
 
-struct TcParams {
+
+// The split activations in global memory (plan scratch): the image the ring stages want, chunk by chunk.
+//   [chunk = k / 256][48 rows][128 bytes]   codes, rows already in the 128-byte swizzle of a shared-memory operand tile
+//   [k / 64][512 bytes]                     block-scale atoms (row n at byte (n % 32) * 16 + (n / 32) * 4 + (k / 16) % 4)
+__host__ __device__ constexpr uint64_t split_code_bytes(uint32_t cols) { return static_cast<uint64_t>((cols + kStageK - 1) / kStageK) * kChunkBytes; }
+__host__ __device__ constexpr uint64_t split_sf_bytes(uint32_t cols) { return static_cast<uint64_t>((cols + kStageK - 1) / kStageK) * kStageSfBytes; }
+__host__ __device__ constexpr uint64_t split_bytes(uint32_t cols) { return split_code_bytes(cols) + split_sf_bytes(cols); }
+
+struct TcPhase {
     const uint8_t* weight_sf;     // scale region of the weight
-    const uint16_t* x;            // [tokens][cols] BF16
+    const uint16_t* x;            // [tokens][cols] BF16 (second phase: what the first phase wrote)
+    uint8_t* split;               // the split activations (layout above)
     void* out;
-    float* partials;              // [tile * 4 + quadrant][slab][32 rows][8 tokens]
+    float* partials;              // [tile * 4 + quadrant][part][32 rows][8 tokens]
     uint32_t* counters;           // [tile * 4 + quadrant], zero between launches
-    uint32_t* status_word;
+    uint32_t* row_max;            // [token] bits of the row's largest magnitude, zero between launches
+    uint32_t* collect;            // SwiGLU epilogue: the next phase's row_max, or null
     uint32_t rows;                // physical weight rows (SwiGLU: gate and up interleaved by 16)
     uint32_t out_rows;            // output width
-    uint32_t cols, tokens, epilogue;
-    uint32_t tiles, k_blocks, slabs;
+    uint32_t cols, epilogue;
+    uint32_t tiles, k_blocks, parts;   // `parts` equal k ranges per tile (1: whole tiles)
+    uint32_t scan;                // this launch finds row_max itself (else the phase before collected it)
     float global_a, global_b;
+};
+
+struct TcParams {
+    TcPhase phase[kMaxPhases];
+    uint32_t phases, tokens;
+    uint32_t* grid_barrier;       // {arrivals, generation}, arrivals zero between launches
+    uint32_t* status_word;
 };
 
 __device__ __forceinline__ void tc_load16(uint32_t taddr, uint32_t (&v)[16]) {
@@ -80,19 +111,116 @@ __device__ __forceinline__ void tc_load16(uint32_t taddr, uint32_t (&v)[16]) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void workers_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// All CTAs of the grid meet (the four worker warps of each; thread `leader` speaks for its CTA). Everything the
+// workers wrote before is visible to every CTA's workers after. Returns false if the wait ran out.
+__device__ __forceinline__ bool grid_meet(const TcParams& p, bool leader, volatile uint32_t* abort_flag) {
+    workers_sync();
+    if (leader) {
+        volatile uint32_t* generation = p.grid_barrier + 1;
+        const uint32_t before = *generation;     // cannot advance until this CTA has arrived
+        __threadfence();
+        if (atomicAdd(p.grid_barrier, 1u) + 1 == gridDim.x) {
+            *static_cast<volatile uint32_t*>(p.grid_barrier) = 0;
+            __threadfence();
+            atomicAdd(p.grid_barrier + 1, 1u);
+        } else {
+            uint32_t spin = 0;
+            while (*generation == before) {
+                if (++spin > kGridWaitLimit || ((spin & 255u) == 255u && *abort_flag)) {
+                    *abort_flag = 1;
+                    atomicCAS(p.status_word, 0u, kErrTcGridBarrier);
+                    break;
+                }
+            }
+        }
+        __threadfence();
+    }
+    workers_sync();
+    return *abort_flag == 0;
+}
+
+// ---- activation split (the four worker warps of every CTA; each CTA a slice) ------------------------------
+// One thread per pair of neighbouring activation elements (one byte of codes per term), eight neighbouring lanes
+// per 16-element group. Term 0 divides by 2^(e - 7), e the exponent of the token row's largest magnitude: its
+// block scales come out below 43 (E4M3 reaches 448) and groups down to 2^-13 of the row's largest still get a
+// normal scale; every further term divides by 8 times less. Per term: the group's largest magnitude by shuffles,
+// an E4M3 scale that covers it (the smallest one, or its neighbour: the quotient by six is rounded up a little
+// instead of divided exactly), the nearest E2M1 level of each element (from an approximate reciprocal: any level
+// next to the quotient will do, because the residual is formed exactly from the level that was chosen), four
+// bytes gathered into a word.
+__device__ __forceinline__ void split_pairs(const TcPhase& ph, uint32_t tokens, uint32_t first_pair, uint32_t count, const float* term_scale,
+                                            uint32_t worker) {
+    const uint32_t lane = worker & 31, pairs_per_row = ph.cols / 2;
+    const uint8_t* sf_base = ph.split + split_code_bytes(ph.cols);
+    for (uint32_t base = 0; base < count; base += kWorkers) {
+        const bool active = base + worker < count;    // count is a multiple of 8: the eight lanes of a group are active together
+        const uint32_t pair = first_pair + (active ? base + worker : 0);
+        const uint32_t token = pair / pairs_per_row, k = (pair - token * pairs_per_row) * 2, group = k >> 4;
+        const uint32_t both = __ldcg(reinterpret_cast<const uint32_t*>(ph.x) + pair);
+        float r0 = __uint_as_float(both << 16), r1 = __uint_as_float(both & 0xffff0000u);
+        float scale = term_scale[token];
+        if (!(scale == scale)) scale = 1.0f;     // the codes of a non-finite row do not matter
+        // inverse of 6 * scale, rounded up a little: the quotient below is never under the exact one
+        float inverse = __uint_as_float(0x7f000000u - __float_as_uint(scale)) * 0x1.555558p-3f;
+        // destination of this group's codes (8 bytes; this lane's 4-lane half writes one word of it) and scale bytes
+        const uint32_t chunk = group >> 4, unit = (group & 15) >> 1, half = group & 1;
+        uint8_t* sf = const_cast<uint8_t*>(sf_base) + static_cast<uint64_t>(group >> 2) * kSfAtomBytes + (group & 3);
+        uint8_t* codes = ph.split + static_cast<uint64_t>(chunk) * kChunkBytes + half * 8 + ((lane >> 2) & 1) * 4;
+#pragma unroll
+        for (uint32_t term = 0; term < kTerms; ++term) {
+            float largest = fmaxf(fabsf(r0), fabsf(r1));
+            largest = fmaxf(largest, __shfl_xor_sync(0xffffffffu, largest, 4));
+            largest = fmaxf(largest, __shfl_xor_sync(0xffffffffu, largest, 2));
+            largest = fmaxf(largest, __shfl_xor_sync(0xffffffffu, largest, 1));
+            uint32_t scale_code = 0;
+            float divisor = 0.0f, q0 = 0.0f, q1 = 0.0f;
+            if (largest > 0.0f) {
+                scale_code = e4m3_ceil_code(largest * inverse);
+                divisor = e4m3_positive_value(scale_code) * scale;   // exact: four significant bits times a power of two
+                q0 = __fdividef(r0, divisor);
+                q1 = __fdividef(r1, divisor);
+            }
+            float l0, l1;
+            const uint32_t byte = e2m1_nearest(q0, &l0) | (e2m1_nearest(q1, &l1) << 4);
+            if (term + 1 < kTerms) {
+                r0 = __fsub_rn(r0, __fmul_rn(l0, divisor));   // both exact
+                r1 = __fsub_rn(r1, __fmul_rn(l1, divisor));
+            }
+            uint32_t word = byte << (8 * (lane & 3));
+            word |= __shfl_xor_sync(0xffffffffu, word, 1);
+            word |= __shfl_xor_sync(0xffffffffu, word, 2);
+            const uint32_t n = term * 8 + token;
+            if (active && (lane & 3) == 0) *reinterpret_cast<uint32_t*>(codes + (n >> 3) * 1024 + (n & 7) * 128 + ((unit ^ (n & 7)) << 4)) = word;
+            if (active && (lane & 7) == 0) sf[(n & 31) * 16 + (n >> 5) * 4] = static_cast<uint8_t>(scale_code);
+            scale *= 0.125f;
+            inverse *= 8.0f;
+        }
+    }
+}
 
 // Finished sums of 32 weight rows (lane = row) for the 8 tokens: scale, activation, rounding, store.
-__device__ __forceinline__ void finish_rows(const TcParams& p, uint32_t tile, uint32_t quadrant, uint32_t lane, const float (&y)[8]) {
-    if (p.epilogue == AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16) {
+__device__ __forceinline__ void finish_rows(const TcPhase& ph, uint32_t tokens, uint32_t tile, uint32_t quadrant, uint32_t lane,
+                                            const float (&y)[8], uint32_t* collected) {
+    if (ph.epilogue == AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16) {
         // 32 physical rows = 16 gate rows (lanes 0..15) and the matching 16 up rows (lanes 16..31)
-        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
+        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(ph.out);
         const uint32_t index = (tile * kTileM + quadrant * 32) / 2 + (lane & 15);
 #pragma unroll
         for (uint32_t token = 0; token < 8; ++token) {
-            const float up = __shfl_sync(0xffffffffu, y[token], (lane & 15) + 16) * p.global_b;
-            const float gate = y[token] * p.global_a;
-            if (lane < 16 && token < p.tokens) {
-                out[static_cast<uint64_t>(token) * p.out_rows + index] = __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
+            const float up = __shfl_sync(0xffffffffu, y[token], (lane & 15) + 16) * ph.global_b;
+            const float gate = y[token] * ph.global_a;
+            uint32_t magnitude = 0;
+            if (lane < 16 && token < tokens) {
+                const __nv_bfloat16 h = __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
+                out[static_cast<uint64_t>(token) * ph.out_rows + index] = h;
+                magnitude = static_cast<uint32_t>(__bfloat16_as_ushort(h) & 0x7fffu) << 16;
+            }
+            if (ph.collect) {
+                // the next phase splits these values: it needs every token row's largest magnitude
+                magnitude = __reduce_max_sync(0xffffffffu, magnitude);
+                if (lane == 0 && magnitude) atomicMax(&collected[token], magnitude);
             }
         }
         return;
@@ -100,44 +228,44 @@ __device__ __forceinline__ void finish_rows(const TcParams& p, uint32_t tile, ui
     const uint32_t row = tile * kTileM + quadrant * 32 + lane;
 #pragma unroll
     for (uint32_t token = 0; token < 8; ++token) {
-        if (token < p.tokens) {
-            const float value = y[token] * p.global_a;
-            if (p.epilogue == AUGUR_NVFP4_SM100_EPILOGUE_LINEAR_F32) {
-                static_cast<float*>(p.out)[static_cast<uint64_t>(token) * p.out_rows + row] = value;
+        if (token < tokens) {
+            const float value = y[token] * ph.global_a;
+            if (ph.epilogue == AUGUR_NVFP4_SM100_EPILOGUE_LINEAR_F32) {
+                static_cast<float*>(ph.out)[static_cast<uint64_t>(token) * ph.out_rows + row] = value;
             } else {
-                static_cast<__nv_bfloat16*>(p.out)[static_cast<uint64_t>(token) * p.out_rows + row] = __float2bfloat16_rn(value);
+                static_cast<__nv_bfloat16*>(ph.out)[static_cast<uint64_t>(token) * ph.out_rows + row] = __float2bfloat16_rn(value);
             }
         }
     }
 }
 
-// This CTA's share of 32 rows of `tile`: finished here if there is one slab, else handed over; the last of
-// the `slabs` arrivals adds all shares in slab order. Whole warps call this.
-__device__ __forceinline__ void contribute_rows(const TcParams& p, uint32_t tile, uint32_t quadrant, uint32_t slab, uint32_t lane,
-                                                const float (&y)[8]) {
-    if (p.slabs == 1) {
-        finish_rows(p, tile, quadrant, lane, y);
+// This CTA's share of 32 rows of `tile`: finished here if tiles are whole, else handed over; the last of the
+// `parts` arrivals adds all shares in part order. Whole warps call this.
+__device__ __forceinline__ void contribute_rows(const TcPhase& ph, uint32_t tokens, uint32_t tile, uint32_t quadrant, uint32_t part,
+                                                uint32_t lane, const float (&y)[8], uint32_t* collected) {
+    if (ph.parts == 1) {
+        finish_rows(ph, tokens, tile, quadrant, lane, y, collected);
         return;
     }
     const uint32_t group = tile * 4 + quadrant;
-    float* slots = p.partials + static_cast<uint64_t>(group) * p.slabs * kSlotFloats;
-    float4* mine = reinterpret_cast<float4*>(slots + static_cast<uint64_t>(slab) * kSlotFloats) + lane * 2;
+    float* slots = ph.partials + static_cast<uint64_t>(group) * ph.parts * kSlotFloats;
+    float4* mine = reinterpret_cast<float4*>(slots + static_cast<uint64_t>(part) * kSlotFloats) + lane * 2;
     mine[0] = make_float4(y[0], y[1], y[2], y[3]);
     mine[1] = make_float4(y[4], y[5], y[6], y[7]);
     __threadfence();
     __syncwarp();
     uint32_t arrived = 0;
-    if (lane == 0) arrived = atomicAdd(&p.counters[group], 1u);
+    if (lane == 0) arrived = atomicAdd(&ph.counters[group], 1u);
     arrived = __shfl_sync(0xffffffffu, arrived, 0);
-    if (arrived + 1 != p.slabs) return;
+    if (arrived + 1 != ph.parts) return;
     __threadfence();
     float sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (uint32_t s0 = 0; s0 < p.slabs; s0 += 4) {
+    for (uint32_t s0 = 0; s0 < ph.parts; s0 += 4) {
         float4 a[4], b[4];
 #pragma unroll
         for (uint32_t j = 0; j < 4; ++j) {
             a[j] = b[j] = make_float4(0, 0, 0, 0);
-            if (s0 + j < p.slabs) {
+            if (s0 + j < ph.parts) {
                 const float4* slot = reinterpret_cast<const float4*>(slots + static_cast<uint64_t>(s0 + j) * kSlotFloats) + lane * 2;
                 a[j] = __ldcg(slot);
                 b[j] = __ldcg(slot + 1);
@@ -145,36 +273,101 @@ __device__ __forceinline__ void contribute_rows(const TcParams& p, uint32_t tile
         }
 #pragma unroll
         for (uint32_t j = 0; j < 4; ++j) {
-            if (s0 + j < p.slabs) {
+            if (s0 + j < ph.parts) {
                 sum[0] += a[j].x; sum[1] += a[j].y; sum[2] += a[j].z; sum[3] += a[j].w;
                 sum[4] += b[j].x; sum[5] += b[j].y; sum[6] += b[j].z; sum[7] += b[j].w;
             }
         }
     }
-    finish_rows(p, tile, quadrant, lane, sum);
-    if (lane == 0) p.counters[group] = 0;   // clean for the next launch
+    finish_rows(ph, tokens, tile, quadrant, lane, sum, collected);
+    if (lane == 0) ph.counters[group] = 0;   // clean for the next launch
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
-gemv_tc_kernel(const __grid_constant__ CUtensorMap map_weight, const TcParams p) {
+// A CTA's ring stages in the order it streams them: over the phases, over its (tile, part) items blockIdx.x,
+// blockIdx.x + gridDim.x, ... of a phase, over the k blocks of an item.
+struct Cursor {
+    uint32_t phase, index, tile, part, kb, kb0, kb1;
+};
+__device__ __forceinline__ bool cursor_load(const TcParams& p, Cursor& c) {
+    while (c.phase < p.phases) {
+        const TcPhase& ph = p.phase[c.phase];
+        const uint32_t item = blockIdx.x + c.index * gridDim.x;
+        if (item < ph.tiles * ph.parts) {
+            c.tile = item / ph.parts;
+            c.part = item - c.tile * ph.parts;
+            c.kb0 = c.part * ph.k_blocks / ph.parts;
+            c.kb1 = (c.part + 1) * ph.k_blocks / ph.parts;
+            c.kb = c.kb0;
+            return true;
+        }
+        ++c.phase;
+        c.index = 0;
+    }
+    return false;
+}
+__device__ __forceinline__ bool cursor_begin(const TcParams& p, Cursor& c) {
+    c = Cursor{0, 0, 0, 0, 0, 0, 0};
+    return cursor_load(p, c);
+}
+__device__ __forceinline__ bool cursor_next(const TcParams& p, Cursor& c) {
+    if (++c.kb < c.kb1) return true;
+    ++c.index;
+    return cursor_load(p, c);
+}
+
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
+tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1, const TcParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* act_codes = smem + kStages * kStageBytes;            // [chunk][48 rows][128 bytes], 128-byte swizzle
-    uint8_t* act_sf = act_codes + kActCodeBytes;                   // [64-k step] x 512-byte atoms
-    float* term_scale = reinterpret_cast<float*>(act_sf + kActSfBytes);   // [token]: scale of term 0 (a power of two)
-    uint32_t* row_max = reinterpret_cast<uint32_t*>(term_scale + 8);      // [token]: bits of the largest magnitude; [8..16): a NaN or infinity seen
-    uint64_t* bars = reinterpret_cast<uint64_t*>(row_max + 16);           // full[S], empty[S], acc_full[2], acc_empty[2]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+    float* term_scale = reinterpret_cast<float*>(smem + kStages * kStageBytes);   // [token]: scale of term 0 in the current phase
+    uint32_t* row_max = reinterpret_cast<uint32_t*>(term_scale + 8);              // [token]: this CTA's share of a scan
+    uint32_t* collected = row_max + 8;                                             // [token]: largest magnitudes of this CTA's SwiGLU outputs
+    volatile uint32_t* acts_ready = collected + 8;                                 // [phase]: the phase's split activations are complete
+    // full[S] (operand codes landed), empty[S], scales_landed[S], scales_ready[S] (copies to tensor memory issued),
+    // acc_full[2], acc_empty[2]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(const_cast<uint32_t*>(acts_ready) + 2);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * kStages + 4);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + kStages);
-    const uint32_t bar_acc_full = smem_u32(bars + 2 * kStages), bar_acc_empty = smem_u32(bars + 2 * kStages + 2);
+    const uint32_t bar_scales_landed = smem_u32(bars + 2 * kStages), bar_scales_ready = smem_u32(bars + 3 * kStages);
+    const uint32_t bar_acc_full = smem_u32(bars + 4 * kStages), bar_acc_empty = smem_u32(bars + 4 * kStages + 2);
 
+    auto issue_weights = [&](uint32_t stage, const Cursor& c) {
+        const TcPhase& ph = p.phase[c.phase];
+        const uint32_t k_valid = min(kStageK, ph.cols - c.kb * kStageK);
+        const uint32_t sf_bytes = k_valid / 64 * kSfAtomBytes;
+        const uint32_t dst = smem_u32(smem + stage * kStageBytes);
+        // the scales first, on a barrier of their own: they are small, land early, and the copy thread moves
+        // them on to tensor memory while the codes are still on their way
+        mbar_expect_tx(bar_scales_landed + 8 * stage, sf_bytes);
+        bulk_load(dst + kStageCodeBytes, ph.weight_sf + (static_cast<uint64_t>(c.tile) * (ph.cols / 64) + c.kb * 4) * kSfAtomBytes, sf_bytes,
+                  bar_scales_landed + 8 * stage);
+        mbar_expect_tx(bar_full + 8 * stage, kStageCodeBytes);
+        tma_load_2d(dst, c.phase ? &map1 : &map0, c.kb * 128, c.tile * kTileM, bar_full + 8 * stage);
+    };
+    auto issue_activations = [&](uint32_t stage, const Cursor& c) {
+        const TcPhase& ph = p.phase[c.phase];
+        const uint32_t k_valid = min(kStageK, ph.cols - c.kb * kStageK);
+        const uint32_t sf_bytes = k_valid / 64 * kSfAtomBytes;
+        const uint32_t dst = smem_u32(smem + stage * kStageBytes);
+        mbar_expect_tx(bar_scales_landed + 8 * stage, sf_bytes);
+        bulk_load(dst + kStageActSf, ph.split + split_code_bytes(ph.cols) + static_cast<uint64_t>(c.kb) * kStageSfBytes, sf_bytes,
+                  bar_scales_landed + 8 * stage);
+        mbar_expect_tx(bar_full + 8 * stage, kChunkBytes);
+        bulk_load(dst + kStageActCodes, ph.split + static_cast<uint64_t>(c.kb) * kChunkBytes, kChunkBytes, bar_full + 8 * stage);
+    };
+
+    Cursor weights_at;               // the producer's place in the weight stream (thread 0 only)
+    bool weights_left = false;
+    uint32_t weights_issued = 0;
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kStages; ++s) {
-            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_full + 8 * s, 2);            // the weight half and the activation half of a stage are announced separately
+            mbar_init(bar_scales_landed + 8 * s, 2);   // likewise for their block scales, which land first
+            mbar_init(bar_scales_ready + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, 1);
         }
         for (uint32_t b = 0; b < 2; ++b) {
@@ -182,9 +375,19 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_weight, const TcParams p)
             mbar_init(bar_acc_empty + 8 * b, 4);   // one arrival per epilogue warp
         }
         *abort_flag = 0;
+        acts_ready[0] = acts_ready[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // The weight halves of the first ring fill go out at once, before anything else is set up: weights depend
+        // on nothing, so HBM is busy while this CTA allocates tensor memory, while the launch before this one
+        // finishes, and while the activations are split.
+        weights_left = cursor_begin(p, weights_at);
+        while (weights_left && weights_issued < kStages) {
+            issue_weights(weights_issued, weights_at);
+            ++weights_issued;
+            weights_left = cursor_next(p, weights_at);
+        }
     }
-    if (threadIdx.x < 16) row_max[threadIdx.x] = 0;
+    if (threadIdx.x >= 64 && threadIdx.x < 64 + 16) row_max[threadIdx.x - 64] = 0;   // row_max and collected
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemColumns)
                      : "memory");
@@ -195,177 +398,207 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_weight, const TcParams p)
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    // ---- this CTA's slab and tiles ----
-    const uint32_t base = gridDim.x / p.slabs, extra = gridDim.x % p.slabs;   // the first `extra` slabs have one CTA more
-    uint32_t slab, place, sharers;
-    if (blockIdx.x < extra * (base + 1)) {
-        slab = blockIdx.x / (base + 1); place = blockIdx.x % (base + 1); sharers = base + 1;
-    } else {
-        const uint32_t rest = blockIdx.x - extra * (base + 1);
-        slab = extra + rest / base; place = rest % base; sharers = base;
-    }
-    const uint32_t tile0 = place * p.tiles / sharers, tile1 = (place + 1) * p.tiles / sharers;
-    const uint32_t kb0 = slab * p.k_blocks / p.slabs, kb1 = (slab + 1) * p.k_blocks / p.slabs;
-    const uint32_t slab_stages = kb1 - kb0;
-    const uint32_t k0 = kb0 * kStageK;
-    const uint32_t slab_k = (kb1 * kStageK < p.cols ? kb1 * kStageK : p.cols) - k0;    // a multiple of 64
-    const uint32_t total_steps = (tile1 - tile0) * slab_stages;                       // ring stages this CTA streams
-    const uint32_t atoms_per_row_block = p.cols / 64;
-
-    auto issue_stage = [&](uint32_t step) {
-        const uint32_t tile = tile0 + step / slab_stages, kb = kb0 + step % slab_stages, stage = step % kStages;
-        const uint32_t k_valid = min(kStageK, p.cols - kb * kStageK);
-        const uint32_t sf_bytes = k_valid / 64 * kSfAtomBytes;
-        const uint32_t dst = smem_u32(smem + stage * kStageBytes), full = bar_full + 8 * stage;
-        mbar_expect_tx(full, kStageCodeBytes + sf_bytes);
-        tma_load_2d(dst, &map_weight, kb * 128, tile * kTileM, full);
-        bulk_load(dst + kStageCodeBytes, p.weight_sf + (static_cast<uint64_t>(tile) * atoms_per_row_block + kb * 4) * kSfAtomBytes,
-                  sf_bytes, full);
-    };
-    // The first ring fill goes out before anything else: weights do not depend on the launch before this one,
-    // so HBM is busy while that launch drains and while the activations are split below.
-    if (threadIdx.x == 0) {
-        const uint32_t first = total_steps < kStages ? total_steps : kStages;
-        for (uint32_t step = 0; step < first; ++step) issue_stage(step);
-    }
-
-    // ---- split the slab's activations into residual NVFP4 terms (all warps) ----
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    const uint32_t groups = slab_k / 16, items = p.tokens * groups;
-    for (uint32_t i = threadIdx.x; i < items; i += kThreads) {
-        const uint32_t token = i / groups, group = i - token * groups;
-        const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<uint64_t>(token) * p.cols + k0 + group * 16);
-        const uint4 lo = __ldcg(src), hi = __ldcg(src + 1);
-        const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-        uint32_t largest = 0;
-#pragma unroll
-        for (uint32_t j = 0; j < 8; ++j) {
-            largest = max(largest, max((w[j] << 16) & 0x7fff0000u, w[j] & 0x7fff0000u));   // magnitudes order like their bit patterns
-        }
-        if (largest >= 0x7f800000u) row_max[8 + token] = 1;
-        atomicMax(&row_max[token], largest);
-    }
-    __syncthreads();
-    if (threadIdx.x < 8) {
-        // term 0 divides by 2^(e - 7), e the exponent of the row's largest magnitude: its block scales come out
-        // below 43 (E4M3 reaches 448) and groups down to 2^-13 of the row's largest still get a normal scale.
-        // Every further term divides by 8 times less. Clamped so that all six stay normal f32 numbers.
-        int field = static_cast<int>(row_max[threadIdx.x] >> 23);
-        field = field < 30 ? 30 : (field > 250 ? 250 : field);
-        float scale = __uint_as_float(static_cast<uint32_t>(field - 7) << 23);
-        if (row_max[8 + threadIdx.x]) scale = __uint_as_float(0x7fc00000u);   // a NaN or infinity in the row: the row's outputs are NaN
-        term_scale[threadIdx.x] = scale;
-    }
-    __syncthreads();
-    for (uint32_t i = threadIdx.x; i < items; i += kThreads) {
-        const uint32_t token = i / groups, group = i - token * groups;
-        const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<uint64_t>(token) * p.cols + k0 + group * 16);
-        const uint4 lo = __ldcg(src), hi = __ldcg(src + 1);
-        const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-        float residual[16];
-#pragma unroll
-        for (uint32_t j = 0; j < 8; ++j) {
-            residual[2 * j] = __uint_as_float(w[j] << 16);
-            residual[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
-        }
-        float scale = term_scale[token];
-        if (!(scale == scale)) scale = 1.0f;     // the codes of a non-finite row do not matter
-        const uint32_t chunk = group >> 4, unit = (group & 15) >> 1, half = group & 1;
-#pragma unroll
-        for (uint32_t term = 0; term < kTerms; ++term) {
-            uint32_t packed[2], scale_code;
-            quantise_term(residual, scale, term + 1 < kTerms, packed, &scale_code);
-            scale *= 0.125f;
-            const uint32_t n = term * 8 + token;
-            uint8_t* row = act_codes + chunk * kChunkBytes + (n >> 3) * 1024 + (n & 7) * 128;
-            *reinterpret_cast<uint2*>(row + ((unit ^ (n & 7)) << 4) + half * 8) = make_uint2(packed[0], packed[1]);
-            act_sf[(group >> 2) * kSfAtomBytes + (n & 31) * 16 + (n >> 5) * 4 + (group & 3)] = static_cast<uint8_t>(scale_code);
-        }
-    }
-    // the tensor core reads shared memory through the asynchronous proxy
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    __syncthreads();
-
     if (warp == 0 && lane == 0) {
-        // ---------------- TMA producer: the rest of the stream ----------------
-        uint32_t phase = 0;
-        for (uint32_t step = kStages; step < total_steps; ++step) {
-            const uint32_t stage = step % kStages;
-            if (!mbar_wait(bar_empty + 8 * stage, phase, abort_flag, p.status_word, kErrTcProducer)) break;
-            issue_stage(step);
-            if (stage == kStages - 1) phase ^= 1;
+        // ---------------- TMA producer ----------------
+        // Weight halves run ahead as far as the ring allows; the activation half of a stage follows as soon as its
+        // phase's split activations are complete. Neither waits for the other.
+        Cursor acts_at;
+        bool acts_left = cursor_begin(p, acts_at);
+        uint32_t acts_issued = 0, idle = 0;
+        while (acts_left) {
+            bool progressed = false;
+            if (weights_left) {
+                // stage of step `weights_issued`: free once the MMAs of the step kStages before it are complete
+                const uint32_t stage = weights_issued % kStages, round = weights_issued / kStages;
+                if (mbar_test(bar_empty + 8 * stage, (round - 1) & 1)) {
+                    issue_weights(stage, weights_at);
+                    ++weights_issued;
+                    weights_left = cursor_next(p, weights_at);
+                    progressed = true;
+                }
+            }
+            if (acts_issued < weights_issued && acts_ready[acts_at.phase]) {
+                // the split activations were written with ordinary stores, by this and other CTAs
+                asm volatile("fence.proxy.async;" ::: "memory");
+                issue_activations(acts_issued % kStages, acts_at);
+                ++acts_issued;
+                acts_left = cursor_next(p, acts_at);
+                progressed = true;
+            }
+            if (progressed) {
+                idle = 0;
+            } else if (++idle > kWaitLimit || ((idle & 1023u) == 1023u && *abort_flag)) {
+                *abort_flag = 1;
+                atomicCAS(p.status_word, 0u, kErrTcProducer);
+                break;
+            }
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer ----------------
         const uint32_t idesc = instr_desc(kCols);
-        const uint32_t tmem_sf_act = tmem_base + kTmemSfAct;
-        // the activations' block scales: tensor-memory resident for the whole launch
-        for (uint32_t a = 0; a < slab_k / 64; ++a) tc_copy_sf(tmem_sf_act + 4 * a, sf_desc(smem_u32(act_sf) + a * kSfAtomBytes));
-        const uint64_t act_desc0 = operand_desc(smem_u32(act_codes));
-        uint32_t step = 0, phase = 0;
+        uint32_t step = 0, item_count = 0;
+        uint32_t acc_phase[2] = {0, 0};
+        Cursor c;
+        bool more = cursor_begin(p, c);
+        while (more) {
+            const uint32_t buffer = item_count & 1;
+            if (c.kb == c.kb0) {
+                // the epilogue must have drained this buffer (two items ago)
+                if (!mbar_wait(bar_acc_empty + 8 * buffer, acc_phase[buffer] ^ 1, abort_flag, p.status_word, kErrTcAccEmpty)) break;
+                tc_fence_after();
+            }
+            const uint32_t acc = tmem_base + kTmemAcc + buffer * 64;
+            const uint32_t stage = step % kStages, parity = (step / kStages) & 1;
+            // operands in shared memory (TMA) and their block scales on the way to tensor memory (copy thread):
+            // a copy and a later MMA execute in issue order, so the copies only have to be issued
+            if (!mbar_wait(bar_full + 8 * stage, parity, abort_flag, p.status_word, kErrTcFull) ||
+                !mbar_wait(bar_scales_ready + 8 * stage, parity, abort_flag, p.status_word, kErrTcScalesReady)) {
+                break;
+            }
+            tc_fence_after();
+            const uint32_t stage_smem = smem_u32(smem + stage * kStageBytes);
+            const uint64_t weight_desc = operand_desc(stage_smem), act_desc = operand_desc(stage_smem + kStageActCodes);
+            const uint32_t tmem_sf_weight = tmem_base + kTmemSfWeight + stage * 16, tmem_sf_act = tmem_base + kTmemSfAct + stage * 16;
+            const uint32_t k_steps = min(kStageK, p.phase[c.phase].cols - c.kb * kStageK) / 64;
+            // each MMA consumes 64 k = 32 bytes of every row: advance the start address by 32 >> 4
+            if (k_steps == 4) {
+#pragma unroll
+                for (uint32_t k = 0; k < 4; ++k) {
+                    tc_mma(acc, weight_desc + 2 * k, act_desc + 2 * k, idesc, tmem_sf_weight + 4 * k, tmem_sf_act + 4 * k,
+                           (c.kb != c.kb0 || k != 0) ? 1u : 0u);
+                }
+            } else {
+                for (uint32_t k = 0; k < k_steps; ++k) {
+                    tc_mma(acc, weight_desc + 2 * k, act_desc + 2 * k, idesc, tmem_sf_weight + 4 * k, tmem_sf_act + 4 * k,
+                           (c.kb != c.kb0 || k != 0) ? 1u : 0u);
+                }
+            }
+            tc_commit(bar_empty + 8 * stage);   // frees the stage when these MMAs have read it
+            if (c.kb + 1 == c.kb1) {
+                tc_commit(bar_acc_full + 8 * buffer);
+                acc_phase[buffer] ^= 1;
+                ++item_count;
+            }
+            ++step;
+            more = cursor_next(p, c);
+        }
+    } else if (warp == 6 && lane == 0) {
+        // ---------------- scale copies: shared memory -> tensor memory, as soon as a stage's scales have landed ----------------
+        // A stage's scale columns in tensor memory are free when its scales land again: the producer refilled the
+        // stage only after the MMAs that read those columns were complete.
+        uint32_t step = 0;
+        Cursor c;
+        bool more = cursor_begin(p, c);
+        while (more) {
+            const uint32_t stage = step % kStages, parity = (step / kStages) & 1;
+            if (!mbar_wait(bar_scales_landed + 8 * stage, parity, abort_flag, p.status_word, kErrTcScalesLanded)) break;
+            tc_fence_after();
+            const uint32_t stage_smem = smem_u32(smem + stage * kStageBytes);
+            const uint64_t weight_sf_desc = sf_desc(stage_smem + kStageCodeBytes), act_sf_desc = sf_desc(stage_smem + kStageActSf);
+            const uint32_t tmem_sf_weight = tmem_base + kTmemSfWeight + stage * 16, tmem_sf_act = tmem_base + kTmemSfAct + stage * 16;
+            const uint32_t k_steps = min(kStageK, p.phase[c.phase].cols - c.kb * kStageK) / 64;
+            if (k_steps == 4) {
+#pragma unroll
+                for (uint32_t k = 0; k < 4; ++k) {
+                    tc_copy_sf(tmem_sf_weight + 4 * k, weight_sf_desc + k * (kSfAtomBytes >> 4));
+                    tc_copy_sf(tmem_sf_act + 4 * k, act_sf_desc + k * (kSfAtomBytes >> 4));
+                }
+            } else {
+                for (uint32_t k = 0; k < k_steps; ++k) {
+                    tc_copy_sf(tmem_sf_weight + 4 * k, weight_sf_desc + k * (kSfAtomBytes >> 4));
+                    tc_copy_sf(tmem_sf_act + 4 * k, act_sf_desc + k * (kSfAtomBytes >> 4));
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(bar_scales_ready + 8 * stage);
+            ++step;
+            more = cursor_next(p, c);
+        }
+    } else if (warp >= 2 && warp < 6) {
+        // ---------------- workers: split the activations of a phase, then run its epilogues ----------------
+        const uint32_t worker = threadIdx.x - 64, quadrant = warp & 3;   // tensor-memory lanes of this warp: 32 * quadrant .. + 31
+        const bool leader = worker == 0;
+        uint32_t item_count = 0;
         uint32_t acc_phase[2] = {0, 0};
         bool alive = true;
-        for (uint32_t tile = tile0; alive && tile < tile1; ++tile) {
-            const uint32_t buffer = (tile - tile0) & 1;
-            // the epilogue must have drained this buffer (two tiles ago)
-            if (!mbar_wait(bar_acc_empty + 8 * buffer, acc_phase[buffer] ^ 1, abort_flag, p.status_word, kErrTcAccEmpty)) break;
-            tc_fence_after();
-            const uint32_t acc = tmem_base + kTmemAcc + buffer * 64;
-            for (uint32_t s = 0; s < slab_stages; ++s, ++step) {
-                const uint32_t stage = step % kStages;
-                if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status_word, kErrTcFull)) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");   // the activations may come from the launch before this one; all stores follow
+        for (uint32_t phase = 0; alive && phase < p.phases; ++phase) {
+            const TcPhase& ph = p.phase[phase];
+            // every CTA has finished the phase before (its output is this phase's input, its maxima are collected)
+            if (phase != 0 && !grid_meet(p, leader, abort_flag)) break;
+            // this CTA's slice of the activations, in whole 16-element groups
+            const uint32_t groups = p.tokens * (ph.cols / 16);
+            const uint32_t first_pair = static_cast<uint32_t>(static_cast<uint64_t>(blockIdx.x) * groups / gridDim.x) * 8;
+            const uint32_t count = static_cast<uint32_t>(static_cast<uint64_t>(blockIdx.x + 1) * groups / gridDim.x) * 8 - first_pair;
+            if (ph.scan) {
+                for (uint32_t i = worker; i < count; i += kWorkers) {
+                    const uint32_t pair = first_pair + i;
+                    const uint32_t both = __ldcg(reinterpret_cast<const uint32_t*>(ph.x) + pair);
+                    atomicMax(&row_max[pair / (ph.cols / 2)], max((both << 16) & 0x7fff0000u, both & 0x7fff0000u));   // magnitudes order like their bit patterns
+                }
+                workers_sync();
+                if (worker < 8 && row_max[worker]) atomicMax(ph.row_max + worker, row_max[worker]);
+                if (!grid_meet(p, leader, abort_flag)) break;
+            }
+            if (worker < 8) {
+                const uint32_t largest = *static_cast<volatile uint32_t*>(ph.row_max + worker);
+                int field = static_cast<int>(largest >> 23);
+                field = field < 30 ? 30 : (field > 250 ? 250 : field);    // all six term scales stay normal f32 numbers
+                float scale = __uint_as_float(static_cast<uint32_t>(field - 7) << 23);
+                if (largest >= 0x7f800000u) scale = __uint_as_float(0x7fc00000u);   // a NaN or infinity in the row: the row's outputs are NaN
+                term_scale[worker] = scale;
+                row_max[worker] = 0;
+            }
+            workers_sync();
+            split_pairs(ph, p.tokens, first_pair, count, term_scale, worker);
+            // every CTA's slice is in place (and readable by the TMA engine) before any CTA loads from the split
+            asm volatile("fence.proxy.async;" ::: "memory");
+            if (!grid_meet(p, leader, abort_flag)) break;
+            if (blockIdx.x == 0 && worker < 8) ph.row_max[worker] = 0;   // every CTA has read them: clean for the next launch
+            if (leader) acts_ready[phase] = 1;
+
+            // ---- epilogues of this CTA's items of the phase ----
+            const uint32_t items = ph.tiles * ph.parts;
+            for (uint32_t item = blockIdx.x; item < items; item += gridDim.x, ++item_count) {
+                const uint32_t tile = item / ph.parts, part = item - tile * ph.parts;
+                const uint32_t buffer = item_count & 1;
+                if (!mbar_wait(bar_acc_full + 8 * buffer, acc_phase[buffer], abort_flag, p.status_word, kErrTcAccFull)) {
                     alive = false;
                     break;
                 }
+                acc_phase[buffer] ^= 1;
                 tc_fence_after();
-                const uint32_t stage_smem = smem_u32(smem + stage * kStageBytes);
-                const uint64_t weight_desc = operand_desc(stage_smem), act_desc = act_desc0 + s * (kChunkBytes >> 4);
-                const uint32_t tmem_sf_weight = tmem_base + kTmemSfWeight + stage * 16;
-                const uint32_t k_steps = min(kStageK, slab_k - s * kStageK) / 64;
-                for (uint32_t k = 0; k < k_steps; ++k) {
-                    tc_copy_sf(tmem_sf_weight + 4 * k, sf_desc(stage_smem + kStageCodeBytes + k * kSfAtomBytes));
-                    // each MMA consumes 64 k = 32 bytes of every row: advance the start address by 32 >> 4
-                    tc_mma(acc, weight_desc + 2 * k, act_desc + 2 * k, idesc, tmem_sf_weight + 4 * k, tmem_sf_act + 4 * (s * 4 + k),
-                           (s | k) ? 1u : 0u);
-                }
-                tc_commit(bar_empty + 8 * stage);   // frees the stage when these MMAs have read it
-                if (stage == kStages - 1) phase ^= 1;
-            }
-            if (alive) tc_commit(bar_acc_full + 8 * buffer);
-            acc_phase[buffer] ^= 1;
-        }
-    } else if (warp >= 2 && warp < 6) {
-        // ---------------- epilogue: accumulator -> sums per token -> finished rows or a partial ----------------
-        const uint32_t quadrant = warp & 3;          // tensor-memory lanes this warp may read: 32 * quadrant .. + 31
-        uint32_t acc_phase[2] = {0, 0};
-        for (uint32_t tile = tile0; tile < tile1; ++tile) {
-            const uint32_t buffer = (tile - tile0) & 1;
-            if (!mbar_wait(bar_acc_full + 8 * buffer, acc_phase[buffer], abort_flag, p.status_word, kErrTcAccFull)) break;
-            acc_phase[buffer] ^= 1;
-            tc_fence_after();
-            uint32_t v[3][16];
-            const uint32_t taddr = tmem_base + kTmemAcc + buffer * 64 + ((quadrant * 32) << 16);
-            tc_load16(taddr, v[0]);
-            tc_load16(taddr + 16, v[1]);
-            tc_load16(taddr + 32, v[2]);
-            tc_wait_ld();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buffer);   // the buffer is free for the tile after next
-            float y[8];
+                uint32_t v[3][16];
+                const uint32_t taddr = tmem_base + kTmemAcc + buffer * 64 + ((quadrant * 32) << 16);
+                tc_load16(taddr, v[0]);
+                tc_load16(taddr + 16, v[1]);
+                tc_load16(taddr + 32, v[2]);
+                tc_wait_ld();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buffer);   // the buffer is free for the item after next
+                float y[8];
 #pragma unroll
-            for (uint32_t token = 0; token < 8; ++token) {
-                // column = term * 8 + token; term t carries the factor 8^-t relative to term 0
-                float sum = 0.0f, factor = 1.0f;
+                for (uint32_t token = 0; token < 8; ++token) {
+                    // column = term * 8 + token; term t carries the factor 8^-t relative to term 0
+                    float sum = 0.0f, factor = 1.0f;
 #pragma unroll
-                for (uint32_t term = 0; term < kTerms; ++term) {
-                    const uint32_t column = term * 8 + token;
-                    sum = fmaf(__uint_as_float(v[column >> 4][column & 15]), factor, sum);
-                    factor *= 0.125f;
+                    for (uint32_t term = 0; term < kTerms; ++term) {
+                        const uint32_t column = term * 8 + token;
+                        sum = fmaf(__uint_as_float(v[column >> 4][column & 15]), factor, sum);
+                        factor *= 0.125f;
+                    }
+                    y[token] = sum * term_scale[token];
                 }
-                y[token] = sum * term_scale[token];
+                contribute_rows(ph, p.tokens, tile, quadrant, part, lane, y, collected);
             }
-            contribute_rows(p, tile, quadrant, slab, lane, y);
+            if (ph.collect) {
+                workers_sync();
+                if (worker < 8) {
+                    if (collected[worker]) atomicMax(ph.collect + worker, collected[worker]);
+                    collected[worker] = 0;
+                }
+            }
         }
     }
 
@@ -379,36 +612,28 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_weight, const TcParams p)
 
 // ---- host side -------------------------------------------------------------------------------------
 struct TcGeometry {
-    uint32_t tiles, k_blocks, slabs, ctas;
+    uint32_t tiles, k_blocks, parts, ctas;
     uint64_t partial_bytes;
 };
 
-// Slabs: at least enough for a slab's activations to fit shared memory; more when there are fewer row tiles than
-// SMs (so that every SM streams) or when that evens out the load. The cost of a candidate is the number of ring
-// stages of its busiest CTA.
+// Whole tiles dealt round-robin over the resident CTAs (two per SM) when there are enough of them; otherwise every
+// tile is cut along k into as many equal parts as there are resident CTAs per tile (at least two ring stages per
+// part, at most 16 parts).
 TcGeometry tc_geometry(uint32_t physical_rows, uint32_t cols, uint32_t sm_count) {
     TcGeometry g{};
     g.tiles = physical_rows / kTileM;
     g.k_blocks = (cols + kStageK - 1) / kStageK;
-    const uint32_t least = (g.k_blocks + kMaxSlabStages - 1) / kMaxSlabStages;
-    uint64_t best_cost = UINT64_MAX;
-    for (uint32_t slabs = least; slabs <= g.k_blocks && slabs <= sm_count; ++slabs) {
-        const uint64_t items = static_cast<uint64_t>(g.tiles) * slabs;
-        const uint32_t ctas = items < sm_count ? static_cast<uint32_t>(items) : sm_count;
-        if (ctas < slabs) continue;
-        const uint32_t fewest_sharers = ctas / slabs;                                      // CTAs of the slabs that have one less
-        const uint32_t most_tiles = (g.tiles + fewest_sharers - 1) / fewest_sharers;
-        const uint32_t most_stages = (g.k_blocks + slabs - 1) / slabs;
-        // every slab costs each row group one hand-over (about a stage's time per eight of them at the end of the launch)
-        const uint64_t cost = static_cast<uint64_t>(most_tiles) * most_stages * 8 + slabs * 4;
-        if (cost < best_cost) {
-            best_cost = cost;
-            g.slabs = slabs;
-            g.ctas = ctas;
-        }
-        if (slabs >= least + 24) break;
+    g.parts = 1;
+    const uint32_t slots = sm_count * kCtasPerSm;   // CTAs resident at once
+    if (g.tiles < slots) {
+        uint32_t parts = slots / g.tiles;
+        if (parts > g.k_blocks / 2) parts = g.k_blocks / 2;
+        if (parts > 16) parts = 16;
+        if (parts > 1) g.parts = parts;
     }
-    g.partial_bytes = g.slabs > 1 ? static_cast<uint64_t>(g.tiles) * 4 * g.slabs * kSlotFloats * 4 : 0;
+    const uint64_t items = static_cast<uint64_t>(g.tiles) * g.parts;
+    g.ctas = items < slots ? static_cast<uint32_t>(items) : slots;
+    g.partial_bytes = g.parts > 1 ? static_cast<uint64_t>(g.tiles) * 4 * g.parts * kSlotFloats * 4 : 0;
     return g;
 }
 
@@ -428,9 +653,16 @@ bool check_tc_scalars(const augur_cuda_nvfp4_sm100_gemv_args_v1* a, uint32_t* ph
     return a->output_len_bytes == static_cast<uint64_t>(a->tokens) * a->rows * out_elem;
 }
 
-// `partial_offset` .. `partial_limit`: the part of the plan scratch this launch may use for its partial sums.
+uint32_t physical_rows_of(const augur_cuda_nvfp4_sm100_gemv_args_v1* a) {
+    return a->epilogue == AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16 ? 2 * a->rows : a->rows;
+}
+
+// What a phase needs of the plan scratch behind the counter regions: the split activations, then the partial sums.
+uint64_t tc_scratch_need(const TcGeometry& g, uint32_t cols) { return (split_bytes(cols) + 255) / 256 * 256 + g.partial_bytes; }
+
+// Scalars, extents, scratch room (`offset` .. `limit` of the plan scratch) and aliasing of one phase.
 bool check_tc(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* plan,
-              const augur_cuda_nvfp4_sm100_gemv_args_v1* a, uint64_t partial_offset, uint64_t partial_limit, bool full,
+              const augur_cuda_nvfp4_sm100_gemv_args_v1* a, uint64_t offset, uint64_t limit, bool full,
               augur_cuda_result_v1* failure) {
     *failure = invalid();
     if (!header_ok(d, s, a)) {
@@ -442,8 +674,8 @@ bool check_tc(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_pla
     uint32_t physical_rows = 0;
     if (!plan_ok(plan, d, s) || !check_tc_scalars(a, &physical_rows)) return false;
     const TcGeometry g = tc_geometry(physical_rows, a->cols, plan->sm_count);
-    if (!g.slabs || g.tiles * 4 > kMaxGroups || partial_offset < kCounterBytes || partial_limit < partial_offset ||
-        g.partial_bytes > partial_limit - partial_offset) {
+    if (g.tiles * 4 > kMaxGroups || offset < kCounterBytes || offset % 256 != 0 || limit < offset ||
+        tc_scratch_need(g, a->cols) > limit - offset) {
         return false;
     }
     const Range r[4] = {{a->weight, a->weight_len_bytes, 256}, {a->input_bf16, a->input_len_bytes, 16},
@@ -477,23 +709,45 @@ bool weight_map(CUtensorMap* map, uint64_t address, uint64_t rows, uint32_t cols
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The grid barrier and the row maxima of both phases live in the plan's header (the 256 bytes in front of the
+// scratch, behind the status word): no other kernel of the library writes there, plan creation zeroes them and
+// every launch leaves them clean.
+uint32_t* header_grid_barrier(const augur_cuda_nvfp4_sm100_plan_v1* plan) { return plan->status_word + 16; }
+uint32_t* header_row_max(const augur_cuda_nvfp4_sm100_plan_v1* plan, uint32_t phase) { return plan->status_word + 32 + 8 * phase; }
+
+// One launch for one or two phases (`b` null: one). Member m uses counter region m and the scratch at offsets[m].
 augur_cuda_result_v1 launch_tc(augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* plan,
-                               const augur_cuda_nvfp4_sm100_gemv_args_v1* a, uint32_t member, uint64_t partial_offset) {
-    const bool pair = a->epilogue == AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16;
-    const uint32_t physical_rows = pair ? 2 * a->rows : a->rows;
-    const TcGeometry g = tc_geometry(physical_rows, a->cols, plan->sm_count);
-    CUtensorMap map;
-    if (!weight_map(&map, a->weight, physical_rows, a->cols)) return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE);
+                               const augur_cuda_nvfp4_sm100_gemv_args_v1* a, const augur_cuda_nvfp4_sm100_gemv_args_v1* b,
+                               const uint64_t (&offsets)[2]) {
+    const augur_cuda_nvfp4_sm100_gemv_args_v1* members[2] = {a, b};
+    CUtensorMap maps[2];
     TcParams p{};
-    p.weight_sf = reinterpret_cast<const uint8_t*>(a->weight) + tcgen05_codes_bytes(physical_rows, a->cols);
-    p.x = reinterpret_cast<const uint16_t*>(a->input_bf16);
-    p.out = reinterpret_cast<void*>(a->output);
-    p.counters = reinterpret_cast<uint32_t*>(plan->scratch + member * kCounterRegionBytes);
-    p.partials = reinterpret_cast<float*>(plan->scratch + partial_offset);
+    p.phases = b ? 2 : 1;
+    p.tokens = a->tokens;
+    p.grid_barrier = header_grid_barrier(plan);
     p.status_word = plan->status_word;
-    p.rows = physical_rows; p.out_rows = a->rows; p.cols = a->cols; p.tokens = a->tokens; p.epilogue = a->epilogue;
-    p.tiles = g.tiles; p.k_blocks = g.k_blocks; p.slabs = g.slabs;
-    p.global_a = a->global_scale; p.global_b = a->global_scale_b;
+    uint32_t grid = 0;
+    for (uint32_t m = 0; m < p.phases; ++m) {
+        const augur_cuda_nvfp4_sm100_gemv_args_v1* args = members[m];
+        const uint32_t physical_rows = physical_rows_of(args);
+        const TcGeometry g = tc_geometry(physical_rows, args->cols, plan->sm_count);
+        if (!weight_map(&maps[m], args->weight, physical_rows, args->cols)) return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE);
+        TcPhase& ph = p.phase[m];
+        ph.weight_sf = reinterpret_cast<const uint8_t*>(args->weight) + tcgen05_codes_bytes(physical_rows, args->cols);
+        ph.x = reinterpret_cast<const uint16_t*>(args->input_bf16);
+        ph.split = plan->scratch + offsets[m];
+        ph.out = reinterpret_cast<void*>(args->output);
+        ph.counters = reinterpret_cast<uint32_t*>(plan->scratch + m * kCounterRegionBytes);
+        ph.partials = reinterpret_cast<float*>(plan->scratch + offsets[m] + (split_bytes(args->cols) + 255) / 256 * 256);
+        ph.row_max = header_row_max(plan, m);
+        ph.collect = (m == 0 && b) ? header_row_max(plan, 1) : nullptr;
+        ph.rows = physical_rows; ph.out_rows = args->rows; ph.cols = args->cols; ph.epilogue = args->epilogue;
+        ph.tiles = g.tiles; ph.k_blocks = g.k_blocks; ph.parts = g.parts;
+        ph.scan = m == 0 ? 1u : 0u;
+        ph.global_a = args->global_scale; ph.global_b = args->global_scale_b;
+        if (g.ctas > grid) grid = g.ctas;
+    }
+    if (!b) maps[1] = maps[0];
     cudaLaunchAttribute attribute{};
     attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attribute.val.programmaticStreamSerializationAllowed = 1;
@@ -501,10 +755,10 @@ augur_cuda_result_v1 launch_tc(augur_cuda_stream_t s, const augur_cuda_nvfp4_sm1
     config.stream = s->stream;
     config.attrs = &attribute;
     config.numAttrs = 1;
-    config.gridDim = dim3(g.ctas);
+    config.gridDim = dim3(grid);
     config.blockDim = dim3(kThreads);
     config.dynamicSmemBytes = kSmemBytes;
-    cudaLaunchKernelEx(&config, gemv_tc_kernel, map, p);
+    cudaLaunchKernelEx(&config, tc_program_kernel, maps[0], maps[1], p);
     count_launch();
     return submitted();
 }
@@ -512,7 +766,7 @@ augur_cuda_result_v1 launch_tc(augur_cuda_stream_t s, const augur_cuda_nvfp4_sm1
 }  // namespace
 
 cudaError_t gemv_tc_configure_device() {
-    return cudaFuncSetAttribute(gemv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    return cudaFuncSetAttribute(tc_program_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
 }
 
 }  // namespace augur_sm100
@@ -527,9 +781,9 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_tc_s
     uint64_t worst = 0;   // over any SM count up to 512
     for (uint32_t sms = 1; sms <= 512; ++sms) {
         const TcGeometry g = tc_geometry(static_cast<uint32_t>(physical), cols, sms);
-        if (g.partial_bytes > worst) worst = g.partial_bytes;
+        if (tc_scratch_need(g, cols) > worst) worst = tc_scratch_need(g, cols);
     }
-    *out_bytes = kCounterBytes + worst;
+    *out_bytes = kCounterBytes + (worst + 255) / 256 * 256;
     return ok();
 }
 
@@ -538,8 +792,7 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_tc_b
     augur_cuda_result_v1 failure;
     if (!check_tc(d, s, plan, a, kCounterBytes, plan ? plan->scratch_bytes : 0, true, &failure)) return failure;
     CUtensorMap probe;
-    const uint32_t physical = a->epilogue == AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16 ? 2 * a->rows : a->rows;
-    return weight_map(&probe, a->weight, physical, a->cols) ? ok() : make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE);
+    return weight_map(&probe, a->weight, physical_rows_of(a), a->cols) ? ok() : make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE);
 }
 
 extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_tc_bf16_prevalidated_submit_v1(
@@ -549,5 +802,68 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_tc_b
     if (consume_injected_fault()) return make_result(AUGUR_CUDA_STATUS_DIAGNOSTIC_FAULT_INJECTED);
     const cudaError_t e = cudaSetDevice(d);
     if (e != cudaSuccess) return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE, e);
-    return launch_tc(s, plan, a, 0, kCounterBytes);
+    const uint64_t offsets[2] = {kCounterBytes, 0};
+    return launch_tc(s, plan, a, nullptr, offsets);
+}
+
+// ---- the MLP block as one launch ----------------------------------------------------------------------
+namespace {
+// Both members plus every cross alias, before anything is enqueued; the members use separate counter regions and
+// separate halves of the scratch behind them.
+bool check_mlp_tc(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* plan,
+                  const augur_cuda_nvfp4_sm100_mlp_args_v1* a, bool full, uint64_t* down_offset, augur_cuda_result_v1* failure) {
+    *failure = invalid();
+    if (!header_ok(d, s, a)) {
+        if (a && s && d >= 0 && s->ordinal == d && a->abi_version != AUGUR_CUDA_ABI_VERSION_V1) {
+            *failure = make_result(AUGUR_CUDA_STATUS_ABI_VERSION_MISMATCH);
+        }
+        return false;
+    }
+    if (!plan_ok(plan, d, s) || plan->scratch_bytes < kCounterBytes) return false;
+    const uint64_t middle = kCounterBytes + (plan->scratch_bytes - kCounterBytes) / 2 / 256 * 256;
+    *down_offset = middle;
+    if (!check_tc(d, s, plan, &a->gate_up, kCounterBytes, middle, false, failure)) return false;
+    if (!check_tc(d, s, plan, &a->down, middle, plan->scratch_bytes, false, failure)) return false;
+    *failure = invalid();
+    if (a->gate_up.epilogue != AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16 || a->down.epilogue == AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16) {
+        return false;
+    }
+    // The intermediate is the one shared range: gate_up writes what down reads.
+    if (a->down.input_bf16 != a->gate_up.output || a->down.input_len_bytes != a->gate_up.output_len_bytes ||
+        a->down.cols != a->gate_up.rows || a->down.tokens != a->gate_up.tokens || a->down.rows != a->gate_up.cols) {
+        return false;
+    }
+    const Range r[6] = {{a->gate_up.weight, a->gate_up.weight_len_bytes, 256},
+                        {a->gate_up.input_bf16, a->gate_up.input_len_bytes, 16},
+                        {a->gate_up.output, a->gate_up.output_len_bytes, 16},
+                        {a->down.weight, a->down.weight_len_bytes, 256},
+                        {a->down.output, a->down.output_len_bytes, 4},
+                        plan_scratch_range(plan)};
+    if (!all_disjoint(r, 6)) return false;
+    return !full || inspect_device_ranges(d, r, 5, failure);
+}
+}  // namespace
+
+extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_mlp_tc_preflight_v1(
+    int32_t d, augur_cuda_stream_t s, augur_cuda_nvfp4_sm100_plan_v1* plan, const augur_cuda_nvfp4_sm100_mlp_args_v1* a) {
+    augur_cuda_result_v1 failure;
+    uint64_t down_offset = 0;
+    if (!check_mlp_tc(d, s, plan, a, true, &down_offset, &failure)) return failure;
+    CUtensorMap probe;
+    return weight_map(&probe, a->gate_up.weight, physical_rows_of(&a->gate_up), a->gate_up.cols) &&
+                   weight_map(&probe, a->down.weight, physical_rows_of(&a->down), a->down.cols)
+               ? ok()
+               : make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE);
+}
+
+extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_mlp_tc_prevalidated_submit_v1(
+    int32_t d, augur_cuda_stream_t s, augur_cuda_nvfp4_sm100_plan_v1* plan, const augur_cuda_nvfp4_sm100_mlp_args_v1* a) {
+    augur_cuda_result_v1 failure;
+    uint64_t down_offset = 0;
+    if (!check_mlp_tc(d, s, plan, a, false, &down_offset, &failure)) return failure;
+    if (consume_injected_fault()) return make_result(AUGUR_CUDA_STATUS_DIAGNOSTIC_FAULT_INJECTED);
+    const cudaError_t e = cudaSetDevice(d);
+    if (e != cudaSuccess) return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE, e);
+    const uint64_t offsets[2] = {kCounterBytes, down_offset};
+    return launch_tc(s, plan, &a->gate_up, &a->down, offsets);
 }

@@ -330,6 +330,49 @@ class Nvfp4Sm100TcProjection:
             s.ordinal, s.handle, self.plan.handle, byref(self.args)))
 
 
+def mlp_tc_scratch_bytes(hidden: int, intermediate: int) -> int:
+    """Plan scratch for the one-launch FFN program: counter regions plus one half of the rest per member."""
+    need = max(gemv_tc_scratch_bytes(intermediate, hidden, abi.EPILOGUE_SWIGLU_BF16), gemv_tc_scratch_bytes(hidden, intermediate))
+    return 2 * need + 512
+
+
+class Nvfp4Sm100TcFfnProgram:
+    """gate|up + SwiGLU, then down, as ONE launch on the tensor-memory path (`mlp_tc`): `gate_up` is the
+    interleaved tcgen05 weight of `upload_gate_up_interleaved`, `down` a tcgen05 weight. Same contract as
+    `Nvfp4Sm100FfnProgram` (qpn.rs:391-492): validated once at bind, `submit_for_plan` only enqueues."""
+
+    def __init__(self, plan: Plan, gate_up: Nvfp4Sm100Weight, down: Nvfp4Sm100Weight, x: torch.Tensor,
+                 intermediate: torch.Tensor, out: torch.Tensor, down_epilogue: int):
+        assert gate_up.layout == abi.LAYOUT_TCGEN05 and down.layout == abi.LAYOUT_TCGEN05
+        self.plan, self.gate_up, self.down = plan, gate_up, down
+        self.x, self.intermediate, self.out = x, intermediate, out
+        self.args = abi.header(abi.MlpArgs)
+        first = gemv_args(gate_up, x, intermediate, abi.EPILOGUE_SWIGLU_BF16)
+        first.rows = gate_up.rows // 2
+        second = gemv_args(down, intermediate, out, down_epilogue)
+        second.global_scale_b = 0.0
+        self.args.gate_up, self.args.down = first, second
+
+    @classmethod
+    def bind(cls, plan: Plan, gate_up: Nvfp4Sm100Weight, down: Nvfp4Sm100Weight, x: torch.Tensor,
+             out: torch.Tensor | None = None, down_epilogue: int = abi.EPILOGUE_LINEAR_BF16):
+        tokens = x.shape[0]
+        intermediate = torch.empty((tokens, gate_up.rows // 2), dtype=torch.bfloat16, device=x.device)
+        if out is None:
+            dtype = torch.float32 if down_epilogue == abi.EPILOGUE_LINEAR_F32 else torch.bfloat16
+            out = torch.empty((tokens, down.rows), dtype=dtype, device=x.device)
+        self = cls(plan, gate_up, down, x, intermediate, out, down_epilogue)
+        s = plan.stream
+        _check("mlp_tc_preflight", abi.lib().augur_cuda_nvfp4_sm100_mlp_tc_preflight_v1(
+            s.ordinal, s.handle, plan.handle, byref(self.args)))
+        return self
+
+    def submit_for_plan(self) -> None:
+        s = self.plan.stream
+        _check("mlp_tc_submit", abi.lib().augur_cuda_nvfp4_sm100_mlp_tc_prevalidated_submit_v1(
+            s.ordinal, s.handle, self.plan.handle, byref(self.args)))
+
+
 class Nvfp4Sm100FfnProgram:
     """gate|up + SwiGLU, then down, as one validated program.
 

@@ -273,8 +273,10 @@ augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_bf16_prevalidat
  * (for EPILOGUE_SWIGLU_BF16: one tensor of 2 * rows physical rows, 16 gate rows alternating with the
  * matching 16 up rows, as interleave_gate_up_host_v1 makes it), rows (physical) a multiple of 128, cols a
  * multiple of 64. The weights reach the tensor cores (tcgen05.mma kind::mxf4nvf4) as TMA delivers them;
- * the BF16 activations are split by the kernel into six NVFP4 residual terms, which reproduces them to
- * about 3e-7 of a 16-element group's largest magnitude. Replaces the same reference entry points as
+ * the BF16 activations are split inside the launch into six NVFP4 residual terms, which reproduces them to
+ * about 3e-7 of a 16-element group's largest magnitude. The launch holds a grid-wide barrier: it needs all
+ * of its CTAs (at most two per SM) resident, so keep other long-running kernels off the device meanwhile; a
+ * barrier wait that runs out sets the plan's status word to 0x307. Replaces the same reference entry points as
  * gemv_bf16_*_v1 (augur_qwen35_nvfp4_qpn_abi.h:134-156), with one weight layout for every token count. */
 augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_tc_scratch_extent_host_v1(
     uint32_t rows, uint32_t cols, uint32_t epilogue, uint64_t* out_bytes);
@@ -284,6 +286,7 @@ augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_tc_bf16_preflig
 augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_tc_bf16_prevalidated_submit_v1(
     int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
     const augur_cuda_nvfp4_sm100_gemv_args_v1* args);
+
 
 /* No counterpart in the reference. The same small-token linear for callers that may not allocate:
  * plan creation calls cudaMalloc, which a host cannot do once it has handed all device memory to
@@ -326,6 +329,19 @@ augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_mlp_preflight_v1(
     int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
     const augur_cuda_nvfp4_sm100_mlp_args_v1* args);
 augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_mlp_prevalidated_submit_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_mlp_args_v1* args);
+
+/* The MLP block on the tensor-memory path as ONE launch: gate|up with SiLU(gate) * up (the interleaved
+ * TCGEN05 weight), then down (TCGEN05), with the intermediate handed on inside the launch and the weight
+ * stream of the down projection already running while the intermediate is completed. Same descriptor and
+ * the same cross-member checks as mlp_*_v1 (both members validated before the one enqueue); replaces
+ * CudaQwen35QpnFfnProgramV1 (crates/augur-backend/src/cuda_qwen35_prefill_cublas/qpn.rs:391-492) for
+ * 1..8 token rows. The plan needs gemv_tc_scratch_extent of each member, side by side. */
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_mlp_tc_preflight_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
+    const augur_cuda_nvfp4_sm100_mlp_args_v1* args);
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_mlp_tc_prevalidated_submit_v1(
     int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
     const augur_cuda_nvfp4_sm100_mlp_args_v1* args);
 

