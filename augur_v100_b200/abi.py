@@ -78,6 +78,14 @@ class GemvArgs(Structure):
                 ("reserved0", c_uint32), ("reserved1", c_uint32)]
 
 
+class Bf16HeadArgs(Structure):
+    _fields_ = [("abi_version", c_uint32), ("struct_size", c_uint32),
+                ("weight", c_uint64), ("weight_len_bytes", c_uint64),
+                ("input", c_uint64), ("input_len_bytes", c_uint64),
+                ("output", c_uint64), ("output_len_bytes", c_uint64),
+                ("rows", c_uint32), ("cols", c_uint32)]
+
+
 class MlpArgs(Structure):
     _fields_ = [("abi_version", c_uint32), ("struct_size", c_uint32),
                 ("gate_up", GemvArgs), ("down", GemvArgs)]
@@ -183,6 +191,8 @@ EXPORTS = {
     "augur_cuda_nvfp4_sm100_mlp_tc_prevalidated_submit_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(MlpArgs)]),
     "augur_cuda_nvfp4_sm100_gemv_bf16_static_scratch_submit_v1": (Result, [c_int32, c_void_p, POINTER(GemvArgs)]),
     "augur_cuda_nvfp4_sm100_static_scratch_status_v1": (Result, [c_int32, c_void_p, POINTER(c_uint32)]),
+    "augur_cuda_nvfp4_sm100_bf16_head_preflight_v1": (Result, [c_int32, c_void_p, POINTER(Bf16HeadArgs)]),
+    "augur_cuda_nvfp4_sm100_bf16_head_prevalidated_submit_v1": (Result, [c_int32, c_void_p, POINTER(Bf16HeadArgs)]),
     "augur_cuda_nvfp4_sm100_mlp_preflight_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(MlpArgs)]),
     "augur_cuda_nvfp4_sm100_mlp_prevalidated_submit_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(MlpArgs)]),
     "augur_cuda_nvfp4_sm100_norm_group_preflight_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(NormGroupArgs)]),

@@ -654,6 +654,38 @@ class Nvfp4Sm100NormGroupProgram:
             s.ordinal, s.handle, self.plan.handle, byref(self.args)))
 
 
+class Bf16Head:
+    """The BF16 vocabulary head bound to one (input, output) pair: weights [rows, cols] BF16 read in place,
+    F32 activations [tokens <= 8, cols], F32 logits [tokens, rows]. Mirrors the reference's shared-head binding
+    (crates/augur-model-qwen35-runtime/src/checkpoint_projection_cuda/dflash_head.rs): preflight at bind,
+    `submit` only enqueues."""
+
+    def __init__(self, stream: Stream, weight: torch.Tensor, x: torch.Tensor, out: torch.Tensor):
+        rows, cols = weight.shape
+        self.stream, self.weight, self.x, self.out = stream, weight, x, out
+        a = abi.header(abi.Bf16HeadArgs)
+        a.weight, a.weight_len_bytes = _ptr(weight), _nbytes(weight)
+        a.input, a.input_len_bytes = _ptr(x), _nbytes(x)
+        a.output, a.output_len_bytes = _ptr(out), _nbytes(out)
+        a.rows, a.cols = rows, cols
+        self.args = a
+
+    @classmethod
+    def bind(cls, stream: Stream, weight: torch.Tensor, x: torch.Tensor, out: torch.Tensor | None = None):
+        if weight.dtype != torch.bfloat16 or x.dtype != torch.float32:
+            raise ValueError("BF16 weights and F32 activations")
+        if out is None:
+            out = torch.empty((x.shape[0], weight.shape[0]), dtype=torch.float32, device=x.device)
+        self = cls(stream, weight, x, out)
+        _check("bf16_head_preflight", abi.lib().augur_cuda_nvfp4_sm100_bf16_head_preflight_v1(
+            stream.ordinal, stream.handle, byref(self.args)))
+        return self
+
+    def submit(self) -> None:
+        _check("bf16_head_submit", abi.lib().augur_cuda_nvfp4_sm100_bf16_head_prevalidated_submit_v1(
+            self.stream.ordinal, self.stream.handle, byref(self.args)))
+
+
 SHAPE_SMALL_BATCH = "small-batch"
 SHAPE_PREFILL = "prefill"
 

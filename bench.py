@@ -326,6 +326,37 @@ def config0_probe(ctx):
     return entry
 
 
+def head_probe(ctx):
+    """The BF16 vocabulary head (248320 x 5120, F32 activations and logits) at 8 token rows: 2.54 GB of weights per
+    call, far more than L2. Bytes: weights once, activations and logits."""
+    import oracle
+    torch, host = ctx.torch, ctx.host
+    rows, cols = 248320, 5120
+    generator = torch.Generator(device=ctx.device)
+    generator.manual_seed(31)
+    weight = (torch.randn((rows, cols), device=ctx.device, generator=generator) * 0.02).to(torch.bfloat16)
+    x = torch.randn((TOKENS, cols), device=ctx.device, generator=generator)
+    head = host.Bf16Head.bind(ctx.stream, weight, x)
+    for _ in range(3):
+        head.submit()
+    reps = 20
+    ms = ctx.timed(head.submit, reps) / reps
+    nbytes = rows * cols * 2 + TOKENS * cols * 4 + TOKENS * rows * 4
+    entry = ctx.hbm_entry(nbytes, nbytes, ms)
+    entry["workload"] = f"BF16 vocabulary head {rows} x {cols}, M={TOKENS}, F32 activations and logits"
+    pick = np.sort(np.random.default_rng(8).choice(rows, size=512, replace=False))
+    index = torch.from_numpy(pick).to(ctx.device)
+    w_bits = weight[index].view(torch.int16).cpu().numpy().view(np.uint16)
+    x_host = x.cpu().numpy()
+    want = oracle.bf16_head_f64(w_bits, x_host)
+    w64 = (w_bits.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    scale = np.linalg.norm(w64, axis=1)[None, :] * np.linalg.norm(x_host.astype(np.float64), axis=1)[:, None]
+    got = head.out[:, index].cpu().numpy().astype(np.float64)
+    entry["parity"] = {"sampled_rows": int(pick.size), "max_error_over_norm_product_vs_fp64": float(np.max(np.abs(got - want) / scale)),
+                       "bound": 1e-7}
+    return entry
+
+
 def prefill_probe(ctx):
     """Configuration 2 on one GPU: the M=4096 GEMMs through the tcgen05 path. Per shape: the mode that is
     accurate against the BF16-activation reference (three residual activation terms; the rate counts the
@@ -685,7 +716,7 @@ def run_library(args):
             extras["config4_prefill_mlp"] = {"error": repr(error)}
         torch.cuda.empty_cache()
         if world == 1:
-            for key, probe in (("config0", config0_probe), ("config2_prefill", prefill_probe)):
+            for key, probe in (("config0", config0_probe), ("config2_prefill", prefill_probe), ("head_bf16", head_probe)):
                 try:
                     extras[key] = probe(ctx)
                 except Exception as error:

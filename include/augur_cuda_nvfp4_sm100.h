@@ -385,6 +385,32 @@ augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_norm_group_prevalida
     int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
     const augur_cuda_nvfp4_sm100_norm_group_args_v1* args);
 
+/* ---- BF16 vocabulary head for 1..8 token rows ------------------------------------ */
+/* Replaces augur_cuda_dflash_bf16_head_f32_rw4_{preflight,submit}_v1 (augur_cuda_runtime.h:2499-2502, struct
+ * augur_cuda_bf16_f32_matvec_args_v1 at :1689-1700, kernel native/augur_dflash_llama_bf16_head.cuh:24-72): the
+ * shared 248320 x 5120 BF16 head of the draft and the verifier, read in place. Same members as the reference
+ * struct; weights [rows][cols] BF16, activations [tokens][cols] F32 (tokens = input_len_bytes / (4 cols),
+ * 1..8), logits [tokens][rows] F32; 16-byte aligned weights and activations as the rw4 entry asks; rows a
+ * multiple of 16, cols a multiple of 64 (any such shape, not only the one vocabulary). Products are exact
+ * (BF16 x BF16 terms of the exactly split F32 activation on the tensor cores), accumulation is F32. */
+typedef struct augur_cuda_nvfp4_sm100_bf16_head_args_v1 {
+    uint32_t abi_version;
+    uint32_t struct_size;
+    augur_cuda_device_ptr_t weight;
+    uint64_t weight_len_bytes;
+    augur_cuda_device_ptr_t input;
+    uint64_t input_len_bytes;
+    augur_cuda_device_ptr_t output;
+    uint64_t output_len_bytes;
+    uint32_t rows;
+    uint32_t cols;
+} augur_cuda_nvfp4_sm100_bf16_head_args_v1;
+
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_bf16_head_preflight_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, const augur_cuda_nvfp4_sm100_bf16_head_args_v1* args);
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_bf16_head_prevalidated_submit_v1(
+    int32_t ordinal, augur_cuda_stream_t stream, const augur_cuda_nvfp4_sm100_bf16_head_args_v1* args);
+
 /* ---- tensor-parallel MLP program: the all-reduce inside the down launch --------- */
 /* No counterpart in the reference (it has no multi-GPU code). Column-parallel gate|up and
  * row-parallel down over up to 8 GPUs of one box, one process per GPU: every rank passes its

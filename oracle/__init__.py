@@ -298,6 +298,14 @@ def rmsnorm_stage(input_f32, weight_f32, epsilon: float, add_a=None, add_b=None)
     return x, out, staged
 
 
+def bf16_head_f64(weight_bf16_bits, x_f32) -> np.ndarray:
+    """logits[token][row] = sum_k w[row][k] * x[token][k] in fp64: the FP64 reference the shared-head GPU test of
+    the reference compares sampled rows with (docs/AUGUR_SHARED_HEAD_RW4_20261016.md, "Configuration and checks";
+    products of a BF16 weight and an F32 activation are exact in fp64, so only the summation rounds)."""
+    w = (np.ascontiguousarray(weight_bf16_bits, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    return np.ascontiguousarray(x_f32, dtype=np.float32).astype(np.float64) @ w.T
+
+
 def max_threads() -> int:
     return int(lib().augur_oracle_max_threads())
 
