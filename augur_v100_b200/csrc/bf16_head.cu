@@ -106,17 +106,23 @@ bf16_head_kernel(const uint16_t* __restrict__ weight, const float* __restrict__ 
             const uint32_t row_g[8] = {w[0].x, w[0].y, w[0].z, w[0].w, w[1].x, w[1].y, w[1].z, w[1].w};
             const uint32_t row_h[8] = {w[2].x, w[2].y, w[2].z, w[2].w, w[3].x, w[3].y, w[3].z, w[3].w};
             const float* base = mine + block * 64;
+            // The tensor core adds into its accumulator without rounding to nearest, so the sum of a 64-k block is
+            // formed in a register set of its own (twelve MMAs deep) and added to the running sum with ordinary
+            // round-to-nearest additions: the error grows like that of the reference's F32 chain.
+            float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (uint32_t j = 0; j < 4; ++j) {
                 const float4 v = *reinterpret_cast<const float4*>(base + j * 16);
                 uint32_t hi0, mid0, lo0, hi1, mid1, lo1;
                 split3(v.x, v.y, hi0, mid0, lo0);
                 split3(v.z, v.w, hi1, mid1, lo1);
-                // the smallest terms first, so that they are not rounded away against a large partial sum
-                mma_bf16_acc(acc, row_g[2 * j], row_h[2 * j], row_g[2 * j + 1], row_h[2 * j + 1], lo0, lo1);
-                mma_bf16_acc(acc, row_g[2 * j], row_h[2 * j], row_g[2 * j + 1], row_h[2 * j + 1], mid0, mid1);
-                mma_bf16_acc(acc, row_g[2 * j], row_h[2 * j], row_g[2 * j + 1], row_h[2 * j + 1], hi0, hi1);
+                // the smallest terms first, so that they are not lost against a large partial sum
+                mma_bf16_acc(part, row_g[2 * j], row_h[2 * j], row_g[2 * j + 1], row_h[2 * j + 1], lo0, lo1);
+                mma_bf16_acc(part, row_g[2 * j], row_h[2 * j], row_g[2 * j + 1], row_h[2 * j + 1], mid0, mid1);
+                mma_bf16_acc(part, row_g[2 * j], row_h[2 * j], row_g[2 * j + 1], row_h[2 * j + 1], hi0, hi1);
             }
+#pragma unroll
+            for (uint32_t i = 0; i < 4; ++i) acc[i] += part[i];
             if (s + kHeadAhead < total) fetch(s + kHeadAhead, ring[a]);
             if (++block == blocks) {
                 // acc: rows g (first two) and g + 8 (last two) of the tile, tokens 2 t4 and 2 t4 + 1

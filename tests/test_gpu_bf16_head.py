@@ -4,8 +4,10 @@ The reference's own test of this kernel (`f32_rw4_head_matches_mmvf8_and_f64_ref
 docs/AUGUR_SHARED_HEAD_RW4_20261016.md) uses the full-vocabulary geometry with outlier activations, compares
 sampled rows with an FP64 reference, checks the Top-20 sets of every token row, rejects misaligned input at
 bind and verifies output guard bytes and zero hot allocations; the same checks are made here.
-Bound: max |logit - fp64| / (||w_row|| * ||x_token||) <= 1e-7 (the reference measures 4.8e-8 for its FP32
-kernel: exact products, F32 accumulation).
+Bound: max |logit - fp64| / (||w_row|| * ||x_token||) <= 1e-7. Products are exact, as in the reference's FP32
+kernel (which measures 4.8e-8 on this metric); the tensor core adds into its accumulator without rounding to
+nearest, so every 64-k block is summed in registers of its own and added to the running sum with ordinary F32
+additions (one long MMA chain measured 7.6e-7; the reference's discarded FP16 tensor-core variant 4.9e-7).
 """
 from ctypes import byref
 
