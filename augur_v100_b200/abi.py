@@ -75,7 +75,7 @@ class GemvArgs(Structure):
                 ("output", c_uint64), ("output_len_bytes", c_uint64),
                 ("rows", c_uint32), ("cols", c_uint32), ("tokens", c_uint32), ("epilogue", c_uint32),
                 ("global_scale", c_float), ("global_scale_b", c_float),
-                ("reserved0", c_uint32), ("reserved1", c_uint32)]
+                ("stored_rows", c_uint32), ("reserved1", c_uint32)]
 
 
 class Bf16HeadArgs(Structure):

@@ -55,6 +55,7 @@ struct GemvParams {
     uint16_t* staged_out;      // SwiGLU epilogue: also write the result as staged fragments (or null)
     uint32_t groups, kb_count, slabs, ctas_per_slab, max_contrib, unit;
     uint32_t rows, cols, tokens, epilogue;
+    uint32_t store_rows;       // rows that are written (the output is [tokens][store_rows]); the rest of the weight rows is padding
     float global_a, global_b;
     // Tensor-parallel exchange (tp_world == 0: none): every rank's exchange buffer as mapped here.
     uint64_t exchange[AUGUR_NVFP4_SM100_MAX_TP_RANKS];
@@ -315,12 +316,13 @@ __device__ __forceinline__ void exchange_push(const GemvParams& p, uint32_t seq,
 }
 
 // Whole warps call this once, after everything else the kernel does.
-__device__ __forceinline__ void exchange_reduce(const GemvParams& p, uint32_t seq, uint32_t warp, uint32_t lane) {
+__device__ __forceinline__ void exchange_reduce(const GemvParams& p, uint32_t seq, uint32_t warp, uint32_t lane, uint32_t cta,
+                                                uint32_t ctas) {
     const uint32_t world = p.tp_world;
     const uint64_t own = exchange_base(p, p.tp_rank);
     constexpr uint32_t kBatch = 4;   // sources polled together, so that their load latencies overlap
     bool arrived = true;
-    for (uint32_t group = blockIdx.x + gridDim.x * warp; group < p.groups; group += gridDim.x * kWarps) {
+    for (uint32_t group = cta + ctas * warp; group < p.groups; group += ctas * kWarps) {
         float sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         for (uint32_t first = 0; first < world; first += kBatch) {
             uint32_t line[kBatch][4][4];
@@ -407,12 +409,12 @@ __device__ __forceinline__ void epilogue(const GemvParams& p, uint32_t seq, uint
     for (uint32_t i = 0; i < 8; ++i) {
         const uint32_t token = 2 * t4 + (i & 1);
         const uint32_t row = group * 32 + (i >> 2) * 16 + g + ((i >> 1) & 1) * 8;
-        if (token < p.tokens) {
+        if (token < p.tokens && row < p.store_rows) {
             const float value = v[i] * p.global_a;
             if (p.epilogue == AUGUR_NVFP4_SM100_EPILOGUE_LINEAR_F32) {
-                static_cast<float*>(p.out)[static_cast<uint64_t>(token) * p.rows + row] = value;
+                static_cast<float*>(p.out)[static_cast<uint64_t>(token) * p.store_rows + row] = value;
             } else {
-                static_cast<__nv_bfloat16*>(p.out)[static_cast<uint64_t>(token) * p.rows + row] = __float2bfloat16_rn(value);
+                static_cast<__nv_bfloat16*>(p.out)[static_cast<uint64_t>(token) * p.store_rows + row] = __float2bfloat16_rn(value);
             }
         }
     }
@@ -566,8 +568,8 @@ __device__ __forceinline__ void contribute(const GemvParams& p, uint32_t seq, ui
     if (lane == 0) p.counters[group] = 0;  // leave the counter clean for the next launch
 }
 
-__global__ void __launch_bounds__(kWarps * 32, 1) gemv_kernel(const GemvParams p) {
-    extern __shared__ __align__(128) uint8_t smem[];
+// The work of CTA `cta` of the `ctas` that share the linear `p`.
+__device__ __forceinline__ void gemv_body(const GemvParams& p, uint32_t cta, uint32_t ctas, uint8_t* smem) {
     // Let the next kernel in the stream become resident on SMs as this grid drains; every
     // kernel of this library defers its global reads of produced data, and all of its global
     // writes, until its own griddepcontrol.wait.
@@ -577,7 +579,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_kernel(const GemvParams p
     uint8_t* scale_area = ring + kWarps * kDepth * kStreamBlockBytes;         // [warps] x 1 KB
     uint64_t* bars = reinterpret_cast<uint64_t*>(scale_area + kWarps * kScaleScratchBytes);   // ring slots, then one for act
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const uint32_t slab = blockIdx.x / p.ctas_per_slab, cta_in_slab = blockIdx.x % p.ctas_per_slab;
+    const uint32_t slab = cta / p.ctas_per_slab, cta_in_slab = cta % p.ctas_per_slab;
     const uint32_t kb_lo = slab * p.kb_count / p.slabs;
     const uint32_t kbs = (slab + 1) * p.kb_count / p.slabs - kb_lo;
     const uint32_t units = p.groups * kbs / p.unit;
@@ -790,13 +792,13 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_kernel(const GemvParams p
     }
     // ---- tensor-parallel: add the ranks' tiles of the row groups assigned to this warp ----
     if (p.tp_world) {
-        exchange_reduce(p, seq, warp, lane);
+        exchange_reduce(p, seq, warp, lane, cta, ctas);
         if (p.tp_sequence == 0) {
             // the last CTA to get here advances the counter for the next launch and clears the arrivals
             __syncthreads();
             if (threadIdx.x == 0) {
                 __threadfence();
-                if (atomicAdd(p.tp_counter + 1, 1u) + 1 == gridDim.x) {
+                if (atomicAdd(p.tp_counter + 1, 1u) + 1 == ctas) {
                     p.tp_counter[1] = 0;
                     p.tp_counter[0] = launches_before + 1;
                 }
@@ -805,13 +807,41 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_kernel(const GemvParams p
     }
 }
 
+__global__ void __launch_bounds__(kWarps * 32, 1) gemv_kernel(const GemvParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    gemv_body(p, blockIdx.x, gridDim.x, smem);
+}
+
+// Up to four linears that read the same staged activations, as one grid (the grouped projections of a norm
+// group): CTA b works for the member whose CTA range holds b. The members share nothing but the input; each has
+// its own counters and partial-sum slots.
+constexpr uint32_t kMaxGroupMembers = 4;
+struct GemvGroupParams {
+    GemvParams member[kMaxGroupMembers];
+    uint32_t first_cta[kMaxGroupMembers + 1];
+};
+__global__ void __launch_bounds__(kWarps * 32, 1) gemv_group_kernel(const __grid_constant__ GemvGroupParams g) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    // a chain of compile-time indices: a run-time index into kernel parameters would copy them to the stack
+    if (blockIdx.x < g.first_cta[1]) {
+        gemv_body(g.member[0], blockIdx.x, g.first_cta[1], smem);
+    } else if (blockIdx.x < g.first_cta[2]) {
+        gemv_body(g.member[1], blockIdx.x - g.first_cta[1], g.first_cta[2] - g.first_cta[1], smem);
+    } else if (blockIdx.x < g.first_cta[3]) {
+        gemv_body(g.member[2], blockIdx.x - g.first_cta[2], g.first_cta[3] - g.first_cta[2], smem);
+    } else {
+        gemv_body(g.member[3], blockIdx.x - g.first_cta[3], g.first_cta[4] - g.first_cta[3], smem);
+    }
+}
+
 constexpr uint32_t kGemvSmemBytes = kMaxSlabBlocks * 4 * 512 + kWarps * kDepth * kStreamBlockBytes +
                                     kWarps * kScaleScratchBytes + (kWarps * kDepth + 1) * 8;
 
 // ---- validation ---------------------------------------------------------------------------
 bool check_gemv_scalars(const augur_cuda_nvfp4_sm100_gemv_args_v1* a, bool* pair) {
-    if (a->reserved0 || a->reserved1 || a->epilogue > AUGUR_NVFP4_SM100_EPILOGUE_LINEAR_F32) return false;
+    if (a->reserved1 || a->epilogue > AUGUR_NVFP4_SM100_EPILOGUE_LINEAR_F32) return false;
     *pair = a->epilogue == AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16;
+    if (a->stored_rows && (*pair || a->stored_rows > a->rows)) return false;   // a trimmed store: plain linears only
     if (!a->rows || !a->cols || a->rows > INT_MAX || a->cols > INT_MAX) return false;
     if (static_cast<uint64_t>(a->rows) * a->cols > UINT32_MAX) return false;
     if (a->cols % kStreamBlockK != 0 || a->rows % (*pair ? 16 : 32) != 0) return false;
@@ -821,7 +851,7 @@ bool check_gemv_scalars(const augur_cuda_nvfp4_sm100_gemv_args_v1* a, bool* pair
     if (a->weight_len_bytes != stream_extent_bytes(*pair, a->rows, a->cols)) return false;
     if (a->input_len_bytes != static_cast<uint64_t>(a->tokens) * a->cols * 2) return false;
     const uint64_t out_elem = a->epilogue == AUGUR_NVFP4_SM100_EPILOGUE_LINEAR_F32 ? 4 : 2;
-    return a->output_len_bytes == static_cast<uint64_t>(a->tokens) * a->rows * out_elem;
+    return a->output_len_bytes == static_cast<uint64_t>(a->tokens) * (a->stored_rows ? a->stored_rows : a->rows) * out_elem;
 }
 
 void gemv_ranges(const augur_cuda_nvfp4_sm100_gemv_args_v1* a, Range (&r)[3]) {
@@ -867,26 +897,41 @@ struct ExchangeTable {
 // `staged_out_offset` (non-zero): the SwiGLU result is also written, staged, at that offset of the plan
 // scratch. `input_is_staged`: the activations were staged there by the producing launch (fixed
 // exponent) and are copied in as they are instead of being staged by the kernel.
+// Kernel parameters of one linear. `sm_share`: the SMs this linear may fill (all of them, or its share of a grouped grid);
+// `counters`: its arrival counters; `staged` / `partials`: where its staged activations are and where its slots go.
+GemvParams make_params(const augur_cuda_nvfp4_sm100_plan_v1* plan, const augur_cuda_nvfp4_sm100_gemv_args_v1* a, uint32_t sm_share,
+                       uint32_t* counters, const uint8_t* staged, float* partials, bool input_is_staged, uint32_t* ctas) {
+    const bool pair = a->epilogue == AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16;
+    const GemvGeometry g = geometry(a->rows, a->cols, pair, sm_share);
+    GemvParams p{};
+    p.weight = reinterpret_cast<const uint8_t*>(a->weight);
+    p.x = reinterpret_cast<const uint16_t*>(a->input_bf16);
+    p.out = reinterpret_cast<void*>(a->output);
+    p.counters = counters;
+    p.staged = staged;
+    p.partials = partials;
+    p.unit = g.unit;
+    p.fixed_factor = input_is_staged ? 0x1p31f : 0.0f;      // (2^31)^2 = 2^(126 - kFixedStageShift)
+    p.status_word = plan->status_word;
+    p.groups = g.groups; p.kb_count = g.kb_count; p.slabs = g.slabs; p.ctas_per_slab = g.ctas_per_slab;
+    p.max_contrib = g.max_contrib;
+    p.rows = a->rows; p.cols = a->cols; p.tokens = a->tokens; p.epilogue = a->epilogue;
+    p.store_rows = a->stored_rows ? a->stored_rows : a->rows;
+    p.global_a = a->global_scale; p.global_b = a->global_scale_b;
+    *ctas = g.slabs * g.ctas_per_slab;
+    return p;
+}
+
 void launch_gemv(augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* plan,
                  const augur_cuda_nvfp4_sm100_gemv_args_v1* a, uint32_t member, uint64_t partial_offset,
                  uint64_t staged_out_offset = 0, bool input_is_staged = false, const ExchangeTable* tp = nullptr) {
     const bool pair = a->epilogue == AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16;
     const GemvGeometry g = geometry(a->rows, a->cols, pair, plan->sm_count);
-    GemvParams p{};
-    p.weight = reinterpret_cast<const uint8_t*>(a->weight);
-    p.x = reinterpret_cast<const uint16_t*>(a->input_bf16);
-    p.out = reinterpret_cast<void*>(a->output);
-    p.counters = reinterpret_cast<uint32_t*>(plan->scratch + member * kCounterRegionBytes);
-    p.staged = plan->scratch + partial_offset;
-    p.partials = reinterpret_cast<float*>(plan->scratch + partial_offset + g.staged_bytes);
-    p.unit = g.unit;
-    p.fixed_factor = input_is_staged ? 0x1p31f : 0.0f;      // (2^31)^2 = 2^(126 - kFixedStageShift)
+    uint32_t ctas = 0;
+    GemvParams p = make_params(plan, a, plan->sm_count, reinterpret_cast<uint32_t*>(plan->scratch + member * kCounterRegionBytes),
+                               plan->scratch + partial_offset, reinterpret_cast<float*>(plan->scratch + partial_offset + g.staged_bytes),
+                               input_is_staged, &ctas);
     p.staged_out = staged_out_offset ? reinterpret_cast<uint16_t*>(plan->scratch + staged_out_offset) : nullptr;
-    p.status_word = plan->status_word;
-    p.groups = g.groups; p.kb_count = g.kb_count; p.slabs = g.slabs; p.ctas_per_slab = g.ctas_per_slab;
-    p.max_contrib = g.max_contrib;
-    p.rows = a->rows; p.cols = a->cols; p.tokens = a->tokens; p.epilogue = a->epilogue;
-    p.global_a = a->global_scale; p.global_b = a->global_scale_b;
     if (tp) {
         for (uint32_t r = 0; r < tp->world; ++r) p.exchange[r] = tp->exchange[r];
         p.tp_world = tp->world; p.tp_rank = tp->rank; p.tp_sequence = tp->sequence;
@@ -910,10 +955,12 @@ void launch_gemv(augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* pl
 
 }  // namespace
 
-// Called once per device from plan creation (a bind-time call): raises the kernel's
+// Called once per device from plan creation (a bind-time call): raises the kernels'
 // dynamic shared-memory limit.
 cudaError_t gemv_configure_device() {
-    return cudaFuncSetAttribute(gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvSmemBytes);
+    const cudaError_t e = cudaFuncSetAttribute(gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvSmemBytes);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(gemv_group_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvSmemBytes);
 }
 
 }  // namespace augur_sm100
@@ -979,7 +1026,7 @@ bool check_mlp(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_pl
     if (!check_gemv(d, s, plan, &a->down, middle, plan->scratch_bytes, false, failure)) return false;
     *failure = invalid();
     if (a->gate_up.epilogue != AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16 ||
-        a->down.epilogue == AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16) {
+        a->down.epilogue == AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16 || a->down.stored_rows) {
         return false;
     }
     // The intermediate is the one shared range: gate_up writes what down reads.
@@ -1130,7 +1177,7 @@ bool check_gemv_tp(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm10
     if (!check_gemv(d, s, plan, &a->linear, kCounterBytes, plan ? plan->scratch_bytes : 0, full, failure)) return false;
     *failure = invalid();
     if (a->reserved || a->world < 1 || a->world > AUGUR_NVFP4_SM100_MAX_TP_RANKS || a->rank >= a->world ||
-        a->linear.epilogue != AUGUR_NVFP4_SM100_EPILOGUE_LINEAR_BF16) {
+        a->linear.epilogue != AUGUR_NVFP4_SM100_EPILOGUE_LINEAR_BF16 || a->linear.stored_rows) {
         return false;
     }
     if (!exchange_table_ok(plan, a->linear, a->exchange, a->exchange_len_bytes, a->world)) return false;
@@ -1181,7 +1228,8 @@ constexpr uint32_t kNormThreads = 256;
 __global__ void __launch_bounds__(kNormThreads) norm_stage_kernel(const float* __restrict__ add_a, const float* __restrict__ add_b,
                                                                    float* __restrict__ input, const float* __restrict__ weight,
                                                                    float* __restrict__ output, __nv_bfloat16* __restrict__ staged,
-                                                                   uint32_t cols, float epsilon, uint32_t residual) {
+                                                                   uint16_t* __restrict__ fragments, uint32_t cols, float epsilon,
+                                                                   uint32_t residual) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");   // the inputs may come from the launch before this one
     __shared__ float partial[kNormThreads];
@@ -1209,8 +1257,50 @@ __global__ void __launch_bounds__(kNormThreads) norm_stage_kernel(const float* _
         // this thread wrote input[base + col] itself when there is a residual
         const float y = __fmul_rn(__fmul_rn(input[base + col], scale), __ldg(weight + col));
         output[base + col] = y;
-        staged[base + col] = __float2bfloat16_rn(y);
+        const __nv_bfloat16 rounded = __float2bfloat16_rn(y);
+        staged[base + col] = rounded;
+        // The same value where the grouped projections read it: their MMA B fragments, shifted by the fixed
+        // staging exponent (k-step = col / 16, fragment register (col % 16) / 8, pair (col % 8) / 2, half col % 2),
+        // so that none of them has to stage the activations for itself.
+        const uint32_t kstep = col >> 4, inner = col & 15;
+        const uint32_t word = ((kstep >> 1) * 32 + blockIdx.x * 4 + ((inner & 7) >> 1)) * 4 + (kstep & 1) * 2 + (inner >> 3);
+        fragments[word * 2 + (inner & 1)] = static_cast<uint16_t>(shift_bf16(__bfloat16_as_ushort(rounded), kFixedStageShift));
     }
+}
+
+// The members of a norm group run as ONE grid: the SMs are dealt out in proportion to the members' weight rows
+// (every member at least one), the staged activations sit once behind the counter regions, the members'
+// partial-sum slots follow side by side, and members 0/1 and 2/3 share a counter region by halves.
+struct GroupLayout {
+    uint32_t share[kMaxGroupMembers];
+    uint64_t staged_offset, partial_offset[kMaxGroupMembers], end;
+};
+GroupLayout group_layout(const augur_cuda_nvfp4_sm100_plan_v1* plan, const augur_cuda_nvfp4_sm100_norm_group_args_v1* a) {
+    GroupLayout layout{};
+    uint64_t total_rows = 0;
+    for (uint32_t i = 0; i < a->count; ++i) total_rows += a->projections[i].rows;
+    uint32_t dealt = 0;
+    for (uint32_t i = 0; i < a->count; ++i) {
+        const uint64_t fair = static_cast<uint64_t>(plan->sm_count) * a->projections[i].rows / (total_rows ? total_rows : 1);
+        layout.share[i] = fair ? static_cast<uint32_t>(fair) : 1;
+        dealt += layout.share[i];
+    }
+    // what rounding down left over goes to the largest member; what the minimum of one took too much comes off it
+    uint32_t largest = 0;
+    for (uint32_t i = 1; i < a->count; ++i) {
+        if (a->projections[i].rows > a->projections[largest].rows) largest = i;
+    }
+    if (dealt < plan->sm_count) layout.share[largest] += plan->sm_count - dealt;
+    if (dealt > plan->sm_count && layout.share[largest] > dealt - plan->sm_count) layout.share[largest] -= dealt - plan->sm_count;
+    layout.staged_offset = kCounterBytes;
+    uint64_t at = kCounterBytes + (static_cast<uint64_t>(a->cols) * 16 + 255) / 256 * 256;
+    for (uint32_t i = 0; i < a->count; ++i) {
+        layout.partial_offset[i] = at;
+        const GemvGeometry g = geometry(a->projections[i].rows, a->projections[i].cols, false, layout.share[i]);
+        at += (g.partial_bytes + 255) / 256 * 256;
+    }
+    layout.end = at;
+    return layout;
 }
 
 bool check_norm_group(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* plan,
@@ -1256,11 +1346,12 @@ bool check_norm_group(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_s
             }
             continue;
         }
-        // each member exactly as a stand-alone small-token linear (launches are stream-ordered and share the scratch)
+        // each member exactly as a stand-alone small-token linear
         if (!check_gemv(d, s, plan, &m, kCounterBytes, plan->scratch_bytes, false, failure)) return false;
         *failure = invalid();
         if (m.epilogue == AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16 || m.input_bf16 != a->staged_bf16 ||
-            m.input_len_bytes != a->staged_len_bytes || m.tokens != a->tokens || m.cols != a->cols) {
+            m.input_len_bytes != a->staged_len_bytes || m.tokens != a->tokens || m.cols != a->cols ||
+            m.rows / 32 > kMaxGroups / 2) {   // two members share a counter region
             return false;
         }
         r[n++] = {m.weight, m.weight_len_bytes, 256};
@@ -1268,6 +1359,9 @@ bool check_norm_group(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_s
     }
     r[n++] = plan_scratch_range(plan);
     if (!all_disjoint(r, n)) return false;
+    // the grouped grid: staged activations once, then every member's slots side by side
+    const GroupLayout layout = group_layout(plan, a);
+    if (layout.end > plan->scratch_bytes) return false;
     return !full || inspect_device_ranges(d, r, n - 1, failure);
 }
 }  // namespace
@@ -1297,17 +1391,34 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_norm_grou
     config.numAttrs = 1;
     config.gridDim = dim3(a->tokens);
     config.blockDim = dim3(kNormThreads);
+    const GroupLayout layout = group_layout(plan, a);
     cudaLaunchKernelEx(&config, norm_stage_kernel, reinterpret_cast<const float*>(a->add_a), reinterpret_cast<const float*>(a->add_b),
                        reinterpret_cast<float*>(a->input_f32), reinterpret_cast<const float*>(a->weight_f32),
-                       reinterpret_cast<float*>(a->output_f32), reinterpret_cast<__nv_bfloat16*>(a->staged_bf16), a->cols,
-                       a->epsilon, a->residual);
+                       reinterpret_cast<float*>(a->output_f32), reinterpret_cast<__nv_bfloat16*>(a->staged_bf16),
+                       reinterpret_cast<uint16_t*>(plan->scratch + layout.staged_offset), a->cols, a->epsilon, a->residual);
     count_launch();
     augur_cuda_result_v1 result = submitted();
-    for (uint32_t i = 0; i < a->count && result.status == AUGUR_CUDA_STATUS_OK; ++i) {
-        launch_gemv(s, plan, &a->projections[i], 0, kCounterBytes);
-        result = submitted();
+    if (result.status != AUGUR_CUDA_STATUS_OK) return result;
+    // all projections of the group in one grid; they copy the staged fragments in and stage nothing themselves
+    GemvGroupParams group{};
+    uint32_t next = 0;
+    for (uint32_t i = 0; i < kMaxGroupMembers; ++i) {
+        group.first_cta[i] = next;
+        if (i >= a->count) continue;
+        uint32_t ctas = 0;
+        uint32_t* counters = reinterpret_cast<uint32_t*>(plan->scratch + (i / 2) * kCounterRegionBytes + (i % 2) * (kCounterRegionBytes / 2));
+        group.member[i] = make_params(plan, &a->projections[i], layout.share[i], counters, plan->scratch + layout.staged_offset,
+                                      reinterpret_cast<float*>(plan->scratch + layout.partial_offset[i]), true, &ctas);
+        next += ctas;
     }
-    return result;
+    group.first_cta[kMaxGroupMembers] = next;
+    for (uint32_t i = a->count; i < kMaxGroupMembers; ++i) group.first_cta[i] = next;   // members that do not exist own no CTA
+    config.gridDim = dim3(next);
+    config.blockDim = dim3(kWarps * 32);
+    config.dynamicSmemBytes = kGemvSmemBytes;
+    cudaLaunchKernelEx(&config, gemv_group_kernel, group);
+    count_launch();
+    return submitted();
 }
 
 // ---- one entry point that allocates nothing -------------------------------------------------

@@ -638,7 +638,7 @@ TcGeometry tc_geometry(uint32_t physical_rows, uint32_t cols, uint32_t sm_count)
 }
 
 bool check_tc_scalars(const augur_cuda_nvfp4_sm100_gemv_args_v1* a, uint32_t* physical_rows) {
-    if (a->reserved0 || a->reserved1 || a->epilogue > AUGUR_NVFP4_SM100_EPILOGUE_LINEAR_F32) return false;
+    if (a->stored_rows || a->reserved1 || a->epilogue > AUGUR_NVFP4_SM100_EPILOGUE_LINEAR_F32) return false;
     const bool pair = a->epilogue == AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16;
     if (!a->rows || !a->cols || a->rows > (1u << 30) || a->cols > INT_MAX) return false;
     *physical_rows = pair ? 2 * a->rows : a->rows;

@@ -618,13 +618,16 @@ class Nvfp4Sm100NormGroupProgram:
     """
 
     def __init__(self, plan: Plan, weights, input_f32: torch.Tensor, norm_weight_f32: torch.Tensor, epsilon: float,
-                 add_a: torch.Tensor | None, add_b: torch.Tensor | None):
+                 add_a: torch.Tensor | None, add_b: torch.Tensor | None, stored_rows=None):
         tokens, cols = input_f32.shape
         self.plan, self.weights, self.input, self.norm_weight = plan, list(weights), input_f32, norm_weight_f32
         self.add_a, self.add_b = add_a, add_b
         self.normalised = torch.empty((tokens, cols), dtype=torch.float32, device=input_f32.device)
         self.staged = torch.empty((tokens, cols), dtype=torch.bfloat16, device=input_f32.device)
-        self.outputs = [torch.empty((tokens, w.rows), dtype=torch.bfloat16, device=input_f32.device) for w in self.weights]
+        # stored_rows[i] (0: all): member i writes only its first rows, e.g. 48 of a gate padded to 64 weight rows
+        self.stored_rows = list(stored_rows) if stored_rows is not None else [0] * len(self.weights)
+        self.outputs = [torch.empty((tokens, keep or w.rows), dtype=torch.bfloat16, device=input_f32.device)
+                        for w, keep in zip(self.weights, self.stored_rows)]
         a = abi.header(abi.NormGroupArgs)
         if add_a is not None:
             a.add_a, a.add_b, a.add_len_bytes, a.residual = _ptr(add_a), _ptr(add_b), _nbytes(add_a), 1
@@ -635,14 +638,15 @@ class Nvfp4Sm100NormGroupProgram:
         a.tokens, a.cols, a.epsilon, a.count = tokens, cols, epsilon, len(self.weights)
         for index, (weight, out) in enumerate(zip(self.weights, self.outputs)):
             a.projections[index] = gemv_args(weight, self.staged, out, abi.EPILOGUE_LINEAR_BF16)
+            a.projections[index].stored_rows = self.stored_rows[index]
         self.args = a
 
     @classmethod
     def bind(cls, plan: Plan, weights, input_f32: torch.Tensor, norm_weight_f32: torch.Tensor, epsilon: float = 1e-6,
-             add_a: torch.Tensor | None = None, add_b: torch.Tensor | None = None):
+             add_a: torch.Tensor | None = None, add_b: torch.Tensor | None = None, stored_rows=None):
         if (add_a is None) != (add_b is None):
             raise ValueError("the residual add takes both operands or none")
-        self = cls(plan, weights, input_f32, norm_weight_f32, epsilon, add_a, add_b)
+        self = cls(plan, weights, input_f32, norm_weight_f32, epsilon, add_a, add_b, stored_rows)
         s = plan.stream
         _check("norm_group_preflight", abi.lib().augur_cuda_nvfp4_sm100_norm_group_preflight_v1(
             s.ordinal, s.handle, plan.handle, byref(self.args)))

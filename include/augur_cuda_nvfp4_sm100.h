@@ -258,7 +258,10 @@ typedef struct augur_cuda_nvfp4_sm100_gemv_args_v1 {
     uint32_t epilogue;
     float global_scale;
     float global_scale_b;                 /* SWIGLU: scale of the up matrix, else 0 */
-    uint32_t reserved0;
+    uint32_t stored_rows;                 /* 0: all rows. Else (LINEAR epilogues) only the first stored_rows rows are written and
+                                           * output is [tokens][stored_rows]: the weight's remaining rows are padding, as for the
+                                           * 48-row gates of the reference's grouped projections, stored trimmed by the same write
+                                           * (docs/AUGUR_GDN_GLUE_B8_20261016.md:18-23) */
     uint32_t reserved1;
 } augur_cuda_nvfp4_sm100_gemv_args_v1;
 
@@ -354,7 +357,10 @@ augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_mlp_tc_prevalidated_
  * scale = 1 / sqrt(mean + epsilon) correctly rounded (the reference uses the approximate rsqrtf)
  * and a BF16 staged copy instead of FP16. With `residual` the value add_a + add_b is stored to
  * input_f32 first. Every projection must take staged_bf16 as its input (same tokens and cols);
- * unused members are zero. tokens 1..8, cols a multiple of 256. Launches: 1 + count. */
+ * unused members are zero. tokens 1..8, cols a multiple of 256. Two launches, as in the reference: the
+ * norm stage, which also writes the activations in the form the projections' MMAs consume (so that no
+ * member stages them again), and ONE grid for all members, the SMs dealt out in proportion to the members'
+ * rows. A member may store trimmed (stored_rows), e.g. 48 of 64 padded rows. */
 typedef struct augur_cuda_nvfp4_sm100_norm_group_args_v1 {
     uint32_t abi_version;
     uint32_t struct_size;

@@ -287,7 +287,8 @@ def _gemv_valid(ctx, rows=64, cols=256, tokens=8):
 GEMV_MUTATIONS = [
     ("abi", lambda a: setattr(a, "abi_version", 0), abi.STATUS_ABI_VERSION_MISMATCH),
     ("struct_size", lambda a: setattr(a, "struct_size", a.struct_size + 8), abi.STATUS_INVALID_ARGUMENT),
-    ("reserved0", lambda a: setattr(a, "reserved0", 1), abi.STATUS_INVALID_ARGUMENT),
+    ("stored rows without the matching output extent", lambda a: setattr(a, "stored_rows", 1), abi.STATUS_INVALID_ARGUMENT),
+    ("stored rows beyond the weight", lambda a: setattr(a, "stored_rows", a.rows + 32), abi.STATUS_INVALID_ARGUMENT),
     ("reserved1", lambda a: setattr(a, "reserved1", 7), abi.STATUS_INVALID_ARGUMENT),
     ("weight len-1", lambda a: setattr(a, "weight_len_bytes", a.weight_len_bytes - 1), abi.STATUS_INVALID_ARGUMENT),
     ("weight len+2304", lambda a: setattr(a, "weight_len_bytes", a.weight_len_bytes + 2304), abi.STATUS_INVALID_ARGUMENT),
@@ -480,7 +481,9 @@ def test_norm_group_program(ctx, residual):
     # [residual add] -> RMSNorm -> BF16 stage -> projections, one program (the reference's GDN-input and post-attention groups)
     host, torch = ctx["host"], ctx["torch"]
     tokens, cols, eps = 8, 5120, 1e-6
-    shapes = [(10240, cols), (6144, cols), (64, cols)] if not residual else [(1024, cols), (2048, cols)]
+    # GDN input group: qkv, z and the two 48-row gates (padded to 64 weight rows, stored trimmed); post-attention: two projections
+    shapes = [(10240, cols), (6144, cols), (64, cols), (64, cols)] if not residual else [(1024, cols), (2048, cols)]
+    stored = [0, 0, 48, 48] if not residual else [0, 0]
     rng = np.random.default_rng(31)
     a = rng.standard_normal((tokens, cols)).astype(np.float32) * 3
     b = rng.standard_normal((tokens, cols)).astype(np.float32)
@@ -492,24 +495,35 @@ def test_norm_group_program(ctx, residual):
     if residual:
         x_dev = torch.zeros((tokens, cols), dtype=torch.float32, device=device)
         program = host.Nvfp4Sm100NormGroupProgram.bind(ctx["plan"], weights, x_dev, torch.from_numpy(norm_weight).to(device), eps,
-                                                       torch.from_numpy(a).to(device), torch.from_numpy(b).to(device))
+                                                       torch.from_numpy(a).to(device), torch.from_numpy(b).to(device), stored_rows=stored)
         want_x, want_y, want_staged = oracle.rmsnorm_stage(None, norm_weight, eps, a, b)
     else:
         x_dev = torch.from_numpy(a).to(device)
-        program = host.Nvfp4Sm100NormGroupProgram.bind(ctx["plan"], weights, x_dev, torch.from_numpy(norm_weight).to(device), eps)
+        program = host.Nvfp4Sm100NormGroupProgram.bind(ctx["plan"], weights, x_dev, torch.from_numpy(norm_weight).to(device), eps,
+                                                       stored_rows=stored)
         want_x, want_y, want_staged = oracle.rmsnorm_stage(a, norm_weight, eps)
     before = host.allocation_snapshot(), host.launch_count()
     program.submit_for_plan()
     ctx["stream"].synchronize()
-    assert host.allocation_snapshot() == before[0] and host.launch_count() - before[1] == 1 + len(shapes)
+    assert host.allocation_snapshot() == before[0] and host.launch_count() - before[1] == 2    # norm stage + one grid for all members
     assert ctx["plan"].device_status() == 0
     # the norm stage is bit-exact with the CPU statement of the reference kernel's order
     assert np.array_equal(x_dev.cpu().numpy().view(np.uint32), want_x.view(np.uint32))
     assert np.array_equal(program.normalised.cpu().numpy().view(np.uint32), want_y.view(np.uint32))
     assert np.array_equal(bits_from_torch_bf16(program.staged).reshape(want_staged.shape), want_staged)
-    for (rows, _), (codes, scales, glob), out in zip(shapes, planes, program.outputs):
+    for (rows, _), keep, (codes, scales, glob), out in zip(shapes, stored, planes, program.outputs):
         y64 = oracle.linear_f64(codes, scales, glob, rows, cols, want_staged, threads=oracle.max_threads())
+        if keep:    # the trimmed store: [tokens][48], the padding rows are computed and never written
+            assert tuple(out.shape) == (tokens, keep)
+            y64 = np.ascontiguousarray(y64[:, :keep])
         assert rel_error(bits_from_torch_bf16(out), y64) <= TOLERANCE
+    # a second submit finds counters and staged fragments in order
+    program.submit_for_plan()
+    ctx["stream"].synchronize()
+    assert ctx["plan"].device_status() == 0
+    for (rows, _), keep, (codes, scales, glob), out in zip(shapes, stored, planes, program.outputs):
+        y64 = oracle.linear_f64(codes, scales, glob, rows, cols, want_staged, threads=oracle.max_threads())
+        assert rel_error(bits_from_torch_bf16(out), np.ascontiguousarray(y64[:, :keep]) if keep else y64) <= TOLERANCE
 
 
 def test_norm_group_rejects_inconsistent_members(ctx):
