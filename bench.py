@@ -16,9 +16,9 @@ Prints one JSON line (rank 0). `value` is whole-job GB/s of algorithmic bytes wi
 HBM; `e2e` is the same through the public host API with the activations copied from pinned host memory
 and the result read back for every pass. The other configurations of the benchmark definition are
 reported under their own keys of the same line, each outside the headline's timed region:
-`config0` (single 17408 x 5120 linear, M=8), `config1_m1` (the MLP block at M=1), `config2_prefill`
-(M=4096 GEMMs), `config3_sweep` (64-layer whole-model linear sweep at M=8), `config4_prefill_mlp`
-(chunked tensor-parallel prefill MLP).
+`config0` (single 17408 x 5120 linear, M=8), `config1_m1` (the MLP block at M=1), `config1_tensor_memory_path`
+(the block as one tcgen05 launch), `config2_prefill` (M=4096 GEMMs), `config3_sweep` (64-layer whole-model linear
+sweep at M=8), `config4_prefill_mlp` (chunked tensor-parallel prefill MLP), `head_bf16` (the BF16 vocabulary head).
 """
 from __future__ import annotations
 
@@ -322,6 +322,63 @@ def config0_probe(ctx):
     entry["parity"] = {"rel_error_vs_fp64_oracle": rel_error(bits(projections[0].out), y64), "bound": 2e-2}
     entry["device_status"] = plan.device_status()
     del projections
+    plan.close()
+    return entry
+
+
+def tensor_memory_path_probe(ctx):
+    """Configuration 1 through the tensor-memory small-token path: the whole MLP block as ONE launch (tcgen05
+    block-scaled MMA on the weights as TMA delivers them, activations split into six NVFP4 terms inside the launch).
+    Eight distinct layers in rotation (1.2 GB of weights); parity of the first against the CPU oracle."""
+    import oracle
+    from augur_v100_b200 import synth
+    torch, host, abi = ctx.torch, ctx.host, ctx.abi
+    generator = torch.Generator(device=ctx.device)
+    generator.manual_seed(2024)
+    count = 8
+    plan = host.Plan(ctx.stream, host.mlp_tc_scratch_bytes(HIDDEN, INTER))
+    x = torch.randn((TOKENS, HIDDEN), device=ctx.device, generator=generator).mul_(8.0).to(torch.bfloat16)
+    programs, first = [], None
+    for index in range(count):
+        gc, gs = device_planes(torch, generator, INTER, HIDDEN, ctx.device)
+        uc, us = device_planes(torch, generator, INTER, HIDDEN, ctx.device)
+
+        def interleave(gate_plane, up_plane):   # 16 gate rows, then the matching 16 up rows
+            width = gate_plane.shape[1]
+            return torch.stack([gate_plane.view(INTER // 16, 16, width), up_plane.view(INTER // 16, 16, width)], dim=1).reshape(2 * INTER, width).contiguous()
+
+        gate_up = host.Nvfp4Sm100Weight.repack_device_planes(ctx.stream, abi.LAYOUT_TCGEN05, 2 * INTER, HIDDEN, interleave(gc, uc),
+                                                             interleave(gs, us), synth.GLOBAL_SCALE)
+        gate_up.global_scale_b = synth.GLOBAL_SCALE
+        dc, ds = device_planes(torch, generator, HIDDEN, INTER, ctx.device)
+        down = host.Nvfp4Sm100Weight.repack_device_planes(ctx.stream, abi.LAYOUT_TCGEN05, HIDDEN, INTER, dc, ds, synth.GLOBAL_SCALE)
+        if index == 0:
+            first = tuple((c.cpu().numpy(), s.cpu().numpy(), synth.GLOBAL_SCALE) for c, s in ((gc, gs), (uc, us), (dc, ds)))
+        programs.append(host.Nvfp4Sm100TcFfnProgram.bind(plan, gate_up, down, x))
+        del gc, gs, uc, us, dc, ds
+
+    def sweep():
+        for program in programs:
+            program.submit_for_plan()
+
+    for _ in range(3):
+        sweep()
+    reps = 40
+    launches_before = host.launch_count()
+    ms = ctx.timed(sweep, reps) / (reps * count)
+    launches = (host.launch_count() - launches_before) // (reps * count)
+    entry = ctx.hbm_entry(layer_bytes(), layer_bytes(), ms)
+    entry.update({"workload": f"config1 through the tensor-memory path: the MLP block as one launch, M={TOKENS}; {count} distinct layers in rotation; ms per layer",
+                  "launches_per_layer": launches, "device_status": plan.device_status()})
+    gate, up, down = first
+    programs[0].submit_for_plan()
+    ctx.stream.synchronize()
+    h64, _ = oracle.mlp_f64(gate, up, down, HIDDEN, INTER, bits(x), threads=oracle.max_threads())
+    h_bits = bits(programs[0].intermediate)
+    y64_from_h = oracle.linear_f64(down[0], down[1], down[2], HIDDEN, INTER, h_bits, threads=oracle.max_threads())
+    entry["parity"] = {"gate_up_rel_error_vs_fp64_oracle": rel_error(h_bits, h64),
+                       "down_rel_error_vs_fp64_oracle": rel_error(bits(programs[0].out), y64_from_h), "bound": 2e-2}
+    del programs
     plan.close()
     return entry
 
@@ -716,7 +773,8 @@ def run_library(args):
             extras["config4_prefill_mlp"] = {"error": repr(error)}
         torch.cuda.empty_cache()
         if world == 1:
-            for key, probe in (("config0", config0_probe), ("config2_prefill", prefill_probe), ("head_bf16", head_probe)):
+            for key, probe in (("config0", config0_probe), ("config1_tensor_memory_path", tensor_memory_path_probe),
+                               ("config2_prefill", prefill_probe), ("head_bf16", head_probe)):
                 try:
                     extras[key] = probe(ctx)
                 except Exception as error:
