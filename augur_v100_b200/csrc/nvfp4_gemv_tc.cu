@@ -7,13 +7,13 @@
 //                plus 2 KB of scales) per stage into a ring in shared memory, tcgen05.cp moves the scales on
 //                to tensor memory, the MMA reads the codes where the TMA put them;
 //   activations  BF16 in global memory. A block-scaled FP4 MMA wants FP4 on both sides, so the launch first
-//                splits them - every CTA a slice, once - into kTerms NVFP4 residual terms (term t holds what
-//                terms 0..t-1 left over) with power-of-two per-token global scales. The terms sit side by side
-//                on the MMA n dimension (column = term * 8 + token); their codes and block scales (8 KB per
-//                256 k, L2-resident) ride along with every weight stage. Six terms reproduce a BF16 value to
-//                about 3e-7 of its group's largest magnitude, below the f32 accumulation noise; one MMA per
-//                64 k covers all tokens and all terms;
-//   accumulator  128 weight rows x 48 columns of f32 in tensor memory, two buffers; the epilogue warps add
+//                splits them - every CTA a slice, once - into kTerms NVFP4 terms: the digits of the value in
+//                radix 8 (digits -4..4, i.e. the E2M1 levels 0, 0.5, .., 2 with a sign), all scales powers of
+//                two. The terms sit side by side on the MMA n dimension (column = term * 8 + token); their
+//                codes and block scales (10 KB per 256 k, L2-resident) ride along with every weight stage.
+//                Eight digits hold a BF16 value exactly when it is within 2^-15 of its group's largest magnitude
+//                and to 2^-24 of that magnitude otherwise; one MMA per 64 k covers all tokens and all terms;
+//   accumulator  128 weight rows x 64 columns of f32 in tensor memory, two buffers; the epilogue warps add
 //                the terms of a token with their scales and finish the rows.
 //
 // A launch runs one phase (a linear) or two (gate|up with SiLU(gate) * up, then down, whose activations are the
@@ -26,7 +26,8 @@
 // doing so while activations are not ready yet (the ring buffers that time); one thread copies block scales to
 // tensor memory; one issues the MMAs; four warps split activations and run the epilogues. The split needs
 // every CTA's slice before any CTA can use it, and the second phase needs every CTA's output of the first:
-// the grid meets at barriers in global memory (all CTAs are resident: the grid never exceeds two CTAs per SM).
+// the grid meets in global memory (all CTAs are resident: the grid never exceeds two CTAs per SM), once in
+// the first phase and twice at the phase boundary.
 //
 // Every wait is bounded; a wait that runs out records a code in the plan's status word, raises a CTA-wide abort
 // flag, and all roles fall through to the common exit where tensor memory is released.
@@ -42,26 +43,27 @@ namespace augur_sm100 {
 namespace {
 using namespace tc;
 
-constexpr uint32_t kTerms = 6;                         // residual terms of the activation split
+constexpr uint32_t kTerms = 8;                         // radix-8 digits of the activation split
 constexpr uint32_t kCols = 8 * kTerms;                 // MMA n: column = term * 8 + token
 constexpr uint32_t kStageK = 256;                      // k per ring stage = one 128-byte swizzled row of codes
 constexpr uint32_t kStageCodeBytes = kTileM * 128;     // 16 KB of weight codes
 constexpr uint32_t kStageSfBytes = 4 * kSfAtomBytes;   // 2 KB: the 4 scale atoms of a stage (weights; activations alike)
-constexpr uint32_t kChunkBytes = kCols * 128;          // 6 KB: activation codes of one 256-k chunk, 48 rows x 128 bytes
+constexpr uint32_t kChunkBytes = kCols * 128;          // 8 KB: activation codes of one 256-k chunk, 64 rows x 128 bytes
 constexpr uint32_t kStageActCodes = kStageCodeBytes + kStageSfBytes;        // offsets inside a stage
 constexpr uint32_t kStageActSf = kStageActCodes + kChunkBytes;
-constexpr uint32_t kStageBytes = kStageActSf + kStageSfBytes;               // 26 KB
+constexpr uint32_t kStageBytes = kStageActSf + kStageSfBytes;               // 28 KB
 constexpr uint32_t kStages = 4;                        // per CTA; two CTAs share an SM
 constexpr uint32_t kThreads = 224;                     // warp 0 TMA, warp 1 MMA, warps 2..5 split and epilogue, warp 6 scale copies
-constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + 1024 /*small state*/;
+constexpr uint32_t kSmemBytes = kStages * kStageBytes + 512 /*small state*/;   // the stages start the (1024-byte aligned) window
 constexpr uint32_t kCtasPerSm = 2;                     // half of an SM's shared and tensor memory each: a CTA of the next launch
                                                        // moves in (and fills its ring) as soon as one of this launch leaves
-constexpr uint32_t kTmemAcc = 0;                       // two accumulators of 64 columns (48 used)
+constexpr uint32_t kTmemAcc = 0;                       // two accumulators of 64 columns
 constexpr uint32_t kTmemSfWeight = 128;                // 16 columns per ring stage
 constexpr uint32_t kTmemSfAct = kTmemSfWeight + kStages * 16;
 constexpr uint32_t kTmemColumns = 256;
 static_assert(kTmemSfAct + kStages * 16 <= kTmemColumns, "tensor memory columns");
-static_assert(kCtasPerSm * kSmemBytes <= 227 * 1024, "two CTAs per SM");
+static_assert(kCtasPerSm * (kSmemBytes + 1024) <= 228 * 1024, "two CTAs per SM, a kilobyte each reserved by the system");
+static_assert(kTerms == 8, "the digit transposition is 8 lanes x 8 nibbles");
 static_assert(kStageBytes % 1024 == 0 && kStageActCodes % 1024 == 0, "swizzled operand tiles are 1024-byte aligned");
 constexpr uint32_t kSlotFloats = 256;                  // one partial: 32 rows x 8 tokens
 constexpr uint32_t kWorkers = 128;                     // the four split / epilogue warps
@@ -69,11 +71,12 @@ constexpr uint32_t kMaxPhases = 2;
 constexpr uint32_t kGridWaitLimit = 1u << 22;          // polls of the grid barrier (a fraction of a microsecond each) before giving up
 
 constexpr uint32_t kErrTcProducer = 0x301, kErrTcFull = 0x302, kErrTcAccEmpty = 0x303, kErrTcAccFull = 0x304,
-                   kErrTcScalesLanded = 0x305, kErrTcScalesReady = 0x306, kErrTcGridBarrier = 0x307;
+                   kErrTcScalesLanded = 0x305, kErrTcScalesReady = 0x306, kErrTcGridBarrier = 0x307, kErrTcWindow = 0x308;
+constexpr uint32_t kHeld = 4;                          // elements a lane keeps in registers between the scan and the split
 
 
 // The split activations in global memory (plan scratch): the image the ring stages want, chunk by chunk.
-//   [chunk = k / 256][48 rows][128 bytes]   codes, rows already in the 128-byte swizzle of a shared-memory operand tile
+//   [chunk = k / 256][64 rows][128 bytes]   codes, rows already in the 128-byte swizzle of a shared-memory operand tile
 //   [k / 64][512 bytes]                     block-scale atoms (row n at byte (n % 32) * 16 + (n / 32) * 4 + (k / 16) % 4)
 __host__ __device__ constexpr uint64_t split_code_bytes(uint32_t cols) { return static_cast<uint64_t>((cols + kStageK - 1) / kStageK) * kChunkBytes; }
 __host__ __device__ constexpr uint64_t split_sf_bytes(uint32_t cols) { return static_cast<uint64_t>((cols + kStageK - 1) / kStageK) * kStageSfBytes; }
@@ -99,7 +102,7 @@ struct TcPhase {
 struct TcParams {
     TcPhase phase[kMaxPhases];
     uint32_t phases, tokens;
-    uint32_t* grid_barrier;       // {arrivals, generation}, arrivals zero between launches
+    uint32_t* grid_barrier;       // {three arrival counters used in turn, index of the next meeting modulo 3}
     uint32_t* status_word;
 };
 
@@ -115,19 +118,23 @@ __device__ __forceinline__ void workers_sync() { asm volatile("bar.sync 1, 128;"
 
 // All CTAs of the grid meet (the four worker warps of each; thread `leader` speaks for its CTA). Everything the
 // workers wrote before is visible to every CTA's workers after. Returns false if the wait ran out.
-__device__ __forceinline__ bool grid_meet(const TcParams& p, bool leader, volatile uint32_t* abort_flag) {
+// Meeting number m (counted over all launches of the plan, modulo 3, in `meeting`) uses counter m % 3: one
+// release-add per CTA, then acquire-loads until all have arrived. The last arriver clears counter (m - 1) % 3,
+// which every CTA has stopped reading (all are at meeting m) and which is not used again before meeting m + 2;
+// nobody gets to meeting m + 2 before the last arriver of m, its store behind it, has arrived at m + 1.
+__device__ __forceinline__ bool grid_meet(const TcParams& p, bool leader, uint32_t& meeting, volatile uint32_t* abort_flag) {
     workers_sync();
     if (leader) {
-        volatile uint32_t* generation = p.grid_barrier + 1;
-        const uint32_t before = *generation;     // cannot advance until this CTA has arrived
-        __threadfence();
-        if (atomicAdd(p.grid_barrier, 1u) + 1 == gridDim.x) {
-            *static_cast<volatile uint32_t*>(p.grid_barrier) = 0;
-            __threadfence();
-            atomicAdd(p.grid_barrier + 1, 1u);
+        uint32_t* mine = p.grid_barrier + meeting;
+        uint32_t arrived;
+        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(arrived) : "l"(mine) : "memory");
+        if (arrived + 1 == gridDim.x) {
+            asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p.grid_barrier + (meeting + 2) % 3), "r"(0u) : "memory");
         } else {
-            uint32_t spin = 0;
-            while (*generation == before) {
+            uint32_t spin = 0, seen;
+            for (;;) {
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+                if (seen >= gridDim.x) break;
                 if (++spin > kGridWaitLimit || ((spin & 255u) == 255u && *abort_flag)) {
                     *abort_flag = 1;
                     atomicCAS(p.status_word, 0u, kErrTcGridBarrier);
@@ -135,67 +142,71 @@ __device__ __forceinline__ bool grid_meet(const TcParams& p, bool leader, volati
                 }
             }
         }
-        __threadfence();
     }
+    meeting = (meeting + 1) % 3;
     workers_sync();
     return *abort_flag == 0;
 }
 
-// ---- activation split (the four worker warps of every CTA; each CTA a slice) ------------------------------
-// One thread per pair of neighbouring activation elements (one byte of codes per term), eight neighbouring lanes
-// per 16-element group. Term 0 divides by 2^(e - 7), e the exponent of the token row's largest magnitude: its
-// block scales come out below 43 (E4M3 reaches 448) and groups down to 2^-13 of the row's largest still get a
-// normal scale; every further term divides by 8 times less. Per term: the group's largest magnitude by shuffles,
-// an E4M3 scale that covers it (the smallest one, or its neighbour: the quotient by six is rounded up a little
-// instead of divided exactly), the nearest E2M1 level of each element (from an approximate reciprocal: any level
-// next to the quotient will do, because the residual is formed exactly from the level that was chosen), four
-// bytes gathered into a word.
-__device__ __forceinline__ void split_pairs(const TcPhase& ph, uint32_t tokens, uint32_t first_pair, uint32_t count, const float* term_scale,
-                                            uint32_t worker) {
-    const uint32_t lane = worker & 31, pairs_per_row = ph.cols / 2;
-    const uint8_t* sf_base = ph.split + split_code_bytes(ph.cols);
-    for (uint32_t base = 0; base < count; base += kWorkers) {
-        const bool active = base + worker < count;    // count is a multiple of 8: the eight lanes of a group are active together
-        const uint32_t pair = first_pair + (active ? base + worker : 0);
-        const uint32_t token = pair / pairs_per_row, k = (pair - token * pairs_per_row) * 2, group = k >> 4;
-        const uint32_t both = __ldcg(reinterpret_cast<const uint32_t*>(ph.x) + pair);
-        float r0 = __uint_as_float(both << 16), r1 = __uint_as_float(both & 0xffff0000u);
-        float scale = term_scale[token];
-        if (!(scale == scale)) scale = 1.0f;     // the codes of a non-finite row do not matter
-        // inverse of 6 * scale, rounded up a little: the quotient below is never under the exact one
-        float inverse = __uint_as_float(0x7f000000u - __float_as_uint(scale)) * 0x1.555558p-3f;
-        // destination of this group's codes (8 bytes; this lane's 4-lane half writes one word of it) and scale bytes
-        const uint32_t chunk = group >> 4, unit = (group & 15) >> 1, half = group & 1;
-        uint8_t* sf = const_cast<uint8_t*>(sf_base) + static_cast<uint64_t>(group >> 2) * kSfAtomBytes + (group & 3);
-        uint8_t* codes = ph.split + static_cast<uint64_t>(chunk) * kChunkBytes + half * 8 + ((lane >> 2) & 1) * 4;
+// ---- activation split (the four worker warps of every CTA; the grid's worker warps share the groups out) ----
+// One lane per element, sixteen neighbouring lanes per 16-element group; warp w of the grid's W worker warps
+// takes the group pairs w, w + W, ... With A the exponent field of the token row's largest magnitude and G that
+// of the group's, the group's block scale is 2^q, q = G + 8 - A (the row's largest group gets 2^8; E4M3 holds
+// powers of two down to 2^-9, smaller groups keep 2^-9 and lose low bits), term t has the global scale
+// 2^(A - 135) * 8^-t, and the element is the integer I = |x| / 2^(q + A - 157): at most 255 * 2^15 for the
+// group's largest element, exact for every element within 2^-15 of it, rounded to nearest below. I is written
+// in radix 8 with digits -4..4 (from the low end: a digit above 4 becomes digit - 8 and carries), digit t being
+// the code of term t: level |digit| / 2, sign of digit times sign of x. Eight digits reach 4 * (8^8 - 1) / 7
+// > 255 * 2^15. The eight lanes of a half group transpose their digits so that lane t holds the eight codes of
+// term t as one word, and store one word each.
+__device__ __forceinline__ uint32_t load_element(const TcPhase& ph, uint32_t tokens, uint32_t group_index, uint32_t lane) {
+    const uint32_t groups_per_row = ph.cols / 16;
+    if (group_index >= tokens * groups_per_row) return 0;
+    return __ldcg(ph.x + static_cast<uint64_t>(group_index) * 16 + (lane & 15));   // rows are contiguous: [tokens][cols]
+}
+
+__device__ __forceinline__ void split_group(const TcPhase& ph, uint32_t tokens, const uint32_t* anchor, uint32_t group_index, uint32_t bits,
+                                            uint32_t lane) {
+    const uint32_t groups_per_row = ph.cols / 16;
+    const bool active = group_index < tokens * groups_per_row;
+    const uint32_t token = active ? group_index / groups_per_row : 0, group = active ? group_index - token * groups_per_row : 0;
+    const uint32_t magnitude = bits & 0x7fffu, negative = (bits >> 15) & 1u;
+    uint32_t largest = max(magnitude, __shfl_xor_sync(0xffffffffu, magnitude, 8));
+    largest = max(largest, __shfl_xor_sync(0xffffffffu, largest, 4));
+    largest = max(largest, __shfl_xor_sync(0xffffffffu, largest, 2));
+    largest = max(largest, __shfl_xor_sync(0xffffffffu, largest, 1));
+    const int a = static_cast<int>(anchor[token]);
+    const int g = max(static_cast<int>(largest >> 7), 1);           // a subnormal has the exponent of field 1
+    const int q = min(max(g + 8 - a, -9), 8);
+    const uint32_t scale_code = q >= -6 ? static_cast<uint32_t>(q + 7) << 3 : 1u << (q + 9);
+    const uint32_t field = magnitude >> 7;
+    const uint32_t significand = field ? 128u + (magnitude & 127u) : magnitude;
+    // |x| = significand * 2^(max(field, 1) - 134); I = |x| * 2^(157 - q - A)
+    const int shift = min(max(static_cast<int>(max(field, 1u)) + 23 - a - q, -16), 15);
+    uint32_t value = shift >= 0 ? significand << shift : (significand + (1u << (-shift - 1))) >> -shift;
+    uint32_t digits = 0;    // code of term t in bits 4t .. 4t + 3
 #pragma unroll
-        for (uint32_t term = 0; term < kTerms; ++term) {
-            float largest = fmaxf(fabsf(r0), fabsf(r1));
-            largest = fmaxf(largest, __shfl_xor_sync(0xffffffffu, largest, 4));
-            largest = fmaxf(largest, __shfl_xor_sync(0xffffffffu, largest, 2));
-            largest = fmaxf(largest, __shfl_xor_sync(0xffffffffu, largest, 1));
-            uint32_t scale_code = 0;
-            float divisor = 0.0f, q0 = 0.0f, q1 = 0.0f;
-            if (largest > 0.0f) {
-                scale_code = e4m3_ceil_code(largest * inverse);
-                divisor = e4m3_positive_value(scale_code) * scale;   // exact: four significant bits times a power of two
-                q0 = __fdividef(r0, divisor);
-                q1 = __fdividef(r1, divisor);
-            }
-            float l0, l1;
-            const uint32_t byte = e2m1_nearest(q0, &l0) | (e2m1_nearest(q1, &l1) << 4);
-            if (term + 1 < kTerms) {
-                r0 = __fsub_rn(r0, __fmul_rn(l0, divisor));   // both exact
-                r1 = __fsub_rn(r1, __fmul_rn(l1, divisor));
-            }
-            uint32_t word = byte << (8 * (lane & 3));
-            word |= __shfl_xor_sync(0xffffffffu, word, 1);
-            word |= __shfl_xor_sync(0xffffffffu, word, 2);
-            const uint32_t n = term * 8 + token;
-            if (active && (lane & 3) == 0) *reinterpret_cast<uint32_t*>(codes + (n >> 3) * 1024 + (n & 7) * 128 + ((unit ^ (n & 7)) << 4)) = word;
-            if (active && (lane & 7) == 0) sf[(n & 31) * 16 + (n >> 5) * 4] = static_cast<uint8_t>(scale_code);
-            scale *= 0.125f;
-            inverse *= 8.0f;
+    for (int term = static_cast<int>(kTerms) - 1; term >= 0; --term) {
+        const uint32_t low = value & 7u;
+        const uint32_t carry = low > 4u ? 1u : 0u;
+        const uint32_t level = carry ? 8u - low : low;
+        value = (value >> 3) + carry;
+        digits |= (level | ((level ? (carry ^ negative) : 0u) << 3)) << (4 * term);
+    }
+    // 8 lanes x 8 nibbles, transposed: lane t of the eight ends up with nibble t of all eight, in lane order
+    uint32_t other = __shfl_xor_sync(0xffffffffu, digits, 4);
+    digits = (lane & 4) ? (other >> 16) | (digits & 0xffff0000u) : (digits & 0x0000ffffu) | (other << 16);
+    other = __shfl_xor_sync(0xffffffffu, digits, 2);
+    digits = (lane & 2) ? ((other & 0xff00ff00u) >> 8) | (digits & 0xff00ff00u) : (digits & 0x00ff00ffu) | ((other & 0x00ff00ffu) << 8);
+    other = __shfl_xor_sync(0xffffffffu, digits, 1);
+    digits = (lane & 1) ? ((other & 0xf0f0f0f0u) >> 4) | (digits & 0xf0f0f0f0u) : (digits & 0x0f0f0f0fu) | ((other & 0x0f0f0f0fu) << 4);
+    if (active) {
+        const uint32_t n = (lane & 7) * 8 + token, chunk = group >> 4, unit = (group & 15) >> 1, half = group & 1;
+        uint8_t* codes = ph.split + static_cast<uint64_t>(chunk) * kChunkBytes + (n >> 3) * 1024 + (n & 7) * 128 + ((unit ^ (n & 7)) << 4);
+        *reinterpret_cast<uint32_t*>(codes + half * 8 + ((lane >> 3) & 1) * 4) = digits;
+        if ((lane & 8) == 0) {
+            uint8_t* sf = ph.split + split_code_bytes(ph.cols) + static_cast<uint64_t>(group >> 2) * kSfAtomBytes + (group & 3);
+            sf[(n & 31) * 16 + (n >> 5) * 4] = static_cast<uint8_t>(scale_code);
         }
     }
 }
@@ -317,11 +328,10 @@ __device__ __forceinline__ bool cursor_next(const TcParams& p, Cursor& c) {
 
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1, const TcParams p) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    extern __shared__ __align__(1024) uint8_t smem[];
     float* term_scale = reinterpret_cast<float*>(smem + kStages * kStageBytes);   // [token]: scale of term 0 in the current phase
-    uint32_t* row_max = reinterpret_cast<uint32_t*>(term_scale + 8);              // [token]: this CTA's share of a scan
-    uint32_t* collected = row_max + 8;                                             // [token]: largest magnitudes of this CTA's SwiGLU outputs
+    uint32_t* anchor = reinterpret_cast<uint32_t*>(term_scale + 8);               // [token]: exponent field the term scales are anchored on
+    uint32_t* collected = anchor + 8;                                              // [token]: largest magnitudes of this CTA's SwiGLU outputs
     volatile uint32_t* acts_ready = collected + 8;                                 // [phase]: the phase's split activations are complete
     // full[S] (operand codes landed), empty[S], scales_landed[S], scales_ready[S] (copies to tensor memory issued),
     // acc_full[2], acc_empty[2]
@@ -330,6 +340,11 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (smem_u32(smem) & 1023u) {
+        // swizzled operand tiles want the window on a 1024-byte boundary, which is where the hardware puts it
+        if (threadIdx.x == 0) atomicCAS(p.status_word, 0u, kErrTcWindow);
+        return;
+    }
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + kStages);
     const uint32_t bar_scales_landed = smem_u32(bars + 2 * kStages), bar_scales_ready = smem_u32(bars + 3 * kStages);
@@ -387,7 +402,7 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
             weights_left = cursor_next(p, weights_at);
         }
     }
-    if (threadIdx.x >= 64 && threadIdx.x < 64 + 16) row_max[threadIdx.x - 64] = 0;   // row_max and collected
+    if (threadIdx.x >= 64 && threadIdx.x < 64 + 16) anchor[threadIdx.x - 64] = 0;   // anchor and collected
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemColumns)
                      : "memory");
@@ -522,38 +537,65 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
         uint32_t acc_phase[2] = {0, 0};
         bool alive = true;
         asm volatile("griddepcontrol.wait;" ::: "memory");   // the activations may come from the launch before this one; all stores follow
+        uint32_t meeting = 0;
+        if (leader) meeting = *static_cast<volatile uint32_t*>(p.grid_barrier + 3);   // written by the launch before, at its last meeting
+        const uint32_t first_pair = (blockIdx.x * 4 + (warp - 2)) * 2 + (lane >> 4), pair_stride = gridDim.x * 8;   // this half warp's groups
         for (uint32_t phase = 0; alive && phase < p.phases; ++phase) {
             const TcPhase& ph = p.phase[phase];
-            // every CTA has finished the phase before (its output is this phase's input, its maxima are collected)
-            if (phase != 0 && !grid_meet(p, leader, abort_flag)) break;
-            // this CTA's slice of the activations, in whole 16-element groups
             const uint32_t groups = p.tokens * (ph.cols / 16);
-            const uint32_t first_pair = static_cast<uint32_t>(static_cast<uint64_t>(blockIdx.x) * groups / gridDim.x) * 8;
-            const uint32_t count = static_cast<uint32_t>(static_cast<uint64_t>(blockIdx.x + 1) * groups / gridDim.x) * 8 - first_pair;
+            uint32_t held[kHeld];
             if (ph.scan) {
-                for (uint32_t i = worker; i < count; i += kWorkers) {
-                    const uint32_t pair = first_pair + i;
-                    const uint32_t both = __ldcg(reinterpret_cast<const uint32_t*>(ph.x) + pair);
-                    atomicMax(&row_max[pair / (ph.cols / 2)], max((both << 16) & 0x7fff0000u, both & 0x7fff0000u));   // magnitudes order like their bit patterns
+                // the row maxima of an input from outside: every lane looks at its own elements (and keeps them)
+#pragma unroll
+                for (uint32_t j = 0; j < kHeld; ++j) held[j] = load_element(ph, p.tokens, first_pair + j * pair_stride, lane);
+                auto note = [&](uint32_t index, uint32_t bits) {   // whole warps: the two groups of a pair go together
+                    uint32_t largest = bits & 0x7fffu;
+                    largest = max(largest, __shfl_xor_sync(0xffffffffu, largest, 8));
+                    largest = max(largest, __shfl_xor_sync(0xffffffffu, largest, 4));
+                    largest = max(largest, __shfl_xor_sync(0xffffffffu, largest, 2));
+                    largest = max(largest, __shfl_xor_sync(0xffffffffu, largest, 1));
+                    if ((lane & 15) == 0 && largest) atomicMax(&collected[index / (ph.cols / 16)], largest << 16);   // zero past the end
+                };
+#pragma unroll
+                for (uint32_t j = 0; j < kHeld; ++j) {
+                    if (first_pair - (lane >> 4) + j * pair_stride < groups) note(first_pair + j * pair_stride, held[j]);
+                }
+                for (uint32_t index = first_pair + kHeld * pair_stride; index - (lane >> 4) < groups; index += pair_stride) {
+                    note(index, load_element(ph, p.tokens, index, lane));
                 }
                 workers_sync();
-                if (worker < 8 && row_max[worker]) atomicMax(ph.row_max + worker, row_max[worker]);
-                if (!grid_meet(p, leader, abort_flag)) break;
+                if (worker < 8) {
+                    if (collected[worker]) atomicMax(ph.row_max + worker, collected[worker]);
+                    collected[worker] = 0;
+                }
+            }
+            // every CTA has found its maxima, or has finished the phase before: its output is this phase's input
+            // and its maxima are collected
+            if (!grid_meet(p, leader, meeting, abort_flag)) break;
+            if (!ph.scan) {
+#pragma unroll
+                for (uint32_t j = 0; j < kHeld; ++j) held[j] = load_element(ph, p.tokens, first_pair + j * pair_stride, lane);
             }
             if (worker < 8) {
-                const uint32_t largest = *static_cast<volatile uint32_t*>(ph.row_max + worker);
-                int field = static_cast<int>(largest >> 23);
-                field = field < 30 ? 30 : (field > 250 ? 250 : field);    // all six term scales stay normal f32 numbers
-                float scale = __uint_as_float(static_cast<uint32_t>(field - 7) << 23);
-                if (largest >= 0x7f800000u) scale = __uint_as_float(0x7fc00000u);   // a NaN or infinity in the row: the row's outputs are NaN
+                // term 0 of the row has the global scale 2^(A - 135): all eight term scales are normal f32 numbers
+                const uint32_t largest = *static_cast<volatile uint32_t*>(ph.row_max + worker) >> 16;
+                const uint32_t a = min(max(largest >> 7, 40u), 250u);
+                float scale = __uint_as_float((a - 8) << 23);
+                if (largest >= 0x7f80u) scale = __uint_as_float(0x7fc00000u);   // a NaN or infinity in the row: the row's outputs are NaN
                 term_scale[worker] = scale;
-                row_max[worker] = 0;
+                anchor[worker] = a;
             }
             workers_sync();
-            split_pairs(ph, p.tokens, first_pair, count, term_scale, worker);
+#pragma unroll
+            for (uint32_t j = 0; j < kHeld; ++j) {
+                if (first_pair - (lane >> 4) + j * pair_stride < groups) split_group(ph, p.tokens, anchor, first_pair + j * pair_stride, held[j], lane);
+            }
+            for (uint32_t index = first_pair + kHeld * pair_stride; index - (lane >> 4) < groups; index += pair_stride) {
+                split_group(ph, p.tokens, anchor, index, load_element(ph, p.tokens, index, lane), lane);
+            }
             // every CTA's slice is in place (and readable by the TMA engine) before any CTA loads from the split
             asm volatile("fence.proxy.async;" ::: "memory");
-            if (!grid_meet(p, leader, abort_flag)) break;
+            if (!grid_meet(p, leader, meeting, abort_flag)) break;
             if (blockIdx.x == 0 && worker < 8) ph.row_max[worker] = 0;   // every CTA has read them: clean for the next launch
             if (leader) acts_ready[phase] = 1;
 
@@ -568,11 +610,10 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
                 }
                 acc_phase[buffer] ^= 1;
                 tc_fence_after();
-                uint32_t v[3][16];
+                uint32_t v[kCols / 16][16];
                 const uint32_t taddr = tmem_base + kTmemAcc + buffer * 64 + ((quadrant * 32) << 16);
-                tc_load16(taddr, v[0]);
-                tc_load16(taddr + 16, v[1]);
-                tc_load16(taddr + 32, v[2]);
+#pragma unroll
+                for (uint32_t j = 0; j < kCols / 16; ++j) tc_load16(taddr + 16 * j, v[j]);
                 tc_wait_ld();
                 tc_fence_before();
                 __syncwarp();
@@ -600,6 +641,8 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
                 }
             }
         }
+        // the next launch goes on counting meetings where this one stopped (every CTA stores the same number)
+        if (alive && leader) p.grid_barrier[3] = meeting;
     }
 
     tc_fence_before();

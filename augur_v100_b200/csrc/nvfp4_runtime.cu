@@ -261,6 +261,11 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_plan_devi
                             plan->owner_stream);
     }
     if (e == cudaSuccess) e = cudaStreamSynchronize(plan->owner_stream);
+    if (e == cudaSuccess && *out_status != 0) {
+        // a wait ran out: the launch left its meeting counters and row maxima (header words 16..63) half used
+        e = cudaMemsetAsync(plan->status_word + 16, 0, (64 - 16) * sizeof(uint32_t), plan->owner_stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(plan->owner_stream);
+    }
     return e == cudaSuccess ? ok() : make_result(AUGUR_CUDA_STATUS_COMPLETION_FAILURE, e);
 }
 

@@ -107,7 +107,7 @@ def test_f32_epilogue(ctx):
     rows, cols, tokens = 256, 2176, 8
     codes, scales, glob, x_bits, proj = _case(ctx, rows, cols, tokens, 11, epilogue=abi.EPILOGUE_LINEAR_F32)
     y64 = oracle.linear_f64(codes, scales, glob, rows, cols, x_bits, threads=4)
-    # the six-term split of the activations and f32 accumulation: far inside the BF16 rounding step (2^-9)
+    # the eight-digit split of the activations and f32 accumulation: far inside the BF16 rounding step (2^-9)
     assert rel_error_f32(proj.out.cpu().numpy(), y64) <= 2e-3
 
 
