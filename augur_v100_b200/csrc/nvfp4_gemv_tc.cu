@@ -419,7 +419,7 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
         // phase's split activations are complete. Neither waits for the other.
         Cursor acts_at;
         bool acts_left = cursor_begin(p, acts_at);
-        uint32_t acts_issued = 0, idle = 0;
+        uint32_t acts_issued = 0, idle = 0, fenced_phases = 0;
         while (acts_left) {
             bool progressed = false;
             if (weights_left) {
@@ -433,8 +433,11 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
                 }
             }
             if (acts_issued < weights_issued && acts_ready[acts_at.phase]) {
-                // the split activations were written with ordinary stores, by this and other CTAs
-                asm volatile("fence.proxy.async;" ::: "memory");
+                if (fenced_phases <= acts_at.phase) {
+                    // the split activations were written with ordinary stores, by this and other CTAs
+                    asm volatile("fence.proxy.async;" ::: "memory");
+                    fenced_phases = acts_at.phase + 1;
+                }
                 issue_activations(acts_issued % kStages, acts_at);
                 ++acts_issued;
                 acts_left = cursor_next(p, acts_at);
