@@ -1,6 +1,6 @@
 // Small-token (1..8) NVFP4 linear and MLP block for sm_100a on the tensor-memory path: the weights go from HBM to
 // the tensor cores without a single per-element instruction on the SMs, and a whole MLP block is ONE launch in
-// which the weight stream never stops.
+// which the weight stream does not stop at the boundary between its two products.
 //
 //   weights      TCGEN05 layout (codes K-major as in the checkpoint, block scales in 512-byte atoms), the
 //                128-row operand of tcgen05.mma kind::mxf4nvf4: TMA brings 128 rows x 256 k (16 KB of codes
@@ -16,18 +16,26 @@
 //   accumulator  128 weight rows x 64 columns of f32 in tensor memory, two buffers; the epilogue warps add
 //                the terms of a token with their scales and finish the rows.
 //
-// A launch runs one phase (a linear) or two (gate|up with SiLU(gate) * up, then down, whose activations are the
-// first phase's output). Per phase a CTA owns whole 128-row tiles over the whole k range whenever there are at
-// least as many tiles as resident CTAs (two per SM); otherwise every tile is cut along k into equal parts, one
-// per CTA: partial sums go to plan scratch with an arrival counter per 32 rows, and the last arriver adds them in
-// part order and finishes the rows. Results are bit-reproducible.
+// A launch is a list of steps, each a set of (row tile, k range) items dealt round-robin to the CTAs (two per
+// SM, all resident: two short rings consumed in order lose less to a late stage than one long ring). A linear
+// is one step: whole tiles when there are at least about as many as CTAs, else every tile cut along k into equal
+// parts whose partial sums meet in plan scratch (arrival counter per 32 rows; the last arriver adds the parts in
+// a fixed order and finishes the rows; bit-reproducible). The MLP block is two steps when the
+// gate|up tiles fit the CTAs: gate|up in whole tiles, then down in k parts. The second product needs every CTA's
+// outputs of the first and their largest magnitudes per token row before it can split them: the CTAs arrive at
+// a counter when their outputs are stored, wait for all, split, arrive at a second counter, and the activation
+// loads of the second product wait for that one; its weights are in the ring by then. With more gate|up tiles
+// than CTAs the block is four steps in two waves - gate|up tiles 0..G-1 (G = CTAs), gate|up tiles G.., down over
+// the k range that the first wave's outputs feed, down over the rest - so that the first wave's outputs are met
+// over and split while the second wave streams: the down partial sums of the two k ranges carry separate
+// power-of-two scales and are added in f32 like any other parts.
 //
-// Roles of a CTA: one thread streams the weight stages of all its work, both phases back to back, and keeps
-// doing so while activations are not ready yet (the ring buffers that time); one thread copies block scales to
-// tensor memory; one issues the MMAs; four warps split activations and run the epilogues. The split needs
-// every CTA's slice before any CTA can use it, and the second phase needs every CTA's output of the first:
-// the grid meets in global memory (all CTAs are resident: the grid never exceeds two CTAs per SM), once in
-// the first phase and twice at the phase boundary.
+// Roles of a CTA: one thread streams the weight halves of the stages of all its items back to back and keeps
+// doing so while activations are not ready yet (the ring buffers that time); one thread sends the activation
+// halves after them; one copies block scales to tensor memory; one issues the MMAs; four warps split activations
+// and run the epilogues. CTAs meet through counters in the
+// plan's header: full meetings before the first product (row maxima of the input, then its split), and
+// arrive-now / wait-later counters per wave.
 //
 // Every wait is bounded; a wait that runs out records a code in the plan's status word, raises a CTA-wide abort
 // flag, and all roles fall through to the common exit where tensor memory is released.
@@ -53,27 +61,35 @@ constexpr uint32_t kStageActCodes = kStageCodeBytes + kStageSfBytes;        // o
 constexpr uint32_t kStageActSf = kStageActCodes + kChunkBytes;
 constexpr uint32_t kStageBytes = kStageActSf + kStageSfBytes;               // 28 KB
 constexpr uint32_t kStages = 4;                        // per CTA; two CTAs share an SM
-constexpr uint32_t kThreads = 224;                     // warp 0 TMA, warp 1 MMA, warps 2..5 split and epilogue, warp 6 scale copies
+constexpr uint32_t kCtasPerSm = 2;                     // two rings consumed in order stall less on a late stage than one of twice the depth
+constexpr uint32_t kThreads = 288;                     // warp 0 TMA of weights, 1 MMA, 2..5 split and epilogue, 6 and 8 scale copies, 7 TMA of activations
 constexpr uint32_t kSmemBytes = kStages * kStageBytes + 512 /*small state*/;   // the stages start the (1024-byte aligned) window
-constexpr uint32_t kCtasPerSm = 2;                     // half of an SM's shared and tensor memory each: a CTA of the next launch
-                                                       // moves in (and fills its ring) as soon as one of this launch leaves
 constexpr uint32_t kTmemAcc = 0;                       // two accumulators of 64 columns
 constexpr uint32_t kTmemSfWeight = 128;                // 16 columns per ring stage
 constexpr uint32_t kTmemSfAct = kTmemSfWeight + kStages * 16;
 constexpr uint32_t kTmemColumns = 256;
 static_assert(kTmemSfAct + kStages * 16 <= kTmemColumns, "tensor memory columns");
+static_assert(kCtasPerSm * kTmemColumns <= 512, "tensor memory of an SM");
 static_assert(kCtasPerSm * (kSmemBytes + 1024) <= 228 * 1024, "two CTAs per SM, a kilobyte each reserved by the system");
 static_assert(kTerms == 8, "the digit transposition is 8 lanes x 8 nibbles");
 static_assert(kStageBytes % 1024 == 0 && kStageActCodes % 1024 == 0, "swizzled operand tiles are 1024-byte aligned");
 constexpr uint32_t kSlotFloats = 256;                  // one partial: 32 rows x 8 tokens
 constexpr uint32_t kWorkers = 128;                     // the four split / epilogue warps
-constexpr uint32_t kMaxPhases = 2;
-constexpr uint32_t kGridWaitLimit = 1u << 22;          // polls of the grid barrier (a fraction of a microsecond each) before giving up
-
-constexpr uint32_t kErrTcProducer = 0x301, kErrTcFull = 0x302, kErrTcAccEmpty = 0x303, kErrTcAccFull = 0x304,
-                   kErrTcScalesLanded = 0x305, kErrTcScalesReady = 0x306, kErrTcGridBarrier = 0x307, kErrTcWindow = 0x308;
+constexpr uint32_t kMaxPhases = 2, kMaxJobs = 3, kMaxSteps = 4;
+constexpr uint32_t kGridWaitLimit = 1u << 22;          // polls of a counter (a fraction of a microsecond each) before giving up
 constexpr uint32_t kHeld = 4;                          // elements a lane keeps in registers between the scan and the split
 
+constexpr uint32_t kErrTcProducer = 0x301, kErrTcFull = 0x302, kErrTcAccEmpty = 0x303, kErrTcAccFull = 0x304,
+                   kErrTcScalesLanded = 0x305, kErrTcScalesReady = 0x306, kErrTcGridBarrier = 0x307, kErrTcWindow = 0x308,
+                   kErrTcWave = 0x309;
+
+// Words of the plan's header (the 256 bytes in front of the scratch; word 0 is the status word) that this kernel
+// owns: no other kernel of the library writes there, plan creation zeroes them, every launch leaves them ready
+// for the next one.
+constexpr uint32_t kHeaderMeeting = 16;    // three arrival counters of the full meetings, used in turn
+constexpr uint32_t kHeaderEpoch = 19;      // meetings held so far, modulo 12 (two per launch)
+constexpr uint32_t kHeaderWave = 20;       // [launch parity][wave]{outputs stored, split stored}
+constexpr uint32_t kHeaderRowMax = 32;     // [job][token] bits of the row's largest magnitude
 
 // The split activations in global memory (plan scratch): the image the ring stages want, chunk by chunk.
 //   [chunk = k / 256][64 rows][128 bytes]   codes, rows already in the 128-byte swizzle of a shared-memory operand tile
@@ -87,23 +103,34 @@ struct TcPhase {
     const uint16_t* x;            // [tokens][cols] BF16 (second phase: what the first phase wrote)
     uint8_t* split;               // the split activations (layout above)
     void* out;
-    float* partials;              // [tile * 4 + quadrant][part][32 rows][8 tokens]
+    float* partials;              // [tile * 4 + quadrant][contributor][32 rows][8 tokens]
     uint32_t* counters;           // [tile * 4 + quadrant], zero between launches
-    uint32_t* row_max;            // [token] bits of the row's largest magnitude, zero between launches
-    uint32_t* collect;            // SwiGLU epilogue: the next phase's row_max, or null
     uint32_t rows;                // physical weight rows (SwiGLU: gate and up interleaved by 16)
     uint32_t out_rows;            // output width
     uint32_t cols, epilogue;
-    uint32_t tiles, k_blocks, parts;   // `parts` equal k ranges per tile (1: whole tiles)
-    uint32_t scan;                // this launch finds row_max itself (else the phase before collected it)
+    uint32_t contributors;        // items per tile over all steps of the phase (1: whole tiles)
     float global_a, global_b;
+};
+
+// One split of activations: groups [group0, group0 + groups) of every token row of a phase's input.
+struct TcJob {
+    uint32_t phase, group0, groups;
+};
+
+// One set of items: tiles [tile0, tile0 + tiles) of a phase over the k blocks [kb0, kb1), every tile in `parts`
+// equal k ranges; the activations come from `job`; a part is contributor slot0 + part of its tile.
+struct TcStep {
+    uint32_t phase, job, tile0, tiles, kb0, kb1, parts, slot0;
+    uint32_t feeds;               // the job that splits this step's outputs (SwiGLU steps of the MLP block), or 0
+    uint32_t keeps;               // every CTA has at most one item of the step and finishes it alone: it splits its own outputs
 };
 
 struct TcParams {
     TcPhase phase[kMaxPhases];
-    uint32_t phases, tokens;
-    uint32_t* grid_barrier;       // {three arrival counters used in turn, index of the next meeting modulo 3}
-    uint32_t* status_word;
+    TcJob job[kMaxJobs];
+    TcStep step[kMaxSteps];
+    uint32_t jobs, steps, tokens;
+    uint32_t* header;             // the plan's header words; header[0] is the status word
 };
 
 __device__ __forceinline__ void tc_load16(uint32_t taddr, uint32_t (&v)[16]) {
@@ -116,31 +143,42 @@ __device__ __forceinline__ void tc_load16(uint32_t taddr, uint32_t (&v)[16]) {
 }
 __device__ __forceinline__ void workers_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
-// All CTAs of the grid meet (the four worker warps of each; thread `leader` speaks for its CTA). Everything the
-// workers wrote before is visible to every CTA's workers after. Returns false if the wait ran out.
-// Meeting number m (counted over all launches of the plan, modulo 3, in `meeting`) uses counter m % 3: one
-// release-add per CTA, then acquire-loads until all have arrived. The last arriver clears counter (m - 1) % 3,
-// which every CTA has stopped reading (all are at meeting m) and which is not used again before meeting m + 2;
-// nobody gets to meeting m + 2 before the last arriver of m, its store behind it, has arrived at m + 1.
+// ---- counters between CTAs (thread `leader` of the four worker warps speaks for its CTA) ----------------------
+__device__ __forceinline__ uint32_t counter_arrive(uint32_t* counter) {
+    uint32_t before;
+    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(before) : "l"(counter) : "memory");
+    return before;
+}
+__device__ __forceinline__ uint32_t counter_read(const uint32_t* counter) {
+    uint32_t seen;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+    return seen;
+}
+// Everything the CTAs wrote before arriving is visible after the wait. False if the wait ran out.
+__device__ __forceinline__ bool counter_wait(const TcParams& p, const uint32_t* counter, uint32_t code, volatile uint32_t* abort_flag) {
+    for (uint32_t spin = 0; counter_read(counter) < gridDim.x;) {
+        if (++spin > kGridWaitLimit || ((spin & 255u) == 255u && *abort_flag)) {
+            *abort_flag = 1;
+            atomicCAS(p.header, 0u, code);
+            return false;
+        }
+    }
+    return true;
+}
+
+// All CTAs of the grid meet. Everything the workers wrote before is visible to every CTA's workers after.
+// Meeting number m (counted over all launches of the plan, modulo 3, in `meeting`) uses counter m % 3. The last
+// arriver clears counter (m - 1) % 3, which every CTA has stopped reading (all are at meeting m) and which is not
+// used again before meeting m + 2; nobody gets to meeting m + 2 before the last arriver of m, its store behind it,
+// has arrived at m + 1.
 __device__ __forceinline__ bool grid_meet(const TcParams& p, bool leader, uint32_t& meeting, volatile uint32_t* abort_flag) {
     workers_sync();
     if (leader) {
-        uint32_t* mine = p.grid_barrier + meeting;
-        uint32_t arrived;
-        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(arrived) : "l"(mine) : "memory");
-        if (arrived + 1 == gridDim.x) {
-            asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p.grid_barrier + (meeting + 2) % 3), "r"(0u) : "memory");
+        uint32_t* mine = p.header + kHeaderMeeting + meeting;
+        if (counter_arrive(mine) + 1 == gridDim.x) {
+            asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p.header + kHeaderMeeting + (meeting + 2) % 3), "r"(0u) : "memory");
         } else {
-            uint32_t spin = 0, seen;
-            for (;;) {
-                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
-                if (seen >= gridDim.x) break;
-                if (++spin > kGridWaitLimit || ((spin & 255u) == 255u && *abort_flag)) {
-                    *abort_flag = 1;
-                    atomicCAS(p.status_word, 0u, kErrTcGridBarrier);
-                    break;
-                }
-            }
+            counter_wait(p, mine, kErrTcGridBarrier, abort_flag);
         }
     }
     meeting = (meeting + 1) % 3;
@@ -150,49 +188,50 @@ __device__ __forceinline__ bool grid_meet(const TcParams& p, bool leader, uint32
 
 // ---- activation split (the four worker warps of every CTA; the grid's worker warps share the groups out) ----
 // One lane per element, sixteen neighbouring lanes per 16-element group; warp w of the grid's W worker warps
-// takes the group pairs w, w + W, ... With A the exponent field of the token row's largest magnitude and G that
-// of the group's, the group's block scale is 2^q, q = G + 8 - A (the row's largest group gets 2^8; E4M3 holds
-// powers of two down to 2^-9, smaller groups keep 2^-9 and lose low bits), term t has the global scale
-// 2^(A - 135) * 8^-t, and the element is the integer I = |x| / 2^(q + A - 157): at most 255 * 2^15 for the
-// group's largest element, exact for every element within 2^-15 of it, rounded to nearest below. I is written
-// in radix 8 with digits -4..4 (from the low end: a digit above 4 becomes digit - 8 and carries), digit t being
-// the code of term t: level |digit| / 2, sign of digit times sign of x. Eight digits reach 4 * (8^8 - 1) / 7
-// > 255 * 2^15. The eight lanes of a half group transpose their digits so that lane t holds the eight codes of
-// term t as one word, and store one word each.
-__device__ __forceinline__ uint32_t load_element(const TcPhase& ph, uint32_t tokens, uint32_t group_index, uint32_t lane) {
-    const uint32_t groups_per_row = ph.cols / 16;
-    if (group_index >= tokens * groups_per_row) return 0;
-    return __ldcg(ph.x + static_cast<uint64_t>(group_index) * 16 + (lane & 15));   // rows are contiguous: [tokens][cols]
+// takes the group pairs w, w + W, ... of a job. With A the exponent field of the largest magnitude of the token
+// row (within the job) and G that of the group's, the group's block scale is 2^q, q = G + 8 - A (the row's
+// largest group gets 2^8; E4M3 holds powers of two down to 2^-9, smaller groups keep 2^-9 and lose low bits),
+// term t has the global scale 2^(A - 155) * 8^t (times the level, half the digit), and the element is the integer I = |x| / 2^(q + A - 156): at
+// most 255 * 2^14 for the group's largest element, exact for every element within 2^-14 of it, rounded to
+// nearest below. I is written in radix 8 with digits -4..3: I plus 4 in every octal place has the digits plus 4
+// as its octal digits (eight of them: 3 * (8^8 - 1) / 7 > 255 * 2^14). Digit t is the code of term t: level
+// |digit| / 2, sign of digit times sign of x; all eight are formed at once in the nibbles of one word. The eight
+// lanes of a half group transpose their words so that lane t holds the eight codes of term t, and store one
+// word each.
+__device__ __forceinline__ uint32_t load_element(const TcPhase& ph, const TcJob& job, uint32_t tokens, uint32_t index, uint32_t lane) {
+    if (index >= tokens * job.groups) return 0;
+    const uint32_t token = index / job.groups, group = job.group0 + (index - token * job.groups);
+    return __ldcg(ph.x + static_cast<uint64_t>(token) * ph.cols + group * 16 + (lane & 15));
 }
 
-__device__ __forceinline__ void split_group(const TcPhase& ph, uint32_t tokens, const uint32_t* anchor, uint32_t group_index, uint32_t bits,
-                                            uint32_t lane) {
-    const uint32_t groups_per_row = ph.cols / 16;
-    const bool active = group_index < tokens * groups_per_row;
-    const uint32_t token = active ? group_index / groups_per_row : 0, group = active ? group_index - token * groups_per_row : 0;
+// First half of a group's split, before the row's anchor is known: the group's largest magnitude (returned), the
+// digits relative to it (`drop` low bits fewer), the codes stored. Whole warps; `index` past the job is inactive.
+__device__ __forceinline__ uint32_t split_codes(const TcPhase& ph, const TcJob& job, uint32_t tokens, uint32_t index, uint32_t bits, uint32_t drop,
+                                                uint32_t lane) {
+    const bool active = index < tokens * job.groups;
+    const uint32_t token = active ? index / job.groups : 0, group = active ? job.group0 + (index - token * job.groups) : 0;
     const uint32_t magnitude = bits & 0x7fffu, negative = (bits >> 15) & 1u;
     uint32_t largest = max(magnitude, __shfl_xor_sync(0xffffffffu, magnitude, 8));
     largest = max(largest, __shfl_xor_sync(0xffffffffu, largest, 4));
     largest = max(largest, __shfl_xor_sync(0xffffffffu, largest, 2));
     largest = max(largest, __shfl_xor_sync(0xffffffffu, largest, 1));
-    const int a = static_cast<int>(anchor[token]);
     const int g = max(static_cast<int>(largest >> 7), 1);           // a subnormal has the exponent of field 1
-    const int q = min(max(g + 8 - a, -9), 8);
-    const uint32_t scale_code = q >= -6 ? static_cast<uint32_t>(q + 7) << 3 : 1u << (q + 9);
     const uint32_t field = magnitude >> 7;
     const uint32_t significand = field ? 128u + (magnitude & 127u) : magnitude;
-    // |x| = significand * 2^(max(field, 1) - 134); I = |x| * 2^(157 - q - A)
-    const int shift = min(max(static_cast<int>(max(field, 1u)) + 23 - a - q, -16), 15);
-    uint32_t value = shift >= 0 ? significand << shift : (significand + (1u << (-shift - 1))) >> -shift;
-    uint32_t digits = 0;    // code of term t in bits 4t .. 4t + 3
-#pragma unroll
-    for (int term = static_cast<int>(kTerms) - 1; term >= 0; --term) {
-        const uint32_t low = value & 7u;
-        const uint32_t carry = low > 4u ? 1u : 0u;
-        const uint32_t level = carry ? 8u - low : low;
-        value = (value >> 3) + carry;
-        digits |= (level | ((level ? (carry ^ negative) : 0u) << 3)) << (4 * term);
-    }
+    // |x| = significand * 2^(max(field, 1) - 134); I = |x| * 2^(156 - q - A) = significand * 2^(field - G + 14) with q = G + 8 - A
+    const int shift = max(static_cast<int>(max(field, 1u)) - g + 14 - static_cast<int>(drop), -16);
+    const uint32_t value = shift >= 0 ? significand << shift : (significand + (1u << (-shift - 1))) >> -shift;
+    // octal digits of I + 44444444 (octal), one per nibble: d = digit + 4 in 0..7
+    uint32_t d = (value + 0x924924u) & 0xffffffu;
+    d = (d & 0x00000fffu) | ((d & 0x00fff000u) << 4);
+    d = (d & 0x003f003fu) | ((d & 0x0fc00fc0u) << 2);
+    d = (d & 0x07070707u) | ((d & 0x38383838u) << 1);
+    // level = |d - 4|: d & 3 where d >= 4, else 4 - d = (~d & 3) + 1; the digit is negative where d < 4
+    const uint32_t upper = (d >> 2) & 0x11111111u, upper_mask = upper * 15u;
+    const uint32_t level = ((d & 0x33333333u) & upper_mask) | (((~d & 0x33333333u) + 0x11111111u) & ~upper_mask);
+    const uint32_t nonzero = (level | (level >> 1) | (level >> 2)) & 0x11111111u;
+    const uint32_t minus = ((upper ^ 0x11111111u) ^ (negative * 0x11111111u)) & nonzero;
+    uint32_t digits = level | (minus << 3);    // code of term t in bits 4t .. 4t + 3
     // 8 lanes x 8 nibbles, transposed: lane t of the eight ends up with nibble t of all eight, in lane order
     uint32_t other = __shfl_xor_sync(0xffffffffu, digits, 4);
     digits = (lane & 4) ? (other >> 16) | (digits & 0xffff0000u) : (digits & 0x0000ffffu) | (other << 16);
@@ -200,20 +239,95 @@ __device__ __forceinline__ void split_group(const TcPhase& ph, uint32_t tokens, 
     digits = (lane & 2) ? ((other & 0xff00ff00u) >> 8) | (digits & 0xff00ff00u) : (digits & 0x00ff00ffu) | ((other & 0x00ff00ffu) << 8);
     other = __shfl_xor_sync(0xffffffffu, digits, 1);
     digits = (lane & 1) ? ((other & 0xf0f0f0f0u) >> 4) | (digits & 0xf0f0f0f0u) : (digits & 0x0f0f0f0fu) | ((other & 0x0f0f0f0fu) << 4);
-    if (active) {
+    // lanes t and t + 8 hold the two words of the group's eight bytes in row n = t * 8 + token
+    other = __shfl_xor_sync(0xffffffffu, digits, 8);
+    if (active && (lane & 8) == 0) {
         const uint32_t n = (lane & 7) * 8 + token, chunk = group >> 4, unit = (group & 15) >> 1, half = group & 1;
         uint8_t* codes = ph.split + static_cast<uint64_t>(chunk) * kChunkBytes + (n >> 3) * 1024 + (n & 7) * 128 + ((unit ^ (n & 7)) << 4);
-        *reinterpret_cast<uint32_t*>(codes + half * 8 + ((lane >> 3) & 1) * 4) = digits;
-        if ((lane & 8) == 0) {
-            uint8_t* sf = ph.split + split_code_bytes(ph.cols) + static_cast<uint64_t>(group >> 2) * kSfAtomBytes + (group & 3);
-            sf[(n & 31) * 16 + (n >> 5) * 4] = static_cast<uint8_t>(scale_code);
+        *reinterpret_cast<uint2*>(codes + half * 8) = make_uint2(digits, other);
+    }
+    return largest;
+}
+
+// Second half, with the row's anchor: the group's block scale 2^q, q = G + 8 - A. A group more than 2^17 below its
+// row's largest magnitude keeps 2^-9 and has its codes redone with that many low bits fewer (rare).
+__device__ __forceinline__ void split_scales(const TcPhase& ph, const TcJob& job, uint32_t tokens, const uint32_t* anchor, uint32_t index,
+                                             uint32_t bits, uint32_t largest, uint32_t lane) {
+    const bool active = index < tokens * job.groups;
+    const uint32_t token = active ? index / job.groups : 0, group = active ? job.group0 + (index - token * job.groups) : 0;
+    const int q = max(static_cast<int>(largest >> 7), 1) + 8 - static_cast<int>(anchor[token]);
+    const uint32_t drop = active && q < -9 ? static_cast<uint32_t>(-9 - q) : 0u;
+    if (__any_sync(0xffffffffu, drop != 0)) split_codes(ph, job, tokens, index, bits, drop, lane);
+    if (active && (lane & 8) == 0) {
+        const int clamped = min(max(q, -9), 8);
+        const uint32_t scale_code = clamped >= -6 ? static_cast<uint32_t>(clamped + 7) << 3 : 1u << (clamped + 9);
+        const uint32_t n = (lane & 7) * 8 + token;
+        uint8_t* sf = ph.split + split_code_bytes(ph.cols) + static_cast<uint64_t>(group >> 2) * kSfAtomBytes + (group & 3);
+        sf[(n & 31) * 16 + (n >> 5) * 4] = static_cast<uint8_t>(scale_code);
+    }
+}
+
+// The term scales of a job from the row maxima every CTA has contributed to (workers 0..7, one token row each).
+__device__ __forceinline__ void job_scales(const TcParams& p, uint32_t job, uint32_t worker, float* term_scale, uint32_t* anchor) {
+    if (worker < 8) {
+        const uint32_t largest = *static_cast<volatile uint32_t*>(p.header + kHeaderRowMax + 8 * job + worker) >> 16;
+        // term 0 of the row has the global scale 2^(A - 155), term 7 2^(A - 134): all normal f32 numbers
+        const uint32_t a = min(max(largest >> 7, 40u), 250u);
+        float scale = __uint_as_float((a - 28) << 23);
+        if (largest >= 0x7f80u) scale = __uint_as_float(0x7fc00000u);   // a NaN or infinity in the row: the row's outputs are NaN
+        term_scale[8 * job + worker] = scale;
+        anchor[8 * job + worker] = a;
+    }
+    workers_sync();
+}
+
+// This CTA's share of a job (group pairs first_pair, first_pair + pair_stride, ...): the first kHeld groups of each
+// lane are in `held`; their codes are stored before the anchor is known (`largest` keeps what the second half
+// needs), groups beyond them only add to the row maxima here and are split whole in the second half.
+__device__ __forceinline__ void share_codes(const TcParams& p, uint32_t job_index, const uint32_t (&held)[kHeld], uint32_t (&largest)[kHeld],
+                                            uint32_t* collected, uint32_t first_pair, uint32_t pair_stride, uint32_t lane) {
+    const TcJob& job = p.job[job_index];
+    const TcPhase& ph = p.phase[job.phase];
+    const uint32_t groups = p.tokens * job.groups, warp_first = first_pair - (lane >> 4);
+#pragma unroll
+    for (uint32_t j = 0; j < kHeld; ++j) {
+        largest[j] = 0;
+        if (warp_first + j * pair_stride < groups) {
+            const uint32_t index = first_pair + j * pair_stride;
+            largest[j] = split_codes(ph, job, p.tokens, index, held[j], 0, lane);
+            if (collected && (lane & 15) == 0 && largest[j]) atomicMax(&collected[index / job.groups], largest[j] << 16);   // zero past the end
         }
+    }
+    if (!collected) return;
+    for (uint32_t index = first_pair + kHeld * pair_stride; index - (lane >> 4) < groups; index += pair_stride) {
+        uint32_t most = load_element(ph, job, p.tokens, index, lane) & 0x7fffu;
+        most = max(most, __shfl_xor_sync(0xffffffffu, most, 8));
+        most = max(most, __shfl_xor_sync(0xffffffffu, most, 4));
+        most = max(most, __shfl_xor_sync(0xffffffffu, most, 2));
+        most = max(most, __shfl_xor_sync(0xffffffffu, most, 1));
+        if ((lane & 15) == 0 && most) atomicMax(&collected[index / job.groups], most << 16);
+    }
+}
+__device__ __forceinline__ void share_scales(const TcParams& p, uint32_t job_index, const uint32_t* anchor, const uint32_t (&held)[kHeld],
+                                             const uint32_t (&largest)[kHeld], uint32_t first_pair, uint32_t pair_stride, uint32_t lane) {
+    const TcJob& job = p.job[job_index];
+    const TcPhase& ph = p.phase[job.phase];
+    const uint32_t groups = p.tokens * job.groups, warp_first = first_pair - (lane >> 4);
+#pragma unroll
+    for (uint32_t j = 0; j < kHeld; ++j) {
+        if (warp_first + j * pair_stride < groups) {
+            split_scales(ph, job, p.tokens, anchor + 8 * job_index, first_pair + j * pair_stride, held[j], largest[j], lane);
+        }
+    }
+    for (uint32_t index = first_pair + kHeld * pair_stride; index - (lane >> 4) < groups; index += pair_stride) {
+        const uint32_t bits = load_element(ph, job, p.tokens, index, lane);
+        split_scales(ph, job, p.tokens, anchor + 8 * job_index, index, bits, split_codes(ph, job, p.tokens, index, bits, 0, lane), lane);
     }
 }
 
 // Finished sums of 32 weight rows (lane = row) for the 8 tokens: scale, activation, rounding, store.
 __device__ __forceinline__ void finish_rows(const TcPhase& ph, uint32_t tokens, uint32_t tile, uint32_t quadrant, uint32_t lane,
-                                            const float (&y)[8], uint32_t* collected) {
+                                            const float (&y)[8], uint32_t* collected, uint32_t* kept) {
     if (ph.epilogue == AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16) {
         // 32 physical rows = 16 gate rows (lanes 0..15) and the matching 16 up rows (lanes 16..31)
         __nv_bfloat16* out = static_cast<__nv_bfloat16*>(ph.out);
@@ -227,9 +341,10 @@ __device__ __forceinline__ void finish_rows(const TcPhase& ph, uint32_t tokens, 
                 const __nv_bfloat16 h = __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
                 out[static_cast<uint64_t>(token) * ph.out_rows + index] = h;
                 magnitude = static_cast<uint32_t>(__bfloat16_as_ushort(h) & 0x7fffu) << 16;
+                if (kept) kept[token] = __bfloat16_as_ushort(h);
             }
-            if (ph.collect) {
-                // the next phase splits these values: it needs every token row's largest magnitude
+            if (collected) {
+                // a later step splits these values: it needs every token row's largest magnitude
                 magnitude = __reduce_max_sync(0xffffffffu, magnitude);
                 if (lane == 0 && magnitude) atomicMax(&collected[token], magnitude);
             }
@@ -250,68 +365,69 @@ __device__ __forceinline__ void finish_rows(const TcPhase& ph, uint32_t tokens, 
     }
 }
 
-// This CTA's share of 32 rows of `tile`: finished here if tiles are whole, else handed over; the last of the
-// `parts` arrivals adds all shares in part order. Whole warps call this.
-__device__ __forceinline__ void contribute_rows(const TcPhase& ph, uint32_t tokens, uint32_t tile, uint32_t quadrant, uint32_t part,
-                                                uint32_t lane, const float (&y)[8], uint32_t* collected) {
-    if (ph.parts == 1) {
-        finish_rows(ph, tokens, tile, quadrant, lane, y, collected);
+// This CTA's share of 32 rows of `tile`: finished here if tiles are whole, else handed over as contributor
+// `slot`; the last of the arrivals adds all shares in slot order. Whole warps call this.
+__device__ __forceinline__ void contribute_rows(const TcPhase& ph, uint32_t tokens, uint32_t tile, uint32_t quadrant, uint32_t slot,
+                                                uint32_t lane, const float (&y)[8], uint32_t* collected, uint32_t* kept) {
+    if (ph.contributors == 1) {
+        finish_rows(ph, tokens, tile, quadrant, lane, y, collected, kept);
         return;
     }
     const uint32_t group = tile * 4 + quadrant;
-    float* slots = ph.partials + static_cast<uint64_t>(group) * ph.parts * kSlotFloats;
-    float4* mine = reinterpret_cast<float4*>(slots + static_cast<uint64_t>(part) * kSlotFloats) + lane * 2;
+    float* slots = ph.partials + static_cast<uint64_t>(group) * ph.contributors * kSlotFloats;
+    float4* mine = reinterpret_cast<float4*>(slots + static_cast<uint64_t>(slot) * kSlotFloats) + lane * 2;
     mine[0] = make_float4(y[0], y[1], y[2], y[3]);
     mine[1] = make_float4(y[4], y[5], y[6], y[7]);
-    __threadfence();
     __syncwarp();
+    // the arrival releases this warp's share and, for the last arriver, acquires the others'
     uint32_t arrived = 0;
-    if (lane == 0) arrived = atomicAdd(&ph.counters[group], 1u);
+    if (lane == 0) arrived = counter_arrive(&ph.counters[group]);
     arrived = __shfl_sync(0xffffffffu, arrived, 0);
-    if (arrived + 1 != ph.parts) return;
-    __threadfence();
+    __syncwarp();
+    if (arrived + 1 != ph.contributors) return;
     float sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (uint32_t s0 = 0; s0 < ph.parts; s0 += 4) {
+    for (uint32_t s0 = 0; s0 < ph.contributors; s0 += 4) {
         float4 a[4], b[4];
 #pragma unroll
         for (uint32_t j = 0; j < 4; ++j) {
             a[j] = b[j] = make_float4(0, 0, 0, 0);
-            if (s0 + j < ph.parts) {
-                const float4* slot = reinterpret_cast<const float4*>(slots + static_cast<uint64_t>(s0 + j) * kSlotFloats) + lane * 2;
-                a[j] = __ldcg(slot);
-                b[j] = __ldcg(slot + 1);
+            if (s0 + j < ph.contributors) {
+                const float4* from = reinterpret_cast<const float4*>(slots + static_cast<uint64_t>(s0 + j) * kSlotFloats) + lane * 2;
+                a[j] = __ldcg(from);
+                b[j] = __ldcg(from + 1);
             }
         }
 #pragma unroll
         for (uint32_t j = 0; j < 4; ++j) {
-            if (s0 + j < ph.parts) {
+            if (s0 + j < ph.contributors) {
                 sum[0] += a[j].x; sum[1] += a[j].y; sum[2] += a[j].z; sum[3] += a[j].w;
                 sum[4] += b[j].x; sum[5] += b[j].y; sum[6] += b[j].z; sum[7] += b[j].w;
             }
         }
     }
-    finish_rows(ph, tokens, tile, quadrant, lane, sum, collected);
+    finish_rows(ph, tokens, tile, quadrant, lane, sum, collected, nullptr);
     if (lane == 0) ph.counters[group] = 0;   // clean for the next launch
 }
 
-// A CTA's ring stages in the order it streams them: over the phases, over its (tile, part) items blockIdx.x,
-// blockIdx.x + gridDim.x, ... of a phase, over the k blocks of an item.
+// A CTA's ring stages in the order it streams them: over the steps, over its items blockIdx.x,
+// blockIdx.x + gridDim.x, ... of a step, over the k blocks of an item.
 struct Cursor {
-    uint32_t phase, index, tile, part, kb, kb0, kb1;
+    uint32_t step, index, tile, part, kb, kb0, kb1;
 };
 __device__ __forceinline__ bool cursor_load(const TcParams& p, Cursor& c) {
-    while (c.phase < p.phases) {
-        const TcPhase& ph = p.phase[c.phase];
+    while (c.step < p.steps) {
+        const TcStep& st = p.step[c.step];
         const uint32_t item = blockIdx.x + c.index * gridDim.x;
-        if (item < ph.tiles * ph.parts) {
-            c.tile = item / ph.parts;
-            c.part = item - c.tile * ph.parts;
-            c.kb0 = c.part * ph.k_blocks / ph.parts;
-            c.kb1 = (c.part + 1) * ph.k_blocks / ph.parts;
+        if (item < st.tiles * st.parts) {
+            const uint32_t tile = item / st.parts, span = st.kb1 - st.kb0;
+            c.tile = st.tile0 + tile;
+            c.part = item - tile * st.parts;
+            c.kb0 = st.kb0 + c.part * span / st.parts;
+            c.kb1 = st.kb0 + (c.part + 1) * span / st.parts;
             c.kb = c.kb0;
             return true;
         }
-        ++c.phase;
+        ++c.step;
         c.index = 0;
     }
     return false;
@@ -329,20 +445,21 @@ __device__ __forceinline__ bool cursor_next(const TcParams& p, Cursor& c) {
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1, const TcParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
-    float* term_scale = reinterpret_cast<float*>(smem + kStages * kStageBytes);   // [token]: scale of term 0 in the current phase
-    uint32_t* anchor = reinterpret_cast<uint32_t*>(term_scale + 8);               // [token]: exponent field the term scales are anchored on
-    uint32_t* collected = anchor + 8;                                              // [token]: largest magnitudes of this CTA's SwiGLU outputs
-    volatile uint32_t* acts_ready = collected + 8;                                 // [phase]: the phase's split activations are complete
+    float* term_scale = reinterpret_cast<float*>(smem + kStages * kStageBytes);   // [job][token]: scale of term 0
+    uint32_t* anchor = reinterpret_cast<uint32_t*>(term_scale + 8 * kMaxJobs);    // [job][token]: exponent field the term scales are anchored on
+    uint32_t* collected = anchor + 8 * kMaxJobs;                                  // [token]: largest magnitudes this CTA has seen (scan, SwiGLU outputs)
+    volatile uint32_t* input_ready = collected + 8;                               // the split of job 0 is complete
+    volatile uint32_t* wave_set = input_ready + 1;                                // which half of the wave counters this launch uses
     // full[S] (operand codes landed), empty[S], scales_landed[S], scales_ready[S] (copies to tensor memory issued),
     // acc_full[2], acc_empty[2]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(const_cast<uint32_t*>(acts_ready) + 2);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(const_cast<uint32_t*>(wave_set) + 1);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * kStages + 4);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (smem_u32(smem) & 1023u) {
         // swizzled operand tiles want the window on a 1024-byte boundary, which is where the hardware puts it
-        if (threadIdx.x == 0) atomicCAS(p.status_word, 0u, kErrTcWindow);
+        if (threadIdx.x == 0) atomicCAS(p.header, 0u, kErrTcWindow);
         return;
     }
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -351,7 +468,8 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
     const uint32_t bar_acc_full = smem_u32(bars + 4 * kStages), bar_acc_empty = smem_u32(bars + 4 * kStages + 2);
 
     auto issue_weights = [&](uint32_t stage, const Cursor& c) {
-        const TcPhase& ph = p.phase[c.phase];
+        const uint32_t phase = p.step[c.step].phase;
+        const TcPhase& ph = p.phase[phase];
         const uint32_t k_valid = min(kStageK, ph.cols - c.kb * kStageK);
         const uint32_t sf_bytes = k_valid / 64 * kSfAtomBytes;
         const uint32_t dst = smem_u32(smem + stage * kStageBytes);
@@ -361,10 +479,10 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
         bulk_load(dst + kStageCodeBytes, ph.weight_sf + (static_cast<uint64_t>(c.tile) * (ph.cols / 64) + c.kb * 4) * kSfAtomBytes, sf_bytes,
                   bar_scales_landed + 8 * stage);
         mbar_expect_tx(bar_full + 8 * stage, kStageCodeBytes);
-        tma_load_2d(dst, c.phase ? &map1 : &map0, c.kb * 128, c.tile * kTileM, bar_full + 8 * stage);
+        tma_load_2d(dst, phase ? &map1 : &map0, c.kb * 128, c.tile * kTileM, bar_full + 8 * stage);
     };
     auto issue_activations = [&](uint32_t stage, const Cursor& c) {
-        const TcPhase& ph = p.phase[c.phase];
+        const TcPhase& ph = p.phase[p.step[c.step].phase];
         const uint32_t k_valid = min(kStageK, ph.cols - c.kb * kStageK);
         const uint32_t sf_bytes = k_valid / 64 * kSfAtomBytes;
         const uint32_t dst = smem_u32(smem + stage * kStageBytes);
@@ -382,7 +500,7 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
         for (uint32_t s = 0; s < kStages; ++s) {
             mbar_init(bar_full + 8 * s, 2);            // the weight half and the activation half of a stage are announced separately
             mbar_init(bar_scales_landed + 8 * s, 2);   // likewise for their block scales, which land first
-            mbar_init(bar_scales_ready + 8 * s, 1);
+            mbar_init(bar_scales_ready + 8 * s, 2);    // one arrival per copy thread
             mbar_init(bar_empty + 8 * s, 1);
         }
         for (uint32_t b = 0; b < 2; ++b) {
@@ -390,7 +508,7 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
             mbar_init(bar_acc_empty + 8 * b, 4);   // one arrival per epilogue warp
         }
         *abort_flag = 0;
-        acts_ready[0] = acts_ready[1] = 0;
+        *input_ready = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         // The weight halves of the first ring fill go out at once, before anything else is set up: weights depend
         // on nothing, so HBM is busy while this CTA allocates tensor memory, while the launch before this one
@@ -402,7 +520,7 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
             weights_left = cursor_next(p, weights_at);
         }
     }
-    if (threadIdx.x >= 64 && threadIdx.x < 64 + 16) anchor[threadIdx.x - 64] = 0;   // anchor and collected
+    if (threadIdx.x >= 64 && threadIdx.x < 64 + 8) collected[threadIdx.x - 64] = 0;
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemColumns)
                      : "memory");
@@ -414,41 +532,58 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0 && lane == 0) {
-        // ---------------- TMA producer ----------------
-        // Weight halves run ahead as far as the ring allows; the activation half of a stage follows as soon as its
-        // phase's split activations are complete. Neither waits for the other.
+        // ---------------- TMA producer, weights: runs ahead as far as the ring allows ----------------
+        while (weights_left) {
+            // stage of step `weights_issued`: free once the MMAs of the step kStages before it are complete
+            const uint32_t stage = weights_issued % kStages, round = weights_issued / kStages;
+            if (!mbar_wait(bar_empty + 8 * stage, (round - 1) & 1, abort_flag, p.header, kErrTcProducer)) break;
+            issue_weights(stage, weights_at);
+            ++weights_issued;
+            weights_left = cursor_next(p, weights_at);
+        }
+    } else if (warp == 7 && lane == 0) {
+        // ---------------- TMA producer, activations: a stage's half follows as soon as the stage is free and the
+        // split it comes from is complete in every CTA ----------------
         Cursor acts_at;
         bool acts_left = cursor_begin(p, acts_at);
-        uint32_t acts_issued = 0, idle = 0, fenced_phases = 0;
+        uint32_t acts_issued = 0, idle = 0, polls = 0, open_jobs = 0;   // jobs 0 .. open_jobs - 1 are known to be complete
         while (acts_left) {
+            const uint32_t stage = acts_issued % kStages, round = acts_issued / kStages;
+            const uint32_t job = p.step[acts_at.step].job;
             bool progressed = false;
-            if (weights_left) {
-                // stage of step `weights_issued`: free once the MMAs of the step kStages before it are complete
-                const uint32_t stage = weights_issued % kStages, round = weights_issued / kStages;
-                if (mbar_test(bar_empty + 8 * stage, (round - 1) & 1)) {
-                    issue_weights(stage, weights_at);
-                    ++weights_issued;
-                    weights_left = cursor_next(p, weights_at);
+            if (round != 0 && !mbar_wait(bar_empty + 8 * stage, (round - 1) & 1, abort_flag, p.header, kErrTcProducer)) break;
+            {
+                if (open_jobs <= job) {
+                    // job 0: this CTA's workers have been through the meeting behind it; later jobs: every CTA has
+                    // arrived at the wave's second counter
+                    bool open = *input_ready != 0;
+                    __threadfence_block();
+                    if (open && job != 0) {
+                        open = counter_read(p.header + kHeaderWave + *wave_set * 4 + (job - 1) * 2 + 1) >= gridDim.x;
+                        if (!open && ++polls > kGridWaitLimit) idle = kWaitLimit;   // a poll of global memory takes about a microsecond
+                    }
+                    if (open) {
+                        // the split activations were written with ordinary stores, by this and other CTAs
+                        asm volatile("fence.proxy.async;" ::: "memory");
+                        open_jobs = job + 1;
+                    }
+                }
+                if (open_jobs > job) {
+                    issue_activations(stage, acts_at);
+                    ++acts_issued;
+                    acts_left = cursor_next(p, acts_at);
                     progressed = true;
                 }
             }
-            if (acts_issued < weights_issued && acts_ready[acts_at.phase]) {
-                if (fenced_phases <= acts_at.phase) {
-                    // the split activations were written with ordinary stores, by this and other CTAs
-                    asm volatile("fence.proxy.async;" ::: "memory");
-                    fenced_phases = acts_at.phase + 1;
-                }
-                issue_activations(acts_issued % kStages, acts_at);
-                ++acts_issued;
-                acts_left = cursor_next(p, acts_at);
-                progressed = true;
-            }
             if (progressed) {
                 idle = 0;
-            } else if (++idle > kWaitLimit || ((idle & 1023u) == 1023u && *abort_flag)) {
-                *abort_flag = 1;
-                atomicCAS(p.status_word, 0u, kErrTcProducer);
-                break;
+            } else {
+                __nanosleep(100);   // leave the issue slots to the warps that are splitting
+                if (++idle > kWaitLimit / 8 || ((idle & 255u) == 255u && *abort_flag)) {
+                    *abort_flag = 1;
+                    atomicCAS(p.header, 0u, kErrTcProducer);
+                    break;
+                }
             }
         }
     } else if (warp == 1 && lane == 0) {
@@ -462,22 +597,22 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
             const uint32_t buffer = item_count & 1;
             if (c.kb == c.kb0) {
                 // the epilogue must have drained this buffer (two items ago)
-                if (!mbar_wait(bar_acc_empty + 8 * buffer, acc_phase[buffer] ^ 1, abort_flag, p.status_word, kErrTcAccEmpty)) break;
+                if (!mbar_wait(bar_acc_empty + 8 * buffer, acc_phase[buffer] ^ 1, abort_flag, p.header, kErrTcAccEmpty)) break;
                 tc_fence_after();
             }
             const uint32_t acc = tmem_base + kTmemAcc + buffer * 64;
             const uint32_t stage = step % kStages, parity = (step / kStages) & 1;
             // operands in shared memory (TMA) and their block scales on the way to tensor memory (copy thread):
             // a copy and a later MMA execute in issue order, so the copies only have to be issued
-            if (!mbar_wait(bar_full + 8 * stage, parity, abort_flag, p.status_word, kErrTcFull) ||
-                !mbar_wait(bar_scales_ready + 8 * stage, parity, abort_flag, p.status_word, kErrTcScalesReady)) {
+            if (!mbar_wait(bar_full + 8 * stage, parity, abort_flag, p.header, kErrTcFull) ||
+                !mbar_wait(bar_scales_ready + 8 * stage, parity, abort_flag, p.header, kErrTcScalesReady)) {
                 break;
             }
             tc_fence_after();
             const uint32_t stage_smem = smem_u32(smem + stage * kStageBytes);
             const uint64_t weight_desc = operand_desc(stage_smem), act_desc = operand_desc(stage_smem + kStageActCodes);
             const uint32_t tmem_sf_weight = tmem_base + kTmemSfWeight + stage * 16, tmem_sf_act = tmem_base + kTmemSfAct + stage * 16;
-            const uint32_t k_steps = min(kStageK, p.phase[c.phase].cols - c.kb * kStageK) / 64;
+            const uint32_t k_steps = min(kStageK, p.phase[p.step[c.step].phase].cols - c.kb * kStageK) / 64;
             // each MMA consumes 64 k = 32 bytes of every row: advance the start address by 32 >> 4
             if (k_steps == 4) {
 #pragma unroll
@@ -500,32 +635,28 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
             ++step;
             more = cursor_next(p, c);
         }
-    } else if (warp == 6 && lane == 0) {
+    } else if ((warp == 6 || warp == 8) && lane == 0) {
         // ---------------- scale copies: shared memory -> tensor memory, as soon as a stage's scales have landed ----------------
-        // A stage's scale columns in tensor memory are free when its scales land again: the producer refilled the
-        // stage only after the MMAs that read those columns were complete.
+        // Two threads, one for the weights' scales and one for the activations': a thread gets one copy accepted
+        // about every hundred cycles. A stage's scale columns in tensor memory are free when its scales land again:
+        // the producer refilled the stage only after the MMAs that read those columns were complete.
+        const bool weights = warp == 6;
         uint32_t step = 0;
         Cursor c;
         bool more = cursor_begin(p, c);
         while (more) {
             const uint32_t stage = step % kStages, parity = (step / kStages) & 1;
-            if (!mbar_wait(bar_scales_landed + 8 * stage, parity, abort_flag, p.status_word, kErrTcScalesLanded)) break;
+            if (!mbar_wait(bar_scales_landed + 8 * stage, parity, abort_flag, p.header, kErrTcScalesLanded)) break;
             tc_fence_after();
             const uint32_t stage_smem = smem_u32(smem + stage * kStageBytes);
-            const uint64_t weight_sf_desc = sf_desc(stage_smem + kStageCodeBytes), act_sf_desc = sf_desc(stage_smem + kStageActSf);
-            const uint32_t tmem_sf_weight = tmem_base + kTmemSfWeight + stage * 16, tmem_sf_act = tmem_base + kTmemSfAct + stage * 16;
-            const uint32_t k_steps = min(kStageK, p.phase[c.phase].cols - c.kb * kStageK) / 64;
+            const uint64_t desc = sf_desc(stage_smem + (weights ? kStageCodeBytes : kStageActSf));
+            const uint32_t columns = tmem_base + (weights ? kTmemSfWeight : kTmemSfAct) + stage * 16;
+            const uint32_t k_steps = min(kStageK, p.phase[p.step[c.step].phase].cols - c.kb * kStageK) / 64;
             if (k_steps == 4) {
 #pragma unroll
-                for (uint32_t k = 0; k < 4; ++k) {
-                    tc_copy_sf(tmem_sf_weight + 4 * k, weight_sf_desc + k * (kSfAtomBytes >> 4));
-                    tc_copy_sf(tmem_sf_act + 4 * k, act_sf_desc + k * (kSfAtomBytes >> 4));
-                }
+                for (uint32_t k = 0; k < 4; ++k) tc_copy_sf(columns + 4 * k, desc + k * (kSfAtomBytes >> 4));
             } else {
-                for (uint32_t k = 0; k < k_steps; ++k) {
-                    tc_copy_sf(tmem_sf_weight + 4 * k, weight_sf_desc + k * (kSfAtomBytes >> 4));
-                    tc_copy_sf(tmem_sf_act + 4 * k, act_sf_desc + k * (kSfAtomBytes >> 4));
-                }
+                for (uint32_t k = 0; k < k_steps; ++k) tc_copy_sf(columns + 4 * k, desc + k * (kSfAtomBytes >> 4));
             }
             tc_fence_before();
             mbar_arrive(bar_scales_ready + 8 * stage);
@@ -533,81 +664,71 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
             more = cursor_next(p, c);
         }
     } else if (warp >= 2 && warp < 6) {
-        // ---------------- workers: split the activations of a phase, then run its epilogues ----------------
+        // ---------------- workers: split activations, run the epilogues ----------------
         const uint32_t worker = threadIdx.x - 64, quadrant = warp & 3;   // tensor-memory lanes of this warp: 32 * quadrant .. + 31
         const bool leader = worker == 0;
+        const uint32_t first_pair = (blockIdx.x * 4 + (warp - 2)) * 2 + (lane >> 4), pair_stride = gridDim.x * 8;   // this half warp's groups of a job
         uint32_t item_count = 0;
         uint32_t acc_phase[2] = {0, 0};
-        bool alive = true;
+        uint32_t held[kHeld], largest[kHeld];
         asm volatile("griddepcontrol.wait;" ::: "memory");   // the activations may come from the launch before this one; all stores follow
-        uint32_t meeting = 0;
-        if (leader) meeting = *static_cast<volatile uint32_t*>(p.grid_barrier + 3);   // written by the launch before, at its last meeting
-        const uint32_t first_pair = (blockIdx.x * 4 + (warp - 2)) * 2 + (lane >> 4), pair_stride = gridDim.x * 8;   // this half warp's groups
-        for (uint32_t phase = 0; alive && phase < p.phases; ++phase) {
-            const TcPhase& ph = p.phase[phase];
-            const uint32_t groups = p.tokens * (ph.cols / 16);
-            uint32_t held[kHeld];
-            if (ph.scan) {
-                // the row maxima of an input from outside: every lane looks at its own elements (and keeps them)
-#pragma unroll
-                for (uint32_t j = 0; j < kHeld; ++j) held[j] = load_element(ph, p.tokens, first_pair + j * pair_stride, lane);
-                auto note = [&](uint32_t index, uint32_t bits) {   // whole warps: the two groups of a pair go together
-                    uint32_t largest = bits & 0x7fffu;
-                    largest = max(largest, __shfl_xor_sync(0xffffffffu, largest, 8));
-                    largest = max(largest, __shfl_xor_sync(0xffffffffu, largest, 4));
-                    largest = max(largest, __shfl_xor_sync(0xffffffffu, largest, 2));
-                    largest = max(largest, __shfl_xor_sync(0xffffffffu, largest, 1));
-                    if ((lane & 15) == 0 && largest) atomicMax(&collected[index / (ph.cols / 16)], largest << 16);   // zero past the end
-                };
-#pragma unroll
-                for (uint32_t j = 0; j < kHeld; ++j) {
-                    if (first_pair - (lane >> 4) + j * pair_stride < groups) note(first_pair + j * pair_stride, held[j]);
-                }
-                for (uint32_t index = first_pair + kHeld * pair_stride; index - (lane >> 4) < groups; index += pair_stride) {
-                    note(index, load_element(ph, p.tokens, index, lane));
-                }
-                workers_sync();
-                if (worker < 8) {
-                    if (collected[worker]) atomicMax(ph.row_max + worker, collected[worker]);
-                    collected[worker] = 0;
-                }
+        uint32_t epoch = 0, meeting = 0;
+        uint32_t* wave = nullptr;                              // this launch's wave counters: [wave]{outputs stored, split stored}
+        if (leader) {
+            epoch = *static_cast<volatile uint32_t*>(p.header + kHeaderEpoch);   // left by the launch before
+            meeting = epoch % 3;
+            const uint32_t set = (epoch >> 1) & 1;
+            wave = p.header + kHeaderWave + set * 4;
+            *wave_set = set;
+            if (blockIdx.x == 0) {
+                // the other half of the wave counters belongs to the launch before (complete) and to the launch after;
+                // the maxima of the later jobs were last read by the launch before and are added to only by CTAs
+                // that have been through a full meeting, i.e. after this CTA has arrived there
+                for (uint32_t i = 0; i < 4; ++i) p.header[kHeaderWave + (set ^ 1) * 4 + i] = 0;
+                for (uint32_t i = 8; i < 8 * p.jobs; ++i) p.header[kHeaderRowMax + i] = 0;
             }
-            // every CTA has found its maxima, or has finished the phase before: its output is this phase's input
-            // and its maxima are collected
-            if (!grid_meet(p, leader, meeting, abort_flag)) break;
-            if (!ph.scan) {
+        }
+        bool alive = true;
+        {
+            // ---- job 0: the input of the first step comes from outside ----
+            const TcJob& job = p.job[0];
 #pragma unroll
-                for (uint32_t j = 0; j < kHeld; ++j) held[j] = load_element(ph, p.tokens, first_pair + j * pair_stride, lane);
-            }
-            if (worker < 8) {
-                // term 0 of the row has the global scale 2^(A - 135): all eight term scales are normal f32 numbers
-                const uint32_t largest = *static_cast<volatile uint32_t*>(ph.row_max + worker) >> 16;
-                const uint32_t a = min(max(largest >> 7, 40u), 250u);
-                float scale = __uint_as_float((a - 8) << 23);
-                if (largest >= 0x7f80u) scale = __uint_as_float(0x7fc00000u);   // a NaN or infinity in the row: the row's outputs are NaN
-                term_scale[worker] = scale;
-                anchor[worker] = a;
-            }
+            for (uint32_t j = 0; j < kHeld; ++j) held[j] = load_element(p.phase[job.phase], job, p.tokens, first_pair + j * pair_stride, lane);
+            // the codes of this CTA's share and the largest magnitudes it has seen; the block scales need the rows' anchors
+            share_codes(p, 0, held, largest, collected, first_pair, pair_stride, lane);
             workers_sync();
-#pragma unroll
-            for (uint32_t j = 0; j < kHeld; ++j) {
-                if (first_pair - (lane >> 4) + j * pair_stride < groups) split_group(ph, p.tokens, anchor, first_pair + j * pair_stride, held[j], lane);
+            if (worker < 8) {
+                if (collected[worker]) atomicMax(p.header + kHeaderRowMax + worker, collected[worker]);
+                collected[worker] = 0;
             }
-            for (uint32_t index = first_pair + kHeld * pair_stride; index - (lane >> 4) < groups; index += pair_stride) {
-                split_group(ph, p.tokens, anchor, index, load_element(ph, p.tokens, index, lane), lane);
+            alive = grid_meet(p, leader, meeting, abort_flag);      // every CTA has contributed its maxima
+            if (alive) {
+                job_scales(p, 0, worker, term_scale, anchor);
+                share_scales(p, 0, anchor, held, largest, first_pair, pair_stride, lane);
+                // every CTA's slice is in place before any CTA loads from the split (the thread that issues the loads
+                // puts a proxy fence between the meeting and them)
+                alive = grid_meet(p, leader, meeting, abort_flag);
             }
-            // every CTA's slice is in place (and readable by the TMA engine) before any CTA loads from the split
-            asm volatile("fence.proxy.async;" ::: "memory");
-            if (!grid_meet(p, leader, meeting, abort_flag)) break;
-            if (blockIdx.x == 0 && worker < 8) ph.row_max[worker] = 0;   // every CTA has read them: clean for the next launch
-            if (leader) acts_ready[phase] = 1;
-
-            // ---- epilogues of this CTA's items of the phase ----
-            const uint32_t items = ph.tiles * ph.parts;
+            if (alive) {
+                if (blockIdx.x == 0 && worker < 8) p.header[kHeaderRowMax + worker] = 0;   // every CTA has read them: clean for the next launch
+                if (leader) {
+                    __threadfence_block();
+                    *input_ready = 1;
+                }
+            }
+        }
+        for (uint32_t s = 0; alive && s < p.steps; ++s) {
+            const TcStep& st = p.step[s];
+            const TcPhase& ph = p.phase[st.phase];
+            uint32_t* gather = st.feeds ? collected : nullptr;
+            uint32_t kept[8] = {0, 0, 0, 0, 0, 0, 0, 0};    // lanes 0..15: the outputs of this warp's 16 columns, as stored
+            uint32_t kept_group = ~0u;                      // their 16-element group in the rows of the next product's input
+            // ---- epilogues of this CTA's items of the step ----
+            const uint32_t items = st.tiles * st.parts;
             for (uint32_t item = blockIdx.x; item < items; item += gridDim.x, ++item_count) {
-                const uint32_t tile = item / ph.parts, part = item - tile * ph.parts;
+                const uint32_t tile = item / st.parts, part = item - tile * st.parts;
                 const uint32_t buffer = item_count & 1;
-                if (!mbar_wait(bar_acc_full + 8 * buffer, acc_phase[buffer], abort_flag, p.status_word, kErrTcAccFull)) {
+                if (!mbar_wait_suspended(bar_acc_full + 8 * buffer, acc_phase[buffer], abort_flag, p.header, kErrTcAccFull)) {
                     alive = false;
                     break;
                 }
@@ -624,28 +745,68 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
                 float y[8];
 #pragma unroll
                 for (uint32_t token = 0; token < 8; ++token) {
-                    // column = term * 8 + token; term t carries the factor 8^-t relative to term 0
+                    // column = term * 8 + token; term t carries the factor 8^t relative to term 0
                     float sum = 0.0f, factor = 1.0f;
 #pragma unroll
                     for (uint32_t term = 0; term < kTerms; ++term) {
                         const uint32_t column = term * 8 + token;
                         sum = fmaf(__uint_as_float(v[column >> 4][column & 15]), factor, sum);
-                        factor *= 0.125f;
+                        factor *= 8.0f;
                     }
-                    y[token] = sum * term_scale[token];
+                    y[token] = sum * term_scale[8 * st.job + token];
                 }
-                contribute_rows(ph, p.tokens, tile, quadrant, part, lane, y, collected);
+                contribute_rows(ph, p.tokens, st.tile0 + tile, quadrant, st.slot0 + part, lane, y, gather, st.keeps ? kept : nullptr);
+                kept_group = (st.tile0 + tile) * 4 + quadrant;
             }
-            if (ph.collect) {
-                workers_sync();
-                if (worker < 8) {
-                    if (collected[worker]) atomicMax(ph.collect + worker, collected[worker]);
-                    collected[worker] = 0;
+            if (!alive || !st.feeds) continue;
+            // ---- this step's outputs are the activations of job `feeds`: maxima, arrive, wait, split, arrive ----
+            const uint32_t w = st.feeds - 1;
+            const TcJob& job = p.job[st.feeds];
+            const TcPhase& next = p.phase[job.phase];
+            workers_sync();
+            if (worker < 8) {
+                if (collected[worker]) atomicMax(p.header + kHeaderRowMax + 8 * st.feeds + worker, collected[worker]);
+                collected[worker] = 0;
+            }
+            workers_sync();
+            if (leader) counter_arrive(wave + 2 * w);
+            // While the other CTAs arrive: every warp writes the codes of the 16 columns it has just stored, from
+            // registers: lanes 0..15 take token rows 0..3, lanes 16..31 rows 4..7, one group each.
+            uint32_t index[4] = {~0u, ~0u, ~0u, ~0u}, bits[4] = {0, 0, 0, 0};
+            if (st.keeps && kept_group != ~0u) {
+#pragma unroll
+                for (uint32_t j = 0; j < 4; ++j) {
+                    const uint32_t token = j + ((lane >> 4) << 2);
+                    const uint32_t theirs = __shfl_sync(0xffffffffu, kept[4 + j], lane & 15);
+                    index[j] = token < p.tokens ? token * job.groups + (kept_group - job.group0) : ~0u;
+                    bits[j] = lane < 16 ? kept[j] : theirs;
+                    largest[j] = split_codes(next, job, p.tokens, index[j], bits[j], 0, lane);
                 }
             }
+            if (leader) counter_wait(p, wave + 2 * w, kErrTcWave, abort_flag);
+            workers_sync();
+            if (*abort_flag) {
+                alive = false;
+                break;
+            }
+            job_scales(p, st.feeds, worker, term_scale, anchor);
+            if (st.keeps) {
+                if (kept_group != ~0u) {
+#pragma unroll
+                    for (uint32_t j = 0; j < 4; ++j) split_scales(next, job, p.tokens, anchor + 8 * st.feeds, index[j], bits[j], largest[j], lane);
+                }
+            } else {
+                // items of several CTAs per tile, or several items per CTA: the outputs are read back, every CTA a share
+#pragma unroll
+                for (uint32_t j = 0; j < kHeld; ++j) held[j] = load_element(next, job, p.tokens, first_pair + j * pair_stride, lane);
+                share_codes(p, st.feeds, held, largest, nullptr, first_pair, pair_stride, lane);
+                share_scales(p, st.feeds, anchor, held, largest, first_pair, pair_stride, lane);
+            }
+            workers_sync();
+            if (leader) counter_arrive(wave + 2 * w + 1);
         }
-        // the next launch goes on counting meetings where this one stopped (every CTA stores the same number)
-        if (alive && leader) p.grid_barrier[3] = meeting;
+        // the next launch goes on counting meetings where this one stopped
+        if (alive && leader && blockIdx.x == 0) p.header[kHeaderEpoch] = (epoch + 2) % 12;
     }
 
     tc_fence_before();
@@ -657,29 +818,66 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
 }
 
 // ---- host side -------------------------------------------------------------------------------------
-struct TcGeometry {
-    uint32_t tiles, k_blocks, parts, ctas;
-    uint64_t partial_bytes;
+// Equal k ranges per tile of a step with `tiles` tiles over `k_blocks` stages on `ctas` CTAs: whole tiles when
+// there are more tiles than half the CTAs, otherwise as many parts as CTAs per tile (at least two stages per
+// part, at most 16 parts).
+uint32_t parts_for(uint32_t tiles, uint32_t k_blocks, uint32_t ctas) {
+    if (tiles * 2 > ctas) return 1;
+    uint32_t parts = ctas / tiles;
+    if (parts > k_blocks / 2) parts = k_blocks / 2;
+    if (parts > 16) parts = 16;
+    return parts > 1 ? parts : 1;
+}
+
+struct TcProgram {
+    TcJob job[kMaxJobs];
+    TcStep step[kMaxSteps];
+    uint32_t jobs, steps, ctas;
+    uint32_t contributors[kMaxPhases];
 };
 
-// Whole tiles dealt round-robin over the resident CTAs (two per SM) when there are enough of them; otherwise every
-// tile is cut along k into as many equal parts as there are resident CTAs per tile (at least two ring stages per
-// part, at most 16 parts).
-TcGeometry tc_geometry(uint32_t physical_rows, uint32_t cols, uint32_t sm_count) {
-    TcGeometry g{};
-    g.tiles = physical_rows / kTileM;
-    g.k_blocks = (cols + kStageK - 1) / kStageK;
-    g.parts = 1;
+// The steps of a linear (`b` null) or of the MLP block on a device with `sm_count` SMs.
+TcProgram tc_program(const augur_cuda_nvfp4_sm100_gemv_args_v1* a, const augur_cuda_nvfp4_sm100_gemv_args_v1* b, uint32_t sm_count) {
+    TcProgram g{};
     const uint32_t slots = sm_count * kCtasPerSm;   // CTAs resident at once
-    if (g.tiles < slots) {
-        uint32_t parts = slots / g.tiles;
-        if (parts > g.k_blocks / 2) parts = g.k_blocks / 2;
-        if (parts > 16) parts = 16;
-        if (parts > 1) g.parts = parts;
+    const uint32_t rows_a = a->epilogue == AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16 ? 2 * a->rows : a->rows;
+    const uint32_t tiles_a = rows_a / kTileM, kb_a = (a->cols + kStageK - 1) / kStageK;
+    g.job[0] = TcJob{0, 0, a->cols / 16};
+    g.jobs = 1;
+    if (!b) {
+        const uint32_t parts = parts_for(tiles_a, kb_a, slots);
+        g.step[0] = TcStep{0, 0, 0, tiles_a, 0, kb_a, parts, 0, 0, 0};
+        g.steps = 1;
+        g.contributors[0] = parts;
+        g.ctas = tiles_a * parts < slots ? tiles_a * parts : slots;
+        return g;
     }
-    const uint64_t items = static_cast<uint64_t>(g.tiles) * g.parts;
-    g.ctas = items < slots ? static_cast<uint32_t>(items) : slots;
-    g.partial_bytes = g.parts > 1 ? static_cast<uint64_t>(g.tiles) * 4 * g.parts * kSlotFloats * 4 : 0;
+    // gate|up in whole tiles, in two waves when there are more tiles than CTAs: a wave's outputs are 64 columns of
+    // the intermediate per tile, and the first wave must end on a k block of the second product
+    const uint32_t tiles_b = b->rows / kTileM, kb_b = (b->cols + kStageK - 1) / kStageK;
+    uint32_t first = tiles_a;
+    if (tiles_a > slots && (slots & ~3u) != 0) first = slots & ~3u;
+    g.ctas = slots;
+    g.contributors[0] = 1;
+    uint32_t s = 0;
+    g.step[s++] = TcStep{0, 0, 0, first, 0, kb_a, 1, 0, 1, first <= slots ? 1u : 0u};
+    g.job[1] = TcJob{1, 0, first * 4};
+    g.jobs = 2;
+    if (first < tiles_a) {
+        g.step[s++] = TcStep{0, 0, first, tiles_a - first, 0, kb_a, 1, 0, 2, tiles_a - first <= slots ? 1u : 0u};
+        g.job[2] = TcJob{1, first * 4, b->cols / 16 - first * 4};
+        g.jobs = 3;
+    }
+    const uint32_t kb_first = first < tiles_a ? first / 4 : kb_b;
+    const uint32_t parts_first = parts_for(tiles_b, kb_first, slots);
+    g.step[s++] = TcStep{1, 1, 0, tiles_b, 0, kb_first, parts_first, 0, 0, 0};
+    g.contributors[1] = parts_first;
+    if (first < tiles_a) {
+        const uint32_t parts_rest = parts_for(tiles_b, kb_b - kb_first, slots);
+        g.step[s++] = TcStep{1, 2, 0, tiles_b, kb_first, kb_b, parts_rest, parts_first, 0, 0};
+        g.contributors[1] += parts_rest;
+    }
+    g.steps = s;
     return g;
 }
 
@@ -703,31 +901,40 @@ uint32_t physical_rows_of(const augur_cuda_nvfp4_sm100_gemv_args_v1* a) {
     return a->epilogue == AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16 ? 2 * a->rows : a->rows;
 }
 
-// What a phase needs of the plan scratch behind the counter regions: the split activations, then the partial sums.
-uint64_t tc_scratch_need(const TcGeometry& g, uint32_t cols) { return (split_bytes(cols) + 255) / 256 * 256 + g.partial_bytes; }
+// What a phase needs of the plan scratch behind the counter regions: the split activations, then the partial
+// sums of `contributors` items per tile.
+uint64_t tc_scratch_need(uint32_t physical_rows, uint32_t cols, uint32_t contributors) {
+    const uint64_t partial_bytes = contributors > 1 ? static_cast<uint64_t>(physical_rows / kTileM) * 4 * contributors * kSlotFloats * 4 : 0;
+    return (split_bytes(cols) + 255) / 256 * 256 + partial_bytes;
+}
 
 // Scalars, extents, scratch room (`offset` .. `limit` of the plan scratch) and aliasing of one phase.
 bool check_tc(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* plan,
-              const augur_cuda_nvfp4_sm100_gemv_args_v1* a, uint64_t offset, uint64_t limit, bool full,
+              const augur_cuda_nvfp4_sm100_gemv_args_v1* a, uint32_t contributors, uint64_t offset, uint64_t limit, bool full,
               augur_cuda_result_v1* failure) {
     *failure = invalid();
-    if (!header_ok(d, s, a)) {
-        if (a && s && d >= 0 && s->ordinal == d && a->abi_version != AUGUR_CUDA_ABI_VERSION_V1) {
-            *failure = make_result(AUGUR_CUDA_STATUS_ABI_VERSION_MISMATCH);
-        }
-        return false;
-    }
     uint32_t physical_rows = 0;
-    if (!plan_ok(plan, d, s) || !check_tc_scalars(a, &physical_rows)) return false;
-    const TcGeometry g = tc_geometry(physical_rows, a->cols, plan->sm_count);
-    if (g.tiles * 4 > kMaxGroups || offset < kCounterBytes || offset % 256 != 0 || limit < offset ||
-        tc_scratch_need(g, a->cols) > limit - offset) {
+    if (!check_tc_scalars(a, &physical_rows)) return false;
+    if (physical_rows / kTileM * 4 > kMaxGroups || offset < kCounterBytes || offset % 256 != 0 || limit < offset ||
+        tc_scratch_need(physical_rows, a->cols, contributors) > limit - offset) {
         return false;
     }
     const Range r[4] = {{a->weight, a->weight_len_bytes, 256}, {a->input_bf16, a->input_len_bytes, 16},
                         {a->output, a->output_len_bytes, 4}, plan_scratch_range(plan)};
     if (!all_disjoint(r, 4)) return false;
     return !full || inspect_device_ranges(d, r, 3, failure);
+}
+
+bool check_tc_header(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* plan, const void* a, uint32_t abi_version,
+                     bool header, augur_cuda_result_v1* failure) {
+    *failure = invalid();
+    if (!header) {
+        if (a && s && d >= 0 && s->ordinal == d && abi_version != AUGUR_CUDA_ABI_VERSION_V1) {
+            *failure = make_result(AUGUR_CUDA_STATUS_ABI_VERSION_MISMATCH);
+        }
+        return false;
+    }
+    return plan_ok(plan, d, s);
 }
 
 // Packed codes as a 2-D byte tensor [rows][cols/2]; boxes of 128 rows x 128 bytes, 128-byte swizzle.
@@ -755,28 +962,23 @@ bool weight_map(CUtensorMap* map, uint64_t address, uint64_t rows, uint32_t cols
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// The grid barrier and the row maxima of both phases live in the plan's header (the 256 bytes in front of the
-// scratch, behind the status word): no other kernel of the library writes there, plan creation zeroes them and
-// every launch leaves them clean.
-uint32_t* header_grid_barrier(const augur_cuda_nvfp4_sm100_plan_v1* plan) { return plan->status_word + 16; }
-uint32_t* header_row_max(const augur_cuda_nvfp4_sm100_plan_v1* plan, uint32_t phase) { return plan->status_word + 32 + 8 * phase; }
-
-// One launch for one or two phases (`b` null: one). Member m uses counter region m and the scratch at offsets[m].
+// One launch for a linear (`b` null) or the MLP block. Member m uses counter region m and the scratch at offsets[m].
 augur_cuda_result_v1 launch_tc(augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* plan,
                                const augur_cuda_nvfp4_sm100_gemv_args_v1* a, const augur_cuda_nvfp4_sm100_gemv_args_v1* b,
                                const uint64_t (&offsets)[2]) {
     const augur_cuda_nvfp4_sm100_gemv_args_v1* members[2] = {a, b};
+    const TcProgram g = tc_program(a, b, plan->sm_count);
     CUtensorMap maps[2];
     TcParams p{};
-    p.phases = b ? 2 : 1;
     p.tokens = a->tokens;
-    p.grid_barrier = header_grid_barrier(plan);
-    p.status_word = plan->status_word;
-    uint32_t grid = 0;
-    for (uint32_t m = 0; m < p.phases; ++m) {
+    p.header = plan->status_word;
+    p.jobs = g.jobs;
+    p.steps = g.steps;
+    for (uint32_t j = 0; j < g.jobs; ++j) p.job[j] = g.job[j];
+    for (uint32_t i = 0; i < g.steps; ++i) p.step[i] = g.step[i];
+    for (uint32_t m = 0; m < (b ? 2u : 1u); ++m) {
         const augur_cuda_nvfp4_sm100_gemv_args_v1* args = members[m];
         const uint32_t physical_rows = physical_rows_of(args);
-        const TcGeometry g = tc_geometry(physical_rows, args->cols, plan->sm_count);
         if (!weight_map(&maps[m], args->weight, physical_rows, args->cols)) return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE);
         TcPhase& ph = p.phase[m];
         ph.weight_sf = reinterpret_cast<const uint8_t*>(args->weight) + tcgen05_codes_bytes(physical_rows, args->cols);
@@ -785,13 +987,9 @@ augur_cuda_result_v1 launch_tc(augur_cuda_stream_t s, const augur_cuda_nvfp4_sm1
         ph.out = reinterpret_cast<void*>(args->output);
         ph.counters = reinterpret_cast<uint32_t*>(plan->scratch + m * kCounterRegionBytes);
         ph.partials = reinterpret_cast<float*>(plan->scratch + offsets[m] + (split_bytes(args->cols) + 255) / 256 * 256);
-        ph.row_max = header_row_max(plan, m);
-        ph.collect = (m == 0 && b) ? header_row_max(plan, 1) : nullptr;
         ph.rows = physical_rows; ph.out_rows = args->rows; ph.cols = args->cols; ph.epilogue = args->epilogue;
-        ph.tiles = g.tiles; ph.k_blocks = g.k_blocks; ph.parts = g.parts;
-        ph.scan = m == 0 ? 1u : 0u;
+        ph.contributors = g.contributors[m];
         ph.global_a = args->global_scale; ph.global_b = args->global_scale_b;
-        if (g.ctas > grid) grid = g.ctas;
     }
     if (!b) maps[1] = maps[0];
     cudaLaunchAttribute attribute{};
@@ -801,13 +999,16 @@ augur_cuda_result_v1 launch_tc(augur_cuda_stream_t s, const augur_cuda_nvfp4_sm1
     config.stream = s->stream;
     config.attrs = &attribute;
     config.numAttrs = 1;
-    config.gridDim = dim3(grid);
+    config.gridDim = dim3(g.ctas);
     config.blockDim = dim3(kThreads);
     config.dynamicSmemBytes = kSmemBytes;
     cudaLaunchKernelEx(&config, tc_program_kernel, maps[0], maps[1], p);
     count_launch();
     return submitted();
 }
+
+// Contributors per tile of a single linear on a device with `sm_count` SMs.
+uint32_t linear_contributors(const augur_cuda_nvfp4_sm100_gemv_args_v1* a, uint32_t sm_count) { return tc_program(a, nullptr, sm_count).contributors[0]; }
 
 }  // namespace
 
@@ -824,19 +1025,24 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_tc_s
     if (!out_bytes || !rows || !cols || cols % 64 != 0 || epilogue > AUGUR_NVFP4_SM100_EPILOGUE_LINEAR_F32) return invalid();
     const uint64_t physical = epilogue == AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16 ? 2ull * rows : rows;
     if (physical % kTileM != 0 || physical * cols > UINT32_MAX) return invalid();
-    uint64_t worst = 0;   // over any SM count up to 512
+    // on any device with up to 512 SMs; the second product of the MLP block has two k ranges, each cut like a linear,
+    // and the first has its tiles in two halves
+    uint32_t contributors = 2;
     for (uint32_t sms = 1; sms <= 512; ++sms) {
-        const TcGeometry g = tc_geometry(static_cast<uint32_t>(physical), cols, sms);
-        if (tc_scratch_need(g, cols) > worst) worst = tc_scratch_need(g, cols);
+        const uint32_t parts = 2 * parts_for(static_cast<uint32_t>(physical / kTileM), (cols + kStageK - 1) / kStageK, sms * kCtasPerSm);
+        if (parts > contributors) contributors = parts;
     }
-    *out_bytes = kCounterBytes + (worst + 255) / 256 * 256;
+    *out_bytes = kCounterBytes + (tc_scratch_need(static_cast<uint32_t>(physical), cols, contributors) + 255) / 256 * 256;
     return ok();
 }
 
 extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_tc_bf16_preflight_v1(
     int32_t d, augur_cuda_stream_t s, augur_cuda_nvfp4_sm100_plan_v1* plan, const augur_cuda_nvfp4_sm100_gemv_args_v1* a) {
     augur_cuda_result_v1 failure;
-    if (!check_tc(d, s, plan, a, kCounterBytes, plan ? plan->scratch_bytes : 0, true, &failure)) return failure;
+    if (!check_tc_header(d, s, plan, a, a ? a->abi_version : 0, header_ok(d, s, a), &failure)) return failure;
+    uint32_t physical = 0;
+    if (!check_tc_scalars(a, &physical)) return invalid();
+    if (!check_tc(d, s, plan, a, linear_contributors(a, plan->sm_count), kCounterBytes, plan->scratch_bytes, true, &failure)) return failure;
     CUtensorMap probe;
     return weight_map(&probe, a->weight, physical_rows_of(a), a->cols) ? ok() : make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE);
 }
@@ -844,7 +1050,10 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_tc_b
 extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_tc_bf16_prevalidated_submit_v1(
     int32_t d, augur_cuda_stream_t s, augur_cuda_nvfp4_sm100_plan_v1* plan, const augur_cuda_nvfp4_sm100_gemv_args_v1* a) {
     augur_cuda_result_v1 failure;
-    if (!check_tc(d, s, plan, a, kCounterBytes, plan ? plan->scratch_bytes : 0, false, &failure)) return failure;
+    if (!check_tc_header(d, s, plan, a, a ? a->abi_version : 0, header_ok(d, s, a), &failure)) return failure;
+    uint32_t physical = 0;
+    if (!check_tc_scalars(a, &physical)) return invalid();
+    if (!check_tc(d, s, plan, a, linear_contributors(a, plan->sm_count), kCounterBytes, plan->scratch_bytes, false, &failure)) return failure;
     if (consume_injected_fault()) return make_result(AUGUR_CUDA_STATUS_DIAGNOSTIC_FAULT_INJECTED);
     const cudaError_t e = cudaSetDevice(d);
     if (e != cudaSuccess) return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE, e);
@@ -858,19 +1067,10 @@ namespace {
 // separate halves of the scratch behind them.
 bool check_mlp_tc(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_plan_v1* plan,
                   const augur_cuda_nvfp4_sm100_mlp_args_v1* a, bool full, uint64_t* down_offset, augur_cuda_result_v1* failure) {
-    *failure = invalid();
-    if (!header_ok(d, s, a)) {
-        if (a && s && d >= 0 && s->ordinal == d && a->abi_version != AUGUR_CUDA_ABI_VERSION_V1) {
-            *failure = make_result(AUGUR_CUDA_STATUS_ABI_VERSION_MISMATCH);
-        }
-        return false;
-    }
-    if (!plan_ok(plan, d, s) || plan->scratch_bytes < kCounterBytes) return false;
-    const uint64_t middle = kCounterBytes + (plan->scratch_bytes - kCounterBytes) / 2 / 256 * 256;
-    *down_offset = middle;
-    if (!check_tc(d, s, plan, &a->gate_up, kCounterBytes, middle, false, failure)) return false;
-    if (!check_tc(d, s, plan, &a->down, middle, plan->scratch_bytes, false, failure)) return false;
-    *failure = invalid();
+    if (!check_tc_header(d, s, plan, a, a ? a->abi_version : 0, header_ok(d, s, a), failure)) return false;
+    if (plan->scratch_bytes < kCounterBytes) return false;
+    uint32_t physical = 0;
+    if (!check_tc_scalars(&a->gate_up, &physical) || !check_tc_scalars(&a->down, &physical)) return false;
     if (a->gate_up.epilogue != AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16 || a->down.epilogue == AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16) {
         return false;
     }
@@ -879,6 +1079,12 @@ bool check_mlp_tc(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100
         a->down.cols != a->gate_up.rows || a->down.tokens != a->gate_up.tokens || a->down.rows != a->gate_up.cols) {
         return false;
     }
+    const TcProgram g = tc_program(&a->gate_up, &a->down, plan->sm_count);
+    const uint64_t middle = kCounterBytes + (plan->scratch_bytes - kCounterBytes) / 2 / 256 * 256;
+    *down_offset = middle;
+    if (!check_tc(d, s, plan, &a->gate_up, g.contributors[0], kCounterBytes, middle, false, failure)) return false;
+    if (!check_tc(d, s, plan, &a->down, g.contributors[1], middle, plan->scratch_bytes, false, failure)) return false;
+    *failure = invalid();
     const Range r[6] = {{a->gate_up.weight, a->gate_up.weight_len_bytes, 256},
                         {a->gate_up.input_bf16, a->gate_up.input_len_bytes, 16},
                         {a->gate_up.output, a->gate_up.output_len_bytes, 16},

@@ -49,6 +49,25 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return false;
 }
 
+// The same with the hardware's suspended wait: the thread gives up its issue slots until the phase completes
+// or about a microsecond has passed, instead of polling. For roles that have nothing else to do.
+__device__ __forceinline__ bool mbar_wait_suspended(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                                    uint32_t* status_word, uint32_t code) {
+    for (uint32_t spin = 0; spin < (1u << 21); ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}"
+            : "=r"(done)
+            : "r"(bar), "r"(parity), "r"(1000u)
+            : "memory");
+        if (done) return true;
+        if (*abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicCAS(status_word, 0u, code);
+    return false;
+}
+
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t x, uint32_t y, uint32_t bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
