@@ -87,8 +87,9 @@ constexpr uint32_t kErrTcProducer = 0x301, kErrTcFull = 0x302, kErrTcAccEmpty = 
 // owns: no other kernel of the library writes there, plan creation zeroes them, every launch leaves them ready
 // for the next one.
 constexpr uint32_t kHeaderMeeting = 16;    // three arrival counters of the full meetings, used in turn
-constexpr uint32_t kHeaderEpoch = 19;      // meetings held so far, modulo 12 (two per launch)
+constexpr uint32_t kHeaderEpoch = 19;      // meetings held so far, modulo 3
 constexpr uint32_t kHeaderWave = 20;       // [launch parity][wave]{outputs stored, split stored}
+constexpr uint32_t kHeaderParity = 28;     // launches so far, modulo 2
 constexpr uint32_t kHeaderRowMax = 32;     // [job][token] bits of the row's largest magnitude
 
 // The split activations in global memory (plan scratch): the image the ring stages want, chunk by chunk.
@@ -149,6 +150,9 @@ __device__ __forceinline__ uint32_t counter_arrive(uint32_t* counter) {
     asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(before) : "l"(counter) : "memory");
     return before;
 }
+__device__ __forceinline__ void counter_arrive_only(uint32_t* counter) {
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");
+}
 __device__ __forceinline__ uint32_t counter_read(const uint32_t* counter) {
     uint32_t seen;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
@@ -170,16 +174,30 @@ __device__ __forceinline__ bool counter_wait(const TcParams& p, const uint32_t* 
 // Meeting number m (counted over all launches of the plan, modulo 3, in `meeting`) uses counter m % 3. The last
 // arriver clears counter (m - 1) % 3, which every CTA has stopped reading (all are at meeting m) and which is not
 // used again before meeting m + 2; nobody gets to meeting m + 2 before the last arriver of m, its store behind it,
-// has arrived at m + 1.
-__device__ __forceinline__ bool grid_meet(const TcParams& p, bool leader, uint32_t& meeting, volatile uint32_t* abort_flag) {
+// has arrived at m + 1. A CTA may raise a flag as it arrives (the arrivals count in the low 16 bits, the flags
+// above them): `*raised` says afterwards whether any CTA did.
+__device__ __forceinline__ bool grid_meet(const TcParams& p, bool leader, uint32_t& meeting, bool raise, volatile uint32_t* raised,
+                                          volatile uint32_t* abort_flag) {
     workers_sync();
     if (leader) {
         uint32_t* mine = p.header + kHeaderMeeting + meeting;
-        if (counter_arrive(mine) + 1 == gridDim.x) {
+        uint32_t seen;
+        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], %2;" : "=r"(seen) : "l"(mine), "r"(raise ? 0x10001u : 1u) : "memory");
+        seen += raise ? 0x10001u : 1u;
+        if ((seen & 0xffffu) == gridDim.x) {
             asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p.header + kHeaderMeeting + (meeting + 2) % 3), "r"(0u) : "memory");
         } else {
-            counter_wait(p, mine, kErrTcGridBarrier, abort_flag);
+            for (uint32_t spin = 0;;) {
+                seen = counter_read(mine);
+                if ((seen & 0xffffu) >= gridDim.x) break;
+                if (++spin > kGridWaitLimit || ((spin & 255u) == 255u && *abort_flag)) {
+                    *abort_flag = 1;
+                    atomicCAS(p.header, 0u, kErrTcGridBarrier);
+                    break;
+                }
+            }
         }
+        *raised = seen >> 16;
     }
     meeting = (meeting + 1) % 3;
     workers_sync();
@@ -204,12 +222,25 @@ __device__ __forceinline__ uint32_t load_element(const TcPhase& ph, const TcJob&
     return __ldcg(ph.x + static_cast<uint64_t>(token) * ph.cols + group * 16 + (lane & 15));
 }
 
+// (Both halves are real functions, not inlined: the code that runs at the boundary between the two products is
+// then the code the launch has already run for its input, and is still in the instruction cache.)
 // First half of a group's split, before the row's anchor is known: the group's largest magnitude (returned), the
 // digits relative to it (`drop` low bits fewer), the codes stored. Whole warps; `index` past the job is inactive.
-__device__ __forceinline__ uint32_t split_codes(const TcPhase& ph, const TcJob& job, uint32_t tokens, uint32_t index, uint32_t bits, uint32_t drop,
-                                                uint32_t lane) {
-    const bool active = index < tokens * job.groups;
-    const uint32_t token = active ? index / job.groups : 0, group = active ? job.group0 + (index - token * job.groups) : 0;
+struct SplitTarget {
+    uint8_t* split;               // the phase's split activations
+    uint32_t sf_offset;           // of its block-scale atoms
+    uint32_t group0, groups;      // the job's groups of every token row
+    uint32_t tokens;
+};
+__device__ __forceinline__ SplitTarget split_target(const TcParams& p, uint32_t job_index) {
+    const TcJob& job = p.job[job_index];
+    const TcPhase& ph = p.phase[job.phase];
+    return SplitTarget{ph.split, static_cast<uint32_t>(split_code_bytes(ph.cols)), job.group0, job.groups, p.tokens};
+}
+
+__device__ __noinline__ uint32_t split_codes(const SplitTarget to, uint32_t index, uint32_t bits, uint32_t drop, uint32_t lane) {
+    const bool active = index < to.tokens * to.groups;
+    const uint32_t token = active ? index / to.groups : 0, group = active ? to.group0 + (index - token * to.groups) : 0;
     const uint32_t magnitude = bits & 0x7fffu, negative = (bits >> 15) & 1u;
     uint32_t largest = max(magnitude, __shfl_xor_sync(0xffffffffu, magnitude, 8));
     largest = max(largest, __shfl_xor_sync(0xffffffffu, largest, 4));
@@ -243,28 +274,30 @@ __device__ __forceinline__ uint32_t split_codes(const TcPhase& ph, const TcJob& 
     other = __shfl_xor_sync(0xffffffffu, digits, 8);
     if (active && (lane & 8) == 0) {
         const uint32_t n = (lane & 7) * 8 + token, chunk = group >> 4, unit = (group & 15) >> 1, half = group & 1;
-        uint8_t* codes = ph.split + static_cast<uint64_t>(chunk) * kChunkBytes + (n >> 3) * 1024 + (n & 7) * 128 + ((unit ^ (n & 7)) << 4);
+        uint8_t* codes = to.split + static_cast<uint64_t>(chunk) * kChunkBytes + (n >> 3) * 1024 + (n & 7) * 128 + ((unit ^ (n & 7)) << 4);
         *reinterpret_cast<uint2*>(codes + half * 8) = make_uint2(digits, other);
     }
     return largest;
 }
 
 // Second half, with the row's anchor: the group's block scale 2^q, q = G + 8 - A. A group more than 2^17 below its
-// row's largest magnitude keeps 2^-9 and has its codes redone with that many low bits fewer (rare).
-__device__ __forceinline__ void split_scales(const TcPhase& ph, const TcJob& job, uint32_t tokens, const uint32_t* anchor, uint32_t index,
-                                             uint32_t bits, uint32_t largest, uint32_t lane) {
-    const bool active = index < tokens * job.groups;
-    const uint32_t token = active ? index / job.groups : 0, group = active ? job.group0 + (index - token * job.groups) : 0;
+// row's largest magnitude keeps 2^-9 and has its codes redone with that many low bits fewer (rare). True if the
+// group is larger than the anchor provides for (an anchor that was guessed).
+__device__ __noinline__ bool split_scales(const SplitTarget to, const uint32_t* anchor, uint32_t index, uint32_t bits, uint32_t largest,
+                                          uint32_t lane) {
+    const bool active = index < to.tokens * to.groups;
+    const uint32_t token = active ? index / to.groups : 0, group = active ? to.group0 + (index - token * to.groups) : 0;
     const int q = max(static_cast<int>(largest >> 7), 1) + 8 - static_cast<int>(anchor[token]);
     const uint32_t drop = active && q < -9 ? static_cast<uint32_t>(-9 - q) : 0u;
-    if (__any_sync(0xffffffffu, drop != 0)) split_codes(ph, job, tokens, index, bits, drop, lane);
+    if (__any_sync(0xffffffffu, drop != 0)) split_codes(to, index, bits, drop, lane);
     if (active && (lane & 8) == 0) {
         const int clamped = min(max(q, -9), 8);
         const uint32_t scale_code = clamped >= -6 ? static_cast<uint32_t>(clamped + 7) << 3 : 1u << (clamped + 9);
         const uint32_t n = (lane & 7) * 8 + token;
-        uint8_t* sf = ph.split + split_code_bytes(ph.cols) + static_cast<uint64_t>(group >> 2) * kSfAtomBytes + (group & 3);
+        uint8_t* sf = to.split + to.sf_offset + static_cast<uint64_t>(group >> 2) * kSfAtomBytes + (group & 3);
         sf[(n & 31) * 16 + (n >> 5) * 4] = static_cast<uint8_t>(scale_code);
     }
+    return active && q > 8;   // the group is larger than the anchor allows for
 }
 
 // The term scales of a job from the row maxima every CTA has contributed to (workers 0..7, one token row each).
@@ -288,13 +321,14 @@ __device__ __forceinline__ void share_codes(const TcParams& p, uint32_t job_inde
                                             uint32_t* collected, uint32_t first_pair, uint32_t pair_stride, uint32_t lane) {
     const TcJob& job = p.job[job_index];
     const TcPhase& ph = p.phase[job.phase];
+    const SplitTarget to = split_target(p, job_index);
     const uint32_t groups = p.tokens * job.groups, warp_first = first_pair - (lane >> 4);
 #pragma unroll
     for (uint32_t j = 0; j < kHeld; ++j) {
         largest[j] = 0;
         if (warp_first + j * pair_stride < groups) {
             const uint32_t index = first_pair + j * pair_stride;
-            largest[j] = split_codes(ph, job, p.tokens, index, held[j], 0, lane);
+            largest[j] = split_codes(to, index, held[j], 0, lane);
             if (collected && (lane & 15) == 0 && largest[j]) atomicMax(&collected[index / job.groups], largest[j] << 16);   // zero past the end
         }
     }
@@ -308,21 +342,22 @@ __device__ __forceinline__ void share_codes(const TcParams& p, uint32_t job_inde
         if ((lane & 15) == 0 && most) atomicMax(&collected[index / job.groups], most << 16);
     }
 }
-__device__ __forceinline__ void share_scales(const TcParams& p, uint32_t job_index, const uint32_t* anchor, const uint32_t (&held)[kHeld],
+__device__ __forceinline__ bool share_scales(const TcParams& p, uint32_t job_index, const uint32_t* anchor, const uint32_t (&held)[kHeld],
                                              const uint32_t (&largest)[kHeld], uint32_t first_pair, uint32_t pair_stride, uint32_t lane) {
+    bool beyond = false;
     const TcJob& job = p.job[job_index];
     const TcPhase& ph = p.phase[job.phase];
+    const SplitTarget to = split_target(p, job_index);
     const uint32_t groups = p.tokens * job.groups, warp_first = first_pair - (lane >> 4);
 #pragma unroll
     for (uint32_t j = 0; j < kHeld; ++j) {
-        if (warp_first + j * pair_stride < groups) {
-            split_scales(ph, job, p.tokens, anchor + 8 * job_index, first_pair + j * pair_stride, held[j], largest[j], lane);
-        }
+        if (warp_first + j * pair_stride < groups) beyond |= split_scales(to, anchor + 8 * job_index, first_pair + j * pair_stride, held[j], largest[j], lane);
     }
     for (uint32_t index = first_pair + kHeld * pair_stride; index - (lane >> 4) < groups; index += pair_stride) {
         const uint32_t bits = load_element(ph, job, p.tokens, index, lane);
-        split_scales(ph, job, p.tokens, anchor + 8 * job_index, index, bits, split_codes(ph, job, p.tokens, index, bits, 0, lane), lane);
+        beyond |= split_scales(to, anchor + 8 * job_index, index, bits, split_codes(to, index, bits, 0, lane), lane);
     }
+    return beyond;
 }
 
 // Finished sums of 32 weight rows (lane = row) for the 8 tokens: scale, activation, rounding, store.
@@ -338,10 +373,13 @@ __device__ __forceinline__ void finish_rows(const TcPhase& ph, uint32_t tokens, 
             const float gate = y[token] * ph.global_a;
             uint32_t magnitude = 0;
             if (lane < 16 && token < tokens) {
-                const __nv_bfloat16 h = __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
-                out[static_cast<uint64_t>(token) * ph.out_rows + index] = h;
+                const __nv_bfloat16 h = __float2bfloat16_rn(__fdividef(gate, 1.0f + __expf(-gate)) * up);   // a few ulp of f32, far below the rounding
                 magnitude = static_cast<uint32_t>(__bfloat16_as_ushort(h) & 0x7fffu) << 16;
-                if (kept) kept[token] = __bfloat16_as_ushort(h);
+                if (kept) {
+                    kept[token] = __bfloat16_as_ushort(h);   // stored by the caller, behind its arrival with the maxima
+                } else {
+                    out[static_cast<uint64_t>(token) * ph.out_rows + index] = h;
+                }
             }
             if (collected) {
                 // a later step splits these values: it needs every token row's largest magnitude
@@ -450,9 +488,11 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
     uint32_t* collected = anchor + 8 * kMaxJobs;                                  // [token]: largest magnitudes this CTA has seen (scan, SwiGLU outputs)
     volatile uint32_t* input_ready = collected + 8;                               // the split of job 0 is complete
     volatile uint32_t* wave_set = input_ready + 1;                                // which half of the wave counters this launch uses
+    volatile uint32_t* raised = wave_set + 1;                                     // flags of the last full meeting
+    uint32_t* beyond = const_cast<uint32_t*>(raised) + 1;                         // a group of this CTA's share was beyond its row's guessed anchor
     // full[S] (operand codes landed), empty[S], scales_landed[S], scales_ready[S] (copies to tensor memory issued),
     // acc_full[2], acc_empty[2]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(const_cast<uint32_t*>(wave_set) + 1);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(beyond + 1);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * kStages + 4);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -521,6 +561,7 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
         }
     }
     if (threadIdx.x >= 64 && threadIdx.x < 64 + 8) collected[threadIdx.x - 64] = 0;
+    if (threadIdx.x == 64) *beyond = 0;
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemColumns)
                      : "memory");
@@ -672,45 +713,74 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
         uint32_t acc_phase[2] = {0, 0};
         uint32_t held[kHeld], largest[kHeld];
         asm volatile("griddepcontrol.wait;" ::: "memory");   // the activations may come from the launch before this one; all stores follow
-        uint32_t epoch = 0, meeting = 0;
+        uint32_t meeting = 0, parity = 0;
         uint32_t* wave = nullptr;                              // this launch's wave counters: [wave]{outputs stored, split stored}
         if (leader) {
-            epoch = *static_cast<volatile uint32_t*>(p.header + kHeaderEpoch);   // left by the launch before
-            meeting = epoch % 3;
-            const uint32_t set = (epoch >> 1) & 1;
-            wave = p.header + kHeaderWave + set * 4;
-            *wave_set = set;
+            meeting = *static_cast<volatile uint32_t*>(p.header + kHeaderEpoch);   // left by the launch before
+            parity = *static_cast<volatile uint32_t*>(p.header + kHeaderParity);
+            wave = p.header + kHeaderWave + parity * 4;
+            *wave_set = parity;
             if (blockIdx.x == 0) {
                 // the other half of the wave counters belongs to the launch before (complete) and to the launch after;
                 // the maxima of the later jobs were last read by the launch before and are added to only by CTAs
                 // that have been through a full meeting, i.e. after this CTA has arrived there
-                for (uint32_t i = 0; i < 4; ++i) p.header[kHeaderWave + (set ^ 1) * 4 + i] = 0;
+                for (uint32_t i = 0; i < 4; ++i) p.header[kHeaderWave + (parity ^ 1) * 4 + i] = 0;
                 for (uint32_t i = 8; i < 8 * p.jobs; ++i) p.header[kHeaderRowMax + i] = 0;
             }
         }
         bool alive = true;
         {
             // ---- job 0: the input of the first step comes from outside ----
+            // Its row maxima would take a meeting of their own. Instead every CTA looks at the same sample, the first
+            // 256 elements of every row, takes the anchors three binades above the sample's maxima, and splits its
+            // share with them; a CTA that finds a group beyond its row's anchor says so as it arrives at the meeting
+            // that follows the split, and then all CTAs do the split again with the true maxima, which they have
+            // collected on the way. Which of the two happens depends on the input alone.
             const TcJob& job = p.job[0];
+            const TcPhase& ph = p.phase[job.phase];
 #pragma unroll
-            for (uint32_t j = 0; j < kHeld; ++j) held[j] = load_element(p.phase[job.phase], job, p.tokens, first_pair + j * pair_stride, lane);
-            // the codes of this CTA's share and the largest magnitudes it has seen; the block scales need the rows' anchors
+            for (uint32_t j = 0; j < kHeld; ++j) held[j] = load_element(ph, job, p.tokens, first_pair + j * pair_stride, lane);
+            {
+                const uint32_t token = worker >> 4;
+                uint32_t packed = 0;
+                if (token < p.tokens) {
+                    const uint4* row = reinterpret_cast<const uint4*>(ph.x + static_cast<uint64_t>(token) * ph.cols);
+                    for (uint32_t i = worker & 15; i < min(ph.cols, 256u) / 8; i += 16) {
+                        const uint4 v = __ldcg(row + i);
+                        packed = __vmaxu2(packed, __vmaxu2(__vmaxu2(v.x & 0x7fff7fffu, v.y & 0x7fff7fffu), __vmaxu2(v.z & 0x7fff7fffu, v.w & 0x7fff7fffu)));
+                    }
+                }
+                uint32_t most = max(packed & 0xffffu, packed >> 16);
+                most = max(most, __shfl_xor_sync(0xffffffffu, most, 8));
+                most = max(most, __shfl_xor_sync(0xffffffffu, most, 4));
+                most = max(most, __shfl_xor_sync(0xffffffffu, most, 2));
+                most = max(most, __shfl_xor_sync(0xffffffffu, most, 1));
+                if ((worker & 15) == 0) {
+                    // term 0 of the row has the global scale 2^(A - 155), term 7 2^(A - 134): all normal f32 numbers
+                    const uint32_t a = min(max((most >> 7) + 3, 40u), 250u);
+                    anchor[token] = a;
+                    term_scale[token] = __uint_as_float((a - 28) << 23);
+                }
+            }
+            workers_sync();
             share_codes(p, 0, held, largest, collected, first_pair, pair_stride, lane);
+            if (share_scales(p, 0, anchor, held, largest, first_pair, pair_stride, lane)) *beyond = 1;   // any lane; a non-finite element is beyond too
             workers_sync();
             if (worker < 8) {
                 if (collected[worker]) atomicMax(p.header + kHeaderRowMax + worker, collected[worker]);
                 collected[worker] = 0;
             }
-            alive = grid_meet(p, leader, meeting, abort_flag);      // every CTA has contributed its maxima
-            if (alive) {
+            // every CTA's slice is in place before any CTA loads from the split (the thread that issues the loads puts
+            // a proxy fence between the meeting and them)
+            alive = grid_meet(p, leader, meeting, *beyond != 0, raised, abort_flag);
+            if (alive && *raised) {
                 job_scales(p, 0, worker, term_scale, anchor);
+                share_codes(p, 0, held, largest, nullptr, first_pair, pair_stride, lane);
                 share_scales(p, 0, anchor, held, largest, first_pair, pair_stride, lane);
-                // every CTA's slice is in place before any CTA loads from the split (the thread that issues the loads
-                // puts a proxy fence between the meeting and them)
-                alive = grid_meet(p, leader, meeting, abort_flag);
+                alive = grid_meet(p, leader, meeting, false, raised, abort_flag);
             }
             if (alive) {
-                if (blockIdx.x == 0 && worker < 8) p.header[kHeaderRowMax + worker] = 0;   // every CTA has read them: clean for the next launch
+                if (blockIdx.x == 0 && worker < 8) p.header[kHeaderRowMax + worker] = 0;   // clean for the next launch
                 if (leader) {
                     __threadfence_block();
                     *input_ready = 1;
@@ -763,24 +833,34 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
             const uint32_t w = st.feeds - 1;
             const TcJob& job = p.job[st.feeds];
             const TcPhase& next = p.phase[job.phase];
+            const SplitTarget to = split_target(p, st.feeds);
             workers_sync();
             if (worker < 8) {
                 if (collected[worker]) atomicMax(p.header + kHeaderRowMax + 8 * st.feeds + worker, collected[worker]);
                 collected[worker] = 0;
             }
             workers_sync();
-            if (leader) counter_arrive(wave + 2 * w);
+            if (leader) counter_arrive_only(wave + 2 * w);
             // While the other CTAs arrive: every warp writes the codes of the 16 columns it has just stored, from
             // registers: lanes 0..15 take token rows 0..3, lanes 16..31 rows 4..7, one group each.
             uint32_t index[4] = {~0u, ~0u, ~0u, ~0u}, bits[4] = {0, 0, 0, 0};
             if (st.keeps && kept_group != ~0u) {
+                // the outputs themselves: nobody in this launch reads them back, and the arrival above, which releases
+                // everything written before it, did not have to wait for them
+                if (lane < 16) {
+                    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(ph.out);
+#pragma unroll
+                    for (uint32_t token = 0; token < 8; ++token) {
+                        if (token < p.tokens) out[static_cast<uint64_t>(token) * ph.out_rows + kept_group * 16 + lane] = __ushort_as_bfloat16(static_cast<unsigned short>(kept[token]));
+                    }
+                }
 #pragma unroll
                 for (uint32_t j = 0; j < 4; ++j) {
                     const uint32_t token = j + ((lane >> 4) << 2);
                     const uint32_t theirs = __shfl_sync(0xffffffffu, kept[4 + j], lane & 15);
                     index[j] = token < p.tokens ? token * job.groups + (kept_group - job.group0) : ~0u;
                     bits[j] = lane < 16 ? kept[j] : theirs;
-                    largest[j] = split_codes(next, job, p.tokens, index[j], bits[j], 0, lane);
+                    largest[j] = split_codes(to, index[j], bits[j], 0, lane);
                 }
             }
             if (leader) counter_wait(p, wave + 2 * w, kErrTcWave, abort_flag);
@@ -793,7 +873,7 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
             if (st.keeps) {
                 if (kept_group != ~0u) {
 #pragma unroll
-                    for (uint32_t j = 0; j < 4; ++j) split_scales(next, job, p.tokens, anchor + 8 * st.feeds, index[j], bits[j], largest[j], lane);
+                    for (uint32_t j = 0; j < 4; ++j) split_scales(to, anchor + 8 * st.feeds, index[j], bits[j], largest[j], lane);
                 }
             } else {
                 // items of several CTAs per tile, or several items per CTA: the outputs are read back, every CTA a share
@@ -803,10 +883,13 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
                 share_scales(p, st.feeds, anchor, held, largest, first_pair, pair_stride, lane);
             }
             workers_sync();
-            if (leader) counter_arrive(wave + 2 * w + 1);
+            if (leader) counter_arrive_only(wave + 2 * w + 1);
         }
-        // the next launch goes on counting meetings where this one stopped
-        if (alive && leader && blockIdx.x == 0) p.header[kHeaderEpoch] = (epoch + 2) % 12;
+        // the next launch goes on counting meetings where this one stopped, with the other half of the wave counters
+        if (alive && leader && blockIdx.x == 0) {
+            p.header[kHeaderEpoch] = meeting;
+            p.header[kHeaderParity] = parity ^ 1;
+        }
     }
 
     tc_fence_before();
