@@ -12,12 +12,17 @@ such passes, so that the timed region of a default run lasts about a second. Wit
 tensor-parallel: column-parallel gate|up, row-parallel down, the all-reduce of the 8 x 5120 output
 inside the down launch (peer stores over NVLink) or by NCCL.
 
+Two small-token kernels exist. On one GPU the headline runs the block as ONE launch of the tensor-memory kernel
+(`tc_program_kernel`: tcgen05 block-scaled MMA straight on the weight tiles TMA delivers); with N > 1 it runs the
+`mma.sync` kernel (`gemv_kernel`, two launches per block), which carries the fused exchange. `--small-token-kernel`
+overrides the choice on one GPU.
+
 Prints one JSON line (rank 0). `value` is whole-job GB/s of algorithmic bytes with inputs resident in
 HBM; `e2e` is the same through the public host API with the activations copied from pinned host memory
 and the result read back for every pass. The other configurations of the benchmark definition are
 reported under their own keys of the same line, each outside the headline's timed region:
-`config0` (single 17408 x 5120 linear, M=8), `config1_m1` (the MLP block at M=1), `config1_tensor_memory_path`
-(the block as one tcgen05 launch), `config2_prefill` (M=4096 GEMMs), `config3_sweep` (64-layer whole-model linear
+`config0` (single 17408 x 5120 linear, M=8), `config1_m1` (the MLP block at M=1), `config1_other_kernel`
+(the block on the small-token kernel that the headline does not use), `config2_prefill` (M=4096 GEMMs), `config3_sweep` (64-layer whole-model linear
 sweep at M=8), `config4_prefill_mlp` (chunked tensor-parallel prefill MLP), `head_bf16` (the BF16 vocabulary head).
 """
 from __future__ import annotations
@@ -63,12 +68,21 @@ def measured_peaks():
 DATASHEET_FP4_TFLOPS = 9000.0    # dense NVFP4 per B200; no measured FP4 figure exists on this pool
 
 
-def recorded_traffic():
-    """DRAM bytes of one gate|up + down launch pair from the tracked ncu summary of the decode kernel, or None."""
-    path = os.path.join(ROOT, "profiles", "gemv_kernel_mlp_m8.md")
+KERNELS = {
+    # name of the choice -> (kernel, launches per block, tracked ncu summary, dtype line)
+    "tensor_memory": ("tc_program_kernel", 1, "tc_program_kernel_mlp_m8.md",
+                      "e2m1 x e2m1 -> f32 on tcgen05 (kind::mxf4nvf4, E4M3 block scales in the MMA); BF16 activations as eight exact radix-8 NVFP4 terms"),
+    "mma_sync": ("gemv_kernel", 2, "gemv_kernel_mlp_m8.md",
+                 "bf16 x bf16 -> f32 (E2M1 codes as BF16 fragments on mma.sync, E4M3 block scales applied in f32)"),
+}
+
+
+def recorded_traffic(summary):
+    """DRAM bytes of the launches of one MLP block from the tracked ncu summary of the kernel, or None."""
+    path = os.path.join(ROOT, "profiles", summary)
     try:
         with open(path) as handle:
-            match = re.search(r"dram_bytes_per_launch_pair:\s*([0-9.eE+]+)", handle.read())
+            match = re.search(r"dram_bytes_per_(?:launch_pair|block):\s*([0-9.eE+]+)", handle.read())
         return float(match.group(1)) if match else None
     except OSError:
         return None
@@ -243,22 +257,34 @@ class Context:
                              "frac": achieved / self.hbm_peak, "peak_source": self.peak_source, "traffic": None}}
 
 
-def build_mlp_layers(ctx, layers, keep_first_planes=False):
-    """`layers` distinct MLP layers of this rank's shard; optionally the compact planes of the first, on the host."""
+def build_mlp_layers(ctx, layers, keep_first_planes=False, kernel="mma_sync", seed=1234):
+    """`layers` distinct MLP layers of this rank's shard in the hot layouts of `kernel`; optionally the compact planes
+    of the first, on the host."""
     from augur_v100_b200 import synth
     torch, host, abi = ctx.torch, ctx.host, ctx.abi
     generator = torch.Generator(device=ctx.device)
-    generator.manual_seed(1234 + ctx.rank)
+    generator.manual_seed(seed + ctx.rank)
     shard = INTER // ctx.world
+
+    def interleave(gate_plane, up_plane):   # 16 gate rows, then the matching 16 up rows
+        width = gate_plane.shape[1]
+        return torch.stack([gate_plane.view(shard // 16, 16, width), up_plane.view(shard // 16, 16, width)], dim=1).reshape(2 * shard, width).contiguous()
+
     built, first = [], None
     for index in range(layers):
         gc, gs = device_planes(torch, generator, shard, HIDDEN, ctx.device)
         uc, us = device_planes(torch, generator, shard, HIDDEN, ctx.device)
-        gate_up = host.Nvfp4Sm100Weight.repack_device_planes(
-            ctx.stream, abi.LAYOUT_STREAM_PAIR, shard, HIDDEN, gc, gs, synth.GLOBAL_SCALE, uc, us, synth.GLOBAL_SCALE)
         dc, ds = device_planes(torch, generator, HIDDEN, shard, ctx.device)
-        down = host.Nvfp4Sm100Weight.repack_device_planes(
-            ctx.stream, abi.LAYOUT_STREAM, HIDDEN, shard, dc, ds, synth.GLOBAL_SCALE)
+        if kernel == "tensor_memory":
+            gate_up = host.Nvfp4Sm100Weight.repack_device_planes(ctx.stream, abi.LAYOUT_TCGEN05, 2 * shard, HIDDEN, interleave(gc, uc),
+                                                                 interleave(gs, us), synth.GLOBAL_SCALE)
+            gate_up.global_scale_b = synth.GLOBAL_SCALE
+            down = host.Nvfp4Sm100Weight.repack_device_planes(ctx.stream, abi.LAYOUT_TCGEN05, HIDDEN, shard, dc, ds, synth.GLOBAL_SCALE)
+        else:
+            gate_up = host.Nvfp4Sm100Weight.repack_device_planes(
+                ctx.stream, abi.LAYOUT_STREAM_PAIR, shard, HIDDEN, gc, gs, synth.GLOBAL_SCALE, uc, us, synth.GLOBAL_SCALE)
+            down = host.Nvfp4Sm100Weight.repack_device_planes(
+                ctx.stream, abi.LAYOUT_STREAM, HIDDEN, shard, dc, ds, synth.GLOBAL_SCALE)
         if index == 0 and keep_first_planes:
             first = tuple((c.cpu().numpy(), s.cpu().numpy(), synth.GLOBAL_SCALE) for c, s in ((gc, gs), (uc, us), (dc, ds)))
         built.append((gate_up, down))
@@ -326,36 +352,20 @@ def config0_probe(ctx):
     return entry
 
 
-def tensor_memory_path_probe(ctx):
-    """Configuration 1 through the tensor-memory small-token path: the whole MLP block as ONE launch (tcgen05
-    block-scaled MMA on the weights as TMA delivers them, activations split into six NVFP4 terms inside the launch).
-    Eight distinct layers in rotation (1.2 GB of weights); parity of the first against the CPU oracle."""
+def other_kernel_probe(ctx, kernel):
+    """Configuration 1 on the small-token kernel the headline does not use: eight distinct layers in rotation (1.2 GB
+    of weights); parity of the first against the CPU oracle."""
     import oracle
-    from augur_v100_b200 import synth
-    torch, host, abi = ctx.torch, ctx.host, ctx.abi
-    generator = torch.Generator(device=ctx.device)
-    generator.manual_seed(2024)
+    torch, host = ctx.torch, ctx.host
     count = 8
-    plan = host.Plan(ctx.stream, host.mlp_tc_scratch_bytes(HIDDEN, INTER))
+    layers, first = build_mlp_layers(ctx, count, keep_first_planes=True, kernel=kernel, seed=2024)
+    tensor_memory = kernel == "tensor_memory"
+    plan = host.Plan(ctx.stream, host.mlp_tc_scratch_bytes(HIDDEN, INTER) if tensor_memory else host.mlp_scratch_bytes(HIDDEN, INTER))
+    generator = torch.Generator(device=ctx.device)
+    generator.manual_seed(77)
     x = torch.randn((TOKENS, HIDDEN), device=ctx.device, generator=generator).mul_(8.0).to(torch.bfloat16)
-    programs, first = [], None
-    for index in range(count):
-        gc, gs = device_planes(torch, generator, INTER, HIDDEN, ctx.device)
-        uc, us = device_planes(torch, generator, INTER, HIDDEN, ctx.device)
-
-        def interleave(gate_plane, up_plane):   # 16 gate rows, then the matching 16 up rows
-            width = gate_plane.shape[1]
-            return torch.stack([gate_plane.view(INTER // 16, 16, width), up_plane.view(INTER // 16, 16, width)], dim=1).reshape(2 * INTER, width).contiguous()
-
-        gate_up = host.Nvfp4Sm100Weight.repack_device_planes(ctx.stream, abi.LAYOUT_TCGEN05, 2 * INTER, HIDDEN, interleave(gc, uc),
-                                                             interleave(gs, us), synth.GLOBAL_SCALE)
-        gate_up.global_scale_b = synth.GLOBAL_SCALE
-        dc, ds = device_planes(torch, generator, HIDDEN, INTER, ctx.device)
-        down = host.Nvfp4Sm100Weight.repack_device_planes(ctx.stream, abi.LAYOUT_TCGEN05, HIDDEN, INTER, dc, ds, synth.GLOBAL_SCALE)
-        if index == 0:
-            first = tuple((c.cpu().numpy(), s.cpu().numpy(), synth.GLOBAL_SCALE) for c, s in ((gc, gs), (uc, us), (dc, ds)))
-        programs.append(host.Nvfp4Sm100TcFfnProgram.bind(plan, gate_up, down, x))
-        del gc, gs, uc, us, dc, ds
+    program_type = host.Nvfp4Sm100TcFfnProgram if tensor_memory else host.Nvfp4Sm100FfnProgram
+    programs = [program_type.bind(plan, gate_up, down, x) for gate_up, down in layers]
 
     def sweep():
         for program in programs:
@@ -368,8 +378,9 @@ def tensor_memory_path_probe(ctx):
     ms = ctx.timed(sweep, reps) / (reps * count)
     launches = (host.launch_count() - launches_before) // (reps * count)
     entry = ctx.hbm_entry(layer_bytes(), layer_bytes(), ms)
-    entry.update({"workload": f"config1 through the tensor-memory path: the MLP block as one launch, M={TOKENS}; {count} distinct layers in rotation; ms per layer",
-                  "launches_per_layer": launches, "device_status": plan.device_status()})
+    entry.update({"workload": f"config1 on {KERNELS[kernel][0]}: the MLP block, M={TOKENS}; {count} distinct layers in rotation; ms per layer",
+                  "kernel": KERNELS[kernel][0], "launches_per_layer": launches, "device_status": plan.device_status()})
+    entry["roofline"]["traffic"] = recorded_traffic(KERNELS[kernel][2])
     gate, up, down = first
     programs[0].submit_for_plan()
     ctx.stream.synchronize()
@@ -378,7 +389,7 @@ def tensor_memory_path_probe(ctx):
     y64_from_h = oracle.linear_f64(down[0], down[1], down[2], HIDDEN, INTER, h_bits, threads=oracle.max_threads())
     entry["parity"] = {"gate_up_rel_error_vs_fp64_oracle": rel_error(h_bits, h64),
                        "down_rel_error_vs_fp64_oracle": rel_error(bits(programs[0].out), y64_from_h), "bound": 2e-2}
-    del programs
+    del programs, layers
     plan.close()
     return entry
 
@@ -604,17 +615,21 @@ def run_library(args):
     torch.cuda.set_stream(side)
     stream = host.Stream(local, side)
     ctx = Context(torch, dist, host, abi, device, stream, side, world, rank)
-    layers, first_planes = build_mlp_layers(ctx, LAYERS, keep_first_planes=(world == 1 and rank == 0))
-    plan = host.Plan(stream, host.mlp_scratch_bytes(HIDDEN, INTER // world))
+    # one GPU: the tensor-memory kernel, one launch per block; tensor-parallel: the mma.sync kernel, which carries the exchange
+    kernel = args.small_token_kernel if world == 1 else "mma_sync"
+    tensor_memory = kernel == "tensor_memory"
+    program_type = host.Nvfp4Sm100TcFfnProgram if tensor_memory else host.Nvfp4Sm100FfnProgram
+    layers, first_planes = build_mlp_layers(ctx, LAYERS, keep_first_planes=(world == 1 and rank == 0), kernel=kernel)
+    plan = host.Plan(stream, host.mlp_tc_scratch_bytes(HIDDEN, INTER) if tensor_memory else host.mlp_scratch_bytes(HIDDEN, INTER // world))
     x_host = torch.randn((TOKENS, HIDDEN), dtype=torch.float32).mul_(8.0).to(torch.bfloat16).pin_memory()
     y_host = torch.empty((TOKENS, HIDDEN), dtype=torch.bfloat16).pin_memory()
     x = x_host.to(device)
     outs = [torch.empty((TOKENS, HIDDEN), dtype=torch.bfloat16, device=device) for _ in range(2)]
-    programs = [host.Nvfp4Sm100FfnProgram.bind(plan, gate_up, down, x, out=outs[index % 2])
+    programs = [program_type.bind(plan, gate_up, down, x, out=outs[index % 2])
                 for index, (gate_up, down) in enumerate(layers)]
     x1 = x[:1].contiguous()
     outs1 = [torch.empty((1, HIDDEN), dtype=torch.bfloat16, device=device) for _ in range(2)]
-    programs_m1 = [host.Nvfp4Sm100FfnProgram.bind(plan, gate_up, down, x1, out=outs1[index % 2])
+    programs_m1 = [program_type.bind(plan, gate_up, down, x1, out=outs1[index % 2])
                    for index, (gate_up, down) in enumerate(layers)]
 
     # With more than one rank the all-reduce is fused into the down launch (peer stores over NVLink);
@@ -773,7 +788,8 @@ def run_library(args):
             extras["config4_prefill_mlp"] = {"error": repr(error)}
         torch.cuda.empty_cache()
         if world == 1:
-            for key, probe in (("config0", config0_probe), ("config1_tensor_memory_path", tensor_memory_path_probe),
+            other = "mma_sync" if tensor_memory else "tensor_memory"
+            for key, probe in (("config0", config0_probe), ("config1_other_kernel", lambda c: other_kernel_probe(c, other)),
                                ("config2_prefill", prefill_probe), ("head_bf16", head_probe)):
                 try:
                     extras[key] = probe(ctx)
@@ -791,27 +807,29 @@ def run_library(args):
     ms_per_pass = ms_per_step / PASSES
     value = pass_bytes / (ms_per_pass * 1e-3) / 1e9
     e2e_pass_ms = e2e_ms / args.steps / PASSES
-    # Per GPU, per layer: the two launches of the streaming kernel read this rank's weight shard once.
+    # Per GPU, per layer: the launches of the block (one, or two) read this rank's weight shard once.
     per_gpu_layer_bytes = 3 * HIDDEN * (INTER // world) * 9 // 16 + 2 * TOKENS * HIDDEN * 2
     launch_pair_ms = ms_per_pass / LAYERS
+    kernel_name, launches_per_block, summary, dtype_line = KERNELS[kernel]
     achieved = per_gpu_layer_bytes / (launch_pair_ms * 1e-3) / 1e9
     line = {
         "metric": "nvfp4_linear_m8_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "bf16 x bf16 -> f32 (E2M1 codes as BF16 fragments on mma.sync, E4M3 block scales applied in f32)",
+        "vs_baseline": None, "dtype": dtype_line,
         "data": "synthetic",
         "config": {"workload": f"config1: NVFP4 MLP block (gate|up+SwiGLU, down), M={TOKENS}, hidden {HIDDEN}, "
                                f"intermediate {INTER}; one step = {PASSES} passes over {LAYERS} distinct layers",
                    "passes_per_step": PASSES, "layers_per_pass": LAYERS, "ms_per_pass": ms_per_pass,
                    "l2": f"inputs larger than L2: {LAYERS * 3 * HIDDEN * INTER * 9 // 16 // world} weight bytes per GPU per pass",
-                   "parallelism": f"tp{world}" if world > 1 else "single", "all_reduce": exchange_note},
+                   "parallelism": f"tp{world}" if world > 1 else "single", "all_reduce": exchange_note,
+                   "small_token_kernel": f"{kernel_name}, {launches_per_block} launch(es) per block"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": ctx.hbm_peak, "unit": "GB/s", "frac": achieved / ctx.hbm_peak,
-                     # dram__bytes_read.sum + dram__bytes_write.sum of one gate|up launch plus one down launch
-                     # (single GPU, full shapes) as recorded in the tracked ncu summary of this kernel
-                     "traffic": recorded_traffic() if world == 1 else None, "traffic_unit": "bytes per launch pair (ncu)",
+                     # dram__bytes_read.sum + dram__bytes_write.sum of the launches of one block (single GPU, full
+                     # shapes) as recorded in the tracked ncu summary of this kernel
+                     "traffic": recorded_traffic(summary) if world == 1 else None, "traffic_unit": "bytes per block (ncu)",
                      "peak_source": ctx.peak_source,
-                     "kernel": "gemv_kernel (gate|up launch + down launch per layer; with N>1 the interval also holds the all-reduce)",
-                     "bytes_per_launch_pair": per_gpu_layer_bytes, "ms_per_launch_pair": launch_pair_ms},
+                     "kernel": f"{kernel_name} ({launches_per_block} launch(es) per block; with N>1 the interval also holds the all-reduce)",
+                     "bytes_per_block": per_gpu_layer_bytes, "ms_per_block": launch_pair_ms},
         "e2e": {"value": pass_bytes / (e2e_pass_ms * 1e-3) / 1e9, "unit": "GB/s",
                 "h2d_bytes_per_step": PASSES * TOKENS * HIDDEN * 2, "d2h_bytes_per_step": PASSES * TOKENS * HIDDEN * 2,
                 "ms_per_step": e2e_ms / args.steps, "submission": e2e_submission,
@@ -837,6 +855,8 @@ def main():
     parser.add_argument("--headline-only", action="store_true",
                         help="time configuration 1 only (skips the other configurations' entries)")
     parser.add_argument("--prefill-mlp-tokens", type=int, default=32768)
+    parser.add_argument("--small-token-kernel", choices=sorted(KERNELS), default="tensor_memory",
+                        help="the kernel of the headline on one GPU (tensor-parallel runs use mma_sync, which carries the exchange)")
     parser.add_argument("--allreduce", choices=["fused", "nccl"], default="fused",
                         help="N>1: all-reduce inside the down launch over peer memory, or NCCL on the BF16 partials")
     parser.add_argument("--layers", type=int, default=LAYERS,
