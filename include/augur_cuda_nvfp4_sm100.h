@@ -276,10 +276,12 @@ augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_bf16_prevalidat
  * (for EPILOGUE_SWIGLU_BF16: one tensor of 2 * rows physical rows, 16 gate rows alternating with the
  * matching 16 up rows, as interleave_gate_up_host_v1 makes it), rows (physical) a multiple of 128, cols a
  * multiple of 64. The weights reach the tensor cores (tcgen05.mma kind::mxf4nvf4) as TMA delivers them;
- * the BF16 activations are split inside the launch into six NVFP4 residual terms, which reproduces them to
- * about 3e-7 of a 16-element group's largest magnitude. The launch holds a grid-wide barrier: it needs all
- * of its CTAs (at most two per SM) resident, so keep other long-running kernels off the device meanwhile; a
- * barrier wait that runs out sets the plan's status word to 0x307. Replaces the same reference entry points as
+ * the BF16 activations are split inside the launch into eight NVFP4 terms (radix-8 digits with power-of-two
+ * scales), exact for every element within 2^-14 of its 16-element group's largest magnitude and to 2^-23 of that
+ * magnitude below; a token row with a non-finite element gives NaN outputs. The CTAs of the launch meet through
+ * counters in the plan's header: it needs all of them (at most two per SM) resident, so keep other long-running
+ * kernels off the device meanwhile; a wait that runs out sets the plan's status word to 0x301..0x309, and reading
+ * the status word then also clears the counters. Replaces the same reference entry points as
  * gemv_bf16_*_v1 (augur_qwen35_nvfp4_qpn_abi.h:134-156), with one weight layout for every token count. */
 augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_tc_scratch_extent_host_v1(
     uint32_t rows, uint32_t cols, uint32_t epilogue, uint64_t* out_bytes);
