@@ -608,6 +608,8 @@ def run_library(args):
     if world > 1:
         # NCCL writes its version / debug lines to stdout by default; stdout carries the one JSON line only
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=device)
 
     # Everything runs on one non-default stream, so that a pass can also be captured into a CUDA graph.

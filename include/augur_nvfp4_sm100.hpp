@@ -427,6 +427,61 @@ inline std::shared_ptr<Nvfp4Sm100Weight> upload_gate_up_interleaved(const std::s
     return Nvfp4Sm100Weight::upload_checkpoint_nvfp4(stream, AUGUR_NVFP4_SM100_LAYOUT_TCGEN05, 2 * inter, hidden, both);
 }
 
+// Plan scratch for the MLP block on the tensor-memory small-token kernel: both members' needs, side by side.
+inline uint64_t mlp_tc_scratch_bytes(uint32_t hidden, uint32_t intermediate) {
+    uint64_t first = 0, second = 0;
+    check("gemv_tc_scratch_extent", augur_cuda_nvfp4_sm100_gemv_tc_scratch_extent_host_v1(intermediate, hidden, AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16, &first));
+    check("gemv_tc_scratch_extent", augur_cuda_nvfp4_sm100_gemv_tc_scratch_extent_host_v1(hidden, intermediate, AUGUR_NVFP4_SM100_EPILOGUE_LINEAR_BF16, &second));
+    return 2 * (first > second ? first : second) + 512;
+}
+
+// The MLP block for tokens 1..8 on the tensor-memory kernel: ONE launch; `gate_up` is the interleaved TCGEN05
+// weight of `upload_gate_up_interleaved` (the weight the prefill program uses), `down` a TCGEN05 weight. Same
+// contract as Nvfp4Sm100FfnProgram.
+class Nvfp4Sm100TcFfnProgram {
+public:
+    static std::unique_ptr<Nvfp4Sm100TcFfnProgram> bind(std::shared_ptr<Plan> plan, std::shared_ptr<Nvfp4Sm100Weight> gate_up,
+                                                        float up_global_scale, std::shared_ptr<Nvfp4Sm100Weight> down,
+                                                        std::shared_ptr<DeviceBuffer> input, std::shared_ptr<DeviceBuffer> output, uint32_t tokens) {
+        if (gate_up->layout() != AUGUR_NVFP4_SM100_LAYOUT_TCGEN05 || down->layout() != AUGUR_NVFP4_SM100_LAYOUT_TCGEN05) {
+            throw std::invalid_argument("gate|up and down must be TCGEN05 weights");
+        }
+        if (plan->stream() != gate_up->stream() || plan->stream() != down->stream()) {
+            throw std::invalid_argument("plan and weights belong to different streams");
+        }
+        std::unique_ptr<Nvfp4Sm100TcFfnProgram> program(new Nvfp4Sm100TcFfnProgram());
+        const Stream& s = *plan->stream();
+        const uint32_t inter = gate_up->rows() / 2;
+        program->intermediate_ = std::make_shared<DeviceBuffer>(s.ordinal(), static_cast<uint64_t>(tokens) * inter * 2);
+        program->args_ = header<augur_cuda_nvfp4_sm100_mlp_args_v1>();
+        program->args_.gate_up = gemv_args(*gate_up, *input, *program->intermediate_, tokens, AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16);
+        program->args_.gate_up.rows = inter;
+        program->args_.gate_up.output_len_bytes = static_cast<uint64_t>(tokens) * inter * 2;
+        program->args_.gate_up.global_scale_b = up_global_scale;
+        program->args_.down = gemv_args(*down, *program->intermediate_, *output, tokens, AUGUR_NVFP4_SM100_EPILOGUE_LINEAR_BF16);
+        check("mlp_tc_preflight", augur_cuda_nvfp4_sm100_mlp_tc_preflight_v1(s.ordinal(), s.handle(), plan->raw(), &program->args_));
+        program->plan_ = std::move(plan);
+        program->gate_up_ = std::move(gate_up);
+        program->down_ = std::move(down);
+        program->input_ = std::move(input);
+        program->output_ = std::move(output);
+        return program;
+    }
+    void submit_for_plan() const {
+        const Stream& s = *plan_->stream();
+        check("mlp_tc_submit", augur_cuda_nvfp4_sm100_mlp_tc_prevalidated_submit_v1(s.ordinal(), s.handle(), plan_->raw(), &args_));
+    }
+    const std::shared_ptr<DeviceBuffer>& intermediate() const { return intermediate_; }
+    const std::shared_ptr<DeviceBuffer>& output() const { return output_; }
+
+private:
+    Nvfp4Sm100TcFfnProgram() = default;
+    augur_cuda_nvfp4_sm100_mlp_args_v1 args_{};
+    std::shared_ptr<Plan> plan_;
+    std::shared_ptr<Nvfp4Sm100Weight> gate_up_, down_;
+    std::shared_ptr<DeviceBuffer> input_, intermediate_, output_;
+};
+
 // The MLP block for wide inputs (any token count): quantise x, gate|up GEMM with SiLU(gate)*up in its epilogue,
 // quantise the intermediate, down GEMM. Four launches; every member is preflighted at bind time.
 class Nvfp4Sm100PrefillFfnProgram {

@@ -236,6 +236,37 @@ int main() {
             std::printf("prefill ffn: rms err %.3e\n", e);
             expect(e <= 2e-2, "prefill FFN within 2e-2 (rms) of the fp64 oracle");
         }
+        // ---- the same FFN, 8 token rows, as ONE launch of the tensor-memory kernel on the prefill program's weights ----
+        {
+            float up_scale = 0.0f;
+            auto tc_gate_up = upload_gate_up_interleaved(stream, inter, hidden, gate_m, up_m, &up_scale);
+            auto tc_down = Nvfp4Sm100Weight::upload_checkpoint_nvfp4(stream, AUGUR_NVFP4_SM100_LAYOUT_TCGEN05, hidden, inter, down_m);
+            auto tc_plan = std::make_shared<Plan>(stream, mlp_tc_scratch_bytes(hidden, inter));
+            auto tc_out = std::make_shared<DeviceBuffer>(0, static_cast<uint64_t>(tokens) * hidden * 2);
+            auto tc_program = Nvfp4Sm100TcFfnProgram::bind(tc_plan, tc_gate_up, up_scale, tc_down, x_dev, tc_out, tokens);
+            tc_program->submit_for_plan();
+            stream->synchronize();
+            const auto before_tc = allocation_snapshot();
+            const uint64_t launches_tc = launch_count();
+            for (int i = 0; i < 10; ++i) tc_program->submit_for_plan();
+            stream->synchronize();
+            expect(allocation_snapshot() == before_tc, "the tensor-memory submit loop allocates nothing");
+            expect(launch_count() - launches_tc == 10, "one launch per program");
+            expect(tc_plan->device_status() == 0, "tensor-memory device status word clean");
+            std::vector<uint16_t> tc_y(tokens * hidden), tc_h(tokens * inter);
+            tc_out->download(*stream, tc_y.data(), tc_y.size() * 2);
+            tc_program->intermediate()->download(*stream, tc_h.data(), tc_h.size() * 2);
+            std::vector<double> h64(tc_h.size()), y64(tc_y.size()), have_h(tc_h.size()), have_y(tc_y.size());
+            expect(augur_oracle_mlp_f64(gate.codes.data(), gate.scales.data(), gate.global, up.codes.data(), up.scales.data(), up.global,
+                                        down.codes.data(), down.scales.data(), down.global, hidden, inter, x.data(), tokens,
+                                        h64.data(), y64.data(), threads) == 0, "oracle mlp");
+            for (size_t i = 0; i < tc_h.size(); ++i) have_h[i] = from_bf16(tc_h[i]);
+            for (size_t i = 0; i < tc_y.size(); ++i) have_y[i] = from_bf16(tc_y[i]);
+            const double eh = rel_error(have_h, h64), ey = rms_error(have_y, y64);
+            std::printf("tensor-memory ffn: h rel err %.3e, y rms err %.3e\n", eh, ey);
+            expect(eh <= 2e-2, "tensor-memory FFN intermediate within 2e-2 of the fp64 oracle");
+            expect(ey <= 2e-2, "tensor-memory FFN output within 2e-2 (rms) of the fp64 oracle");
+        }
         // ---- norm group: residual add -> RMSNorm -> BF16 stage -> two projections, 8 token rows ----
         {
             const uint32_t rows_a = 256, rows_b = 64;
