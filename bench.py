@@ -347,6 +347,30 @@ def config0_probe(ctx):
     ctx.stream.synchronize()
     entry["parity"] = {"rel_error_vs_fp64_oracle": rel_error(bits(projections[0].out), y64), "bound": 2e-2}
     entry["device_status"] = plan.device_status()
+    entry["kernel"] = KERNELS["mma_sync"][0]
+    del projections
+    plan.close()
+    torch.cuda.empty_cache()
+
+    # the same linear on the tensor-memory kernel (weights in the tcgen05 layout)
+    generator.manual_seed(99)
+    torch.randn((TOKENS, cols), device=ctx.device, generator=generator)   # the same draws as above: x, then the planes
+    plan = host.Plan(ctx.stream, host.gemv_tc_scratch_bytes(rows, cols))
+    projections = []
+    for index in range(count):
+        codes, scales = device_planes(torch, generator, rows, cols, ctx.device)
+        weight = host.Nvfp4Sm100Weight.repack_device_planes(ctx.stream, abi.LAYOUT_TCGEN05, rows, cols, codes, scales, synth.GLOBAL_SCALE)
+        projections.append(host.Nvfp4Sm100TcProjection.bind(plan, weight, x))
+        del codes, scales
+    for _ in range(3):
+        sweep()
+    other = ctx.hbm_entry(linear_bytes(rows, cols, TOKENS), linear_bytes(rows, cols, TOKENS), ctx.timed(sweep, rounds) / (rounds * count))
+    projections[0].submit_for_plan()
+    ctx.stream.synchronize()
+    other["parity"] = {"rel_error_vs_fp64_oracle": rel_error(bits(projections[0].out), y64), "bound": 2e-2}
+    other["device_status"] = plan.device_status()
+    other["kernel"] = KERNELS["tensor_memory"][0]
+    entry["tensor_memory_kernel"] = other
     del projections
     plan.close()
     return entry
