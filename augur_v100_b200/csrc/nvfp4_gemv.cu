@@ -1484,7 +1484,7 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_bf16
     view.owner_stream = s->stream;
     view.status_word = reinterpret_cast<uint32_t*>(device->address);
     view.scratch = device->address + kPlanHeaderBytes;
-    view.scratch_bytes = AUGUR_NVFP4_SM100_STATIC_SCRATCH_BYTES - kPlanHeaderBytes;
+    view.scratch_bytes = AUGUR_NVFP4_SM100_STATIC_SCRATCH_BYTES - kPlanHeaderBytes - kPlanTrailerBytes;   // the range a plan claims ends with a trailer
     view.sm_count = device->sm_count;
     // The same checks as the plan-based submit; a shape whose scratch need exceeds the fixed
     // array fails here with INVALID_ARGUMENT before anything is enqueued.

@@ -90,6 +90,9 @@ constexpr uint32_t kHeaderMeeting = 16;    // three arrival counters of the full
 constexpr uint32_t kHeaderEpoch = 19;      // meetings held so far, modulo 3
 constexpr uint32_t kHeaderWave = 20;       // [launch parity][wave]{outputs stored, split stored}
 constexpr uint32_t kHeaderParity = 28;     // launches so far, modulo 2
+// The plan's trailer: [launch parity][wave][CTA] one 64-bit word per CTA with the exponent fields of the largest
+// magnitudes of its outputs, one byte per token row (0: not written yet).
+constexpr uint32_t kMaxCtas = static_cast<uint32_t>(kPlanTrailerBytes / 32);
 constexpr uint32_t kHeaderRowMax = 32;     // [job][token] bits of the row's largest magnitude
 
 // The split activations in global memory (plan scratch): the image the ring stages want, chunk by chunk.
@@ -132,6 +135,7 @@ struct TcParams {
     TcStep step[kMaxSteps];
     uint32_t jobs, steps, tokens;
     uint32_t* header;             // the plan's header words; header[0] is the status word
+    unsigned long long* slots;    // the plan's trailer
 };
 
 __device__ __forceinline__ void tc_load16(uint32_t taddr, uint32_t (&v)[16]) {
@@ -490,9 +494,10 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
     volatile uint32_t* wave_set = input_ready + 1;                                // which half of the wave counters this launch uses
     volatile uint32_t* raised = wave_set + 1;                                     // flags of the last full meeting
     uint32_t* beyond = const_cast<uint32_t*>(raised) + 1;                         // a group of this CTA's share was beyond its row's guessed anchor
+    uint32_t* gathered = beyond + 1;                                              // [worker warp][2]: bytewise maxima of the slots a warp has read
     // full[S] (operand codes landed), empty[S], scales_landed[S], scales_ready[S] (copies to tensor memory issued),
     // acc_full[2], acc_empty[2]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(beyond + 1);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(gathered + 8);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * kStages + 4);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -763,6 +768,8 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
                 }
             }
             workers_sync();
+            // the other half of the trailer belongs to the launch before (complete) and to the launch after
+            for (uint32_t i = blockIdx.x * kWorkers + worker; i < 2 * kMaxCtas; i += gridDim.x * kWorkers) p.slots[(*wave_set ^ 1) * 2 * kMaxCtas + i] = 0;
             share_codes(p, 0, held, largest, collected, first_pair, pair_stride, lane);
             if (share_scales(p, 0, anchor, held, largest, first_pair, pair_stride, lane)) *beyond = 1;   // any lane; a non-finite element is beyond too
             workers_sync();
@@ -835,25 +842,30 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
             const TcPhase& next = p.phase[job.phase];
             const SplitTarget to = split_target(p, st.feeds);
             workers_sync();
-            if (worker < 8) {
-                if (collected[worker]) atomicMax(p.header + kHeaderRowMax + 8 * st.feeds + worker, collected[worker]);
-                collected[worker] = 0;
+            if (st.keeps) {
+                // this CTA's maxima as one word of its own: exponent fields, one byte per token row (40 at least, so the
+                // word is never 0; 251 for a non-finite value). Nothing has to be visible with it, so no release.
+                if (leader) {
+                    unsigned long long word = 0;
+                    for (uint32_t token = 0; token < 8; ++token) {
+                        const uint32_t field = collected[token] >> 23;
+                        word |= static_cast<unsigned long long>(field >= 255 ? 251u : min(max(field, 40u), 250u)) << (8 * token);
+                        collected[token] = 0;
+                    }
+                    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p.slots + (*wave_set * 2 + w) * kMaxCtas + blockIdx.x), "l"(word) : "memory");
+                }
+            } else {
+                if (worker < 8) {
+                    if (collected[worker]) atomicMax(p.header + kHeaderRowMax + 8 * st.feeds + worker, collected[worker]);
+                    collected[worker] = 0;
+                }
+                workers_sync();
+                if (leader) counter_arrive_only(wave + 2 * w);
             }
-            workers_sync();
-            if (leader) counter_arrive_only(wave + 2 * w);
             // While the other CTAs arrive: every warp writes the codes of the 16 columns it has just stored, from
             // registers: lanes 0..15 take token rows 0..3, lanes 16..31 rows 4..7, one group each.
             uint32_t index[4] = {~0u, ~0u, ~0u, ~0u}, bits[4] = {0, 0, 0, 0};
             if (st.keeps && kept_group != ~0u) {
-                // the outputs themselves: nobody in this launch reads them back, and the arrival above, which releases
-                // everything written before it, did not have to wait for them
-                if (lane < 16) {
-                    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(ph.out);
-#pragma unroll
-                    for (uint32_t token = 0; token < 8; ++token) {
-                        if (token < p.tokens) out[static_cast<uint64_t>(token) * ph.out_rows + kept_group * 16 + lane] = __ushort_as_bfloat16(static_cast<unsigned short>(kept[token]));
-                    }
-                }
 #pragma unroll
                 for (uint32_t j = 0; j < 4; ++j) {
                     const uint32_t token = j + ((lane >> 4) << 2);
@@ -863,13 +875,60 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
                     largest[j] = split_codes(to, index[j], bits[j], 0, lane);
                 }
             }
-            if (leader) counter_wait(p, wave + 2 * w, kErrTcWave, abort_flag);
-            workers_sync();
+            if (st.keeps) {
+                // every CTA's word: a worker reads a few until they are written, the warps and then the CTA combine them
+                uint32_t low = 0, high = 0;
+                for (uint32_t first = worker; first < gridDim.x; first += 4 * kWorkers) {
+                    unsigned long long word[4];
+#pragma unroll
+                    for (uint32_t k = 0; k < 4; ++k) {   // all at once; one that is not written yet is read again below
+                        word[k] = 0x2828282828282828ull;
+                        if (first + k * kWorkers < gridDim.x) {
+                            asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(word[k]) : "l"(p.slots + (*wave_set * 2 + w) * kMaxCtas + first + k * kWorkers) : "memory");
+                        }
+                    }
+#pragma unroll
+                    for (uint32_t k = 0; k < 4; ++k) {
+                        for (uint32_t spin = 0; word[k] == 0;) {
+                            asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(word[k]) : "l"(p.slots + (*wave_set * 2 + w) * kMaxCtas + first + k * kWorkers) : "memory");
+                            if (word[k] == 0 && (++spin > kGridWaitLimit || ((spin & 255u) == 255u && *abort_flag))) {
+                                *abort_flag = 1;
+                                atomicCAS(p.header, 0u, kErrTcWave);
+                                break;
+                            }
+                        }
+                        low = __vmaxu4(low, static_cast<uint32_t>(word[k]));
+                        high = __vmaxu4(high, static_cast<uint32_t>(word[k] >> 32));
+                    }
+                }
+#pragma unroll
+                for (uint32_t offset = 16; offset; offset >>= 1) {
+                    low = __vmaxu4(low, __shfl_xor_sync(0xffffffffu, low, offset));
+                    high = __vmaxu4(high, __shfl_xor_sync(0xffffffffu, high, offset));
+                }
+                if (lane == 0) {
+                    gathered[(warp - 2) * 2] = low;
+                    gathered[(warp - 2) * 2 + 1] = high;
+                }
+                workers_sync();
+                if (worker < 8) {
+                    uint32_t field = 0;
+                    for (uint32_t k = 0; k < 4; ++k) field = max(field, (gathered[k * 2 + (worker >> 2)] >> (8 * (worker & 3))) & 0xffu);
+                    // term 0 of the row has the global scale 2^(A - 155), term 7 2^(A - 134): all normal f32 numbers
+                    const uint32_t a = min(field, 250u);
+                    term_scale[8 * st.feeds + worker] = field > 250 ? __uint_as_float(0x7fc00000u) : __uint_as_float((a - 28) << 23);
+                    anchor[8 * st.feeds + worker] = a;
+                }
+                workers_sync();
+            } else {
+                if (leader) counter_wait(p, wave + 2 * w, kErrTcWave, abort_flag);
+                workers_sync();
+            }
             if (*abort_flag) {
                 alive = false;
                 break;
             }
-            job_scales(p, st.feeds, worker, term_scale, anchor);
+            if (!st.keeps) job_scales(p, st.feeds, worker, term_scale, anchor);
             if (st.keeps) {
                 if (kept_group != ~0u) {
 #pragma unroll
@@ -884,6 +943,17 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
             }
             workers_sync();
             if (leader) counter_arrive_only(wave + 2 * w + 1);
+            if (st.keeps && kept_group != ~0u) {
+                // the outputs themselves, last: nobody in this launch reads them back, and neither arrival above had to
+                // wait for them
+                if (lane < 16) {
+                    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(ph.out);
+#pragma unroll
+                    for (uint32_t token = 0; token < 8; ++token) {
+                        if (token < p.tokens) out[static_cast<uint64_t>(token) * ph.out_rows + kept_group * 16 + lane] = __ushort_as_bfloat16(static_cast<unsigned short>(kept[token]));
+                    }
+                }
+            }
         }
         // the next launch goes on counting meetings where this one stopped, with the other half of the wave counters
         if (alive && leader && blockIdx.x == 0) {
@@ -943,11 +1013,11 @@ TcProgram tc_program(const augur_cuda_nvfp4_sm100_gemv_args_v1* a, const augur_c
     g.ctas = slots;
     g.contributors[0] = 1;
     uint32_t s = 0;
-    g.step[s++] = TcStep{0, 0, 0, first, 0, kb_a, 1, 0, 1, first <= slots ? 1u : 0u};
+    g.step[s++] = TcStep{0, 0, 0, first, 0, kb_a, 1, 0, 1, first <= slots && slots <= kMaxCtas ? 1u : 0u};
     g.job[1] = TcJob{1, 0, first * 4};
     g.jobs = 2;
     if (first < tiles_a) {
-        g.step[s++] = TcStep{0, 0, first, tiles_a - first, 0, kb_a, 1, 0, 2, tiles_a - first <= slots ? 1u : 0u};
+        g.step[s++] = TcStep{0, 0, first, tiles_a - first, 0, kb_a, 1, 0, 2, tiles_a - first <= slots && slots <= kMaxCtas ? 1u : 0u};
         g.job[2] = TcJob{1, first * 4, b->cols / 16 - first * 4};
         g.jobs = 3;
     }
@@ -1055,6 +1125,7 @@ augur_cuda_result_v1 launch_tc(augur_cuda_stream_t s, const augur_cuda_nvfp4_sm1
     TcParams p{};
     p.tokens = a->tokens;
     p.header = plan->status_word;
+    p.slots = reinterpret_cast<unsigned long long*>(plan->scratch + plan->scratch_bytes);
     p.jobs = g.jobs;
     p.steps = g.steps;
     for (uint32_t j = 0; j < g.jobs; ++j) p.job[j] = g.job[j];

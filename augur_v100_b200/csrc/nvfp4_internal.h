@@ -38,6 +38,8 @@ namespace augur_sm100 {
 
 constexpr uint32_t kPlanMagic = 0x4e56'4634u;  // "NVF4"
 constexpr uint64_t kPlanHeaderBytes = 256;     // status word + padding in front of the scratch
+constexpr uint64_t kPlanTrailerBytes = 16384;  // behind the scratch, outside what `scratch_bytes` counts: words that only the
+                                               // tensor-memory small-token kernel writes (one per CTA, four sets)
 
 struct Range {
     uint64_t address, bytes, alignment;

@@ -86,7 +86,7 @@ bool plan_ok(const augur_cuda_nvfp4_sm100_plan_v1* plan, int32_t ordinal, augur_
 }
 
 Range plan_scratch_range(const augur_cuda_nvfp4_sm100_plan_v1* plan) {
-    return {reinterpret_cast<uint64_t>(plan->status_word), plan->scratch_bytes + kPlanHeaderBytes, 256};
+    return {reinterpret_cast<uint64_t>(plan->status_word), plan->scratch_bytes + kPlanHeaderBytes + kPlanTrailerBytes, 256};
 }
 
 bool consume_injected_fault() {
@@ -195,14 +195,14 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_plan_crea
     if (e != cudaSuccess) return make_result(AUGUR_CUDA_STATUS_RUNTIME_FAILURE, e);
     const uint64_t rounded = (scratch_len_bytes + 255) / 256 * 256;
     void* memory = nullptr;
-    e = cudaMalloc(&memory, rounded + kPlanHeaderBytes);
+    e = cudaMalloc(&memory, rounded + kPlanHeaderBytes + kPlanTrailerBytes);
     if (e != cudaSuccess) {
         cudaGetLastError();
         return make_result(AUGUR_CUDA_STATUS_OUT_OF_MEMORY, e);
     }
     count_allocation();
     // Arrival counters and the status word must start at zero; kernels leave them at zero.
-    e = cudaMemsetAsync(memory, 0, rounded + kPlanHeaderBytes, stream->stream);
+    e = cudaMemsetAsync(memory, 0, rounded + kPlanHeaderBytes + kPlanTrailerBytes, stream->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(stream->stream);
     auto* plan = e == cudaSuccess ? new (std::nothrow) augur_cuda_nvfp4_sm100_plan_v1{} : nullptr;
     if (!plan) {
@@ -262,8 +262,9 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_plan_devi
     }
     if (e == cudaSuccess) e = cudaStreamSynchronize(plan->owner_stream);
     if (e == cudaSuccess && *out_status != 0) {
-        // a wait ran out: the launch left its meeting counters and row maxima (header words 16..63) half used
+        // a wait ran out: the launch left its meeting counters and row maxima (header words 16..63, trailer) half used
         e = cudaMemsetAsync(plan->status_word + 16, 0, (64 - 16) * sizeof(uint32_t), plan->owner_stream);
+        if (e == cudaSuccess) e = cudaMemsetAsync(plan->scratch + plan->scratch_bytes, 0, kPlanTrailerBytes, plan->owner_stream);
         if (e == cudaSuccess) e = cudaStreamSynchronize(plan->owner_stream);
     }
     return e == cudaSuccess ? ok() : make_result(AUGUR_CUDA_STATUS_COMPLETION_FAILURE, e);
