@@ -242,9 +242,16 @@ __device__ __forceinline__ SplitTarget split_target(const TcParams& p, uint32_t 
     return SplitTarget{ph.split, static_cast<uint32_t>(split_code_bytes(ph.cols)), job.group0, job.groups, p.tokens};
 }
 
-__device__ __noinline__ uint32_t split_codes(const SplitTarget to, uint32_t index, uint32_t bits, uint32_t drop, uint32_t lane) {
-    const bool active = index < to.tokens * to.groups;
-    const uint32_t token = active ? index / to.groups : 0, group = active ? to.group0 + (index - token * to.groups) : 0;
+// A group of a job by its index, as (token row, group of the row); the token row is ~0 past the job's end.
+__device__ __forceinline__ uint2 group_of(const SplitTarget& to, uint32_t index) {
+    if (index >= to.tokens * to.groups) return make_uint2(~0u, 0u);
+    const uint32_t token = index / to.groups;
+    return make_uint2(token, to.group0 + (index - token * to.groups));
+}
+
+__device__ __noinline__ uint32_t split_codes(const SplitTarget to, uint2 where, uint32_t bits, uint32_t drop, uint32_t lane) {
+    const bool active = where.x != ~0u;
+    const uint32_t token = active ? where.x : 0, group = where.y;
     const uint32_t magnitude = bits & 0x7fffu, negative = (bits >> 15) & 1u;
     uint32_t largest = max(magnitude, __shfl_xor_sync(0xffffffffu, magnitude, 8));
     largest = max(largest, __shfl_xor_sync(0xffffffffu, largest, 4));
@@ -287,13 +294,13 @@ __device__ __noinline__ uint32_t split_codes(const SplitTarget to, uint32_t inde
 // Second half, with the row's anchor: the group's block scale 2^q, q = G + 8 - A. A group more than 2^17 below its
 // row's largest magnitude keeps 2^-9 and has its codes redone with that many low bits fewer (rare). True if the
 // group is larger than the anchor provides for (an anchor that was guessed).
-__device__ __noinline__ bool split_scales(const SplitTarget to, const uint32_t* anchor, uint32_t index, uint32_t bits, uint32_t largest,
+__device__ __noinline__ bool split_scales(const SplitTarget to, const uint32_t* anchor, uint2 where, uint32_t bits, uint32_t largest,
                                           uint32_t lane) {
-    const bool active = index < to.tokens * to.groups;
-    const uint32_t token = active ? index / to.groups : 0, group = active ? to.group0 + (index - token * to.groups) : 0;
+    const bool active = where.x != ~0u;
+    const uint32_t token = active ? where.x : 0, group = where.y;
     const int q = max(static_cast<int>(largest >> 7), 1) + 8 - static_cast<int>(anchor[token]);
     const uint32_t drop = active && q < -9 ? static_cast<uint32_t>(-9 - q) : 0u;
-    if (__any_sync(0xffffffffu, drop != 0)) split_codes(to, index, bits, drop, lane);
+    if (__any_sync(0xffffffffu, drop != 0)) split_codes(to, where, bits, drop, lane);
     if (active && (lane & 8) == 0) {
         const int clamped = min(max(q, -9), 8);
         const uint32_t scale_code = clamped >= -6 ? static_cast<uint32_t>(clamped + 7) << 3 : 1u << (clamped + 9);
@@ -332,7 +339,7 @@ __device__ __forceinline__ void share_codes(const TcParams& p, uint32_t job_inde
         largest[j] = 0;
         if (warp_first + j * pair_stride < groups) {
             const uint32_t index = first_pair + j * pair_stride;
-            largest[j] = split_codes(to, index, held[j], 0, lane);
+            largest[j] = split_codes(to, group_of(to, index), held[j], 0, lane);
             if (collected && (lane & 15) == 0 && largest[j]) atomicMax(&collected[index / job.groups], largest[j] << 16);   // zero past the end
         }
     }
@@ -355,11 +362,11 @@ __device__ __forceinline__ bool share_scales(const TcParams& p, uint32_t job_ind
     const uint32_t groups = p.tokens * job.groups, warp_first = first_pair - (lane >> 4);
 #pragma unroll
     for (uint32_t j = 0; j < kHeld; ++j) {
-        if (warp_first + j * pair_stride < groups) beyond |= split_scales(to, anchor + 8 * job_index, first_pair + j * pair_stride, held[j], largest[j], lane);
+        if (warp_first + j * pair_stride < groups) beyond |= split_scales(to, anchor + 8 * job_index, group_of(to, first_pair + j * pair_stride), held[j], largest[j], lane);
     }
     for (uint32_t index = first_pair + kHeld * pair_stride; index - (lane >> 4) < groups; index += pair_stride) {
         const uint32_t bits = load_element(ph, job, p.tokens, index, lane);
-        beyond |= split_scales(to, anchor + 8 * job_index, index, bits, split_codes(to, index, bits, 0, lane), lane);
+        beyond |= split_scales(to, anchor + 8 * job_index, group_of(to, index), bits, split_codes(to, group_of(to, index), bits, 0, lane), lane);
     }
     return beyond;
 }
@@ -864,15 +871,16 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
             }
             // While the other CTAs arrive: every warp writes the codes of the 16 columns it has just stored, from
             // registers: lanes 0..15 take token rows 0..3, lanes 16..31 rows 4..7, one group each.
-            uint32_t index[4] = {~0u, ~0u, ~0u, ~0u}, bits[4] = {0, 0, 0, 0};
+            uint2 where[4];
+            uint32_t bits[4] = {0, 0, 0, 0};
             if (st.keeps && kept_group != ~0u) {
 #pragma unroll
                 for (uint32_t j = 0; j < 4; ++j) {
                     const uint32_t token = j + ((lane >> 4) << 2);
                     const uint32_t theirs = __shfl_sync(0xffffffffu, kept[4 + j], lane & 15);
-                    index[j] = token < p.tokens ? token * job.groups + (kept_group - job.group0) : ~0u;
+                    where[j] = make_uint2(token < p.tokens ? token : ~0u, kept_group);
                     bits[j] = lane < 16 ? kept[j] : theirs;
-                    largest[j] = split_codes(to, index[j], bits[j], 0, lane);
+                    largest[j] = split_codes(to, where[j], bits[j], 0, lane);
                 }
             }
             if (st.keeps) {
@@ -932,7 +940,7 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
             if (st.keeps) {
                 if (kept_group != ~0u) {
 #pragma unroll
-                    for (uint32_t j = 0; j < 4; ++j) split_scales(to, anchor + 8 * st.feeds, index[j], bits[j], largest[j], lane);
+                    for (uint32_t j = 0; j < 4; ++j) split_scales(to, anchor + 8 * st.feeds, where[j], bits[j], largest[j], lane);
                 }
             } else {
                 // items of several CTAs per tile, or several items per CTA: the outputs are read back, every CTA a share
