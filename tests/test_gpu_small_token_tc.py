@@ -212,3 +212,77 @@ def test_config1_full_mlp_block_as_one_launch(ctx, tokens):
         assert np.array_equal(bits_from_torch_bf16(program.out), first)
     finally:
         plan.close()
+
+
+def test_more_gate_up_tiles_than_ctas_runs_in_two_waves(ctx):
+    # 320 gate|up tiles on at most 2 CTAs per SM: the first wave's outputs are split while the second wave streams,
+    # and the down product is cut into the k range each wave feeds (separate scales, partial sums added in f32)
+    host = ctx["host"]
+    hidden, inter, tokens = 256, 20480, 8
+    gate = synth.make_weight(30, 92, "gate", inter, hidden)
+    up = synth.make_weight(30, 92, "up", inter, hidden)
+    down = synth.make_weight(30, 92, "down", hidden, inter)
+    gate_up_w = host.upload_gate_up_interleaved(ctx["stream"], inter, hidden, *gate, *up)
+    down_w = host.Nvfp4Sm100Weight.upload_checkpoint_nvfp4(ctx["stream"], abi.LAYOUT_TCGEN05, hidden, inter, *down)
+    x_bits = synth.f32_to_bf16_bits(np.random.default_rng(31).standard_normal((tokens, hidden)).astype(np.float32) * 4.0)
+    x = torch_bf16_from_bits(x_bits, ctx["device"])
+    plan = host.Plan(ctx["stream"], host.mlp_tc_scratch_bytes(hidden, inter))
+    try:
+        program = host.Nvfp4Sm100TcFfnProgram.bind(plan, gate_up_w, down_w, x)
+        program.submit_for_plan()
+        ctx["stream"].synchronize()
+        assert plan.device_status() == 0, hex(plan.device_status())
+        first = bits_from_torch_bf16(program.out).copy()
+        threads = oracle.max_threads()
+        h64, _ = oracle.mlp_f64(gate, up, down, hidden, inter, x_bits, threads=threads)
+        h_bits = bits_from_torch_bf16(program.intermediate)
+        assert rel_error(h_bits, h64) <= TOLERANCE
+        y64_from_h = oracle.linear_f64(down[0], down[1], down[2], hidden, inter, h_bits, threads=threads)
+        assert rel_error(first, y64_from_h) <= TOLERANCE
+        for _ in range(2):
+            program.out.zero_()
+            program.submit_for_plan()
+            ctx["stream"].synchronize()
+            assert np.array_equal(bits_from_torch_bf16(program.out), first)
+        assert plan.device_status() == 0
+    finally:
+        plan.close()
+
+
+def test_programs_of_different_shapes_share_a_plan(ctx):
+    # the counters, maxima and per-CTA words a launch leaves in the plan are ready for whatever launch comes next:
+    # a linear in k parts, the MLP block, a linear in whole tiles, in turn, each repeating its own bits
+    host = ctx["host"]
+    hidden, inter, tokens = 1024, 2176, 8
+    gate = synth.make_weight(40, 93, "gate", inter, hidden)
+    up = synth.make_weight(40, 93, "up", inter, hidden)
+    down = synth.make_weight(40, 93, "down", hidden, inter)
+    wide = synth.make_weight(41, 93, "wide", 128 * 300, 256)
+    gate_up_w = host.upload_gate_up_interleaved(ctx["stream"], inter, hidden, *gate, *up)
+    down_w = host.Nvfp4Sm100Weight.upload_checkpoint_nvfp4(ctx["stream"], abi.LAYOUT_TCGEN05, hidden, inter, *down)
+    wide_w = host.Nvfp4Sm100Weight.upload_checkpoint_nvfp4(ctx["stream"], abi.LAYOUT_TCGEN05, 128 * 300, 256, *wide)
+    rng = np.random.default_rng(42)
+    x = torch_bf16_from_bits(synth.f32_to_bf16_bits(rng.standard_normal((tokens, hidden)).astype(np.float32)), ctx["device"])
+    x_inter = torch_bf16_from_bits(synth.f32_to_bf16_bits(rng.standard_normal((tokens, inter)).astype(np.float32)), ctx["device"])
+    x_narrow = torch_bf16_from_bits(synth.f32_to_bf16_bits(rng.standard_normal((3, 256)).astype(np.float32)), ctx["device"])
+    need = max(host.mlp_tc_scratch_bytes(hidden, inter), host.gemv_tc_scratch_bytes(128 * 300, 256))
+    plan = host.Plan(ctx["stream"], need)
+    try:
+        programs = [host.Nvfp4Sm100TcProjection.bind(plan, down_w, x_inter),          # 8 tiles in k parts
+                    host.Nvfp4Sm100TcFfnProgram.bind(plan, gate_up_w, down_w, x),     # the block
+                    host.Nvfp4Sm100TcProjection.bind(plan, wide_w, x_narrow)]         # 300 whole tiles, 3 token rows
+        firsts = []
+        for program in programs:
+            program.submit_for_plan()
+            ctx["stream"].synchronize()
+            firsts.append(bits_from_torch_bf16(program.out).copy())
+        for order in ((1, 0, 2), (2, 1, 1, 0), (0, 2, 1)):
+            for index in order:
+                programs[index].out.zero_()
+                programs[index].submit_for_plan()
+            ctx["stream"].synchronize()
+            assert plan.device_status() == 0, hex(plan.device_status())
+            for index in set(order):
+                assert np.array_equal(bits_from_torch_bf16(programs[index].out), firsts[index]), index
+    finally:
+        plan.close()
