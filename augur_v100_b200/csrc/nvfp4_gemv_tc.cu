@@ -378,6 +378,7 @@ __device__ __forceinline__ void finish_rows(const TcPhase& ph, uint32_t tokens, 
         // 32 physical rows = 16 gate rows (lanes 0..15) and the matching 16 up rows (lanes 16..31)
         __nv_bfloat16* out = static_cast<__nv_bfloat16*>(ph.out);
         const uint32_t index = (tile * kTileM + quadrant * 32) / 2 + (lane & 15);
+        uint32_t fields_low = 0, fields_high = 0;   // exponent fields of this lane's outputs, a byte per token row
 #pragma unroll
         for (uint32_t token = 0; token < 8; ++token) {
             const float up = __shfl_sync(0xffffffffu, y[token], (lane & 15) + 16) * ph.global_b;
@@ -388,15 +389,26 @@ __device__ __forceinline__ void finish_rows(const TcPhase& ph, uint32_t tokens, 
                 magnitude = static_cast<uint32_t>(__bfloat16_as_ushort(h) & 0x7fffu) << 16;
                 if (kept) {
                     kept[token] = __bfloat16_as_ushort(h);   // stored by the caller, behind its arrival with the maxima
+                    (token < 4 ? fields_low : fields_high) |= (magnitude >> 23) << (8 * (token & 3));
                 } else {
                     out[static_cast<uint64_t>(token) * ph.out_rows + index] = h;
                 }
             }
-            if (collected) {
+            if (collected && !kept) {
                 // a later step splits these values: it needs every token row's largest magnitude
                 magnitude = __reduce_max_sync(0xffffffffu, magnitude);
                 if (lane == 0 && magnitude) atomicMax(&collected[token], magnitude);
             }
+        }
+        if (kept) {
+            // the caller only needs the exponent fields, the largest per token row over this warp: two words
+#pragma unroll
+            for (uint32_t offset = 8; offset; offset >>= 1) {
+                fields_low = __vmaxu4(fields_low, __shfl_xor_sync(0xffffffffu, fields_low, offset));
+                fields_high = __vmaxu4(fields_high, __shfl_xor_sync(0xffffffffu, fields_high, offset));
+            }
+            kept[8] = fields_low;
+            kept[9] = fields_high;
         }
         return;
     }
@@ -805,7 +817,7 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
             const TcStep& st = p.step[s];
             const TcPhase& ph = p.phase[st.phase];
             uint32_t* gather = st.feeds ? collected : nullptr;
-            uint32_t kept[8] = {0, 0, 0, 0, 0, 0, 0, 0};    // lanes 0..15: the outputs of this warp's 16 columns, as stored
+            uint32_t kept[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};    // lanes 0..15: the outputs of this warp's 16 columns, as stored; their exponent fields
             uint32_t kept_group = ~0u;                      // their 16-element group in the rows of the next product's input
             // ---- epilogues of this CTA's items of the step ----
             const uint32_t items = st.tiles * st.parts;
@@ -848,6 +860,10 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
             const TcJob& job = p.job[st.feeds];
             const TcPhase& next = p.phase[job.phase];
             const SplitTarget to = split_target(p, st.feeds);
+            if (st.keeps && lane == 0) {
+                gathered[(warp - 2) * 2] = kept[8];
+                gathered[(warp - 2) * 2 + 1] = kept[9];
+            }
             workers_sync();
             if (st.keeps) {
                 // this CTA's maxima as one word of its own: exponent fields, one byte per token row (40 at least, so the
@@ -855,12 +871,13 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
                 if (leader) {
                     unsigned long long word = 0;
                     for (uint32_t token = 0; token < 8; ++token) {
-                        const uint32_t field = collected[token] >> 23;
+                        uint32_t field = 0;
+                        for (uint32_t k = 0; k < 4; ++k) field = max(field, (gathered[k * 2 + (token >> 2)] >> (8 * (token & 3))) & 0xffu);
                         word |= static_cast<unsigned long long>(field >= 255 ? 251u : min(max(field, 40u), 250u)) << (8 * token);
-                        collected[token] = 0;
                     }
                     asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p.slots + (*wave_set * 2 + w) * kMaxCtas + blockIdx.x), "l"(word) : "memory");
                 }
+                workers_sync();   // `gathered` is used again below
             } else {
                 if (worker < 8) {
                     if (collected[worker]) atomicMax(p.header + kHeaderRowMax + 8 * st.feeds + worker, collected[worker]);
