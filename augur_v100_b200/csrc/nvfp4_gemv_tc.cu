@@ -62,7 +62,7 @@ constexpr uint32_t kStageActSf = kStageActCodes + kChunkBytes;
 constexpr uint32_t kStageBytes = kStageActSf + kStageSfBytes;               // 28 KB
 constexpr uint32_t kStages = 4;                        // per CTA; two CTAs share an SM
 constexpr uint32_t kCtasPerSm = 2;                     // two rings consumed in order stall less on a late stage than one of twice the depth
-constexpr uint32_t kThreads = 288;                     // warp 0 TMA of weights, 1 MMA, 2..5 split and epilogue, 6 and 8 scale copies, 7 TMA of activations
+constexpr uint32_t kThreads = 416;                     // warp 0 TMA of weights, 1 MMA, 2..9 split and epilogue, 10 and 12 scale copies, 11 TMA of activations
 constexpr uint32_t kSmemBytes = kStages * kStageBytes + 512 /*small state*/;   // the stages start the (1024-byte aligned) window
 constexpr uint32_t kTmemAcc = 0;                       // two accumulators of 64 columns
 constexpr uint32_t kTmemSfWeight = 128;                // 16 columns per ring stage
@@ -74,7 +74,7 @@ static_assert(kCtasPerSm * (kSmemBytes + 1024) <= 228 * 1024, "two CTAs per SM, 
 static_assert(kTerms == 8, "the digit transposition is 8 lanes x 8 nibbles");
 static_assert(kStageBytes % 1024 == 0 && kStageActCodes % 1024 == 0, "swizzled operand tiles are 1024-byte aligned");
 constexpr uint32_t kSlotFloats = 256;                  // one partial: 32 rows x 8 tokens
-constexpr uint32_t kWorkers = 128;                     // the four split / epilogue warps
+constexpr uint32_t kWorkers = 256;                     // the eight split / epilogue warps: two per quarter of the accumulator's rows, four token rows each
 constexpr uint32_t kMaxPhases = 2, kMaxJobs = 3, kMaxSteps = 4;
 constexpr uint32_t kGridWaitLimit = 1u << 22;          // polls of a counter (a fraction of a microsecond each) before giving up
 constexpr uint32_t kHeld = 4;                          // elements a lane keeps in registers between the scan and the split
@@ -108,7 +108,7 @@ struct TcPhase {
     uint8_t* split;               // the split activations (layout above)
     void* out;
     float* partials;              // [tile * 4 + quadrant][contributor][32 rows][8 tokens]
-    uint32_t* counters;           // [tile * 4 + quadrant], zero between launches
+    uint32_t* counters;           // [tile * 4 + quadrant][half of the token rows], zero between launches
     uint32_t rows;                // physical weight rows (SwiGLU: gate and up interleaved by 16)
     uint32_t out_rows;            // output width
     uint32_t cols, epilogue;
@@ -146,7 +146,10 @@ __device__ __forceinline__ void tc_load16(uint32_t taddr, uint32_t (&v)[16]) {
         : "r"(taddr)
         : "memory");
 }
-__device__ __forceinline__ void workers_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void tc_load4(uint32_t taddr, uint32_t (&v)[4]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void workers_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 // ---- counters between CTAs (thread `leader` of the four worker warps speaks for its CTA) ----------------------
 __device__ __forceinline__ uint32_t counter_arrive(uint32_t* counter) {
@@ -371,25 +374,27 @@ __device__ __forceinline__ bool share_scales(const TcParams& p, uint32_t job_ind
     return beyond;
 }
 
-// Finished sums of 32 weight rows (lane = row) for the 8 tokens: scale, activation, rounding, store.
-__device__ __forceinline__ void finish_rows(const TcPhase& ph, uint32_t tokens, uint32_t tile, uint32_t quadrant, uint32_t lane,
-                                            const float (&y)[8], uint32_t* collected, uint32_t* kept) {
+// Finished sums of 32 weight rows (lane = row) for the token rows token0 .. token0 + 3: scale, activation, rounding,
+// store. `kept` (SwiGLU): the outputs stay with the caller, [0..3] as stored, [4] their exponent fields, a byte per row.
+__device__ __forceinline__ void finish_rows(const TcPhase& ph, uint32_t tokens, uint32_t tile, uint32_t quadrant, uint32_t token0, uint32_t lane,
+                                            const float (&y)[4], uint32_t* collected, uint32_t* kept) {
     if (ph.epilogue == AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16) {
         // 32 physical rows = 16 gate rows (lanes 0..15) and the matching 16 up rows (lanes 16..31)
         __nv_bfloat16* out = static_cast<__nv_bfloat16*>(ph.out);
         const uint32_t index = (tile * kTileM + quadrant * 32) / 2 + (lane & 15);
-        uint32_t fields_low = 0, fields_high = 0;   // exponent fields of this lane's outputs, a byte per token row
+        uint32_t fields = 0;   // exponent fields of this lane's outputs
 #pragma unroll
-        for (uint32_t token = 0; token < 8; ++token) {
-            const float up = __shfl_sync(0xffffffffu, y[token], (lane & 15) + 16) * ph.global_b;
-            const float gate = y[token] * ph.global_a;
+        for (uint32_t j = 0; j < 4; ++j) {
+            const uint32_t token = token0 + j;
+            const float up = __shfl_sync(0xffffffffu, y[j], (lane & 15) + 16) * ph.global_b;
+            const float gate = y[j] * ph.global_a;
             uint32_t magnitude = 0;
             if (lane < 16 && token < tokens) {
                 const __nv_bfloat16 h = __float2bfloat16_rn(__fdividef(gate, 1.0f + __expf(-gate)) * up);   // a few ulp of f32, far below the rounding
                 magnitude = static_cast<uint32_t>(__bfloat16_as_ushort(h) & 0x7fffu) << 16;
                 if (kept) {
-                    kept[token] = __bfloat16_as_ushort(h);   // stored by the caller, behind its arrival with the maxima
-                    (token < 4 ? fields_low : fields_high) |= (magnitude >> 23) << (8 * (token & 3));
+                    kept[j] = __bfloat16_as_ushort(h);   // stored by the caller, behind its arrival with the maxima
+                    fields |= (magnitude >> 23) << (8 * j);
                 } else {
                     out[static_cast<uint64_t>(token) * ph.out_rows + index] = h;
                 }
@@ -401,22 +406,19 @@ __device__ __forceinline__ void finish_rows(const TcPhase& ph, uint32_t tokens, 
             }
         }
         if (kept) {
-            // the caller only needs the exponent fields, the largest per token row over this warp: two words
+            // the caller only needs the exponent fields, the largest per token row over this warp
 #pragma unroll
-            for (uint32_t offset = 8; offset; offset >>= 1) {
-                fields_low = __vmaxu4(fields_low, __shfl_xor_sync(0xffffffffu, fields_low, offset));
-                fields_high = __vmaxu4(fields_high, __shfl_xor_sync(0xffffffffu, fields_high, offset));
-            }
-            kept[8] = fields_low;
-            kept[9] = fields_high;
+            for (uint32_t offset = 8; offset; offset >>= 1) fields = __vmaxu4(fields, __shfl_xor_sync(0xffffffffu, fields, offset));
+            kept[4] = fields;
         }
         return;
     }
     const uint32_t row = tile * kTileM + quadrant * 32 + lane;
 #pragma unroll
-    for (uint32_t token = 0; token < 8; ++token) {
+    for (uint32_t j = 0; j < 4; ++j) {
+        const uint32_t token = token0 + j;
         if (token < tokens) {
-            const float value = y[token] * ph.global_a;
+            const float value = y[j] * ph.global_a;
             if (ph.epilogue == AUGUR_NVFP4_SM100_EPILOGUE_LINEAR_F32) {
                 static_cast<float*>(ph.out)[static_cast<uint64_t>(token) * ph.out_rows + row] = value;
             } else {
@@ -426,48 +428,44 @@ __device__ __forceinline__ void finish_rows(const TcPhase& ph, uint32_t tokens, 
     }
 }
 
-// This CTA's share of 32 rows of `tile`: finished here if tiles are whole, else handed over as contributor
-// `slot`; the last of the arrivals adds all shares in slot order. Whole warps call this.
-__device__ __forceinline__ void contribute_rows(const TcPhase& ph, uint32_t tokens, uint32_t tile, uint32_t quadrant, uint32_t slot,
-                                                uint32_t lane, const float (&y)[8], uint32_t* collected, uint32_t* kept) {
+// This warp's share (four token rows) of 32 rows of `tile`: finished here if tiles are whole, else handed over as
+// contributor `slot`; the last of the arrivals adds all shares in slot order. Whole warps call this.
+__device__ __forceinline__ void contribute_rows(const TcPhase& ph, uint32_t tokens, uint32_t tile, uint32_t quadrant, uint32_t token0, uint32_t slot,
+                                                uint32_t lane, const float (&y)[4], uint32_t* collected, uint32_t* kept) {
     if (ph.contributors == 1) {
-        finish_rows(ph, tokens, tile, quadrant, lane, y, collected, kept);
+        finish_rows(ph, tokens, tile, quadrant, token0, lane, y, collected, kept);
         return;
     }
     const uint32_t group = tile * 4 + quadrant;
     float* slots = ph.partials + static_cast<uint64_t>(group) * ph.contributors * kSlotFloats;
-    float4* mine = reinterpret_cast<float4*>(slots + static_cast<uint64_t>(slot) * kSlotFloats) + lane * 2;
-    mine[0] = make_float4(y[0], y[1], y[2], y[3]);
-    mine[1] = make_float4(y[4], y[5], y[6], y[7]);
+    float4* mine = reinterpret_cast<float4*>(slots + static_cast<uint64_t>(slot) * kSlotFloats) + lane * 2 + (token0 >> 2);
+    *mine = make_float4(y[0], y[1], y[2], y[3]);
     __syncwarp();
     // the arrival releases this warp's share and, for the last arriver, acquires the others'
     uint32_t arrived = 0;
-    if (lane == 0) arrived = counter_arrive(&ph.counters[group]);
+    if (lane == 0) arrived = counter_arrive(&ph.counters[group * 2 + (token0 >> 2)]);
     arrived = __shfl_sync(0xffffffffu, arrived, 0);
     __syncwarp();
     if (arrived + 1 != ph.contributors) return;
-    float sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (uint32_t s0 = 0; s0 < ph.contributors; s0 += 4) {
-        float4 a[4], b[4];
+    float sum[4] = {0, 0, 0, 0};
+    for (uint32_t s0 = 0; s0 < ph.contributors; s0 += 8) {
+        float4 a[8];
 #pragma unroll
-        for (uint32_t j = 0; j < 4; ++j) {
-            a[j] = b[j] = make_float4(0, 0, 0, 0);
+        for (uint32_t j = 0; j < 8; ++j) {
+            a[j] = make_float4(0, 0, 0, 0);
             if (s0 + j < ph.contributors) {
-                const float4* from = reinterpret_cast<const float4*>(slots + static_cast<uint64_t>(s0 + j) * kSlotFloats) + lane * 2;
-                a[j] = __ldcg(from);
-                b[j] = __ldcg(from + 1);
+                a[j] = __ldcg(reinterpret_cast<const float4*>(slots + static_cast<uint64_t>(s0 + j) * kSlotFloats) + lane * 2 + (token0 >> 2));
             }
         }
 #pragma unroll
-        for (uint32_t j = 0; j < 4; ++j) {
+        for (uint32_t j = 0; j < 8; ++j) {
             if (s0 + j < ph.contributors) {
                 sum[0] += a[j].x; sum[1] += a[j].y; sum[2] += a[j].z; sum[3] += a[j].w;
-                sum[4] += b[j].x; sum[5] += b[j].y; sum[6] += b[j].z; sum[7] += b[j].w;
             }
         }
     }
-    finish_rows(ph, tokens, tile, quadrant, lane, sum, collected, nullptr);
-    if (lane == 0) ph.counters[group] = 0;   // clean for the next launch
+    finish_rows(ph, tokens, tile, quadrant, token0, lane, sum, collected, nullptr);
+    if (lane == 0) ph.counters[group * 2 + (token0 >> 2)] = 0;   // clean for the next launch
 }
 
 // A CTA's ring stages in the order it streams them: over the steps, over its items blockIdx.x,
@@ -513,10 +511,10 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
     volatile uint32_t* wave_set = input_ready + 1;                                // which half of the wave counters this launch uses
     volatile uint32_t* raised = wave_set + 1;                                     // flags of the last full meeting
     uint32_t* beyond = const_cast<uint32_t*>(raised) + 1;                         // a group of this CTA's share was beyond its row's guessed anchor
-    uint32_t* gathered = beyond + 1;                                              // [worker warp][2]: bytewise maxima of the slots a warp has read
+    uint32_t* gathered = beyond + 1;                                              // [worker warp][2]: bytewise maxima of what a warp has seen
     // full[S] (operand codes landed), empty[S], scales_landed[S], scales_ready[S] (copies to tensor memory issued),
     // acc_full[2], acc_empty[2]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(gathered + 8);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(gathered + 16);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * kStages + 4);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -569,7 +567,7 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
         }
         for (uint32_t b = 0; b < 2; ++b) {
             mbar_init(bar_acc_full + 8 * b, 1);
-            mbar_init(bar_acc_empty + 8 * b, 4);   // one arrival per epilogue warp
+            mbar_init(bar_acc_empty + 8 * b, 8);   // one arrival per epilogue warp
         }
         *abort_flag = 0;
         *input_ready = 0;
@@ -606,7 +604,7 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
             ++weights_issued;
             weights_left = cursor_next(p, weights_at);
         }
-    } else if (warp == 7 && lane == 0) {
+    } else if (warp == 11 && lane == 0) {
         // ---------------- TMA producer, activations: a stage's half follows as soon as the stage is free and the
         // split it comes from is complete in every CTA ----------------
         Cursor acts_at;
@@ -700,12 +698,12 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
             ++step;
             more = cursor_next(p, c);
         }
-    } else if ((warp == 6 || warp == 8) && lane == 0) {
+    } else if ((warp == 10 || warp == 12) && lane == 0) {
         // ---------------- scale copies: shared memory -> tensor memory, as soon as a stage's scales have landed ----------------
         // Two threads, one for the weights' scales and one for the activations': a thread gets one copy accepted
         // about every hundred cycles. A stage's scale columns in tensor memory are free when its scales land again:
         // the producer refilled the stage only after the MMAs that read those columns were complete.
-        const bool weights = warp == 6;
+        const bool weights = warp == 10;
         uint32_t step = 0;
         Cursor c;
         bool more = cursor_begin(p, c);
@@ -728,11 +726,12 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
             ++step;
             more = cursor_next(p, c);
         }
-    } else if (warp >= 2 && warp < 6) {
+    } else if (warp >= 2 && warp < 10) {
         // ---------------- workers: split activations, run the epilogues ----------------
         const uint32_t worker = threadIdx.x - 64, quadrant = warp & 3;   // tensor-memory lanes of this warp: 32 * quadrant .. + 31
+        const uint32_t token0 = ((warp - 2) >> 2) * 4;                   // and its four token rows
         const bool leader = worker == 0;
-        const uint32_t first_pair = (blockIdx.x * 4 + (warp - 2)) * 2 + (lane >> 4), pair_stride = gridDim.x * 8;   // this half warp's groups of a job
+        const uint32_t first_pair = (blockIdx.x * 8 + (warp - 2)) * 2 + (lane >> 4), pair_stride = gridDim.x * 16;   // this half warp's groups of a job
         uint32_t item_count = 0;
         uint32_t acc_phase[2] = {0, 0};
         uint32_t held[kHeld], largest[kHeld];
@@ -765,21 +764,22 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
 #pragma unroll
             for (uint32_t j = 0; j < kHeld; ++j) held[j] = load_element(ph, job, p.tokens, first_pair + j * pair_stride, lane);
             {
-                const uint32_t token = worker >> 4;
+                const uint32_t token = worker >> 5;   // a warp per token row
                 uint32_t packed = 0;
                 if (token < p.tokens) {
                     const uint4* row = reinterpret_cast<const uint4*>(ph.x + static_cast<uint64_t>(token) * ph.cols);
-                    for (uint32_t i = worker & 15; i < min(ph.cols, 256u) / 8; i += 16) {
+                    for (uint32_t i = lane; i < min(ph.cols, 256u) / 8; i += 32) {
                         const uint4 v = __ldcg(row + i);
                         packed = __vmaxu2(packed, __vmaxu2(__vmaxu2(v.x & 0x7fff7fffu, v.y & 0x7fff7fffu), __vmaxu2(v.z & 0x7fff7fffu, v.w & 0x7fff7fffu)));
                     }
                 }
                 uint32_t most = max(packed & 0xffffu, packed >> 16);
+                most = max(most, __shfl_xor_sync(0xffffffffu, most, 16));
                 most = max(most, __shfl_xor_sync(0xffffffffu, most, 8));
                 most = max(most, __shfl_xor_sync(0xffffffffu, most, 4));
                 most = max(most, __shfl_xor_sync(0xffffffffu, most, 2));
                 most = max(most, __shfl_xor_sync(0xffffffffu, most, 1));
-                if ((worker & 15) == 0) {
+                if (lane == 0) {
                     // term 0 of the row has the global scale 2^(A - 155), term 7 2^(A - 134): all normal f32 numbers
                     const uint32_t a = min(max((most >> 7) + 3, 40u), 250u);
                     anchor[token] = a;
@@ -817,7 +817,7 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
             const TcStep& st = p.step[s];
             const TcPhase& ph = p.phase[st.phase];
             uint32_t* gather = st.feeds ? collected : nullptr;
-            uint32_t kept[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};    // lanes 0..15: the outputs of this warp's 16 columns, as stored; their exponent fields
+            uint32_t kept[5] = {0, 0, 0, 0, 0};             // lanes 0..15: the outputs of this warp's 16 columns and 4 token rows, as stored; their exponent fields
             uint32_t kept_group = ~0u;                      // their 16-element group in the rows of the next product's input
             // ---- epilogues of this CTA's items of the step ----
             const uint32_t items = st.tiles * st.parts;
@@ -830,28 +830,28 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
                 }
                 acc_phase[buffer] ^= 1;
                 tc_fence_after();
-                uint32_t v[kCols / 16][16];
-                const uint32_t taddr = tmem_base + kTmemAcc + buffer * 64 + ((quadrant * 32) << 16);
+                // column = term * 8 + token: this warp's four token rows are four neighbouring columns of every term
+                uint32_t v[kTerms][4];
+                const uint32_t taddr = tmem_base + kTmemAcc + buffer * 64 + token0 + ((quadrant * 32) << 16);
 #pragma unroll
-                for (uint32_t j = 0; j < kCols / 16; ++j) tc_load16(taddr + 16 * j, v[j]);
+                for (uint32_t term = 0; term < kTerms; ++term) tc_load4(taddr + 8 * term, v[term]);
                 tc_wait_ld();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buffer);   // the buffer is free for the item after next
-                float y[8];
+                float y[4];
 #pragma unroll
-                for (uint32_t token = 0; token < 8; ++token) {
-                    // column = term * 8 + token; term t carries the factor 8^t relative to term 0
+                for (uint32_t j = 0; j < 4; ++j) {
+                    // term t carries the factor 8^t relative to term 0
                     float sum = 0.0f, factor = 1.0f;
 #pragma unroll
                     for (uint32_t term = 0; term < kTerms; ++term) {
-                        const uint32_t column = term * 8 + token;
-                        sum = fmaf(__uint_as_float(v[column >> 4][column & 15]), factor, sum);
+                        sum = fmaf(__uint_as_float(v[term][j]), factor, sum);
                         factor *= 8.0f;
                     }
-                    y[token] = sum * term_scale[8 * st.job + token];
+                    y[j] = sum * term_scale[8 * st.job + token0 + j];
                 }
-                contribute_rows(ph, p.tokens, st.tile0 + tile, quadrant, st.slot0 + part, lane, y, gather, st.keeps ? kept : nullptr);
+                contribute_rows(ph, p.tokens, st.tile0 + tile, quadrant, token0, st.slot0 + part, lane, y, gather, st.keeps ? kept : nullptr);
                 kept_group = (st.tile0 + tile) * 4 + quadrant;
             }
             if (!alive || !st.feeds) continue;
@@ -860,10 +860,7 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
             const TcJob& job = p.job[st.feeds];
             const TcPhase& next = p.phase[job.phase];
             const SplitTarget to = split_target(p, st.feeds);
-            if (st.keeps && lane == 0) {
-                gathered[(warp - 2) * 2] = kept[8];
-                gathered[(warp - 2) * 2 + 1] = kept[9];
-            }
+            if (st.keeps && lane == 0) gathered[warp - 2] = kept[4];   // warps 2..5: token rows 0..3, warps 6..9: rows 4..7
             workers_sync();
             if (st.keeps) {
                 // this CTA's maxima as one word of its own: exponent fields, one byte per token row (40 at least, so the
@@ -872,7 +869,7 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
                     unsigned long long word = 0;
                     for (uint32_t token = 0; token < 8; ++token) {
                         uint32_t field = 0;
-                        for (uint32_t k = 0; k < 4; ++k) field = max(field, (gathered[k * 2 + (token >> 2)] >> (8 * (token & 3))) & 0xffu);
+                        for (uint32_t k = 0; k < 4; ++k) field = max(field, (gathered[(token >> 2) * 4 + k] >> (8 * (token & 3))) & 0xffu);
                         word |= static_cast<unsigned long long>(field >= 255 ? 251u : min(max(field, 40u), 250u)) << (8 * token);
                     }
                     asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p.slots + (*wave_set * 2 + w) * kMaxCtas + blockIdx.x), "l"(word) : "memory");
@@ -886,15 +883,15 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
                 workers_sync();
                 if (leader) counter_arrive_only(wave + 2 * w);
             }
-            // While the other CTAs arrive: every warp writes the codes of the 16 columns it has just stored, from
-            // registers: lanes 0..15 take token rows 0..3, lanes 16..31 rows 4..7, one group each.
-            uint2 where[4];
-            uint32_t bits[4] = {0, 0, 0, 0};
+            // While the other CTAs arrive: every warp writes the codes of the 16 columns and 4 token rows it has just
+            // computed, from registers: lanes 0..15 take its first two token rows, lanes 16..31 the other two, a group each.
+            uint2 where[2];
+            uint32_t bits[2] = {0, 0};
             if (st.keeps && kept_group != ~0u) {
 #pragma unroll
-                for (uint32_t j = 0; j < 4; ++j) {
-                    const uint32_t token = j + ((lane >> 4) << 2);
-                    const uint32_t theirs = __shfl_sync(0xffffffffu, kept[4 + j], lane & 15);
+                for (uint32_t j = 0; j < 2; ++j) {
+                    const uint32_t token = token0 + j + ((lane >> 4) << 1);
+                    const uint32_t theirs = __shfl_sync(0xffffffffu, kept[2 + j], lane & 15);
                     where[j] = make_uint2(token < p.tokens ? token : ~0u, kept_group);
                     bits[j] = lane < 16 ? kept[j] : theirs;
                     largest[j] = split_codes(to, where[j], bits[j], 0, lane);
@@ -938,7 +935,7 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
                 workers_sync();
                 if (worker < 8) {
                     uint32_t field = 0;
-                    for (uint32_t k = 0; k < 4; ++k) field = max(field, (gathered[k * 2 + (worker >> 2)] >> (8 * (worker & 3))) & 0xffu);
+                    for (uint32_t k = 0; k < 8; ++k) field = max(field, (gathered[k * 2 + (worker >> 2)] >> (8 * (worker & 3))) & 0xffu);
                     // term 0 of the row has the global scale 2^(A - 155), term 7 2^(A - 134): all normal f32 numbers
                     const uint32_t a = min(field, 250u);
                     term_scale[8 * st.feeds + worker] = field > 250 ? __uint_as_float(0x7fc00000u) : __uint_as_float((a - 28) << 23);
@@ -957,7 +954,7 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
             if (st.keeps) {
                 if (kept_group != ~0u) {
 #pragma unroll
-                    for (uint32_t j = 0; j < 4; ++j) split_scales(to, anchor + 8 * st.feeds, where[j], bits[j], largest[j], lane);
+                    for (uint32_t j = 0; j < 2; ++j) split_scales(to, anchor + 8 * st.feeds, where[j], bits[j], largest[j], lane);
                 }
             } else {
                 // items of several CTAs per tile, or several items per CTA: the outputs are read back, every CTA a share
@@ -974,8 +971,8 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
                 if (lane < 16) {
                     __nv_bfloat16* out = static_cast<__nv_bfloat16*>(ph.out);
 #pragma unroll
-                    for (uint32_t token = 0; token < 8; ++token) {
-                        if (token < p.tokens) out[static_cast<uint64_t>(token) * ph.out_rows + kept_group * 16 + lane] = __ushort_as_bfloat16(static_cast<unsigned short>(kept[token]));
+                    for (uint32_t j = 0; j < 4; ++j) {
+                        if (token0 + j < p.tokens) out[static_cast<uint64_t>(token0 + j) * ph.out_rows + kept_group * 16 + lane] = __ushort_as_bfloat16(static_cast<unsigned short>(kept[j]));
                     }
                 }
             }
@@ -1093,7 +1090,7 @@ bool check_tc(int32_t d, augur_cuda_stream_t s, const augur_cuda_nvfp4_sm100_pla
     *failure = invalid();
     uint32_t physical_rows = 0;
     if (!check_tc_scalars(a, &physical_rows)) return false;
-    if (physical_rows / kTileM * 4 > kMaxGroups || offset < kCounterBytes || offset % 256 != 0 || limit < offset ||
+    if (physical_rows / kTileM * 8 > kMaxGroups || offset < kCounterBytes || offset % 256 != 0 || limit < offset ||
         tc_scratch_need(physical_rows, a->cols, contributors) > limit - offset) {
         return false;
     }

@@ -569,7 +569,11 @@ def sweep_probe(ctx, exchange):
     plan = host.Plan(ctx.stream, scratch)
     x = torch.randn((TOKENS, HIDDEN), device=ctx.device, generator=generator).to(torch.bfloat16)
     wide = torch.randn((TOKENS, 10240 // world), device=ctx.device, generator=generator).to(torch.bfloat16)
-    mlp_layers, _ = build_mlp_layers(ctx, SWEEP_LAYERS)
+    # one GPU: the MLP blocks on the tensor-memory kernel (one launch each), with a plan of their own
+    tensor_memory = world == 1
+    mlp_layers, _ = build_mlp_layers(ctx, SWEEP_LAYERS, kernel="tensor_memory" if tensor_memory else "mma_sync")
+    mlp_plan = host.Plan(ctx.stream, host.mlp_tc_scratch_bytes(HIDDEN, INTER)) if tensor_memory else plan
+    program_type = host.Nvfp4Sm100TcFfnProgram if tensor_memory else host.Nvfp4Sm100FfnProgram
     outs = [torch.empty((TOKENS, HIDDEN), dtype=torch.bfloat16, device=ctx.device) for _ in range(2)]
     programs = []
     for index, (gate_up, down) in enumerate(mlp_layers):
@@ -583,7 +587,7 @@ def sweep_probe(ctx, exchange):
             if how == "row" and exchange is not None:
                 projection = tp.RowParallelLinear(projection, exchange)
             layer.append(projection)
-        program = host.Nvfp4Sm100FfnProgram.bind(plan, gate_up, down, x, out=outs[index % 2])
+        program = program_type.bind(mlp_plan, gate_up, down, x, out=outs[index % 2])
         if exchange is not None:
             program = tp.FusedExchangeProgram(program, exchange)
         layer.append(program)
@@ -608,8 +612,11 @@ def sweep_probe(ctx, exchange):
     entry.update({"workload": f"config3: {SWEEP_LAYERS} layers x (MLP 5120 -> 2x17408 -> 5120, 5120 -> 10240, 5120 -> 5120, 10240 -> 5120), "
                               f"M={TOKENS}, tp{world}", "weight_bytes_per_verify_pass": weights_total,
                   "weight_bytes_per_gpu": weights_total // world, "launches_per_pass": launches,
-                  "device_status": plan.device_status()})
+                  "mlp_kernel": KERNELS["tensor_memory" if tensor_memory else "mma_sync"][0],
+                  "device_status": plan.device_status() | mlp_plan.device_status()})
     del programs, mlp_layers
+    if mlp_plan is not plan:
+        mlp_plan.close()
     plan.close()
     return entry
 
