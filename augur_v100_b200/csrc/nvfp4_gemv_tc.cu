@@ -641,7 +641,7 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
             if (progressed) {
                 idle = 0;
             } else {
-                __nanosleep(100);   // leave the issue slots to the warps that are splitting
+                if (job == 0) __nanosleep(100);   // polling shared memory: leave the issue slots to the warps that are splitting
                 if (++idle > kWaitLimit / 8 || ((idle & 255u) == 255u && *abort_flag)) {
                     *abort_flag = 1;
                     atomicCAS(p.header, 0u, kErrTcProducer);
@@ -865,14 +865,24 @@ tc_program_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constan
             if (st.keeps) {
                 // this CTA's maxima as one word of its own: exponent fields, one byte per token row (40 at least, so the
                 // word is never 0; 251 for a non-finite value). Nothing has to be visible with it, so no release.
-                if (leader) {
-                    unsigned long long word = 0;
-                    for (uint32_t token = 0; token < 8; ++token) {
+                if (worker < 32) {   // the first worker warp: lanes 0..7 a token row each, then the eight bytes gathered in lane 0
+                    uint32_t low = 0, high = 0;
+                    if (lane < 8) {
                         uint32_t field = 0;
-                        for (uint32_t k = 0; k < 4; ++k) field = max(field, (gathered[(token >> 2) * 4 + k] >> (8 * (token & 3))) & 0xffu);
-                        word |= static_cast<unsigned long long>(field >= 255 ? 251u : min(max(field, 40u), 250u)) << (8 * token);
+                        for (uint32_t k = 0; k < 4; ++k) field = max(field, (gathered[(lane >> 2) * 4 + k] >> (8 * (lane & 3))) & 0xffu);
+                        const uint32_t byte = (field >= 255 ? 251u : min(max(field, 40u), 250u)) << (8 * (lane & 3));
+                        low = lane < 4 ? byte : 0;
+                        high = lane < 4 ? 0 : byte;
                     }
-                    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p.slots + (*wave_set * 2 + w) * kMaxCtas + blockIdx.x), "l"(word) : "memory");
+#pragma unroll
+                    for (uint32_t offset = 4; offset; offset >>= 1) {
+                        low |= __shfl_xor_sync(0xffffffffu, low, offset);
+                        high |= __shfl_xor_sync(0xffffffffu, high, offset);
+                    }
+                    if (lane == 0) {
+                        const unsigned long long word = (static_cast<unsigned long long>(high) << 32) | low;
+                        asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p.slots + (*wave_set * 2 + w) * kMaxCtas + blockIdx.x), "l"(word) : "memory");
+                    }
                 }
                 workers_sync();   // `gathered` is used again below
             } else {
