@@ -286,3 +286,46 @@ def test_programs_of_different_shapes_share_a_plan(ctx):
                 assert np.array_equal(bits_from_torch_bf16(programs[index].out), firsts[index]), index
     finally:
         plan.close()
+
+
+def test_one_gate_up_tile_far_larger_than_the_others(ctx):
+    # the anchors of the intermediate come from every CTA's maxima: one tile whose outputs are far larger than all
+    # others' (block scales times 8 on its gate and up rows) sets them for everybody, and the other tiles' groups
+    # get small block scales. Same bound as every other case; the bits repeat.
+    host = ctx["host"]
+    hidden, inter, tokens = 256, 1536, 8
+    gate = list(synth.make_weight(50, 94, "gate", inter, hidden))
+    up = list(synth.make_weight(50, 94, "up", inter, hidden))
+    down = synth.make_weight(50, 94, "down", hidden, inter)
+    for plane in (gate, up):
+        scales = plane[1].copy().reshape(inter, hidden // 16)
+        tile = scales[5 * 64:6 * 64]
+        scales[5 * 64:6 * 64] = np.where(tile > 0, np.minimum(tile.astype(np.int32) + 24, 0x7E), tile).astype(scales.dtype)   # E4M3 exponent + 3
+        plane[1] = scales.reshape(plane[1].shape)
+    gate, up = tuple(gate), tuple(up)
+    gate_up_w = host.upload_gate_up_interleaved(ctx["stream"], inter, hidden, *gate, *up)
+    down_w = host.Nvfp4Sm100Weight.upload_checkpoint_nvfp4(ctx["stream"], abi.LAYOUT_TCGEN05, hidden, inter, *down)
+    x_bits = synth.f32_to_bf16_bits(np.random.default_rng(51).standard_normal((tokens, hidden)).astype(np.float32))
+    x = torch_bf16_from_bits(x_bits, ctx["device"])
+    plan = host.Plan(ctx["stream"], host.mlp_tc_scratch_bytes(hidden, inter))
+    try:
+        program = host.Nvfp4Sm100TcFfnProgram.bind(plan, gate_up_w, down_w, x)
+        program.submit_for_plan()
+        ctx["stream"].synchronize()
+        assert plan.device_status() == 0, hex(plan.device_status())
+        first = bits_from_torch_bf16(program.out).copy()
+        threads = oracle.max_threads()
+        h64, _ = oracle.mlp_f64(gate, up, down, hidden, inter, x_bits, threads=threads)
+        ratio = np.abs(h64[:, 5 * 64:6 * 64]).max() / np.abs(np.delete(h64, np.s_[5 * 64:6 * 64], axis=1)).max()
+        assert ratio > 32.0, ratio            # the case is what it claims to be
+        h_bits = bits_from_torch_bf16(program.intermediate)
+        assert rel_error(h_bits, h64) <= TOLERANCE
+        y64_from_h = oracle.linear_f64(down[0], down[1], down[2], hidden, inter, h_bits, threads=threads)
+        assert rel_error(first, y64_from_h) <= TOLERANCE
+        program.out.zero_()
+        program.submit_for_plan()
+        ctx["stream"].synchronize()
+        assert np.array_equal(bits_from_torch_bf16(program.out), first)
+        assert plan.device_status() == 0
+    finally:
+        plan.close()
