@@ -5,6 +5,7 @@
 
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include <cstdint>
@@ -129,6 +130,13 @@ __device__ __forceinline__ uint32_t instr_desc(uint32_t n) {
 }
 
 
+// max(a, b, c), NaN if any is.
+__device__ __forceinline__ float max_or_nan(float a, float b, float c) {
+    float d;
+    asm("max.NaN.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 // Smallest positive E4M3 code whose value is >= d (d > 0), 126 if none.
 __device__ __forceinline__ uint32_t e4m3_ceil_code(float d) {
     if (d > 448.0f) return 126;
@@ -171,27 +179,90 @@ __device__ __forceinline__ uint32_t e2m1_nearest(float v, float* level) {
     return negative ? (m | 8u) : m;
 }
 
+// Eight quotients -> eight codes, element i in nibble i, by the hardware converter: round to nearest even,
+// magnitudes above 6 (infinities too) to 6. It differs from "nearest, ties toward zero, zero always code 0" in
+// three places, put right here: at 0.75, 1.75 and 3.5 "even" is the larger level, so such a quotient goes in
+// one ulp nearer to zero; a negative quotient that rounds to zero comes out as code 8; and a NaN comes out
+// as +6 (the caller keeps groups with a NaN off this path).
+__device__ __forceinline__ float off_the_tie(float q) {
+    const float a = fabsf(q);
+    uint32_t bits = __float_as_uint(q);
+    if (a == 0.75f || a == 1.75f || a == 3.5f) bits -= 1;
+    return __uint_as_float(bits);
+}
+__device__ __forceinline__ uint32_t e2m1x8_nearest(const float2 (&q)[4]) {
+    uint32_t codes;
+    asm("{\n .reg .b8 b0, b1, b2, b3;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n"
+        "mov.b32 %0, {b0, b1, b2, b3};\n}"
+        : "=r"(codes)
+        : "f"(off_the_tie(q[0].x)), "f"(off_the_tie(q[0].y)), "f"(off_the_tie(q[1].x)), "f"(off_the_tie(q[1].y)),
+          "f"(off_the_tie(q[2].x)), "f"(off_the_tie(q[2].y)), "f"(off_the_tie(q[3].x)), "f"(off_the_tie(q[3].y)));
+    const uint32_t nonzero = (codes | (codes >> 1) | (codes >> 2)) & 0x11111111u;   // bit 0 of every nibble with a magnitude
+    return codes & ((nonzero << 3) | 0x77777777u);
+}
+
+// The signed levels of eight codes (hardware E2M1 -> F16 pairs, widened).
+__device__ __forceinline__ void e2m1x8_levels(uint32_t codes, float2 (&level)[4]) {
+    uint32_t pair[4];
+    asm("{\n .reg .b8 b0, b1, b2, b3;\n mov.b32 {b0, b1, b2, b3}, %4;\n"
+        "cvt.rn.f16x2.e2m1x2 %0, b0;\n cvt.rn.f16x2.e2m1x2 %1, b1;\n"
+        "cvt.rn.f16x2.e2m1x2 %2, b2;\n cvt.rn.f16x2.e2m1x2 %3, b3;\n}"
+        : "=r"(pair[0]), "=r"(pair[1]), "=r"(pair[2]), "=r"(pair[3])
+        : "r"(codes));
+#pragma unroll
+    for (uint32_t i = 0; i < 4; ++i) level[i] = __half22float2(*reinterpret_cast<const __half2*>(&pair[i]));
+}
+
 // The 16 quotients of a group share one divisor. With y = RN(1/d), two Newton steps on the quotient (each
 // an exact FMA residual) end on the correctly rounded x / d whenever d and x are well inside the normal
-// range and d is not of the all-ones mantissa form; the kernel checks that once per group (`kFast`) and
-// otherwise divides. An x below 2^-65 (d is at least 2^-63 here) has a quotient under a quarter, i.e. code 0
-// whatever the last bits are, and is not sent through the steps, which could leave the normal range.
-template <bool kFast, bool kMoreTerms>
-__device__ __forceinline__ void quantise_group(float (&residual)[16], float divisor, float reciprocal, uint32_t (&packed)[2]) {
+// range and d is not of the all-ones mantissa form; the kernel checks that once per group and otherwise
+// divides. An x so small that a residual of the steps is subnormal (below 2^-103) has a quotient under
+// 2^-40 (d is at least 2^-63 here), and the error that the lost bits leave in it is under 2^-87: code 0
+// either way. This path holds no NaN (the caller checks), works on pairs of elements with the two-wide
+// F32 instructions and rounds with the hardware converter.
+template <bool kMoreTerms>
+__device__ __forceinline__ void quantise_group_fast(float (&residual)[16], float divisor, float reciprocal, uint32_t (&packed)[2]) {
+    const float2 y = make_float2(reciprocal, reciprocal), minus_d = make_float2(-divisor, -divisor);
+#pragma unroll
+    for (uint32_t half = 0; half < 2; ++half) {
+        float2 x[4], quotient[4];
+#pragma unroll
+        for (uint32_t i = 0; i < 4; ++i) {
+            x[i] = make_float2(residual[8 * half + 2 * i], residual[8 * half + 2 * i + 1]);
+            float2 q = __fmul2_rn(x[i], y);
+            float2 r = __ffma2_rn(q, minus_d, x[i]);
+            q = __ffma2_rn(r, y, q);
+            r = __ffma2_rn(q, minus_d, x[i]);
+            quotient[i] = __ffma2_rn(r, y, q);
+        }
+        packed[half] = e2m1x8_nearest(quotient);
+        if (kMoreTerms) {
+            float2 level[4];
+            e2m1x8_levels(packed[half], level);
+#pragma unroll
+            for (uint32_t i = 0; i < 4; ++i) {
+                // x - RN(level * d). The product is rounded one element at a time: a two-wide product feeding a
+                // two-wide sum came out fused into one operation (one rounding), however it was written.
+                const float2 product = make_float2(__fmul_rn(level[i].x, -divisor), __fmul_rn(level[i].y, -divisor));
+                const float2 rest = __fadd2_rn(x[i], product);
+                residual[8 * half + 2 * i] = rest.x;
+                residual[8 * half + 2 * i + 1] = rest.y;
+            }
+        }
+    }
+}
+
+// The same without those conditions: IEEE division, rounding in software, NaN quotients included.
+template <bool kMoreTerms>
+__device__ __forceinline__ void quantise_group_any(float (&residual)[16], float divisor, uint32_t (&packed)[2]) {
 #pragma unroll
     for (uint32_t i = 0; i < 16; ++i) {
         const float x = residual[i];
-        float normalized;
-        if (kFast) {
-            float q = x * reciprocal;
-            float r = fmaf(-q, divisor, x);
-            q = fmaf(r, reciprocal, q);
-            r = fmaf(-q, divisor, x);
-            q = fmaf(r, reciprocal, q);
-            normalized = fabsf(x) < 0x1p-65f ? 0.0f : q;
-        } else {
-            normalized = divisor == 0.0f ? 0.0f : __fdiv_rn(x, divisor);
-        }
+        const float normalized = divisor == 0.0f ? 0.0f : __fdiv_rn(x, divisor);
         float level;
         const uint32_t code = e2m1_nearest(normalized, &level);
         packed[i >> 3] += code << (4 * (i & 7));   // disjoint fields: a sum, so that shift and add fuse
@@ -199,15 +270,9 @@ __device__ __forceinline__ void quantise_group(float (&residual)[16], float divi
     }
 }
 
-// One residual term of one 16-element group: the block scale (smallest E4M3 value >= amax / (6 g)), the 16 codes
-// (nearest level of x / (scale * g), ties toward zero) and, if another term follows, the residual it quantises.
-// `kMoreTerms` is a compile-time choice: the last term of a group needs neither the levels nor the residual.
-template <bool kMoreTerms>
-__device__ __forceinline__ void quantise_term_as(float (&residual)[16], float global_scale, uint32_t (&packed)[2],
-                                                 uint32_t* scale_code_out) {
-    float maximum = 0.0f;
-#pragma unroll
-    for (uint32_t i = 0; i < 16; ++i) maximum = fmaxf(maximum, fabsf(residual[i]));
+// Block scale of a group with largest magnitude `maximum`: the smallest E4M3 value >= maximum / (6 g) and its
+// code; returns the divisor scale * g.
+__device__ __forceinline__ float group_divisor(float maximum, float global_scale, uint32_t* scale_code_out) {
     const float desired = __fdiv_rn(maximum, __fmul_rn(6.0f, global_scale));
     uint32_t scale_code = 0;
     float scale = 0.0f;
@@ -215,17 +280,35 @@ __device__ __forceinline__ void quantise_term_as(float (&residual)[16], float gl
         scale_code = e4m3_ceil_code(desired);
         scale = e4m3_positive_value(scale_code);
     }
-    const float divisor = __fmul_rn(scale, global_scale);
+    *scale_code_out = scale_code;
+    return __fmul_rn(scale, global_scale);
+}
+
+// One residual term of one 16-element group: the block scale, the 16 codes (nearest level of x / (scale * g),
+// ties toward zero) and, if another term follows, the residual it quantises.
+// `kMoreTerms` is a compile-time choice: the last term of a group needs neither the levels nor the residual.
+template <bool kMoreTerms>
+__device__ __forceinline__ void quantise_term_as(float (&residual)[16], float global_scale, uint32_t (&packed)[2],
+                                                 uint32_t* scale_code_out) {
+    // This maximum carries a NaN along, which keeps the group off the fast path; the reference's maximum
+    // leaves NaNs out, and only the other path computes it.
+    float maximum = 0.0f;
+#pragma unroll
+    for (uint32_t i = 0; i < 16; i += 2) maximum = max_or_nan(maximum, fabsf(residual[i]), fabsf(residual[i + 1]));
+    float divisor = group_divisor(maximum, global_scale, scale_code_out);
     const uint32_t divisor_field = (__float_as_uint(divisor) >> 23) & 0xffu, largest_field = (__float_as_uint(maximum) >> 23) & 0xffu;
     const bool fast = divisor_field >= 64u && divisor_field <= 190u && (__float_as_uint(divisor) & 0x7fffffu) != 0x7fffffu &&
                       largest_field <= 190u;
     packed[0] = packed[1] = 0;
     if (fast) {
-        quantise_group<true, kMoreTerms>(residual, divisor, __frcp_rn(divisor), packed);
+        quantise_group_fast<kMoreTerms>(residual, divisor, __frcp_rn(divisor), packed);
     } else {
-        quantise_group<false, kMoreTerms>(residual, divisor, 0.0f, packed);
+        maximum = 0.0f;
+#pragma unroll
+        for (uint32_t i = 0; i < 16; ++i) maximum = fmaxf(maximum, fabsf(residual[i]));
+        divisor = group_divisor(maximum, global_scale, scale_code_out);
+        quantise_group_any<kMoreTerms>(residual, divisor, packed);
     }
-    *scale_code_out = scale_code;
 }
 __device__ __forceinline__ void quantise_term(float (&residual)[16], float global_scale, bool more_terms, uint32_t (&packed)[2],
                                               uint32_t* scale_code_out) {

@@ -33,6 +33,11 @@ def test_activation_quantiser_is_bit_exact(ctx, tokens, cols, terms, glob):
     x[1, 16:32] *= 1e-6                   # below the smallest scale
     x[2, 32:48] *= 1e4                    # saturates the largest scale when glob is small
     x[3, :8] = [0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, -0.25]   # ties (after scaling by an exact scale)
+    x[3, 8:16] = [-0.75, -1.25, -1.75, -2.5, -3.5, -5.0, 6.0, -6.0]
+    x[4, 3] = -1e-4                       # a negative quotient that rounds to zero: code 0, not "minus zero"
+    x[4, 16:24] = [np.nan, 1.0, -2.0, 0.3, np.nan, 6.0, -0.1, 0.0]   # a NaN quotient clamps to -6; the maximum leaves NaNs out
+    x[4, 40] = np.inf                     # largest scale, code +6, every later residual infinite
+    x[4, 50] = -np.inf
     x_bits = synth.f32_to_bf16_bits(x)
     weight = host.Nvfp4Sm100Weight(ctx["stream"], abi.LAYOUT_TCGEN05, 128, cols,
                                    torch.zeros(host.repack_extent(abi.LAYOUT_TCGEN05, 128, cols), dtype=torch.uint8,
