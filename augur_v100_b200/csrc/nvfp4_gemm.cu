@@ -714,11 +714,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_const
                     if (p.quant_out) {
                         // The BF16 values this lane holds, quantised for the next GEMM while the next tile's MMAs run.
                         const uint32_t group = n_tile * (kTileN / 32) + half * 4 + c;
-                        float residual[16];
+                        float2 residual[8];
 #pragma unroll
                         for (uint32_t i = 0; i < 8; ++i) {
-                            residual[2 * i] = __uint_as_float(packed[i] << 16);
-                            residual[2 * i + 1] = __uint_as_float(packed[i] & 0xffff0000u);
+                            residual[i] = make_float2(__uint_as_float(packed[i] << 16), __uint_as_float(packed[i] & 0xffff0000u));
                         }
 #pragma unroll
                         for (uint32_t term = 0; term < 3; ++term) {
@@ -810,11 +809,10 @@ __global__ void act_quant_kernel(const uint16_t* __restrict__ x, uint8_t* __rest
     const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<uint64_t>(token) * cols + group * 16);
     const uint4 lo = __ldg(src), hi = __ldg(src + 1);
     const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-    float residual[16];
+    float2 residual[8];   // pairs of neighbouring elements, as the two-wide F32 instructions take them
 #pragma unroll
     for (uint32_t i = 0; i < 8; ++i) {
-        residual[2 * i] = __uint_as_float(words[i] << 16);
-        residual[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000u);
+        residual[i] = make_float2(__uint_as_float(words[i] << 16), __uint_as_float(words[i] & 0xffff0000u));
     }
     // every term's code plane has whole 128-row tiles (the rows past `tokens` are never written and
     // only ever feed output rows that are not stored)

@@ -181,14 +181,13 @@ __device__ __forceinline__ uint32_t e2m1_nearest(float v, float* level) {
 
 // Eight quotients -> eight codes, element i in nibble i, by the hardware converter: round to nearest even,
 // magnitudes above 6 (infinities too) to 6. It differs from "nearest, ties toward zero, zero always code 0" in
-// three places, put right here: at 0.75, 1.75 and 3.5 "even" is the larger level, so such a quotient goes in
-// one ulp nearer to zero; a negative quotient that rounds to zero comes out as code 8; and a NaN comes out
-// as +6 (the caller keeps groups with a NaN off this path).
+// three places, put right here. At 0.75, 1.75 and 3.5 "even" is the larger level. A tie is a value of at most
+// three significant bits; every quotient that short (low 21 bits of the pattern zero) goes in one or two ulps
+// nearer to zero, which takes a tie to the level below and changes nothing else: the values passed over
+// are not short, so none of them is a tie, and a zero stays a zero. A negative quotient that rounds to zero
+// comes out as code 8. And a NaN comes out as +6 (the caller keeps groups with a NaN off this path).
 __device__ __forceinline__ float off_the_tie(float q) {
-    const float a = fabsf(q);
-    uint32_t bits = __float_as_uint(q);
-    if (a == 0.75f || a == 1.75f || a == 3.5f) bits -= 1;
-    return __uint_as_float(bits);
+    return (__float_as_uint(q) & 0x1fffffu) == 0 ? __fmul_rn(q, 0x1.fffffcp-1f) : q;   // q * (1 - 2^-23)
 }
 __device__ __forceinline__ uint32_t e2m1x8_nearest(const float2 (&q)[4]) {
     uint32_t codes;
@@ -225,14 +224,14 @@ __device__ __forceinline__ void e2m1x8_levels(uint32_t codes, float2 (&level)[4]
 // either way. This path holds no NaN (the caller checks), works on pairs of elements with the two-wide
 // F32 instructions and rounds with the hardware converter.
 template <bool kMoreTerms>
-__device__ __forceinline__ void quantise_group_fast(float (&residual)[16], float divisor, float reciprocal, uint32_t (&packed)[2]) {
+__device__ __forceinline__ void quantise_group_fast(float2 (&residual)[8], float divisor, float reciprocal, uint32_t (&packed)[2]) {
     const float2 y = make_float2(reciprocal, reciprocal), minus_d = make_float2(-divisor, -divisor);
 #pragma unroll
     for (uint32_t half = 0; half < 2; ++half) {
         float2 x[4], quotient[4];
 #pragma unroll
         for (uint32_t i = 0; i < 4; ++i) {
-            x[i] = make_float2(residual[8 * half + 2 * i], residual[8 * half + 2 * i + 1]);
+            x[i] = residual[4 * half + i];
             float2 q = __fmul2_rn(x[i], y);
             float2 r = __ffma2_rn(q, minus_d, x[i]);
             q = __ffma2_rn(r, y, q);
@@ -248,9 +247,7 @@ __device__ __forceinline__ void quantise_group_fast(float (&residual)[16], float
                 // x - RN(level * d). The product is rounded one element at a time: a two-wide product feeding a
                 // two-wide sum came out fused into one operation (one rounding), however it was written.
                 const float2 product = make_float2(__fmul_rn(level[i].x, -divisor), __fmul_rn(level[i].y, -divisor));
-                const float2 rest = __fadd2_rn(x[i], product);
-                residual[8 * half + 2 * i] = rest.x;
-                residual[8 * half + 2 * i + 1] = rest.y;
+                residual[4 * half + i] = __fadd2_rn(x[i], product);
             }
         }
     }
@@ -258,15 +255,19 @@ __device__ __forceinline__ void quantise_group_fast(float (&residual)[16], float
 
 // The same without those conditions: IEEE division, rounding in software, NaN quotients included.
 template <bool kMoreTerms>
-__device__ __forceinline__ void quantise_group_any(float (&residual)[16], float divisor, uint32_t (&packed)[2]) {
+__device__ __forceinline__ float quantise_element_any(float x, float divisor, uint32_t shift, uint32_t* packed) {
+    const float normalized = divisor == 0.0f ? 0.0f : __fdiv_rn(x, divisor);
+    float level;
+    const uint32_t code = e2m1_nearest(normalized, &level);
+    *packed += code << shift;   // disjoint fields: a sum, so that shift and add fuse
+    return kMoreTerms ? __fsub_rn(x, __fmul_rn(level, divisor)) : x;
+}
+template <bool kMoreTerms>
+__device__ __forceinline__ void quantise_group_any(float2 (&residual)[8], float divisor, uint32_t (&packed)[2]) {
 #pragma unroll
-    for (uint32_t i = 0; i < 16; ++i) {
-        const float x = residual[i];
-        const float normalized = divisor == 0.0f ? 0.0f : __fdiv_rn(x, divisor);
-        float level;
-        const uint32_t code = e2m1_nearest(normalized, &level);
-        packed[i >> 3] += code << (4 * (i & 7));   // disjoint fields: a sum, so that shift and add fuse
-        if (kMoreTerms) residual[i] = __fsub_rn(x, __fmul_rn(level, divisor));
+    for (uint32_t i = 0; i < 8; ++i) {
+        residual[i].x = quantise_element_any<kMoreTerms>(residual[i].x, divisor, 8 * (i & 3), &packed[i >> 2]);
+        residual[i].y = quantise_element_any<kMoreTerms>(residual[i].y, divisor, 8 * (i & 3) + 4, &packed[i >> 2]);
     }
 }
 
@@ -288,13 +289,13 @@ __device__ __forceinline__ float group_divisor(float maximum, float global_scale
 // ties toward zero) and, if another term follows, the residual it quantises.
 // `kMoreTerms` is a compile-time choice: the last term of a group needs neither the levels nor the residual.
 template <bool kMoreTerms>
-__device__ __forceinline__ void quantise_term_as(float (&residual)[16], float global_scale, uint32_t (&packed)[2],
+__device__ __forceinline__ void quantise_term_as(float2 (&residual)[8], float global_scale, uint32_t (&packed)[2],
                                                  uint32_t* scale_code_out) {
     // This maximum carries a NaN along, which keeps the group off the fast path; the reference's maximum
     // leaves NaNs out, and only the other path computes it.
     float maximum = 0.0f;
 #pragma unroll
-    for (uint32_t i = 0; i < 16; i += 2) maximum = max_or_nan(maximum, fabsf(residual[i]), fabsf(residual[i + 1]));
+    for (uint32_t i = 0; i < 8; ++i) maximum = max_or_nan(maximum, fabsf(residual[i].x), fabsf(residual[i].y));
     float divisor = group_divisor(maximum, global_scale, scale_code_out);
     const uint32_t divisor_field = (__float_as_uint(divisor) >> 23) & 0xffu, largest_field = (__float_as_uint(maximum) >> 23) & 0xffu;
     const bool fast = divisor_field >= 64u && divisor_field <= 190u && (__float_as_uint(divisor) & 0x7fffffu) != 0x7fffffu &&
@@ -305,12 +306,12 @@ __device__ __forceinline__ void quantise_term_as(float (&residual)[16], float gl
     } else {
         maximum = 0.0f;
 #pragma unroll
-        for (uint32_t i = 0; i < 16; ++i) maximum = fmaxf(maximum, fabsf(residual[i]));
+        for (uint32_t i = 0; i < 8; ++i) maximum = fmaxf(maximum, fmaxf(fabsf(residual[i].x), fabsf(residual[i].y)));
         divisor = group_divisor(maximum, global_scale, scale_code_out);
         quantise_group_any<kMoreTerms>(residual, divisor, packed);
     }
 }
-__device__ __forceinline__ void quantise_term(float (&residual)[16], float global_scale, bool more_terms, uint32_t (&packed)[2],
+__device__ __forceinline__ void quantise_term(float2 (&residual)[8], float global_scale, bool more_terms, uint32_t (&packed)[2],
                                               uint32_t* scale_code_out) {
     if (more_terms) {
         quantise_term_as<true>(residual, global_scale, packed, scale_code_out);
