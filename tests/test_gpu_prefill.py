@@ -52,6 +52,30 @@ def test_activation_quantiser_is_bit_exact(ctx, tokens, cols, terms, glob):
     assert np.array_equal(codes, want_codes)
 
 
+@pytest.mark.parametrize("glob", [0.01, 0.37, 3.0e-3, 1.0 / 3.0, 7.5])
+def test_activation_quantiser_is_bit_exact_for_any_global_scale(ctx, glob):
+    """A global scale that is not a power of two makes every divisor a full-width significand: level * divisor is
+    then inexact, and the residual must be x - RN(level * divisor) with both roundings (a fused multiply-subtract
+    shifts the third term's block scales); the quotients hardly ever sit on a tie, but the residuals' largest
+    magnitudes sit right on an E4M3 boundary far more often than chance."""
+    host, torch = ctx["host"], ctx["torch"]
+    tokens, cols, terms = 192, 1024, 3
+    rng = np.random.default_rng(int(glob * 1e6))
+    x = (rng.standard_normal((tokens, cols)) * rng.choice([0.01, 1.0, 30.0], size=(tokens, 1))).astype(np.float32)
+    x_bits = synth.f32_to_bf16_bits(x)
+    weight = host.Nvfp4Sm100Weight(ctx["stream"], abi.LAYOUT_TCGEN05, 128, cols,
+                                   torch.zeros(host.repack_extent(abi.LAYOUT_TCGEN05, 128, cols), dtype=torch.uint8,
+                                               device=ctx["device"]), 1.0)
+    lin = host.Nvfp4Sm100PrefillLinear.bind(ctx["plan"], weight, torch_bf16_from_bits(x_bits, ctx["device"]),
+                                            terms=terms, activation_global_scale=glob)
+    lin.submit_quant()
+    ctx["stream"].synchronize()
+    codes, scales = lin.staged_planes()
+    want_codes, want_scales = oracle.act_quant(x_bits, tokens, cols, glob, terms)
+    assert np.array_equal(scales, want_scales)
+    assert np.array_equal(codes, want_codes)
+
+
 def _run_gemm(ctx, w_planes, a_codes, a_scales, rows, cols, tokens, terms, g_w, g_a, plan=None):
     """Uploads explicit weight and (already quantised) activation planes and runs the GEMM entry."""
     host, torch = ctx["host"], ctx["torch"]
