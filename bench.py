@@ -553,7 +553,7 @@ SWEEP_LAYERS = 64
 SWEEP_SHAPES = ((10240, 5120, "column"), (5120, 5120, "column"), (5120, 10240, "row"))   # rows, cols, how it shards
 
 
-def sweep_probe(ctx, exchange):
+def sweep_probe(ctx, exchange, kernel):
     """Configuration 3: 64 layers, each the MLP block plus the projections 5120 -> 10240, 5120 -> 5120 and
     10240 -> 5120, all NVFP4 at M=8. With N > 1 the first two are column-parallel (row slices, outputs stay
     sharded), the third is row-parallel (k slices) with the all-reduce inside its launch, the MLP as in the
@@ -569,12 +569,15 @@ def sweep_probe(ctx, exchange):
     plan = host.Plan(ctx.stream, scratch)
     x = torch.randn((TOKENS, HIDDEN), device=ctx.device, generator=generator).to(torch.bfloat16)
     wide = torch.randn((TOKENS, 10240 // world), device=ctx.device, generator=generator).to(torch.bfloat16)
-    # the MLP blocks stay on the mma.sync kernel here: between the attention-shaped launches of that kernel the
-    # one-launch tensor-memory block measured 2 % slower (5.58 against 5.48 ms per pass), because neither neighbour
-    # can start its prologue while the other's CTAs hold the SMs
-    tensor_memory = False
+    # On one GPU every launch of the pass is on the chosen kernel. (Mixed, the one-launch tensor-memory block between
+    # attention-shaped launches of the mma.sync kernel measured 5.58 ms per pass against 5.48 all mma.sync and 5.31 all
+    # tensor-memory: a launch starts its prologue under the tail of a neighbour of its own kind only.)
+    tensor_memory = kernel == "tensor_memory" and world == 1
     mlp_layers, _ = build_mlp_layers(ctx, SWEEP_LAYERS, kernel="tensor_memory" if tensor_memory else "mma_sync")
-    mlp_plan = host.Plan(ctx.stream, host.mlp_tc_scratch_bytes(HIDDEN, INTER)) if tensor_memory else plan
+    mlp_plan = plan
+    if tensor_memory:
+        mlp_plan = host.Plan(ctx.stream, max([host.mlp_tc_scratch_bytes(HIDDEN, INTER)] +
+                                             [host.gemv_tc_scratch_bytes(rows, cols) for rows, cols, _ in SWEEP_SHAPES]))
     program_type = host.Nvfp4Sm100TcFfnProgram if tensor_memory else host.Nvfp4Sm100FfnProgram
     outs = [torch.empty((TOKENS, HIDDEN), dtype=torch.bfloat16, device=ctx.device) for _ in range(2)]
     programs = []
@@ -583,9 +586,13 @@ def sweep_probe(ctx, exchange):
         for rows, cols, how in SWEEP_SHAPES:
             r, c = (rows // world, cols) if how == "column" else (rows, cols // world)
             codes, scales = device_planes(torch, generator, r, c, ctx.device)
-            weight = host.Nvfp4Sm100Weight.repack_device_planes(ctx.stream, abi.LAYOUT_STREAM, r, c, codes, scales, synth.GLOBAL_SCALE)
+            layout = abi.LAYOUT_TCGEN05 if tensor_memory else abi.LAYOUT_STREAM
+            weight = host.Nvfp4Sm100Weight.repack_device_planes(ctx.stream, layout, r, c, codes, scales, synth.GLOBAL_SCALE)
             del codes, scales
-            projection = host.Nvfp4Sm100Projection.bind(plan, weight, x if how == "column" else wide)
+            if tensor_memory:
+                projection = host.Nvfp4Sm100TcProjection.bind(mlp_plan, weight, x if how == "column" else wide)
+            else:
+                projection = host.Nvfp4Sm100Projection.bind(plan, weight, x if how == "column" else wide)
             if how == "row" and exchange is not None:
                 projection = tp.RowParallelLinear(projection, exchange)
             layer.append(projection)
@@ -614,7 +621,7 @@ def sweep_probe(ctx, exchange):
     entry.update({"workload": f"config3: {SWEEP_LAYERS} layers x (MLP 5120 -> 2x17408 -> 5120, 5120 -> 10240, 5120 -> 5120, 10240 -> 5120), "
                               f"M={TOKENS}, tp{world}", "weight_bytes_per_verify_pass": weights_total,
                   "weight_bytes_per_gpu": weights_total // world, "launches_per_pass": launches,
-                  "mlp_kernel": KERNELS["tensor_memory" if tensor_memory else "mma_sync"][0],
+                  "kernel": KERNELS["tensor_memory" if tensor_memory else "mma_sync"][0],
                   "device_status": plan.device_status() | mlp_plan.device_status()})
     del programs, mlp_layers
     if mlp_plan is not plan:
@@ -809,7 +816,7 @@ def run_library(args):
     torch.cuda.empty_cache()
     if not args.headline_only:
         try:
-            extras["config3_sweep"] = sweep_probe(ctx, exchange)
+            extras["config3_sweep"] = sweep_probe(ctx, exchange, kernel)
         except Exception as error:  # reported, never hidden
             extras["config3_sweep"] = {"error": repr(error)}
         torch.cuda.empty_cache()
