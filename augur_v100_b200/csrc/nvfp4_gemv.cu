@@ -1219,6 +1219,7 @@ namespace {
 static_assert(sizeof(augur_cuda_nvfp4_sm100_norm_group_args_v1) == 472, "norm_group ABI");
 
 constexpr uint32_t kNormThreads = 256;
+constexpr uint32_t kNormHeld = 24;       // columns of a row that one thread keeps in registers (rows up to 6144 wide)
 
 // One CTA per token row. The arithmetic order is the reference kernel's, so that the F32 output is
 // reproducible on a CPU: lane l accumulates value * value over columns l, l + 256, ... (multiply and
@@ -1235,16 +1236,46 @@ __global__ void __launch_bounds__(kNormThreads) norm_stage_kernel(const float* _
     __shared__ float partial[kNormThreads];
     const uint32_t lane = threadIdx.x;
     const uint64_t base = static_cast<uint64_t>(blockIdx.x) * cols;
+    // A row of up to 256 * kNormHeld columns is held in registers: all of a thread's loads are in flight at once
+    // (each is a round trip to L2), and the second pass reads nothing but the weights, which are fetched with them.
+    // The arithmetic and its order are the same on both paths.
+    const bool held_row = cols <= kNormThreads * kNormHeld;
+    float held[kNormHeld], gain[kNormHeld];
     float sum = 0.0f;
-    for (uint32_t col = lane; col < cols; col += kNormThreads) {
-        float value;
-        if (residual) {
-            value = __fadd_rn(__ldcg(add_a + base + col), __ldcg(add_b + base + col));
-            input[base + col] = value;
-        } else {
-            value = __ldcg(input + base + col);
+    if (held_row) {
+        float other[kNormHeld];
+#pragma unroll
+        for (uint32_t i = 0; i < kNormHeld; ++i) {
+            const uint32_t col = lane + i * kNormThreads;
+            held[i] = gain[i] = other[i] = 0.0f;
+            if (col < cols) {
+                held[i] = residual ? __ldcg(add_a + base + col) : __ldcg(input + base + col);
+                if (residual) other[i] = __ldcg(add_b + base + col);
+                gain[i] = __ldg(weight + col);
+            }
         }
-        sum = __fadd_rn(sum, __fmul_rn(value, value));
+#pragma unroll
+        for (uint32_t i = 0; i < kNormHeld; ++i) {
+            const uint32_t col = lane + i * kNormThreads;
+            if (col < cols) {
+                if (residual) {
+                    held[i] = __fadd_rn(held[i], other[i]);
+                    input[base + col] = held[i];
+                }
+                sum = __fadd_rn(sum, __fmul_rn(held[i], held[i]));
+            }
+        }
+    } else {
+        for (uint32_t col = lane; col < cols; col += kNormThreads) {
+            float value;
+            if (residual) {
+                value = __fadd_rn(__ldcg(add_a + base + col), __ldcg(add_b + base + col));
+                input[base + col] = value;
+            } else {
+                value = __ldcg(input + base + col);
+            }
+            sum = __fadd_rn(sum, __fmul_rn(value, value));
+        }
     }
     partial[lane] = sum;
     __syncthreads();
@@ -1253,9 +1284,8 @@ __global__ void __launch_bounds__(kNormThreads) norm_stage_kernel(const float* _
         __syncthreads();
     }
     const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(partial[0], static_cast<float>(cols)), epsilon)));
-    for (uint32_t col = lane; col < cols; col += kNormThreads) {
-        // this thread wrote input[base + col] itself when there is a residual
-        const float y = __fmul_rn(__fmul_rn(input[base + col], scale), __ldg(weight + col));
+    auto emit = [&](uint32_t col, float value, float w) {
+        const float y = __fmul_rn(__fmul_rn(value, scale), w);
         output[base + col] = y;
         const __nv_bfloat16 rounded = __float2bfloat16_rn(y);
         staged[base + col] = rounded;
@@ -1265,6 +1295,16 @@ __global__ void __launch_bounds__(kNormThreads) norm_stage_kernel(const float* _
         const uint32_t kstep = col >> 4, inner = col & 15;
         const uint32_t word = ((kstep >> 1) * 32 + blockIdx.x * 4 + ((inner & 7) >> 1)) * 4 + (kstep & 1) * 2 + (inner >> 3);
         fragments[word * 2 + (inner & 1)] = static_cast<uint16_t>(shift_bf16(__bfloat16_as_ushort(rounded), kFixedStageShift));
+    };
+    if (held_row) {
+#pragma unroll
+        for (uint32_t i = 0; i < kNormHeld; ++i) {
+            const uint32_t col = lane + i * kNormThreads;
+            if (col < cols) emit(col, held[i], gain[i]);
+        }
+    } else {
+        // this thread wrote input[base + col] itself when there is a residual
+        for (uint32_t col = lane; col < cols; col += kNormThreads) emit(col, input[base + col], __ldg(weight + col));
     }
 }
 

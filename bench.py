@@ -23,7 +23,8 @@ and the result read back for every pass. The other configurations of the benchma
 reported under their own keys of the same line, each outside the headline's timed region:
 `config0` (single 17408 x 5120 linear, M=8), `config1_m1` (the MLP block at M=1), `config1_other_kernel`
 (the block on the small-token kernel that the headline does not use), `config2_prefill` (M=4096 GEMMs), `config3_sweep` (64-layer whole-model linear
-sweep at M=8), `config4_prefill_mlp` (chunked tensor-parallel prefill MLP), `head_bf16` (the BF16 vocabulary head).
+sweep at M=8), `config4_prefill_mlp` (chunked tensor-parallel prefill MLP), `head_bf16` (the BF16 vocabulary head),
+`norm_group` (RMSNorm + stage + four projections of one input, grouped against one launch per projection).
 """
 from __future__ import annotations
 
@@ -553,6 +554,68 @@ SWEEP_LAYERS = 64
 SWEEP_SHAPES = ((10240, 5120, "column"), (5120, 5120, "column"), (5120, 10240, "row"))   # rows, cols, how it shards
 
 
+def norm_group_probe(ctx):
+    """The GDN-input group at M=8: RMSNorm -> BF16 stage -> four projections of the same input (10240, 6144 and two
+    48-row gates held as 64 weight rows), eight distinct groups in rotation (381 MB of weights, more than L2). Timed
+    as the grouped program (norm stage + one grid for all members: 2 launches) and as the norm stage with one launch
+    per projection (5 launches), which is how the members run when they are not grouped."""
+    import oracle
+    from augur_v100_b200 import synth
+    torch, host, abi = ctx.torch, ctx.host, ctx.abi
+    generator = torch.Generator(device=ctx.device)
+    generator.manual_seed(4242)
+    cols, count = HIDDEN, 8
+    shapes, stored = [(10240, cols), (6144, cols), (64, cols), (64, cols)], [0, 0, 48, 48]
+    plan = host.Plan(ctx.stream, 64 << 20)   # the group's members take their partial-sum regions side by side
+    norm_weight = 1.0 + 0.1 * torch.randn((cols,), device=ctx.device, generator=generator)
+    x = 3.0 * torch.randn((TOKENS, cols), device=ctx.device, generator=generator)
+    grouped, separate, first = [], [], None
+    for index in range(count):
+        weights = []
+        for rows, _ in shapes:
+            codes, scales = device_planes(torch, generator, rows, cols, ctx.device)
+            weights.append(host.Nvfp4Sm100Weight.repack_device_planes(ctx.stream, abi.LAYOUT_STREAM, rows, cols, codes, scales,
+                                                                      synth.GLOBAL_SCALE))
+            if index == 0 and rows == shapes[0][0]:
+                first = (codes.cpu().numpy(), scales.cpu().numpy())
+            del codes, scales
+        grouped.append(host.Nvfp4Sm100NormGroupProgram.bind(plan, weights, x, norm_weight, stored_rows=stored))
+        lone = host.Nvfp4Sm100NormGroupProgram.bind(plan, weights[:1], x, norm_weight)
+        separate.append([lone] + [host.Nvfp4Sm100Projection.bind(plan, weight, lone.staged) for weight in weights[1:]])
+
+    def run_grouped():
+        for program in grouped:
+            program.submit_for_plan()
+
+    def run_separate():
+        for members in separate:
+            for member in members:
+                member.submit_for_plan()
+
+    weight_bytes = sum(rows * cols * 9 // 16 for rows, _ in shapes)
+    rounds, results = 50, {}
+    for label, body in (("grouped", run_grouped), ("one_launch_per_projection", run_separate)):
+        for _ in range(3):
+            body()
+        launches_before = host.launch_count()
+        ms = ctx.timed(body, rounds) / (rounds * count)
+        results[label] = ctx.hbm_entry(weight_bytes, weight_bytes, ms)
+        results[label]["launches"] = (host.launch_count() - launches_before) // (rounds * count)
+    entry = results["grouped"]
+    entry["one_launch_per_projection"] = results["one_launch_per_projection"]
+    entry["workload"] = (f"norm group (GDN input): RMSNorm + BF16 stage + projections {[rows for rows, _ in shapes]} x {cols} "
+                         f"(gates stored as 48 rows), M={TOKENS}; {count} distinct groups in rotation; bytes = weight bytes")
+    grouped[0].submit_for_plan()
+    ctx.stream.synchronize()
+    y64 = oracle.linear_f64(first[0], first[1], synth.GLOBAL_SCALE, shapes[0][0], cols, bits(grouped[0].staged), threads=oracle.max_threads())
+    entry["parity"] = {"first_member_rel_error_vs_fp64_oracle_same_staged_activations": rel_error(bits(grouped[0].outputs[0]), y64),
+                       "bound": 2e-2}
+    entry["device_status"] = plan.device_status()
+    del grouped, separate
+    plan.close()
+    return entry
+
+
 def sweep_probe(ctx, exchange, kernel):
     """Configuration 3: 64 layers, each the MLP block plus the projections 5120 -> 10240, 5120 -> 5120 and
     10240 -> 5120, all NVFP4 at M=8. With N > 1 the first two are column-parallel (row slices, outputs stay
@@ -832,7 +895,7 @@ def run_library(args):
         if world == 1:
             other = "mma_sync" if tensor_memory else "tensor_memory"
             for key, probe in (("config0", config0_probe), ("config1_other_kernel", lambda c: other_kernel_probe(c, other)),
-                               ("config2_prefill", prefill_probe), ("head_bf16", head_probe)):
+                               ("config2_prefill", prefill_probe), ("head_bf16", head_probe), ("norm_group", norm_group_probe)):
                 try:
                     extras[key] = probe(ctx)
                 except Exception as error:
