@@ -86,6 +86,19 @@ class Bf16HeadArgs(Structure):
                 ("rows", c_uint32), ("cols", c_uint32)]
 
 
+class TcStep(Structure):
+    _fields_ = [(name, c_uint32) for name in ("phase", "job", "tile0", "tiles", "kb0", "kb1", "parts", "slot0", "feeds", "keeps")]
+
+
+class TcJob(Structure):
+    _fields_ = [("phase", c_uint32), ("group0", c_uint32), ("groups", c_uint32)]
+
+
+class TcProgram(Structure):
+    _fields_ = [("steps", c_uint32), ("jobs", c_uint32), ("ctas", c_uint32), ("contributors", c_uint32 * 2),
+                ("step", TcStep * 4), ("job", TcJob * 3)]
+
+
 class MlpArgs(Structure):
     _fields_ = [("abi_version", c_uint32), ("struct_size", c_uint32),
                 ("gate_up", GemvArgs), ("down", GemvArgs)]
@@ -185,6 +198,8 @@ EXPORTS = {
     "augur_cuda_nvfp4_sm100_gemv_bf16_preflight_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(GemvArgs)]),
     "augur_cuda_nvfp4_sm100_gemv_bf16_prevalidated_submit_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(GemvArgs)]),
     "augur_cuda_nvfp4_sm100_gemv_tc_scratch_extent_host_v1": (Result, [c_uint32, c_uint32, c_uint32, POINTER(c_uint64)]),
+    "augur_cuda_nvfp4_sm100_tc_program_describe_host_v1": (Result, [c_uint32, c_uint32, c_uint32, c_uint32, c_uint32, c_uint32,
+                                                                     POINTER(TcProgram)]),
     "augur_cuda_nvfp4_sm100_gemv_tc_bf16_preflight_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(GemvArgs)]),
     "augur_cuda_nvfp4_sm100_gemv_tc_bf16_prevalidated_submit_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(GemvArgs)]),
     "augur_cuda_nvfp4_sm100_mlp_tc_preflight_v1": (Result, [c_int32, c_void_p, c_void_p, POINTER(MlpArgs)]),

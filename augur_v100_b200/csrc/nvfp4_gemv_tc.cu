@@ -1222,6 +1222,43 @@ extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_tc_s
     return ok();
 }
 
+static_assert(kMaxSteps == 4 && kMaxJobs == 3 && kMaxPhases == 2, "the described program has the kernel's bounds");
+
+extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_tc_program_describe_host_v1(
+    uint32_t rows_a, uint32_t cols_a, uint32_t epilogue_a, uint32_t rows_b, uint32_t cols_b, uint32_t sm_count,
+    augur_cuda_nvfp4_sm100_tc_program_v1* out) {
+    if (!out || !sm_count || sm_count > 512) return invalid();
+    // the scalar rules of the entries, on the fields that shape the program
+    augur_cuda_nvfp4_sm100_gemv_args_v1 a{}, b{};
+    a.rows = rows_a;
+    a.cols = cols_a;
+    a.epilogue = rows_b ? static_cast<uint32_t>(AUGUR_NVFP4_SM100_EPILOGUE_SWIGLU_BF16) : epilogue_a;
+    b.rows = rows_b;
+    b.cols = cols_b;
+    b.epilogue = AUGUR_NVFP4_SM100_EPILOGUE_LINEAR_BF16;
+    for (const augur_cuda_nvfp4_sm100_gemv_args_v1* m : {&a, &b}) {
+        if (m == &b && !rows_b) break;
+        const uint64_t physical = physical_rows_of(m);
+        if (m->epilogue > AUGUR_NVFP4_SM100_EPILOGUE_LINEAR_F32 || !m->rows || !m->cols || m->rows > (1u << 30) ||
+            physical % kTileM != 0 || m->cols % 64 != 0 || physical * m->cols > UINT32_MAX || physical / kTileM * 8 > kMaxGroups) {
+            return invalid();
+        }
+    }
+    if (rows_b && (cols_b != rows_a || rows_b != cols_a)) return invalid();   // the second product consumes the first's outputs
+    const TcProgram g = tc_program(&a, rows_b ? &b : nullptr, sm_count);
+    *out = augur_cuda_nvfp4_sm100_tc_program_v1{};
+    out->steps = g.steps;
+    out->jobs = g.jobs;
+    out->ctas = g.ctas;
+    for (uint32_t i = 0; i < kMaxPhases; ++i) out->contributors[i] = g.contributors[i];
+    for (uint32_t i = 0; i < g.steps; ++i) {
+        const TcStep& st = g.step[i];
+        out->step[i] = {st.phase, st.job, st.tile0, st.tiles, st.kb0, st.kb1, st.parts, st.slot0, st.feeds, st.keeps};
+    }
+    for (uint32_t i = 0; i < g.jobs; ++i) out->job[i] = {g.job[i].phase, g.job[i].group0, g.job[i].groups};
+    return ok();
+}
+
 extern "C" augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_gemv_tc_bf16_preflight_v1(
     int32_t d, augur_cuda_stream_t s, augur_cuda_nvfp4_sm100_plan_v1* plan, const augur_cuda_nvfp4_sm100_gemv_args_v1* a) {
     augur_cuda_result_v1 failure;

@@ -350,6 +350,33 @@ augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_mlp_tc_prevalidated_
     int32_t ordinal, augur_cuda_stream_t stream, augur_cuda_nvfp4_sm100_plan_v1* plan,
     const augur_cuda_nvfp4_sm100_mlp_args_v1* args);
 
+/* How a tensor-memory launch is laid out on a device with `sm_count` SMs: a host-side computation (no device
+ * access, no allocation) for diagnostics and for tests of the split. A launch is a list of steps; a step is a set
+ * of items (tile, part) dealt round-robin over the CTAs (item i goes to CTA i mod ctas): tiles [tile0, tile0 + tiles)
+ * of 128 physical weight rows of product `phase`, each over the 256-deep k blocks [kb0, kb1) cut into `parts` equal
+ * ranges (part p: [kb0 + p * (kb1 - kb0) / parts, kb0 + (p + 1) * (kb1 - kb0) / parts)); the partial sums of a tile
+ * meet in contributor slots slot0 + part of `contributors[phase]`. Its activations are job `job`: the 16-element
+ * groups [group0, group0 + groups) of every token row of the input of product `phase`, split inside the launch;
+ * `feeds` names the job that this step's outputs become (0: none), `keeps` says that every CTA has at most one item
+ * of the step and splits its own outputs from registers. `rows_b` = 0 describes a linear (`epilogue_a` as in the
+ * gemv arguments, `rows_a` logical rows), otherwise the MLP block `rows_a` = intermediate, `cols_a` = hidden,
+ * `rows_b` = hidden, `cols_b` = intermediate. */
+typedef struct augur_cuda_nvfp4_sm100_tc_step_v1 {
+    uint32_t phase, job, tile0, tiles, kb0, kb1, parts, slot0, feeds, keeps;
+} augur_cuda_nvfp4_sm100_tc_step_v1;
+typedef struct augur_cuda_nvfp4_sm100_tc_job_v1 {
+    uint32_t phase, group0, groups;
+} augur_cuda_nvfp4_sm100_tc_job_v1;
+typedef struct augur_cuda_nvfp4_sm100_tc_program_v1 {
+    uint32_t steps, jobs, ctas;
+    uint32_t contributors[2];
+    augur_cuda_nvfp4_sm100_tc_step_v1 step[4];
+    augur_cuda_nvfp4_sm100_tc_job_v1 job[3];
+} augur_cuda_nvfp4_sm100_tc_program_v1;
+augur_cuda_result_v1 AUGUR_CUDA_CALL augur_cuda_nvfp4_sm100_tc_program_describe_host_v1(
+    uint32_t rows_a, uint32_t cols_a, uint32_t epilogue_a, uint32_t rows_b, uint32_t cols_b, uint32_t sm_count,
+    augur_cuda_nvfp4_sm100_tc_program_v1* out);
+
 /* ---- norm group: [residual add] -> RMSNorm -> BF16 stage -> 1..4 small-token projections ----- */
 /* Replaces augur_cuda_qwen35_qpn_norm_group_b8_{preflight,prevalidated_submit}_v1
  * (native augur_qwen35_gdn_input_b8.cuh:19-49,50-110): GDN input (norm, then the in-projections)
