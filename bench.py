@@ -736,6 +736,7 @@ def run_library(args):
     outs1 = [torch.empty((1, HIDDEN), dtype=torch.bfloat16, device=device) for _ in range(2)]
     programs_m1 = [program_type.bind(plan, gate_up, down, x1, out=outs1[index % 2])
                    for index, (gate_up, down) in enumerate(layers)]
+    shard_programs = programs    # this rank's shard without any exchange (the same objects the exchange wraps)
 
     # With more than one rank the all-reduce is fused into the down launch (peer stores over NVLink);
     # --allreduce nccl, or a failed symmetric-memory set-up (reported in the line), uses NCCL instead.
@@ -855,6 +856,23 @@ def run_library(args):
     per_gpu_m1 = 3 * HIDDEN * (INTER // world) * 9 // 16 + 2 * HIDDEN * 2
     extras["config1_m1"] = ctx.hbm_entry(per_gpu_m1, layer_bytes(1), m1_ms)
     extras["config1_m1"]["workload"] = f"config1 at M=1: the same {LAYERS} layers, one token row; ms per layer"
+
+    if world > 1:
+        # What the exchange costs: the same layers with every rank running its shard alone (no exchange, outputs are
+        # partial sums), beside the headline's time per layer, which has the exchange and the wait for the slowest rank.
+        def shard_pass():
+            for program in shard_programs:
+                program.submit_for_plan()
+
+        for _ in range(3):
+            shard_pass()
+        shard_ms = ctx.timed(shard_pass, reps) / (reps * LAYERS)
+        with_exchange_ms = total_ms / (args.steps * PASSES * LAYERS)
+        extras["config1_shard_without_exchange"] = {
+            "ms_per_layer": shard_ms, "ms_per_layer_with_exchange": with_exchange_ms,
+            "exchange_and_rank_skew_ms": with_exchange_ms - shard_ms,
+            "workload": f"config1, tp{world}: each rank's shard of the {LAYERS} layers with no exchange (max over ranks), "
+                        "beside the headline's time per layer"}
 
     # parity of the timed programs against the CPU oracle (one GPU: the first layer, both token counts)
     parity = None
