@@ -870,7 +870,7 @@ def run_library(args):
         with_exchange_ms = total_ms / (args.steps * PASSES * LAYERS)
         extras["config1_shard_without_exchange"] = {
             "ms_per_layer": shard_ms, "ms_per_layer_with_exchange": with_exchange_ms,
-            "exchange_and_rank_skew_ms": with_exchange_ms - shard_ms,
+            "exchange_and_rank_skew_ms": with_exchange_ms - shard_ms, "device_status": plan.device_status(),
             "workload": f"config1, tp{world}: each rank's shard of the {LAYERS} layers with no exchange (max over ranks), "
                         "beside the headline's time per layer"}
 
