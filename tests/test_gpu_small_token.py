@@ -526,6 +526,33 @@ def test_norm_group_program(ctx, residual):
         assert rel_error(bits_from_torch_bf16(out), np.ascontiguousarray(y64[:, :keep]) if keep else y64) <= TOLERANCE
 
 
+@pytest.mark.parametrize("cols", [256, 6144, 6400])
+def test_norm_stage_row_widths(ctx, cols):
+    # rows up to 6144 columns are held in registers by the norm stage, wider ones take the looping path: the same bits
+    host, torch = ctx["host"], ctx["torch"]
+    tokens, eps, rows = 5, 1e-5, 64
+    rng = np.random.default_rng(cols)
+    a = rng.standard_normal((tokens, cols)).astype(np.float32) * 2
+    b = rng.standard_normal((tokens, cols)).astype(np.float32)
+    norm_weight = (1.0 + 0.1 * rng.standard_normal(cols)).astype(np.float32)
+    codes, scales, glob = synth.make_weight(9, 65, "w", rows, cols)
+    weight = host.Nvfp4Sm100Weight.upload_checkpoint_nvfp4(ctx["stream"], abi.LAYOUT_STREAM, rows, cols, codes, scales, glob)
+    device = ctx["device"]
+    for residual in (False, True):
+        x_dev = torch.zeros((tokens, cols), dtype=torch.float32, device=device) if residual else torch.from_numpy(a).to(device)
+        extra = (torch.from_numpy(a).to(device), torch.from_numpy(b).to(device)) if residual else ()
+        program = host.Nvfp4Sm100NormGroupProgram.bind(ctx["plan"], [weight], x_dev, torch.from_numpy(norm_weight).to(device), eps, *extra)
+        program.submit_for_plan()
+        ctx["stream"].synchronize()
+        assert ctx["plan"].device_status() == 0
+        want_x, want_y, want_staged = oracle.rmsnorm_stage(None, norm_weight, eps, a, b) if residual else oracle.rmsnorm_stage(a, norm_weight, eps)
+        assert np.array_equal(x_dev.cpu().numpy().view(np.uint32), want_x.view(np.uint32))
+        assert np.array_equal(program.normalised.cpu().numpy().view(np.uint32), want_y.view(np.uint32))
+        assert np.array_equal(bits_from_torch_bf16(program.staged).reshape(want_staged.shape), want_staged)
+        y64 = oracle.linear_f64(codes, scales, glob, rows, cols, want_staged, threads=oracle.max_threads())
+        assert rel_error(bits_from_torch_bf16(program.outputs[0]), y64) <= TOLERANCE
+
+
 def test_norm_group_rejects_inconsistent_members(ctx):
     host, torch = ctx["host"], ctx["torch"]
     tokens, cols = 4, 512
