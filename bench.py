@@ -24,7 +24,8 @@ reported under their own keys of the same line, each outside the headline's time
 `config0` (single 17408 x 5120 linear, M=8), `config1_m1` (the MLP block at M=1), `config1_other_kernel`
 (the block on the small-token kernel that the headline does not use), `config2_prefill` (M=4096 GEMMs), `config3_sweep` (64-layer whole-model linear
 sweep at M=8), `config4_prefill_mlp` (chunked tensor-parallel prefill MLP), `head_bf16` (the BF16 vocabulary head),
-`norm_group` (RMSNorm + stage + four projections of one input, grouped against one launch per projection).
+`norm_group` (RMSNorm + stage + four projections of one input, grouped against one launch per projection); with more than
+one GPU also `config1_shard_without_exchange` (every rank's shard of the block alone: what the exchange and rank skew cost).
 """
 from __future__ import annotations
 
